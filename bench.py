@@ -1,0 +1,424 @@
+"""Benchmark of the quantized-matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl qx|reference]
+
+Headline workload (N = 1): the 4-bit block GEMV at FFN-up shape -- M=1, K=4096 f32
+activations ~N(0,1), N=14336 x K=4096 q4_0 weights (33 MB) -- measured as achieved HBM
+GB/s: algorithmic bytes (packed weights + activations read + outputs written) / time.
+A step is one GEMV call. The weights fit in L2, so the timed loop rotates over several
+distinct weight copies whose total size exceeds L2 (stated in `config`). With N > 1 every
+rank holds one such shard of an (N*14336) x 4096 matrix (weak scaling), computes its
+output slice and all ranks exchange slices (all-gather), as the sharded configurations of
+this path do.
+
+Prints ONE JSON line (rank 0). `value` is timed with inputs resident in HBM, `e2e` through
+the host-pointer C entry point with pinned host buffers (host<->device copies inside the
+timed region), `cpu_baseline` is the reference's CPU path on this host's cores on a
+bounded sample, `roofline` relates the step to the measured HBM copy bandwidth.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+METRIC = "decode GEMV achieved HBM GB/s"
+WORKLOAD = "cfg1_q4_0_gemv"
+GRAPH_CHUNK = 100
+
+
+def load_workloads():
+    return entry._load_file(entry.PKG_NAME + ".workloads", os.path.join(entry.PKG_DIR, "workloads.py"))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            data = json.load(f)
+        return float(data["hbm_gbs"]), float(data.get("bf16_tflops", 0.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and clock-event reasons through NVML (read-only) while a region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, device_index: int, period_s: float = 0.004):
+        super().__init__(daemon=True)
+        self.period = period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(device_index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.ok = False
+
+    def _one(self):
+        nv = self.nv
+        self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+        try:
+            mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+        except Exception:
+            mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+        for bit, name in self.REASONS.items():
+            if mask & bit:
+                self.reasons.add(name)
+
+    def run(self):
+        if not self.ok:
+            return
+        while not self._halt.is_set():
+            try:
+                self._one()
+            except Exception:
+                break
+            time.sleep(self.period)
+
+    def stop(self):
+        self._halt.set()
+        if self.is_alive():
+            self.join()
+        if self.ok and not self.samples:
+            try:
+                self._one()
+            except Exception:
+                pass
+        return {
+            "sm_mhz": statistics.median(self.samples) if self.samples else None,
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.samples),
+        }
+
+
+# ---------------------------------------------------------------------------------------
+# CPU arm: the reference's own implementation on the host cores
+# ---------------------------------------------------------------------------------------
+
+def cpu_engine():
+    """(kind, call, threads): the built reference library when present, else the oracle port."""
+    oracle_mod = entry.load_oracle()
+    threads = os.cpu_count() or 1
+    if oracle_mod.Reference.available():
+        ref = oracle_mod.Reference()
+        ref.set_num_threads(threads)
+        return "reference", ref, threads, ref.variants()
+    return "port", oracle_mod.Oracle(), 1, {}
+
+
+def time_cpu_gemv(engine_kind, engine, fmt, packed, x, n, k, budget_s, max_calls):
+    """Median seconds per call of the CPU GEMV over rows [0, n); at least 3 calls."""
+    def call():
+        if engine_kind == "reference":
+            return engine.qgemv(fmt, packed, x, n, k)
+        return engine.qgemv(fmt, packed, x, n, k, 0)
+    call()
+    times, start = [], time.perf_counter()
+    while len(times) < max_calls and (len(times) < 3 or time.perf_counter() - start < budget_s):
+        t0 = time.perf_counter()
+        call()
+        times.append(time.perf_counter() - t0)
+    return statistics.median(times), len(times)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = load_workloads()
+    c = wl.CONFIGS[WORKLOAD]
+    fmt, n, k = c["fmt"], c["n"], c["k"]
+    packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0)
+    x = wl.activations_f32(1, k, seed=0)[0].copy()
+    kind, engine, threads, variants = cpu_engine()
+
+    def call(rows):
+        if kind == "reference":
+            engine.qgemv(fmt, packed, x, rows, k)
+        else:
+            engine.qgemv(fmt, packed, x, rows, k, 0)
+    # bound the run to about two minutes: shrink the per-step row sample if needed
+    call(n)
+    t0 = time.perf_counter()
+    for _ in range(3):
+        call(n)
+    per_call = (time.perf_counter() - t0) / 3
+    rows = n
+    total_steps = args.steps + args.warmup
+    if per_call * total_steps > 120.0:
+        rows = int(max(32 * threads, min(n, n * 120.0 / (per_call * total_steps))))
+        rows -= rows % 32
+        rows = max(rows, 32)
+    for _ in range(args.warmup):
+        call(rows)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        call(rows)
+    elapsed = time.perf_counter() - t0
+    step_bytes = wl.algorithmic_bytes_qgemv(fmt, 1, rows, k)
+    value = step_bytes * args.steps / elapsed / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "m": 1, "n": n, "k": k, "format": "q4_0",
+                   "rows_per_step": rows, "variants": variants},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind,
+                         "sample": f"{args.steps} calls of the reference qgemv over {rows} of {n} rows"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------
+
+def run_qx_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    qx = entry.load_package()
+    wl = load_workloads()
+    c = wl.CONFIGS[WORKLOAD]
+    fmt, n, k = c["fmt"], c["n"], c["k"]
+    step_bytes = wl.algorithmic_bytes_qgemv(fmt, 1, n, k)
+    hbm_peak, bf16_peak, peak_kind = measured_peaks()
+    info = qx.device_info()
+
+    # distinct weight copies whose total size exceeds L2, rotated step by step
+    copies = max(2, -(-2 * info["l2_bytes"] // (n * (k // 32) * 18)))
+    handles = []
+    for i in range(copies):
+        packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=rank * 1000 + i)
+        h = qx.PackedWeights()
+        qx.check(h.prepare(fmt, packed, n, k), "qx_weights_prepare")
+        handles.append(h)
+    x_host = wl.activations_f32(1, k, seed=0)
+    x_dev = torch.from_numpy(x_host).cuda()
+    y_full = torch.zeros(world * n, device="cuda")
+    y_local = y_full[rank * n:(rank + 1) * n]
+
+    def step(i):
+        qx.check(handles[i % copies].qgemm_dev(x_dev, y_local, 1, n), "qx_qgemm_prepacked_dev")
+        if world > 1:
+            dist.all_gather_into_tensor(y_full, y_local)
+
+    launches0 = qx.launch_count()
+    step(0)
+    launches_per_step = qx.launch_count() - launches0
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+
+    graph = None
+    chunk = GRAPH_CHUNK - GRAPH_CHUNK % copies or copies
+    if world == 1 and args.steps >= chunk:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(chunk):
+                step(i)
+        graph.replay()
+        torch.cuda.synchronize()
+
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    done = 0
+    if graph is not None:
+        while done + chunk <= args.steps:
+            graph.replay()
+            done += chunk
+    for i in range(done, args.steps):
+        step(i)
+    stop.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    elapsed_ms = start.elapsed_time(stop)
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([elapsed_ms], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms = float(t.item())
+    value = step_bytes * world * args.steps / (elapsed_ms * 1e-3) / 1e9
+
+    # end to end through the host-pointer entry point: pinned x in, pinned y out, every step
+    x_pin = torch.from_numpy(x_host).pin_memory()
+    y_pin = torch.zeros(n).pin_memory()
+    e2e_steps = max(10, min(args.steps, 2000))
+    for i in range(3):
+        qx.check(handles[i % copies].qgemm_prepacked_ptr(x_pin.data_ptr(), y_pin.data_ptr(), 1), "e2e")
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        qx.check(handles[i % copies].qgemm_prepacked_ptr(x_pin.data_ptr(), y_pin.data_ptr(), 1), "e2e")
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e_value = step_bytes * world * e2e_steps / e2e_s / 1e9
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    per_launch_gbs = step_bytes * args.steps / (elapsed_ms * 1e-3) / 1e9  # this rank's GPU
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "m": 1, "n": n, "k": k, "format": "q4_0",
+                   "sharding": f"rows x{world}" if world > 1 else "none",
+                   "l2_policy": f"rotates {copies} distinct weight copies "
+                                f"({copies * n * (k // 32) * 18 / 1e6:.0f} MB > L2 {info['l2_bytes'] / 1e6:.0f} MB)",
+                   "cuda_graph": graph is not None, "variants": qx.variants()},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k,
+                "d2h_bytes_per_step": 4 * n, "steps": e2e_steps},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": {"bound": "hbm", "achieved": per_launch_gbs, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": per_launch_gbs / hbm_peak, "traffic": None,
+                     "peak_source": f"{peak_kind} HBM copy bandwidth",
+                     "frac_of_nominal_8TBs": per_launch_gbs / 8000.0,
+                     "note": "achieved = algorithmic bytes / whole step time (activation "
+                             "quantizer launch and launch gaps included)"},
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(wl, c)
+        try:
+            line["extra"] = extra_measurements(qx, wl, torch, hbm_peak)
+        except Exception as exc:  # the headline line must still be printed
+            line["extra"] = {"error": repr(exc)}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(wl, c):
+    fmt, n, k = c["fmt"], c["n"], c["k"]
+    packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0)
+    x = wl.activations_f32(1, k, seed=0)[0].copy()
+    kind, engine, threads, variants = cpu_engine()
+    seconds, calls = time_cpu_gemv(kind, engine, fmt, packed, x, n, k, budget_s=10.0, max_calls=4000)
+    return {"value": wl.algorithmic_bytes_qgemv(fmt, 1, n, k) / seconds / 1e9, "unit": "GB/s",
+            "cores": threads, "kind": kind, "ms_per_call": seconds * 1e3,
+            "sample": f"median of {calls} full-size qgemv calls ({n}x{k} q4_0)", "variants": variants}
+
+
+def _time_calls(torch, fn, iters, warm=3):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e-3
+
+
+def extra_measurements(qx, wl, torch, hbm_peak):
+    """The other benchmark configurations on one GPU (not the headline; explanatory)."""
+    out = {}
+    # cfg2: W8A8 prefill GEMM, TOPS
+    c = wl.CONFIGS["cfg2_w8a8_gemm"]
+    m, n, k = c["m"], c["n"], c["k"]
+    w, x, ws, xs = wl.w8a8_inputs(m, n, k, seed=0)
+    dev = [torch.from_numpy(a).cuda() for a in (w, x, ws, xs)]
+    y = torch.zeros((m, n), device="cuda")
+    sec = _time_calls(torch, lambda: qx.check(qx.int8_gemm_dev(*dev, y, m, n, k), "int8"), 50)
+    out["cfg2_w8a8_gemm"] = {"tops": 2.0 * m * n * k / sec / 1e12, "us": sec * 1e6,
+                             "frac_of_nominal_4500_tops": 2.0 * m * n * k / sec / 4.5e15,
+                             "variant": qx.variants()["int8_gemm"]}
+    del dev, y
+    # cfg0: q8_0 GEMV 4096x4096 (rotating copies beyond L2)
+    c = wl.CONFIGS["cfg0_q8_0_gemv"]
+    fmt, n, k = c["fmt"], c["n"], c["k"]
+    handles = []
+    for i in range(16):
+        h = qx.PackedWeights()
+        qx.check(h.prepare(fmt, wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=i), n, k), "prep")
+        handles.append(h)
+    xd = torch.from_numpy(wl.activations_f32(1, k)).cuda()
+    yd = torch.zeros(n, device="cuda")
+    state = {"i": 0}
+
+    def gemv():
+        qx.check(handles[state["i"] % 16].qgemm_dev(xd, yd, 1, n), "gemv")
+        state["i"] += 1
+    sec = _time_calls(torch, gemv, 400)
+    out["cfg0_q8_0_gemv"] = {"gbs": wl.algorithmic_bytes_qgemv(fmt, 1, n, k) / sec / 1e9, "us": sec * 1e6}
+    for h in handles:
+        h.reset()
+    # cfg3: batched q8_0 GEMV, 240 MB of weights (> L2), M sweep
+    c = wl.CONFIGS["cfg3_q8_0_batched"]
+    fmt, n, k = c["fmt"], c["n"], c["k"]
+    h = qx.PackedWeights()
+    qx.check(h.prepare(fmt, wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0), n, k), "prep")
+    sweep = {}
+    for m in c["m_sweep"]:
+        xd = torch.from_numpy(wl.activations_f32(m, k)).cuda()
+        yd = torch.zeros((m, n), device="cuda")
+        sec = _time_calls(torch, lambda: qx.check(h.qgemm_dev(xd, yd, m, n), "gemm"), 20 if m == 1 else 5, 2)
+        gbs = wl.algorithmic_bytes_qgemv(fmt, m, n, k) / sec / 1e9
+        sweep[f"m{m}"] = {"gbs": gbs, "us": sec * 1e6, "frac_of_measured_hbm": gbs / hbm_peak}
+    out["cfg3_q8_0_batched"] = sweep
+    h.reset()
+    return out
+
+
+def main():
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=20000)
+    parser.add_argument("--warmup", type=int, default=200)
+    parser.add_argument("--impl", default="qx", choices=["qx", "reference"])
+    args = parser.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "qx" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_qx_arm(args)
+
+
+if __name__ == "__main__":
+    main()

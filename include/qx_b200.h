@@ -1,0 +1,220 @@
+/*
+ * qx_b200 -- C ABI of the B200 (sm_100a) implementation of the QuixiCore-CPU quantized
+ * matmul hot path: q8_0 / q4_0 GEMV and batched qgemm, W8A8 int8 GEMM, W8A32 GEMM and
+ * prepared (device-resident) packed weights.
+ *
+ * Every entry point below is the binding target for one public function of the
+ * reference's `quixicore_cpu::` namespace; the comment above each declaration names the
+ * reference declaration (file:line inside the reference project) it replaces. Argument
+ * order, meaning, validation order and returned status values follow the reference.
+ * Plain pointers and sizes only; no C++ or torch types cross this boundary.
+ *
+ * Pointer conventions
+ *   - entry points WITHOUT a suffix take HOST pointers, copy inputs to the GPU, run the
+ *     kernel on the library's own stream and copy the result back before returning
+ *     (drop-in semantics of the reference: synchronous, caller owns every buffer);
+ *   - entry points ending in `_dev` take DEVICE pointers and a `cudaStream_t` passed as
+ *     `void*`; they enqueue work and return without synchronising.
+ *
+ * There is no CPU fallback: without a usable sm_100 device every compute entry point
+ * returns QX_STATUS_DEVICE_ERROR.
+ */
+#ifndef QX_B200_H_
+#define QX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+/* Every entry point is exported with default visibility; the library itself is built
+ * with hidden visibility so nothing else leaks. */
+#if defined(_WIN32)
+#define QX_API __declspec(dllexport)
+#else
+#define QX_API __attribute__((visibility("default")))
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* quixicore_cpu::Status, include/quixicore_cpu/status.h:5-11 (values 0..4 identical).
+ * QX_STATUS_DEVICE_ERROR is additive: a CUDA runtime / driver call failed or no
+ * sm_100 device is present. qx_last_error_string() describes the failure. */
+typedef enum qx_status {
+  QX_STATUS_OK = 0,
+  QX_STATUS_INVALID_SHAPE = 1,
+  QX_STATUS_UNSUPPORTED_FORMAT = 2,
+  QX_STATUS_INVALID_ARGUMENT = 3,
+  QX_STATUS_OUT_OF_MEMORY = 4,
+  QX_STATUS_DEVICE_ERROR = 5
+} qx_status;
+
+/* quixicore_cpu::QuantFormat, include/quixicore_cpu/qgemv.h:10-51. Numeric values are
+ * stable; this path implements kQ8_0 (0) and kQ4_0 (1). Every other value is reported
+ * as QX_STATUS_UNSUPPORTED_FORMAT by every entry point. */
+enum { QX_FORMAT_Q8_0 = 0, QX_FORMAT_Q4_0 = 1 };
+
+/* ---- device discovery: replaces quixicore_cpu::cpu_features(),
+ * include/quixicore_cpu/cpu_features.h:13-41 (CPUID probing becomes device / NVLink
+ * discovery). Fills *info for the current CUDA device. */
+typedef struct qx_device_info {
+  int device;               /* CUDA ordinal */
+  int sm_major, sm_minor;   /* compute capability */
+  int sm_count;
+  int max_smem_per_block;   /* opt-in bytes */
+  int l2_bytes;
+  size_t hbm_bytes;
+  int visible_devices;      /* CUDA devices visible to this process */
+  int peer_access_mask;     /* bit i set: this device can map device i's memory */
+  char name[64];
+} qx_device_info;
+QX_API qx_status qx_device_query(qx_device_info* info);
+QX_API const char* qx_last_error_string(void);
+
+/* ---- sizes, authoring ---------------------------------------------------------- */
+
+/* qgemv_packed_size, include/quixicore_cpu/qgemv.h:70-71 (src/dispatch/qgemv.cpp:198-208) */
+QX_API qx_status qx_qgemv_packed_size(int format, long long n, long long k, size_t* size);
+/* qgemv_pack, include/quixicore_cpu/qgemv.h:77-78 (src/dispatch/qgemv.cpp:210-275):
+ * quantise row-major f32 weights [n,k] into packed blocks. Host pointers. */
+QX_API qx_status qx_qgemv_pack(int format, const float* weights, long long n, long long k,
+                        void* packed);
+/* qgemv_unpack, include/quixicore_cpu/qgemv.h:89-90 (src/dispatch/qgemv.cpp:277-300) */
+QX_API qx_status qx_qgemv_unpack(int format, const void* packed, long long n, long long k,
+                          float* weights);
+
+/* ---- GEMV / batched GEMM over canonical packed bytes (host pointers) ---------------- */
+
+/* qgemv, include/quixicore_cpu/qgemv.h:108-109 (src/dispatch/qgemv.cpp:337-365) */
+QX_API qx_status qx_qgemv(int format, const void* packed, const float* x, float* y,
+                   long long n, long long k);
+/* qgemm, include/quixicore_cpu/qgemm.h:19-20 (kernels/quantization/qgemm_ref.cpp:141-164) */
+QX_API qx_status qx_qgemm(int format, const void* packed_weights, const float* x, float* y,
+                   long long m, long long n, long long k);
+/* qgemv_variant, include/quixicore_cpu/qgemv.h (src/dispatch/qgemv.cpp:392-405): name of
+ * the kernel family that serves the format, "unsupported" otherwise. */
+QX_API const char* qx_qgemv_variant(int format);
+
+/* ---- prepared weights: replaces quixicore_cpu::CpuPackedWeights,
+ * include/quixicore_cpu/packed_weights.h:72-97 (src/memory/packed_weights.cpp:197-278).
+ * The handle owns a device-resident, re-laid-out copy of the canonical bytes (split
+ * planes: block codes and fp16 scales; same total size as the canonical bytes). */
+typedef struct qx_weights qx_weights;
+
+/* CpuPackedWeightsInfo, include/quixicore_cpu/packed_weights.h:36-67 (the fields that
+ * have a device meaning). */
+typedef struct qx_weights_info {
+  int format;
+  long long rows, columns;
+  long long block_size, blocks_per_row;
+  size_t block_bytes;
+  size_t contract_bytes;      /* canonical packed size */
+  size_t prepared_bytes;      /* device bytes held by the handle */
+  double memory_amplification;
+  uint64_t preparation_ns;
+  int device;
+  int has_dense_bf16;         /* 1 after the first prefill GEMM built its fp16 tile cache */
+} qx_weights_info;
+
+/* CpuPackedWeights::prepare(format, contract_packed, rows, columns, layout),
+ * packed_weights.h:82-84. `contract_packed` is a HOST pointer to canonical bytes; they
+ * are copied (the caller may free them). Row range [row_begin, row_begin+row_count) of
+ * the [rows, columns] matrix is kept on the current device: pass 0 / rows for the whole
+ * matrix, or one shard's range when weights are sharded by output row over GPUs. */
+QX_API qx_status qx_weights_prepare(int format, const void* contract_packed, long long rows,
+                             long long columns, long long row_begin, long long row_count,
+                             qx_weights** out);
+/* Same, from canonical bytes already resident on the device (no host copy). */
+QX_API qx_status qx_weights_prepare_dev(int format, const void* contract_packed_dev,
+                                 long long rows, long long columns, long long row_begin,
+                                 long long row_count, void* stream, qx_weights** out);
+/* CpuPackedWeights::info(), packed_weights.h:88 */
+QX_API qx_status qx_weights_get_info(const qx_weights* weights, qx_weights_info* info);
+/* CpuPackedWeights::reset() / destructor, packed_weights.h:75,86 */
+QX_API void qx_weights_destroy(qx_weights* weights);
+
+/* Workspace, include/quixicore_cpu/workspace.h:19-58: reusable scratch arena, here in
+ * device memory. NULL in the calls below selects a per-device default workspace owned
+ * by the library (grown on demand, never shrunk). Calls that share a workspace must be
+ * ordered on one stream. */
+typedef struct qx_workspace qx_workspace;
+QX_API qx_status qx_workspace_create(size_t reserve_bytes, qx_workspace** out);
+QX_API size_t qx_workspace_capacity(const qx_workspace* workspace);
+QX_API void qx_workspace_destroy(qx_workspace* workspace);
+
+/* qgemm_prepacked(weights, x, y, m, workspace), include/quixicore_cpu/qgemm.h:26-27
+ * (kernels/quantization/qgemm_panel.cpp:214-287). x [m, columns] f32, y [m, rows_kept]
+ * f32, HOST pointers; m == 1 is the decode GEMV. */
+QX_API qx_status qx_qgemm_prepacked(const qx_weights* weights, const float* x, float* y,
+                             long long m, qx_workspace* workspace);
+/* Same with DEVICE pointers on `stream`. ldy is the row stride of y in floats (>= rows
+ * kept); pass the full N and an offset pointer to write a shard's slice in place. */
+QX_API qx_status qx_qgemm_prepacked_dev(const qx_weights* weights, const float* x_dev,
+                                 float* y_dev, long long m, long long ldy,
+                                 qx_workspace* workspace, void* stream);
+/* qgemm_prepacked_storage with bf16 input, include/quixicore_cpu/qgemm.h:32-34 restricted
+ * to FloatStorageType::kBF16 input and f32 output: the M >= 64 prefill GEMM. x_bf16_dev
+ * [m, columns] bf16 bits, device pointers. */
+QX_API qx_status qx_qgemm_prepacked_bf16_dev(const qx_weights* weights, const uint16_t* x_bf16_dev,
+                                      float* y_dev, long long m, long long ldy,
+                                      qx_workspace* workspace, void* stream);
+
+/* ---- W8A8 ---------------------------------------------------------------------- */
+
+/* int8_gemm, include/quixicore_cpu/qgemm.h:235-239 (src/dispatch/int8_gemm.cpp:67-94).
+ * W [n,k] int8, X [m,k] int8, Y [m,n] f32 = float(acc) * weight_scale[o] *
+ * activation_scale[r], acc exact. HOST pointers. */
+QX_API qx_status qx_int8_gemm(const int8_t* weights, const int8_t* x, const float* weight_scale,
+                       const float* activation_scale, const int32_t* weight_row_sum,
+                       const int* activation_zero_point, float* y, long long m,
+                       long long n, long long k, int asymmetric);
+/* qgemm_w8a8, include/quixicore_cpu/qgemm.h:250-252 */
+QX_API qx_status qx_qgemm_w8a8(const int8_t* weights, const int8_t* x, const float* weight_scale,
+                        const float* activation_scale, float* y, long long m,
+                        long long n, long long k);
+/* qgemm_w8a8_azp, include/quixicore_cpu/qgemm.h:253-257 */
+QX_API qx_status qx_qgemm_w8a8_azp(const int8_t* weights, const int8_t* x,
+                            const float* weight_scale, const float* activation_scale,
+                            const int32_t* weight_row_sum, const int* activation_zero_point,
+                            float* y, long long m, long long n, long long k);
+/* int8_gemm_variant, include/quixicore_cpu/qgemm.h:240 */
+QX_API const char* qx_int8_gemm_variant(void);
+/* Device-pointer form. The reference validates that every scale is finite on each call
+ * (src/dispatch/int8_gemm.cpp:78-85); here that scan runs on the device and a non-finite
+ * scale makes the call return QX_STATUS_INVALID_ARGUMENT only when `check_scales` is
+ * non-zero (it costs one small kernel and a 4-byte read-back, i.e. a synchronisation).
+ * ldy: row stride of y in floats. acc_i32_dev (optional, may be NULL) receives the raw
+ * int32 accumulators [m,n] (after the zero-point correction) for bit-exact checks. */
+QX_API qx_status qx_int8_gemm_dev(const int8_t* weights_dev, const int8_t* x_dev,
+                           const float* weight_scale_dev, const float* activation_scale_dev,
+                           const int32_t* weight_row_sum_dev,
+                           const int* activation_zero_point_dev, float* y_dev,
+                           int32_t* acc_i32_dev, long long m, long long n, long long k,
+                           long long ldy, int asymmetric, int check_scales, void* stream);
+
+/* ---- W8A32 --------------------------------------------------------------------- */
+
+/* qgemm_w8a32, include/quixicore_cpu/qgemm.h:244-246 (src/dispatch/w8a32_gemm.cpp:61-73).
+ * HOST pointers. */
+QX_API qx_status qx_qgemm_w8a32(const int8_t* weights, const float* weight_scale, const float* x,
+                         float* y, long long m, long long n, long long k);
+/* qgemm_w8a32_variant, include/quixicore_cpu/qgemm.h:247 */
+QX_API const char* qx_qgemm_w8a32_variant(void);
+QX_API qx_status qx_qgemm_w8a32_dev(const int8_t* weights_dev, const float* weight_scale_dev,
+                             const float* x_dev, float* y_dev, long long m, long long n,
+                             long long k, long long ldy, int check_scales,
+                             qx_workspace* workspace, void* stream);
+
+/* ---- threading: set_num_threads / num_threads, include/quixicore_cpu/threading.h:11-12.
+ * The fork-join pool is replaced by CUDA streams; these are kept so callers link. The
+ * value is stored and returned, results never depend on it. */
+QX_API void qx_set_num_threads(int n);
+QX_API int qx_num_threads(void);
+
+/* Number of kernels this library has launched in the calling process (all streams). */
+QX_API unsigned long long qx_kernel_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QX_B200_H_ */

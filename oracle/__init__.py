@@ -1,0 +1,281 @@
+"""TEST INFRASTRUCTURE ONLY: ctypes bindings of the two CPU checkers.
+
+``Oracle`` binds ``oracle/libqx_oracle.so`` (the plain-C restatement in
+``qx_oracle.c``); ``Reference`` binds ``oracle/_ref/libqx_ref.so`` (the unmodified
+QuixiCore-CPU library built by ``oracle/Makefile``) when that file exists. Only the
+tests, the smoke check and the CPU-baseline legs of the benchmark import this module;
+the product package never does.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ORACLE_SO = os.path.join(HERE, "libqx_oracle.so")
+REF_SO = os.path.join(HERE, "_ref", "libqx_ref.so")
+
+Q8_0, Q4_0 = 0, 1
+BLOCK_BYTES = {Q8_0: 34, Q4_0: 18}
+OK, INVALID_SHAPE, UNSUPPORTED_FORMAT, INVALID_ARGUMENT, OUT_OF_MEMORY = range(5)
+
+_ll = C.c_longlong
+_vp = C.c_void_p
+
+
+def build(reference_root: str = "/root/reference") -> None:
+    """Compile the C restatement, and the reference library when its sources exist."""
+    subprocess.check_call(["make", "-s", "-C", HERE, "oracle"])
+    if os.path.isdir(reference_root):
+        subprocess.check_call(
+            ["make", "-s", "-j8", "-C", HERE, "ref", f"REF={reference_root}"])
+
+
+def _ptr(array):
+    if array is None:
+        return None
+    assert array.flags["C_CONTIGUOUS"]
+    return array.ctypes.data_as(_vp)
+
+
+def packed_size(fmt: int, n: int, k: int) -> int:
+    return n * (k // 32) * BLOCK_BYTES[fmt]
+
+
+class Oracle:
+    """Plain-C restatement (qx_oracle.c)."""
+
+    def __init__(self, path: str = ORACLE_SO):
+        if not os.path.exists(path):
+            build()
+        self.lib = L = C.CDLL(path)
+        L.qxo_fp16_to_fp32.restype = C.c_float
+        L.qxo_fp16_to_fp32.argtypes = [C.c_uint16]
+        L.qxo_fp32_to_fp16.restype = C.c_uint16
+        L.qxo_fp32_to_fp16.argtypes = [C.c_float]
+        L.qxo_float_to_bf16.restype = C.c_uint16
+        L.qxo_float_to_bf16.argtypes = [C.c_float]
+        L.qxo_bf16_to_float.restype = C.c_float
+        L.qxo_bf16_to_float.argtypes = [C.c_uint16]
+        L.qxo_qgemv_packed_size.argtypes = [C.c_int, _ll, _ll, C.POINTER(C.c_size_t)]
+        L.qxo_qgemv_pack.argtypes = [C.c_int, _vp, _ll, _ll, _vp]
+        L.qxo_qgemv_unpack.argtypes = [C.c_int, _vp, _ll, _ll, _vp]
+        L.qxo_qgemv.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll, C.c_int]
+        L.qxo_qgemm.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll, C.c_int]
+        L.qxo_qgemm_f64.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll]
+        L.qxo_int8_gemm.argtypes = [_vp] * 8 + [_ll, _ll, _ll, C.c_int]
+        L.qxo_qgemm_w8a32.argtypes = [_vp] * 4 + [_ll, _ll, _ll]
+        L.qxo_qgemm_w8a32_avx512_order.argtypes = [_vp] * 4 + [_ll, _ll, _ll]
+        L.qxo_qgemm_w8a32_f64.argtypes = [_vp] * 4 + [_ll, _ll, _ll]
+        L.qxo_qgemm_w8a32_f64.restype = None
+        L.qxo_panel_bytes.restype = _ll
+        L.qxo_panel_bytes.argtypes = [C.c_int, _ll, _ll, _ll]
+        L.qxo_build_panel.argtypes = [C.c_int, _vp, _ll, _ll, _ll, _vp]
+
+    # scalar conversions
+    def fp16_to_fp32(self, h):
+        return self.lib.qxo_fp16_to_fp32(h)
+
+    def fp32_to_fp16(self, v):
+        return self.lib.qxo_fp32_to_fp16(v)
+
+    def float_to_bf16(self, v):
+        return self.lib.qxo_float_to_bf16(v)
+
+    def bf16_to_float(self, h):
+        return self.lib.qxo_bf16_to_float(h)
+
+    def qgemv_packed_size(self, fmt, n, k, want_size=True):
+        size = C.c_size_t(0)
+        status = self.lib.qxo_qgemv_packed_size(
+            fmt, n, k, C.byref(size) if want_size else None)
+        return status, size.value
+
+    def pack(self, fmt, weights, n, k):
+        packed = np.zeros(packed_size(fmt, n, k), np.uint8)
+        status = self.lib.qxo_qgemv_pack(fmt, _ptr(weights), n, k, _ptr(packed))
+        return status, packed
+
+    def unpack(self, fmt, packed, n, k):
+        out = np.zeros((n, k), np.float32)
+        status = self.lib.qxo_qgemv_unpack(fmt, _ptr(packed), n, k, _ptr(out))
+        return status, out
+
+    def qgemv(self, fmt, packed, x, n, k, q4_variant=0):
+        y = np.zeros(n, np.float32)
+        status = self.lib.qxo_qgemv(fmt, _ptr(packed), _ptr(x), _ptr(y), n, k, q4_variant)
+        return status, y
+
+    def qgemm(self, fmt, packed, x, m, n, k, q4_variant=0):
+        y = np.zeros((m, n), np.float32)
+        status = self.lib.qxo_qgemm(fmt, _ptr(packed), _ptr(x), _ptr(y), m, n, k, q4_variant)
+        return status, y
+
+    def qgemm_f64(self, fmt, packed, x, m, n, k):
+        y = np.zeros((m, n), np.float64)
+        status = self.lib.qxo_qgemm_f64(fmt, _ptr(packed), _ptr(x), _ptr(y), m, n, k)
+        return status, y
+
+    def int8_gemm(self, w, x, ws, xs, m, n, k, row_sum=None, zp=None, asymmetric=False):
+        y = np.zeros((m, n), np.float32)
+        acc = np.zeros((m, n), np.int64)
+        status = self.lib.qxo_int8_gemm(_ptr(w), _ptr(x), _ptr(ws), _ptr(xs), _ptr(row_sum),
+                                        _ptr(zp), _ptr(y), _ptr(acc), m, n, k,
+                                        1 if asymmetric else 0)
+        return status, y, acc
+
+    def qgemm_w8a32(self, w, ws, x, m, n, k, avx512_order=False):
+        y = np.zeros((m, n), np.float32)
+        fn = self.lib.qxo_qgemm_w8a32_avx512_order if avx512_order else self.lib.qxo_qgemm_w8a32
+        status = fn(_ptr(w), _ptr(ws), _ptr(x), _ptr(y), m, n, k)
+        return status, y
+
+    def qgemm_w8a32_f64(self, w, ws, x, m, n, k):
+        y = np.zeros((m, n), np.float64)
+        self.lib.qxo_qgemm_w8a32_f64(_ptr(w), _ptr(ws), _ptr(x), _ptr(y), m, n, k)
+        return y
+
+    def build_panel(self, fmt, packed, rows, cols, tile):
+        size = self.lib.qxo_panel_bytes(fmt, rows, cols, tile)
+        panel = np.full(max(size, 1), 0xAB, np.uint8)
+        status = self.lib.qxo_build_panel(fmt, _ptr(packed), rows, cols, tile, _ptr(panel))
+        return status, panel[:max(size, 0)]
+
+
+class Reference:
+    """The unmodified reference library behind oracle/ref_shim.cpp."""
+
+    @staticmethod
+    def available(path: str = REF_SO) -> bool:
+        return os.path.exists(path)
+
+    def __init__(self, path: str = REF_SO):
+        self.lib = L = C.CDLL(path)
+        L.qxref_qgemv_packed_size.argtypes = [C.c_int, _ll, _ll, C.POINTER(C.c_size_t)]
+        L.qxref_qgemv_pack.argtypes = [C.c_int, _vp, _ll, _ll, _vp]
+        L.qxref_qgemv_unpack.argtypes = [C.c_int, _vp, _ll, _ll, _vp]
+        L.qxref_qgemv.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll]
+        L.qxref_qgemm.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll]
+        L.qxref_int8_gemm.argtypes = [_vp] * 7 + [_ll, _ll, _ll, C.c_int]
+        L.qxref_qgemm_w8a8.argtypes = [_vp] * 5 + [_ll, _ll, _ll]
+        L.qxref_qgemm_w8a32.argtypes = [_vp] * 4 + [_ll, _ll, _ll]
+        L.qxref_packed_create.argtypes = [C.c_int, _vp, _ll, _ll, C.c_int, C.POINTER(_vp)]
+        L.qxref_packed_destroy.argtypes = [_vp]
+        L.qxref_packed_destroy.restype = None
+        L.qxref_packed_info.argtypes = [_vp, C.POINTER(_ll)]
+        L.qxref_packed_info.restype = None
+        L.qxref_packed_panel.argtypes = [_vp]
+        L.qxref_packed_panel.restype = _vp
+        L.qxref_qgemm_prepacked.argtypes = [_vp, _vp, _vp, _ll]
+        L.qxref_set_num_threads.argtypes = [C.c_int]
+        L.qxref_set_num_threads.restype = None
+        L.qxref_qgemv_variant.restype = C.c_char_p
+        L.qxref_qgemv_variant.argtypes = [C.c_int]
+        L.qxref_int8_gemm_variant.restype = C.c_char_p
+        L.qxref_qgemm_w8a32_variant.restype = C.c_char_p
+        L.qxref_fp16_to_fp32.restype = C.c_float
+        L.qxref_fp16_to_fp32.argtypes = [C.c_uint16]
+        L.qxref_fp32_to_fp16.restype = C.c_uint16
+        L.qxref_fp32_to_fp16.argtypes = [C.c_float]
+        L.qxref_float_to_bf16.restype = C.c_uint16
+        L.qxref_float_to_bf16.argtypes = [C.c_float]
+        L.qxref_bf16_to_float.restype = C.c_float
+        L.qxref_bf16_to_float.argtypes = [C.c_uint16]
+
+    def set_num_threads(self, n):
+        self.lib.qxref_set_num_threads(int(n))
+
+    def num_threads(self):
+        return self.lib.qxref_num_threads()
+
+    def variants(self):
+        return {
+            "qgemv_q8_0": self.lib.qxref_qgemv_variant(Q8_0).decode(),
+            "qgemv_q4_0": self.lib.qxref_qgemv_variant(Q4_0).decode(),
+            "int8_gemm": self.lib.qxref_int8_gemm_variant().decode(),
+            "qgemm_w8a32": self.lib.qxref_qgemm_w8a32_variant().decode(),
+        }
+
+    def fp16_to_fp32(self, h):
+        return self.lib.qxref_fp16_to_fp32(h)
+
+    def fp32_to_fp16(self, v):
+        return self.lib.qxref_fp32_to_fp16(v)
+
+    def float_to_bf16(self, v):
+        return self.lib.qxref_float_to_bf16(v)
+
+    def bf16_to_float(self, h):
+        return self.lib.qxref_bf16_to_float(h)
+
+    def qgemv_packed_size(self, fmt, n, k, want_size=True):
+        size = C.c_size_t(0)
+        status = self.lib.qxref_qgemv_packed_size(
+            fmt, n, k, C.byref(size) if want_size else None)
+        return status, size.value
+
+    def pack(self, fmt, weights, n, k):
+        packed = np.zeros(packed_size(fmt, n, k), np.uint8)
+        status = self.lib.qxref_qgemv_pack(fmt, _ptr(weights), n, k, _ptr(packed))
+        return status, packed
+
+    def unpack(self, fmt, packed, n, k):
+        out = np.zeros((n, k), np.float32)
+        status = self.lib.qxref_qgemv_unpack(fmt, _ptr(packed), n, k, _ptr(out))
+        return status, out
+
+    def qgemv(self, fmt, packed, x, n, k):
+        y = np.zeros(n, np.float32)
+        status = self.lib.qxref_qgemv(fmt, _ptr(packed), _ptr(x), _ptr(y), n, k)
+        return status, y
+
+    def qgemm(self, fmt, packed, x, m, n, k):
+        y = np.zeros((m, n), np.float32)
+        status = self.lib.qxref_qgemm(fmt, _ptr(packed), _ptr(x), _ptr(y), m, n, k)
+        return status, y
+
+    def int8_gemm(self, w, x, ws, xs, m, n, k, row_sum=None, zp=None, asymmetric=False):
+        y = np.zeros((m, n), np.float32)
+        status = self.lib.qxref_int8_gemm(_ptr(w), _ptr(x), _ptr(ws), _ptr(xs), _ptr(row_sum),
+                                          _ptr(zp), _ptr(y), m, n, k, 1 if asymmetric else 0)
+        return status, y
+
+    def qgemm_w8a8(self, w, x, ws, xs, m, n, k):
+        y = np.zeros((m, n), np.float32)
+        status = self.lib.qxref_qgemm_w8a8(_ptr(w), _ptr(x), _ptr(ws), _ptr(xs), _ptr(y), m, n, k)
+        return status, y
+
+    def qgemm_w8a32(self, w, ws, x, m, n, k):
+        y = np.zeros((m, n), np.float32)
+        status = self.lib.qxref_qgemm_w8a32(_ptr(w), _ptr(ws), _ptr(x), _ptr(y), m, n, k)
+        return status, y
+
+    def prepacked(self, fmt, packed, rows, cols, layout=0):
+        handle = _vp()
+        status = self.lib.qxref_packed_create(fmt, _ptr(packed), rows, cols, layout,
+                                              C.byref(handle))
+        return status, handle
+
+    def prepacked_info(self, handle):
+        out = (_ll * 6)()
+        self.lib.qxref_packed_info(handle, out)
+        keys = ["rows", "columns", "row_tile", "blocks_per_row", "block_bytes", "panel_bytes"]
+        return dict(zip(keys, list(out)))
+
+    def prepacked_panel(self, handle):
+        info = self.prepacked_info(handle)
+        address = self.lib.qxref_packed_panel(handle)
+        return np.ctypeslib.as_array(
+            C.cast(address, C.POINTER(C.c_uint8)), shape=(info["panel_bytes"],)).copy()
+
+    def qgemm_prepacked(self, handle, x, m, n):
+        y = np.zeros((m, n), np.float32)
+        status = self.lib.qxref_qgemm_prepacked(handle, _ptr(x), _ptr(y), m)
+        return status, y
+
+    def prepacked_destroy(self, handle):
+        self.lib.qxref_packed_destroy(handle)

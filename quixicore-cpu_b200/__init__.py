@@ -1,0 +1,268 @@
+"""Python glue over ``libqx_b200.so`` (ctypes): the host-side mirror of the reference's
+public ``quixicore_cpu::`` functions for the quantized-matmul path.
+
+The shared library is the product; this module only marshals pointers. Functions whose
+reference counterpart takes host buffers accept numpy arrays and call the host-pointer
+C entry points; functions ending in ``_dev`` accept torch CUDA tensors and enqueue on
+torch's current stream. Importing this module without the built library raises: there is
+no Python, torch or CPU fallback for any compute entry point.
+
+The directory name contains a hyphen, so load the package through
+``__graft_entry__.load_package()`` (it registers it as ``quixicore_cpu_b200``).
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libqx_b200.so")
+
+Q8_0, Q4_0 = 0, 1
+BLOCK_BYTES = {Q8_0: 34, Q4_0: 18}
+OK, INVALID_SHAPE, UNSUPPORTED_FORMAT, INVALID_ARGUMENT, OUT_OF_MEMORY, DEVICE_ERROR = range(6)
+STATUS_NAMES = ["kOk", "kInvalidShape", "kUnsupportedFormat", "kInvalidArgument",
+                "kOutOfMemory", "kDeviceError"]
+
+_ll, _vp, _sz = C.c_longlong, C.c_void_p, C.c_size_t
+
+
+class QxError(RuntimeError):
+    def __init__(self, status, where, detail=""):
+        self.status = status
+        super().__init__(f"{where}: {STATUS_NAMES[status]} {detail}".strip())
+
+
+class WeightsInfo(C.Structure):
+    _fields_ = [("format", C.c_int), ("rows", _ll), ("columns", _ll), ("block_size", _ll),
+                ("blocks_per_row", _ll), ("block_bytes", _sz), ("contract_bytes", _sz),
+                ("prepared_bytes", _sz), ("memory_amplification", C.c_double),
+                ("preparation_ns", C.c_uint64), ("device", C.c_int), ("has_dense_bf16", C.c_int)]
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [("device", C.c_int), ("sm_major", C.c_int), ("sm_minor", C.c_int),
+                ("sm_count", C.c_int), ("max_smem_per_block", C.c_int), ("l2_bytes", C.c_int),
+                ("hbm_bytes", _sz), ("visible_devices", C.c_int), ("peer_access_mask", C.c_int),
+                ("name", C.c_char * 64)]
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python quixicore-cpu_b200/build.py` "
+            "(nvcc, sm_100a). There is no fallback implementation.")
+    lib = C.CDLL(LIB_PATH)
+    sig = {
+        "qx_device_query": [C.POINTER(DeviceInfo)],
+        "qx_qgemv_packed_size": [C.c_int, _ll, _ll, C.POINTER(_sz)],
+        "qx_qgemv_pack": [C.c_int, _vp, _ll, _ll, _vp],
+        "qx_qgemv_unpack": [C.c_int, _vp, _ll, _ll, _vp],
+        "qx_qgemv": [C.c_int, _vp, _vp, _vp, _ll, _ll],
+        "qx_qgemm": [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll],
+        "qx_weights_prepare": [C.c_int, _vp, _ll, _ll, _ll, _ll, C.POINTER(_vp)],
+        "qx_weights_prepare_dev": [C.c_int, _vp, _ll, _ll, _ll, _ll, _vp, C.POINTER(_vp)],
+        "qx_weights_get_info": [_vp, C.POINTER(WeightsInfo)],
+        "qx_workspace_create": [_sz, C.POINTER(_vp)],
+        "qx_qgemm_prepacked": [_vp, _vp, _vp, _ll, _vp],
+        "qx_qgemm_prepacked_dev": [_vp, _vp, _vp, _ll, _ll, _vp, _vp],
+        "qx_qgemm_prepacked_bf16_dev": [_vp, _vp, _vp, _ll, _ll, _vp, _vp],
+        "qx_int8_gemm": [_vp] * 7 + [_ll, _ll, _ll, C.c_int],
+        "qx_qgemm_w8a8": [_vp] * 5 + [_ll, _ll, _ll],
+        "qx_qgemm_w8a8_azp": [_vp] * 7 + [_ll, _ll, _ll],
+        "qx_int8_gemm_dev": [_vp] * 8 + [_ll, _ll, _ll, _ll, C.c_int, C.c_int, _vp],
+        "qx_qgemm_w8a32": [_vp] * 4 + [_ll, _ll, _ll],
+        "qx_qgemm_w8a32_dev": [_vp] * 4 + [_ll, _ll, _ll, _ll, C.c_int, _vp, _vp],
+    }
+    for name, argtypes in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = C.c_int
+    for name in ("qx_last_error_string", "qx_qgemv_variant", "qx_int8_gemm_variant",
+                 "qx_qgemm_w8a32_variant"):
+        getattr(lib, name).restype = C.c_char_p
+    lib.qx_qgemv_variant.argtypes = [C.c_int]
+    lib.qx_weights_destroy.argtypes = [_vp]
+    lib.qx_weights_destroy.restype = None
+    lib.qx_workspace_destroy.argtypes = [_vp]
+    lib.qx_workspace_destroy.restype = None
+    lib.qx_workspace_capacity.argtypes = [_vp]
+    lib.qx_workspace_capacity.restype = _sz
+    lib.qx_set_num_threads.argtypes = [C.c_int]
+    lib.qx_set_num_threads.restype = None
+    lib.qx_num_threads.restype = C.c_int
+    lib.qx_kernel_launch_count.restype = C.c_ulonglong
+    return lib
+
+
+lib = _load()
+
+
+def _np(a):
+    if a is None:
+        return None
+    assert isinstance(a, np.ndarray) and a.flags["C_CONTIGUOUS"], "need a contiguous numpy array"
+    return a.ctypes.data_as(_vp)
+
+
+def _dev(t):
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "need a contiguous CUDA tensor"
+    return _vp(t.data_ptr())
+
+
+def _stream():
+    import torch
+    return _vp(torch.cuda.current_stream().cuda_stream)
+
+
+def last_error() -> str:
+    return (lib.qx_last_error_string() or b"").decode()
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        raise QxError(status, where, last_error())
+
+
+def launch_count() -> int:
+    return int(lib.qx_kernel_launch_count())
+
+
+def device_info() -> dict:
+    info = DeviceInfo()
+    check(lib.qx_device_query(C.byref(info)), "qx_device_query")
+    out = {name: getattr(info, name) for name, _ in DeviceInfo._fields_}
+    out["name"] = info.name.decode()
+    return out
+
+
+# ---- reference-shaped host-pointer calls: return (status, result) like the C functions ----
+
+def qgemv_packed_size(fmt, n, k, want_size=True):
+    size = _sz(0)
+    status = lib.qx_qgemv_packed_size(fmt, n, k, C.byref(size) if want_size else None)
+    return status, size.value
+
+
+def qgemv_pack(fmt, weights, n, k):
+    packed = np.zeros(n * (k // 32) * BLOCK_BYTES[fmt], np.uint8)
+    return lib.qx_qgemv_pack(fmt, _np(weights), n, k, _np(packed)), packed
+
+
+def qgemv_unpack(fmt, packed, n, k):
+    out = np.zeros((n, k), np.float32)
+    return lib.qx_qgemv_unpack(fmt, _np(packed), n, k, _np(out)), out
+
+
+def qgemv(fmt, packed, x, n, k):
+    y = np.zeros(n, np.float32)
+    return lib.qx_qgemv(fmt, _np(packed), _np(x), _np(y), n, k), y
+
+
+def qgemm(fmt, packed, x, m, n, k):
+    y = np.zeros((m, n), np.float32)
+    return lib.qx_qgemm(fmt, _np(packed), _np(x), _np(y), m, n, k), y
+
+
+def int8_gemm(w, x, ws, xs, m, n, k, row_sum=None, zp=None, asymmetric=False):
+    y = np.zeros((m, n), np.float32)
+    status = lib.qx_int8_gemm(_np(w), _np(x), _np(ws), _np(xs), _np(row_sum), _np(zp), _np(y),
+                              m, n, k, 1 if asymmetric else 0)
+    return status, y
+
+
+def qgemm_w8a8(w, x, ws, xs, m, n, k):
+    y = np.zeros((m, n), np.float32)
+    return lib.qx_qgemm_w8a8(_np(w), _np(x), _np(ws), _np(xs), _np(y), m, n, k), y
+
+
+def qgemm_w8a32(w, ws, x, m, n, k):
+    y = np.zeros((m, n), np.float32)
+    return lib.qx_qgemm_w8a32(_np(w), _np(ws), _np(x), _np(y), m, n, k), y
+
+
+def variants() -> dict:
+    return {
+        "qgemv_q8_0": lib.qx_qgemv_variant(Q8_0).decode(),
+        "qgemv_q4_0": lib.qx_qgemv_variant(Q4_0).decode(),
+        "int8_gemm": lib.qx_int8_gemm_variant().decode(),
+        "qgemm_w8a32": lib.qx_qgemm_w8a32_variant().decode(),
+    }
+
+
+class PackedWeights:
+    """Device-resident prepared weights (mirror of quixicore_cpu::CpuPackedWeights)."""
+
+    def __init__(self):
+        self.handle = _vp()
+
+    def prepare(self, fmt, packed, rows, columns, row_begin=0, row_count=None) -> int:
+        self.reset()
+        row_count = rows if row_count is None else row_count
+        if packed is not None and not isinstance(packed, np.ndarray):
+            ptr = _dev(packed)
+            return lib.qx_weights_prepare_dev(fmt, ptr, rows, columns, row_begin, row_count,
+                                              _stream(), C.byref(self.handle))
+        return lib.qx_weights_prepare(fmt, _np(packed), rows, columns, row_begin, row_count,
+                                      C.byref(self.handle))
+
+    def ready(self) -> bool:
+        return bool(self.handle)
+
+    def info(self) -> dict:
+        info = WeightsInfo()
+        check(lib.qx_weights_get_info(self.handle, C.byref(info)), "qx_weights_get_info")
+        return {name: getattr(info, name) for name, _ in WeightsInfo._fields_}
+
+    def reset(self) -> None:
+        if self.handle:
+            lib.qx_weights_destroy(self.handle)
+            self.handle = _vp()
+
+    def __del__(self):
+        try:
+            self.reset()
+        except Exception:
+            pass
+
+    # host buffers (numpy): the reference-facing call
+    def qgemm_prepacked(self, x, m, y=None):
+        rows = self.info()["rows"] if self.handle else 0
+        if y is None:
+            y = np.zeros((m, max(rows, 1)), np.float32)
+        return lib.qx_qgemm_prepacked(self.handle, _np(x), _np(y), m, None), y
+
+    # raw host pointers (e.g. pinned torch tensors): the end-to-end timed call
+    def qgemm_prepacked_ptr(self, x_ptr, y_ptr, m) -> int:
+        return lib.qx_qgemm_prepacked(self.handle, _vp(x_ptr), _vp(y_ptr), m, None)
+
+    # device tensors, torch's current stream
+    def qgemm_dev(self, x, y, m, ldy=None) -> int:
+        ldy = y.shape[-1] if ldy is None else ldy
+        return lib.qx_qgemm_prepacked_dev(self.handle, _dev(x), _vp(y.data_ptr()), m, ldy, None,
+                                          _stream())
+
+    def qgemm_bf16_dev(self, x_bf16, y, m, ldy=None) -> int:
+        ldy = y.shape[-1] if ldy is None else ldy
+        return lib.qx_qgemm_prepacked_bf16_dev(self.handle, _dev(x_bf16), _vp(y.data_ptr()), m,
+                                               ldy, None, _stream())
+
+
+def int8_gemm_dev(w, x, ws, xs, y, m, n, k, row_sum=None, zp=None, acc=None, ldy=None,
+                  check_scales=False) -> int:
+    ldy = n if ldy is None else ldy
+    return lib.qx_int8_gemm_dev(_dev(w), _dev(x), _dev(ws), _dev(xs), _dev(row_sum), _dev(zp),
+                                _vp(y.data_ptr()), _dev(acc), m, n, k, ldy,
+                                1 if row_sum is not None else 0, 1 if check_scales else 0,
+                                _stream())
+
+
+def qgemm_w8a32_dev(w, ws, x, y, m, n, k, ldy=None, check_scales=False) -> int:
+    ldy = n if ldy is None else ldy
+    return lib.qx_qgemm_w8a32_dev(_dev(w), _dev(ws), _dev(x), _vp(y.data_ptr()), m, n, k, ldy,
+                                  1 if check_scales else 0, None, _stream())

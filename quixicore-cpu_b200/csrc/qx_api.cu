@@ -1,0 +1,369 @@
+// extern "C" entry points. Validation order and status values follow the reference's
+// dispatch layer (file:line given at each function); the host-pointer forms then stage
+// the operands through device memory on the library's own stream and wait for the
+// result, the `_dev` forms only enqueue.
+
+#include <cmath>
+#include <cstring>
+
+#include "qx_int8_gemm.cuh"
+#include "qx_weights.cuh"
+
+namespace qx {
+qx_status launch_pack(int format, const float* w_dev, long long total_blocks, void* packed_dev,
+                      int* bad_dev, cudaStream_t stream);
+qx_status launch_unpack(int format, const void* packed_dev, long long total_blocks, float* w_dev,
+                        cudaStream_t stream);
+qx_status launch_q4_gemm_bf16(const qx_weights* w, const uint16_t* x_bf16_dev, float* y_dev,
+                              long long m, long long ldy, qx_workspace* ws, cudaStream_t stream);
+
+namespace {
+
+// Carves 256-byte aligned pieces out of the context's staging buffer.
+struct Staging {
+  DeviceContext* ctx;
+  size_t offset = 0;
+  size_t sizes[8];
+  int count = 0;
+  size_t add(size_t bytes) {
+    sizes[count++] = bytes;
+    const size_t at = offset;
+    offset += align_up(bytes == 0 ? 1 : bytes, 256);
+    return at;
+  }
+  uint8_t* at(size_t off) const { return static_cast<uint8_t*>(ctx->staging) + off; }
+};
+
+qx_status h2d(void* dst, const void* src, size_t bytes, cudaStream_t s) {
+  QX_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, s));
+  return QX_STATUS_OK;
+}
+qx_status d2h(void* dst, const void* src, size_t bytes, cudaStream_t s) {
+  QX_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, s));
+  return QX_STATUS_OK;
+}
+
+// After a synchronise: a kernel whose bounded wait gave up leaves a code in flag[1].
+qx_status check_device_error(DeviceContext* ctx) {
+  int words[2] = {0, 0};
+  QX_CUDA_TRY(cudaMemcpy(words, ctx->flag, sizeof words, cudaMemcpyDeviceToHost));
+  if (words[1] != 0) {
+    (void)cudaMemset(ctx->flag, 0, 8);
+    set_last_error_text("a tensor-core kernel gave up a bounded wait (pipeline stalled)");
+    return QX_STATUS_DEVICE_ERROR;
+  }
+  return QX_STATUS_OK;
+}
+
+bool all_finite_host(const float* v, long long count) {
+  for (long long i = 0; i < count; ++i) {
+    if (!std::isfinite(v[i])) return false;
+  }
+  return true;
+}
+
+}  // namespace
+}  // namespace qx
+
+using namespace qx;
+
+extern "C" {
+
+// src/dispatch/qgemv.cpp:198-208
+qx_status qx_qgemv_packed_size(int format, long long n, long long k, size_t* size) {
+  QX_TRY(validate_nk(format, n, k));
+  if (size == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  return packed_bytes(format, n, k, size);
+}
+
+// src/dispatch/qgemv.cpp:215-275 (q8_0 / q4_0 branch)
+qx_status qx_qgemv_pack(int format, const float* weights, long long n, long long k,
+                        void* packed) {
+  QX_TRY(validate_nk(format, n, k));
+  size_t bytes = 0;
+  if (packed_bytes(format, n, k, &bytes) != QX_STATUS_OK) return QX_STATUS_INVALID_SHAPE;
+  if (weights == nullptr || packed == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  Staging st{ctx};
+  const size_t w_bytes = static_cast<size_t>(n) * k * sizeof(float);
+  const size_t off_w = st.add(w_bytes), off_p = st.add(bytes);
+  QX_TRY(ctx->ensure_staging(st.offset));
+  QX_CUDA_TRY(cudaMemsetAsync(ctx->flag, 0, 4, ctx->stream));
+  QX_TRY(h2d(st.at(off_w), weights, w_bytes, ctx->stream));
+  QX_TRY(launch_pack(format, reinterpret_cast<const float*>(st.at(off_w)), n * (k / kBlockK),
+                     st.at(off_p), ctx->flag, ctx->stream));
+  int bad = 0;
+  QX_TRY(d2h(&bad, ctx->flag, 4, ctx->stream));
+  QX_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  if (bad != 0) return QX_STATUS_INVALID_ARGUMENT;  // non-finite weight, nothing written
+  QX_CUDA_TRY(cudaMemcpy(packed, st.at(off_p), bytes, cudaMemcpyDeviceToHost));
+  return QX_STATUS_OK;
+}
+
+// src/dispatch/qgemv.cpp:277-300
+qx_status qx_qgemv_unpack(int format, const void* packed, long long n, long long k,
+                          float* weights) {
+  QX_TRY(validate_nk(format, n, k));
+  size_t bytes = 0;
+  if (packed_bytes(format, n, k, &bytes) != QX_STATUS_OK) return QX_STATUS_INVALID_SHAPE;
+  if (packed == nullptr || weights == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  Staging st{ctx};
+  const size_t w_bytes = static_cast<size_t>(n) * k * sizeof(float);
+  const size_t off_p = st.add(bytes), off_w = st.add(w_bytes);
+  QX_TRY(ctx->ensure_staging(st.offset));
+  QX_TRY(h2d(st.at(off_p), packed, bytes, ctx->stream));
+  QX_TRY(launch_unpack(format, st.at(off_p), n * (k / kBlockK),
+                       reinterpret_cast<float*>(st.at(off_w)), ctx->stream));
+  QX_TRY(d2h(weights, st.at(off_w), w_bytes, ctx->stream));
+  QX_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  return QX_STATUS_OK;
+}
+
+// kernels/quantization/qgemm_ref.cpp:141-164: shape -> null -> packed-size status.
+qx_status qx_qgemm(int format, const void* packed_weights, const float* x, float* y,
+                   long long m, long long n, long long k) {
+  if (!valid_product2(m, k) || !valid_product2(m, n)) return QX_STATUS_INVALID_SHAPE;
+  if (packed_weights == nullptr || x == nullptr || y == nullptr) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  size_t bytes = 0;
+  QX_TRY(qx_qgemv_packed_size(format, n, k, &bytes));
+  qx_weights* w = nullptr;
+  QX_TRY(qx_weights_prepare(format, packed_weights, n, k, 0, n, &w));
+  const qx_status status = qx_qgemm_prepacked(w, x, y, m, nullptr);
+  qx_weights_destroy(w);
+  return status;
+}
+
+// src/dispatch/qgemv.cpp:337-365: format/shape -> size -> null pointers.
+qx_status qx_qgemv(int format, const void* packed, const float* x, float* y, long long n,
+                   long long k) {
+  QX_TRY(validate_nk(format, n, k));
+  size_t bytes = 0;
+  if (packed_bytes(format, n, k, &bytes) != QX_STATUS_OK) return QX_STATUS_INVALID_SHAPE;
+  if (packed == nullptr || x == nullptr || y == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  return qx_qgemm(format, packed, x, y, 1, n, k);
+}
+
+const char* qx_qgemv_variant(int format) {
+  if (format == QX_FORMAT_Q8_0) return "sm100a_dp4a_q8_0";
+  if (format == QX_FORMAT_Q4_0) return "sm100a_dp4a_q4_0";
+  return "unsupported";
+}
+
+// kernels/quantization/qgemm_panel.cpp:214-233
+qx_status qx_qgemm_prepacked(const qx_weights* weights, const float* x, float* y, long long m,
+                             qx_workspace* workspace) {
+  if (weights == nullptr) return QX_STATUS_INVALID_ARGUMENT;  // !weights.ready()
+  if (!valid_product3(m, weights->rows, weights->columns)) return QX_STATUS_INVALID_SHAPE;
+  if (x == nullptr || y == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  Staging st{ctx};
+  const size_t x_bytes = static_cast<size_t>(m) * weights->columns * sizeof(float);
+  const size_t y_bytes = static_cast<size_t>(m) * weights->rows * sizeof(float);
+  const size_t off_x = st.add(x_bytes), off_y = st.add(y_bytes);
+  QX_TRY(ctx->ensure_staging(st.offset));
+  QX_TRY(h2d(st.at(off_x), x, x_bytes, ctx->stream));
+  QX_TRY(launch_qgemm_f32(weights, reinterpret_cast<const float*>(st.at(off_x)),
+                          reinterpret_cast<float*>(st.at(off_y)), m, weights->rows,
+                          workspace != nullptr ? workspace : &ctx->workspace, ctx->stream));
+  QX_TRY(d2h(y, st.at(off_y), y_bytes, ctx->stream));
+  QX_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+  return QX_STATUS_OK;
+}
+
+qx_status qx_qgemm_prepacked_dev(const qx_weights* weights, const float* x_dev, float* y_dev,
+                                 long long m, long long ldy, qx_workspace* workspace,
+                                 void* stream) {
+  if (weights == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  if (!valid_product3(m, weights->rows, weights->columns) || ldy < weights->rows) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  if (x_dev == nullptr || y_dev == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  return launch_qgemm_f32(weights, x_dev, y_dev, m, ldy,
+                          workspace != nullptr ? workspace : &ctx->workspace,
+                          static_cast<cudaStream_t>(stream));
+}
+
+qx_status qx_qgemm_prepacked_bf16_dev(const qx_weights* weights, const uint16_t* x_bf16_dev,
+                                      float* y_dev, long long m, long long ldy,
+                                      qx_workspace* workspace, void* stream) {
+  if (weights == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  if (!valid_product3(m, weights->rows, weights->columns) || ldy < weights->rows) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  if (x_bf16_dev == nullptr || y_dev == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  return launch_q4_gemm_bf16(weights, x_bf16_dev, y_dev, m, ldy,
+                             workspace != nullptr ? workspace : &ctx->workspace,
+                             static_cast<cudaStream_t>(stream));
+}
+
+// src/dispatch/int8_gemm.cpp:67-94: shape -> null -> finite scales.
+qx_status qx_int8_gemm(const int8_t* weights, const int8_t* x, const float* weight_scale,
+                       const float* activation_scale, const int32_t* weight_row_sum,
+                       const int* activation_zero_point, float* y, long long m, long long n,
+                       long long k, int asymmetric) {
+  if (!valid_product3(m, n, k)) return QX_STATUS_INVALID_SHAPE;
+  if (weights == nullptr || x == nullptr || weight_scale == nullptr ||
+      activation_scale == nullptr || y == nullptr ||
+      (asymmetric && (weight_row_sum == nullptr || activation_zero_point == nullptr))) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  if (!all_finite_host(weight_scale, n) || !all_finite_host(activation_scale, m)) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  Staging st{ctx};
+  const size_t w_bytes = static_cast<size_t>(n) * k, x_bytes = static_cast<size_t>(m) * k;
+  const size_t y_bytes = static_cast<size_t>(m) * n * sizeof(float);
+  const size_t off_w = st.add(w_bytes), off_x = st.add(x_bytes), off_ws = st.add(n * 4),
+               off_as = st.add(m * 4), off_rs = st.add(n * 4), off_zp = st.add(m * 4),
+               off_y = st.add(y_bytes);
+  QX_TRY(ctx->ensure_staging(st.offset));
+  cudaStream_t s = ctx->stream;
+  QX_TRY(h2d(st.at(off_w), weights, w_bytes, s));
+  QX_TRY(h2d(st.at(off_x), x, x_bytes, s));
+  QX_TRY(h2d(st.at(off_ws), weight_scale, n * 4, s));
+  QX_TRY(h2d(st.at(off_as), activation_scale, m * 4, s));
+  if (asymmetric) {
+    QX_TRY(h2d(st.at(off_rs), weight_row_sum, n * 4, s));
+    QX_TRY(h2d(st.at(off_zp), activation_zero_point, m * 4, s));
+  }
+  Int8GemmArgs a{};
+  a.w = reinterpret_cast<const int8_t*>(st.at(off_w));
+  a.x = reinterpret_cast<const int8_t*>(st.at(off_x));
+  a.ws = reinterpret_cast<const float*>(st.at(off_ws));
+  a.as = reinterpret_cast<const float*>(st.at(off_as));
+  a.row_sum = asymmetric ? reinterpret_cast<const int32_t*>(st.at(off_rs)) : nullptr;
+  a.zp = asymmetric ? reinterpret_cast<const int*>(st.at(off_zp)) : nullptr;
+  a.y = reinterpret_cast<float*>(st.at(off_y));
+  a.acc = nullptr;
+  a.m = m;
+  a.n = n;
+  a.k = k;
+  a.ldy = n;
+  a.asymmetric = asymmetric != 0;
+  QX_TRY(launch_int8_gemm(a, s));
+  QX_TRY(d2h(y, st.at(off_y), y_bytes, s));
+  QX_CUDA_TRY(cudaStreamSynchronize(s));
+  return check_device_error(ctx);
+}
+
+// kernels/quantization/qgemm_extended_ref.cpp:142-147
+qx_status qx_qgemm_w8a8(const int8_t* weights, const int8_t* x, const float* weight_scale,
+                        const float* activation_scale, float* y, long long m, long long n,
+                        long long k) {
+  return qx_int8_gemm(weights, x, weight_scale, activation_scale, nullptr, nullptr, y, m, n, k, 0);
+}
+
+// kernels/quantization/qgemm_extended_ref.cpp:149-156
+qx_status qx_qgemm_w8a8_azp(const int8_t* weights, const int8_t* x, const float* weight_scale,
+                            const float* activation_scale, const int32_t* weight_row_sum,
+                            const int* activation_zero_point, float* y, long long m,
+                            long long n, long long k) {
+  return qx_int8_gemm(weights, x, weight_scale, activation_scale, weight_row_sum,
+                      activation_zero_point, y, m, n, k, 1);
+}
+
+const char* qx_int8_gemm_variant(void) { return int8_gemm_variant_name(); }
+
+qx_status qx_int8_gemm_dev(const int8_t* weights_dev, const int8_t* x_dev,
+                           const float* weight_scale_dev, const float* activation_scale_dev,
+                           const int32_t* weight_row_sum_dev, const int* activation_zero_point_dev,
+                           float* y_dev, int32_t* acc_i32_dev, long long m, long long n,
+                           long long k, long long ldy, int asymmetric, int check_scales,
+                           void* stream) {
+  if (!valid_product3(m, n, k) || ldy < n) return QX_STATUS_INVALID_SHAPE;
+  if (weights_dev == nullptr || x_dev == nullptr || weight_scale_dev == nullptr ||
+      activation_scale_dev == nullptr || y_dev == nullptr ||
+      (asymmetric && (weight_row_sum_dev == nullptr || activation_zero_point_dev == nullptr))) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (check_scales) {
+    QX_CUDA_TRY(cudaMemsetAsync(ctx->flag, 0, 4, s));
+    QX_TRY(launch_check_finite(weight_scale_dev, n, ctx->flag, s));
+    QX_TRY(launch_check_finite(activation_scale_dev, m, ctx->flag, s));
+    int bad = 0;
+    QX_CUDA_TRY(cudaMemcpyAsync(&bad, ctx->flag, 4, cudaMemcpyDeviceToHost, s));
+    QX_CUDA_TRY(cudaStreamSynchronize(s));
+    if (bad != 0) return QX_STATUS_INVALID_ARGUMENT;
+  }
+  Int8GemmArgs a{weights_dev, x_dev, weight_scale_dev, activation_scale_dev, weight_row_sum_dev,
+                 activation_zero_point_dev, y_dev, acc_i32_dev, m, n, k, ldy, asymmetric != 0};
+  return launch_int8_gemm(a, s);
+}
+
+// src/dispatch/w8a32_gemm.cpp:61-73
+qx_status qx_qgemm_w8a32(const int8_t* weights, const float* weight_scale, const float* x,
+                         float* y, long long m, long long n, long long k) {
+  if (!valid_product3(m, n, k)) return QX_STATUS_INVALID_SHAPE;
+  if (weights == nullptr || weight_scale == nullptr || x == nullptr || y == nullptr) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  if (!all_finite_host(weight_scale, n)) return QX_STATUS_INVALID_ARGUMENT;
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  Staging st{ctx};
+  const size_t w_bytes = static_cast<size_t>(n) * k;
+  const size_t x_bytes = static_cast<size_t>(m) * k * sizeof(float);
+  const size_t y_bytes = static_cast<size_t>(m) * n * sizeof(float);
+  const size_t off_w = st.add(w_bytes), off_ws = st.add(n * 4), off_x = st.add(x_bytes),
+               off_y = st.add(y_bytes);
+  QX_TRY(ctx->ensure_staging(st.offset));
+  cudaStream_t s = ctx->stream;
+  QX_TRY(h2d(st.at(off_w), weights, w_bytes, s));
+  QX_TRY(h2d(st.at(off_ws), weight_scale, n * 4, s));
+  QX_TRY(h2d(st.at(off_x), x, x_bytes, s));
+  QX_TRY(launch_w8a32(reinterpret_cast<const int8_t*>(st.at(off_w)),
+                      reinterpret_cast<const float*>(st.at(off_ws)),
+                      reinterpret_cast<const float*>(st.at(off_x)),
+                      reinterpret_cast<float*>(st.at(off_y)), m, n, k, n, &ctx->workspace, s));
+  QX_TRY(d2h(y, st.at(off_y), y_bytes, s));
+  QX_CUDA_TRY(cudaStreamSynchronize(s));
+  return check_device_error(ctx);
+}
+
+const char* qx_qgemm_w8a32_variant(void) { return "sm100a_fma"; }
+
+qx_status qx_qgemm_w8a32_dev(const int8_t* weights_dev, const float* weight_scale_dev,
+                             const float* x_dev, float* y_dev, long long m, long long n,
+                             long long k, long long ldy, int check_scales,
+                             qx_workspace* workspace, void* stream) {
+  if (!valid_product3(m, n, k) || ldy < n) return QX_STATUS_INVALID_SHAPE;
+  if (weights_dev == nullptr || weight_scale_dev == nullptr || x_dev == nullptr ||
+      y_dev == nullptr) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (check_scales) {
+    QX_CUDA_TRY(cudaMemsetAsync(ctx->flag, 0, 4, s));
+    QX_TRY(launch_check_finite(weight_scale_dev, n, ctx->flag, s));
+    int bad = 0;
+    QX_CUDA_TRY(cudaMemcpyAsync(&bad, ctx->flag, 4, cudaMemcpyDeviceToHost, s));
+    QX_CUDA_TRY(cudaStreamSynchronize(s));
+    if (bad != 0) return QX_STATUS_INVALID_ARGUMENT;
+  }
+  return launch_w8a32(weights_dev, weight_scale_dev, x_dev, y_dev, m, n, k, ldy,
+                      workspace != nullptr ? workspace : &ctx->workspace, s);
+}
+
+}  // extern "C"

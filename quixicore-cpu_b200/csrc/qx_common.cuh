@@ -1,0 +1,86 @@
+// Shared declarations of the qx_b200 library: status helpers, the per-device context
+// (stream + default workspace), launch accounting and small device utilities.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstddef>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+
+#include "qx_b200.h"
+
+namespace qx {
+
+constexpr int kBlockK = 32;  // elements per q8_0 / q4_0 block
+
+// ---- error reporting -------------------------------------------------------------
+void set_last_error(const char* where, cudaError_t code);
+void set_last_error_text(const char* text);
+
+#define QX_CUDA_TRY(expr)                                  \
+  do {                                                     \
+    const cudaError_t qx_err_ = (expr);                    \
+    if (qx_err_ != cudaSuccess) {                          \
+      ::qx::set_last_error(#expr, qx_err_);                \
+      return qx_err_ == cudaErrorMemoryAllocation          \
+                 ? QX_STATUS_OUT_OF_MEMORY                 \
+                 : QX_STATUS_DEVICE_ERROR;                 \
+    }                                                      \
+  } while (0)
+
+#define QX_TRY(expr)                                       \
+  do {                                                     \
+    const qx_status qx_st_ = (expr);                       \
+    if (qx_st_ != QX_STATUS_OK) return qx_st_;             \
+  } while (0)
+
+// Every kernel launch goes through this counter (qx_kernel_launch_count()).
+extern std::atomic<unsigned long long> g_launches;
+inline void count_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// ---- device workspace (grow-only arena, mirrors quixicore_cpu::Workspace) ----------
+}  // namespace qx
+
+struct qx_workspace {
+  int device = -1;
+  void* base = nullptr;
+  size_t capacity = 0;
+  // Returns a 256-byte aligned device pointer valid until the next reserve() that
+  // grows the arena. Growing synchronises the device (cudaFree of the old block).
+  qx_status reserve(size_t bytes);
+  ~qx_workspace();
+};
+
+namespace qx {
+
+struct DeviceContext {
+  int device = -1;
+  cudaDeviceProp prop{};
+  cudaStream_t stream = nullptr;  // used by the host-pointer entry points
+  qx_workspace workspace;         // default workspace (NULL workspace argument)
+  std::mutex mutex;               // serialises host-pointer calls on this device
+  // staging buffers for host-pointer calls (grow-only)
+  void* staging = nullptr;
+  size_t staging_bytes = 0;
+  int* flag = nullptr;            // 4-byte device word for scale checks
+  qx_status ensure_staging(size_t bytes);
+};
+
+// Context of the current CUDA device; creates it on first use. Fails with
+// QX_STATUS_DEVICE_ERROR when no sm_100 device is usable.
+qx_status current_context(DeviceContext** out);
+
+// ---- shape validation shared by the entry points ------------------------------------
+bool valid_product3(long long a, long long b, long long c);
+bool valid_product2(long long a, long long b);
+bool format_info(int format, size_t* block_bytes);
+qx_status validate_nk(int format, long long n, long long k);
+qx_status packed_bytes(int format, long long n, long long k, size_t* size);
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+}  // namespace qx

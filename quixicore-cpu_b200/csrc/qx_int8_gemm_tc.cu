@@ -1,0 +1,361 @@
+// W8A8 prefill GEMM on the 5th-generation tensor cores.
+//
+// Replaces int8_gemm_{ref,avx2,avx512_vnni}_kernel of the reference
+// (kernels/quantization/int8_gemm_ref.cpp:9-32, int8_gemm_avx512.cpp:77-100):
+//   acc[r,o] = sum_k W[o,k] * X[r,k]   (exact, int32 in TMEM)
+//   Y[r,o]   = float(acc - zp[r]*row_sum[o]) * ws[o] * as[r]     (two rounded multiplies,
+//              left to right, as int8_gemm_ref.cpp:28-29)
+//
+// Mapping. Both operands are K-contiguous, so both are "K-major" MMA operands and need
+// no transposition. The WEIGHT tile is the MMA's A operand (128 output channels = 128
+// TMEM lanes) and the ACTIVATION tile is B (up to 256 tokens = TMEM columns). With that
+// orientation an epilogue thread owns one output channel and walks over tokens, so for a
+// fixed token the 32 lanes of a warp store 32 consecutive floats of Y: fully coalesced
+// stores without a shared-memory transpose.
+//
+// Pipeline (persistent CTAs, one per SM, 192 threads):
+//   warp 0      TMA producer: 128-byte-swizzled K-slabs of W (128 x 128 B) and X
+//               (BN x 128 B) into a 4-stage shared-memory ring (full/empty mbarriers)
+//   warp 1      MMA issuer: one thread issues tcgen05.mma kind::i8 (K = 32 per
+//               instruction, four per slab) into one of two TMEM accumulators
+//   warps 2-5   epilogue: tcgen05.ld -> int->f32 -> scale -> global stores, overlapped
+//               with the next tile's MMAs through the second accumulator
+// No cluster launch and no multicast: every CTA loads its own operands.
+
+#include <cuda.h>
+
+#include "qx_int8_gemm.cuh"
+#include "qx_sm100.cuh"
+
+namespace qx {
+
+// ---- host: tensor-map encoding ------------------------------------------------------
+namespace {
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                              const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                              const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = []() -> EncodeFn {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &result) !=
+            cudaSuccess ||
+        result != cudaDriverEntryPointSuccess) {
+      (void)cudaGetLastError();
+      return nullptr;
+    }
+    return reinterpret_cast<EncodeFn>(ptr);
+  }();
+  return fn;
+}
+}  // namespace
+
+bool encode_tma_2d(CUtensorMap* map, CUtensorMapDataType dtype, int elem_bytes, const void* base,
+                   uint64_t inner_elems, uint64_t rows, uint64_t row_stride_bytes,
+                   uint32_t box_inner_elems, uint32_t box_rows) {
+  EncodeFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  (void)elem_bytes;
+  const cuuint64_t dims[2] = {inner_elems, rows};
+  const cuuint64_t strides[1] = {row_stride_bytes};
+  const cuuint32_t box[2] = {box_inner_elems, box_rows};
+  const cuuint32_t elem_strides[2] = {1, 1};
+  return fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+namespace {
+
+constexpr int kBM = 128;        // output channels per tile (MMA M, TMEM lanes)
+constexpr int kBK = 128;        // bytes of K per pipeline stage (one swizzle atom)
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;  // two accumulators of up to 256 columns
+
+struct TcParams {
+  const float* ws;
+  const float* as;
+  const int32_t* row_sum;
+  const int* zp;
+  float* y;
+  int32_t* acc;
+  long long m, n, ldy;
+  int k_slabs;   // ceil(k / 128)
+  int bn;        // tokens per tile: multiple of 32, <= 256
+  int o_tiles, r_tiles;
+  int asymmetric;
+  int* error;    // device word, set non-zero when a bounded wait gave up
+};
+
+struct __align__(8) TcBarriers {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
+    const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+    const TcParams p) {
+  using namespace sm100;
+  extern __shared__ uint8_t smem_raw[];
+  // stage ring, 1024-byte aligned for the 128-byte swizzle
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  const uint32_t a_bytes = kBM * kBK;
+  const uint32_t b_bytes = static_cast<uint32_t>(p.bn) * kBK;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+  TcBarriers* bars = reinterpret_cast<TcBarriers*>(smem + kStages * stage_bytes);
+  float* as_tile = reinterpret_cast<float*>(bars + 1);  // [2][256] activation scales
+  int* zp_tile = reinterpret_cast<int*>(as_tile + 2 * 256);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars->full[s], 1);
+      mbar_init(&bars->empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&bars->tmem_full[a], 1);
+      mbar_init(&bars->tmem_empty[a], 4);
+    }
+    bars->abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const int total_tiles = p.o_tiles * p.r_tiles;
+  const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) |
+                         (static_cast<uint32_t>(p.bn >> 3) << 17) |
+                         (static_cast<uint32_t>(kBM >> 4) << 24);
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int o0 = (tile / p.r_tiles) * kBM;
+        const int r0 = (tile % p.r_tiles) * p.bn;
+        for (int ks = 0; ks < p.k_slabs; ++ks) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * stage_bytes;
+          mbar_arrive_expect_tx(&bars->full[stage], stage_bytes);
+          tma_load_2d(sa, &map_w, &bars->full[stage], ks * kBK, o0);
+          tma_load_2d(sa + a_bytes, &map_x, &bars->full[stage], ks * kBK, r0);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error, 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * 256u;
+        for (int ks = 0; ks < p.k_slabs; ++ks) {
+          if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * stage_bytes);
+          const uint64_t a_desc = make_sw128_kmajor_desc(sa);
+          const uint64_t b_desc = make_sw128_kmajor_desc(sa + a_bytes);
+#pragma unroll
+          for (int kk = 0; kk < kBK / 32; ++kk) {
+            // advance 32 bytes of K inside the swizzle atom: +2 in the (addr >> 4) field
+            mma_i8_ss(d_tmem, a_desc + static_cast<uint64_t>(kk * 2),
+                      b_desc + static_cast<uint64_t>(kk * 2), idesc, (ks | kk) != 0 ? 1u : 0u);
+          }
+          tc_commit(&bars->empty[stage]);  // frees the slab once the MMAs have read it
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit(&bars->tmem_full[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error, 2);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
+    const int epi_thread = threadIdx.x - 64;  // 0..127
+    uint32_t acc = 0, acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const long long o = static_cast<long long>(tile / p.r_tiles) * kBM + quarter * 32 + lane;
+      const long long r0 = static_cast<long long>(tile % p.r_tiles) * p.bn;
+      // stage this tile's activation scales (and zero points) for broadcast reads
+      float* as_s = as_tile + acc * 256;
+      int* zp_s = zp_tile + acc * 256;
+      for (int i = epi_thread; i < p.bn; i += 128) {
+        const long long r = r0 + i;
+        as_s[i] = r < p.m ? p.as[r] : 0.0f;
+        zp_s[i] = (p.asymmetric && r < p.m) ? p.zp[r] : 0;
+      }
+      const bool o_ok = o < p.n;
+      const float wscale = o_ok ? p.ws[o] : 0.0f;
+      const long long rsum = (p.asymmetric && o_ok) ? p.row_sum[o] : 0;
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
+
+      if (!mbar_wait(&bars->tmem_full[acc], acc_phase, abort_flag)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after_sync();
+      for (int c = 0; c < p.bn / 32; ++c) {
+        uint32_t v[32];
+        const uint32_t taddr =
+            tmem_base + acc * 256u + static_cast<uint32_t>(c * 32) +
+            (static_cast<uint32_t>(quarter * 32) << 16);
+        tmem_ld_32x32(taddr, v);
+        tmem_ld_wait();
+        if (o_ok) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const long long r = r0 + c * 32 + j;
+            if (r < p.m) {
+              const int raw = static_cast<int>(v[j]);
+              float f;
+              if (p.asymmetric) {
+                const long long dot = static_cast<long long>(raw) - zp_s[c * 32 + j] * rsum;
+                f = __ll2float_rn(dot);
+                if (p.acc != nullptr) p.acc[r * p.n + o] = static_cast<int32_t>(dot);
+              } else {
+                f = __int2float_rn(raw);
+                if (p.acc != nullptr) p.acc[r * p.n + o] = raw;
+              }
+              p.y[r * p.ldy + o] = __fmul_rn(__fmul_rn(f, wscale), as_s[c * 32 + j]);
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      atomicExch(p.error, 3);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+size_t tc_smem_bytes(int bn) {
+  return 1024 + static_cast<size_t>(kStages) * (kBM * kBK + bn * kBK) + sizeof(TcBarriers) +
+         2 * 256 * sizeof(float) + 2 * 256 * sizeof(int) + 64;
+}
+
+}  // namespace
+
+bool int8_gemm_tc_supported(const Int8GemmArgs& a) {
+  if (a.k % 16 != 0 || a.k > 131000) return false;  // TMA row stride; int32 exactness
+  if ((reinterpret_cast<uintptr_t>(a.w) | reinterpret_cast<uintptr_t>(a.x)) & 15u) return false;
+  if (a.m > (1LL << 30) || a.n > (1LL << 30)) return false;
+  return encode_fn() != nullptr;
+}
+
+qx_status launch_int8_gemm_tc(const Int8GemmArgs& a, cudaStream_t stream) {
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  int bn = 256;
+  if (a.m < 256) bn = static_cast<int>((a.m + 31) / 32 * 32);
+  CUtensorMap map_w, map_x;
+  if (!encode_tma_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, static_cast<uint64_t>(a.k),
+                     static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k), kBK, kBM) ||
+      !encode_tma_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.x, static_cast<uint64_t>(a.k),
+                     static_cast<uint64_t>(a.m), static_cast<uint64_t>(a.k), kBK,
+                     static_cast<uint32_t>(bn))) {
+    set_last_error_text("cuTensorMapEncodeTiled failed for the W8A8 operands");
+    return QX_STATUS_DEVICE_ERROR;
+  }
+  TcParams p{};
+  p.ws = a.ws;
+  p.as = a.as;
+  p.row_sum = a.row_sum;
+  p.zp = a.zp;
+  p.y = a.y;
+  p.acc = a.acc;
+  p.m = a.m;
+  p.n = a.n;
+  p.ldy = a.ldy;
+  p.k_slabs = static_cast<int>((a.k + kBK - 1) / kBK);
+  p.bn = bn;
+  p.o_tiles = static_cast<int>((a.n + kBM - 1) / kBM);
+  p.r_tiles = static_cast<int>((a.m + bn - 1) / bn);
+  p.asymmetric = a.asymmetric ? 1 : 0;
+  p.error = ctx->flag + 1;
+
+  const size_t smem = tc_smem_bytes(bn);
+  static bool attr_set = false;
+  if (!attr_set) {
+    QX_CUDA_TRY(cudaFuncSetAttribute(int8_gemm_tc_kernel,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(tc_smem_bytes(256))));
+    attr_set = true;
+  }
+  const long long tiles = static_cast<long long>(p.o_tiles) * p.r_tiles;
+  const int grid = static_cast<int>(tiles < ctx->prop.multiProcessorCount
+                                        ? tiles
+                                        : ctx->prop.multiProcessorCount);
+  int8_gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(map_w, map_x, p);
+  count_launch();
+  QX_CUDA_TRY(cudaGetLastError());
+  return QX_STATUS_OK;
+}
+
+}  // namespace qx

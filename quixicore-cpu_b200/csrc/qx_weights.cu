@@ -1,0 +1,200 @@
+// Prepared weights: load-time re-layout of canonical GGUF blocks into device planes.
+// Counterpart of CpuPackedWeights::prepare (src/memory/packed_weights.cpp:197-278); like
+// the reference's panel build it runs once per weight matrix, outside any timed region.
+
+#include <chrono>
+#include <new>
+
+#include "qx_weights.cuh"
+
+namespace qx {
+namespace {
+
+// One thread per block. Canonical blocks are only 2-byte aligned (34 / 18 byte stride),
+// so they are read as 16-bit words; the planes are written with 16-byte stores.
+template <int FMT>
+__global__ void __launch_bounds__(256) relayout_kernel(const unsigned short* __restrict__ src,
+                                                       long long total_blocks,
+                                                       uint4* __restrict__ codes,
+                                                       unsigned short* __restrict__ scales) {
+  constexpr int kWords = FMT == QX_FORMAT_Q8_0 ? 17 : 9;  // 16-bit words per block
+  const long long blk = blockIdx.x * 256LL + threadIdx.x;
+  if (blk >= total_blocks) return;
+  const unsigned short* in = src + blk * kWords;
+  scales[blk] = in[0];
+  uint32_t w[(kWords - 1) / 2];
+#pragma unroll
+  for (int i = 0; i < (kWords - 1) / 2; ++i) {
+    w[i] = static_cast<uint32_t>(in[1 + 2 * i]) | (static_cast<uint32_t>(in[2 + 2 * i]) << 16);
+  }
+  if (FMT == QX_FORMAT_Q8_0) {
+    codes[2 * blk] = make_uint4(w[0], w[1], w[2], w[3]);
+    codes[2 * blk + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+    codes[blk] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
+}  // namespace
+
+qx_status launch_relayout(int format, const uint8_t* src, long long rows, long long nb,
+                          uint8_t* codes, unsigned short* scales, cudaStream_t stream) {
+  const long long total = rows * nb;
+  const unsigned grid = static_cast<unsigned>((total + 255) / 256);
+  if (format == QX_FORMAT_Q8_0) {
+    relayout_kernel<QX_FORMAT_Q8_0><<<grid, 256, 0, stream>>>(
+        reinterpret_cast<const unsigned short*>(src), total, reinterpret_cast<uint4*>(codes), scales);
+  } else {
+    relayout_kernel<QX_FORMAT_Q4_0><<<grid, 256, 0, stream>>>(
+        reinterpret_cast<const unsigned short*>(src), total, reinterpret_cast<uint4*>(codes), scales);
+  }
+  count_launch();
+  QX_CUDA_TRY(cudaGetLastError());
+  return QX_STATUS_OK;
+}
+
+namespace {
+
+qx_status prepare_common(int format, const void* contract, bool contract_on_device,
+                         long long rows, long long columns, long long row_begin,
+                         long long row_count, cudaStream_t stream, bool sync,
+                         qx_weights** out) {
+  const auto t0 = std::chrono::steady_clock::now();
+  if (out == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  *out = nullptr;
+  // CpuPackedWeights::prepare: null check first, then the packed-size validation
+  // (packed_weights.cpp:201-208).
+  if (contract == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  size_t contract_bytes = 0;
+  QX_TRY(validate_nk(format, rows, columns));
+  QX_TRY(packed_bytes(format, rows, columns, &contract_bytes));
+  if (row_begin < 0 || row_count <= 0 || row_begin > rows - row_count) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+
+  size_t block_bytes = 0;
+  format_info(format, &block_bytes);
+  const long long nb = columns / kBlockK;
+  const size_t shard_bytes = static_cast<size_t>(row_count) * nb * block_bytes;
+  const size_t code_bytes = static_cast<size_t>(row_count) * nb * (block_bytes - 2);
+  const size_t scale_bytes = static_cast<size_t>(row_count) * nb * 2;
+
+  auto* w = new (std::nothrow) qx_weights();
+  if (w == nullptr) return QX_STATUS_OUT_OF_MEMORY;
+  w->format = format;
+  w->device = ctx->device;
+  w->rows_total = rows;
+  w->row_begin = row_begin;
+  w->rows = row_count;
+  w->columns = columns;
+  w->blocks_per_row = nb;
+  w->block_bytes = block_bytes;
+  w->contract_bytes = shard_bytes;
+
+  auto fail = [&](qx_status status) {
+    qx_weights_destroy(w);
+    return status;
+  };
+  cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&w->codes), align_up(code_bytes, 256));
+  if (err == cudaSuccess) {
+    err = cudaMalloc(reinterpret_cast<void**>(&w->scales), align_up(scale_bytes, 256));
+  }
+  if (err != cudaSuccess) {
+    set_last_error("cudaMalloc(prepared planes)", err);
+    return fail(err == cudaErrorMemoryAllocation ? QX_STATUS_OUT_OF_MEMORY
+                                                 : QX_STATUS_DEVICE_ERROR);
+  }
+  w->prepared_bytes = code_bytes + scale_bytes;
+
+  const uint8_t* shard_src = static_cast<const uint8_t*>(contract) +
+                             static_cast<size_t>(row_begin) * nb * block_bytes;
+  void* temp = nullptr;
+  const uint8_t* device_src = shard_src;
+  if (!contract_on_device) {
+    err = cudaMalloc(&temp, align_up(shard_bytes, 256));
+    if (err != cudaSuccess) {
+      set_last_error("cudaMalloc(canonical staging)", err);
+      return fail(err == cudaErrorMemoryAllocation ? QX_STATUS_OUT_OF_MEMORY
+                                                   : QX_STATUS_DEVICE_ERROR);
+    }
+    err = cudaMemcpyAsync(temp, shard_src, shard_bytes, cudaMemcpyHostToDevice, stream);
+    if (err != cudaSuccess) {
+      set_last_error("cudaMemcpyAsync(canonical bytes)", err);
+      (void)cudaFree(temp);
+      return fail(QX_STATUS_DEVICE_ERROR);
+    }
+    device_src = static_cast<const uint8_t*>(temp);
+  }
+  qx_status status =
+      launch_relayout(format, device_src, row_count, nb, w->codes, w->scales, stream);
+  if (status == QX_STATUS_OK && (sync || temp != nullptr)) {
+    err = cudaStreamSynchronize(stream);
+    if (err != cudaSuccess) {
+      set_last_error("cudaStreamSynchronize(prepare)", err);
+      status = QX_STATUS_DEVICE_ERROR;
+    }
+  }
+  if (temp != nullptr) (void)cudaFree(temp);
+  if (status != QX_STATUS_OK) return fail(status);
+  w->preparation_ns = static_cast<uint64_t>(
+      std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0)
+          .count());
+  *out = w;
+  return QX_STATUS_OK;
+}
+
+}  // namespace
+}  // namespace qx
+
+extern "C" {
+
+qx_status qx_weights_prepare(int format, const void* contract_packed, long long rows,
+                             long long columns, long long row_begin, long long row_count,
+                             qx_weights** out) {
+  qx::DeviceContext* ctx = nullptr;
+  if (out == nullptr || contract_packed == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  QX_TRY(qx::validate_nk(format, rows, columns));
+  QX_TRY(qx::current_context(&ctx));
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  return qx::prepare_common(format, contract_packed, false, rows, columns, row_begin, row_count,
+                            ctx->stream, true, out);
+}
+
+qx_status qx_weights_prepare_dev(int format, const void* contract_packed_dev, long long rows,
+                                 long long columns, long long row_begin, long long row_count,
+                                 void* stream, qx_weights** out) {
+  return qx::prepare_common(format, contract_packed_dev, true, rows, columns, row_begin,
+                            row_count, static_cast<cudaStream_t>(stream), false, out);
+}
+
+qx_status qx_weights_get_info(const qx_weights* w, qx_weights_info* info) {
+  if (w == nullptr || info == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  info->format = w->format;
+  info->rows = w->rows;
+  info->columns = w->columns;
+  info->block_size = qx::kBlockK;
+  info->blocks_per_row = w->blocks_per_row;
+  info->block_bytes = w->block_bytes;
+  info->contract_bytes = w->contract_bytes;
+  info->prepared_bytes = w->prepared_bytes + w->dense_cache_bytes;
+  info->memory_amplification =
+      w->contract_bytes == 0 ? 0.0
+                             : static_cast<double>(info->prepared_bytes) /
+                                   static_cast<double>(w->contract_bytes);
+  info->preparation_ns = w->preparation_ns;
+  info->device = w->device;
+  info->has_dense_bf16 = w->dense_cache != nullptr ? 1 : 0;
+  return QX_STATUS_OK;
+}
+
+void qx_weights_destroy(qx_weights* w) {
+  if (w == nullptr) return;
+  if (w->codes != nullptr) (void)cudaFree(w->codes);
+  if (w->scales != nullptr) (void)cudaFree(w->scales);
+  if (w->dense_cache != nullptr) (void)cudaFree(w->dense_cache);
+  delete w;
+}
+
+}  // extern "C"

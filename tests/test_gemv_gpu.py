@@ -1,0 +1,181 @@
+"""Parity of the q8_0 / q4_0 GEMV and batched qgemm CUDA path with the CPU oracle.
+Every call goes through the C ABI (ctypes)."""
+
+import numpy as np
+import pytest
+
+from conftest import assert_bit_equal, assert_close_f32_path, assert_close_ref_test
+
+pytestmark = pytest.mark.gpu
+Q8_0, Q4_0 = 0, 1
+DIST = {Q8_0: (0.001, 0.02), Q4_0: (0.002, 0.04)}
+
+
+def _ladder(wl, n, k, seed):
+    values = wl.xorshift_uniform(seed, n * k + k)
+    return values[:n * k].reshape(n, k).copy(), values[n * k:].copy()
+
+
+def test_q8_0_reference_ladder(qx, orc, wl, golden, gold_inputs):
+    """Shapes, seeds and bounds of tests/correctness/test_qgemv.cpp:229-297."""
+    for n, k in gold_inputs.Q8_LADDER:
+        w, x = _ladder(wl, n, k, (0x9E3779B9 ^ (n * 131 + k)) & 0xFFFFFFFF)
+        _, packed = orc.pack(Q8_0, w, n, k)
+        status, y = qx.qgemv(Q8_0, packed, x, n, k)
+        assert status == qx.OK, qx.last_error()
+        assert_close_f32_path(y, golden["default"][f"q8_{n}x{k}_y"], f"q8_0 {n}x{k} vs reference f32")
+        _, y64 = orc.qgemm_f64(Q8_0, packed, x.reshape(1, k), 1, n, k)
+        assert_close_ref_test(y, y64[0], f"q8_0 {n}x{k} vs float64")
+        status, y2 = qx.qgemv(Q8_0, packed, x, n, k)
+        assert_bit_equal(y, y2, "rerun determinism")  # test_qgemv.cpp:273-276
+
+
+def test_q4_0_reference_case(qx, orc, wl, golden):
+    n, k = 33, 512
+    w, x = _ladder(wl, n, k, 0xD1B54A32)
+    _, packed = orc.pack(Q4_0, w, n, k)
+    status, y = qx.qgemv(Q4_0, packed, x, n, k)
+    assert status == qx.OK, qx.last_error()
+    assert_close_f32_path(y, golden["default"]["q4_33x512_y"], "q4_0 vs reference avx2 path")
+    assert_close_f32_path(y, golden["forced_ref"]["q4_33x512_y"], "q4_0 vs reference portable path")
+    _, y64 = orc.qgemm_f64(Q4_0, packed, x.reshape(1, k), 1, n, k)
+    assert_close_ref_test(y, y64[0], "q4_0 vs float64")
+
+
+def test_subnormal_scale_block(qx, orc, golden):
+    packed = golden["default"]["q8_subnormal_packed"]
+    status, y = qx.qgemv(Q8_0, packed, np.ones(32, np.float32), 1, 32)
+    assert status == qx.OK
+    _, dq = orc.unpack(Q8_0, packed, 1, 32)
+    assert dq[0, 0] != 0 and abs(y[0] - 32.0 * dq[0, 0]) < 1e-6
+
+
+@pytest.mark.parametrize("name", ["cfg0_q8_0_gemv", "cfg1_q4_0_gemv"])
+def test_decode_gemv_full_config(qx, orc, wl, name):
+    c = wl.CONFIGS[name]
+    fmt, n, k = c["fmt"], c["n"], c["k"]
+    packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0)
+    x = wl.activations_f32(1, k, seed=0)
+    weights = qx.PackedWeights()
+    assert weights.prepare(fmt, packed, n, k) == qx.OK, qx.last_error()
+    info = weights.info()
+    assert info["prepared_bytes"] == info["contract_bytes"] == packed.size  # no amplification
+    status, y = weights.qgemm_prepacked(x, 1)
+    assert status == qx.OK, qx.last_error()
+    for variant in (0, 1):
+        _, ref = orc.qgemm(fmt, packed, x, 1, n, k, q4_variant=variant)
+        assert_close_f32_path(y, ref, f"{name} variant {variant}")
+    # the drop-in entry point on canonical host bytes gives the same bits
+    status, y_host = qx.qgemv(fmt, packed, x[0], n, k)
+    assert status == qx.OK
+    assert_bit_equal(y_host, y[0], "qgemv == qgemm_prepacked")
+
+
+@pytest.mark.parametrize("fmt", [Q8_0, Q4_0])
+def test_batched_rows_equal_single_gemv(qx, orc, wl, fmt):
+    """qgemm is M independent GEMVs in the reference (qgemm_ref.cpp:156-162)."""
+    n, k = 1536, 8192
+    packed = wl.packed_blocks(fmt, n, k, *DIST[fmt], seed=3)
+    weights = qx.PackedWeights()
+    assert weights.prepare(fmt, packed, n, k) == qx.OK
+    x = wl.activations_f32(32, k, seed=3)
+    singles = [weights.qgemm_prepacked(x[r:r + 1].copy(), 1)[1][0] for r in range(32)]
+    for m in (1, 4, 8, 16, 32):
+        status, y = weights.qgemm_prepacked(x[:m].copy(), m)
+        assert status == qx.OK, qx.last_error()
+        for r in range(m):
+            assert_bit_equal(y[r], singles[r], f"fmt {fmt} m={m} row {r}")
+    _, ref = orc.qgemm(fmt, packed, x[:4].copy(), 4, n, k, q4_variant=0)
+    assert_close_f32_path(np.stack(singles[:4]), ref, "batched vs oracle")
+
+
+@pytest.mark.parametrize("fmt", [Q8_0, Q4_0])
+def test_ragged_shapes(qx, orc, wl, fmt):
+    for n, k, m in [(1, 32, 1), (3, 64, 2), (5, 96, 1), (33, 160, 3), (7, 1024, 1), (257, 2080, 1),
+                    (19, 3072, 1), (40, 14336, 1), (2, 16384, 1), (3, 16416, 2)]:
+        packed = wl.packed_blocks(fmt, n, k, *DIST[fmt], seed=n * 7 + k)
+        x = wl.activations_f32(m, k, seed=k)
+        status, y = qx.qgemm(fmt, packed, x, m, n, k)
+        assert status == qx.OK, qx.last_error()
+        _, ref = orc.qgemm(fmt, packed, x, m, n, k, q4_variant=0)
+        assert_close_f32_path(y, ref, f"fmt {fmt} {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("fmt", [Q8_0, Q4_0])
+def test_row_sharded_weights_match_unsharded(qx, wl, fmt):
+    n, k = 2048 + 64, 4096
+    packed = wl.packed_blocks(fmt, n, k, *DIST[fmt], seed=9)
+    x = wl.activations_f32(1, k, seed=9)
+    full = qx.PackedWeights()
+    assert full.prepare(fmt, packed, n, k) == qx.OK
+    _, y_full = full.qgemm_prepacked(x, 1)
+    for world in (2, 4, 8):
+        pieces = []
+        for rank in range(world):
+            begin = n * rank // world
+            count = n * (rank + 1) // world - begin
+            shard = qx.PackedWeights()
+            assert shard.prepare(fmt, packed, n, k, begin, count) == qx.OK
+            assert shard.info()["rows"] == count
+            pieces.append(shard.qgemm_prepacked(x, 1)[1][0])
+        assert_bit_equal(np.concatenate(pieces), y_full[0], f"world {world}")
+    bad = qx.PackedWeights()
+    assert bad.prepare(fmt, packed, n, k, n - 3, 4) == qx.INVALID_SHAPE
+
+
+def test_activation_edge_cases(qx, orc, wl):
+    fmt, n, k = Q4_0, 64, 4096
+    packed = wl.packed_blocks(fmt, n, k, *DIST[fmt], seed=4)
+    weights = qx.PackedWeights()
+    assert weights.prepare(fmt, packed, n, k) == qx.OK
+    zero = np.zeros((1, k), np.float32)
+    assert np.all(weights.qgemm_prepacked(zero, 1)[1] == 0.0)
+    # wide dynamic range inside and across blocks; one block of exact powers of two
+    x = wl.activations_f32(1, k, seed=5)
+    x[0, :32] *= 1e-20
+    x[0, 32:64] *= 1e12
+    x[0, 64:96] = 2.0 ** np.arange(-16, 16)
+    x[0, 96] = 8388607.0
+    x[0, 128:160] = 0.0
+    _, y = weights.qgemm_prepacked(x, 1)
+    _, y64 = orc.qgemm_f64(fmt, packed, x, 1, n, k)
+    _, ref = orc.qgemm(fmt, packed, x, 1, n, k)
+    scale = np.abs(y64).max()
+    # not worse than the reference's own f32 path on the same input (both vs float64)
+    assert np.abs(y - y64).max() <= max(2.0 * np.abs(ref - y64).max(), 1e-6 * scale)
+
+
+def test_device_pointer_entry_with_row_stride(qx, orc, wl):
+    import torch
+    fmt, n, k, m = Q8_0, 512, 2048, 3
+    packed = wl.packed_blocks(fmt, n, k, *DIST[fmt], seed=12)
+    x = wl.activations_f32(m, k, seed=12)
+    weights = qx.PackedWeights()
+    assert weights.prepare(fmt, torch.from_numpy(packed).cuda(), n, k) == qx.OK  # device bytes
+    ldy = n + 40
+    y = torch.full((m, ldy), -7.0, device="cuda")
+    assert weights.qgemm_dev(torch.from_numpy(x).cuda(), y, m, ldy) == qx.OK
+    torch.cuda.synchronize()
+    got = y.cpu().numpy()
+    _, ref = orc.qgemm(fmt, packed, x, m, n, k)
+    assert_close_f32_path(got[:, :n], ref, "device entry")
+    assert np.all(got[:, n:] == -7.0), "wrote outside its slice"
+
+
+def test_bf16_activation_entry(qx, orc, wl):
+    import torch
+    fmt, n, k, m = Q4_0, 256, 1024, 80
+    packed = wl.packed_blocks(fmt, n, k, *DIST[fmt], seed=13)
+    xb = wl.to_bf16_bits(wl.activations_f32(m, k, seed=13))
+    weights = qx.PackedWeights()
+    assert weights.prepare(fmt, packed, n, k) == qx.OK
+    y = torch.zeros((m, n), device="cuda")
+    x_dev = torch.from_numpy(xb.view(np.int16)).cuda()
+    assert weights.qgemm_bf16_dev(x_dev, y, m) == qx.OK, qx.last_error()
+    torch.cuda.synchronize()
+    _, ref = orc.qgemm(fmt, packed, wl.bf16_bits_to_f32(xb), m, n, k)
+    # stated tolerance of the 4-bit prefill GEMM: 1e-2 relative, with an absolute floor of
+    # 1e-2 of the row's rms for outputs near zero
+    got = y.cpu().numpy()
+    floor = 1e-2 * np.sqrt((ref.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
+    assert np.all(np.abs(got - ref) <= 1e-2 * np.abs(ref) + floor)
