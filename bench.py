@@ -245,7 +245,7 @@ def run_qx_arm(args):
 
     graph = None
     chunk = GRAPH_CHUNK - GRAPH_CHUNK % copies or copies
-    if world == 1 and args.steps >= chunk:
+    if world == 1 and args.steps >= chunk and not args.no_graph:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             for i in range(chunk):
@@ -321,7 +321,7 @@ def run_qx_arm(args):
                      "note": "achieved = algorithmic bytes / whole step time (activation "
                              "quantizer launch and launch gaps included)"},
     }
-    if world == 1:
+    if world == 1 and not args.no_extra:
         line["cpu_baseline"] = cpu_baseline(wl, c)
         try:
             line["extra"] = extra_measurements(qx, wl, torch, hbm_peak)
@@ -412,6 +412,9 @@ def main():
     parser.add_argument("--steps", type=int, default=20000)
     parser.add_argument("--warmup", type=int, default=200)
     parser.add_argument("--impl", default="qx", choices=["qx", "reference"])
+    parser.add_argument("--no-extra", action="store_true",
+                        help="skip the non-headline configurations and the CPU baseline (profiling runs)")
+    parser.add_argument("--no-graph", action="store_true", help="launch every step eagerly")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "qx" else args.warmup
     if args.impl == "reference":
