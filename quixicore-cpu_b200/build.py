@@ -17,6 +17,8 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
     "-I", os.path.join(ROOT, "include"), "-I", CSRC,
 ]
+# developer switch: QX_B200_DEFINES="-DQX_GEMV_PROFILE" adds per-role wait accounting
+NVCC_FLAGS += os.environ.get("QX_B200_DEFINES", "").split()
 
 
 def sources():

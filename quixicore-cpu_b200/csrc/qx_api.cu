@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstring>
 
+#include "qx_gemv_tc.cuh"
 #include "qx_int8_gemm.cuh"
 #include "qx_weights.cuh"
 
@@ -49,6 +50,9 @@ qx_status check_device_error(DeviceContext* ctx) {
   QX_CUDA_TRY(cudaMemcpy(words, ctx->flag, sizeof words, cudaMemcpyDeviceToHost));
   if (words[1] != 0) {
     (void)cudaMemset(ctx->flag, 0, 8);
+    if (ctx->workspace.base != nullptr) {  // an aborted kernel may leave counters behind
+      (void)cudaMemset(ctx->workspace.base, 0, kWorkspaceCounterBytes);
+    }
     set_last_error_text("a tensor-core kernel gave up a bounded wait (pipeline stalled)");
     return QX_STATUS_DEVICE_ERROR;
   }
@@ -151,8 +155,7 @@ qx_status qx_qgemv(int format, const void* packed, const float* x, float* y, lon
 }
 
 const char* qx_qgemv_variant(int format) {
-  if (format == QX_FORMAT_Q8_0) return "sm100a_dp4a_q8_0";
-  if (format == QX_FORMAT_Q4_0) return "sm100a_dp4a_q4_0";
+  if (format == QX_FORMAT_Q8_0 || format == QX_FORMAT_Q4_0) return gemv_variant_name();
   return "unsupported";
 }
 
@@ -176,7 +179,7 @@ qx_status qx_qgemm_prepacked(const qx_weights* weights, const float* x, float* y
                           workspace != nullptr ? workspace : &ctx->workspace, ctx->stream));
   QX_TRY(d2h(y, st.at(off_y), y_bytes, ctx->stream));
   QX_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-  return QX_STATUS_OK;
+  return check_device_error(ctx);
 }
 
 qx_status qx_qgemm_prepacked_dev(const qx_weights* weights, const float* x_dev, float* y_dev,

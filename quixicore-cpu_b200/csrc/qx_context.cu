@@ -128,6 +128,7 @@ qx_status qx_workspace::reserve(size_t bytes) {
   const size_t want = qx::align_up(bytes + bytes / 8, 1 << 20);
   QX_CUDA_TRY(cudaMalloc(&base, want));
   capacity = want;
+  QX_CUDA_TRY(cudaMemset(base, 0, qx::kWorkspaceCounterBytes));
   return QX_STATUS_OK;
 }
 

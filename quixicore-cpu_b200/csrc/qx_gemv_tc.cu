@@ -1,0 +1,706 @@
+// Decode GEMV / small-batch qgemm on the tensor cores (tcgen05 kind::i8 + TMEM).
+//
+// Why tensor cores for a GEMV: at HBM speed one SM must consume ~22 bytes of packed
+// weights per clock, i.e. 1.2 q4_0 blocks of 32 weights. Dequantising and multiplying
+// those on the CUDA cores needs ~90 instructions per block -- the whole issue budget.
+// Here the 8-bit products run on the tensor core instead: the weight codes are the MMA's
+// A operand (128 weight rows x 32 codes of one block), the activation digits (three
+// balanced base-256 digits per activation, see qx_gemv.cuh) are the B operand (8..96
+// digit columns), and one MMA per block leaves the three exact integer block sums of 128
+// rows in TMEM. The CUDA cores only combine the digits and apply the fp16 block scale:
+// ~10 instructions per block.
+//
+// One K-slab (4 blocks = 128 elements of 128 rows) per pipeline stage:
+//   q8_0  the 16 KiB code slab is one TMA tile (128-byte swizzle) straight from the panel
+//   q4_0  eight producer warps read the 8 KiB packed slab with coalesced 16-byte loads
+//         (register-prefetched several slabs ahead), split the nibbles and store the
+//         unsigned codes into the same swizzled layout
+//   both  the activation digit slab (TMA) and the slab's 512 fp16 scales (bulk copy)
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (one thread), 2-5 = epilogue (thread =
+// weight row, accumulators in registers), 6-13 = q4_0 unpack producers.
+//
+// Work split and summation order. K is cut into units of `unit_slabs` slabs, a function of
+// K alone. A row's result is defined as the sum, in ascending order, of its unit sums,
+// each accumulated block by block from zero -- so it does not depend on the number of
+// rows, on how rows are sharded over GPUs, on the batch size or on the SM count. The
+// (row tile, unit) sequence is cut into equal contiguous ranges, one per persistent CTA,
+// so every SM streams the same number of bytes. A CTA that owns all units of a tile adds
+// them in registers; a tile shared by several CTAs goes through per-unit partial sums in
+// scratch memory and is finished, in the same order, by the last CTA to arrive.
+
+#include <cuda.h>
+
+#include "qx_gemv_tc.cuh"
+#include "qx_sm100.cuh"
+
+namespace qx {
+namespace {
+
+using namespace sm100;
+
+constexpr int kABytes = kTileRows * 128;  // unpacked code slab in shared memory
+constexpr int kSBytes = kSlabBlocks * kTileRows * 2;
+constexpr int kUnpackWarps = 8;
+constexpr int kPrefetch = 6;  // q4_0 slabs held in registers ahead of the smem ring
+
+template <int NMMA>
+struct TcGeom {
+  static constexpr int kBBytes = NMMA * 128;
+  static constexpr int kMaxM = NMMA / kDigitStride;
+  static constexpr int kXBytes = kMaxM * kSlabBlocks * 16;  // block constants of one slab
+  static constexpr int kStageBytes = kABytes + kBBytes + kSBytes + kXBytes + (1024 - kXBytes % 1024) % 1024;
+  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  static constexpr int kColStride = NMMA <= 32 ? 32 : NMMA;  // TMEM columns per block
+  static constexpr int kBlocksPerT = NMMA <= 64 ? 4 : 2;   // blocks per TMEM stage
+  static constexpr int kTCols = kBlocksPerT * kColStride;  // 128 or 256
+  static constexpr int kTStages = 512 / kTCols;            // 4 or 2
+  // blocks whose TMEM loads are issued before one wait (register budget: 64 values)
+  static constexpr int kLdBatch = NMMA <= 16 ? 4 : (NMMA == 32 ? 2 : 1);
+};
+
+struct GemvTcParams {
+  const uint4* codes;            // q4_0 producers read the packed panel directly
+  const unsigned short* scales;  // panel [tile][slab][4][128]
+  const XConst* xc;              // [slab][m][4]
+  float* y;
+  float* partial;                // [tile][unit][m][128]
+  int* counters;                 // [tile]
+  int* error;
+  long long ldy, rows;
+  int m, nbpad, slabs, tiles;
+  int unit_slabs, units_per_tile;  // K split: units of unit_slabs slabs
+  long long total_units;
+  long long* debug;  // [ctas][16] cycle counters, profiling builds only
+};
+
+template <int NMMA>
+struct __align__(8) GemvBarriers {
+  uint64_t full[TcGeom<NMMA>::kStages];
+  uint64_t empty[TcGeom<NMMA>::kStages];
+  uint64_t tmem_full[TcGeom<NMMA>::kTStages];
+  uint64_t tmem_empty[TcGeom<NMMA>::kTStages];
+  uint32_t tmem_base;
+  int abort_flag;
+  int last_flag;
+};
+
+__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gsrc, uint32_t bytes,
+                                              uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes),
+      "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// Optional per-role wait accounting (build with -DQX_GEMV_PROFILE): cycles spent in each
+// kind of barrier wait, written per CTA to GemvTcParams::debug. Compiled out otherwise.
+#ifdef QX_GEMV_PROFILE
+#define QX_PROF_DECL(name) long long name = 0
+#define QX_PROF_WAIT(counter, expr)            \
+  [&]() {                                      \
+    const long long qx_t0_ = clock64();        \
+    const bool qx_ok_ = (expr);                \
+    counter += clock64() - qx_t0_;             \
+    return qx_ok_;                             \
+  }()
+#define QX_PROF_STORE(slot, value) \
+  if (p.debug != nullptr) p.debug[blockIdx.x * 16 + (slot)] = (value)
+#define QX_PROF_NOW() clock64()
+#else
+#define QX_PROF_DECL(name)
+#define QX_PROF_WAIT(counter, expr) (expr)
+#define QX_PROF_STORE(slot, value)
+#define QX_PROF_NOW() 0
+#endif
+
+template <int N>
+__device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N]);
+template <>
+__device__ __forceinline__ void tmem_ld_cols<8>(uint32_t taddr, uint32_t (&v)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]),
+                 "=r"(v[6]), "=r"(v[7])
+               : "r"(taddr)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld_cols<16>(uint32_t taddr, uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
+        "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
+        "=r"(v[14]), "=r"(v[15])
+      : "r"(taddr)
+      : "memory");
+}
+template <>
+__device__ __forceinline__ void tmem_ld_cols<32>(uint32_t taddr, uint32_t (&v)[32]) {
+  tmem_ld_32x32(taddr, v);
+}
+
+// start of CTA c's slab range
+__device__ __forceinline__ long long range_start(long long c, long long total, long long ctas) {
+  return c * total / ctas;
+}
+template <int FMT, int NMMA>
+__global__ void __launch_bounds__(FMT == QX_FORMAT_Q4_0 ? 448 : 192, 1)
+gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+               const GemvTcParams p) {
+  using G = TcGeom<NMMA>;
+  constexpr bool kQ4 = FMT == QX_FORMAT_Q4_0;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  auto* bars = reinterpret_cast<GemvBarriers<NMMA>*>(smem + G::kStages * G::kStageBytes);
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < G::kStages; ++s) {
+      mbar_init(&bars->full[s], kQ4 ? 1 + kUnpackWarps : 1);
+      mbar_init(&bars->empty[s], 1 + 4);  // MMA commit + four epilogue warps (scales read)
+    }
+    for (int t = 0; t < G::kTStages; ++t) {
+      mbar_init(&bars->tmem_full[t], 1);
+      mbar_init(&bars->tmem_empty[t], 4);
+    }
+    bars->abort_flag = 0;
+    bars->last_flag = 0;
+    mbar_fence_init();
+    if (!kQ4) prefetch_tensormap(&map_a);
+    prefetch_tensormap(&map_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = bars->tmem_base;
+
+  const long long u_begin = range_start(blockIdx.x, p.total_units, gridDim.x);
+  const long long u_end = range_start(blockIdx.x + 1LL, p.total_units, gridDim.x);
+  // units tile every row tile's slabs contiguously, so a CTA's units are one contiguous
+  // range of global slabs (tile * slabs + slab)
+  long long s_begin = 0, s_end = 0;
+  if (u_end > u_begin) {
+    const long long last = u_end - 1;
+    const int last_end = static_cast<int>(last % p.units_per_tile + 1) * p.unit_slabs;
+    s_begin = (u_begin / p.units_per_tile) * p.slabs + (u_begin % p.units_per_tile) * p.unit_slabs;
+    s_end = (last / p.units_per_tile) * p.slabs + (last_end < p.slabs ? last_end : p.slabs);
+  }
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      QX_PROF_DECL(w_empty);
+      const long long t_start = QX_PROF_NOW();
+      int slab = static_cast<int>(s_begin % p.slabs);
+      for (long long gs = s_begin; gs < s_end; ++gs, slab = slab + 1 == p.slabs ? 0 : slab + 1) {
+        if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag))) {
+          ok = false;
+          break;
+        }
+        uint8_t* st = smem + stage * G::kStageBytes;
+        const uint32_t x_bytes = static_cast<uint32_t>(p.m) * kSlabBlocks * 16u;
+        mbar_arrive_expect_tx(&bars->full[stage],
+                              (kQ4 ? 0 : kABytes) + G::kBBytes + kSBytes + x_bytes);
+        if (!kQ4) {
+          tma_load_2d(st, &map_a, &bars->full[stage], 0,
+                      static_cast<int>(gs * kTileRows));
+        }
+        tma_load_2d(st + kABytes, &map_b, &bars->full[stage], slab * kSlabK, 0);
+        bulk_copy_g2s(st + kABytes + G::kBBytes, p.scales + gs * (kSlabBlocks * kTileRows),
+                      kSBytes, &bars->full[stage]);
+        bulk_copy_g2s(st + kABytes + G::kBBytes + kSBytes,
+                      p.xc + static_cast<long long>(slab) * p.m * kSlabBlocks, x_bytes,
+                      &bars->full[stage]);
+        if (++stage == G::kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      QX_PROF_STORE(0, w_empty);
+      QX_PROF_STORE(1, QX_PROF_NOW() - t_start);
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error, 11);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------
+    if (elect_one()) {
+      const uint32_t idesc = (2u << 4) | ((kQ4 ? 0u : 1u) << 7) | (1u << 10) |
+                             (static_cast<uint32_t>(NMMA >> 3) << 17) |
+                             (static_cast<uint32_t>(kTileRows >> 4) << 24);
+      uint32_t stage = 0, phase = 0, ts = 0, tphase = 0;
+      bool ok = true;
+      QX_PROF_DECL(w_full);
+      QX_PROF_DECL(w_tempty);
+      for (long long gs = s_begin; gs < s_end && ok; ++gs) {
+        if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->full[stage], phase, abort_flag))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t sa = smem_u32(smem + stage * G::kStageBytes);
+        const uint64_t a_desc = make_sw128_kmajor_desc(sa);
+        const uint64_t b_desc = make_sw128_kmajor_desc(sa + kABytes);
+#pragma unroll
+        for (int j = 0; j < kSlabBlocks; ++j) {
+          if (j % G::kBlocksPerT == 0) {
+            if (!QX_PROF_WAIT(w_tempty, mbar_wait(&bars->tmem_empty[ts], tphase ^ 1u, abort_flag))) {
+              ok = false;
+              break;
+            }
+            tc_fence_after_sync();
+          }
+          const uint32_t d_tmem = tmem_base + ts * G::kTCols + (j % G::kBlocksPerT) * G::kColStride;
+          // one block = 32 bytes of K inside the swizzle atom: +2 in the (addr >> 4) field
+          mma_i8_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * j),
+                    b_desc + static_cast<uint64_t>(2 * j), idesc, 0u);
+          if (j % G::kBlocksPerT == G::kBlocksPerT - 1) {
+            tc_commit(&bars->tmem_full[ts]);
+            if (++ts == G::kTStages) {
+              ts = 0;
+              tphase ^= 1u;
+            }
+          }
+        }
+        if (!ok) break;
+        tc_commit(&bars->empty[stage]);
+        if (++stage == G::kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      QX_PROF_STORE(2, w_full);
+      QX_PROF_STORE(3, w_tempty);
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error, 12);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------ epilogue ----------------------------------
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int epi_thread = threadIdx.x - 64;
+    float acc[G::kMaxM], total[G::kMaxM];  // current unit; units of a tile this CTA owns
+#pragma unroll
+    for (int m = 0; m < G::kMaxM; ++m) acc[m] = total[m] = 0.0f;
+    int units_written = 0;
+    uint32_t stage = 0, phase = 0, ts = 0, tphase = 0;
+    bool ok = true;
+    QX_PROF_DECL(w_tfull);
+    QX_PROF_DECL(w_sfull);
+    const long long t_start = QX_PROF_NOW();
+    int tile = static_cast<int>(s_begin / p.slabs);
+    int slab = static_cast<int>(s_begin - static_cast<long long>(tile) * p.slabs);
+    int unit = slab / p.unit_slabs;
+    int slab_in_unit = slab - unit * p.unit_slabs;
+    for (long long gs = s_begin; gs < s_end && ok; ++gs) {
+      const uint8_t* stage_base = smem + stage * G::kStageBytes;
+      const unsigned short* sc =
+          reinterpret_cast<const unsigned short*>(stage_base + kABytes + G::kBBytes);
+      const int4* xcs = reinterpret_cast<const int4*>(stage_base + kABytes + G::kBBytes + kSBytes);
+      constexpr int kChunk = NMMA <= 32 ? NMMA : 32;
+      constexpr int kChunksPerBlock = NMMA / kChunk;
+      float dsc[kSlabBlocks];
+#pragma unroll
+      for (int jb = 0; jb < kSlabBlocks; jb += G::kLdBatch) {
+        if (jb % G::kBlocksPerT == 0) {
+          if (!QX_PROF_WAIT(w_tfull, mbar_wait(&bars->tmem_full[ts], tphase, abort_flag))) {
+            ok = false;
+            break;
+          }
+          tc_fence_after_sync();
+          if (jb == 0) {
+            // the stage's barrier completed before the MMAs ran; waiting on it here makes
+            // the bulk-copied scales and block constants visible to this thread
+            if (!QX_PROF_WAIT(w_sfull, mbar_wait(&bars->full[stage], phase, abort_flag))) {
+              ok = false;
+              break;
+            }
+#pragma unroll
+            for (int j = 0; j < kSlabBlocks; ++j) {
+              dsc[j] = half_bits_to_float(sc[j * kTileRows + row_in_tile]);
+            }
+          }
+        }
+#pragma unroll
+        for (int ch = 0; ch < kChunksPerBlock; ch += 2) {
+          // issue the loads of this batch (up to 64 values), then wait once
+          uint32_t v[G::kLdBatch * (kChunksPerBlock > 1 ? 2 : 1)][kChunk];
+#pragma unroll
+          for (int jj = 0; jj < G::kLdBatch; ++jj) {
+            const int j = jb + jj;
+            const uint32_t taddr = tmem_base + ts * G::kTCols +
+                                   (j % G::kBlocksPerT) * G::kColStride +
+                                   (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll
+            for (int c = 0; c < (kChunksPerBlock > 1 ? 2 : 1); ++c) {
+              const int c0 = (ch + c) * kChunk;
+              if (c0 < kDigitStride * p.m) {  // warp-uniform: later columns are unused
+                tmem_ld_cols<kChunk>(taddr + c0, v[jj * (kChunksPerBlock > 1 ? 2 : 1) + c]);
+              }
+            }
+          }
+          tmem_ld_wait();
+          const bool last_of_tstage =
+              (jb + G::kLdBatch) % G::kBlocksPerT == 0 && ch + 2 >= kChunksPerBlock;
+          if (last_of_tstage) {  // values are in registers: hand the TMEM stage back now
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->tmem_empty[ts]);
+          }
+#pragma unroll
+          for (int jj = 0; jj < G::kLdBatch; ++jj) {
+            const int j = jb + jj;
+#pragma unroll
+            for (int c = 0; c < (kChunksPerBlock > 1 ? 2 : 1); ++c) {
+              const int c0 = (ch + c) * kChunk;
+#pragma unroll
+              for (int mm = 0; mm < kChunk / kDigitStride; ++mm) {
+                const int m = c0 / kDigitStride + mm;  // columns 4m..4m+2 hold its digits
+                if (m < p.m) {
+                  const int4 raw = xcs[m * kSlabBlocks + j];
+                  const uint32_t* vv4 = v[jj * (kChunksPerBlock > 1 ? 2 : 1) + c];
+                  const int s0 = static_cast<int>(vv4[kDigitStride * mm]);
+                  const int s1 = static_cast<int>(vv4[kDigitStride * mm + 1]);
+                  const int s2 = static_cast<int>(vv4[kDigitStride * mm + 2]);
+                  const int u = s1 * 256 + s0 - (kQ4 ? raw.y : 0);
+                  const int hi = s2 - (kQ4 ? raw.z : 0);
+                  acc[m] = fmaf(combine_digits(u, hi), __fmul_rn(dsc[j], __int_as_float(raw.x)),
+                                acc[m]);
+                }
+              }
+            }
+          }
+          if (last_of_tstage) {
+            if (++ts == G::kTStages) {
+              ts = 0;
+              tphase ^= 1u;
+            }
+          }
+        }
+      }
+      if (!ok) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->empty[stage]);  // scales / constants consumed
+      if (++stage == G::kStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+
+      // ---- unit / tile boundaries ----
+      const bool unit_end = slab_in_unit + 1 == p.unit_slabs || slab == p.slabs - 1;
+      if (unit_end) {
+        const long long tile_first = gs - slab;
+        const bool owns_tile = s_begin <= tile_first && s_end >= tile_first + p.slabs;
+        if (owns_tile) {
+#pragma unroll
+          for (int m = 0; m < G::kMaxM; ++m) {
+            total[m] += acc[m];
+            acc[m] = 0.0f;
+          }
+        } else {
+          float* mine = p.partial +
+                        ((static_cast<long long>(tile) * p.units_per_tile + unit) * p.m) * kTileRows;
+#pragma unroll
+          for (int m = 0; m < G::kMaxM; ++m) {
+            if (m < p.m) mine[m * kTileRows + row_in_tile] = acc[m];
+            acc[m] = 0.0f;
+          }
+          ++units_written;
+        }
+        const bool share_end = slab == p.slabs - 1 || gs == s_end - 1;
+        if (share_end) {
+          const long long row = static_cast<long long>(tile) * kTileRows + row_in_tile;
+          if (owns_tile) {
+            if (row < p.rows) {
+#pragma unroll
+              for (int m = 0; m < G::kMaxM; ++m)
+                if (m < p.m) p.y[m * p.ldy + row] = total[m];
+            }
+          } else {
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (epi_thread == 0) {
+              const int old = atomicAdd(p.counters + tile, units_written);
+              const int last = old + units_written == p.units_per_tile ? 1 : 0;
+              if (last) p.counters[tile] = 0;  // ready for the next launch
+              bars->last_flag = last;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (bars->last_flag != 0) {
+              __threadfence();
+              const float* base =
+                  p.partial + (static_cast<long long>(tile) * p.units_per_tile * p.m) * kTileRows;
+#pragma unroll
+              for (int m = 0; m < G::kMaxM; ++m) {
+                if (m < p.m) {
+                  float sum = 0.0f;
+                  for (int u = 0; u < p.units_per_tile; ++u) {
+                    sum += __ldcg(base + (static_cast<long long>(u) * p.m + m) * kTileRows +
+                                  row_in_tile);
+                  }
+                  if (row < p.rows) p.y[m * p.ldy + row] = sum;
+                }
+              }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag is reused
+          }
+          units_written = 0;
+#pragma unroll
+          for (int m = 0; m < G::kMaxM; ++m) total[m] = 0.0f;
+        }
+      }
+      // advance (tile, slab, unit) without divisions
+      if (++slab == p.slabs) {
+        slab = 0;
+        ++tile;
+        unit = 0;
+        slab_in_unit = 0;
+      } else if (++slab_in_unit == p.unit_slabs) {
+        slab_in_unit = 0;
+        ++unit;
+      }
+    }
+    if (epi_thread == 0) {
+      QX_PROF_STORE(4, w_tfull);
+      QX_PROF_STORE(5, w_sfull);
+      QX_PROF_STORE(6, QX_PROF_NOW() - t_start);
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      atomicExch(p.error, 13);
+    }
+  } else if (kQ4) {
+    // ------------------------------ q4_0 unpack producers ---------------------
+    const int pt = threadIdx.x - 6 * 32;  // 0..255: items pt and pt + 256 of each slab
+    uint4 buf[kPrefetch][2];
+#pragma unroll
+    for (int i = 0; i < kPrefetch; ++i) {
+      const long long gs = s_begin + i;
+      if (gs < s_end) {
+        buf[i][0] = __ldcs(p.codes + gs * 512 + pt);
+        buf[i][1] = __ldcs(p.codes + gs * 512 + 256 + pt);
+      }
+    }
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    QX_PROF_DECL(w_empty);
+    const long long t_start = QX_PROF_NOW();
+    for (long long base = s_begin; base < s_end && ok; base += kPrefetch) {
+#pragma unroll
+      for (int i = 0; i < kPrefetch; ++i) {
+        const long long gs = base + i;
+        if (gs < s_end && ok) {
+          if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag))) {
+            ok = false;
+          } else {
+            uint8_t* a_smem = smem + stage * G::kStageBytes;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int item = pt + h * 256;
+              const int r = item >> 2, j = item & 3;
+              const uint4 w = buf[i][h];
+              uint4 lo, hi;
+              lo.x = w.x & 0x0F0F0F0Fu; hi.x = (w.x >> 4) & 0x0F0F0F0Fu;
+              lo.y = w.y & 0x0F0F0F0Fu; hi.y = (w.y >> 4) & 0x0F0F0F0Fu;
+              lo.z = w.z & 0x0F0F0F0Fu; hi.z = (w.z >> 4) & 0x0F0F0F0Fu;
+              lo.w = w.w & 0x0F0F0F0Fu; hi.w = (w.w >> 4) & 0x0F0F0F0Fu;
+              // row r of the slab: 128 bytes, 16-byte chunk c stored at c ^ (r & 7)
+              uint8_t* rowp = a_smem + r * 128;
+              *reinterpret_cast<uint4*>(rowp + (((2 * j) ^ (r & 7)) << 4)) = lo;      // elements 0..15
+              *reinterpret_cast<uint4*>(rowp + (((2 * j + 1) ^ (r & 7)) << 4)) = hi;  // 16..31
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->full[stage]);
+            if (++stage == G::kStages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+            const long long next = gs + kPrefetch;
+            if (next < s_end) {
+              buf[i][0] = __ldcs(p.codes + next * 512 + pt);
+              buf[i][1] = __ldcs(p.codes + next * 512 + 256 + pt);
+            }
+          }
+        }
+      }
+    }
+    if (pt == 0) {
+      QX_PROF_STORE(7, w_empty);
+      QX_PROF_STORE(8, QX_PROF_NOW() - t_start);
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      atomicExch(p.error, 14);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int NMMA>
+constexpr size_t gemv_smem_bytes() {
+  return 1024 + static_cast<size_t>(TcGeom<NMMA>::kStages) * TcGeom<NMMA>::kStageBytes +
+         sizeof(GemvBarriers<NMMA>) + 64;
+}
+
+template <int FMT, int NMMA>
+qx_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemvTcParams& p,
+                     int grid, cudaStream_t stream) {
+  constexpr size_t smem = gemv_smem_bytes<NMMA>();
+  static bool attr_set = false;
+  if (!attr_set) {
+    QX_CUDA_TRY(cudaFuncSetAttribute(gemv_tc_kernel<FMT, NMMA>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem)));
+    attr_set = true;
+  }
+  gemv_tc_kernel<FMT, NMMA><<<grid, FMT == QX_FORMAT_Q4_0 ? 448 : 192, smem, stream>>>(map_a, map_b, p);
+  count_launch();
+  QX_CUDA_TRY(cudaGetLastError());
+  return QX_STATUS_OK;
+}
+
+template <int FMT>
+qx_status launch_fmt(int ncols, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                     const GemvTcParams& p, int grid, cudaStream_t stream) {
+  switch (ncols) {
+    case 8: return launch_one<FMT, 8>(map_a, map_b, p, grid, stream);
+    case 16: return launch_one<FMT, 16>(map_a, map_b, p, grid, stream);
+    case 32: return launch_one<FMT, 32>(map_a, map_b, p, grid, stream);
+    case 64: return launch_one<FMT, 64>(map_a, map_b, p, grid, stream);
+    case 128: return launch_one<FMT, 128>(map_a, map_b, p, grid, stream);
+    default: break;
+  }
+  set_last_error_text("gemv: unsupported digit column count");
+  return QX_STATUS_DEVICE_ERROR;
+}
+
+}  // namespace
+
+// Device buffer the profiling build writes its cycle counters to (null otherwise).
+long long* gemv_profile_buffer() {
+#ifdef QX_GEMV_PROFILE
+  static long long* buffer = []() {
+    long long* ptr = nullptr;
+    if (cudaMalloc(&ptr, 1024 * 16 * sizeof(long long)) != cudaSuccess) return static_cast<long long*>(nullptr);
+    (void)cudaMemset(ptr, 0, 1024 * 16 * sizeof(long long));
+    return ptr;
+  }();
+  return buffer;
+#else
+  return nullptr;
+#endif
+}
+
+// K split: units of U slabs with at most 32 units per row; a function of K alone.
+static int unit_slabs_for(long long slabs) { return static_cast<int>((slabs + 31) / 32); }
+
+qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScratch* out) {
+  if (w->tiles > kMaxCounterTiles) {
+    set_last_error_text("qgemm: more than 2M weight rows per device are not supported");
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  const int unit_slabs = unit_slabs_for(w->slabs);
+  const int units_per_tile = static_cast<int>((w->slabs + unit_slabs - 1) / unit_slabs);
+  const long long total_units = w->tiles * units_per_tile;
+  const int ncols = digit_columns(m);
+  const long long kpad = w->slabs * kSlabK;
+  size_t off = kCounterBytes;
+  out->xd_offset = off;
+  off += align_up(static_cast<size_t>(ncols) * kpad, 256);
+  out->xc_offset = off;
+  off += align_up(static_cast<size_t>(m) * w->slabs * kSlabBlocks * sizeof(XConst), 256);
+  out->partial_offset = off;
+  off += align_up(static_cast<size_t>(total_units) * m * kTileRows * sizeof(float), 256);
+  out->total_bytes = off;
+  out->ctas = static_cast<int>(total_units < sm_count ? total_units : sm_count);
+  out->unit_slabs = unit_slabs;
+  out->units_per_tile = units_per_tile;
+  return QX_STATUS_OK;
+}
+
+qx_status launch_gemv_tc(const qx_weights* w, const int8_t* xd, const XConst* xc, float* y,
+                         int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
+                         qx_workspace* /*ws*/, cudaStream_t stream) {
+  const int ncols = digit_columns(m);
+  const long long kpad = w->slabs * kSlabK;
+  CUtensorMap map_a, map_b;
+  const uint64_t panel_rows = static_cast<uint64_t>(w->tiles) * w->slabs * kTileRows;
+  bool ok = encode_tma_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xd, static_cast<uint64_t>(kpad),
+                          static_cast<uint64_t>(ncols), static_cast<uint64_t>(kpad), kSlabK,
+                          static_cast<uint32_t>(ncols));
+  if (w->format == QX_FORMAT_Q8_0) {
+    ok = ok && encode_tma_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->codes, 128, panel_rows,
+                             128, 128, kTileRows);
+  } else {
+    map_a = map_b;  // unused by the q4_0 kernel
+  }
+  if (!ok) {
+    set_last_error_text("cuTensorMapEncodeTiled failed for the GEMV operands");
+    return QX_STATUS_DEVICE_ERROR;
+  }
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  GemvTcParams p{};
+  p.codes = reinterpret_cast<const uint4*>(w->codes);
+  p.scales = w->scales;
+  p.xc = xc;
+  p.y = y;
+  p.partial = reinterpret_cast<float*>(ws_base + scratch.partial_offset);
+  p.counters = reinterpret_cast<int*>(ws_base);
+  p.error = ctx->flag + 1;
+  p.ldy = ldy;
+  p.rows = w->rows;
+  p.m = m;
+  p.nbpad = static_cast<int>(w->slabs) * kSlabBlocks;
+  p.slabs = static_cast<int>(w->slabs);
+  p.tiles = static_cast<int>(w->tiles);
+  p.unit_slabs = scratch.unit_slabs;
+  p.units_per_tile = scratch.units_per_tile;
+  p.total_units = w->tiles * scratch.units_per_tile;
+  p.debug = gemv_profile_buffer();
+  if (w->format == QX_FORMAT_Q8_0) {
+    return launch_fmt<QX_FORMAT_Q8_0>(ncols, map_a, map_b, p, scratch.ctas, stream);
+  }
+  return launch_fmt<QX_FORMAT_Q4_0>(ncols, map_a, map_b, p, scratch.ctas, stream);
+}
+
+}  // namespace qx
+
+#ifdef QX_GEMV_PROFILE
+// Profiling builds only: copies the per-CTA cycle counters of the last launches to the
+// host (16 values per CTA) and clears them.
+extern "C" QX_API int qx_debug_gemv_profile(long long* host_out, int ctas) {
+  long long* buffer = qx::gemv_profile_buffer();
+  if (buffer == nullptr || ctas > 1024) return -1;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
+  if (cudaMemcpy(host_out, buffer, sizeof(long long) * 16 * ctas, cudaMemcpyDeviceToHost) !=
+      cudaSuccess) {
+    return -3;
+  }
+  (void)cudaMemset(buffer, 0, 1024 * 16 * sizeof(long long));
+  return 0;
+}
+#endif

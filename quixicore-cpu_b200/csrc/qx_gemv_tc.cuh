@@ -1,0 +1,31 @@
+// Launch interface of the tensor-core decode GEMV (qx_gemv_tc.cu).
+#pragma once
+
+#include "qx_gemv.cuh"
+#include "qx_weights.cuh"
+
+namespace qx {
+
+constexpr int kGemvMaxBatch = 32;          // activation rows per launch (128 digit columns)
+constexpr size_t kCounterBytes = kWorkspaceCounterBytes;  // tile arrival counters
+constexpr long long kMaxCounterTiles = kCounterBytes / 4;
+
+struct GemvScratch {
+  size_t xd_offset, xc_offset, partial_offset, total_bytes;
+  int ctas;             // persistent CTAs of the launch
+  int unit_slabs;       // slabs per K unit (a function of K alone)
+  int units_per_tile;
+};
+
+// Scratch of one launch with `m` activation rows on a device with `sm_count` SMs. The
+// first kCounterBytes of every workspace hold the per-tile arrival counters (zero
+// between launches); the rest is laid out per call.
+qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScratch* out);
+
+qx_status launch_gemv_tc(const qx_weights* w, const int8_t* xd, const XConst* xc, float* y,
+                         int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
+                         qx_workspace* ws, cudaStream_t stream);
+
+const char* gemv_variant_name();
+
+}  // namespace qx

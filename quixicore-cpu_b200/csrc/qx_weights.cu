@@ -10,43 +10,58 @@
 namespace qx {
 namespace {
 
-// One thread per block. Canonical blocks are only 2-byte aligned (34 / 18 byte stride),
-// so they are read as 16-bit words; the planes are written with 16-byte stores.
+// One thread per panel block slot (tile, slab, row-in-tile, block-in-slab). Canonical
+// blocks are only 2-byte aligned (34 / 18 byte stride), so they are read as 16-bit words;
+// slots past the last row or block are written as zeros.
 template <int FMT>
 __global__ void __launch_bounds__(256) relayout_kernel(const unsigned short* __restrict__ src,
-                                                       long long total_blocks,
+                                                       long long rows, long long nb,
+                                                       long long slabs, long long total_slots,
                                                        uint4* __restrict__ codes,
                                                        unsigned short* __restrict__ scales) {
   constexpr int kWords = FMT == QX_FORMAT_Q8_0 ? 17 : 9;  // 16-bit words per block
-  const long long blk = blockIdx.x * 256LL + threadIdx.x;
-  if (blk >= total_blocks) return;
-  const unsigned short* in = src + blk * kWords;
-  scales[blk] = in[0];
+  const long long slot = blockIdx.x * 256LL + threadIdx.x;
+  if (slot >= total_slots) return;
+  const int j = static_cast<int>(slot % kSlabBlocks);
+  const int r = static_cast<int>((slot / kSlabBlocks) % kTileRows);
+  const long long ts = slot / (kSlabBlocks * kTileRows);  // tile * slabs + slab
+  const long long s = ts % slabs, tile = ts / slabs;
+  const long long row = tile * kTileRows + r, b = s * kSlabBlocks + j;
   uint32_t w[(kWords - 1) / 2];
+  unsigned short scale = 0;
 #pragma unroll
-  for (int i = 0; i < (kWords - 1) / 2; ++i) {
-    w[i] = static_cast<uint32_t>(in[1 + 2 * i]) | (static_cast<uint32_t>(in[2 + 2 * i]) << 16);
+  for (int i = 0; i < (kWords - 1) / 2; ++i) w[i] = 0;
+  if (row < rows && b < nb) {
+    const unsigned short* in = src + (row * nb + b) * kWords;
+    scale = in[0];
+#pragma unroll
+    for (int i = 0; i < (kWords - 1) / 2; ++i) {
+      w[i] = static_cast<uint32_t>(in[1 + 2 * i]) | (static_cast<uint32_t>(in[2 + 2 * i]) << 16);
+    }
   }
+  scales[(ts * kSlabBlocks + j) * kTileRows + r] = scale;
   if (FMT == QX_FORMAT_Q8_0) {
-    codes[2 * blk] = make_uint4(w[0], w[1], w[2], w[3]);
-    codes[2 * blk + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+    codes[2 * slot] = make_uint4(w[0], w[1], w[2], w[3]);
+    codes[2 * slot + 1] = make_uint4(w[4], w[5], w[6], w[7]);
   } else {
-    codes[blk] = make_uint4(w[0], w[1], w[2], w[3]);
+    codes[slot] = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
 }  // namespace
 
-qx_status launch_relayout(int format, const uint8_t* src, long long rows, long long nb,
-                          uint8_t* codes, unsigned short* scales, cudaStream_t stream) {
-  const long long total = rows * nb;
+qx_status launch_relayout(const qx_weights* w, const uint8_t* src, cudaStream_t stream) {
+  const long long total = w->tiles * w->slabs * kTileRows * kSlabBlocks;
   const unsigned grid = static_cast<unsigned>((total + 255) / 256);
-  if (format == QX_FORMAT_Q8_0) {
+  const auto* in = reinterpret_cast<const unsigned short*>(src);
+  if (w->format == QX_FORMAT_Q8_0) {
     relayout_kernel<QX_FORMAT_Q8_0><<<grid, 256, 0, stream>>>(
-        reinterpret_cast<const unsigned short*>(src), total, reinterpret_cast<uint4*>(codes), scales);
+        in, w->rows, w->blocks_per_row, w->slabs, total, reinterpret_cast<uint4*>(w->codes),
+        w->scales);
   } else {
     relayout_kernel<QX_FORMAT_Q4_0><<<grid, 256, 0, stream>>>(
-        reinterpret_cast<const unsigned short*>(src), total, reinterpret_cast<uint4*>(codes), scales);
+        in, w->rows, w->blocks_per_row, w->slabs, total, reinterpret_cast<uint4*>(w->codes),
+        w->scales);
   }
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
@@ -78,8 +93,6 @@ qx_status prepare_common(int format, const void* contract, bool contract_on_devi
   format_info(format, &block_bytes);
   const long long nb = columns / kBlockK;
   const size_t shard_bytes = static_cast<size_t>(row_count) * nb * block_bytes;
-  const size_t code_bytes = static_cast<size_t>(row_count) * nb * (block_bytes - 2);
-  const size_t scale_bytes = static_cast<size_t>(row_count) * nb * 2;
 
   auto* w = new (std::nothrow) qx_weights();
   if (w == nullptr) return QX_STATUS_OUT_OF_MEMORY;
@@ -92,6 +105,10 @@ qx_status prepare_common(int format, const void* contract, bool contract_on_devi
   w->blocks_per_row = nb;
   w->block_bytes = block_bytes;
   w->contract_bytes = shard_bytes;
+  w->tiles = (row_count + kTileRows - 1) / kTileRows;
+  w->slabs = (nb + kSlabBlocks - 1) / kSlabBlocks;
+  const size_t code_bytes = w->code_plane_bytes();
+  const size_t scale_bytes = w->scale_plane_bytes();
 
   auto fail = [&](qx_status status) {
     qx_weights_destroy(w);
@@ -128,7 +145,7 @@ qx_status prepare_common(int format, const void* contract, bool contract_on_devi
     device_src = static_cast<const uint8_t*>(temp);
   }
   qx_status status =
-      launch_relayout(format, device_src, row_count, nb, w->codes, w->scales, stream);
+      launch_relayout(w, device_src, stream);
   if (status == QX_STATUS_OK && (sync || temp != nullptr)) {
     err = cudaStreamSynchronize(stream);
     if (err != cudaSuccess) {

@@ -1,16 +1,23 @@
 // Device-resident prepared weights (the B200 counterpart of CpuPackedWeights,
 // src/memory/packed_weights.cpp:141-278).
 //
-// HBM layout ("split planes"). The canonical GGUF bytes interleave a 2-byte fp16 scale
+// HBM layout ("row-tile panels"). The canonical GGUF bytes interleave a 2-byte fp16 scale
 // with 32 (q8_0) or 16 (q4_0) code bytes, so no block starts on a 16-byte boundary. At
-// prepare time one pass re-lays them out, for the rows kept on this device, as
-//   codes  [rows][blocks_per_row][32 | 16] bytes   16-byte aligned, row-major
-//   scales [rows][blocks_per_row]          fp16 bits
-// which is byte-for-byte the same amount of data (34 or 18 bytes per block) but lets a
-// warp read 32 consecutive blocks of a row as one contiguous, 128-bit-vectorised span.
+// prepare time one pass re-lays the rows kept on this device out as tiles of 128 rows by
+// K-slabs of 4 blocks (128 elements), the unit one CTA pipeline stage consumes:
+//   codes  [tile][slab][row 0..127][4 blocks x (32 | 16) code bytes]   16 KiB | 8 KiB per slab
+//   scales [tile][slab][block 0..3][row 0..127] fp16 bits              1 KiB per slab
+// Each (tile, slab) is one contiguous span, so a stage is a single fully coalesced /
+// TMA-tiled read; rows of a code slab are 128 (64) bytes, exactly the 128-byte swizzle
+// atom of the tensor-core operand. Same byte count as the canonical layout (34 / 18
+// bytes per block) whenever rows % 128 == 0 and columns % 128 == 0 -- every benchmark
+// shape -- otherwise the last tile / slab is zero padded (a zero scale contributes 0).
+// This is the device counterpart of the reference's [row_panel, k_block, row_lane,
+// block_bytes] CPU panel (src/memory/packed_weights.cpp:253-266).
 #pragma once
 
 #include "qx_common.cuh"
+#include "qx_gemv.cuh"
 
 struct qx_weights {
   int format = 0;
@@ -20,6 +27,8 @@ struct qx_weights {
   long long rows = 0;        // rows kept
   long long columns = 0;
   long long blocks_per_row = 0;
+  long long tiles = 0;       // ceil(rows / 128)
+  long long slabs = 0;       // ceil(blocks_per_row / 4)
   size_t block_bytes = 0;
   size_t contract_bytes = 0;
   size_t prepared_bytes = 0;
@@ -30,14 +39,22 @@ struct qx_weights {
   // until built.
   void* dense_cache = nullptr;
   size_t dense_cache_bytes = 0;
+
+  size_t code_bytes_per_block() const { return block_bytes - 2; }
+  size_t code_plane_bytes() const {
+    return static_cast<size_t>(tiles) * slabs * qx::kTileRows * qx::kSlabBlocks *
+           code_bytes_per_block();
+  }
+  size_t scale_plane_bytes() const {
+    return static_cast<size_t>(tiles) * slabs * qx::kTileRows * qx::kSlabBlocks * 2;
+  }
 };
 
 namespace qx {
 
-// Re-layout canonical blocks [rows][nb][block_bytes] -> split planes. `src` points at
-// the first kept row's first block (device memory, 2-byte aligned).
-qx_status launch_relayout(int format, const uint8_t* src, long long rows, long long nb,
-                          uint8_t* codes, unsigned short* scales, cudaStream_t stream);
+// Re-layout canonical blocks [rows][nb][block_bytes] -> panels. `src` points at the first
+// kept row's first block (device memory, 2-byte aligned).
+qx_status launch_relayout(const qx_weights* w, const uint8_t* src, cudaStream_t stream);
 
 // y[m][ldy] (+ row offset already applied by the caller) = x[m][k] . dequant(W)^T
 qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev,
