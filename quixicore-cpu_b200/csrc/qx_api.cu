@@ -4,6 +4,7 @@
 // result, the `_dev` forms only enqueue.
 
 #include <cmath>
+#include <cstdio>
 #include <cstring>
 
 #include "qx_gemv_tc.cuh"
@@ -53,7 +54,11 @@ qx_status check_device_error(DeviceContext* ctx) {
     if (ctx->workspace.base != nullptr) {  // an aborted kernel may leave counters behind
       (void)cudaMemset(ctx->workspace.base, 0, kWorkspaceCounterBytes);
     }
-    set_last_error_text("a tensor-core kernel gave up a bounded wait (pipeline stalled)");
+    char text[96];
+    std::snprintf(text, sizeof text,
+                  "a tensor-core kernel gave up a bounded wait (pipeline stalled, role code %d)",
+                  words[1]);
+    set_last_error_text(text);
     return QX_STATUS_DEVICE_ERROR;
   }
   return QX_STATUS_OK;

@@ -18,7 +18,7 @@ namespace qx {
 constexpr int kBlockK = 32;  // elements per q8_0 / q4_0 block
 // Every workspace starts with this many bytes of arrival counters that kernels leave at
 // zero when they finish; reserve() zeroes them whenever it (re)allocates.
-constexpr size_t kWorkspaceCounterBytes = 64 << 10;
+constexpr size_t kWorkspaceCounterBytes = 1 << 20;
 
 // ---- error reporting -------------------------------------------------------------
 void set_last_error(const char* where, cudaError_t code);

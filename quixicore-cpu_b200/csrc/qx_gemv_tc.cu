@@ -5,28 +5,33 @@
 // those on the CUDA cores needs ~90 instructions per block -- the whole issue budget.
 // Here the 8-bit products run on the tensor core instead: the weight codes are the MMA's
 // A operand (128 weight rows x 32 codes of one block), the activation digits (three
-// balanced base-256 digits per activation, see qx_gemv.cuh) are the B operand (8..96
+// balanced base-256 digits per activation, see qx_gemv.cuh) are the B operand (8..128
 // digit columns), and one MMA per block leaves the three exact integer block sums of 128
 // rows in TMEM. The CUDA cores only combine the digits and apply the fp16 block scale:
 // ~10 instructions per block.
 //
 // One K-slab (4 blocks = 128 elements of 128 rows) per pipeline stage:
 //   q8_0  the 16 KiB code slab is one TMA tile (128-byte swizzle) straight from the panel
-//   q4_0  eight producer warps read the 8 KiB packed slab with coalesced 16-byte loads
-//         (register-prefetched several slabs ahead), split the nibbles and store the
-//         unsigned codes into the same swizzled layout
+//   q4_0  the 8 KiB packed slab is one bulk copy into a deep ring of packed slabs (the
+//         bytes in flight); eight producer warps read it back, split the nibbles and store
+//         the unsigned codes into the same swizzled layout the TMA tile would have
 //   both  the activation digit slab (TMA) and the slab's 512 fp16 scales (bulk copy)
-// Warp roles: 0 = TMA producer, 1 = MMA issuer (one thread), 2-5 = epilogue (thread =
-// weight row, accumulators in registers), 6-13 = q4_0 unpack producers.
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (one thread), 2-9 = epilogue (thread =
+// weight row, accumulators in registers; two sets of four warps take alternate K units),
+// then for q4_0 one unpack warp per stage and a packed-slab loader warp (its own warp: a
+// waiting lane would stall the other lanes of its warp).
 //
 // Work split and summation order. K is cut into units of `unit_slabs` slabs, a function of
 // K alone. A row's result is defined as the sum, in ascending order, of its unit sums,
 // each accumulated block by block from zero -- so it does not depend on the number of
 // rows, on how rows are sharded over GPUs, on the batch size or on the SM count. The
 // (row tile, unit) sequence is cut into equal contiguous ranges, one per persistent CTA,
-// so every SM streams the same number of bytes. A CTA that owns all units of a tile adds
-// them in registers; a tile shared by several CTAs goes through per-unit partial sums in
-// scratch memory and is finished, in the same order, by the last CTA to arrive.
+// so every SM streams the same number of bytes. A row's even and odd units are summed
+// separately (two sets of epilogue warps take alternate units) and added at the end. A
+// CTA that owns all units of a tile sums them in registers; a tile shared by several CTAs
+// goes through per-unit partial sums in scratch memory. Either way each thread counts
+// its share in on a per-row counter and the thread that completes the count adds the
+// pieces in the fixed order: no thread waits for another one.
 
 #include <cuda.h>
 
@@ -40,20 +45,32 @@ using namespace sm100;
 
 constexpr int kABytes = kTileRows * 128;  // unpacked code slab in shared memory
 constexpr int kSBytes = kSlabBlocks * kTileRows * 2;
-constexpr int kUnpackWarps = 8;
-constexpr int kPrefetch = 6;  // q4_0 slabs held in registers ahead of the smem ring
+constexpr int kEpilogueWarps = 8;   // two sets of four (one warp per TMEM lane quarter)
+constexpr int kFirstUnpackWarp = 2 + kEpilogueWarps;
+constexpr int kRawBytes = kTileRows * kSlabBlocks * 16;  // packed q4_0 slab (8 KiB)
 
-template <int NMMA>
+template <int FMT, int NMMA>
 struct TcGeom {
   static constexpr int kBBytes = NMMA * 128;
   static constexpr int kMaxM = NMMA / kDigitStride;
   static constexpr int kXBytes = kMaxM * kSlabBlocks * 16;  // block constants of one slab
   static constexpr int kStageBytes = kABytes + kBBytes + kSBytes + kXBytes + (1024 - kXBytes % 1024) % 1024;
-  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  // q8_0: the stage ring itself holds the bytes in flight. q4_0: every stage is paired with
+  // a packed-slab buffer filled by a bulk copy (the bytes in flight) and owned by one
+  // unpack warp, so up to eight slabs are being unpacked at the same time.
+  static constexpr int kBudget = FMT == QX_FORMAT_Q4_0 ? 220 * 1024 : 200 * 1024;
+  static constexpr int kPerStage = kStageBytes + (FMT == QX_FORMAT_Q4_0 ? kRawBytes : 0);
+  static constexpr int kStages = kBudget / kPerStage > 8 ? 8 : kBudget / kPerStage;
+  static constexpr int kRawStages = FMT == QX_FORMAT_Q4_0 ? kStages : 0;
+  // warps: TMA, MMA, 8 epilogue, then for q4_0 one unpack warp per stage and the loader
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps + (FMT == QX_FORMAT_Q4_0 ? kStages + 1 : 0));
   static constexpr int kColStride = NMMA <= 32 ? 32 : NMMA;  // TMEM columns per block
   static constexpr int kBlocksPerT = NMMA <= 64 ? 4 : 2;   // blocks per TMEM stage
   static constexpr int kTCols = kBlocksPerT * kColStride;  // 128 or 256
   static constexpr int kTStages = 512 / kTCols;            // 4 or 2
+  // Each epilogue set has its own ring of TMEM stages, so every TMEM barrier is used by
+  // one set only (a parity wait cannot tell apart phases two steps apart).
+  static constexpr int kTPerSet = kTStages / 2;           // 2 or 1
   // blocks whose TMEM loads are issued before one wait (register budget: 64 values)
   static constexpr int kLdBatch = NMMA <= 16 ? 4 : (NMMA == 32 ? 2 : 1);
 };
@@ -63,25 +80,27 @@ struct GemvTcParams {
   const unsigned short* scales;  // panel [tile][slab][4][128]
   const XConst* xc;              // [slab][m][4]
   float* y;
-  float* partial;                // [tile][unit][m][128]
-  int* counters;                 // [tile]
+  float* partial;                // [tile][slot][m][128], slot = K unit (or even/odd sum)
+  int* counters;                 // [tile][128], one per weight row
   int* error;
   long long ldy, rows;
   int m, nbpad, slabs, tiles;
   int unit_slabs, units_per_tile;  // K split: units of unit_slabs slabs
+  int slots_per_tile;              // max(units_per_tile, 2)
   long long total_units;
   long long* debug;  // [ctas][16] cycle counters, profiling builds only
 };
 
-template <int NMMA>
+template <int FMT, int NMMA>
 struct __align__(8) GemvBarriers {
-  uint64_t full[TcGeom<NMMA>::kStages];
-  uint64_t empty[TcGeom<NMMA>::kStages];
-  uint64_t tmem_full[TcGeom<NMMA>::kTStages];
-  uint64_t tmem_empty[TcGeom<NMMA>::kTStages];
+  uint64_t full[TcGeom<FMT, NMMA>::kStages];
+  uint64_t empty[TcGeom<FMT, NMMA>::kStages];
+  uint64_t tmem_full[TcGeom<FMT, NMMA>::kTStages];
+  uint64_t tmem_empty[TcGeom<FMT, NMMA>::kTStages];
+  uint64_t raw_full[12];
+  uint64_t raw_empty[12];
   uint32_t tmem_base;
   int abort_flag;
-  int last_flag;
 };
 
 __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gsrc, uint32_t bytes,
@@ -148,30 +167,34 @@ __device__ __forceinline__ long long range_start(long long c, long long total, l
   return c * total / ctas;
 }
 template <int FMT, int NMMA>
-__global__ void __launch_bounds__(FMT == QX_FORMAT_Q4_0 ? 448 : 192, 1)
+__global__ void __launch_bounds__((TcGeom<FMT, NMMA>::kThreads), 1)
 gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                const GemvTcParams p) {
-  using G = TcGeom<NMMA>;
+  using G = TcGeom<FMT, NMMA>;
   constexpr bool kQ4 = FMT == QX_FORMAT_Q4_0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  auto* bars = reinterpret_cast<GemvBarriers<NMMA>*>(smem + G::kStages * G::kStageBytes);
+  uint8_t* raw_ring = smem + G::kStages * G::kStageBytes;  // q4_0 only
+  auto* bars = reinterpret_cast<GemvBarriers<FMT, NMMA>*>(raw_ring + G::kRawStages * kRawBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = &bars->abort_flag;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < G::kStages; ++s) {
-      mbar_init(&bars->full[s], kQ4 ? 1 + kUnpackWarps : 1);
+      mbar_init(&bars->full[s], kQ4 ? 2 : 1);  // TMA bytes (+ the stage's unpack warp)
       mbar_init(&bars->empty[s], 1 + 4);  // MMA commit + four epilogue warps (scales read)
     }
     for (int t = 0; t < G::kTStages; ++t) {
       mbar_init(&bars->tmem_full[t], 1);
       mbar_init(&bars->tmem_empty[t], 4);
     }
+    for (int r = 0; r < G::kRawStages; ++r) {
+      mbar_init(&bars->raw_full[r], 1);
+      mbar_init(&bars->raw_empty[r], 1);
+    }
     bars->abort_flag = 0;
-    bars->last_flag = 0;
     mbar_fence_init();
     if (!kQ4) prefetch_tensormap(&map_a);
     prefetch_tensormap(&map_b);
@@ -199,7 +222,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (elect_one()) {
+    if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       QX_PROF_DECL(w_empty);
@@ -242,11 +265,18 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const uint32_t idesc = (2u << 4) | ((kQ4 ? 0u : 1u) << 7) | (1u << 10) |
                              (static_cast<uint32_t>(NMMA >> 3) << 17) |
                              (static_cast<uint32_t>(kTileRows >> 4) << 24);
-      uint32_t stage = 0, phase = 0, ts = 0, tphase = 0;
+      uint32_t stage = 0, phase = 0;
+      uint32_t ring_pos[2] = {0, 0}, ring_phase[2] = {0, 0};  // per epilogue set
       bool ok = true;
       QX_PROF_DECL(w_full);
       QX_PROF_DECL(w_tempty);
+      int slab = static_cast<int>(s_begin % p.slabs);
+      int unit = slab / p.unit_slabs;
+      int slab_in_unit = slab - unit * p.unit_slabs;
       for (long long gs = s_begin; gs < s_end && ok; ++gs) {
+        const int eset = unit & 1;
+        uint32_t ts = eset * G::kTPerSet + ring_pos[eset];
+        uint32_t tphase = ring_phase[eset];
         if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->full[stage], phase, abort_flag))) {
           ok = false;
           break;
@@ -270,10 +300,12 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     b_desc + static_cast<uint64_t>(2 * j), idesc, 0u);
           if (j % G::kBlocksPerT == G::kBlocksPerT - 1) {
             tc_commit(&bars->tmem_full[ts]);
-            if (++ts == G::kTStages) {
-              ts = 0;
-              tphase ^= 1u;
+            if (++ring_pos[eset] == G::kTPerSet) {
+              ring_pos[eset] = 0;
+              ring_phase[eset] ^= 1u;
             }
+            ts = eset * G::kTPerSet + ring_pos[eset];
+            tphase = ring_phase[eset];
           }
         }
         if (!ok) break;
@@ -281,6 +313,14 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (++stage == G::kStages) {
           stage = 0;
           phase ^= 1u;
+        }
+        if (++slab == p.slabs) {
+          slab = 0;
+          unit = 0;
+          slab_in_unit = 0;
+        } else if (++slab_in_unit == p.unit_slabs) {
+          slab_in_unit = 0;
+          ++unit;
         }
       }
       QX_PROF_STORE(2, w_full);
@@ -290,16 +330,48 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         atomicExch(p.error, 12);
       }
     }
-  } else if (warp < 6) {
+  } else if (warp < 2 + kEpilogueWarps) {
     // ------------------------------ epilogue ----------------------------------
+    // Two sets of four warps; set e takes the K units with (unit & 1) == e, so while one
+    // set waits on barriers, TMEM loads and conversions the other one issues. A row's
+    // result is (sum of even units, ascending) + (sum of odd units, ascending).
+    const int eset = (warp - 2) >> 2;
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const int epi_thread = threadIdx.x - 64;
     float acc[G::kMaxM], total[G::kMaxM];  // current unit; units of a tile this CTA owns
 #pragma unroll
     for (int m = 0; m < G::kMaxM; ++m) acc[m] = total[m] = 0.0f;
-    int units_written = 0;
-    uint32_t stage = 0, phase = 0, ts = 0, tphase = 0;
+    int units_mine = 0;  // units of the current split tile this thread has written
+    // deferred completion check of the last published share
+    int pend_old = 0, pend_add = 0, pend_tile = 0, pend_target = 0;
+    bool pend_owned = false;
+    auto resolve_pending = [&]() {
+      if (pend_add > 0 && pend_old + pend_add == pend_target) {
+        const long long row = static_cast<long long>(pend_tile) * kTileRows + row_in_tile;
+        const float* slots = p.partial + (static_cast<long long>(pend_tile) * p.slots_per_tile *
+                                          p.m) * kTileRows;
+        const int count = pend_owned ? 2 : p.units_per_tile;
+#pragma unroll
+        for (int m = 0; m < G::kMaxM; ++m) {
+          if (m < p.m) {
+            // owned tiles hold (even sum, odd sum); split tiles hold one sum per unit
+            float even = 0.0f, odd = 0.0f;
+            for (int u = 0; u < count; u += 2) {
+              even += __ldcg(slots + (static_cast<long long>(u) * p.m + m) * kTileRows + row_in_tile);
+            }
+            for (int u = 1; u < count; u += 2) {
+              odd += __ldcg(slots + (static_cast<long long>(u) * p.m + m) * kTileRows + row_in_tile);
+            }
+            if (row < p.rows) p.y[m * p.ldy + row] = even + odd;
+          }
+        }
+        p.counters[static_cast<long long>(pend_tile) * kTileRows + row_in_tile] = 0;  // next launch
+      }
+      pend_add = 0;
+    };
+    uint32_t stage = 0, phase = 0, ring_pos = 0, tphase = 0;
+    uint32_t ts = eset * G::kTPerSet;
     bool ok = true;
     QX_PROF_DECL(w_tfull);
     QX_PROF_DECL(w_sfull);
@@ -309,6 +381,8 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     int unit = slab / p.unit_slabs;
     int slab_in_unit = slab - unit * p.unit_slabs;
     for (long long gs = s_begin; gs < s_end && ok; ++gs) {
+      const bool mine = (unit & 1) == eset;
+      if (mine) {
       const uint8_t* stage_base = smem + stage * G::kStageBytes;
       const unsigned short* sc =
           reinterpret_cast<const unsigned short*>(stage_base + kABytes + G::kBBytes);
@@ -387,16 +461,18 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
           }
           if (last_of_tstage) {
-            if (++ts == G::kTStages) {
-              ts = 0;
+            if (++ring_pos == G::kTPerSet) {
+              ring_pos = 0;
               tphase ^= 1u;
             }
+            ts = eset * G::kTPerSet + ring_pos;
           }
         }
       }
       if (!ok) break;
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->empty[stage]);  // scales / constants consumed
+      }
       if (++stage == G::kStages) {
         stage = 0;
         phase ^= 1u;
@@ -407,60 +483,53 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (unit_end) {
         const long long tile_first = gs - slab;
         const bool owns_tile = s_begin <= tile_first && s_end >= tile_first + p.slabs;
-        if (owns_tile) {
+        float* tile_slots = p.partial + (static_cast<long long>(tile) * p.slots_per_tile * p.m) *
+                                            kTileRows;
+        if (mine) {
+          if (owns_tile) {
 #pragma unroll
-          for (int m = 0; m < G::kMaxM; ++m) {
-            total[m] += acc[m];
-            acc[m] = 0.0f;
-          }
-        } else {
-          float* mine = p.partial +
-                        ((static_cast<long long>(tile) * p.units_per_tile + unit) * p.m) * kTileRows;
+            for (int m = 0; m < G::kMaxM; ++m) {
+              total[m] += acc[m];
+              acc[m] = 0.0f;
+            }
+          } else {
+            float* part = tile_slots + static_cast<long long>(unit) * p.m * kTileRows;
 #pragma unroll
-          for (int m = 0; m < G::kMaxM; ++m) {
-            if (m < p.m) mine[m * kTileRows + row_in_tile] = acc[m];
-            acc[m] = 0.0f;
+            for (int m = 0; m < G::kMaxM; ++m) {
+              if (m < p.m) part[m * kTileRows + row_in_tile] = acc[m];
+              acc[m] = 0.0f;
+            }
+            ++units_mine;
           }
-          ++units_written;
         }
         const bool share_end = slab == p.slabs - 1 || gs == s_end - 1;
         if (share_end) {
-          const long long row = static_cast<long long>(tile) * kTileRows + row_in_tile;
+          // Publish this thread's share of the row and count it in on the row's counter
+          // (release); whoever completes the count finishes the row (acquire). Rows are
+          // independent, so no thread ever waits for another one here, and the result of
+          // the atomic is only looked at one share later (or after the loop).
+          resolve_pending();
+          int add = units_mine;
           if (owns_tile) {
-            if (row < p.rows) {
+            // the sums of the even and of the odd units go to slots 0 and 1
+            float* slot = tile_slots + static_cast<long long>(eset) * p.m * kTileRows;
 #pragma unroll
-              for (int m = 0; m < G::kMaxM; ++m)
-                if (m < p.m) p.y[m * p.ldy + row] = total[m];
-            }
-          } else {
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (epi_thread == 0) {
-              const int old = atomicAdd(p.counters + tile, units_written);
-              const int last = old + units_written == p.units_per_tile ? 1 : 0;
-              if (last) p.counters[tile] = 0;  // ready for the next launch
-              bars->last_flag = last;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (bars->last_flag != 0) {
-              __threadfence();
-              const float* base =
-                  p.partial + (static_cast<long long>(tile) * p.units_per_tile * p.m) * kTileRows;
-#pragma unroll
-              for (int m = 0; m < G::kMaxM; ++m) {
-                if (m < p.m) {
-                  float sum = 0.0f;
-                  for (int u = 0; u < p.units_per_tile; ++u) {
-                    sum += __ldcg(base + (static_cast<long long>(u) * p.m + m) * kTileRows +
-                                  row_in_tile);
-                  }
-                  if (row < p.rows) p.y[m * p.ldy + row] = sum;
-                }
-              }
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");  // last_flag is reused
+            for (int m = 0; m < G::kMaxM; ++m)
+              if (m < p.m) slot[m * kTileRows + row_in_tile] = total[m];
+            add = 1;
           }
-          units_written = 0;
+          if (add > 0) {
+            int* counter = p.counters + static_cast<long long>(tile) * kTileRows + row_in_tile;
+            asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;"
+                         : "=r"(pend_old)
+                         : "l"(counter), "r"(add)
+                         : "memory");
+            pend_add = add;
+            pend_tile = tile;
+            pend_target = owns_tile ? 2 : p.units_per_tile;
+            pend_owned = owns_tile;
+          }
+          units_mine = 0;
 #pragma unroll
           for (int m = 0; m < G::kMaxM; ++m) total[m] = 0.0f;
         }
@@ -476,6 +545,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         ++unit;
       }
     }
+    resolve_pending();
     if (epi_thread == 0) {
       QX_PROF_STORE(4, w_tfull);
       QX_PROF_STORE(5, w_sfull);
@@ -485,64 +555,82 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       *abort_flag = 1;
       atomicExch(p.error, 13);
     }
-  } else if (kQ4) {
-    // ------------------------------ q4_0 unpack producers ---------------------
-    const int pt = threadIdx.x - 6 * 32;  // 0..255: items pt and pt + 256 of each slab
-    uint4 buf[kPrefetch][2];
-#pragma unroll
-    for (int i = 0; i < kPrefetch; ++i) {
-      const long long gs = s_begin + i;
-      if (gs < s_end) {
-        buf[i][0] = __ldcs(p.codes + gs * 512 + pt);
-        buf[i][1] = __ldcs(p.codes + gs * 512 + 256 + pt);
+  } else if (kQ4 && warp == kFirstUnpackWarp + G::kStages) {
+    // ------------------------------ q4_0 packed-slab loader ------------------
+    if (lane == 0) {
+      // packed q4_0 slabs: one 8 KiB bulk copy each, as far ahead as the raw ring allows
+      uint32_t rs = 0, rphase = 0;
+      bool ok = true;
+      for (long long gs = s_begin; gs < s_end; ++gs) {
+        if (!mbar_wait(&bars->raw_empty[rs], rphase ^ 1u, abort_flag)) {
+          ok = false;
+          break;
+        }
+        mbar_arrive_expect_tx(&bars->raw_full[rs], kRawBytes);
+        bulk_copy_g2s(raw_ring + rs * kRawBytes, p.codes + gs * (kRawBytes / 16), kRawBytes,
+                      &bars->raw_full[rs]);
+        if (++rs == G::kRawStages) {
+          rs = 0;
+          rphase ^= 1u;
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicExch(p.error, 15);
       }
     }
-    uint32_t stage = 0, phase = 0;
+  } else if (kQ4) {
+    // ------------------------------ q4_0 unpack producers ---------------------
+    // Unpack warp u owns stage u and packed buffer u: it handles every kStages-th slab on
+    // its own, so the waits and fences of different slabs overlap across warps.
+    const int u = warp - kFirstUnpackWarp;
+    const int pt = threadIdx.x - kFirstUnpackWarp * 32;
     bool ok = true;
     QX_PROF_DECL(w_empty);
+    QX_PROF_DECL(w_raw);
     const long long t_start = QX_PROF_NOW();
-    for (long long base = s_begin; base < s_end && ok; base += kPrefetch) {
+    if (u < G::kStages) {
+      uint32_t phase = 0;
+      const uint4* raw = reinterpret_cast<const uint4*>(raw_ring + u * kRawBytes);
+      uint8_t* a_smem = smem + u * G::kStageBytes;
+      for (long long gs = s_begin + u; gs < s_end; gs += G::kStages, phase ^= 1u) {
+        if (!QX_PROF_WAIT(w_raw, mbar_wait(&bars->raw_full[u], phase, abort_flag)) ||
+            !QX_PROF_WAIT(w_empty, mbar_wait(&bars->empty[u], phase ^ 1u, abort_flag))) {
+          ok = false;
+          break;
+        }
 #pragma unroll
-      for (int i = 0; i < kPrefetch; ++i) {
-        const long long gs = base + i;
-        if (gs < s_end && ok) {
-          if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag))) {
-            ok = false;
-          } else {
-            uint8_t* a_smem = smem + stage * G::kStageBytes;
+        for (int it = 0; it < 16; it += 4) {
+          uint4 packed[4];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int item = pt + h * 256;
-              const int r = item >> 2, j = item & 3;
-              const uint4 w = buf[i][h];
-              uint4 lo, hi;
-              lo.x = w.x & 0x0F0F0F0Fu; hi.x = (w.x >> 4) & 0x0F0F0F0Fu;
-              lo.y = w.y & 0x0F0F0F0Fu; hi.y = (w.y >> 4) & 0x0F0F0F0Fu;
-              lo.z = w.z & 0x0F0F0F0Fu; hi.z = (w.z >> 4) & 0x0F0F0F0Fu;
-              lo.w = w.w & 0x0F0F0F0Fu; hi.w = (w.w >> 4) & 0x0F0F0F0Fu;
-              // row r of the slab: 128 bytes, 16-byte chunk c stored at c ^ (r & 7)
-              uint8_t* rowp = a_smem + r * 128;
-              *reinterpret_cast<uint4*>(rowp + (((2 * j) ^ (r & 7)) << 4)) = lo;      // elements 0..15
-              *reinterpret_cast<uint4*>(rowp + (((2 * j + 1) ^ (r & 7)) << 4)) = hi;  // 16..31
-            }
-            fence_proxy_async_smem();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->full[stage]);
-            if (++stage == G::kStages) {
-              stage = 0;
-              phase ^= 1u;
-            }
-            const long long next = gs + kPrefetch;
-            if (next < s_end) {
-              buf[i][0] = __ldcs(p.codes + next * 512 + pt);
-              buf[i][1] = __ldcs(p.codes + next * 512 + 256 + pt);
-            }
+          for (int h = 0; h < 4; ++h) packed[h] = raw[(it + h) * 32 + lane];
+#pragma unroll
+          for (int h = 0; h < 4; ++h) {
+            const int item = (it + h) * 32 + lane;
+            const int r = item >> 2, j = item & 3;
+            const uint4 w = packed[h];
+            uint4 lo, hi;
+            lo.x = w.x & 0x0F0F0F0Fu; hi.x = (w.x >> 4) & 0x0F0F0F0Fu;
+            lo.y = w.y & 0x0F0F0F0Fu; hi.y = (w.y >> 4) & 0x0F0F0F0Fu;
+            lo.z = w.z & 0x0F0F0F0Fu; hi.z = (w.z >> 4) & 0x0F0F0F0Fu;
+            lo.w = w.w & 0x0F0F0F0Fu; hi.w = (w.w >> 4) & 0x0F0F0F0Fu;
+            // row r of the slab: 128 bytes, 16-byte chunk c stored at c ^ (r & 7)
+            uint8_t* rowp = a_smem + r * 128;
+            *reinterpret_cast<uint4*>(rowp + (((2 * j) ^ (r & 7)) << 4)) = lo;      // elements 0..15
+            *reinterpret_cast<uint4*>(rowp + (((2 * j + 1) ^ (r & 7)) << 4)) = hi;  // 16..31
           }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->raw_empty[u]);  // packed buffer may be refilled
+          mbar_arrive(&bars->full[u]);       // unpacked codes are in place
         }
       }
     }
     if (pt == 0) {
       QX_PROF_STORE(7, w_empty);
+      QX_PROF_STORE(9, w_raw);
       QX_PROF_STORE(8, QX_PROF_NOW() - t_start);
     }
     if (!ok) {
@@ -559,16 +647,17 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-template <int NMMA>
+template <int FMT, int NMMA>
 constexpr size_t gemv_smem_bytes() {
-  return 1024 + static_cast<size_t>(TcGeom<NMMA>::kStages) * TcGeom<NMMA>::kStageBytes +
-         sizeof(GemvBarriers<NMMA>) + 64;
+  return 1024 + static_cast<size_t>(TcGeom<FMT, NMMA>::kStages) * TcGeom<FMT, NMMA>::kStageBytes +
+         static_cast<size_t>(TcGeom<FMT, NMMA>::kRawStages) * kRawBytes +
+         sizeof(GemvBarriers<FMT, NMMA>) + 64;
 }
 
 template <int FMT, int NMMA>
 qx_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const GemvTcParams& p,
                      int grid, cudaStream_t stream) {
-  constexpr size_t smem = gemv_smem_bytes<NMMA>();
+  constexpr size_t smem = gemv_smem_bytes<FMT, NMMA>();
   static bool attr_set = false;
   if (!attr_set) {
     QX_CUDA_TRY(cudaFuncSetAttribute(gemv_tc_kernel<FMT, NMMA>,
@@ -576,7 +665,7 @@ qx_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const G
                                      static_cast<int>(smem)));
     attr_set = true;
   }
-  gemv_tc_kernel<FMT, NMMA><<<grid, FMT == QX_FORMAT_Q4_0 ? 448 : 192, smem, stream>>>(map_a, map_b, p);
+  gemv_tc_kernel<FMT, NMMA><<<grid, TcGeom<FMT, NMMA>::kThreads, smem, stream>>>(map_a, map_b, p);
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
   return QX_STATUS_OK;
@@ -619,7 +708,7 @@ static int unit_slabs_for(long long slabs) { return static_cast<int>((slabs + 31
 
 qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScratch* out) {
   if (w->tiles > kMaxCounterTiles) {
-    set_last_error_text("qgemm: more than 2M weight rows per device are not supported");
+    set_last_error_text("qgemm: more than 262144 weight rows per prepared handle are not supported");
     return QX_STATUS_INVALID_SHAPE;
   }
   const int unit_slabs = unit_slabs_for(w->slabs);
@@ -633,7 +722,8 @@ qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScra
   out->xc_offset = off;
   off += align_up(static_cast<size_t>(m) * w->slabs * kSlabBlocks * sizeof(XConst), 256);
   out->partial_offset = off;
-  off += align_up(static_cast<size_t>(total_units) * m * kTileRows * sizeof(float), 256);
+  const int slots = units_per_tile > 2 ? units_per_tile : 2;
+  off += align_up(static_cast<size_t>(w->tiles) * slots * m * kTileRows * sizeof(float), 256);
   out->total_bytes = off;
   out->ctas = static_cast<int>(total_units < sm_count ? total_units : sm_count);
   out->unit_slabs = unit_slabs;
@@ -679,6 +769,7 @@ qx_status launch_gemv_tc(const qx_weights* w, const int8_t* xd, const XConst* xc
   p.tiles = static_cast<int>(w->tiles);
   p.unit_slabs = scratch.unit_slabs;
   p.units_per_tile = scratch.units_per_tile;
+  p.slots_per_tile = scratch.units_per_tile > 2 ? scratch.units_per_tile : 2;
   p.total_units = w->tiles * scratch.units_per_tile;
   p.debug = gemv_profile_buffer();
   if (w->format == QX_FORMAT_Q8_0) {

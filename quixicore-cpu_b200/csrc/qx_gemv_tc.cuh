@@ -8,7 +8,7 @@ namespace qx {
 
 constexpr int kGemvMaxBatch = 32;          // activation rows per launch (128 digit columns)
 constexpr size_t kCounterBytes = kWorkspaceCounterBytes;  // tile arrival counters
-constexpr long long kMaxCounterTiles = kCounterBytes / 4;
+constexpr long long kMaxCounterTiles = kCounterBytes / 4 / kTileRows;  // one counter per row
 
 struct GemvScratch {
   size_t xd_offset, xc_offset, partial_offset, total_bytes;

@@ -1,7 +1,7 @@
 // Thin inline-PTX wrappers for the sm_100a features the GEMM kernels use: mbarrier,
 // TMA tiled loads (no cluster multicast anywhere), tcgen05 MMA / TMEM. Every wait is
-// bounded: after kSpinLimit failed polls it gives up and returns false so the kernel
-// can record an error status and drain instead of hanging the GPU.
+// bounded in time: after kWaitLimitNs it gives up and returns false so the kernel can
+// record an error status and drain instead of hanging the GPU.
 #pragma once
 
 #include <cuda.h>
@@ -12,7 +12,15 @@
 namespace qx {
 namespace sm100 {
 
-constexpr uint32_t kSpinLimit = 1u << 22;
+// A wait gives up after this much wall time on the GPU's nanosecond timer (a poll of a
+// barrier that is not ready may itself sleep for a while, so counting polls is no bound).
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -57,11 +65,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait. Returns false when the limit ran out or *abort_flag became non-zero.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag) {
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long start = global_timer_ns();
+  for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 1023u) == 1023u && *abort_flag != 0) return false;
+    if ((spin & 63u) == 0u) {
+      if (*abort_flag != 0) return false;
+      if (global_timer_ns() - start > kWaitLimitNs) return false;
+    }
   }
-  return false;
 }
 
 // ---- TMA ---------------------------------------------------------------------------

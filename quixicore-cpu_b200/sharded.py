@@ -1,0 +1,78 @@
+"""Row (output-channel) sharding of a packed weight matrix over the ranks of one node.
+
+Every output element depends on one weight row and one activation row, so the weights
+shard by rows with no reduction crossing a shard (the reference partitions rows over its
+threads in the same way, src/threading/thread_pool.cpp:22-29). Rank r keeps the
+contiguous row range ``shard_rows(n, world, r)`` of the canonical ``[n][k/32]`` block
+array, activations are replicated, and the output slices are exchanged with one
+all-gather (semantics of ``all_gather`` in kernels/collectives/collectives_ref.cpp:26-37).
+
+The compute step is injected: on GPUs it is ``PackedWeights.qgemm_dev`` of this package;
+the CPU tests run the same host logic over gloo with a stand-in compute function.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+TILE = 128  # prepared panels are tiles of 128 rows: keep shard boundaries on tiles
+
+
+def shard_rows(n: int, world: int, rank: int, align: int = TILE) -> Tuple[int, int]:
+    """(first row, row count) of rank's shard: contiguous, in rank order, covering [0, n).
+    Boundaries fall on multiples of `align` where n allows it."""
+    if world < 1 or not 0 <= rank < world or n < 1:
+        raise ValueError("bad shard request")
+    units = (n + align - 1) // align
+    begin = min(n, (units * rank // world) * align)
+    end = min(n, (units * (rank + 1) // world) * align)
+    return begin, end - begin
+
+
+class ShardedLinear:
+    """y[m, n] = x[m, k] . dequant(W)^T with W's rows sharded over the process group.
+
+    compute(x [m, k], out) fills this rank's slice: `out` is a [m, rows_local] view whose
+    row stride (out.stride(0)) may exceed rows_local. forward() returns the full y on every
+    rank.
+    """
+
+    def __init__(self, n: int, k: int, compute: Callable[[torch.Tensor, torch.Tensor], None],
+                 group: Optional[dist.ProcessGroup] = None, device: str = "cpu"):
+        self.n, self.k = n, k
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.begin, self.rows = shard_rows(n, self.world, self.rank)
+        self.ranges = [shard_rows(n, self.world, r) for r in range(self.world)]
+        self.max_rows = max(rows for _, rows in self.ranges)
+        self.uniform = all(rows == self.max_rows for _, rows in self.ranges)
+        self.compute = compute
+        self.device = device
+
+    def forward(self, x: torch.Tensor, y: Optional[torch.Tensor] = None) -> torch.Tensor:
+        m = x.shape[0]
+        if y is None:
+            y = torch.empty((m, self.n), dtype=torch.float32, device=self.device)
+        if self.world == 1:
+            self.compute(x, y)
+            return y
+        if m == 1 and self.uniform:
+            # contiguous slices: compute in place and gather straight into y
+            local = y[0, self.begin:self.begin + self.rows]
+            self.compute(x, local.view(1, self.rows))
+            dist.all_gather_into_tensor(y.view(-1), local, group=self.group)
+            return y
+        # strided or uneven slices: gather [world][m][max_rows], then place the columns
+        local = torch.zeros((m, self.max_rows), dtype=torch.float32, device=self.device)
+        self.compute(x, local[:, :self.rows])
+        gathered = torch.empty((self.world, m, self.max_rows), dtype=torch.float32,
+                               device=self.device)
+        dist.all_gather_into_tensor(gathered.view(self.world * m, self.max_rows), local,
+                                    group=self.group)
+        for r, (begin, rows) in enumerate(self.ranges):
+            y[:, begin:begin + rows] = gathered[r, :, :rows]
+        return y
