@@ -18,16 +18,17 @@ namespace qx {
 namespace {
 
 // ------------------------------------------------------------------------------------
-// activation digits: x[m][k] f32 -> digit matrix xd[ncols][kpad] int8 (row 4*m+d = digit
-// d of activation row m, d < 3; row 4*m+3, unused rows and the K padding are written as zeros) and the
-// per-block constants xc[slab][m][4].
+// activation digits: x[m][k] f32 -> one image per K-slab (see ximage_bytes): digit rows
+// (row 4*m+d = digit d of activation row m, d < 3; row 4*m+3, unused rows and the K padding
+// are written as zeros) followed by the per-block constants.
 // One group of 8 threads per (virtual row, block); virtual rows beyond m only zero-fill.
 // ------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict__ x,
-                                                         int8_t* __restrict__ xd,
-                                                         XConst* __restrict__ xc, int m, int k,
+                                                         uint8_t* __restrict__ ximg, int m, int k,
                                                          int nb, int nbpad, int ncols,
                                                          long long total_groups) {
+  // let the GEMV kernel behind this one start its set-up and weight pipeline right away
+  asm volatile("griddepcontrol.launch_dependents;");
   const long long group = blockIdx.x * 32LL + (threadIdx.x >> 3);
   const int q = threadIdx.x & 7;
   const bool in_range = group < total_groups;
@@ -74,12 +75,13 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
     for (int s = 1; s < 8; s <<= 1) psum[d] += __shfl_xor_sync(0xffffffffu, psum[d], s);
   }
   if (!in_range) return;
-  const long long kpad = static_cast<long long>(nbpad) * 32;
+  uint8_t* image = ximg + static_cast<long long>(b / kSlabBlocks) * ximage_bytes(ncols);
+  const int j = b % kSlabBlocks;
 #pragma unroll
   for (int d = 0; d < kDigitStride; ++d) {
     const int col = vm * kDigitStride + d;
     if (col < ncols) {
-      *reinterpret_cast<uint32_t*>(xd + col * kpad + b * 32 + q * 4) =
+      *reinterpret_cast<uint32_t*>(image + ximage_digit_offset(col, j, q)) =
           (real && d < 3) ? word[d < 3 ? d : 0] : 0u;
     }
   }
@@ -89,8 +91,7 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
     c.k01 = real ? 8 * (256 * psum[1] + psum[0]) : 0;
     c.p2x8 = real ? 8 * psum[2] : 0;
     c.pad = 0;
-    // [slab][m][block in slab]: one contiguous span per slab for the kernel's bulk copy
-    xc[(static_cast<long long>(b / kSlabBlocks) * m + vm) * kSlabBlocks + b % kSlabBlocks] = c;
+    reinterpret_cast<XConst*>(image + ncols * 128)[vm * kSlabBlocks + j] = c;
   }
 }
 
@@ -107,15 +108,15 @@ __device__ __forceinline__ float warp_tree_sum(float v) {
 // ------------------------------------------------------------------------------------
 template <int FMT>
 __global__ void __launch_bounds__(256) gemv_dp4a_kernel(
-    const uint4* __restrict__ codes, const unsigned short* __restrict__ scales,
-    const int8_t* __restrict__ xd, const XConst* __restrict__ xc, float* __restrict__ y,
-    long long n, int nb, int nbpad, long long slabs, long long ldy) {
+    const uint8_t* __restrict__ panel, const uint8_t* __restrict__ ximg, int ncols,
+    float* __restrict__ y, long long n, int nb, long long slabs, long long ldy) {
   constexpr int kVec = FMT == QX_FORMAT_Q8_0 ? 2 : 1;  // 16-byte vectors of codes per block
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);
   if (row >= n) return;
   const int m = blockIdx.y;
-  const long long kpad = static_cast<long long>(nbpad) * 32;
+  constexpr size_t kCodeBytes = FMT == QX_FORMAT_Q8_0 ? 32 : 16;
+  constexpr size_t kSlabCodes = kTileRows * kSlabBlocks * kCodeBytes;
   const long long tile = row / kTileRows;
   const int r = static_cast<int>(row % kTileRows);
   float acc = 0.0f;
@@ -125,22 +126,25 @@ __global__ void __launch_bounds__(256) gemv_dp4a_kernel(
     if (b < nb) {
       const long long ts = tile * slabs + b / kSlabBlocks;
       const int j = b % kSlabBlocks;
-      const long long slot = (ts * kTileRows + r) * kSlabBlocks + j;
+      const uint8_t* span = panel + ts * (kSlabCodes + kTileRows * kSlabBlocks * 2);
+      const uint4* codes = reinterpret_cast<const uint4*>(span + (r * kSlabBlocks + j) * kCodeBytes);
+      const uint8_t* image = ximg + static_cast<long long>(b / kSlabBlocks) * ximage_bytes(ncols);
       uint32_t w[8];
 #pragma unroll
       for (int i = 0; i < kVec; ++i) {
-        const uint4 c = __ldg(codes + slot * kVec + i);
+        const uint4 c = __ldg(codes + i);
         w[4 * i] = c.x; w[4 * i + 1] = c.y; w[4 * i + 2] = c.z; w[4 * i + 3] = c.w;
       }
       uint32_t dig[3][8];
 #pragma unroll
       for (int d = 0; d < 3; ++d) {
-        const uint4* src = reinterpret_cast<const uint4*>(xd + (m * kDigitStride + d) * kpad + b * 32);
-        const uint4 lo = __ldg(src), hi = __ldg(src + 1);
+        const int col = m * kDigitStride + d;
+        const uint4 lo = __ldg(reinterpret_cast<const uint4*>(image + ximage_digit_offset(col, j, 0)));
+        const uint4 hi = __ldg(reinterpret_cast<const uint4*>(image + ximage_digit_offset(col, j, 4)));
         dig[d][0] = lo.x; dig[d][1] = lo.y; dig[d][2] = lo.z; dig[d][3] = lo.w;
         dig[d][4] = hi.x; dig[d][5] = hi.y; dig[d][6] = hi.z; dig[d][7] = hi.w;
       }
-      const XConst c = xc[(static_cast<long long>(b / kSlabBlocks) * gridDim.y + m) * kSlabBlocks + j];
+      const XConst c = reinterpret_cast<const XConst*>(image + ncols * 128)[m * kSlabBlocks + j];
       int s[3];
       if (FMT == QX_FORMAT_Q8_0) {
 #pragma unroll
@@ -166,7 +170,8 @@ __global__ void __launch_bounds__(256) gemv_dp4a_kernel(
         s[0] -= c.k01;  // together with s[1]*256 below: -8 * sum_j (256*p1 + p0)
         s[2] -= c.p2x8;
       }
-      const float d = half_bits_to_float(scales[(ts * kSlabBlocks + j) * kTileRows + r]);
+      const float d = half_bits_to_float(
+          reinterpret_cast<const unsigned short*>(span + kSlabCodes)[j * kTileRows + r]);
       v = __fmul_rn(combine_digits(s[1] * 256 + s[0], s[2]), __fmul_rn(d, c.scale));
     }
     acc += warp_tree_sum(v);
@@ -186,8 +191,8 @@ bool force_dp4a() {
 
 const char* gemv_variant_name() { return force_dp4a() ? "sm100a_dp4a" : "sm100a_tcgen05_digits"; }
 
-// Workspace layout of one GEMV call: [digit matrix | block constants | split-K partials |
-// tile counters]; sizes depend only on (m, k, rows).
+// Workspace layout of one GEMV call: [row counters | activation slab images | per-unit
+// partial sums]; sizes depend only on (m, k, rows).
 qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev,
                            long long m, long long ldy, qx_workspace* ws,
                            cudaStream_t stream) {
@@ -207,26 +212,24 @@ qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev
     QX_TRY(gemv_scratch_layout(w, mc, ctx->prop.multiProcessorCount, &scratch));
     QX_TRY(ws->reserve(scratch.total_bytes));
     uint8_t* base = static_cast<uint8_t*>(ws->base);
-    int8_t* xd = reinterpret_cast<int8_t*>(base + scratch.xd_offset);
-    XConst* xc = reinterpret_cast<XConst*>(base + scratch.xc_offset);
+    uint8_t* ximg = base + scratch.ximg_offset;
 
     const int vrows = ncols / kDigitStride;
     const long long groups = static_cast<long long>(vrows) * nbpad;
     quantize_x_kernel<<<static_cast<unsigned>((groups + 31) / 32), 256, 0, stream>>>(
-        x_dev + m0 * w->columns, xd, xc, mc, static_cast<int>(w->columns), nb, nbpad, ncols, groups);
+        x_dev + m0 * w->columns, ximg, mc, static_cast<int>(w->columns), nb, nbpad, ncols, groups);
     count_launch();
     float* y = y_dev + m0 * ldy;
     if (!force_dp4a()) {
-      QX_TRY(launch_gemv_tc(w, xd, xc, y, mc, ldy, base, scratch, ws, stream));
+      QX_TRY(launch_gemv_tc(w, ximg, y, mc, ldy, base, scratch, stream));
     } else {
       const dim3 grid(static_cast<unsigned>((w->rows + 7) / 8), static_cast<unsigned>(mc));
-      const uint4* codes = reinterpret_cast<const uint4*>(w->codes);
       if (w->format == QX_FORMAT_Q8_0) {
-        gemv_dp4a_kernel<QX_FORMAT_Q8_0><<<grid, 256, 0, stream>>>(
-            codes, w->scales, xd, xc, y, w->rows, nb, nbpad, w->slabs, ldy);
+        gemv_dp4a_kernel<QX_FORMAT_Q8_0><<<grid, 256, 0, stream>>>(w->panel, ximg, ncols, y, w->rows,
+                                                                   nb, w->slabs, ldy);
       } else {
-        gemv_dp4a_kernel<QX_FORMAT_Q4_0><<<grid, 256, 0, stream>>>(
-            codes, w->scales, xd, xc, y, w->rows, nb, nbpad, w->slabs, ldy);
+        gemv_dp4a_kernel<QX_FORMAT_Q4_0><<<grid, 256, 0, stream>>>(w->panel, ximg, ncols, y, w->rows,
+                                                                   nb, w->slabs, ldy);
       }
       count_launch();
     }

@@ -40,6 +40,18 @@ __host__ __device__ inline int digit_columns(int m) {
   return c <= 8 ? 8 : (c <= 16 ? 16 : (c <= 32 ? 32 : (c <= 64 ? 64 : 128)));
 }
 
+// Activation side of one K-slab as the tensor-core kernel wants it in shared memory, kept
+// in that form in scratch memory so that one bulk copy brings it in:
+//   [ digit rows: ncols rows x 128 bytes, 16-byte chunks swizzled like a 128B-swizzle TMA
+//     tile (chunk c of row r stored at c ^ (r & 7)) | XConst[ncols / 4][4 blocks] ]
+__host__ __device__ inline int ximage_bytes(int ncols) { return ncols * 128 + ncols * 16; }
+// byte offset, inside a slab image, of the 4 digit bytes of elements 4q..4q+3 of block j
+// (0..3) in digit row `col`
+__host__ __device__ inline int ximage_digit_offset(int col, int j, int q) {
+  const int chunk = 2 * j + (q >> 2);
+  return (col >> 3) * 1024 + (col & 7) * 128 + ((chunk ^ (col & 7)) << 4) + (q & 3) * 4;
+}
+
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
   int d;
   asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));

@@ -47,18 +47,20 @@ constexpr int kABytes = kTileRows * 128;  // unpacked code slab in shared memory
 constexpr int kSBytes = kSlabBlocks * kTileRows * 2;
 constexpr int kEpilogueWarps = 8;   // two sets of four (one warp per TMEM lane quarter)
 constexpr int kFirstUnpackWarp = 2 + kEpilogueWarps;
-constexpr int kRawBytes = kTileRows * kSlabBlocks * 16;  // packed q4_0 slab (8 KiB)
+constexpr int kRawBytes = kTileRows * kSlabBlocks * 16 + kSBytes;  // packed q4_0 slab + scales (9 KiB)
+constexpr int kQ8SpanRows = (kABytes + kSBytes) / 128;              // q8_0 slab span as 128-byte rows
 
 template <int FMT, int NMMA>
 struct TcGeom {
   static constexpr int kBBytes = NMMA * 128;
   static constexpr int kMaxM = NMMA / kDigitStride;
-  static constexpr int kXBytes = kMaxM * kSlabBlocks * 16;  // block constants of one slab
-  static constexpr int kStageBytes = kABytes + kBBytes + kSBytes + kXBytes + (1024 - kXBytes % 1024) % 1024;
+  static constexpr int kXBytes = NMMA * 144;  // activation slab image: digit rows + constants
+  // stage: [codes 16 KiB][scales 1 KiB][activation image], padded to the swizzle atom
+  static constexpr int kStageBytes = (kABytes + kSBytes + kXBytes + 1023) / 1024 * 1024;
   // q8_0: the stage ring itself holds the bytes in flight. q4_0: every stage is paired with
   // a packed-slab buffer filled by a bulk copy (the bytes in flight) and owned by one
   // unpack warp, so up to eight slabs are being unpacked at the same time.
-  static constexpr int kBudget = FMT == QX_FORMAT_Q4_0 ? 220 * 1024 : 200 * 1024;
+  static constexpr int kBudget = FMT == QX_FORMAT_Q4_0 ? 224 * 1024 : 200 * 1024;
   static constexpr int kPerStage = kStageBytes + (FMT == QX_FORMAT_Q4_0 ? kRawBytes : 0);
   static constexpr int kStages = kBudget / kPerStage > 8 ? 8 : kBudget / kPerStage;
   static constexpr int kRawStages = FMT == QX_FORMAT_Q4_0 ? kStages : 0;
@@ -76,9 +78,8 @@ struct TcGeom {
 };
 
 struct GemvTcParams {
-  const uint4* codes;            // q4_0 producers read the packed panel directly
-  const unsigned short* scales;  // panel [tile][slab][4][128]
-  const XConst* xc;              // [slab][m][4]
+  const uint8_t* panel;          // [tile][slab]{codes, scales}; q4_0 is read by bulk copies
+  const uint8_t* ximg;           // [slab] activation images (ximage_bytes(NMMA) each)
   float* y;
   float* partial;                // [tile][slot][m][128], slot = K unit (or even/odd sum)
   int* counters;                 // [tile][128], one per weight row
@@ -197,7 +198,6 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     bars->abort_flag = 0;
     mbar_fence_init();
     if (!kQ4) prefetch_tensormap(&map_a);
-    prefetch_tensormap(&map_b);
   }
   if (warp == 1) {
     tmem_alloc(&bars->tmem_base, 512);
@@ -228,25 +228,21 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       QX_PROF_DECL(w_empty);
       const long long t_start = QX_PROF_NOW();
       int slab = static_cast<int>(s_begin % p.slabs);
+      // the activation images are written by the preceding kernel in the stream
+      asm volatile("griddepcontrol.wait;" ::: "memory");
       for (long long gs = s_begin; gs < s_end; ++gs, slab = slab + 1 == p.slabs ? 0 : slab + 1) {
         if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag))) {
           ok = false;
           break;
         }
         uint8_t* st = smem + stage * G::kStageBytes;
-        const uint32_t x_bytes = static_cast<uint32_t>(p.m) * kSlabBlocks * 16u;
-        mbar_arrive_expect_tx(&bars->full[stage],
-                              (kQ4 ? 0 : kABytes) + G::kBBytes + kSBytes + x_bytes);
+        mbar_arrive_expect_tx(&bars->full[stage], (kQ4 ? 0 : kABytes + kSBytes) + G::kXBytes);
         if (!kQ4) {
-          tma_load_2d(st, &map_a, &bars->full[stage], 0,
-                      static_cast<int>(gs * kTileRows));
+          // codes and scales of the slab: one tile of 136 rows x 128 bytes
+          tma_load_2d(st, &map_a, &bars->full[stage], 0, static_cast<int>(gs * kQ8SpanRows));
         }
-        tma_load_2d(st + kABytes, &map_b, &bars->full[stage], slab * kSlabK, 0);
-        bulk_copy_g2s(st + kABytes + G::kBBytes, p.scales + gs * (kSlabBlocks * kTileRows),
-                      kSBytes, &bars->full[stage]);
-        bulk_copy_g2s(st + kABytes + G::kBBytes + kSBytes,
-                      p.xc + static_cast<long long>(slab) * p.m * kSlabBlocks, x_bytes,
-                      &bars->full[stage]);
+        bulk_copy_g2s(st + kABytes + kSBytes, p.ximg + static_cast<long long>(slab) * G::kXBytes,
+                      G::kXBytes, &bars->full[stage]);
         if (++stage == G::kStages) {
           stage = 0;
           phase ^= 1u;
@@ -284,7 +280,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tc_fence_after_sync();
         const uint32_t sa = smem_u32(smem + stage * G::kStageBytes);
         const uint64_t a_desc = make_sw128_kmajor_desc(sa);
-        const uint64_t b_desc = make_sw128_kmajor_desc(sa + kABytes);
+        const uint64_t b_desc = make_sw128_kmajor_desc(sa + kABytes + kSBytes);
 #pragma unroll
         for (int j = 0; j < kSlabBlocks; ++j) {
           if (j % G::kBlocksPerT == 0) {
@@ -342,6 +338,15 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     float acc[G::kMaxM], total[G::kMaxM];  // current unit; units of a tile this CTA owns
 #pragma unroll
     for (int m = 0; m < G::kMaxM; ++m) acc[m] = total[m] = 0.0f;
+    // byte offset of this row's scale of block j inside the stage's 1 KiB scale area. q4_0:
+    // linear [block][row] (copied by the unpack warp). q8_0: the area arrived as rows
+    // 128..135 of the swizzled TMA tile, so 16-byte chunks are permuted by the row index.
+    auto scale_offset = [&](int j) {
+      const int linear = (j * kTileRows + row_in_tile) * 2;
+      if (kQ4) return linear;
+      const int r128 = linear >> 7, chunk = (linear >> 4) & 7;
+      return r128 * 128 + ((chunk ^ (r128 & 7)) << 4) + (linear & 15);
+    };
     int units_mine = 0;  // units of the current split tile this thread has written
     // deferred completion check of the last published share
     int pend_old = 0, pend_add = 0, pend_tile = 0, pend_target = 0;
@@ -384,9 +389,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       const bool mine = (unit & 1) == eset;
       if (mine) {
       const uint8_t* stage_base = smem + stage * G::kStageBytes;
-      const unsigned short* sc =
-          reinterpret_cast<const unsigned short*>(stage_base + kABytes + G::kBBytes);
-      const int4* xcs = reinterpret_cast<const int4*>(stage_base + kABytes + G::kBBytes + kSBytes);
+      const int4* xcs = reinterpret_cast<const int4*>(stage_base + kABytes + kSBytes + G::kBBytes);
       constexpr int kChunk = NMMA <= 32 ? NMMA : 32;
       constexpr int kChunksPerBlock = NMMA / kChunk;
       float dsc[kSlabBlocks];
@@ -407,7 +410,8 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
 #pragma unroll
             for (int j = 0; j < kSlabBlocks; ++j) {
-              dsc[j] = half_bits_to_float(sc[j * kTileRows + row_in_tile]);
+              dsc[j] = half_bits_to_float(*reinterpret_cast<const unsigned short*>(
+                  stage_base + kABytes + scale_offset(j)));
             }
           }
         }
@@ -558,7 +562,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   } else if (kQ4 && warp == kFirstUnpackWarp + G::kStages) {
     // ------------------------------ q4_0 packed-slab loader ------------------
     if (lane == 0) {
-      // packed q4_0 slabs: one 8 KiB bulk copy each, as far ahead as the raw ring allows
+      // packed q4_0 slab + its scales: one 9 KiB bulk copy, as far ahead as the ring allows
       uint32_t rs = 0, rphase = 0;
       bool ok = true;
       for (long long gs = s_begin; gs < s_end; ++gs) {
@@ -567,7 +571,7 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           break;
         }
         mbar_arrive_expect_tx(&bars->raw_full[rs], kRawBytes);
-        bulk_copy_g2s(raw_ring + rs * kRawBytes, p.codes + gs * (kRawBytes / 16), kRawBytes,
+        bulk_copy_g2s(raw_ring + rs * kRawBytes, p.panel + gs * kRawBytes, kRawBytes,
                       &bars->raw_full[rs]);
         if (++rs == G::kRawStages) {
           rs = 0;
@@ -620,6 +624,11 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             *reinterpret_cast<uint4*>(rowp + (((2 * j + 1) ^ (r & 7)) << 4)) = hi;  // 16..31
           }
         }
+        // the slab's 512 fp16 scales ride behind the codes: move them next to the stage
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          reinterpret_cast<uint4*>(a_smem + kABytes)[h * 32 + lane] = raw[512 + h * 32 + lane];
+        }
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
@@ -665,7 +674,21 @@ qx_status launch_one(const CUtensorMap& map_a, const CUtensorMap& map_b, const G
                                      static_cast<int>(smem)));
     attr_set = true;
   }
-  gemv_tc_kernel<FMT, NMMA><<<grid, TcGeom<FMT, NMMA>::kThreads, smem, stream>>>(map_a, map_b, p);
+  // Programmatic dependent launch: this kernel may start while the activation quantizer
+  // in front of it is still running. Everything that does not depend on the activations
+  // (barrier set-up, TMEM allocation, the weight pipeline) proceeds; the thread that
+  // copies the activation images waits for the quantizer's results (griddepcontrol.wait).
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(static_cast<unsigned>(grid));
+  config.blockDim = dim3(TcGeom<FMT, NMMA>::kThreads);
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  QX_CUDA_TRY(cudaLaunchKernelEx(&config, gemv_tc_kernel<FMT, NMMA>, map_a, map_b, p));
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
   return QX_STATUS_OK;
@@ -717,10 +740,8 @@ qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScra
   const int ncols = digit_columns(m);
   const long long kpad = w->slabs * kSlabK;
   size_t off = kCounterBytes;
-  out->xd_offset = off;
-  off += align_up(static_cast<size_t>(ncols) * kpad, 256);
-  out->xc_offset = off;
-  off += align_up(static_cast<size_t>(m) * w->slabs * kSlabBlocks * sizeof(XConst), 256);
+  out->ximg_offset = off;
+  off += align_up(static_cast<size_t>(w->slabs) * ximage_bytes(ncols), 256);
   out->partial_offset = off;
   const int slots = units_per_tile > 2 ? units_per_tile : 2;
   off += align_up(static_cast<size_t>(w->tiles) * slots * m * kTileRows * sizeof(float), 256);
@@ -731,32 +752,25 @@ qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScra
   return QX_STATUS_OK;
 }
 
-qx_status launch_gemv_tc(const qx_weights* w, const int8_t* xd, const XConst* xc, float* y,
-                         int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                         qx_workspace* /*ws*/, cudaStream_t stream) {
+qx_status launch_gemv_tc(const qx_weights* w, const uint8_t* ximg, float* y, int m,
+                         long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
+                         cudaStream_t stream) {
   const int ncols = digit_columns(m);
   const long long kpad = w->slabs * kSlabK;
-  CUtensorMap map_a, map_b;
-  const uint64_t panel_rows = static_cast<uint64_t>(w->tiles) * w->slabs * kTileRows;
-  bool ok = encode_tma_2d(&map_b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xd, static_cast<uint64_t>(kpad),
-                          static_cast<uint64_t>(ncols), static_cast<uint64_t>(kpad), kSlabK,
-                          static_cast<uint32_t>(ncols));
+  CUtensorMap map_a{}, map_b{};  // map_b is unused (kept for the kernel signature)
   if (w->format == QX_FORMAT_Q8_0) {
-    ok = ok && encode_tma_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->codes, 128, panel_rows,
-                             128, 128, kTileRows);
-  } else {
-    map_a = map_b;  // unused by the q4_0 kernel
-  }
-  if (!ok) {
-    set_last_error_text("cuTensorMapEncodeTiled failed for the GEMV operands");
-    return QX_STATUS_DEVICE_ERROR;
+    const uint64_t span_rows = static_cast<uint64_t>(w->tiles) * w->slabs * kQ8SpanRows;
+    if (!encode_tma_2d(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w->panel, 128, span_rows, 128, 128,
+                       kQ8SpanRows)) {
+      set_last_error_text("cuTensorMapEncodeTiled failed for the GEMV weight panel");
+      return QX_STATUS_DEVICE_ERROR;
+    }
   }
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
   GemvTcParams p{};
-  p.codes = reinterpret_cast<const uint4*>(w->codes);
-  p.scales = w->scales;
-  p.xc = xc;
+  p.panel = w->panel;
+  p.ximg = ximg;
   p.y = y;
   p.partial = reinterpret_cast<float*>(ws_base + scratch.partial_offset);
   p.counters = reinterpret_cast<int*>(ws_base);

@@ -11,7 +11,7 @@ constexpr size_t kCounterBytes = kWorkspaceCounterBytes;  // tile arrival counte
 constexpr long long kMaxCounterTiles = kCounterBytes / 4 / kTileRows;  // one counter per row
 
 struct GemvScratch {
-  size_t xd_offset, xc_offset, partial_offset, total_bytes;
+  size_t ximg_offset, partial_offset, total_bytes;
   int ctas;             // persistent CTAs of the launch
   int unit_slabs;       // slabs per K unit (a function of K alone)
   int units_per_tile;
@@ -22,9 +22,10 @@ struct GemvScratch {
 // between launches); the rest is laid out per call.
 qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScratch* out);
 
-qx_status launch_gemv_tc(const qx_weights* w, const int8_t* xd, const XConst* xc, float* y,
-                         int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                         qx_workspace* ws, cudaStream_t stream);
+// ximg: activation slab images written by the quantizer (qx_gemv.cu)
+qx_status launch_gemv_tc(const qx_weights* w, const uint8_t* ximg, float* y, int m,
+                         long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
+                         cudaStream_t stream);
 
 const char* gemv_variant_name();
 

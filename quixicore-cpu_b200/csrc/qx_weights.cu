@@ -17,8 +17,7 @@ template <int FMT>
 __global__ void __launch_bounds__(256) relayout_kernel(const unsigned short* __restrict__ src,
                                                        long long rows, long long nb,
                                                        long long slabs, long long total_slots,
-                                                       uint4* __restrict__ codes,
-                                                       unsigned short* __restrict__ scales) {
+                                                       uint8_t* __restrict__ panel) {
   constexpr int kWords = FMT == QX_FORMAT_Q8_0 ? 17 : 9;  // 16-bit words per block
   const long long slot = blockIdx.x * 256LL + threadIdx.x;
   if (slot >= total_slots) return;
@@ -39,13 +38,13 @@ __global__ void __launch_bounds__(256) relayout_kernel(const unsigned short* __r
       w[i] = static_cast<uint32_t>(in[1 + 2 * i]) | (static_cast<uint32_t>(in[2 + 2 * i]) << 16);
     }
   }
-  scales[(ts * kSlabBlocks + j) * kTileRows + r] = scale;
-  if (FMT == QX_FORMAT_Q8_0) {
-    codes[2 * slot] = make_uint4(w[0], w[1], w[2], w[3]);
-    codes[2 * slot + 1] = make_uint4(w[4], w[5], w[6], w[7]);
-  } else {
-    codes[slot] = make_uint4(w[0], w[1], w[2], w[3]);
-  }
+  constexpr size_t kCodeBytes = FMT == QX_FORMAT_Q8_0 ? 32 : 16;
+  constexpr size_t kSlabCodes = kTileRows * kSlabBlocks * kCodeBytes;
+  uint8_t* span = panel + ts * (kSlabCodes + kTileRows * kSlabBlocks * 2);
+  reinterpret_cast<unsigned short*>(span + kSlabCodes)[j * kTileRows + r] = scale;
+  uint4* codes = reinterpret_cast<uint4*>(span + (r * kSlabBlocks + j) * kCodeBytes);
+  codes[0] = make_uint4(w[0], w[1], w[2], w[3]);
+  if (FMT == QX_FORMAT_Q8_0) codes[1] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
 }  // namespace
@@ -56,12 +55,10 @@ qx_status launch_relayout(const qx_weights* w, const uint8_t* src, cudaStream_t 
   const auto* in = reinterpret_cast<const unsigned short*>(src);
   if (w->format == QX_FORMAT_Q8_0) {
     relayout_kernel<QX_FORMAT_Q8_0><<<grid, 256, 0, stream>>>(
-        in, w->rows, w->blocks_per_row, w->slabs, total, reinterpret_cast<uint4*>(w->codes),
-        w->scales);
+        in, w->rows, w->blocks_per_row, w->slabs, total, w->panel);
   } else {
     relayout_kernel<QX_FORMAT_Q4_0><<<grid, 256, 0, stream>>>(
-        in, w->rows, w->blocks_per_row, w->slabs, total, reinterpret_cast<uint4*>(w->codes),
-        w->scales);
+        in, w->rows, w->blocks_per_row, w->slabs, total, w->panel);
   }
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
@@ -107,23 +104,19 @@ qx_status prepare_common(int format, const void* contract, bool contract_on_devi
   w->contract_bytes = shard_bytes;
   w->tiles = (row_count + kTileRows - 1) / kTileRows;
   w->slabs = (nb + kSlabBlocks - 1) / kSlabBlocks;
-  const size_t code_bytes = w->code_plane_bytes();
-  const size_t scale_bytes = w->scale_plane_bytes();
+  const size_t panel_bytes = w->panel_bytes();
 
   auto fail = [&](qx_status status) {
     qx_weights_destroy(w);
     return status;
   };
-  cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&w->codes), align_up(code_bytes, 256));
-  if (err == cudaSuccess) {
-    err = cudaMalloc(reinterpret_cast<void**>(&w->scales), align_up(scale_bytes, 256));
-  }
+  cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&w->panel), align_up(panel_bytes, 256));
   if (err != cudaSuccess) {
     set_last_error("cudaMalloc(prepared planes)", err);
     return fail(err == cudaErrorMemoryAllocation ? QX_STATUS_OUT_OF_MEMORY
                                                  : QX_STATUS_DEVICE_ERROR);
   }
-  w->prepared_bytes = code_bytes + scale_bytes;
+  w->prepared_bytes = panel_bytes;
 
   const uint8_t* shard_src = static_cast<const uint8_t*>(contract) +
                              static_cast<size_t>(row_begin) * nb * block_bytes;
@@ -208,8 +201,7 @@ qx_status qx_weights_get_info(const qx_weights* w, qx_weights_info* info) {
 
 void qx_weights_destroy(qx_weights* w) {
   if (w == nullptr) return;
-  if (w->codes != nullptr) (void)cudaFree(w->codes);
-  if (w->scales != nullptr) (void)cudaFree(w->scales);
+  if (w->panel != nullptr) (void)cudaFree(w->panel);
   if (w->dense_cache != nullptr) (void)cudaFree(w->dense_cache);
   delete w;
 }

@@ -5,11 +5,11 @@
 // with 32 (q8_0) or 16 (q4_0) code bytes, so no block starts on a 16-byte boundary. At
 // prepare time one pass re-lays the rows kept on this device out as tiles of 128 rows by
 // K-slabs of 4 blocks (128 elements), the unit one CTA pipeline stage consumes:
-//   codes  [tile][slab][row 0..127][4 blocks x (32 | 16) code bytes]   16 KiB | 8 KiB per slab
-//   scales [tile][slab][block 0..3][row 0..127] fp16 bits              1 KiB per slab
-// Each (tile, slab) is one contiguous span, so a stage is a single fully coalesced /
-// TMA-tiled read; rows of a code slab are 128 (64) bytes, exactly the 128-byte swizzle
-// atom of the tensor-core operand. Same byte count as the canonical layout (34 / 18
+//   panel [tile][slab]{ codes  [row 0..127][4 blocks x (32 | 16) code bytes]  16 KiB | 8 KiB
+//                       scales [block 0..3][row 0..127] fp16 bits             1 KiB }
+// Each (tile, slab) is one contiguous span of 17 KiB (q8_0) or 9 KiB (q4_0), so a stage
+// is ONE fully coalesced bulk / TMA-tiled read; rows of a q8_0 code slab are 128 bytes,
+// exactly the 128-byte swizzle atom of the tensor-core operand. Same byte count as the canonical layout (34 / 18
 // bytes per block) whenever rows % 128 == 0 and columns % 128 == 0 -- every benchmark
 // shape -- otherwise the last tile / slab is zero padded (a zero scale contributes 0).
 // This is the device counterpart of the reference's [row_panel, k_block, row_lane,
@@ -33,21 +33,19 @@ struct qx_weights {
   size_t contract_bytes = 0;
   size_t prepared_bytes = 0;
   uint64_t preparation_ns = 0;
-  uint8_t* codes = nullptr;         // device
-  unsigned short* scales = nullptr; // device, fp16 bits
+  uint8_t* panel = nullptr;  // device: [tile][slab]{codes, scales}
   // Lazily built by the prefill GEMM (see qx_q4_gemm.cu); not part of prepared_bytes
   // until built.
   void* dense_cache = nullptr;
   size_t dense_cache_bytes = 0;
 
   size_t code_bytes_per_block() const { return block_bytes - 2; }
-  size_t code_plane_bytes() const {
-    return static_cast<size_t>(tiles) * slabs * qx::kTileRows * qx::kSlabBlocks *
-           code_bytes_per_block();
+  // bytes of the codes / of the whole span of one (tile, slab)
+  size_t slab_code_bytes() const {
+    return static_cast<size_t>(qx::kTileRows) * qx::kSlabBlocks * code_bytes_per_block();
   }
-  size_t scale_plane_bytes() const {
-    return static_cast<size_t>(tiles) * slabs * qx::kTileRows * qx::kSlabBlocks * 2;
-  }
+  size_t slab_bytes() const { return slab_code_bytes() + qx::kTileRows * qx::kSlabBlocks * 2; }
+  size_t panel_bytes() const { return static_cast<size_t>(tiles) * slabs * slab_bytes(); }
 };
 
 namespace qx {
