@@ -159,6 +159,33 @@ QX_API qx_status qx_qgemm_prepacked_bf16_dev(const qx_weights* weights, const ui
                                       float* y_dev, long long m, long long ldy,
                                       qx_workspace* workspace, void* stream);
 
+/* Decode GEMV (m = 1) that never allocates device memory. No counterpart in the
+ * reference (its scratch is ordinary host memory).
+ *
+ * Who needs it: hosts that run the decode step where cudaMalloc / cudaFree are not
+ * available to them -- a serving loop whose device memory is handed out once by the
+ * application's own pool, a process whose GPU allocations are metered by an external
+ * broker, or a latency-critical thread that cannot afford the device-wide synchronisation
+ * an allocation implies. qx_qgemm_prepacked_dev grows a workspace on demand; this entry
+ * point instead keeps all of its scratch (activation images, partial sums, row counters)
+ * in one 6 MiB array that is part of the library image on every GPU that loads it, from
+ * load until process exit. `weights` is a handle prepared earlier (preparing allocates;
+ * do it at load time); x_dev [columns] and y_dev [rows] are device pointers.
+ *
+ * Limits and rules:
+ *  - the matrix must fit the array: about rows * min(32, columns/128) * 4 bytes <= 5 MiB
+ *    (every benchmark shape fits, e.g. 28672 x 8192); larger ones are rejected with
+ *    QX_STATUS_INVALID_SHAPE and a message from qx_last_error_string();
+ *  - the first call on a device looks up the array's device address (no allocation, but a
+ *    runtime query): make that call before starting any stream capture;
+ *  - all calls on a GPU share the array and it keeps the previous call's contents; each
+ *    call clears the counters it needs on `stream` first. Calls that could overlap on the
+ *    GPU (different streams, no ordering) race on it: keep them on one stream or order
+ *    them with events.
+ * Results are bit-identical to qx_qgemm_prepacked_dev with m = 1. */
+QX_API qx_status qx_qgemv_prepacked_noalloc_dev(const qx_weights* weights, const float* x_dev,
+                                                float* y_dev, void* stream);
+
 /* ---- W8A8 ---------------------------------------------------------------------- */
 
 /* int8_gemm, include/quixicore_cpu/qgemm.h:235-239 (src/dispatch/int8_gemm.cpp:67-94).

@@ -70,6 +70,7 @@ def _load():
         "qx_qgemm_prepacked": [_vp, _vp, _vp, _ll, _vp],
         "qx_qgemm_prepacked_dev": [_vp, _vp, _vp, _ll, _ll, _vp, _vp],
         "qx_qgemm_prepacked_bf16_dev": [_vp, _vp, _vp, _ll, _ll, _vp, _vp],
+        "qx_qgemv_prepacked_noalloc_dev": [_vp, _vp, _vp, _vp],
         "qx_int8_gemm": [_vp] * 7 + [_ll, _ll, _ll, C.c_int],
         "qx_qgemm_w8a8": [_vp] * 5 + [_ll, _ll, _ll],
         "qx_qgemm_w8a8_azp": [_vp] * 7 + [_ll, _ll, _ll],
@@ -246,6 +247,11 @@ class PackedWeights:
         ldy = y.shape[-1] if ldy is None else ldy
         return lib.qx_qgemm_prepacked_dev(self.handle, _dev(x), _vp(y.data_ptr()), m, ldy, None,
                                           _stream())
+
+    def qgemv_noalloc_dev(self, x, y) -> int:
+        """Decode GEMV through the entry point that never allocates device memory."""
+        return lib.qx_qgemv_prepacked_noalloc_dev(self.handle, _dev(x), _vp(y.data_ptr()),
+                                                  _stream())
 
     def qgemm_bf16_dev(self, x_bf16, y, m, ldy=None) -> int:
         ldy = y.shape[-1] if ldy is None else ldy

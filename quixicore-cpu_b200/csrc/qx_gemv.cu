@@ -9,6 +9,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "qx_gemv.cuh"
 #include "qx_gemv_tc.cuh"
@@ -240,3 +241,103 @@ qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev
 }
 
 }  // namespace qx
+
+// ------------------------------------------------------------------------------------
+// Decode GEMV for callers that must not allocate device memory.
+//
+// Some hosts of this library run the decode step where cudaMalloc is off limits: inside a
+// serving loop whose memory is handed out once at start-up by the application's own pool,
+// inside a process whose GPU allocations are metered or capped by an external broker, or
+// in a latency-critical thread where the implicit device synchronisation of cudaMalloc /
+// cudaFree is not acceptable. The regular entry points grow a workspace on demand and so
+// may allocate; this one never does. Its scratch memory (activation slab images, per-unit
+// partial sums, per-row counters and the pipeline error word) lives in the array below,
+// which every GPU that loads the library holds from module load until the process exits.
+// ------------------------------------------------------------------------------------
+namespace qx {
+namespace {
+
+constexpr size_t kNoAllocScratchBytes = 6u << 20;  // 6 MiB per GPU
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+struct NoAllocDevice {
+  uint8_t* scratch = nullptr;  // device address of g_noalloc_scratch on this GPU
+  int sm_count = 0;
+  bool ready = false;
+};
+NoAllocDevice g_noalloc_devices[64];
+std::mutex g_noalloc_mutex;
+
+// Once per device, with that device current: resolve the array's device address. The name
+// g_noalloc_scratch is only a host-side handle in host code; kernels need this address.
+qx_status noalloc_device(NoAllocDevice** out) {
+  int device = -1;
+  QX_CUDA_TRY(cudaGetDevice(&device));
+  if (device < 0 || device >= 64) {
+    set_last_error_text("device ordinal out of range");
+    return QX_STATUS_DEVICE_ERROR;
+  }
+  std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+  NoAllocDevice& entry = g_noalloc_devices[device];
+  if (!entry.ready) {
+    int major = 0, sms = 0;
+    QX_CUDA_TRY(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device));
+    QX_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
+    if (major != 10) {
+      set_last_error_text("device is not compute capability 10.x (B200); kernels are sm_100a only");
+      return QX_STATUS_DEVICE_ERROR;
+    }
+    void* address = nullptr;
+    QX_CUDA_TRY(cudaGetSymbolAddress(&address, g_noalloc_scratch));
+    entry.scratch = static_cast<uint8_t*>(address);
+    entry.sm_count = sms;
+    entry.ready = true;
+  }
+  *out = &entry;
+  return QX_STATUS_OK;
+}
+
+}  // namespace
+}  // namespace qx
+
+extern "C" qx_status qx_qgemv_prepacked_noalloc_dev(const qx_weights* weights, const float* x_dev,
+                                                     float* y_dev, void* stream) {
+  using namespace qx;
+  if (weights == nullptr || x_dev == nullptr || y_dev == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  NoAllocDevice* dev = nullptr;
+  QX_TRY(noalloc_device(&dev));
+  int device = -1;
+  QX_CUDA_TRY(cudaGetDevice(&device));
+  if (weights->device != device) {
+    set_last_error_text("qgemv (no-alloc): the weights were prepared on another device");
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  if (weights->columns > (1LL << 24)) return QX_STATUS_INVALID_SHAPE;
+  GemvScratch scratch;
+  QX_TRY(gemv_scratch_layout(weights, 1, dev->sm_count, &scratch));
+  const size_t error_offset = align_up(scratch.total_bytes, 256);
+  if (error_offset + 256 > kNoAllocScratchBytes) {
+    set_last_error_text(
+        "qgemv (no-alloc): this weight matrix needs more scratch than the 6 MiB static array "
+        "(limit is about rows * ceil(columns/128 units) * 4 B <= 5 MiB; use qx_qgemm_prepacked_dev)");
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  uint8_t* base = dev->scratch;
+  // The array keeps whatever the previous call left. The kernel expects the row counters it
+  // uses and the error word to be zero; everything else is fully rewritten before it is read.
+  QX_CUDA_TRY(cudaMemsetAsync(base, 0, static_cast<size_t>(weights->tiles) * kTileRows * sizeof(int), s));
+  QX_CUDA_TRY(cudaMemsetAsync(base + error_offset, 0, 256, s));
+
+  uint8_t* ximg = base + scratch.ximg_offset;
+  const int nb = static_cast<int>(weights->blocks_per_row);
+  const int nbpad = static_cast<int>(weights->slabs) * kSlabBlocks;
+  const int ncols = digit_columns(1);
+  const long long groups = static_cast<long long>(ncols / kDigitStride) * nbpad;
+  quantize_x_kernel<<<static_cast<unsigned>((groups + 31) / 32), 256, 0, s>>>(
+      x_dev, ximg, 1, static_cast<int>(weights->columns), nb, nbpad, ncols, groups);
+  count_launch();
+  QX_CUDA_TRY(cudaGetLastError());
+  return launch_gemv_tc_at(weights, ximg, y_dev, 1, weights->rows, base, scratch,
+                           reinterpret_cast<int*>(base + error_offset), s);
+}

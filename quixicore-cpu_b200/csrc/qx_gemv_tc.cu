@@ -755,6 +755,14 @@ qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScra
 qx_status launch_gemv_tc(const qx_weights* w, const uint8_t* ximg, float* y, int m,
                          long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
                          cudaStream_t stream) {
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  return launch_gemv_tc_at(w, ximg, y, m, ldy, ws_base, scratch, ctx->flag + 1, stream);
+}
+
+qx_status launch_gemv_tc_at(const qx_weights* w, const uint8_t* ximg, float* y, int m,
+                            long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
+                            int* error_word, cudaStream_t stream) {
   const int ncols = digit_columns(m);
   const long long kpad = w->slabs * kSlabK;
   CUtensorMap map_a{}, map_b{};  // map_b is unused (kept for the kernel signature)
@@ -766,15 +774,13 @@ qx_status launch_gemv_tc(const qx_weights* w, const uint8_t* ximg, float* y, int
       return QX_STATUS_DEVICE_ERROR;
     }
   }
-  DeviceContext* ctx = nullptr;
-  QX_TRY(current_context(&ctx));
   GemvTcParams p{};
   p.panel = w->panel;
   p.ximg = ximg;
   p.y = y;
   p.partial = reinterpret_cast<float*>(ws_base + scratch.partial_offset);
   p.counters = reinterpret_cast<int*>(ws_base);
-  p.error = ctx->flag + 1;
+  p.error = error_word;
   p.ldy = ldy;
   p.rows = w->rows;
   p.m = m;
