@@ -116,27 +116,6 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
-// Optional per-role wait accounting (build with -DQX_GEMV_PROFILE): cycles spent in each
-// kind of barrier wait, written per CTA to GemvTcParams::debug. Compiled out otherwise.
-#ifdef QX_GEMV_PROFILE
-#define QX_PROF_DECL(name) long long name = 0
-#define QX_PROF_WAIT(counter, expr)            \
-  [&]() {                                      \
-    const long long qx_t0_ = clock64();        \
-    const bool qx_ok_ = (expr);                \
-    counter += clock64() - qx_t0_;             \
-    return qx_ok_;                             \
-  }()
-#define QX_PROF_STORE(slot, value) \
-  if (p.debug != nullptr) p.debug[blockIdx.x * 16 + (slot)] = (value)
-#define QX_PROF_NOW() clock64()
-#else
-#define QX_PROF_DECL(name)
-#define QX_PROF_WAIT(counter, expr) (expr)
-#define QX_PROF_STORE(slot, value)
-#define QX_PROF_NOW() 0
-#endif
-
 template <int N>
 __device__ __forceinline__ void tmem_ld_cols(uint32_t taddr, uint32_t (&v)[N]);
 template <>

@@ -13,16 +13,18 @@
 // fixed token the 32 lanes of a warp store 32 consecutive floats of Y: fully coalesced
 // stores without a shared-memory transpose.
 //
-// Pipeline (persistent CTAs, one per SM, 192 threads):
+// Pipeline (persistent CTAs, one per SM, 320 threads):
 //   warp 0      TMA producer: 128-byte-swizzled K-slabs of W (128 x 128 B) and X
 //               (BN x 128 B) into a 4-stage shared-memory ring (full/empty mbarriers)
 //   warp 1      MMA issuer: one thread issues tcgen05.mma kind::i8 (K = 32 per
 //               instruction, four per slab) into one of two TMEM accumulators
-//   warps 2-5   epilogue: tcgen05.ld -> int->f32 -> scale -> global stores, overlapped
+//   warps 2-9   epilogue: tcgen05.ld -> int->f32 -> scale -> global stores, overlapped
 //               with the next tile's MMAs through the second accumulator
 // No cluster launch and no multicast: every CTA loads its own operands.
 
 #include <cuda.h>
+
+#include <cstdlib>
 
 #include "qx_int8_gemm.cuh"
 #include "qx_sm100.cuh"
@@ -71,8 +73,10 @@ namespace {
 
 constexpr int kBM = 128;        // output channels per tile (MMA M, TMEM lanes)
 constexpr int kBK = 128;        // bytes of K per pipeline stage (one swizzle atom)
-constexpr int kStages = 4;
-constexpr int kThreads = 192;
+constexpr int kMaxStages = 4;
+__host__ __device__ constexpr int stages_for(int na) { return na == 1 ? 4 : 3; }
+constexpr int kEpiWarps = 8;  // two per TMEM lane quarter, splitting the token columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kTmemCols = 512;  // two accumulators of up to 256 columns
 
 struct TcParams {
@@ -88,26 +92,35 @@ struct TcParams {
   int o_tiles, r_tiles;
   int asymmetric;
   int* error;    // device word, set non-zero when a bounded wait gave up
+  long long* debug;  // profiling builds only
 };
 
-struct __align__(8) TcBarriers {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+// 16-byte aligned and sized: the activation-scale tile behind it is read as float4
+struct __align__(16) TcBarriers {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
 
+// NA = weight tiles of 128 channels per CTA tile. NA = 1: 128 x bn outputs, two TMEM
+// accumulators (epilogue overlaps the next tile). NA = 2: 256 x bn outputs from one
+// activation slab per step -- a third less operand traffic from L2 per MAC, which is what
+// bounds this shape -- at the price of a single accumulator set (all 512 TMEM columns).
+template <int NA>
 __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
     const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
     const TcParams p) {
+  constexpr uint32_t kAccBuffers = NA == 1 ? 2 : 1;
+  constexpr int kStages = stages_for(NA);
   using namespace sm100;
   extern __shared__ uint8_t smem_raw[];
   // stage ring, 1024-byte aligned for the 128-byte swizzle
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  const uint32_t a_bytes = kBM * kBK;
+  const uint32_t a_bytes = NA * kBM * kBK;
   const uint32_t b_bytes = static_cast<uint32_t>(p.bn) * kBK;
   const uint32_t stage_bytes = a_bytes + b_bytes;
   TcBarriers* bars = reinterpret_cast<TcBarriers*>(smem + kStages * stage_bytes);
@@ -125,7 +138,7 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&bars->tmem_full[a], 1);
-      mbar_init(&bars->tmem_empty[a], 4);
+      mbar_init(&bars->tmem_empty[a], kEpiWarps);
     }
     bars->abort_flag = 0;
     mbar_fence_init();
@@ -151,11 +164,13 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      QX_PROF_DECL(w_empty);
+      const long long t_start = QX_PROF_NOW();
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int o0 = (tile / p.r_tiles) * kBM;
+        const int o0 = (tile / p.r_tiles) * (NA * kBM);
         const int r0 = (tile % p.r_tiles) * p.bn;
         for (int ks = 0; ks < p.k_slabs; ++ks) {
-          if (!mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag)) {
+          if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag))) {
             ok = false;
             break;
           }
@@ -169,6 +184,8 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
           }
         }
       }
+      QX_PROF_STORE(0, w_empty);
+      QX_PROF_STORE(1, QX_PROF_NOW() - t_start);
       if (!ok) {
         *abort_flag = 1;
         atomicExch(p.error, 1);
@@ -179,15 +196,18 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
     if (elect_one()) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
+      QX_PROF_DECL(w_full);
+      QX_PROF_DECL(w_tempty);
+      const long long t_start = QX_PROF_NOW();
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
+        if (!QX_PROF_WAIT(w_tempty, mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, abort_flag))) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * 256u;
+        const uint32_t d_tmem = tmem_base + acc * (NA * 256u);
         for (int ks = 0; ks < p.k_slabs; ++ks) {
-          if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+          if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->full[stage], phase, abort_flag))) {
             ok = false;
             break;
           }
@@ -198,8 +218,13 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
 #pragma unroll
           for (int kk = 0; kk < kBK / 32; ++kk) {
             // advance 32 bytes of K inside the swizzle atom: +2 in the (addr >> 4) field
-            mma_i8_ss(d_tmem, a_desc + static_cast<uint64_t>(kk * 2),
-                      b_desc + static_cast<uint64_t>(kk * 2), idesc, (ks | kk) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int na = 0; na < NA; ++na) {
+              // weight tile `na` starts kBM rows (16 KiB) further into the slab
+              mma_i8_ss(d_tmem + na * 256u,
+                        a_desc + static_cast<uint64_t>(kk * 2 + na * ((kBM * kBK) >> 4)),
+                        b_desc + static_cast<uint64_t>(kk * 2), idesc, (ks | kk) != 0 ? 1u : 0u);
+            }
           }
           tc_commit(&bars->empty[stage]);  // frees the slab once the MMAs have read it
           if (++stage == kStages) {
@@ -209,11 +234,14 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
         }
         if (!ok) break;
         tc_commit(&bars->tmem_full[acc]);
-        if (++acc == 2) {
+        if (++acc == kAccBuffers) {
           acc = 0;
           acc_phase ^= 1u;
         }
       }
+      QX_PROF_STORE(2, w_full);
+      QX_PROF_STORE(3, w_tempty);
+      QX_PROF_STORE(6, QX_PROF_NOW() - t_start);
       if (!ok) {
         *abort_flag = 1;
         atomicExch(p.error, 2);
@@ -221,54 +249,79 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
-    const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 belong to this warp
-    const int epi_thread = threadIdx.x - 64;  // 0..127
+    // Eight warps: warp w reads TMEM lanes 32*(w & 3).. (its channel quarter) and takes the
+    // 32-token column chunks c with (c & 1) == half. A thread owns one output channel, so
+    // for a fixed token the 32 lanes store 32 consecutive floats of Y.
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    const int epi_thread = threadIdx.x - 64;  // 0..255
     uint32_t acc = 0, acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const long long o = static_cast<long long>(tile / p.r_tiles) * kBM + quarter * 32 + lane;
+      const long long o_base = static_cast<long long>(tile / p.r_tiles) * (NA * kBM) + quarter * 32 + lane;
       const long long r0 = static_cast<long long>(tile % p.r_tiles) * p.bn;
       // stage this tile's activation scales (and zero points) for broadcast reads
       float* as_s = as_tile + acc * 256;
       int* zp_s = zp_tile + acc * 256;
-      for (int i = epi_thread; i < p.bn; i += 128) {
+      for (int i = epi_thread; i < p.bn; i += 32 * kEpiWarps) {
         const long long r = r0 + i;
         as_s[i] = r < p.m ? p.as[r] : 0.0f;
         zp_s[i] = (p.asymmetric && r < p.m) ? p.zp[r] : 0;
       }
-      const bool o_ok = o < p.n;
-      const float wscale = o_ok ? p.ws[o] : 0.0f;
-      const long long rsum = (p.asymmetric && o_ok) ? p.row_sum[o] : 0;
-      asm volatile("bar.sync 1, 128;" ::: "memory");  // epilogue warps only
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // epilogue warps only
 
       if (!mbar_wait(&bars->tmem_full[acc], acc_phase, abort_flag)) {
         ok = false;
         break;
       }
       tc_fence_after_sync();
-      for (int c = 0; c < p.bn / 32; ++c) {
-        uint32_t v[32];
-        const uint32_t taddr =
-            tmem_base + acc * 256u + static_cast<uint32_t>(c * 32) +
-            (static_cast<uint32_t>(quarter * 32) << 16);
-        tmem_ld_32x32(taddr, v);
-        tmem_ld_wait();
-        if (o_ok) {
+      const int chunks = p.bn / 32;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const long long r = r0 + c * 32 + j;
-            if (r < p.m) {
-              const int raw = static_cast<int>(v[j]);
-              float f;
-              if (p.asymmetric) {
-                const long long dot = static_cast<long long>(raw) - zp_s[c * 32 + j] * rsum;
-                f = __ll2float_rn(dot);
-                if (p.acc != nullptr) p.acc[r * p.n + o] = static_cast<int32_t>(dot);
-              } else {
-                f = __int2float_rn(raw);
-                if (p.acc != nullptr) p.acc[r * p.n + o] = raw;
+      for (int na = 0; na < NA; ++na) {
+        const long long o = o_base + na * kBM;
+        const bool o_ok = o < p.n;
+        const float wscale = o_ok ? p.ws[o] : 0.0f;
+        const long long rsum = (p.asymmetric && o_ok) ? p.row_sum[o] : 0;
+        for (int c = half; c < chunks; c += 2) {
+          uint32_t v[32];
+          const uint32_t taddr = tmem_base + (acc * NA + na) * 256u + static_cast<uint32_t>(c * 32) +
+                                 (static_cast<uint32_t>(quarter * 32) << 16);
+          tmem_ld_32x32(taddr, v);
+          tmem_ld_wait();
+          if (!o_ok) continue;
+          const long long rc = r0 + c * 32;
+          float* yp = p.y + rc * p.ldy + o;
+          const float* sc = as_s + c * 32;
+          if (!p.asymmetric && p.acc == nullptr && rc + 32 <= p.m) {
+            // common case: whole chunk in range, symmetric, no accumulator dump
+#pragma unroll
+            for (int j4 = 0; j4 < 32; j4 += 4) {
+              const float4 s4 = *reinterpret_cast<const float4*>(sc + j4);
+              const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+              for (int jj = 0; jj < 4; ++jj) {
+                const float f = __int2float_rn(static_cast<int>(v[j4 + jj]));
+                *yp = __fmul_rn(__fmul_rn(f, wscale), sv[jj]);
+                yp += p.ldy;
               }
-              p.y[r * p.ldy + o] = __fmul_rn(__fmul_rn(f, wscale), as_s[c * 32 + j]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const long long r = rc + j;
+              if (r < p.m) {
+                const int raw = static_cast<int>(v[j]);
+                float f;
+                if (p.asymmetric) {
+                  const long long dot = static_cast<long long>(raw) - zp_s[c * 32 + j] * rsum;
+                  f = __ll2float_rn(dot);
+                  if (p.acc != nullptr) p.acc[r * p.n + o] = static_cast<int32_t>(dot);
+                } else {
+                  f = __int2float_rn(raw);
+                  if (p.acc != nullptr) p.acc[r * p.n + o] = raw;
+                }
+                p.y[r * p.ldy + o] = __fmul_rn(__fmul_rn(f, wscale), sc[j]);
+              }
             }
           }
         }
@@ -276,7 +329,7 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->tmem_empty[acc]);
-      if (++acc == 2) {
+      if (++acc == kAccBuffers) {
         acc = 0;
         acc_phase ^= 1u;
       }
@@ -295,8 +348,8 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
   }
 }
 
-size_t tc_smem_bytes(int bn) {
-  return 1024 + static_cast<size_t>(kStages) * (kBM * kBK + bn * kBK) + sizeof(TcBarriers) +
+size_t tc_smem_bytes(int na, int bn) {
+  return 1024 + static_cast<size_t>(stages_for(na)) * (na * kBM * kBK + bn * kBK) + sizeof(TcBarriers) +
          2 * 256 * sizeof(float) + 2 * 256 * sizeof(int) + 64;
 }
 
@@ -309,14 +362,45 @@ bool int8_gemm_tc_supported(const Int8GemmArgs& a) {
   return encode_fn() != nullptr;
 }
 
+namespace {
+template <int NA>
+qx_status launch_tc_na(const CUtensorMap& map_w, const CUtensorMap& map_x, const TcParams& p,
+                       int grid, cudaStream_t stream) {
+  static bool attr_set = false;
+  if (!attr_set) {
+    QX_CUDA_TRY(cudaFuncSetAttribute(int8_gemm_tc_kernel<NA>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(tc_smem_bytes(NA, 256))));
+    attr_set = true;
+  }
+  int8_gemm_tc_kernel<NA><<<grid, kThreads, tc_smem_bytes(NA, p.bn), stream>>>(map_w, map_x, p);
+  count_launch();
+  QX_CUDA_TRY(cudaGetLastError());
+  return QX_STATUS_OK;
+}
+
+// weight tiles per CTA tile: 2 (256 channels) when that still gives most SMs a tile
+int choose_weight_tiles(long long n, long long r_tiles, int sm_count) {
+  if (const char* forced = std::getenv("QX_B200_INT8_WEIGHT_TILES")) {
+    if (forced[0] == '1') return 1;
+    if (forced[0] == '2') return 2;
+  }
+  const long long tiles2 = (n + 2 * kBM - 1) / (2 * kBM) * r_tiles;
+  return tiles2 * 10 >= static_cast<long long>(sm_count) * 6 ? 2 : 1;
+}
+}  // namespace
+
 qx_status launch_int8_gemm_tc(const Int8GemmArgs& a, cudaStream_t stream) {
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
   int bn = 256;
   if (a.m < 256) bn = static_cast<int>((a.m + 31) / 32 * 32);
+  const long long r_tiles = (a.m + bn - 1) / bn;
+  const int na = choose_weight_tiles(a.n, r_tiles, ctx->prop.multiProcessorCount);
   CUtensorMap map_w, map_x;
   if (!encode_tma_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.w, static_cast<uint64_t>(a.k),
-                     static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k), kBK, kBM) ||
+                     static_cast<uint64_t>(a.n), static_cast<uint64_t>(a.k), kBK,
+                     static_cast<uint32_t>(na * kBM)) ||
       !encode_tma_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, a.x, static_cast<uint64_t>(a.k),
                      static_cast<uint64_t>(a.m), static_cast<uint64_t>(a.k), kBK,
                      static_cast<uint32_t>(bn))) {
@@ -335,27 +419,17 @@ qx_status launch_int8_gemm_tc(const Int8GemmArgs& a, cudaStream_t stream) {
   p.ldy = a.ldy;
   p.k_slabs = static_cast<int>((a.k + kBK - 1) / kBK);
   p.bn = bn;
-  p.o_tiles = static_cast<int>((a.n + kBM - 1) / kBM);
-  p.r_tiles = static_cast<int>((a.m + bn - 1) / bn);
+  p.o_tiles = static_cast<int>((a.n + na * kBM - 1) / (na * kBM));
+  p.r_tiles = static_cast<int>(r_tiles);
   p.asymmetric = a.asymmetric ? 1 : 0;
   p.error = ctx->flag + 1;
-
-  const size_t smem = tc_smem_bytes(bn);
-  static bool attr_set = false;
-  if (!attr_set) {
-    QX_CUDA_TRY(cudaFuncSetAttribute(int8_gemm_tc_kernel,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(tc_smem_bytes(256))));
-    attr_set = true;
-  }
+  p.debug = gemv_profile_buffer();
   const long long tiles = static_cast<long long>(p.o_tiles) * p.r_tiles;
   const int grid = static_cast<int>(tiles < ctx->prop.multiProcessorCount
                                         ? tiles
                                         : ctx->prop.multiProcessorCount);
-  int8_gemm_tc_kernel<<<grid, kThreads, smem, stream>>>(map_w, map_x, p);
-  count_launch();
-  QX_CUDA_TRY(cudaGetLastError());
-  return QX_STATUS_OK;
+  return na == 2 ? launch_tc_na<2>(map_w, map_x, p, grid, stream)
+                 : launch_tc_na<1>(map_w, map_x, p, grid, stream);
 }
 
 }  // namespace qx

@@ -172,6 +172,30 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
 
 }  // namespace sm100
 
+// Optional per-role wait accounting (build with -DQX_GEMV_PROFILE): cycles spent in each
+// kind of barrier wait, written per CTA to the kernel parameter `debug`. Compiled out otherwise.
+#ifdef QX_GEMV_PROFILE
+#define QX_PROF_DECL(name) long long name = 0
+#define QX_PROF_WAIT(counter, expr)            \
+  [&]() {                                      \
+    const long long qx_t0_ = clock64();        \
+    const bool qx_ok_ = (expr);                \
+    counter += clock64() - qx_t0_;             \
+    return qx_ok_;                             \
+  }()
+#define QX_PROF_STORE(slot, value) \
+  if (p.debug != nullptr) p.debug[blockIdx.x * 16 + (slot)] = (value)
+#define QX_PROF_NOW() clock64()
+#else
+#define QX_PROF_DECL(name)
+#define QX_PROF_WAIT(counter, expr) (expr)
+#define QX_PROF_STORE(slot, value)
+#define QX_PROF_NOW() 0
+#endif
+
+// Device buffer [1024 CTAs][16] the profiling build writes its counters to (null otherwise).
+long long* gemv_profile_buffer();
+
 // Host side: cuTensorMapEncodeTiled through the runtime's driver entry point lookup (the
 // library does not link libcuda). Encodes a row-major 2D tensor [rows][row_bytes /
 // elem_bytes] with the given box and the 128-byte swizzle.
