@@ -76,6 +76,9 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
     for (int s = 1; s < 8; s <<= 1) psum[d] += __shfl_xor_sync(0xffffffffu, psum[d], s);
   }
   if (!in_range) return;
+  // The images may still be read by the GEMV launched before this kernel (both are
+  // launched programmatically, so this kernel can start early): wait for it to finish.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   uint8_t* image = ximg + static_cast<long long>(b / kSlabBlocks) * ximage_bytes(ncols);
   const int j = b % kSlabBlocks;
 #pragma unroll
@@ -217,8 +220,19 @@ qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev
 
     const int vrows = ncols / kDigitStride;
     const long long groups = static_cast<long long>(vrows) * nbpad;
-    quantize_x_kernel<<<static_cast<unsigned>((groups + 31) / 32), 256, 0, stream>>>(
-        x_dev + m0 * w->columns, ximg, mc, static_cast<int>(w->columns), nb, nbpad, ncols, groups);
+    {
+      cudaLaunchConfig_t config{};
+      config.gridDim = dim3(static_cast<unsigned>((groups + 31) / 32));
+      config.blockDim = dim3(256);
+      config.stream = stream;
+      cudaLaunchAttribute attribute{};
+      attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attribute.val.programmaticStreamSerializationAllowed = 1;
+      config.attrs = &attribute;
+      config.numAttrs = 1;
+      QX_CUDA_TRY(cudaLaunchKernelEx(&config, quantize_x_kernel, x_dev + m0 * w->columns, ximg, mc,
+                                     static_cast<int>(w->columns), nb, nbpad, ncols, groups));
+    }
     count_launch();
     float* y = y_dev + m0 * ldy;
     if (!force_dp4a()) {

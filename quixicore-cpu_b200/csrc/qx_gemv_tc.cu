@@ -160,6 +160,9 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = &bars->abort_flag;
+  // kernels queued behind this one may be scheduled as soon as SMs free up; whatever they
+  // touch of this kernel's data they guard with their own griddepcontrol.wait
+  asm volatile("griddepcontrol.launch_dependents;");
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < G::kStages; ++s) {
