@@ -18,84 +18,122 @@
 namespace qx {
 namespace {
 
-// ------------------------------------------------------------------------------------
-// activation digits: x[m][k] f32 -> one image per K-slab (see ximage_bytes): digit rows
-// (row 4*m+d = digit d of activation row m, d < 3; row 4*m+3, unused rows and the K padding
-// are written as zeros) followed by the per-block constants.
-// One group of 8 threads per (virtual row, block); virtual rows beyond m only zero-fill.
-// ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict__ x,
-                                                         uint8_t* __restrict__ ximg, int m, int k,
-                                                         int nb, int nbpad, int ncols,
-                                                         long long total_groups) {
-  // let the GEMV kernel behind this one start its set-up and weight pipeline right away
-  asm volatile("griddepcontrol.launch_dependents;");
-  const long long group = blockIdx.x * 32LL + (threadIdx.x >> 3);
-  const int q = threadIdx.x & 7;
-  const bool in_range = group < total_groups;
-  const int vm = in_range ? static_cast<int>(group / nbpad) : 0;
-  const int b = in_range ? static_cast<int>(group % nbpad) : 0;
-  const bool real = in_range && vm < m && b < nb;
-  float v[4] = {0.f, 0.f, 0.f, 0.f};
-  if (real) {
-    const float* src = x + static_cast<long long>(vm) * k + b * 32 + q * 4;
+// Balanced base-256 digit `d` (0..3) of t: t = sum_d 256^d * digit_d, digits 0..2 in
+// [-128, 127].
+__device__ __forceinline__ int balanced_digit(int t, int d) {
+  int p = ((t + 128) & 255) - 128;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = src[i];
+  for (int i = 0; i < 3; ++i) {
+    if (i < d) {
+      t = (t - p) >> 8;
+      p = i == 2 ? t : ((t + 128) & 255) - 128;
+    }
   }
+  return p;
+}
+
+// Envelope of one 32-element block: *scale_up = 2^(22-e), *scale = 2^(e-22) with 2^e
+// above the largest magnitude; NaN scale (and *finite false) for a non-finite element.
+__device__ __forceinline__ void block_envelope(const float (&v)[32], float* scale_up, float* scale,
+                                               bool* finite) {
   // max of |bits|: orders finite < inf < NaN, so non-finite inputs are detected
   uint32_t amax_bits = 0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) amax_bits = max(amax_bits, __float_as_uint(v[i]) & 0x7FFFFFFFu);
-#pragma unroll
-  for (int s = 1; s < 8; s <<= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, s));
+  for (int i = 0; i < 32; ++i) amax_bits = max(amax_bits, __float_as_uint(v[i]) & 0x7FFFFFFFu);
   const uint32_t eb_raw = amax_bits >> 23;
-  const bool finite = eb_raw != 255u;
-  const uint32_t eb = max(eb_raw, 30u);                       // envelope 2^(eb-126) > amax
-  const float scale_up = __uint_as_float((275u - eb) << 23);  // 2^(22 - e)
-  float scale = __uint_as_float((eb - 21u) << 23);            // 2^(e - 22)
-  if (!finite) scale = __uint_as_float(0x7FC00000u);          // NaN/inf in -> NaN out
-  uint32_t word[3] = {0, 0, 0};
-  int psum[3] = {0, 0, 0};
+  *finite = eb_raw != 255u;
+  const uint32_t eb = max(eb_raw, 30u);                  // envelope 2^(eb-126) > amax
+  *scale_up = __uint_as_float((275u - eb) << 23);        // 2^(22 - e)
+  *scale = *finite ? __uint_as_float((eb - 21u) << 23)   // 2^(e - 22)
+                   : __uint_as_float(0x7FC00000u);       // NaN/inf in -> NaN out
+}
+
+// ------------------------------------------------------------------------------------
+// Activation digits: x[m][k] f32 -> one image per K-slab (layout: qx_gemv.cuh). The first
+// `chunk_threads` threads write one 16-byte chunk of a digit row each (zeros outside the
+// block class of the row, for padded rows and for the K padding); the remaining threads
+// write one XConst each.
+// ------------------------------------------------------------------------------------
+template <int FMT>
+__global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict__ x,
+                                                         uint8_t* __restrict__ ximg, int m, int mp,
+                                                         int k, int nb, long long chunk_threads,
+                                                         long long total_threads) {
+  // let the GEMV kernel behind this one start its set-up and weight pipeline right away
+  asm volatile("griddepcontrol.launch_dependents;");
+  const long long t = blockIdx.x * 256LL + threadIdx.x;
+  if (t >= total_threads) return;
+  const int ncols = digit_columns(FMT, mp);
+  const int group = group_blocks(FMT, mp);
+  const size_t image_bytes = ximage_bytes(FMT, mp);
+  float v[32];
+  if (t < chunk_threads) {
+    const int c16 = static_cast<int>(t & 15);
+    const int n = static_cast<int>((t >> 4) % ncols);
+    const long long slab = (t >> 4) / ncols;
+    const int which = c16 >> 3, cc = c16 & 7;
+    const int j = FMT == QX_FORMAT_Q8_0 ? 4 * which + (cc >> 1) : cc;
+    const int half = cc & 1;
+    const int klass = n / (4 * mp), row = (n >> 2) % mp, d = n & 3;
+    const long long b = slab * kSlabBlocks + j;
+    const bool digit_used = FMT == QX_FORMAT_Q8_0 ? d < 3 : (which == 1 || d < 3);
+    const bool active = (j % group) == klass && row < m && b < nb && digit_used;
+    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+    if (active) {
+      const float* src = x + static_cast<long long>(row) * k + b * 32;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int t = finite ? __float2int_rn(v[i] * scale_up) : 0;  // |t| <= 2^22
-    const int p0 = ((t + 128) & 255) - 128;
-    const int t1 = (t - p0) >> 8;
-    const int p1 = ((t1 + 128) & 255) - 128;
-    const int p2 = (t1 - p1) >> 8;
-    word[0] |= static_cast<uint32_t>(p0 & 255) << (8 * i);
-    word[1] |= static_cast<uint32_t>(p1 & 255) << (8 * i);
-    word[2] |= static_cast<uint32_t>(p2 & 255) << (8 * i);
-    psum[0] += p0;
-    psum[1] += p1;
-    psum[2] += p2;
-  }
+      for (int i = 0; i < 32; ++i) v[i] = src[i];
+      float scale_up, scale;
+      bool finite;
+      block_envelope(v, &scale_up, &scale, &finite);
+      uint32_t word[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-  for (int d = 0; d < 3; ++d) {
-#pragma unroll
-    for (int s = 1; s < 8; s <<= 1) psum[d] += __shfl_xor_sync(0xffffffffu, psum[d], s);
-  }
-  if (!in_range) return;
-  // The images may still be read by the GEMV launched before this kernel (both are
-  // launched programmatically, so this kernel can start early): wait for it to finish.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  uint8_t* image = ximg + static_cast<long long>(b / kSlabBlocks) * ximage_bytes(ncols);
-  const int j = b % kSlabBlocks;
-#pragma unroll
-  for (int d = 0; d < kDigitStride; ++d) {
-    const int col = vm * kDigitStride + d;
-    if (col < ncols) {
-      *reinterpret_cast<uint32_t*>(image + ximage_digit_offset(col, j, q)) =
-          (real && d < 3) ? word[d < 3 ? d : 0] : 0u;
+      for (int i = 0; i < 16; ++i) {
+        int value = 0;
+        if (finite) {
+          if (FMT == QX_FORMAT_Q8_0) {
+            value = __float2int_rn((half != 0 ? v[16 + i] : v[i]) * scale_up);  // |t| <= 2^22
+          } else {
+            const int lo = __float2int_rn(v[i] * scale_up);
+            value = which == 0 ? lo : __float2int_rn(v[16 + i] * scale_up) - 16 * lo;
+          }
+        }
+        word[i >> 2] |= static_cast<uint32_t>(balanced_digit(value, d) & 255) << (8 * (i & 3));
+      }
+      out = make_uint4(word[0], word[1], word[2], word[3]);
     }
-  }
-  if (q == 0 && vm < m) {
+    // The images may still be read by the GEMV launched before this kernel (both are
+    // launched programmatically, so this kernel can start early): wait for it to finish.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    *reinterpret_cast<uint4*>(ximg + slab * image_bytes + ximage_chunk_offset(ncols, which, n, cc)) =
+        out;
+  } else {
+    const long long u = t - chunk_threads;
+    const int row = static_cast<int>(u % mp);
+    const int j = static_cast<int>((u / mp) % kSlabBlocks);
+    const long long slab = u / (static_cast<long long>(mp) * kSlabBlocks);
+    const long long b = slab * kSlabBlocks + j;
     XConst c;
-    c.scale = real ? scale : 0.0f;
-    c.k01 = real ? 8 * (256 * psum[1] + psum[0]) : 0;
-    c.p2x8 = real ? 8 * psum[2] : 0;
-    c.pad = 0;
-    reinterpret_cast<XConst*>(image + ncols * 128)[vm * kSlabBlocks + j] = c;
+    c.scale = 0.0f;
+    c.k_lo = c.k_hi = c.pad = 0;
+    if (row < m && b < nb) {
+      const float* src = x + static_cast<long long>(row) * k + b * 32;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = src[i];
+      float scale_up;
+      bool finite;
+      block_envelope(v, &scale_up, &c.scale, &finite);
+      if (FMT == QX_FORMAT_Q4_0 && finite) {
+        int sum = 0;  // |sum| <= 32 * 2^22
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sum += __float2int_rn(v[i] * scale_up);
+        const int k8 = 8 * sum;
+        c.k_lo = k8 & 0xFFFF;
+        c.k_hi = k8 >> 16;
+      }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    *reinterpret_cast<XConst*>(ximg + slab * image_bytes + ximage_const_offset(ncols, mp, j, row)) = c;
   }
 }
 
@@ -107,20 +145,19 @@ __device__ __forceinline__ float warp_tree_sum(float v) {
 
 // ------------------------------------------------------------------------------------
 // CUDA-core kernel: one warp per (weight row, activation row); lanes stride over blocks.
-// Reduction: per group of 32 consecutive blocks a fixed xor-butterfly (16, 8, 4, 2, 1),
-// groups added in ascending order, so the result does not depend on the launch shape.
+// Same digit arithmetic as the tensor-core kernel, block by block with dp4a. Reduction:
+// per group of 32 consecutive blocks a fixed xor-butterfly (16, 8, 4, 2, 1), groups added
+// in ascending order, so the result does not depend on the launch shape.
 // ------------------------------------------------------------------------------------
 template <int FMT>
 __global__ void __launch_bounds__(256) gemv_dp4a_kernel(
-    const uint8_t* __restrict__ panel, const uint8_t* __restrict__ ximg, int ncols,
+    const uint8_t* __restrict__ panel, const uint8_t* __restrict__ ximg, int mp,
     float* __restrict__ y, long long n, int nb, long long slabs, long long ldy) {
-  constexpr int kVec = FMT == QX_FORMAT_Q8_0 ? 2 : 1;  // 16-byte vectors of codes per block
   const int lane = threadIdx.x & 31;
   const long long row = blockIdx.x * 8LL + (threadIdx.x >> 5);
   if (row >= n) return;
   const int m = blockIdx.y;
-  constexpr size_t kCodeBytes = FMT == QX_FORMAT_Q8_0 ? 32 : 16;
-  constexpr size_t kSlabCodes = kTileRows * kSlabBlocks * kCodeBytes;
+  const int ncols = digit_columns(FMT, mp);
   const long long tile = row / kTileRows;
   const int r = static_cast<int>(row % kTileRows);
   float acc = 0.0f;
@@ -128,55 +165,51 @@ __global__ void __launch_bounds__(256) gemv_dp4a_kernel(
     const int b = base + lane;
     float v = 0.0f;
     if (b < nb) {
-      const long long ts = tile * slabs + b / kSlabBlocks;
       const int j = b % kSlabBlocks;
-      const uint8_t* span = panel + ts * (kSlabCodes + kTileRows * kSlabBlocks * 2);
-      const uint4* codes = reinterpret_cast<const uint4*>(span + (r * kSlabBlocks + j) * kCodeBytes);
-      const uint8_t* image = ximg + static_cast<long long>(b / kSlabBlocks) * ximage_bytes(ncols);
-      uint32_t w[8];
-#pragma unroll
-      for (int i = 0; i < kVec; ++i) {
-        const uint4 c = __ldg(codes + i);
-        w[4 * i] = c.x; w[4 * i + 1] = c.y; w[4 * i + 2] = c.z; w[4 * i + 3] = c.w;
-      }
-      uint32_t dig[3][8];
-#pragma unroll
-      for (int d = 0; d < 3; ++d) {
-        const int col = m * kDigitStride + d;
-        const uint4 lo = __ldg(reinterpret_cast<const uint4*>(image + ximage_digit_offset(col, j, 0)));
-        const uint4 hi = __ldg(reinterpret_cast<const uint4*>(image + ximage_digit_offset(col, j, 4)));
-        dig[d][0] = lo.x; dig[d][1] = lo.y; dig[d][2] = lo.z; dig[d][3] = lo.w;
-        dig[d][4] = hi.x; dig[d][5] = hi.y; dig[d][6] = hi.z; dig[d][7] = hi.w;
-      }
-      const XConst c = reinterpret_cast<const XConst*>(image + ncols * 128)[m * kSlabBlocks + j];
-      int s[3];
+      const uint8_t* span = panel + (tile * slabs + b / kSlabBlocks) * slab_span_bytes(FMT);
+      const uint8_t* image = ximg + static_cast<long long>(b / kSlabBlocks) * ximage_bytes(FMT, mp);
+      const XConst c = *reinterpret_cast<const XConst*>(image + ximage_const_offset(ncols, mp, j, m));
+      int s[4] = {0, 0, 0, 0};
       if (FMT == QX_FORMAT_Q8_0) {
 #pragma unroll
-        for (int d = 0; d < 3; ++d) {
-          int t = 0;
+        for (int half = 0; half < 2; ++half) {
+          const uint4 w = __ldg(reinterpret_cast<const uint4*>(span + panel_code_offset_q8(r, j, half)));
 #pragma unroll
-          for (int i = 0; i < 8; ++i) t = dp4a_ss(w[i], dig[d][i], t);
-          s[d] = t;
+          for (int d = 0; d < 3; ++d) {
+            const uint4 g = __ldg(reinterpret_cast<const uint4*>(
+                image + ximage_chunk_offset(ncols, j >> 2, digit_row(FMT, mp, j, m, d),
+                                            2 * (j & 3) + half)));
+            s[d] = dp4a_ss(w.x, g.x, s[d]);
+            s[d] = dp4a_ss(w.y, g.y, s[d]);
+            s[d] = dp4a_ss(w.z, g.z, s[d]);
+            s[d] = dp4a_ss(w.w, g.w, s[d]);
+          }
         }
       } else {
-        // byte i of the block: low nibble = element i, high nibble = element i + 16; the
-        // high nibbles are used in place (16 * nibble), so their sums are multiples of 16
+        // raw bytes against the digits of t_i, high nibbles against the digits of z_i
+        const uint4 w = __ldg(reinterpret_cast<const uint4*>(span + panel_code_offset_q4(r, j)));
+        const uint4 h = make_uint4((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu,
+                                   (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu);
 #pragma unroll
-        for (int d = 0; d < 3; ++d) {
-          int lo = 0, hi = 0;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            lo = dp4a_us(w[i] & 0x0F0F0F0Fu, dig[d][i], lo);
-            hi = dp4a_us(w[i] & 0xF0F0F0F0u, dig[d][4 + i], hi);
+        for (int d = 0; d < 4; ++d) {
+          const int nrow = digit_row(FMT, mp, j, m, d);
+          if (d < 3) {
+            const uint4 g = __ldg(reinterpret_cast<const uint4*>(image + ximage_chunk_offset(ncols, 0, nrow, j)));
+            s[d] = dp4a_us(w.x, g.x, s[d]);
+            s[d] = dp4a_us(w.y, g.y, s[d]);
+            s[d] = dp4a_us(w.z, g.z, s[d]);
+            s[d] = dp4a_us(w.w, g.w, s[d]);
           }
-          s[d] = lo + (hi >> 4);
+          const uint4 z = __ldg(reinterpret_cast<const uint4*>(image + ximage_chunk_offset(ncols, 1, nrow, j)));
+          s[d] = dp4a_us(h.x, z.x, s[d]);
+          s[d] = dp4a_us(h.y, z.y, s[d]);
+          s[d] = dp4a_us(h.z, z.z, s[d]);
+          s[d] = dp4a_us(h.w, z.w, s[d]);
         }
-        s[0] -= c.k01;  // together with s[1]*256 below: -8 * sum_j (256*p1 + p0)
-        s[2] -= c.p2x8;
       }
       const float d = half_bits_to_float(
-          reinterpret_cast<const unsigned short*>(span + kSlabCodes)[j * kTileRows + r]);
-      v = __fmul_rn(combine_digits(s[1] * 256 + s[0], s[2]), __fmul_rn(d, c.scale));
+          *reinterpret_cast<const unsigned short*>(span + panel_scale_offset(FMT, r, j)));
+      v = __fmul_rn(block_sum(s[0], s[1], s[2], s[3], c.k_lo, c.k_hi), __fmul_rn(d, c.scale));
     }
     acc += warp_tree_sum(v);
   }
@@ -191,6 +224,36 @@ bool force_dp4a() {
   return forced;
 }
 
+// Enqueues the quantizer for `m` activation rows (x_dev [m][columns]) into `ximg`.
+// `programmatic`: launched so that it may start before the kernel ahead of it in the stream
+// has finished (it waits for that kernel itself before it writes).
+qx_status launch_quantizer(const qx_weights* w, const float* x_dev, uint8_t* ximg, int m,
+                           bool programmatic, cudaStream_t stream) {
+  const int mp = padded_batch(m);
+  const long long chunk_threads =
+      static_cast<long long>(w->slabs) * digit_columns(w->format, mp) * 16;
+  const long long total_threads = chunk_threads + static_cast<long long>(w->slabs) * kSlabBlocks * mp;
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(static_cast<unsigned>((total_threads + 255) / 256));
+  config.blockDim = dim3(256);
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = programmatic ? 1 : 0;
+  const int k = static_cast<int>(w->columns), nb = static_cast<int>(w->blocks_per_row);
+  if (w->format == QX_FORMAT_Q8_0) {
+    QX_CUDA_TRY(cudaLaunchKernelEx(&config, quantize_x_kernel<QX_FORMAT_Q8_0>, x_dev, ximg, m, mp, k,
+                                   nb, chunk_threads, total_threads));
+  } else {
+    QX_CUDA_TRY(cudaLaunchKernelEx(&config, quantize_x_kernel<QX_FORMAT_Q4_0>, x_dev, ximg, m, mp, k,
+                                   nb, chunk_threads, total_threads));
+  }
+  count_launch();
+  return QX_STATUS_OK;
+}
+
 }  // namespace
 
 const char* gemv_variant_name() { return force_dp4a() ? "sm100a_dp4a" : "sm100a_tcgen05_digits"; }
@@ -200,9 +263,6 @@ const char* gemv_variant_name() { return force_dp4a() ? "sm100a_dp4a" : "sm100a_
 qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev,
                            long long m, long long ldy, qx_workspace* ws,
                            cudaStream_t stream) {
-  const int nb = static_cast<int>(w->blocks_per_row);
-  const int nbpad = static_cast<int>(w->slabs) * kSlabBlocks;
-  const long long kpad = static_cast<long long>(nbpad) * 32;
   if (w->columns > (1LL << 24) || w->rows > (1LL << 31) - 256) {
     set_last_error_text("qgemm: shape beyond the GEMV kernels' 32-bit tile indices");
     return QX_STATUS_INVALID_SHAPE;
@@ -211,45 +271,28 @@ qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev
   QX_TRY(current_context(&ctx));
   for (long long m0 = 0; m0 < m; m0 += kGemvMaxBatch) {
     const int mc = static_cast<int>(m - m0 < kGemvMaxBatch ? m - m0 : kGemvMaxBatch);
-    const int ncols = digit_columns(mc);
     GemvScratch scratch;
     QX_TRY(gemv_scratch_layout(w, mc, ctx->prop.multiProcessorCount, &scratch));
     QX_TRY(ws->reserve(scratch.total_bytes));
     uint8_t* base = static_cast<uint8_t*>(ws->base);
     uint8_t* ximg = base + scratch.ximg_offset;
-
-    const int vrows = ncols / kDigitStride;
-    const long long groups = static_cast<long long>(vrows) * nbpad;
-    {
-      cudaLaunchConfig_t config{};
-      config.gridDim = dim3(static_cast<unsigned>((groups + 31) / 32));
-      config.blockDim = dim3(256);
-      config.stream = stream;
-      cudaLaunchAttribute attribute{};
-      attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attribute.val.programmaticStreamSerializationAllowed = 1;
-      config.attrs = &attribute;
-      config.numAttrs = 1;
-      QX_CUDA_TRY(cudaLaunchKernelEx(&config, quantize_x_kernel, x_dev + m0 * w->columns, ximg, mc,
-                                     static_cast<int>(w->columns), nb, nbpad, ncols, groups));
-    }
-    count_launch();
+    QX_TRY(launch_quantizer(w, x_dev + m0 * w->columns, ximg, mc, true, stream));
     float* y = y_dev + m0 * ldy;
     if (!force_dp4a()) {
       QX_TRY(launch_gemv_tc(w, ximg, y, mc, ldy, base, scratch, stream));
     } else {
       const dim3 grid(static_cast<unsigned>((w->rows + 7) / 8), static_cast<unsigned>(mc));
+      const int mp = padded_batch(mc), nb = static_cast<int>(w->blocks_per_row);
       if (w->format == QX_FORMAT_Q8_0) {
-        gemv_dp4a_kernel<QX_FORMAT_Q8_0><<<grid, 256, 0, stream>>>(w->panel, ximg, ncols, y, w->rows,
-                                                                   nb, w->slabs, ldy);
+        gemv_dp4a_kernel<QX_FORMAT_Q8_0><<<grid, 256, 0, stream>>>(w->panel, ximg, mp, y, w->rows, nb,
+                                                                   w->slabs, ldy);
       } else {
-        gemv_dp4a_kernel<QX_FORMAT_Q4_0><<<grid, 256, 0, stream>>>(w->panel, ximg, ncols, y, w->rows,
-                                                                   nb, w->slabs, ldy);
+        gemv_dp4a_kernel<QX_FORMAT_Q4_0><<<grid, 256, 0, stream>>>(w->panel, ximg, mp, y, w->rows, nb,
+                                                                   w->slabs, ldy);
       }
       count_launch();
     }
     QX_CUDA_TRY(cudaGetLastError());
-    (void)kpad;
   }
   return QX_STATUS_OK;
 }
@@ -333,7 +376,7 @@ extern "C" qx_status qx_qgemv_prepacked_noalloc_dev(const qx_weights* weights, c
   if (error_offset + 256 > kNoAllocScratchBytes) {
     set_last_error_text(
         "qgemv (no-alloc): this weight matrix needs more scratch than the 6 MiB static array "
-        "(limit is about rows * ceil(columns/128 units) * 4 B <= 5 MiB; use qx_qgemm_prepacked_dev)");
+        "(limit is about rows * min(32, columns/256) * 4 B <= 5 MiB; use qx_qgemm_prepacked_dev)");
     return QX_STATUS_INVALID_SHAPE;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -344,14 +387,7 @@ extern "C" qx_status qx_qgemv_prepacked_noalloc_dev(const qx_weights* weights, c
   QX_CUDA_TRY(cudaMemsetAsync(base + error_offset, 0, 256, s));
 
   uint8_t* ximg = base + scratch.ximg_offset;
-  const int nb = static_cast<int>(weights->blocks_per_row);
-  const int nbpad = static_cast<int>(weights->slabs) * kSlabBlocks;
-  const int ncols = digit_columns(1);
-  const long long groups = static_cast<long long>(ncols / kDigitStride) * nbpad;
-  quantize_x_kernel<<<static_cast<unsigned>((groups + 31) / 32), 256, 0, s>>>(
-      x_dev, ximg, 1, static_cast<int>(weights->columns), nb, nbpad, ncols, groups);
-  count_launch();
-  QX_CUDA_TRY(cudaGetLastError());
+  QX_TRY(launch_quantizer(weights, x_dev, ximg, 1, false, s));
   return launch_gemv_tc_at(weights, ximg, y_dev, 1, weights->rows, base, scratch,
                            reinterpret_cast<int*>(base + error_offset), s);
 }

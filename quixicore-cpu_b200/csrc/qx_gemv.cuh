@@ -1,18 +1,25 @@
 // Shared definitions of the decode GEMV / small-batch qgemm kernels: the prepared-weight
-// panel geometry, the activation digit tables and the dp4a helpers.
+// panel geometry, the activation digit images and the dp4a helpers.
 //
 // Arithmetic. The reference computes, per weight row and per 32-element block b,
 //   sum_b = sum_j float(q_j) * x_j   (f32),       y += d_b * sum_b
 // (kernels/quantization/qgemv_ref.cpp:62-82, qgemv_w8a8_ref.cpp:95-118). Here each block
 // of activations is first written as a 23-bit signed fixed-point number under a
 // power-of-two block envelope, x_j ~= scale_b * t_j with |t_j| <= 2^22, and t_j is split
-// into three balanced base-256 digits, t = 65536*p2 + 256*p1 + p0, each in [-128, 127].
-// The 32-term dot product then becomes three exact 8-bit integer dot products -- done by
-// the tensor core (tcgen05 kind::i8) or by dp4a -- combined once per block in f32:
-//   sum_b = scale_b * (65536*S2 + 256*S1 + S0).
+// into balanced base-256 digits, t = 65536*p2 + 256*p1 + p0, each in [-128, 127].
+// The 32-term dot product then becomes exact 8-bit integer dot products -- done by the
+// tensor core (tcgen05 kind::i8) or by dp4a -- combined once per block in f32:
+//   sum_b = scale_b * (2^24*S3 + 65536*S2 + 256*S1 + S0).
 // The only rounding on the activation side is the fixed-point step, at most 2^-23 of the
 // block envelope per element, the order of one f32 rounding in the reference's own
 // 32-term sum; the integer sums are exact.
+//
+// q4_0 without unpacking the low nibbles. Byte i of a block holds element i (low nibble,
+// lo_i) and element i + 16 (high nibble, hi_i). With w_i = lo_i + 16*hi_i the raw byte,
+//   sum_i lo_i*t_i + hi_i*t_{i+16} = sum_i w_i*t_i + sum_i hi_i*(t_{i+16} - 16*t_i),
+// so the raw bytes are one 8-bit operand (against the digits of t_i, i < 16) and only the
+// high nibbles have to be extracted (against the four digits of z_i = t_{i+16} - 16*t_i,
+// |z_i| < 2^27). The "-8" of the format is the per-block constant 8 * sum_j t_j.
 #pragma once
 
 #include "qx_common.cuh"
@@ -20,36 +27,80 @@
 namespace qx {
 
 constexpr int kTileRows = 128;   // weight rows per panel tile (= MMA M = TMEM lanes)
-constexpr int kSlabBlocks = 4;   // 32-element blocks per K-slab (128 elements)
+constexpr int kSlabBlocks = 8;   // 32-element blocks per K-slab (256 elements)
 constexpr int kSlabK = kSlabBlocks * kBlockK;
+constexpr int kSlabScaleBytes = kTileRows * kSlabBlocks * 2;  // [row][block] fp16 bits
 
-// Per (activation row m, block b) constants, 16 bytes.
+// ---- prepared-weight panel: one contiguous span per (tile of 128 rows, K-slab) ---------
+//   q8_0: two code sub-tiles (blocks 0-3, blocks 4-7) of [128 rows][128 bytes], then scales
+//   q4_0: one code sub-tile [128 rows][8 blocks x 16 packed bytes], then scales
+// Inside a sub-tile the 16-byte chunk c of row r is stored at chunk c ^ (r & 7): the
+// 128-byte swizzle the tensor-core operand descriptors expect, already applied in HBM so
+// that a stage is filled by one plain bulk copy.
+__host__ __device__ constexpr int slab_code_bytes(int format) {
+  return format == QX_FORMAT_Q8_0 ? kTileRows * kSlabBlocks * 32 : kTileRows * kSlabBlocks * 16;
+}
+__host__ __device__ constexpr int slab_span_bytes(int format) {
+  return slab_code_bytes(format) + kSlabScaleBytes;
+}
+// byte offset inside a span of the 16 code bytes `half` (0: elements 0-15, 1: 16-31) of
+// block j of row r (q8_0), or of the 16 packed bytes of block j (q4_0)
+__host__ __device__ inline int panel_code_offset_q8(int r, int j, int half) {
+  return (j >> 2) * (kTileRows * 128) + r * 128 + (((2 * (j & 3) + half) ^ (r & 7)) << 4);
+}
+__host__ __device__ inline int panel_code_offset_q4(int r, int j) {
+  return r * 128 + ((j ^ (r & 7)) << 4);
+}
+__host__ __device__ inline int panel_scale_offset(int format, int r, int j) {
+  return slab_code_bytes(format) + (r * kSlabBlocks + j) * 2;
+}
+
+// ---- activation side -------------------------------------------------------------------
+// A launch handles mp = 1, 2, 4, 8, 16 or 32 activation rows (m rounded up). The digit
+// matrix of a slab has four columns per (block class, activation row): columns
+//   n = ((j mod G) * mp + row) * 4 + digit,       G = group_blocks(format, mp),
+// and column n is non-zero only in the K range of the blocks j with that class. One MMA
+// accumulator of N = 4*mp*G columns therefore holds the digit sums of G consecutive
+// blocks side by side (block-diagonal B operand): for mp = 1 a single accumulator of 32
+// columns carries a whole slab.
+__host__ __device__ constexpr int padded_batch(int m) {
+  return m <= 1 ? 1 : (m <= 2 ? 2 : (m <= 4 ? 4 : (m <= 8 ? 8 : (m <= 16 ? 16 : 32))));
+}
+__host__ __device__ constexpr int group_blocks(int format, int mp) {
+  const int g = kSlabBlocks / mp < 1 ? 1 : kSlabBlocks / mp;
+  // a q4_0 MMA step spans 32 packed bytes = two blocks
+  return format == QX_FORMAT_Q4_0 && g < 2 ? 2 : g;
+}
+__host__ __device__ constexpr int digit_columns(int format, int mp) {
+  return 4 * mp * group_blocks(format, mp);
+}
+__host__ __device__ inline int digit_row(int format, int mp, int j, int row, int digit) {
+  return ((j % group_blocks(format, mp)) * mp + row) * 4 + digit;
+}
+
+// Per (block j, activation row) constants, 16 bytes.
 struct __align__(16) XConst {
-  float scale;  // 2^(e-22): x_j ~= scale * t_j
-  int k01;      // 8 * (256*P1 + P0), P_d = sum_j digit_d(t_j): the q4_0 "-8" offset
-  int p2x8;     // 8 * P2
+  float scale;  // 2^(e-22): x_j ~= scale * t_j (NaN when the block holds a non-finite value)
+  int k_lo;     // q4_0: 8 * sum_j t_j = 65536 * k_hi + k_lo, 0 <= k_lo < 65536
+  int k_hi;
   int pad;
 };
 
-// Columns of the digit matrix used by a batch of m activation rows: four per row (three
-// digits and one zero column, so a row's digits never straddle a 16-column group),
-// rounded up to the sizes the tensor-core kernel is built for.
-constexpr int kDigitStride = 4;
-__host__ __device__ inline int digit_columns(int m) {
-  const int c = kDigitStride * m;
-  return c <= 8 ? 8 : (c <= 16 ? 16 : (c <= 32 ? 32 : (c <= 64 ? 64 : 128)));
+// Activation side of one K-slab ("image"), in the form the tensor-core kernel wants in
+// shared memory, so one bulk copy brings it in:
+//   q8_0: [sub-tile 0 | sub-tile 1], each [N digit rows][128 bytes] (blocks 0-3 | 4-7)
+//   q4_0: [digits of t_i, i < 16 | digits of z_i], each [N rows][8 blocks x 16 bytes]
+//   then XConst[8 blocks][mp]
+// with 16-byte chunks swizzled by the row index like the weight sub-tiles.
+__host__ __device__ constexpr int ximage_bytes(int format, int mp) {
+  return digit_columns(format, mp) * 256 + 128 * mp;
 }
-
-// Activation side of one K-slab as the tensor-core kernel wants it in shared memory, kept
-// in that form in scratch memory so that one bulk copy brings it in:
-//   [ digit rows: ncols rows x 128 bytes, 16-byte chunks swizzled like a 128B-swizzle TMA
-//     tile (chunk c of row r stored at c ^ (r & 7)) | XConst[ncols / 4][4 blocks] ]
-__host__ __device__ inline int ximage_bytes(int ncols) { return ncols * 128 + ncols * 16; }
-// byte offset, inside a slab image, of the 4 digit bytes of elements 4q..4q+3 of block j
-// (0..3) in digit row `col`
-__host__ __device__ inline int ximage_digit_offset(int col, int j, int q) {
-  const int chunk = 2 * j + (q >> 2);
-  return (col >> 3) * 1024 + (col & 7) * 128 + ((chunk ^ (col & 7)) << 4) + (q & 3) * 4;
+// offset of the 16 digit bytes of (digit row n, chunk cc) in half-image `which`
+__host__ __device__ inline int ximage_chunk_offset(int ncols, int which, int n, int cc) {
+  return which * ncols * 128 + n * 128 + ((cc ^ (n & 7)) << 4);
+}
+__host__ __device__ inline int ximage_const_offset(int ncols, int mp, int j, int row) {
+  return ncols * 256 + (j * mp + row) * 16;
 }
 
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
@@ -63,9 +114,13 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
   return d;
 }
 
-// 65536*v + u rounded once to f32 (|u| < 2^31).
+// 65536*v + u rounded to f32 (|u|, |v| < 2^29).
 __device__ __forceinline__ float combine_digits(int u, int v) {
   return fmaf((float)v, 65536.0f, (float)u);
+}
+// One block's term from its four digit sums: f32(2^24*s3 + 65536*s2 + 256*s1 + s0 - k).
+__device__ __forceinline__ float block_sum(int s0, int s1, int s2, int s3, int k_lo, int k_hi) {
+  return combine_digits(s1 * 256 + s0 - k_lo, s3 * 256 + s2 - k_hi);
 }
 
 // fp16 bits -> f32, identical to kernels/common/fp16.h:11-37 for every finite or

@@ -15,6 +15,10 @@ namespace sm100 {
 // A wait gives up after this much wall time on the GPU's nanosecond timer (a poll of a
 // barrier that is not ready may itself sleep for a while, so counting polls is no bound).
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+// Upper bound the hardware may keep a waiting thread suspended inside one try_wait (it
+// wakes at once when the barrier phase completes): waiting warps then take no issue
+// slots from the warps that have work.
+constexpr uint32_t kSuspendHintNs = 1000000u;
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
@@ -55,10 +59,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return done != 0;
 }
@@ -184,16 +188,23 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
     return qx_ok_;                             \
   }()
 #define QX_PROF_STORE(slot, value) \
-  if (p.debug != nullptr) p.debug[blockIdx.x * 16 + (slot)] = (value)
+  if (p.debug != nullptr) p.debug[blockIdx.x * 32 + (slot)] = (value)
 #define QX_PROF_NOW() clock64()
+#define QX_PROF_BEGIN() const long long qx_tb_ = clock64()
+#define QX_PROF_END(counter) counter += clock64() - qx_tb_
+#define QX_PROF_STAMP(slot) \
+  if (p.debug != nullptr) p.debug[blockIdx.x * 32 + (slot)] = static_cast<long long>(sm100::global_timer_ns())
 #else
 #define QX_PROF_DECL(name)
 #define QX_PROF_WAIT(counter, expr) (expr)
 #define QX_PROF_STORE(slot, value)
 #define QX_PROF_NOW() 0
+#define QX_PROF_BEGIN()
+#define QX_PROF_END(counter)
+#define QX_PROF_STAMP(slot)
 #endif
 
-// Device buffer [1024 CTAs][16] the profiling build writes its counters to (null otherwise).
+// Device buffer [1024 CTAs][32] the profiling build writes its counters to (null otherwise).
 long long* gemv_profile_buffer();
 
 // Host side: cuTensorMapEncodeTiled through the runtime's driver entry point lookup (the

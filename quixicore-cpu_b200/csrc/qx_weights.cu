@@ -38,13 +38,14 @@ __global__ void __launch_bounds__(256) relayout_kernel(const unsigned short* __r
       w[i] = static_cast<uint32_t>(in[1 + 2 * i]) | (static_cast<uint32_t>(in[2 + 2 * i]) << 16);
     }
   }
-  constexpr size_t kCodeBytes = FMT == QX_FORMAT_Q8_0 ? 32 : 16;
-  constexpr size_t kSlabCodes = kTileRows * kSlabBlocks * kCodeBytes;
-  uint8_t* span = panel + ts * (kSlabCodes + kTileRows * kSlabBlocks * 2);
-  reinterpret_cast<unsigned short*>(span + kSlabCodes)[j * kTileRows + r] = scale;
-  uint4* codes = reinterpret_cast<uint4*>(span + (r * kSlabBlocks + j) * kCodeBytes);
-  codes[0] = make_uint4(w[0], w[1], w[2], w[3]);
-  if (FMT == QX_FORMAT_Q8_0) codes[1] = make_uint4(w[4], w[5], w[6], w[7]);
+  uint8_t* span = panel + ts * slab_span_bytes(FMT);
+  *reinterpret_cast<unsigned short*>(span + panel_scale_offset(FMT, r, j)) = scale;
+  if constexpr (FMT == QX_FORMAT_Q8_0) {
+    *reinterpret_cast<uint4*>(span + panel_code_offset_q8(r, j, 0)) = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4*>(span + panel_code_offset_q8(r, j, 1)) = make_uint4(w[4], w[5], w[6], w[7]);
+  } else {
+    *reinterpret_cast<uint4*>(span + panel_code_offset_q4(r, j)) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
 }
 
 }  // namespace

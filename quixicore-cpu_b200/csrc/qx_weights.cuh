@@ -4,14 +4,15 @@
 // HBM layout ("row-tile panels"). The canonical GGUF bytes interleave a 2-byte fp16 scale
 // with 32 (q8_0) or 16 (q4_0) code bytes, so no block starts on a 16-byte boundary. At
 // prepare time one pass re-lays the rows kept on this device out as tiles of 128 rows by
-// K-slabs of 4 blocks (128 elements), the unit one CTA pipeline stage consumes:
-//   panel [tile][slab]{ codes  [row 0..127][4 blocks x (32 | 16) code bytes]  16 KiB | 8 KiB
-//                       scales [block 0..3][row 0..127] fp16 bits             1 KiB }
-// Each (tile, slab) is one contiguous span of 17 KiB (q8_0) or 9 KiB (q4_0), so a stage
-// is ONE fully coalesced bulk / TMA-tiled read; rows of a q8_0 code slab are 128 bytes,
-// exactly the 128-byte swizzle atom of the tensor-core operand. Same byte count as the canonical layout (34 / 18
-// bytes per block) whenever rows % 128 == 0 and columns % 128 == 0 -- every benchmark
-// shape -- otherwise the last tile / slab is zero padded (a zero scale contributes 0).
+// K-slabs of 8 blocks (256 elements), the unit one CTA pipeline stage consumes:
+//   panel [tile][slab]{ codes  [row 0..127][8 blocks x (32 | 16) code bytes]  32 KiB | 16 KiB
+//                       scales [row 0..127][block 0..7] fp16 bits             2 KiB }
+// Each (tile, slab) is one contiguous span of 34 KiB (q8_0) or 18 KiB (q4_0), so a stage
+// is ONE fully coalesced bulk read; code rows are 128 bytes with their 16-byte chunks
+// already permuted into the 128-byte swizzle of the tensor-core operand (qx_gemv.cuh).
+// Same byte count as the canonical layout (34 / 18 bytes per block) whenever
+// rows % 128 == 0 and columns % 256 == 0 -- every benchmark shape -- otherwise the last
+// tile / slab is zero padded (a zero scale contributes 0).
 // This is the device counterpart of the reference's [row_panel, k_block, row_lane,
 // block_bytes] CPU panel (src/memory/packed_weights.cpp:253-266).
 #pragma once
@@ -28,7 +29,7 @@ struct qx_weights {
   long long columns = 0;
   long long blocks_per_row = 0;
   long long tiles = 0;       // ceil(rows / 128)
-  long long slabs = 0;       // ceil(blocks_per_row / 4)
+  long long slabs = 0;       // ceil(blocks_per_row / 8)
   size_t block_bytes = 0;
   size_t contract_bytes = 0;
   size_t prepared_bytes = 0;
@@ -40,11 +41,8 @@ struct qx_weights {
   size_t dense_cache_bytes = 0;
 
   size_t code_bytes_per_block() const { return block_bytes - 2; }
-  // bytes of the codes / of the whole span of one (tile, slab)
-  size_t slab_code_bytes() const {
-    return static_cast<size_t>(qx::kTileRows) * qx::kSlabBlocks * code_bytes_per_block();
-  }
-  size_t slab_bytes() const { return slab_code_bytes() + qx::kTileRows * qx::kSlabBlocks * 2; }
+  // bytes of the whole span of one (tile, slab)
+  size_t slab_bytes() const { return static_cast<size_t>(qx::slab_span_bytes(format)); }
   size_t panel_bytes() const { return static_cast<size_t>(tiles) * slabs * slab_bytes(); }
 };
 
