@@ -276,10 +276,13 @@ qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev
     QX_TRY(ws->reserve(scratch.total_bytes));
     uint8_t* base = static_cast<uint8_t*>(ws->base);
     uint8_t* ximg = base + scratch.ximg_offset;
-    QX_TRY(launch_quantizer(w, x_dev + m0 * w->columns, ximg, mc, true, stream));
+    const float* x = x_dev + m0 * w->columns;
+    if (force_dp4a() || !gemv_tc_quantizes_in_kernel(mc)) {
+      QX_TRY(launch_quantizer(w, x, ximg, mc, true, stream));
+    }
     float* y = y_dev + m0 * ldy;
     if (!force_dp4a()) {
-      QX_TRY(launch_gemv_tc(w, ximg, y, mc, ldy, base, scratch, stream));
+      QX_TRY(launch_gemv_tc(w, x, ximg, y, mc, ldy, base, scratch, stream));
     } else {
       const dim3 grid(static_cast<unsigned>((w->rows + 7) / 8), static_cast<unsigned>(mc));
       const int mp = padded_batch(mc), nb = static_cast<int>(w->blocks_per_row);
@@ -387,7 +390,6 @@ extern "C" qx_status qx_qgemv_prepacked_noalloc_dev(const qx_weights* weights, c
   QX_CUDA_TRY(cudaMemsetAsync(base + error_offset, 0, 256, s));
 
   uint8_t* ximg = base + scratch.ximg_offset;
-  QX_TRY(launch_quantizer(weights, x_dev, ximg, 1, false, s));
-  return launch_gemv_tc_at(weights, ximg, y_dev, 1, weights->rows, base, scratch,
+  return launch_gemv_tc_at(weights, x_dev, ximg, y_dev, 1, weights->rows, base, scratch,
                            reinterpret_cast<int*>(base + error_offset), s);
 }

@@ -9,9 +9,12 @@
 // rows land in TMEM. The CUDA cores only combine the digits and apply the fp16 block
 // scale: ~10 instructions per block and row.
 //
-// One K-slab (8 blocks = 256 elements of 128 rows) per pipeline stage, filled by two bulk
-// copies: the slab's span of the prepared panel (codes already in the operand's swizzled
-// layout, then the fp16 scales) and the slab's activation image. The B operand is block
+// One K-slab (8 blocks = 256 elements of 128 rows) per pipeline step. Its span of the
+// prepared panel (codes already in the operand's swizzled layout, then the fp16 scales)
+// arrives by one bulk copy into a deep ring of weight slots; its activation image is
+// either built in place by a quantizer warp (one or two activation rows: no second
+// kernel, nothing between this kernel and the weights) or copied from the images the
+// quantizer kernel wrote. The B operand is block
 // diagonal: its N = 32..256 columns are (block class, activation row, digit), so one
 // accumulator holds the sums of several blocks side by side and, for one or two
 // activation rows, a single TMEM load brings a whole slab to the epilogue thread.
@@ -21,7 +24,8 @@
 //         second tile (4 more MMAs against the digits of t[i+16] - 16*t[i])
 // Warp roles: 0 = copy producer (one thread), 1 = MMA issuer (one thread), 2-9 = epilogue
 // (thread = weight row, accumulators in registers; two sets of four warps take alternate
-// K units), 10-13 = q4_0 high-nibble extraction (one slab per warp, round robin).
+// K units), then for q4_0 four warps for the high nibbles (one slab per warp, round robin)
+// and, for decode batches, the activation quantizer warp.
 //
 // Work split and summation order. K is cut into units of `unit_slabs` slabs, a function of
 // K alone. A row's result is defined as (sum of its even units) + (sum of its odd units),
@@ -47,43 +51,62 @@ constexpr int kEpilogueWarps = 8;   // two sets of four (one warp per TMEM lane 
 constexpr int kFirstUnpackWarp = 2 + kEpilogueWarps;
 constexpr int kSmemLimit = 227 * 1024;
 
+// weight slots (at most 8) that fit beside `work_slots` work slots
+constexpr int weight_slots_fit(int budget, int work_bytes, int weight_bytes, int work_slots) {
+  return (budget - work_slots * work_bytes) / weight_bytes > 8
+             ? 8
+             : (budget - work_slots * work_bytes) / weight_bytes;
+}
+
 template <int FMT, int MP>
 struct TcGeom {
   static constexpr bool kQ4 = FMT == QX_FORMAT_Q4_0;
+  // Decode batches (one or two activation rows) quantize the activations inside the kernel
+  // (one more warp); larger batches read images written by the quantizer kernel.
+  static constexpr bool kFused = MP <= 2;
   static constexpr int kG = group_blocks(FMT, MP);     // blocks per accumulator
   static constexpr int kN = digit_columns(FMT, MP);    // MMA N = accumulator columns
   static constexpr int kGroups = kSlabBlocks / kG;     // accumulators per slab
-  static constexpr int kWBytes = slab_span_bytes(FMT);   // copied per slab: codes + scales
+  // Two rings in shared memory. Weight slots hold a slab's span of the panel as copied
+  // (the bytes in flight: as many slots as fit). Work slots hold what exists only around
+  // the MMAs of a slab: the q4_0 high-nibble tile and the activation image.
+  static constexpr int kWBytes = slab_span_bytes(FMT);   // 34 KiB | 18 KiB
   static constexpr int kScaleOffset = slab_code_bytes(FMT);
-  static constexpr int kHOffset = 18 * 1024;           // q4_0: high-nibble tile (16 KiB)
-  static constexpr int kABytes = 34 * 1024;            // weight part of a stage
+  static constexpr int kHBytes = kQ4 ? kTileRows * 128 : 0;
   static constexpr int kBBytes = kN * 256;
   static constexpr int kXBytes = ximage_bytes(FMT, MP);  // digit rows + constants
-  static constexpr int kStageBytes = (kABytes + kXBytes + 1023) / 1024 * 1024;
-  static constexpr int kStagesFit = (kSmemLimit - 1024 - 2048) / kStageBytes;
-  static constexpr int kStages = kStagesFit > 8 ? 8 : kStagesFit;
+  static constexpr int kWorkBytes = (kHBytes + kXBytes + 1023) / 1024 * 1024;
+  static constexpr int kBudget = kSmemLimit - 1024 - 2048;  // alignment slack, barriers
+  static constexpr int kWorkSlots =
+      weight_slots_fit(kBudget, kWorkBytes, kWBytes, 3) == weight_slots_fit(kBudget, kWorkBytes, kWBytes, 2)
+          ? 3
+          : 2;
+  static constexpr int kSlots = weight_slots_fit(kBudget, kWorkBytes, kWBytes, kWorkSlots);
   static constexpr int kTCols = kN;                    // TMEM columns per accumulator
   static constexpr int kTStages = 512 / kTCols > 16 ? 16 : 512 / kTCols;
   // Each epilogue set has its own ring of accumulators, so every TMEM barrier is used by
   // one set only (a parity wait cannot tell apart phases two steps apart).
   static constexpr int kTPerSet = kTStages / 2;
   static constexpr int kUnpackWarps = kQ4 ? 4 : 0;
-  static constexpr int kThreads = 32 * (2 + kEpilogueWarps + kUnpackWarps);
+  static constexpr int kQuantWarp = 2 + kEpilogueWarps + kUnpackWarps;  // fused only
+  static constexpr int kThreads = 32 * (2 + kEpilogueWarps + kUnpackWarps + (kFused ? 1 : 0));
   static constexpr int kLdCols = kN >= 64 ? 64 : 32;   // columns fetched per TMEM wait
-  static_assert(kStages >= 2 && kTPerSet >= 1 && kN >= 32 && kN <= 256, "geometry");
-  static_assert(kScaleOffset + kSlabScaleBytes == kWBytes && kWBytes <= kABytes, "span");
-  static_assert(!kQ4 || kWBytes == kHOffset, "q4_0 stage layout");
+  static_assert(kSlots >= 2 && kSlots >= kWorkSlots && kTPerSet >= 1 && kN >= 32 && kN <= 256,
+                "geometry");
+  static_assert(kScaleOffset + kSlabScaleBytes == kWBytes && kWBytes % 1024 == 0, "span");
 };
 
 struct GemvTcParams {
   const uint8_t* panel;          // [tile][slab] spans
-  const uint8_t* ximg;           // [slab] activation images
+  const uint8_t* ximg;           // [slab] activation images (batches above two rows)
+  const float* x;                // [m][ldx] activations (decode batches)
   float* y;
   float* partial;                // [tile][unit][m][128] unit sums
   int* counters;                 // [tile][128], one per weight row
   int* error;
-  long long ldy, rows;
-  int m, slabs, tiles;
+  long long ldy, ldx, rows;
+  int m, slabs, tiles, nb;
+  int x_vector;                  // x and ldx allow 16-byte loads
   int unit_slabs, units_per_tile;  // K split: units of unit_slabs slabs
   long long total_units;
   long long* debug;  // [ctas][32] counters, profiling builds only
@@ -91,9 +114,10 @@ struct GemvTcParams {
 
 template <int FMT, int MP>
 struct __align__(8) GemvBarriers {
-  uint64_t full[TcGeom<FMT, MP>::kStages];       // both bulk copies of the stage landed
-  uint64_t empty[TcGeom<FMT, MP>::kStages];      // MMAs done + scales / constants consumed
-  uint64_t high_full[TcGeom<FMT, MP>::kStages];  // q4_0: high-nibble tile written
+  uint64_t raw_full[TcGeom<FMT, MP>::kSlots];    // the slab's span landed in its weight slot
+  uint64_t done[TcGeom<FMT, MP>::kSlots];        // MMAs done + scales / constants consumed
+  uint64_t x_full[TcGeom<FMT, MP>::kWorkSlots];  // activation image in the work slot
+  uint64_t high_full[TcGeom<FMT, MP>::kWorkSlots];  // q4_0: high-nibble tile written
   uint64_t tmem_full[TcGeom<FMT, MP>::kTStages];
   uint64_t tmem_empty[TcGeom<FMT, MP>::kTStages];
   uint32_t tmem_base;
@@ -117,6 +141,111 @@ __device__ __forceinline__ long long range_start(long long c, long long total, l
   return c * total / ctas;
 }
 
+// Ring position i mod `slots` with the parity of i / slots.
+struct RingPos {
+  uint32_t slot = 0, phase = 0;
+  __device__ __forceinline__ void advance(uint32_t slots) {
+    if (++slot == slots) {
+      slot = 0;
+      phase ^= 1u;
+    }
+  }
+};
+
+// Four values -> the bytes of balanced base-256 digit d (0..3) of each, packed in a word.
+__device__ __forceinline__ void pack_digits(const int (&t)[4], uint32_t (&word)[4]) {
+  word[0] = word[1] = word[2] = word[3] = 0u;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int p0 = ((t[i] + 128) & 255) - 128;
+    const int t1 = (t[i] - p0) >> 8;
+    const int p1 = ((t1 + 128) & 255) - 128;
+    const int t2 = (t1 - p1) >> 8;
+    const int p2 = ((t2 + 128) & 255) - 128;
+    const int p3 = (t2 - p2) >> 8;
+    word[0] |= static_cast<uint32_t>(p0 & 255) << (8 * i);
+    word[1] |= static_cast<uint32_t>(p1 & 255) << (8 * i);
+    word[2] |= static_cast<uint32_t>(p2 & 255) << (8 * i);
+    word[3] |= static_cast<uint32_t>(p3 & 255) << (8 * i);
+  }
+}
+
+// In-kernel activation quantizer (decode batches): writes slab `xslab`'s image into a work
+// slot whose digit area is zero outside the block-diagonal positions. Lane (b = lane / 4,
+// q = lane % 4) handles elements 4q..4q+3 and 16+4q..16+4q+3 of block b of every row:
+// `lo` / `hi` are those values (zeros past the end of the row).
+template <int FMT, int MP>
+__device__ __forceinline__ void write_slab_image(uint8_t* digits, const float4 (&lo)[MP],
+                                                 const float4 (&hi)[MP], bool block_valid,
+                                                 int lane) {
+  using G = TcGeom<FMT, MP>;
+  const int b = lane >> 2, q = lane & 3;
+  XConst* consts = reinterpret_cast<XConst*>(digits + G::kBBytes);
+#pragma unroll
+  for (int m = 0; m < MP; ++m) {
+    const float v[8] = {lo[m].x, lo[m].y, lo[m].z, lo[m].w, hi[m].x, hi[m].y, hi[m].z, hi[m].w};
+    // max of |bits|: orders finite < inf < NaN, so non-finite inputs are detected
+    uint32_t amax_bits = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax_bits = max(amax_bits, __float_as_uint(v[i]) & 0x7FFFFFFFu);
+    amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 1));
+    amax_bits = max(amax_bits, __shfl_xor_sync(0xffffffffu, amax_bits, 2));
+    const uint32_t eb_raw = amax_bits >> 23;
+    const bool finite = eb_raw != 255u;
+    const uint32_t eb = max(eb_raw, 30u);                       // envelope 2^(eb-126) > amax
+    const float scale_up = __uint_as_float((275u - eb) << 23);  // 2^(22 - e)
+    float scale = finite ? __uint_as_float((eb - 21u) << 23)    // 2^(e - 22)
+                         : __uint_as_float(0x7FC00000u);        // NaN/inf in -> NaN out
+    if (!block_valid) scale = 0.0f;
+    int t_lo[4], t_hi[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      t_lo[i] = finite ? __float2int_rn(v[i] * scale_up) : 0;  // |t| <= 2^22
+      t_hi[i] = finite ? __float2int_rn(v[4 + i] * scale_up) : 0;
+    }
+    const int n = ((b % G::kG) * MP + m) * 4;  // digit row of digit 0
+    uint32_t w_lo[4], w_hi[4];
+    pack_digits(t_lo, w_lo);
+    if (FMT == QX_FORMAT_Q8_0) {
+      pack_digits(t_hi, w_hi);
+      uint8_t* tile = digits + (b >> 2) * (G::kN * 128);
+#pragma unroll
+      for (int d = 0; d < 3; ++d) {
+        const int row = n + d;
+        *reinterpret_cast<uint32_t*>(tile + row * 128 + (((2 * (b & 3)) ^ (row & 7)) << 4) + 4 * q) = w_lo[d];
+        *reinterpret_cast<uint32_t*>(tile + row * 128 + (((2 * (b & 3) + 1) ^ (row & 7)) << 4) + 4 * q) = w_hi[d];
+      }
+    } else {
+      int z[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) z[i] = t_hi[i] - 16 * t_lo[i];
+      pack_digits(z, w_hi);
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const int row = n + d;
+        const int offset = row * 128 + ((b ^ (row & 7)) << 4) + 4 * q;
+        if (d < 3) *reinterpret_cast<uint32_t*>(digits + offset) = w_lo[d];
+        *reinterpret_cast<uint32_t*>(digits + G::kN * 128 + offset) = w_hi[d];
+      }
+    }
+    int sum = 0;
+    if (FMT == QX_FORMAT_Q4_0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sum += t_lo[i] + t_hi[i];
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    }
+    if (q == 0) {
+      XConst c;
+      c.scale = scale;
+      c.k_lo = (8 * sum) & 0xFFFF;
+      c.k_hi = (8 * sum) >> 16;
+      c.pad = 0;
+      consts[b * MP + m] = c;
+    }
+  }
+}
+
 template <int FMT, int MP>
 __global__ void __launch_bounds__((TcGeom<FMT, MP>::kThreads), 1)
 gemv_tc_kernel(const GemvTcParams p) {
@@ -125,7 +254,8 @@ gemv_tc_kernel(const GemvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  auto* bars = reinterpret_cast<GemvBarriers<FMT, MP>*>(smem + G::kStages * G::kStageBytes);
+  uint8_t* work_ring = smem + G::kSlots * G::kWBytes;  // slot: [high nibbles (q4_0) | image]
+  auto* bars = reinterpret_cast<GemvBarriers<FMT, MP>*>(work_ring + G::kWorkSlots * G::kWorkBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = &bars->abort_flag;
@@ -135,9 +265,12 @@ gemv_tc_kernel(const GemvTcParams p) {
   if (threadIdx.x == 0) QX_PROF_STAMP(10);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < G::kStages; ++s) {
-      mbar_init(&bars->full[s], 1);       // the producer's expect_tx arrival
-      mbar_init(&bars->empty[s], 1 + 4);  // MMA commit + four epilogue warps (scales read)
+    for (int s = 0; s < G::kSlots; ++s) {
+      mbar_init(&bars->raw_full[s], 1);  // the producer's expect_tx arrival
+      mbar_init(&bars->done[s], 1 + 4);  // MMA commit + four epilogue warps
+    }
+    for (int s = 0; s < G::kWorkSlots; ++s) {
+      mbar_init(&bars->x_full[s], 1);  // expect_tx arrival, or the quantizer warp
       mbar_init(&bars->high_full[s], 1);
     }
     for (int t = 0; t < G::kTStages; ++t) {
@@ -150,6 +283,14 @@ gemv_tc_kernel(const GemvTcParams p) {
   if (warp == 1) {
     tmem_alloc(&bars->tmem_base, 512);
     tmem_relinquish();
+  }
+  if (G::kFused) {
+    // the quantizer warp only ever writes the block-diagonal positions of the digit areas
+    for (int s = 0; s < G::kWorkSlots; ++s) {
+      uint4* area = reinterpret_cast<uint4*>(work_ring + s * G::kWorkBytes + G::kHBytes);
+      for (int i = threadIdx.x; i < G::kBBytes / 16; i += G::kThreads) area[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -172,44 +313,56 @@ gemv_tc_kernel(const GemvTcParams p) {
 
   if (warp == 0) {
     // ------------------------------ copy producer -----------------------------
+    // Slab i uses weight slot i mod kSlots and work slot i mod kWorkSlots; both are free
+    // again when slab i is done. The weights run kSlots slabs ahead, the images
+    // kWorkSlots: after slab i - kWorkSlots is done, the image of slab i and the weights
+    // of slab i + kSlots - kWorkSlots go into the slots it used.
     if (lane == 0) {
       bool ok = true;
       QX_PROF_DECL(w_empty);
       const uint8_t* wsrc = p.panel + s_begin * G::kWBytes;
       int xslab = static_cast<int>(s_begin % p.slabs);
       // The weights do not depend on the kernel in front of this one: start the first
-      // stages' weight copies at once, and only then wait for the activation images.
-      const int prologue = count < G::kStages ? count : G::kStages;
-      for (int i = 0; i < prologue; ++i) {
-        mbar_arrive_expect_tx(&bars->full[i], G::kWBytes + G::kXBytes);
-        bulk_copy_g2s(smem + i * G::kStageBytes, wsrc, G::kWBytes, &bars->full[i]);
+      // copies at once, and only then wait for the activation images.
+      const int ahead = count < G::kSlots ? count : G::kSlots;
+      for (int i = 0; i < ahead; ++i) {
+        mbar_arrive_expect_tx(&bars->raw_full[i], G::kWBytes);
+        bulk_copy_g2s(smem + i * G::kWBytes, wsrc, G::kWBytes, &bars->raw_full[i]);
         wsrc += G::kWBytes;
       }
-      asm volatile("griddepcontrol.wait;" ::: "memory");
-      QX_PROF_STAMP(12);
-      for (int i = 0; i < prologue; ++i) {
-        bulk_copy_g2s(smem + i * G::kStageBytes + G::kABytes,
-                      p.ximg + static_cast<long long>(xslab) * G::kXBytes, G::kXBytes,
-                      &bars->full[i]);
-        xslab = xslab + 1 == p.slabs ? 0 : xslab + 1;
+      if (!G::kFused) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        QX_PROF_STAMP(12);
+        for (int i = 0; i < G::kWorkSlots && i < count; ++i) {
+          mbar_arrive_expect_tx(&bars->x_full[i], G::kXBytes);
+          bulk_copy_g2s(work_ring + i * G::kWorkBytes + G::kHBytes,
+                        p.ximg + static_cast<long long>(xslab) * G::kXBytes, G::kXBytes,
+                        &bars->x_full[i]);
+          xslab = xslab + 1 == p.slabs ? 0 : xslab + 1;
+        }
       }
-      uint32_t stage = 0, phase = 1;
-      for (int i = prologue; i < count; ++i) {
-        if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag))) {
+      RingPos freed;           // slab i - kWorkSlots in the weight ring
+      uint32_t work_slot = 0;  // i mod kWorkSlots
+      for (int i = G::kWorkSlots; i < count; ++i) {
+        if (G::kFused && i + G::kSlots - G::kWorkSlots >= count) break;  // no more weights
+        if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag))) {
           ok = false;
           break;
         }
-        uint8_t* st = smem + stage * G::kStageBytes;
-        mbar_arrive_expect_tx(&bars->full[stage], G::kWBytes + G::kXBytes);
-        bulk_copy_g2s(st, wsrc, G::kWBytes, &bars->full[stage]);
-        bulk_copy_g2s(st + G::kABytes, p.ximg + static_cast<long long>(xslab) * G::kXBytes,
-                      G::kXBytes, &bars->full[stage]);
-        wsrc += G::kWBytes;
-        xslab = xslab + 1 == p.slabs ? 0 : xslab + 1;
-        if (++stage == G::kStages) {
-          stage = 0;
-          phase ^= 1u;
+        if (!G::kFused) {
+          mbar_arrive_expect_tx(&bars->x_full[work_slot], G::kXBytes);
+          bulk_copy_g2s(work_ring + work_slot * G::kWorkBytes + G::kHBytes,
+                        p.ximg + static_cast<long long>(xslab) * G::kXBytes, G::kXBytes,
+                        &bars->x_full[work_slot]);
+          xslab = xslab + 1 == p.slabs ? 0 : xslab + 1;
         }
+        if (i + G::kSlots - G::kWorkSlots < count) {
+          mbar_arrive_expect_tx(&bars->raw_full[freed.slot], G::kWBytes);
+          bulk_copy_g2s(smem + freed.slot * G::kWBytes, wsrc, G::kWBytes, &bars->raw_full[freed.slot]);
+          wsrc += G::kWBytes;
+        }
+        freed.advance(G::kSlots);
+        if (++work_slot == G::kWorkSlots) work_slot = 0;
       }
       QX_PROF_STORE(0, w_empty);
       if (!ok) {
@@ -223,10 +376,10 @@ gemv_tc_kernel(const GemvTcParams p) {
       const uint32_t idesc = (2u << 4) | ((kQ4 ? 0u : 1u) << 7) | (1u << 10) |
                              (static_cast<uint32_t>(G::kN >> 3) << 17) |
                              (static_cast<uint32_t>(kTileRows >> 4) << 24);
-      uint32_t stage = 0, phase = 0;
+      RingPos raw, work;
       uint32_t pos0 = 0, pos1 = 0, par0 = 0, par1 = 0;  // accumulator ring of each epilogue set
       bool ok = true;
-      int gave_up = 12;  // which wait ran out: 12 stage, 16 accumulator, 17 high-nibble tile
+      int gave_up = 12;  // which wait ran out: 12 weights, 15 image, 16 accumulator, 17 high nibbles
       QX_PROF_DECL(w_full);
       QX_PROF_DECL(w_tempty);
       int slab = static_cast<int>(s_begin % p.slabs);
@@ -234,12 +387,19 @@ gemv_tc_kernel(const GemvTcParams p) {
       int slab_in_unit = slab - unit * p.unit_slabs;
       for (int i = 0; i < count && ok; ++i) {
         const uint32_t eset = static_cast<uint32_t>(unit & 1);
-        if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->full[stage], phase, abort_flag))) {
+        if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) {
           ok = false;
           break;
         }
+        if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag))) {
+          ok = false;
+          gave_up = 15;
+          break;
+        }
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(smem + stage * G::kStageBytes);
+        const uint32_t sa = smem_u32(smem + raw.slot * G::kWBytes);
+        const uint32_t sw = smem_u32(work_ring + work.slot * G::kWorkBytes);
+        const uint32_t sb = sw + G::kHBytes;  // digit rows
 #pragma unroll
         for (int g = 0; g < G::kGroups; ++g) {
           const uint32_t pos = eset != 0u ? pos1 : pos0;
@@ -258,8 +418,7 @@ gemv_tc_kernel(const GemvTcParams p) {
             for (int b = 0; b < G::kG; ++b) {
               const int j = g * G::kG + b;
               const uint64_t a_desc = make_sw128_kmajor_desc(sa + (j >> 2) * (kTileRows * 128));
-              const uint64_t b_desc =
-                  make_sw128_kmajor_desc(sa + G::kABytes + (j >> 2) * (G::kN * 128));
+              const uint64_t b_desc = make_sw128_kmajor_desc(sb + (j >> 2) * (G::kN * 128));
               mma_i8_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * (j & 3)),
                         b_desc + static_cast<uint64_t>(2 * (j & 3)), idesc, b > 0 ? 1u : 0u);
             }
@@ -268,22 +427,22 @@ gemv_tc_kernel(const GemvTcParams p) {
             // nibbles once their tile is written
             constexpr int kSteps = G::kG / 2;
             const uint64_t a_raw = make_sw128_kmajor_desc(sa);
-            const uint64_t b_low = make_sw128_kmajor_desc(sa + G::kABytes);
+            const uint64_t b_low = make_sw128_kmajor_desc(sb);
 #pragma unroll
             for (int t = 0; t < kSteps; ++t) {
               const uint64_t k = static_cast<uint64_t>(2 * (g * kSteps + t));
               mma_i8_ss(d_tmem, a_raw + k, b_low + k, idesc, t > 0 ? 1u : 0u);
             }
             if (g == 0) {
-              if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->high_full[stage], phase, abort_flag))) {
+              if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->high_full[work.slot], work.phase, abort_flag))) {
                 ok = false;
                 gave_up = 17;
                 break;
               }
               tc_fence_after_sync();
             }
-            const uint64_t a_high = make_sw128_kmajor_desc(sa + G::kHOffset);
-            const uint64_t b_high = make_sw128_kmajor_desc(sa + G::kABytes + G::kN * 128);
+            const uint64_t a_high = make_sw128_kmajor_desc(sw);
+            const uint64_t b_high = make_sw128_kmajor_desc(sb + G::kN * 128);
 #pragma unroll
             for (int t = 0; t < kSteps; ++t) {
               const uint64_t k = static_cast<uint64_t>(2 * (g * kSteps + t));
@@ -302,11 +461,9 @@ gemv_tc_kernel(const GemvTcParams p) {
           }
         }
         if (!ok) break;
-        tc_commit(&bars->empty[stage]);
-        if (++stage == G::kStages) {
-          stage = 0;
-          phase ^= 1u;
-        }
+        tc_commit(&bars->done[raw.slot]);
+        raw.advance(G::kSlots);
+        work.advance(G::kWorkSlots);
         if (++slab == p.slabs) {
           slab = 0;
           unit = 0;
@@ -361,7 +518,8 @@ gemv_tc_kernel(const GemvTcParams p) {
       }
       pend_add = 0;
     };
-    uint32_t stage = 0, phase = 0, ring_pos = 0, tphase = 0;
+    RingPos raw, work;
+    uint32_t ring_pos = 0, tphase = 0;
     bool ok = true;
     QX_PROF_DECL(w_tfull);
     const long long t_start = QX_PROF_NOW();
@@ -372,8 +530,9 @@ gemv_tc_kernel(const GemvTcParams p) {
     for (int i = 0; i < count && ok; ++i) {
       const bool mine = (unit & 1) == eset;
       if (mine) {
-        const uint8_t* stage_base = smem + stage * G::kStageBytes;
-        const int4* xcs = reinterpret_cast<const int4*>(stage_base + G::kABytes + G::kBBytes);
+        const uint8_t* raw_base = smem + raw.slot * G::kWBytes;
+        const int4* xcs = reinterpret_cast<const int4*>(work_ring + work.slot * G::kWorkBytes +
+                                                        G::kHBytes + G::kBBytes);
         uint32_t scw[4] = {0u, 0u, 0u, 0u};  // this row's eight fp16 block scales
 #pragma unroll
         for (int g = 0; g < G::kGroups; ++g) {
@@ -385,13 +544,14 @@ gemv_tc_kernel(const GemvTcParams p) {
           tc_fence_after_sync();
           if (i == 0 && g == 0 && epi_thread == 0) QX_PROF_STAMP(13);
           if (g == 0) {
-            // the stage's barrier completed before the MMAs ran; waiting on it here makes
-            // the bulk-copied scales and block constants visible to this thread
-            if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
+            // these barriers completed before the MMAs ran; waiting on them here makes the
+            // copied scales and the block constants visible to this thread
+            if (!mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag) ||
+                !mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag)) {
               ok = false;
               break;
             }
-            const uint4 s4 = *reinterpret_cast<const uint4*>(stage_base + G::kScaleOffset +
+            const uint4 s4 = *reinterpret_cast<const uint4*>(raw_base + G::kScaleOffset +
                                                              row_in_tile * (kSlabBlocks * 2));
             scw[0] = s4.x; scw[1] = s4.y; scw[2] = s4.z; scw[3] = s4.w;
           }
@@ -435,12 +595,10 @@ gemv_tc_kernel(const GemvTcParams p) {
         }
         if (!ok) break;
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->empty[stage]);  // scales / constants consumed
+        if (lane == 0) mbar_arrive(&bars->done[raw.slot]);  // scales / constants consumed
       }
-      if (++stage == G::kStages) {
-        stage = 0;
-        phase ^= 1u;
-      }
+      raw.advance(G::kSlots);
+      work.advance(G::kWorkSlots);
 
       // ---- unit / tile boundaries ----
       const bool unit_end = slab_in_unit + 1 == p.unit_slabs || slab == p.slabs - 1;
@@ -494,31 +652,39 @@ gemv_tc_kernel(const GemvTcParams p) {
     }
     if (!ok) {
       *abort_flag = 1;
-      atomicCAS(p.error, 0, 13);
+      atomicExch(p.error, 13);
     }
-  } else if (kQ4) {
+  } else if (kQ4 && warp < kFirstUnpackWarp + G::kUnpackWarps) {
     // ------------------------------ q4_0 high nibbles -------------------------
     // The raw tile is [128 rows][8 blocks x 16 bytes] with swizzled chunks; the high-nibble
     // tile has the same layout, so the extraction is position by position.
+    // Every warp waits for every slab in order and works on each fourth one: a warp that
+    // skipped barrier phases could take a phase two steps back for the one it waits for.
     const int u = warp - kFirstUnpackWarp;
     bool ok = true;
     QX_PROF_DECL(w_raw);
-    // Every warp waits for every slab in order and works on each fourth one: a warp that
-    // skipped barrier phases could take a phase two steps back for the one it waits for.
-    uint32_t stage = 0, phase = 0;
+    RingPos raw, freed;  // slab i / slab i - kWorkSlots in the weight ring
+    uint32_t work_slot = 0;
     for (int i = 0; i < count; ++i) {
-      if (!QX_PROF_WAIT(w_raw, mbar_wait(&bars->full[stage], phase, abort_flag))) {
+      if (!QX_PROF_WAIT(w_raw, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) {
         ok = false;
         break;
       }
-      if ((i % G::kUnpackWarps) == u) {
-        const uint4* raw = reinterpret_cast<const uint4*>(smem + stage * G::kStageBytes);
-        uint4* high = reinterpret_cast<uint4*>(smem + stage * G::kStageBytes + G::kHOffset);
+      if (i >= G::kWorkSlots) {  // the work slot's previous tile has been consumed
+        if (!mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        freed.advance(G::kSlots);
+      }
+      if ((i % (G::kUnpackWarps > 0 ? G::kUnpackWarps : 1)) == u) {
+        const uint4* packed = reinterpret_cast<const uint4*>(smem + raw.slot * G::kWBytes);
+        uint4* high = reinterpret_cast<uint4*>(work_ring + work_slot * G::kWorkBytes);
 #pragma unroll
         for (int it = 0; it < 32; it += 8) {
           uint4 w[8];
 #pragma unroll
-          for (int h = 0; h < 8; ++h) w[h] = raw[(it + h) * 32 + lane];
+          for (int h = 0; h < 8; ++h) w[h] = packed[(it + h) * 32 + lane];
 #pragma unroll
           for (int h = 0; h < 8; ++h) {
             uint4 o;
@@ -531,17 +697,76 @@ gemv_tc_kernel(const GemvTcParams p) {
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->high_full[stage]);
+        if (lane == 0) mbar_arrive(&bars->high_full[work_slot]);
       }
-      if (++stage == G::kStages) {
-        stage = 0;
-        phase ^= 1u;
-      }
+      raw.advance(G::kSlots);
+      if (++work_slot == G::kWorkSlots) work_slot = 0;
     }
     if (lane == 0 && u == 0) QX_PROF_STORE(9, w_raw);
     if (!ok) {
       *abort_flag = 1;
       atomicCAS(p.error, 0, 14);
+    }
+  } else if (G::kFused && warp == G::kQuantWarp) {
+    // ------------------------------ activation quantizer ----------------------
+    // Builds each slab's image in its work slot. Lane (b, q): elements 4q..4q+3 and
+    // 16+4q..16+4q+3 of block b; the next slab's values are fetched one slab ahead.
+    bool ok = true;
+    const int b = lane >> 2, q = lane & 3;
+    int xslab = static_cast<int>(s_begin % p.slabs);
+    RingPos freed;
+    uint32_t work_slot = 0;
+    float4 lo[MP], hi[MP];
+    bool valid = false;
+    auto fetch = [&](int slab_index) {
+      const int block = slab_index * kSlabBlocks + b;
+      valid = block < p.nb;
+#pragma unroll
+      for (int m = 0; m < MP; ++m) {
+        lo[m] = hi[m] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (valid && m < p.m) {
+          const float* src = p.x + static_cast<long long>(m) * p.ldx + block * 32 + 4 * q;
+          if (p.x_vector != 0) {
+            lo[m] = __ldg(reinterpret_cast<const float4*>(src));
+            hi[m] = __ldg(reinterpret_cast<const float4*>(src + 16));
+          } else {  // activations not on a 16-byte boundary
+            lo[m] = make_float4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3));
+            hi[m] = make_float4(__ldg(src + 16), __ldg(src + 17), __ldg(src + 18), __ldg(src + 19));
+          }
+        }
+      }
+    };
+    // the activations may be the output of the kernel in front of this one
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (lane == 0) QX_PROF_STAMP(12);
+    if (count > 0) fetch(xslab);
+    for (int i = 0; i < count; ++i) {
+      float4 cur_lo[MP], cur_hi[MP];
+#pragma unroll
+      for (int m = 0; m < MP; ++m) {
+        cur_lo[m] = lo[m];
+        cur_hi[m] = hi[m];
+      }
+      const bool cur_valid = valid;
+      xslab = xslab + 1 == p.slabs ? 0 : xslab + 1;
+      if (i + 1 < count) fetch(xslab);
+      if (i >= G::kWorkSlots) {  // the work slot's previous image has been consumed
+        if (!mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag)) {
+          ok = false;
+          break;
+        }
+        freed.advance(G::kSlots);
+      }
+      write_slab_image<FMT, MP>(work_ring + work_slot * G::kWorkBytes + G::kHBytes, cur_lo, cur_hi,
+                                cur_valid, lane);
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->x_full[work_slot]);
+      if (++work_slot == G::kWorkSlots) work_slot = 0;
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      atomicCAS(p.error, 0, 18);
     }
   }
 
@@ -556,7 +781,8 @@ gemv_tc_kernel(const GemvTcParams p) {
 
 template <int FMT, int MP>
 constexpr size_t gemv_smem_bytes() {
-  return 1024 + static_cast<size_t>(TcGeom<FMT, MP>::kStages) * TcGeom<FMT, MP>::kStageBytes +
+  return 1024 + static_cast<size_t>(TcGeom<FMT, MP>::kSlots) * TcGeom<FMT, MP>::kWBytes +
+         static_cast<size_t>(TcGeom<FMT, MP>::kWorkSlots) * TcGeom<FMT, MP>::kWorkBytes +
          sizeof(GemvBarriers<FMT, MP>) + 64;
 }
 
@@ -571,10 +797,11 @@ qx_status launch_one(const GemvTcParams& p, int grid, cudaStream_t stream) {
                                      static_cast<int>(smem)));
     attr_set = true;
   }
-  // Programmatic dependent launch: this kernel may start while the activation quantizer
-  // in front of it is still running. Everything that does not depend on the activations
-  // (barrier set-up, TMEM allocation, the first weight copies) proceeds; the thread that
-  // copies the activation images waits for the quantizer's results (griddepcontrol.wait).
+  // Programmatic dependent launch: this kernel may start while the kernel in front of it
+  // (the activation quantizer, or whatever produces the activations) is still running.
+  // Everything that does not depend on the activations (barrier set-up, TMEM allocation,
+  // the first weight copies) proceeds; the thread or warp that reads the activations or
+  // their images waits for that kernel's results (griddepcontrol.wait).
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(static_cast<unsigned>(grid));
   config.blockDim = dim3(TcGeom<FMT, MP>::kThreads);
@@ -646,20 +873,26 @@ qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScra
   return QX_STATUS_OK;
 }
 
-qx_status launch_gemv_tc(const qx_weights* w, const uint8_t* ximg, float* y, int m,
+bool gemv_tc_quantizes_in_kernel(int m) { return padded_batch(m) <= 2; }
+
+qx_status launch_gemv_tc(const qx_weights* w, const float* x, const uint8_t* ximg, float* y, int m,
                          long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
                          cudaStream_t stream) {
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
-  return launch_gemv_tc_at(w, ximg, y, m, ldy, ws_base, scratch, ctx->flag + 1, stream);
+  return launch_gemv_tc_at(w, x, ximg, y, m, ldy, ws_base, scratch, ctx->flag + 1, stream);
 }
 
-qx_status launch_gemv_tc_at(const qx_weights* w, const uint8_t* ximg, float* y, int m,
-                            long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
+qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* ximg, float* y,
+                            int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
                             int* error_word, cudaStream_t stream) {
   GemvTcParams p{};
   p.panel = w->panel;
   p.ximg = ximg;
+  p.x = x;
+  p.ldx = w->columns;
+  p.nb = static_cast<int>(w->blocks_per_row);
+  p.x_vector = reinterpret_cast<uintptr_t>(x) % 16 == 0 ? 1 : 0;
   p.y = y;
   p.partial = reinterpret_cast<float*>(ws_base + scratch.partial_offset);
   p.counters = reinterpret_cast<int*>(ws_base);

@@ -22,15 +22,20 @@ struct GemvScratch {
 // between launches); the rest is laid out per call.
 qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScratch* out);
 
-// ximg: activation slab images written by the quantizer (qx_gemv.cu)
-qx_status launch_gemv_tc(const qx_weights* w, const uint8_t* ximg, float* y, int m,
+// Batches of one or two activation rows are quantized inside the GEMV kernel (it reads x);
+// larger ones need the slab images written by the quantizer kernel first (qx_gemv.cu).
+bool gemv_tc_quantizes_in_kernel(int m);
+
+// x: activations [m][columns] f32; ximg: activation slab images (unused when the kernel
+// quantizes itself)
+qx_status launch_gemv_tc(const qx_weights* w, const float* x, const uint8_t* ximg, float* y, int m,
                          long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
                          cudaStream_t stream);
 
 // Same, with the device word that receives a non-zero role code when a bounded wait gives
 // up passed in by the caller instead of taken from the per-device context.
-qx_status launch_gemv_tc_at(const qx_weights* w, const uint8_t* ximg, float* y, int m,
-                            long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
+qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* ximg, float* y,
+                            int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
                             int* error_word, cudaStream_t stream);
 
 const char* gemv_variant_name();
