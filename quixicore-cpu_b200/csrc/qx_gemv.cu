@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
     const int half = cc & 1;
     const int klass = n / (4 * mp), row = (n >> 2) % mp, d = n & 3;
     const long long b = slab * kSlabBlocks + j;
-    const bool digit_used = FMT == QX_FORMAT_Q8_0 ? d < 3 : (which == 1 || d < 3);
+    const bool digit_used = FMT == QX_FORMAT_Q8_0 ? d < 3 : true;
     const bool active = (j % group) == klass && row < m && b < nb && digit_used;
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
     if (active) {
@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
             value = __float2int_rn((half != 0 ? v[16 + i] : v[i]) * scale_up);  // |t| <= 2^22
           } else {
             const int lo = __float2int_rn(v[i] * scale_up);
-            value = which == 0 ? lo : __float2int_rn(v[16 + i] * scale_up) - 16 * lo;
+            value = which == 0 ? 16 * lo : __float2int_rn(v[16 + i] * scale_up) - 16 * lo;
           }
         }
         word[i >> 2] |= static_cast<uint32_t>(balanced_digit(value, d) & 255) << (8 * (i & 3));
@@ -127,10 +127,9 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
         int sum = 0;  // |sum| <= 32 * 2^22
 #pragma unroll
         for (int i = 0; i < 32; ++i) sum += __float2int_rn(v[i] * scale_up);
-        const int k8 = 8 * sum;
-        c.k_lo = k8 & 0xFFFF;
-        c.k_hi = k8 >> 16;
+        q4_offset_constants(sum, &c.k_lo, &c.k_hi);
       }
+      if (FMT == QX_FORMAT_Q4_0) c.scale *= 0.0625f;  // the digit sums carry a factor 16
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     *reinterpret_cast<XConst*>(ximg + slab * image_bytes + ximage_const_offset(ncols, mp, j, row)) = c;
@@ -186,20 +185,18 @@ __global__ void __launch_bounds__(256) gemv_dp4a_kernel(
           }
         }
       } else {
-        // raw bytes against the digits of t_i, high nibbles against the digits of z_i
+        // raw bytes against the digits of 16*t_i, masked bytes against the digits of z_i
         const uint4 w = __ldg(reinterpret_cast<const uint4*>(span + panel_code_offset_q4(r, j)));
-        const uint4 h = make_uint4((w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu,
-                                   (w.z >> 4) & 0x0F0F0F0Fu, (w.w >> 4) & 0x0F0F0F0Fu);
+        const uint4 h = make_uint4(w.x & 0xF0F0F0F0u, w.y & 0xF0F0F0F0u, w.z & 0xF0F0F0F0u,
+                                   w.w & 0xF0F0F0F0u);
 #pragma unroll
         for (int d = 0; d < 4; ++d) {
           const int nrow = digit_row(FMT, mp, j, m, d);
-          if (d < 3) {
-            const uint4 g = __ldg(reinterpret_cast<const uint4*>(image + ximage_chunk_offset(ncols, 0, nrow, j)));
-            s[d] = dp4a_us(w.x, g.x, s[d]);
-            s[d] = dp4a_us(w.y, g.y, s[d]);
-            s[d] = dp4a_us(w.z, g.z, s[d]);
-            s[d] = dp4a_us(w.w, g.w, s[d]);
-          }
+          const uint4 g = __ldg(reinterpret_cast<const uint4*>(image + ximage_chunk_offset(ncols, 0, nrow, j)));
+          s[d] = dp4a_us(w.x, g.x, s[d]);
+          s[d] = dp4a_us(w.y, g.y, s[d]);
+          s[d] = dp4a_us(w.z, g.z, s[d]);
+          s[d] = dp4a_us(w.w, g.w, s[d]);
           const uint4 z = __ldg(reinterpret_cast<const uint4*>(image + ximage_chunk_offset(ncols, 1, nrow, j)));
           s[d] = dp4a_us(h.x, z.x, s[d]);
           s[d] = dp4a_us(h.y, z.y, s[d]);

@@ -14,12 +14,15 @@
 // block envelope per element, the order of one f32 rounding in the reference's own
 // 32-term sum; the integer sums are exact.
 //
-// q4_0 without unpacking the low nibbles. Byte i of a block holds element i (low nibble,
-// lo_i) and element i + 16 (high nibble, hi_i). With w_i = lo_i + 16*hi_i the raw byte,
-//   sum_i lo_i*t_i + hi_i*t_{i+16} = sum_i w_i*t_i + sum_i hi_i*(t_{i+16} - 16*t_i),
-// so the raw bytes are one 8-bit operand (against the digits of t_i, i < 16) and only the
-// high nibbles have to be extracted (against the four digits of z_i = t_{i+16} - 16*t_i,
-// |z_i| < 2^27). The "-8" of the format is the per-block constant 8 * sum_j t_j.
+// q4_0 without unpacking the nibbles. Byte i of a block holds element i (low nibble,
+// lo_i) and element i + 16 (high nibble, hi_i). With w_i = lo_i + 16*hi_i the raw byte and
+// h_i = 16*hi_i = w_i & 0xF0,
+//   16 * sum_i (lo_i*t_i + hi_i*t_{i+16}) = sum_i w_i*(16*t_i) + sum_i h_i*(t_{i+16} - 16*t_i),
+// so the raw bytes are one unsigned 8-bit operand (against the four digits of 16*t_i,
+// i < 16) and the masked bytes a second one (against the four digits of
+// z_i = t_{i+16} - 16*t_i, |z_i| < 2^27): one AND per word is all the unpacking there is.
+// The factor 16 is folded into the block's power-of-two scale, and the "-8" of the format
+// is the per-block constant 16 * 8 * sum_j t_j.
 #pragma once
 
 #include "qx_common.cuh"
@@ -80,8 +83,9 @@ __host__ __device__ inline int digit_row(int format, int mp, int j, int row, int
 
 // Per (block j, activation row) constants, 16 bytes.
 struct __align__(16) XConst {
-  float scale;  // 2^(e-22): x_j ~= scale * t_j (NaN when the block holds a non-finite value)
-  int k_lo;     // q4_0: 8 * sum_j t_j = 65536 * k_hi + k_lo, 0 <= k_lo < 65536
+  float scale;  // 2^(e-22): x_j ~= scale * t_j (NaN when the block holds a non-finite value);
+                // q4_0: 2^(e-26), the digit sums carry a factor 16
+  int k_lo;     // q4_0: 128 * sum_j t_j = 65536 * k_hi + k_lo, 0 <= k_lo < 65536
   int k_hi;
   int pad;
 };
@@ -89,7 +93,7 @@ struct __align__(16) XConst {
 // Activation side of one K-slab ("image"), in the form the tensor-core kernel wants in
 // shared memory, so one bulk copy brings it in:
 //   q8_0: [sub-tile 0 | sub-tile 1], each [N digit rows][128 bytes] (blocks 0-3 | 4-7)
-//   q4_0: [digits of t_i, i < 16 | digits of z_i], each [N rows][8 blocks x 16 bytes]
+//   q4_0: [digits of 16*t_i, i < 16 | digits of z_i], each [N rows][8 blocks x 16 bytes]
 //   then XConst[8 blocks][mp]
 // with 16-byte chunks swizzled by the row index like the weight sub-tiles.
 __host__ __device__ constexpr int ximage_bytes(int format, int mp) {
@@ -121,6 +125,13 @@ __device__ __forceinline__ float combine_digits(int u, int v) {
 // One block's term from its four digit sums: f32(2^24*s3 + 65536*s2 + 256*s1 + s0 - k).
 __device__ __forceinline__ float block_sum(int s0, int s1, int s2, int s3, int k_lo, int k_hi) {
   return combine_digits(s1 * 256 + s0 - k_lo, s3 * 256 + s2 - k_hi);
+}
+
+// q4_0 block constants from sum = sum_j t_j (|sum| <= 2^27): 128 * sum split at bit 16
+// without leaving 32 bits.
+__host__ __device__ inline void q4_offset_constants(int sum, int* k_lo, int* k_hi) {
+  *k_lo = (sum & 0x1FF) << 7;
+  *k_hi = sum >> 9;
 }
 
 // fp16 bits -> f32, identical to kernels/common/fp16.h:11-37 for every finite or

@@ -20,12 +20,12 @@
 // activation rows, a single TMEM load brings a whole slab to the epilogue thread.
 //   q8_0  8 MMAs per slab (one per block, K = 32 code bytes)
 //   q4_0  the raw packed bytes are an unsigned operand as they are (4 MMAs against the
-//         digits of the low-nibble activations); four warps extract the high nibbles into a
-//         second tile (4 more MMAs against the digits of t[i+16] - 16*t[i])
+//         digits of 16*t[i]); four warps mask out the high nibbles into a second tile (4
+//         more MMAs against the digits of t[i+16] - 16*t[i]): see qx_gemv.cuh
 // Warp roles: 0 = copy producer (one thread), 1 = MMA issuer (one thread), 2-9 = epilogue
 // (thread = weight row, accumulators in registers; two sets of four warps take alternate
-// K units), then for q4_0 four warps for the high nibbles (one slab per warp, round robin)
-// and, for decode batches, the activation quantizer warp.
+// K units), then for q4_0 four warps for the high nibbles (a quarter of every slab each)
+// and, for decode batches, three activation quantizer warps (one per work slot).
 //
 // Work split and summation order. K is cut into units of `unit_slabs` slabs, a function of
 // K alone. A row's result is defined as (sum of its even units) + (sum of its odd units),
@@ -75,12 +75,23 @@ struct TcGeom {
   static constexpr int kHBytes = kQ4 ? kTileRows * 128 : 0;
   static constexpr int kBBytes = kN * 256;
   static constexpr int kXBytes = ximage_bytes(FMT, MP);  // digit rows + constants
-  static constexpr int kWorkBytes = (kHBytes + kXBytes + 1023) / 1024 * 1024;
-  static constexpr int kBudget = kSmemLimit - 1024 - 2048;  // alignment slack, barriers
-  static constexpr int kWorkSlots =
-      weight_slots_fit(kBudget, kWorkBytes, kWBytes, 3) == weight_slots_fit(kBudget, kWorkBytes, kWBytes, 2)
-          ? 3
-          : 2;
+  // When the kernel quantizes itself the block constants live in their own small ring,
+  // one entry per weight slot, because they are needed longer (until the epilogue has
+  // read them) than the operands of the MMAs.
+  static constexpr int kConstBytes = 128 * MP;
+  static constexpr int kWorkBytes = (kHBytes + (kFused ? kBBytes : kXBytes) + 1023) / 1024 * 1024;
+  // ... and the activations of the next slabs wait in a small ring of their own (copied
+  // there asynchronously a few slabs ahead: a load from L2 takes longer than a slab).
+  static constexpr int kQuantWarps = 3;  // == kWorkSlots when the kernel quantizes itself
+  static constexpr int kXRingSlots = 4;  // per quantizer warp
+  static constexpr int kXRingBytes = kFused ? kQuantWarps * kXRingSlots * MP * kSlabK * 4 : 0;
+  static constexpr int kBudget = kSmemLimit - 1024 - 2048 - (kFused ? 8 * kConstBytes : 0) -
+                                 kXRingBytes;  // slack, barriers, constants, activation ring
+  // three work slots unless that costs more than one weight slot
+  static constexpr int kWorkSlots = weight_slots_fit(kBudget, kWorkBytes, kWBytes, 3) + 1 >=
+                                            weight_slots_fit(kBudget, kWorkBytes, kWBytes, 2)
+                                        ? 3
+                                        : 2;
   static constexpr int kSlots = weight_slots_fit(kBudget, kWorkBytes, kWBytes, kWorkSlots);
   static constexpr int kTCols = kN;                    // TMEM columns per accumulator
   static constexpr int kTStages = 512 / kTCols > 16 ? 16 : 512 / kTCols;
@@ -89,10 +100,12 @@ struct TcGeom {
   static constexpr int kTPerSet = kTStages / 2;
   static constexpr int kUnpackWarps = kQ4 ? 4 : 0;
   static constexpr int kQuantWarp = 2 + kEpilogueWarps + kUnpackWarps;  // fused only
-  static constexpr int kThreads = 32 * (2 + kEpilogueWarps + kUnpackWarps + (kFused ? 1 : 0));
+  static constexpr int kThreads =
+      32 * (2 + kEpilogueWarps + kUnpackWarps + (kFused ? kQuantWarps : 0));
   static constexpr int kLdCols = kN >= 64 ? 64 : 32;   // columns fetched per TMEM wait
   static_assert(kSlots >= 2 && kSlots >= kWorkSlots && kTPerSet >= 1 && kN >= 32 && kN <= 256,
                 "geometry");
+  static_assert(!kFused || kWorkSlots == kQuantWarps, "one quantizer warp per work slot");
   static_assert(kScaleOffset + kSlabScaleBytes == kWBytes && kWBytes % 1024 == 0, "span");
 };
 
@@ -118,6 +131,8 @@ struct __align__(8) GemvBarriers {
   uint64_t done[TcGeom<FMT, MP>::kSlots];        // MMAs done + scales / constants consumed
   uint64_t x_full[TcGeom<FMT, MP>::kWorkSlots];  // activation image in the work slot
   uint64_t high_full[TcGeom<FMT, MP>::kWorkSlots];  // q4_0: high-nibble tile written
+  uint64_t mma_done[TcGeom<FMT, MP>::kWorkSlots];   // the slab's MMAs have read the work slot
+  uint64_t const_full[TcGeom<FMT, MP>::kSlots];     // block constants written (in-kernel quantizer)
   uint64_t tmem_full[TcGeom<FMT, MP>::kTStages];
   uint64_t tmem_empty[TcGeom<FMT, MP>::kTStages];
   uint32_t tmem_base;
@@ -150,37 +165,45 @@ struct RingPos {
       phase ^= 1u;
     }
   }
+  __device__ __forceinline__ void advance_by(uint32_t steps, uint32_t slots) {
+    slot += steps;
+    while (slot >= slots) {
+      slot -= slots;
+      phase ^= 1u;
+    }
+  }
 };
 
-// Four values -> the bytes of balanced base-256 digit d (0..3) of each, packed in a word.
-__device__ __forceinline__ void pack_digits(const int (&t)[4], uint32_t (&word)[4]) {
-  word[0] = word[1] = word[2] = word[3] = 0u;
+// The low bytes of four values, packed into a word.
+__device__ __forceinline__ uint32_t pack_low_bytes(int a, int b, int c, int d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+// word[d] = the balanced base-256 digits d (as signed bytes) of t[0..3], d < ND. The digit
+// is the low byte of the running quotient, and removing it is (t + 128) >> 8.
+template <int ND>
+__device__ __forceinline__ void pack_digits(int (&t)[4], uint32_t (&word)[4]) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int p0 = ((t[i] + 128) & 255) - 128;
-    const int t1 = (t[i] - p0) >> 8;
-    const int p1 = ((t1 + 128) & 255) - 128;
-    const int t2 = (t1 - p1) >> 8;
-    const int p2 = ((t2 + 128) & 255) - 128;
-    const int p3 = (t2 - p2) >> 8;
-    word[0] |= static_cast<uint32_t>(p0 & 255) << (8 * i);
-    word[1] |= static_cast<uint32_t>(p1 & 255) << (8 * i);
-    word[2] |= static_cast<uint32_t>(p2 & 255) << (8 * i);
-    word[3] |= static_cast<uint32_t>(p3 & 255) << (8 * i);
+  for (int d = 0; d < ND; ++d) {
+    word[d] = pack_low_bytes(t[0], t[1], t[2], t[3]);
+    if (d + 1 < ND) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) t[i] = (t[i] + 128) >> 8;
+    }
   }
 }
 
-// In-kernel activation quantizer (decode batches): writes slab `xslab`'s image into a work
-// slot whose digit area is zero outside the block-diagonal positions. Lane (b = lane / 4,
-// q = lane % 4) handles elements 4q..4q+3 and 16+4q..16+4q+3 of block b of every row:
-// `lo` / `hi` are those values (zeros past the end of the row).
+// In-kernel activation quantizer (decode batches): writes a slab's digits into a work slot
+// whose digit area is zero outside the block-diagonal positions, and its block constants.
+// Lane (b = lane / 4, q = lane % 4) handles elements 4q..4q+3 and 16+4q..16+4q+3 of block
+// b of every row: `lo` / `hi` are those values (zeros past the end of the row);
+// digit_offset[m][d] is the lane's byte offset in the digit area for digit d of row m.
 template <int FMT, int MP>
-__device__ __forceinline__ void write_slab_image(uint8_t* digits, const float4 (&lo)[MP],
-                                                 const float4 (&hi)[MP], bool block_valid,
-                                                 int lane) {
+__device__ __forceinline__ void write_slab_image(uint8_t* digits, XConst* consts,
+                                                 const int (&digit_offset)[MP][4],
+                                                 const float4 (&lo)[MP], const float4 (&hi)[MP],
+                                                 bool block_valid, int lane) {
   using G = TcGeom<FMT, MP>;
   const int b = lane >> 2, q = lane & 3;
-  XConst* consts = reinterpret_cast<XConst*>(digits + G::kBBytes);
 #pragma unroll
   for (int m = 0; m < MP; ++m) {
     const float v[8] = {lo[m].x, lo[m].y, lo[m].z, lo[m].w, hi[m].x, hi[m].y, hi[m].z, hi[m].w};
@@ -193,56 +216,49 @@ __device__ __forceinline__ void write_slab_image(uint8_t* digits, const float4 (
     const uint32_t eb_raw = amax_bits >> 23;
     const bool finite = eb_raw != 255u;
     const uint32_t eb = max(eb_raw, 30u);                       // envelope 2^(eb-126) > amax
-    const float scale_up = __uint_as_float((275u - eb) << 23);  // 2^(22 - e)
-    float scale = finite ? __uint_as_float((eb - 21u) << 23)    // 2^(e - 22)
-                         : __uint_as_float(0x7FC00000u);        // NaN/inf in -> NaN out
+    const float scale_up = finite ? __uint_as_float((275u - eb) << 23) : 0.0f;  // 2^(22 - e)
+    // 2^(e - 22); q4_0: 2^(e - 26), its digit sums carry a factor 16
+    float scale = __uint_as_float((eb - (FMT == QX_FORMAT_Q4_0 ? 25u : 21u)) << 23);
+    if (!finite) scale = __uint_as_float(0x7FC00000u);  // NaN/inf in -> NaN out
     if (!block_valid) scale = 0.0f;
     int t_lo[4], t_hi[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      t_lo[i] = finite ? __float2int_rn(v[i] * scale_up) : 0;  // |t| <= 2^22
-      t_hi[i] = finite ? __float2int_rn(v[4 + i] * scale_up) : 0;
+      // |t| <= 2^22 (a non-finite block has scale_up = 0; 0 * inf = NaN converts to 0)
+      t_lo[i] = __float2int_rn(v[i] * scale_up);
+      t_hi[i] = __float2int_rn(v[4 + i] * scale_up);
     }
-    const int n = ((b % G::kG) * MP + m) * 4;  // digit row of digit 0
     uint32_t w_lo[4], w_hi[4];
-    pack_digits(t_lo, w_lo);
     if (FMT == QX_FORMAT_Q8_0) {
-      pack_digits(t_hi, w_hi);
-      uint8_t* tile = digits + (b >> 2) * (G::kN * 128);
+      pack_digits<3>(t_lo, w_lo);
+      pack_digits<3>(t_hi, w_hi);
 #pragma unroll
       for (int d = 0; d < 3; ++d) {
-        const int row = n + d;
-        *reinterpret_cast<uint32_t*>(tile + row * 128 + (((2 * (b & 3)) ^ (row & 7)) << 4) + 4 * q) = w_lo[d];
-        *reinterpret_cast<uint32_t*>(tile + row * 128 + (((2 * (b & 3) + 1) ^ (row & 7)) << 4) + 4 * q) = w_hi[d];
+        // the second half of the block is the neighbouring 16-byte chunk
+        *reinterpret_cast<uint32_t*>(digits + digit_offset[m][d]) = w_lo[d];
+        *reinterpret_cast<uint32_t*>(digits + (digit_offset[m][d] ^ 16)) = w_hi[d];
       }
     } else {
-      int z[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) z[i] = t_hi[i] - 16 * t_lo[i];
-      pack_digits(z, w_hi);
-#pragma unroll
-      for (int d = 0; d < 4; ++d) {
-        const int row = n + d;
-        const int offset = row * 128 + ((b ^ (row & 7)) << 4) + 4 * q;
-        if (d < 3) *reinterpret_cast<uint32_t*>(digits + offset) = w_lo[d];
-        *reinterpret_cast<uint32_t*>(digits + G::kN * 128 + offset) = w_hi[d];
-      }
-    }
-    int sum = 0;
-    if (FMT == QX_FORMAT_Q4_0) {
+      int sum = 0;
 #pragma unroll
       for (int i = 0; i < 4; ++i) sum += t_lo[i] + t_hi[i];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        t_lo[i] *= 16;
+        t_hi[i] -= t_lo[i];  // z_i
+      }
+      pack_digits<4>(t_lo, w_lo);
+      pack_digits<4>(t_hi, w_hi);
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        *reinterpret_cast<uint32_t*>(digits + digit_offset[m][d]) = w_lo[d];
+        *reinterpret_cast<uint32_t*>(digits + G::kN * 128 + digit_offset[m][d]) = w_hi[d];
+      }
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (q == 0) q4_offset_constants(sum, &consts[b * MP + m].k_lo, &consts[b * MP + m].k_hi);
     }
-    if (q == 0) {
-      XConst c;
-      c.scale = scale;
-      c.k_lo = (8 * sum) & 0xFFFF;
-      c.k_hi = (8 * sum) >> 16;
-      c.pad = 0;
-      consts[b * MP + m] = c;
-    }
+    if (q == 0) consts[b * MP + m].scale = scale;
   }
 }
 
@@ -255,7 +271,10 @@ gemv_tc_kernel(const GemvTcParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* work_ring = smem + G::kSlots * G::kWBytes;  // slot: [high nibbles (q4_0) | image]
-  auto* bars = reinterpret_cast<GemvBarriers<FMT, MP>*>(work_ring + G::kWorkSlots * G::kWorkBytes);
+  // block constants of the slab in each weight slot (only when the kernel quantizes itself)
+  uint8_t* const_ring = work_ring + G::kWorkSlots * G::kWorkBytes;
+  uint8_t* x_ring = const_ring + (G::kFused ? G::kSlots * G::kConstBytes : 0);
+  auto* bars = reinterpret_cast<GemvBarriers<FMT, MP>*>(x_ring + G::kXRingBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = &bars->abort_flag;
@@ -268,10 +287,12 @@ gemv_tc_kernel(const GemvTcParams p) {
     for (int s = 0; s < G::kSlots; ++s) {
       mbar_init(&bars->raw_full[s], 1);  // the producer's expect_tx arrival
       mbar_init(&bars->done[s], 1 + 4);  // MMA commit + four epilogue warps
+      mbar_init(&bars->const_full[s], 1);
     }
     for (int s = 0; s < G::kWorkSlots; ++s) {
       mbar_init(&bars->x_full[s], 1);  // expect_tx arrival, or the quantizer warp
-      mbar_init(&bars->high_full[s], 1);
+      mbar_init(&bars->high_full[s], kQ4 ? G::kUnpackWarps : 1);
+      mbar_init(&bars->mma_done[s], 1);
     }
     for (int t = 0; t < G::kTStages; ++t) {
       mbar_init(&bars->tmem_full[t], 1);
@@ -382,6 +403,8 @@ gemv_tc_kernel(const GemvTcParams p) {
       int gave_up = 12;  // which wait ran out: 12 weights, 15 image, 16 accumulator, 17 high nibbles
       QX_PROF_DECL(w_full);
       QX_PROF_DECL(w_tempty);
+      QX_PROF_DECL(w_x);
+      QX_PROF_DECL(w_high);
       int slab = static_cast<int>(s_begin % p.slabs);
       int unit = slab / p.unit_slabs;
       int slab_in_unit = slab - unit * p.unit_slabs;
@@ -391,7 +414,7 @@ gemv_tc_kernel(const GemvTcParams p) {
           ok = false;
           break;
         }
-        if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag))) {
+        if (!QX_PROF_WAIT(w_x, mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag))) {
           ok = false;
           gave_up = 15;
           break;
@@ -434,7 +457,7 @@ gemv_tc_kernel(const GemvTcParams p) {
               mma_i8_ss(d_tmem, a_raw + k, b_low + k, idesc, t > 0 ? 1u : 0u);
             }
             if (g == 0) {
-              if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->high_full[work.slot], work.phase, abort_flag))) {
+              if (!QX_PROF_WAIT(w_high, mbar_wait(&bars->high_full[work.slot], work.phase, abort_flag))) {
                 ok = false;
                 gave_up = 17;
                 break;
@@ -461,6 +484,7 @@ gemv_tc_kernel(const GemvTcParams p) {
           }
         }
         if (!ok) break;
+        if (G::kFused) tc_commit(&bars->mma_done[work.slot]);
         tc_commit(&bars->done[raw.slot]);
         raw.advance(G::kSlots);
         work.advance(G::kWorkSlots);
@@ -475,6 +499,8 @@ gemv_tc_kernel(const GemvTcParams p) {
       }
       QX_PROF_STORE(2, w_full);
       QX_PROF_STORE(3, w_tempty);
+      QX_PROF_STORE(16, w_x);
+      QX_PROF_STORE(17, w_high);
       if (!ok) {
         *abort_flag = 1;
         atomicCAS(p.error, 0, gave_up);
@@ -531,8 +557,9 @@ gemv_tc_kernel(const GemvTcParams p) {
       const bool mine = (unit & 1) == eset;
       if (mine) {
         const uint8_t* raw_base = smem + raw.slot * G::kWBytes;
-        const int4* xcs = reinterpret_cast<const int4*>(work_ring + work.slot * G::kWorkBytes +
-                                                        G::kHBytes + G::kBBytes);
+        const int4* xcs = reinterpret_cast<const int4*>(
+            G::kFused ? const_ring + raw.slot * G::kConstBytes
+                      : work_ring + work.slot * G::kWorkBytes + G::kHBytes + G::kBBytes);
         uint32_t scw[4] = {0u, 0u, 0u, 0u};  // this row's eight fp16 block scales
 #pragma unroll
         for (int g = 0; g < G::kGroups; ++g) {
@@ -546,8 +573,11 @@ gemv_tc_kernel(const GemvTcParams p) {
           if (g == 0) {
             // these barriers completed before the MMAs ran; waiting on them here makes the
             // copied scales and the block constants visible to this thread
+            // (the in-kernel quantizer's work slot may already hold a later slab: its
+            // constants have a barrier with the lifetime of the weight slot)
             if (!mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag) ||
-                !mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag)) {
+                !(G::kFused ? mbar_wait(&bars->const_full[raw.slot], raw.phase, abort_flag)
+                            : mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag))) {
               ok = false;
               break;
             }
@@ -656,113 +686,178 @@ gemv_tc_kernel(const GemvTcParams p) {
     }
   } else if (kQ4 && warp < kFirstUnpackWarp + G::kUnpackWarps) {
     // ------------------------------ q4_0 high nibbles -------------------------
-    // The raw tile is [128 rows][8 blocks x 16 bytes] with swizzled chunks; the high-nibble
-    // tile has the same layout, so the extraction is position by position.
-    // Every warp waits for every slab in order and works on each fourth one: a warp that
-    // skipped barrier phases could take a phase two steps back for the one it waits for.
+    // The raw tile is [128 rows][8 blocks x 16 bytes] with swizzled chunks; the tile of the
+    // masked bytes (16 * high nibble) has the same layout, so the extraction is position by
+    // position. The four warps take a quarter of every slab each.
     const int u = warp - kFirstUnpackWarp;
     bool ok = true;
     QX_PROF_DECL(w_raw);
-    RingPos raw, freed;  // slab i / slab i - kWorkSlots in the weight ring
-    uint32_t work_slot = 0;
+    QX_PROF_DECL(w_slot);
+    const long long t_u0 = QX_PROF_NOW();
+    RingPos raw, work, freed;  // freed: slab i - kWorkSlots in the weight ring
     for (int i = 0; i < count; ++i) {
       if (!QX_PROF_WAIT(w_raw, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) {
         ok = false;
         break;
       }
       if (i >= G::kWorkSlots) {  // the work slot's previous tile has been consumed
-        if (!mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag)) {
+        const bool free_now = QX_PROF_WAIT(
+            w_slot, G::kFused ? mbar_wait(&bars->mma_done[work.slot], work.phase ^ 1u, abort_flag)
+                              : mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag));
+        if (!free_now) {
           ok = false;
           break;
         }
         freed.advance(G::kSlots);
       }
-      if ((i % (G::kUnpackWarps > 0 ? G::kUnpackWarps : 1)) == u) {
-        const uint4* packed = reinterpret_cast<const uint4*>(smem + raw.slot * G::kWBytes);
-        uint4* high = reinterpret_cast<uint4*>(work_ring + work_slot * G::kWorkBytes);
+      const uint4* packed = reinterpret_cast<const uint4*>(smem + raw.slot * G::kWBytes) + u * 256;
+      uint4* high = reinterpret_cast<uint4*>(work_ring + work.slot * G::kWorkBytes) + u * 256;
+      uint4 w[8];
 #pragma unroll
-        for (int it = 0; it < 32; it += 8) {
-          uint4 w[8];
+      for (int h = 0; h < 8; ++h) w[h] = packed[h * 32 + lane];
 #pragma unroll
-          for (int h = 0; h < 8; ++h) w[h] = packed[(it + h) * 32 + lane];
-#pragma unroll
-          for (int h = 0; h < 8; ++h) {
-            uint4 o;
-            o.x = (w[h].x >> 4) & 0x0F0F0F0Fu;
-            o.y = (w[h].y >> 4) & 0x0F0F0F0Fu;
-            o.z = (w[h].z >> 4) & 0x0F0F0F0Fu;
-            o.w = (w[h].w >> 4) & 0x0F0F0F0Fu;
-            high[(it + h) * 32 + lane] = o;
-          }
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->high_full[work_slot]);
+      for (int h = 0; h < 8; ++h) {
+        high[h * 32 + lane] = make_uint4(w[h].x & 0xF0F0F0F0u, w[h].y & 0xF0F0F0F0u,
+                                         w[h].z & 0xF0F0F0F0u, w[h].w & 0xF0F0F0F0u);
       }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->high_full[work.slot]);
       raw.advance(G::kSlots);
-      if (++work_slot == G::kWorkSlots) work_slot = 0;
+      work.advance(G::kWorkSlots);
     }
-    if (lane == 0 && u == 0) QX_PROF_STORE(9, w_raw);
+    if (lane == 0 && u == 0) {
+      QX_PROF_STORE(9, w_raw);
+      QX_PROF_STORE(20, w_slot);
+      QX_PROF_STORE(21, QX_PROF_NOW() - t_u0);
+    }
     if (!ok) {
       *abort_flag = 1;
       atomicCAS(p.error, 0, 14);
     }
-  } else if (G::kFused && warp == G::kQuantWarp) {
-    // ------------------------------ activation quantizer ----------------------
-    // Builds each slab's image in its work slot. Lane (b, q): elements 4q..4q+3 and
-    // 16+4q..16+4q+3 of block b; the next slab's values are fetched one slab ahead.
+  } else if (G::kFused && warp >= G::kQuantWarp) {
+    // ------------------------------ activation quantizers ---------------------
+    // Quantizer warp w builds the images of slabs w, w + 3, ... in work slot w (one warp
+    // per work slot: building an image is a long dependent chain, three of them overlap).
+    // Lane (b, q): elements 4q..4q+3 and 16+4q..16+4q+3 of block b. Every lane copies its
+    // own values into a ring in shared memory kAhead of its slabs before it needs them
+    // (cp.async: no registers held meanwhile; a load from L2 takes longer than a slab).
+    constexpr int kW = G::kQuantWarps;
+    constexpr int kAhead = G::kXRingSlots - 1;
+    const int qw = warp - G::kQuantWarp;
     bool ok = true;
     const int b = lane >> 2, q = lane & 3;
-    int xslab = static_cast<int>(s_begin % p.slabs);
-    RingPos freed;
-    uint32_t work_slot = 0;
-    float4 lo[MP], hi[MP];
-    bool valid = false;
-    auto fetch = [&](int slab_index) {
-      const int block = slab_index * kSlabBlocks + b;
-      valid = block < p.nb;
+    const int first_slab = static_cast<int>((s_begin + qw) % p.slabs);
+    const int step = kW % p.slabs;  // slabs wrap around at the end of a row tile
+    int copy_slab = first_slab, use_slab = first_slab;
+    int copy_i = qw;  // CTA-local index of the next slab to copy
+    RingPos raw;
+    raw.advance_by(static_cast<uint32_t>(qw), G::kSlots);
+    uint32_t slot_uses = 0;  // images built in this warp's work slot so far
+    float* lane_ring = reinterpret_cast<float*>(x_ring) + qw * (G::kXRingSlots * MP * kSlabK) +
+                       b * 32 + 4 * q;
+    uint32_t copy_entry = 0, use_entry = 0;
+    auto copy_ahead = [&]() {
+      if (copy_i < count) {
+        const int block = copy_slab * kSlabBlocks + b;
+        if (block < p.nb) {
+          float* entry = lane_ring + copy_entry * (MP * kSlabK);
 #pragma unroll
-      for (int m = 0; m < MP; ++m) {
-        lo[m] = hi[m] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (valid && m < p.m) {
-          const float* src = p.x + static_cast<long long>(m) * p.ldx + block * 32 + 4 * q;
-          if (p.x_vector != 0) {
-            lo[m] = __ldg(reinterpret_cast<const float4*>(src));
-            hi[m] = __ldg(reinterpret_cast<const float4*>(src + 16));
-          } else {  // activations not on a 16-byte boundary
-            lo[m] = make_float4(__ldg(src), __ldg(src + 1), __ldg(src + 2), __ldg(src + 3));
-            hi[m] = make_float4(__ldg(src + 16), __ldg(src + 17), __ldg(src + 18), __ldg(src + 19));
+          for (int m = 0; m < MP; ++m) {
+            if (m < p.m) {
+              const float* src = p.x + static_cast<long long>(m) * p.ldx + block * 32 + 4 * q;
+              if (p.x_vector != 0) {
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(
+                                 smem_u32(entry + m * kSlabK)),
+                             "l"(src)
+                             : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(
+                                 smem_u32(entry + m * kSlabK + 16)),
+                             "l"(src + 16)
+                             : "memory");
+              } else {  // activations not on a 16-byte boundary
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  entry[m * kSlabK + e] = __ldg(src + e);
+                  entry[m * kSlabK + 16 + e] = __ldg(src + 16 + e);
+                }
+              }
+            }
           }
         }
+        copy_slab += step;
+        if (copy_slab >= p.slabs) copy_slab -= p.slabs;
+        copy_i += kW;
+        copy_entry = copy_entry + 1 == G::kXRingSlots ? 0 : copy_entry + 1;
       }
+      asm volatile("cp.async.commit_group;" ::: "memory");  // one group per call, even if empty
     };
+    int digit_offset[MP][4];
+#pragma unroll
+    for (int m = 0; m < MP; ++m) {
+#pragma unroll
+      for (int d = 0; d < 4; ++d) {
+        const int row = ((b % G::kG) * MP + m) * 4 + d;
+        digit_offset[m][d] =
+            kQ4 ? row * 128 + ((b ^ (row & 7)) << 4) + 4 * q
+                : (b >> 2) * (G::kN * 128) + row * 128 + (((2 * (b & 3)) ^ (row & 7)) << 4) + 4 * q;
+      }
+    }
+    uint8_t* digits = work_ring + qw * G::kWorkBytes + G::kHBytes;
     // the activations may be the output of the kernel in front of this one
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (lane == 0) QX_PROF_STAMP(12);
-    if (count > 0) fetch(xslab);
-    for (int i = 0; i < count; ++i) {
+    if (lane == 0 && qw == 0) QX_PROF_STAMP(12);
+    QX_PROF_DECL(w_free);
+    QX_PROF_DECL(c_image);
+    const long long t_q0 = QX_PROF_NOW();
+    for (int k = 0; k < kAhead; ++k) copy_ahead();
+    for (int i = qw; i < count; i += kW) {
+      copy_ahead();
+      // all but the newest kAhead groups have landed: slab i's values are in the ring
+      asm volatile("cp.async.wait_group %0;" ::"n"(kAhead) : "memory");
       float4 cur_lo[MP], cur_hi[MP];
+      const bool cur_valid = use_slab * kSlabBlocks + b < p.nb;
+      const float* entry = lane_ring + use_entry * (MP * kSlabK);
 #pragma unroll
       for (int m = 0; m < MP; ++m) {
-        cur_lo[m] = lo[m];
-        cur_hi[m] = hi[m];
-      }
-      const bool cur_valid = valid;
-      xslab = xslab + 1 == p.slabs ? 0 : xslab + 1;
-      if (i + 1 < count) fetch(xslab);
-      if (i >= G::kWorkSlots) {  // the work slot's previous image has been consumed
-        if (!mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag)) {
-          ok = false;
-          break;
+        cur_lo[m] = cur_hi[m] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (cur_valid && m < p.m) {
+          cur_lo[m] = *reinterpret_cast<const float4*>(entry + m * kSlabK);
+          cur_hi[m] = *reinterpret_cast<const float4*>(entry + m * kSlabK + 16);
         }
-        freed.advance(G::kSlots);
       }
-      write_slab_image<FMT, MP>(work_ring + work_slot * G::kWorkBytes + G::kHBytes, cur_lo, cur_hi,
-                                cur_valid, lane);
+      use_slab += step;
+      if (use_slab >= p.slabs) use_slab -= p.slabs;
+      use_entry = use_entry + 1 == G::kXRingSlots ? 0 : use_entry + 1;
+      // The MMAs of this work slot's previous slab have read its digits. The weights of slab
+      // i have landed in their slot, so the slab that used the slot (and its constants)
+      // before is done; the wait on mma_done made sure this is not an older phase.
+      if ((slot_uses > 0 &&
+           !QX_PROF_WAIT(w_free, mbar_wait(&bars->mma_done[qw], (slot_uses - 1u) & 1u, abort_flag))) ||
+          !QX_PROF_WAIT(w_free, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) {
+        ok = false;
+        break;
+      }
+      {
+        QX_PROF_BEGIN();
+        write_slab_image<FMT, MP>(digits,
+                                  reinterpret_cast<XConst*>(const_ring + raw.slot * G::kConstBytes),
+                                  digit_offset, cur_lo, cur_hi, cur_valid, lane);
+        QX_PROF_END(c_image);
+      }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->x_full[work_slot]);
-      if (++work_slot == G::kWorkSlots) work_slot = 0;
+      if (lane == 0) {
+        mbar_arrive(&bars->x_full[qw]);
+        mbar_arrive(&bars->const_full[raw.slot]);
+      }
+      raw.advance_by(kW, G::kSlots);
+      ++slot_uses;
+    }
+    if (lane == 0 && qw == 0) {
+      QX_PROF_STORE(18, w_free);
+      QX_PROF_STORE(19, QX_PROF_NOW() - t_q0);
+      QX_PROF_STORE(22, c_image);
     }
     if (!ok) {
       *abort_flag = 1;
@@ -783,7 +878,8 @@ template <int FMT, int MP>
 constexpr size_t gemv_smem_bytes() {
   return 1024 + static_cast<size_t>(TcGeom<FMT, MP>::kSlots) * TcGeom<FMT, MP>::kWBytes +
          static_cast<size_t>(TcGeom<FMT, MP>::kWorkSlots) * TcGeom<FMT, MP>::kWorkBytes +
-         sizeof(GemvBarriers<FMT, MP>) + 64;
+         (TcGeom<FMT, MP>::kFused ? TcGeom<FMT, MP>::kSlots * TcGeom<FMT, MP>::kConstBytes : 0) +
+         TcGeom<FMT, MP>::kXRingBytes + sizeof(GemvBarriers<FMT, MP>) + 64;
 }
 
 template <int FMT, int MP>
