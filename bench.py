@@ -318,8 +318,8 @@ def run_qx_arm(args):
                      "frac": per_launch_gbs / hbm_peak, "traffic": None,
                      "peak_source": f"{peak_kind} HBM copy bandwidth",
                      "frac_of_nominal_8TBs": per_launch_gbs / 8000.0,
-                     "note": "achieved = algorithmic bytes / whole step time (activation "
-                             "quantizer launch and launch gaps included)"},
+                     "note": "achieved = algorithmic bytes / whole step time (one kernel per "
+                             "step; launch gaps included)"},
     }
     if world == 1 and not args.no_extra:
         line["cpu_baseline"] = cpu_baseline(wl, c)

@@ -48,6 +48,20 @@ __device__ __forceinline__ void block_envelope(const float (&v)[32], float* scal
                    : __uint_as_float(0x7FC00000u);       // NaN/inf in -> NaN out
 }
 
+// One block of activations (16-byte loads when the row allows them).
+__device__ __forceinline__ void load_block(const float* src, int x_vector, float (&v)[32]) {
+  if (x_vector != 0) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float4 f = __ldg(reinterpret_cast<const float4*>(src) + i);
+      v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __ldg(src + i);
+  }
+}
+
 // ------------------------------------------------------------------------------------
 // Activation digits: x[m][k] f32 -> one image per K-slab (layout: qx_gemv.cuh). The first
 // `chunk_threads` threads write one 16-byte chunk of a digit row each (zeros outside the
@@ -57,7 +71,8 @@ __device__ __forceinline__ void block_envelope(const float (&v)[32], float* scal
 template <int FMT>
 __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict__ x,
                                                          uint8_t* __restrict__ ximg, int m, int mp,
-                                                         int k, int nb, long long chunk_threads,
+                                                         int k, int nb, int x_vector,
+                                                         long long chunk_threads,
                                                          long long total_threads) {
   // let the GEMV kernel behind this one start its set-up and weight pipeline right away
   asm volatile("griddepcontrol.launch_dependents;");
@@ -80,9 +95,7 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
     const bool active = (j % group) == klass && row < m && b < nb && digit_used;
     uint4 out = make_uint4(0u, 0u, 0u, 0u);
     if (active) {
-      const float* src = x + static_cast<long long>(row) * k + b * 32;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = src[i];
+      load_block(x + static_cast<long long>(row) * k + b * 32, x_vector, v);
       float scale_up, scale;
       bool finite;
       block_envelope(v, &scale_up, &scale, &finite);
@@ -117,9 +130,7 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
     c.scale = 0.0f;
     c.k_lo = c.k_hi = c.pad = 0;
     if (row < m && b < nb) {
-      const float* src = x + static_cast<long long>(row) * k + b * 32;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) v[i] = src[i];
+      load_block(x + static_cast<long long>(row) * k + b * 32, x_vector, v);
       float scale_up;
       bool finite;
       block_envelope(v, &scale_up, &c.scale, &finite);
@@ -206,7 +217,9 @@ __global__ void __launch_bounds__(256) gemv_dp4a_kernel(
       }
       const float d = half_bits_to_float(
           *reinterpret_cast<const unsigned short*>(span + panel_scale_offset(FMT, r, j)));
-      v = __fmul_rn(block_sum(s[0], s[1], s[2], s[3], c.k_lo, c.k_hi), __fmul_rn(d, c.scale));
+      const float sum = FMT == QX_FORMAT_Q8_0 ? block_sum(s[0], s[1], s[2])
+                                              : block_sum(s[0], s[1], s[2], s[3], c.k_lo, c.k_hi);
+      v = __fmul_rn(sum, __fmul_rn(d, c.scale));
     }
     acc += warp_tree_sum(v);
   }
@@ -240,12 +253,13 @@ qx_status launch_quantizer(const qx_weights* w, const float* x_dev, uint8_t* xim
   config.attrs = &attribute;
   config.numAttrs = programmatic ? 1 : 0;
   const int k = static_cast<int>(w->columns), nb = static_cast<int>(w->blocks_per_row);
+  const int x_vector = reinterpret_cast<uintptr_t>(x_dev) % 16 == 0 ? 1 : 0;
   if (w->format == QX_FORMAT_Q8_0) {
     QX_CUDA_TRY(cudaLaunchKernelEx(&config, quantize_x_kernel<QX_FORMAT_Q8_0>, x_dev, ximg, m, mp, k,
-                                   nb, chunk_threads, total_threads));
+                                   nb, x_vector, chunk_threads, total_threads));
   } else {
     QX_CUDA_TRY(cudaLaunchKernelEx(&config, quantize_x_kernel<QX_FORMAT_Q4_0>, x_dev, ximg, m, mp, k,
-                                   nb, chunk_threads, total_threads));
+                                   nb, x_vector, chunk_threads, total_threads));
   }
   count_launch();
   return QX_STATUS_OK;

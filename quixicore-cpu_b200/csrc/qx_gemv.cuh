@@ -118,13 +118,23 @@ __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
   return d;
 }
 
-// 65536*v + u rounded to f32 (|u|, |v| < 2^29).
-__device__ __forceinline__ float combine_digits(int u, int v) {
-  return fmaf((float)v, 65536.0f, (float)u);
+// int -> f32 for |s| < 2^22 without the conversion unit (an integer add and a float
+// subtract: the int lands in the mantissa of 1.5 * 2^23). Exact.
+__device__ __forceinline__ float small_int_to_float(int s) {
+  return __int_as_float(s + 0x4B400000) - 12582912.0f;
 }
-// One block's term from its four digit sums: f32(2^24*s3 + 65536*s2 + 256*s1 + s0 - k).
+// One block's term from its digit sums (each |s_d| < 2^21): 65536*s2 + 256*s1 + s0 (q8_0) or
+// 2^24*s3 + 65536*s2 + 256*s1 + s0 - (65536*k_hi + k_lo) (q4_0), rounded to f32 as
+// RN(65536*hi + RN(lo)) with lo = 256*s1 + s0 - k_lo and hi = 256*s3 + s2 - k_hi
+// (|hi| < 2^24 is exact).
+__device__ __forceinline__ float block_sum(int s0, int s1, int s2) {
+  return fmaf(small_int_to_float(s2), 65536.0f,
+              fmaf(small_int_to_float(s1), 256.0f, small_int_to_float(s0)));
+}
 __device__ __forceinline__ float block_sum(int s0, int s1, int s2, int s3, int k_lo, int k_hi) {
-  return combine_digits(s1 * 256 + s0 - k_lo, s3 * 256 + s2 - k_hi);
+  const float lo = fmaf(small_int_to_float(s1), 256.0f, small_int_to_float(s0 - k_lo));
+  const float hi = fmaf(small_int_to_float(s3), 256.0f, small_int_to_float(s2 - k_hi));
+  return fmaf(hi, 65536.0f, lo);
 }
 
 // q4_0 block constants from sum = sum_j t_j (|sum| <= 2^27): 128 * sum split at bit 16

@@ -69,7 +69,7 @@ struct TcGeom {
   static constexpr int kGroups = kSlabBlocks / kG;     // accumulators per slab
   // Two rings in shared memory. Weight slots hold a slab's span of the panel as copied
   // (the bytes in flight: as many slots as fit). Work slots hold what exists only around
-  // the MMAs of a slab: the q4_0 high-nibble tile and the activation image.
+  // the MMAs of a slab: the q4_0 masked-byte tile and the digits built in the kernel.
   static constexpr int kWBytes = slab_span_bytes(FMT);   // 34 KiB | 18 KiB
   static constexpr int kScaleOffset = slab_code_bytes(FMT);
   static constexpr int kHBytes = kQ4 ? kTileRows * 128 : 0;
@@ -79,7 +79,10 @@ struct TcGeom {
   // one entry per weight slot, because they are needed longer (until the epilogue has
   // read them) than the operands of the MMAs.
   static constexpr int kConstBytes = 128 * MP;
-  static constexpr int kWorkBytes = (kHBytes + (kFused ? kBBytes : kXBytes) + 1023) / 1024 * 1024;
+  // Images that come from the quantizer kernel travel with the weights (copied as far
+  // ahead); images built in the kernel sit in the work slot.
+  static constexpr int kSlotBytes = kWBytes + (kFused ? 0 : (kXBytes + 1023) / 1024 * 1024);
+  static constexpr int kWorkBytes = (kHBytes + (kFused ? kBBytes : 0) + 1023) / 1024 * 1024;
   // ... and the activations of the next slabs wait in a small ring of their own (copied
   // there asynchronously a few slabs ahead: a load from L2 takes longer than a slab).
   static constexpr int kQuantWarps = 3;  // == kWorkSlots when the kernel quantizes itself
@@ -88,11 +91,11 @@ struct TcGeom {
   static constexpr int kBudget = kSmemLimit - 1024 - 2048 - (kFused ? 8 * kConstBytes : 0) -
                                  kXRingBytes;  // slack, barriers, constants, activation ring
   // three work slots unless that costs more than one weight slot
-  static constexpr int kWorkSlots = weight_slots_fit(kBudget, kWorkBytes, kWBytes, 3) + 1 >=
-                                            weight_slots_fit(kBudget, kWorkBytes, kWBytes, 2)
+  static constexpr int kWorkSlots = weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, 3) + 1 >=
+                                            weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, 2)
                                         ? 3
                                         : 2;
-  static constexpr int kSlots = weight_slots_fit(kBudget, kWorkBytes, kWBytes, kWorkSlots);
+  static constexpr int kSlots = weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, kWorkSlots);
   static constexpr int kTCols = kN;                    // TMEM columns per accumulator
   static constexpr int kTStages = 512 / kTCols > 16 ? 16 : 512 / kTCols;
   // Each epilogue set has its own ring of accumulators, so every TMEM barrier is used by
@@ -103,8 +106,7 @@ struct TcGeom {
   static constexpr int kThreads =
       32 * (2 + kEpilogueWarps + kUnpackWarps + (kFused ? kQuantWarps : 0));
   static constexpr int kLdCols = kN >= 64 ? 64 : 32;   // columns fetched per TMEM wait
-  static_assert(kSlots >= 2 && kSlots >= kWorkSlots && kTPerSet >= 1 && kN >= 32 && kN <= 256,
-                "geometry");
+  static_assert(kSlots >= 2 && kTPerSet >= 1 && kN >= 32 && kN <= 256, "geometry");
   static_assert(!kFused || kWorkSlots == kQuantWarps, "one quantizer warp per work slot");
   static_assert(kScaleOffset + kSlabScaleBytes == kWBytes && kWBytes % 1024 == 0, "span");
 };
@@ -270,7 +272,7 @@ gemv_tc_kernel(const GemvTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* work_ring = smem + G::kSlots * G::kWBytes;  // slot: [high nibbles (q4_0) | image]
+  uint8_t* work_ring = smem + G::kSlots * G::kSlotBytes;  // slot: [masked bytes (q4_0) | digits]
   // block constants of the slab in each weight slot (only when the kernel quantizes itself)
   uint8_t* const_ring = work_ring + G::kWorkSlots * G::kWorkBytes;
   uint8_t* x_ring = const_ring + (G::kFused ? G::kSlots * G::kConstBytes : 0);
@@ -290,7 +292,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       mbar_init(&bars->const_full[s], 1);
     }
     for (int s = 0; s < G::kWorkSlots; ++s) {
-      mbar_init(&bars->x_full[s], 1);  // expect_tx arrival, or the quantizer warp
+      mbar_init(&bars->x_full[s], 1);  // the slot's quantizer warp
       mbar_init(&bars->high_full[s], kQ4 ? G::kUnpackWarps : 1);
       mbar_init(&bars->mma_done[s], 1);
     }
@@ -334,56 +336,47 @@ gemv_tc_kernel(const GemvTcParams p) {
 
   if (warp == 0) {
     // ------------------------------ copy producer -----------------------------
-    // Slab i uses weight slot i mod kSlots and work slot i mod kWorkSlots; both are free
-    // again when slab i is done. The weights run kSlots slabs ahead, the images
-    // kWorkSlots: after slab i - kWorkSlots is done, the image of slab i and the weights
-    // of slab i + kSlots - kWorkSlots go into the slots it used.
+    // Slab i uses weight slot i mod kSlots, free again when slab i - kSlots is done.
     if (lane == 0) {
       bool ok = true;
       QX_PROF_DECL(w_empty);
+      constexpr uint32_t kTxBytes = G::kWBytes + (G::kFused ? 0 : G::kXBytes);
       const uint8_t* wsrc = p.panel + s_begin * G::kWBytes;
       int xslab = static_cast<int>(s_begin % p.slabs);
       // The weights do not depend on the kernel in front of this one: start the first
       // copies at once, and only then wait for the activation images.
       const int ahead = count < G::kSlots ? count : G::kSlots;
       for (int i = 0; i < ahead; ++i) {
-        mbar_arrive_expect_tx(&bars->raw_full[i], G::kWBytes);
-        bulk_copy_g2s(smem + i * G::kWBytes, wsrc, G::kWBytes, &bars->raw_full[i]);
+        mbar_arrive_expect_tx(&bars->raw_full[i], kTxBytes);
+        bulk_copy_g2s(smem + i * G::kSlotBytes, wsrc, G::kWBytes, &bars->raw_full[i]);
         wsrc += G::kWBytes;
       }
       if (!G::kFused) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         QX_PROF_STAMP(12);
-        for (int i = 0; i < G::kWorkSlots && i < count; ++i) {
-          mbar_arrive_expect_tx(&bars->x_full[i], G::kXBytes);
-          bulk_copy_g2s(work_ring + i * G::kWorkBytes + G::kHBytes,
+        for (int i = 0; i < ahead; ++i) {
+          bulk_copy_g2s(smem + i * G::kSlotBytes + G::kWBytes,
                         p.ximg + static_cast<long long>(xslab) * G::kXBytes, G::kXBytes,
-                        &bars->x_full[i]);
+                        &bars->raw_full[i]);
           xslab = xslab + 1 == p.slabs ? 0 : xslab + 1;
         }
       }
-      RingPos freed;           // slab i - kWorkSlots in the weight ring
-      uint32_t work_slot = 0;  // i mod kWorkSlots
-      for (int i = G::kWorkSlots; i < count; ++i) {
-        if (G::kFused && i + G::kSlots - G::kWorkSlots >= count) break;  // no more weights
+      RingPos freed;  // slab i - kSlots
+      for (int i = G::kSlots; i < count; ++i) {
         if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag))) {
           ok = false;
           break;
         }
+        uint8_t* slot = smem + freed.slot * G::kSlotBytes;
+        mbar_arrive_expect_tx(&bars->raw_full[freed.slot], kTxBytes);
+        bulk_copy_g2s(slot, wsrc, G::kWBytes, &bars->raw_full[freed.slot]);
+        wsrc += G::kWBytes;
         if (!G::kFused) {
-          mbar_arrive_expect_tx(&bars->x_full[work_slot], G::kXBytes);
-          bulk_copy_g2s(work_ring + work_slot * G::kWorkBytes + G::kHBytes,
-                        p.ximg + static_cast<long long>(xslab) * G::kXBytes, G::kXBytes,
-                        &bars->x_full[work_slot]);
+          bulk_copy_g2s(slot + G::kWBytes, p.ximg + static_cast<long long>(xslab) * G::kXBytes,
+                        G::kXBytes, &bars->raw_full[freed.slot]);
           xslab = xslab + 1 == p.slabs ? 0 : xslab + 1;
         }
-        if (i + G::kSlots - G::kWorkSlots < count) {
-          mbar_arrive_expect_tx(&bars->raw_full[freed.slot], G::kWBytes);
-          bulk_copy_g2s(smem + freed.slot * G::kWBytes, wsrc, G::kWBytes, &bars->raw_full[freed.slot]);
-          wsrc += G::kWBytes;
-        }
         freed.advance(G::kSlots);
-        if (++work_slot == G::kWorkSlots) work_slot = 0;
       }
       QX_PROF_STORE(0, w_empty);
       if (!ok) {
@@ -414,15 +407,16 @@ gemv_tc_kernel(const GemvTcParams p) {
           ok = false;
           break;
         }
-        if (!QX_PROF_WAIT(w_x, mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag))) {
+        if (G::kFused &&
+            !QX_PROF_WAIT(w_x, mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag))) {
           ok = false;
           gave_up = 15;
           break;
         }
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(smem + raw.slot * G::kWBytes);
+        const uint32_t sa = smem_u32(smem + raw.slot * G::kSlotBytes);
         const uint32_t sw = smem_u32(work_ring + work.slot * G::kWorkBytes);
-        const uint32_t sb = sw + G::kHBytes;  // digit rows
+        const uint32_t sb = G::kFused ? sw + G::kHBytes : sa + G::kWBytes;  // digit rows
 #pragma unroll
         for (int g = 0; g < G::kGroups; ++g) {
           const uint32_t pos = eset != 0u ? pos1 : pos0;
@@ -484,7 +478,7 @@ gemv_tc_kernel(const GemvTcParams p) {
           }
         }
         if (!ok) break;
-        if (G::kFused) tc_commit(&bars->mma_done[work.slot]);
+        tc_commit(&bars->mma_done[work.slot]);
         tc_commit(&bars->done[raw.slot]);
         raw.advance(G::kSlots);
         work.advance(G::kWorkSlots);
@@ -556,10 +550,10 @@ gemv_tc_kernel(const GemvTcParams p) {
     for (int i = 0; i < count && ok; ++i) {
       const bool mine = (unit & 1) == eset;
       if (mine) {
-        const uint8_t* raw_base = smem + raw.slot * G::kWBytes;
+        const uint8_t* raw_base = smem + raw.slot * G::kSlotBytes;
         const int4* xcs = reinterpret_cast<const int4*>(
             G::kFused ? const_ring + raw.slot * G::kConstBytes
-                      : work_ring + work.slot * G::kWorkBytes + G::kHBytes + G::kBBytes);
+                      : raw_base + G::kWBytes + G::kBBytes);
         uint32_t scw[4] = {0u, 0u, 0u, 0u};  // this row's eight fp16 block scales
 #pragma unroll
         for (int g = 0; g < G::kGroups; ++g) {
@@ -576,8 +570,7 @@ gemv_tc_kernel(const GemvTcParams p) {
             // (the in-kernel quantizer's work slot may already hold a later slab: its
             // constants have a barrier with the lifetime of the weight slot)
             if (!mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag) ||
-                !(G::kFused ? mbar_wait(&bars->const_full[raw.slot], raw.phase, abort_flag)
-                            : mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag))) {
+                (G::kFused && !mbar_wait(&bars->const_full[raw.slot], raw.phase, abort_flag))) {
               ok = false;
               break;
             }
@@ -611,7 +604,7 @@ gemv_tc_kernel(const GemvTcParams p) {
                 const int s2 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 2) & 31]);
                 const int s3 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 3) & 31]);
                 const float sum = kQ4 ? block_sum(s0, s1, s2, s3, xc.y, xc.z)
-                                      : combine_digits(s1 * 256 + s0, s2);
+                                      : block_sum(s0, s1, s2);
                 const float d = half_bits_to_float(
                     static_cast<unsigned short>((scw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
                 acc[m] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[m]);
@@ -694,23 +687,19 @@ gemv_tc_kernel(const GemvTcParams p) {
     QX_PROF_DECL(w_raw);
     QX_PROF_DECL(w_slot);
     const long long t_u0 = QX_PROF_NOW();
-    RingPos raw, work, freed;  // freed: slab i - kWorkSlots in the weight ring
+    RingPos raw, work;
     for (int i = 0; i < count; ++i) {
       if (!QX_PROF_WAIT(w_raw, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) {
         ok = false;
         break;
       }
       if (i >= G::kWorkSlots) {  // the work slot's previous tile has been consumed
-        const bool free_now = QX_PROF_WAIT(
-            w_slot, G::kFused ? mbar_wait(&bars->mma_done[work.slot], work.phase ^ 1u, abort_flag)
-                              : mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag));
-        if (!free_now) {
+        if (!QX_PROF_WAIT(w_slot, mbar_wait(&bars->mma_done[work.slot], work.phase ^ 1u, abort_flag))) {
           ok = false;
           break;
         }
-        freed.advance(G::kSlots);
       }
-      const uint4* packed = reinterpret_cast<const uint4*>(smem + raw.slot * G::kWBytes) + u * 256;
+      const uint4* packed = reinterpret_cast<const uint4*>(smem + raw.slot * G::kSlotBytes) + u * 256;
       uint4* high = reinterpret_cast<uint4*>(work_ring + work.slot * G::kWorkBytes) + u * 256;
       uint4 w[8];
 #pragma unroll
@@ -876,7 +865,7 @@ gemv_tc_kernel(const GemvTcParams p) {
 
 template <int FMT, int MP>
 constexpr size_t gemv_smem_bytes() {
-  return 1024 + static_cast<size_t>(TcGeom<FMT, MP>::kSlots) * TcGeom<FMT, MP>::kWBytes +
+  return 1024 + static_cast<size_t>(TcGeom<FMT, MP>::kSlots) * TcGeom<FMT, MP>::kSlotBytes +
          static_cast<size_t>(TcGeom<FMT, MP>::kWorkSlots) * TcGeom<FMT, MP>::kWorkBytes +
          (TcGeom<FMT, MP>::kFused ? TcGeom<FMT, MP>::kSlots * TcGeom<FMT, MP>::kConstBytes : 0) +
          TcGeom<FMT, MP>::kXRingBytes + sizeof(GemvBarriers<FMT, MP>) + 64;
