@@ -173,7 +173,7 @@ QX_API qx_status qx_qgemm_prepacked_bf16_dev(const qx_weights* weights, const ui
  * do it at load time); x_dev [columns] and y_dev [rows] are device pointers.
  *
  * Limits and rules:
- *  - the matrix must fit the array: about rows * min(32, columns/256) * 4 bytes <= 5 MiB
+ *  - the matrix must fit the array: about rows * min(16, columns/256) * 4 bytes <= 5 MiB
  *    (every benchmark shape fits, e.g. 28672 x 8192); larger ones are rejected with
  *    QX_STATUS_INVALID_SHAPE and a message from qx_last_error_string();
  *  - the first call on a device looks up the array's device address (no allocation, but a

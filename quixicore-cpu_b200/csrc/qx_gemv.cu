@@ -390,7 +390,7 @@ extern "C" qx_status qx_qgemv_prepacked_noalloc_dev(const qx_weights* weights, c
   if (error_offset + 256 > kNoAllocScratchBytes) {
     set_last_error_text(
         "qgemv (no-alloc): this weight matrix needs more scratch than the 6 MiB static array "
-        "(limit is about rows * min(32, columns/256) * 4 B <= 5 MiB; use qx_qgemm_prepacked_dev)");
+        "(limit is about rows * min(16, columns/256) * 4 B <= 5 MiB; use qx_qgemm_prepacked_dev)");
     return QX_STATUS_INVALID_SHAPE;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);

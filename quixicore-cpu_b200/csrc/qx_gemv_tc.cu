@@ -96,7 +96,14 @@ struct TcGeom {
                                         ? 3
                                         : 2;
   static constexpr int kSlots = weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, kWorkSlots);
-  static constexpr int kTCols = kN;                    // TMEM columns per accumulator
+  // One TMEM stage (the unit handed from the MMA issuer to an epilogue set) holds several
+  // accumulators when they are narrow: up to 128 columns for small batches (a whole slab
+  // per hand-over), 64 for larger ones (more stages in flight matter more there).
+  static constexpr int kStageTarget = MP <= 8 ? 128 : 64;
+  static constexpr int kGroupsPerStage =
+      kN >= kStageTarget ? 1 : (kStageTarget / kN < kGroups ? kStageTarget / kN : kGroups);
+  static constexpr int kStagesPerSlab = kGroups / kGroupsPerStage;
+  static constexpr int kTCols = kN * kGroupsPerStage;  // TMEM columns per stage
   static constexpr int kTStages = 512 / kTCols > 16 ? 16 : 512 / kTCols;
   // Each epilogue set has its own ring of accumulators, so every TMEM barrier is used by
   // one set only (a parity wait cannot tell apart phases two steps apart).
@@ -105,7 +112,8 @@ struct TcGeom {
   static constexpr int kQuantWarp = 2 + kEpilogueWarps + kUnpackWarps;  // fused only
   static constexpr int kThreads =
       32 * (2 + kEpilogueWarps + kUnpackWarps + (kFused ? kQuantWarps : 0));
-  static constexpr int kLdCols = kN >= 64 ? 64 : 32;   // columns fetched per TMEM wait
+  static constexpr int kLdCols = kTCols >= 64 ? 64 : 32;   // columns fetched per TMEM wait
+  static constexpr bool kRollGroups = MP >= 8;
   static_assert(kSlots >= 2 && kTPerSet >= 1 && kN >= 32 && kN <= 256, "geometry");
   static_assert(!kFused || kWorkSlots == kQuantWarps, "one quantizer warp per work slot");
   static_assert(kScaleOffset + kSlabScaleBytes == kWBytes && kWBytes % 1024 == 0, "span");
@@ -422,13 +430,15 @@ gemv_tc_kernel(const GemvTcParams p) {
           const uint32_t pos = eset != 0u ? pos1 : pos0;
           const uint32_t par = eset != 0u ? par1 : par0;
           const uint32_t ts = eset * G::kTPerSet + pos;
-          if (!QX_PROF_WAIT(w_tempty, mbar_wait(&bars->tmem_empty[ts], par ^ 1u, abort_flag))) {
-            ok = false;
-            gave_up = 16;
-            break;
+          if (g % G::kGroupsPerStage == 0) {
+            if (!QX_PROF_WAIT(w_tempty, mbar_wait(&bars->tmem_empty[ts], par ^ 1u, abort_flag))) {
+              ok = false;
+              gave_up = 16;
+              break;
+            }
+            tc_fence_after_sync();
           }
-          tc_fence_after_sync();
-          const uint32_t d_tmem = tmem_base + ts * G::kTCols;
+          const uint32_t d_tmem = tmem_base + ts * G::kTCols + (g % G::kGroupsPerStage) * G::kN;
           if (!kQ4) {
             // one MMA per block: 32 code bytes inside the swizzle atom = +2 in (addr >> 4)
 #pragma unroll
@@ -466,15 +476,17 @@ gemv_tc_kernel(const GemvTcParams p) {
               mma_i8_ss(d_tmem, a_high + k, b_high + k, idesc, 1u);
             }
           }
-          tc_commit(&bars->tmem_full[ts]);
-          const uint32_t next = pos + 1 == G::kTPerSet ? 0u : pos + 1;
-          const uint32_t flip = pos + 1 == G::kTPerSet ? 1u : 0u;
-          if (eset != 0u) {
-            pos1 = next;
-            par1 ^= flip;
-          } else {
-            pos0 = next;
-            par0 ^= flip;
+          if (g % G::kGroupsPerStage == G::kGroupsPerStage - 1) {
+            tc_commit(&bars->tmem_full[ts]);
+            const uint32_t next = pos + 1 == G::kTPerSet ? 0u : pos + 1;
+            const uint32_t flip = pos + 1 == G::kTPerSet ? 1u : 0u;
+            if (eset != 0u) {
+              pos1 = next;
+              par1 ^= flip;
+            } else {
+              pos0 = next;
+              par0 ^= flip;
+            }
           }
         }
         if (!ok) break;
@@ -521,18 +533,23 @@ gemv_tc_kernel(const GemvTcParams p) {
         const float* slots = p.partial +
                              static_cast<long long>(pend_tile) * p.units_per_tile * p.m * kTileRows +
                              row_in_tile;
+        for (int m = 0; m < p.m; ++m) {
+          // units_per_tile <= 16: fetch all unit sums first (independent loads), then add
+          // the even and the odd ones in ascending order
+          float v[16];
 #pragma unroll
-        for (int m = 0; m < MP; ++m) {
-          if (m < p.m) {
-            float even = 0.0f, odd = 0.0f;
-            for (int u = 0; u < p.units_per_tile; u += 2) {
-              even += __ldcg(slots + (static_cast<long long>(u) * p.m + m) * kTileRows);
-            }
-            for (int u = 1; u < p.units_per_tile; u += 2) {
-              odd += __ldcg(slots + (static_cast<long long>(u) * p.m + m) * kTileRows);
-            }
-            if (row < p.rows) p.y[m * p.ldy + row] = even + odd;
+          for (int u = 0; u < 16; ++u) {
+            v[u] = u < p.units_per_tile
+                       ? __ldcg(slots + (static_cast<long long>(u) * p.m + m) * kTileRows)
+                       : 0.0f;
           }
+          float even = 0.0f, odd = 0.0f;
+#pragma unroll
+          for (int u = 0; u < 16; u += 2) {
+            if (u < p.units_per_tile) even += v[u];
+            if (u + 1 < p.units_per_tile) odd += v[u + 1];
+          }
+          if (row < p.rows) p.y[m * p.ldy + row] = even + odd;
         }
         p.counters[static_cast<long long>(pend_tile) * kTileRows + row_in_tile] = 0;  // next launch
       }
@@ -555,16 +572,18 @@ gemv_tc_kernel(const GemvTcParams p) {
             G::kFused ? const_ring + raw.slot * G::kConstBytes
                       : raw_base + G::kWBytes + G::kBBytes);
         uint32_t scw[4] = {0u, 0u, 0u, 0u};  // this row's eight fp16 block scales
-#pragma unroll
-        for (int g = 0; g < G::kGroups; ++g) {
+        // (large batches keep the loop over accumulators rolled: unrolled, the loop body
+        // would not fit the instruction cache)
+#pragma unroll(G::kRollGroups ? 1 : G::kStagesPerSlab)
+        for (int st = 0; st < G::kStagesPerSlab; ++st) {
           const uint32_t ts = eset * G::kTPerSet + ring_pos;
           if (!QX_PROF_WAIT(w_tfull, mbar_wait(&bars->tmem_full[ts], tphase, abort_flag))) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          if (i == 0 && g == 0 && epi_thread == 0) QX_PROF_STAMP(13);
-          if (g == 0) {
+          if (i == 0 && st == 0 && epi_thread == 0) QX_PROF_STAMP(13);
+          if (st == 0) {
             // these barriers completed before the MMAs ran; waiting on them here makes the
             // copied scales and the block constants visible to this thread
             // (the in-kernel quantizer's work slot may already hold a later slab: its
@@ -574,19 +593,21 @@ gemv_tc_kernel(const GemvTcParams p) {
               ok = false;
               break;
             }
-            const uint4 s4 = *reinterpret_cast<const uint4*>(raw_base + G::kScaleOffset +
-                                                             row_in_tile * (kSlabBlocks * 2));
-            scw[0] = s4.x; scw[1] = s4.y; scw[2] = s4.z; scw[3] = s4.w;
+            if (!G::kRollGroups) {
+              const uint4 s4 = *reinterpret_cast<const uint4*>(raw_base + G::kScaleOffset +
+                                                               row_in_tile * (kSlabBlocks * 2));
+              scw[0] = s4.x; scw[1] = s4.y; scw[2] = s4.z; scw[3] = s4.w;
+            }
           }
 #pragma unroll
-          for (int c0 = 0; c0 < G::kN; c0 += G::kLdCols) {
+          for (int c0 = 0; c0 < G::kTCols; c0 += G::kLdCols) {
             uint32_t v[G::kLdCols / 32][32];
             const uint32_t taddr = tmem_base + ts * G::kTCols + c0 +
                                    (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
             for (int h = 0; h < G::kLdCols / 32; ++h) tmem_ld_32x32(taddr + 32 * h, v[h]);
             tmem_ld_wait();
-            if (c0 + G::kLdCols == G::kN) {  // all values in registers: hand the accumulator back
+            if (c0 + G::kLdCols == G::kTCols) {  // all values in registers: hand the stage back
               tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) mbar_arrive(&bars->tmem_empty[ts]);
@@ -594,9 +615,10 @@ gemv_tc_kernel(const GemvTcParams p) {
 #pragma unroll
             for (int q = 0; q < G::kLdCols / 4; ++q) {
               // columns 4*idx .. 4*idx+3: the four digit sums of (block class, activation row)
-              const int idx = c0 / 4 + q;
+              const int column = c0 + 4 * q;  // in the stage: accumulator, then (class, row)
+              const int idx = (column % G::kN) / 4;
               const int m = idx % MP;
-              const int j = g * G::kG + idx / MP;
+              const int j = (st * G::kGroupsPerStage + column / G::kN) * G::kG + idx / MP;
               if (m < p.m) {
                 const int4 xc = xcs[j * MP + m];  // {scale, k_lo, k_hi, -}
                 const int s0 = static_cast<int>(v[(4 * q) >> 5][(4 * q) & 31]);
@@ -606,7 +628,10 @@ gemv_tc_kernel(const GemvTcParams p) {
                 const float sum = kQ4 ? block_sum(s0, s1, s2, s3, xc.y, xc.z)
                                       : block_sum(s0, s1, s2);
                 const float d = half_bits_to_float(
-                    static_cast<unsigned short>((scw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
+                    G::kRollGroups
+                        ? *reinterpret_cast<const unsigned short*>(
+                              raw_base + G::kScaleOffset + (row_in_tile * kSlabBlocks + j) * 2)
+                        : static_cast<unsigned short>((scw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
                 acc[m] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[m]);
               }
             }
@@ -935,8 +960,8 @@ long long* gemv_profile_buffer() {
 #endif
 }
 
-// K split: units of U slabs with at most 32 units per row; a function of K alone.
-static int unit_slabs_for(long long slabs) { return static_cast<int>((slabs + 31) / 32); }
+// K split: units of U slabs with at most 16 units per row; a function of K alone.
+static int unit_slabs_for(long long slabs) { return static_cast<int>((slabs + 15) / 16); }
 
 qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScratch* out) {
   if (w->tiles > kMaxCounterTiles) {

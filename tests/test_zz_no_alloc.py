@@ -47,7 +47,7 @@ def test_no_alloc_matches_regular_entry_twice(qx, orc, wl, fmt, n, k):
 
 def test_no_alloc_rejects_oversized_matrix(qx, wl):
     import torch
-    fmt, n, k = 1, 65536, 8192  # needs 65536 * 32 * 4 B = 8 MiB of unit sums
+    fmt, n, k = 1, 131072, 4096  # needs 131072 * 16 * 4 B = 8 MiB of unit sums
     packed = np.zeros(n * (k // 32) * 18, np.uint8)
     weights = qx.PackedWeights()
     assert weights.prepare(fmt, packed, n, k) == qx.OK, qx.last_error()
