@@ -246,12 +246,22 @@ def run_qx_arm(args):
     graph = None
     chunk = GRAPH_CHUNK - GRAPH_CHUNK % copies or copies
     if world == 1 and args.steps >= chunk and not args.no_graph:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for i in range(chunk):
-                step(i)
-        graph.replay()
-        torch.cuda.synchronize()
+        # The steps are captured once and replayed, so the host's launch cost stays out of the
+        # timed region. Sharded runs launch step by step: a graph that also held the NCCL
+        # all-gathers did not make progress on two GPUs (both ranks stopped inside the first
+        # replay), so that combination is not used.
+        try:
+            captured = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(captured):
+                for i in range(chunk):
+                    step(i)
+            captured.replay()
+            torch.cuda.synchronize()
+            graph = captured
+        except Exception as exc:  # fall back to plain launches
+            print(f"bench: graph capture failed ({exc!r}); timing plain launches", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
 
     if world > 1:
         dist.barrier()
