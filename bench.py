@@ -334,7 +334,7 @@ def run_qx_arm(args):
     if world == 1 and not args.no_extra:
         line["cpu_baseline"] = cpu_baseline(wl, c)
         try:
-            line["extra"] = extra_measurements(qx, wl, torch, hbm_peak)
+            line["extra"] = extra_measurements(qx, wl, torch, hbm_peak, bf16_peak)
         except Exception as exc:  # the headline line must still be printed
             line["extra"] = {"error": repr(exc)}
     print(json.dumps(line), flush=True)
@@ -374,7 +374,7 @@ def _time_calls(torch, fn, iters, warm=3):
     return a.elapsed_time(b) / (3 * iters) * 1e-3
 
 
-def extra_measurements(qx, wl, torch, hbm_peak):
+def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak):
     """The other benchmark configurations on one GPU (not the headline; explanatory)."""
     out = {}
     # cfg2: W8A8 prefill GEMM, TOPS (three weight copies = 176 MB, rotated, so W comes from HBM)
@@ -423,6 +423,20 @@ def extra_measurements(qx, wl, torch, hbm_peak):
     out["cfg3_q8_0_batched"] = sweep
     for h in pair:
         h.reset()
+    # cfg4: 4-bit prefill GEMM, q4_0 weights x bf16 activations (operands far larger than L2)
+    c = wl.CONFIGS["cfg4_q4_0_prefill"]
+    fmt, n, k, m = c["fmt"], c["n"], c["k"], c["m"]
+    h = qx.PackedWeights()
+    qx.check(h.prepare(fmt, wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0), n, k), "prep")
+    xb = wl.to_bf16_bits(wl.activations_f32(m, k, seed=4))
+    xd = torch.from_numpy(xb.view(np.int16)).cuda()
+    yd = torch.zeros((m, n), device="cuda")
+    sec = _time_calls(torch, lambda i: qx.check(h.qgemm_bf16_dev(xd, yd, m), "prefill"), 5, 1)
+    tflops = 2.0 * m * n * k / sec / 1e12
+    out["cfg4_q4_0_prefill"] = {"tflops": tflops, "ms": sec * 1e3,
+                                "frac_of_measured_bf16": tflops / bf16_peak if bf16_peak else None,
+                                "note": "includes the activation staging pre-pass"}
+    h.reset()
     return out
 
 

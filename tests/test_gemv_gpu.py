@@ -162,9 +162,11 @@ def test_device_pointer_entry_with_row_stride(qx, orc, wl):
     assert np.all(got[:, n:] == -7.0), "wrote outside its slice"
 
 
-def test_bf16_activation_entry(qx, orc, wl):
+def test_bf16_activation_entry_small_batch(qx, orc, wl):
+    """Below 64 rows the bf16 entry widens to f32 and takes the digit kernels (f32-path
+    tolerance); the tensor-core prefill kernel has its own tests."""
     import torch
-    fmt, n, k, m = Q4_0, 256, 1024, 80
+    fmt, n, k, m = Q4_0, 256, 1024, 24
     packed = wl.packed_blocks(fmt, n, k, *DIST[fmt], seed=13)
     xb = wl.to_bf16_bits(wl.activations_f32(m, k, seed=13))
     weights = qx.PackedWeights()
@@ -174,8 +176,4 @@ def test_bf16_activation_entry(qx, orc, wl):
     assert weights.qgemm_bf16_dev(x_dev, y, m) == qx.OK, qx.last_error()
     torch.cuda.synchronize()
     _, ref = orc.qgemm(fmt, packed, wl.bf16_bits_to_f32(xb), m, n, k)
-    # stated tolerance of the 4-bit prefill GEMM: 1e-2 relative, with an absolute floor of
-    # 1e-2 of the row's rms for outputs near zero
-    got = y.cpu().numpy()
-    floor = 1e-2 * np.sqrt((ref.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
-    assert np.all(np.abs(got - ref) <= 1e-2 * np.abs(ref) + floor)
+    assert_close_f32_path(y.cpu().numpy(), ref, "bf16 entry, small batch")
