@@ -374,8 +374,25 @@ def _time_calls(torch, fn, iters, warm=3):
     return a.elapsed_time(b) / (3 * iters) * 1e-3
 
 
-def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak):
-    """The other benchmark configurations on one GPU (not the headline; explanatory)."""
+EXTRA_CASES = ("cfg2_w8a8_gemm", "cfg0_q8_0_gemv", "cfg3_q8_0_batched", "cfg4_q4_0_prefill")
+
+
+def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak, only=None):
+    """The other benchmark configurations on one GPU (not the headline; explanatory). `only`
+    names a single one of EXTRA_CASES (profiling runs)."""
+    out = {}
+    if only in (None, "cfg2_w8a8_gemm"):
+        out.update(_extra_cfg2(qx, wl, torch))
+    if only in (None, "cfg0_q8_0_gemv"):
+        out.update(_extra_cfg0(qx, wl, torch, hbm_peak))
+    if only in (None, "cfg3_q8_0_batched"):
+        out.update(_extra_cfg3(qx, wl, torch, hbm_peak))
+    if only in (None, "cfg4_q4_0_prefill"):
+        out.update(_extra_cfg4(qx, wl, torch, bf16_peak))
+    return out
+
+
+def _extra_cfg2(qx, wl, torch):
     out = {}
     # cfg2: W8A8 prefill GEMM, TOPS (three weight copies = 176 MB, rotated, so W comes from HBM)
     c = wl.CONFIGS["cfg2_w8a8_gemm"]
@@ -389,7 +406,11 @@ def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak):
     out["cfg2_w8a8_gemm"] = {"tops": 2.0 * m * n * k / sec / 1e12, "us": sec * 1e6,
                              "frac_of_nominal_4500_tops": 2.0 * m * n * k / sec / 4.5e15,
                              "variant": qx.variants()["int8_gemm"]}
-    del w_copies, y
+    return out
+
+
+def _extra_cfg0(qx, wl, torch, hbm_peak):
+    out = {}
     # cfg0: q8_0 GEMV 4096x4096 (16 rotating copies = 285 MB > L2)
     c = wl.CONFIGS["cfg0_q8_0_gemv"]
     fmt, n, k = c["fmt"], c["n"], c["k"]
@@ -405,6 +426,11 @@ def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak):
     out["cfg0_q8_0_gemv"] = {"gbs": gbs, "us": sec * 1e6, "frac_of_measured_hbm": gbs / hbm_peak}
     for h in handles:
         h.reset()
+    return out
+
+
+def _extra_cfg3(qx, wl, torch, hbm_peak):
+    out = {}
     # cfg3: batched q8_0 GEMV, two copies of the 240 MB weights alternate (> L2), M sweep
     c = wl.CONFIGS["cfg3_q8_0_batched"]
     fmt, n, k = c["fmt"], c["n"], c["k"]
@@ -423,6 +449,11 @@ def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak):
     out["cfg3_q8_0_batched"] = sweep
     for h in pair:
         h.reset()
+    return out
+
+
+def _extra_cfg4(qx, wl, torch, bf16_peak):
+    out = {}
     # cfg4: 4-bit prefill GEMM, q4_0 weights x bf16 activations (operands far larger than L2)
     c = wl.CONFIGS["cfg4_q4_0_prefill"]
     fmt, n, k, m = c["fmt"], c["n"], c["k"], c["m"]
@@ -449,10 +480,19 @@ def main():
     parser.add_argument("--no-extra", action="store_true",
                         help="skip the non-headline configurations and the CPU baseline (profiling runs)")
     parser.add_argument("--no-graph", action="store_true", help="launch every step eagerly")
+    parser.add_argument("--extra-only", choices=EXTRA_CASES, default=None,
+                        help="run just this non-headline configuration and print its figures "
+                             "(profiling runs)")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "qx" else args.warmup
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.extra_only is not None:
+        import torch
+        torch.cuda.set_device(0)
+        hbm_peak, bf16_peak, _ = measured_peaks()
+        print(json.dumps(extra_measurements(entry.load_package(), load_workloads(), torch, hbm_peak,
+                                            bf16_peak, only=args.extra_only)), flush=True)
     else:
         run_qx_arm(args)
 
