@@ -103,3 +103,28 @@ def test_device_scale_check_and_stride(qx, wl):
     want = ((x.astype(np.int64) @ w.astype(np.int64).T).astype(np.float32) * ws[None, :]) * xs[:, None]
     assert_bit_equal(got[:, :n], want)
     assert np.all(got[:, n:] == 3.0)
+
+
+@pytest.mark.parametrize("shape,asym", [((512, 1024, 4096), False), ((300, 640, 2048), True),
+                                        ((96, 2048, 1024), False)])
+def test_stream_k_split_is_exact(qx, orc, wl, shape, asym, monkeypatch):
+    """With the K-slab sequence cut into one contiguous range per SM, tiles are finished from
+    int32 partial sums of several CTAs: same exact accumulators and f32 bits as whole tiles,
+    and stable over repeated launches (the tile counters return to zero)."""
+    m, n, k = shape
+    w, x, ws, xs = wl.w8a8_inputs(m, n, k, seed=m + n)
+    rng = np.random.default_rng(7)
+    row_sum = w.astype(np.int64).sum(axis=1).astype(np.int32)
+    zp = rng.integers(-20, 21, m).astype(np.int32)
+    results = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("QX_B200_INT8_STREAM_K", mode)
+        for _ in range(2):
+            status, y = qx.int8_gemm(w, x, ws, xs, m, n, k, row_sum if asym else None,
+                                     zp if asym else None, asym)
+            assert status == qx.OK, qx.last_error()
+            results.setdefault(mode, []).append(y)
+    _, ref, _ = orc.int8_gemm(w, x, ws, xs, m, n, k, row_sum, zp, asym)
+    for mode, ys in results.items():
+        for y in ys:
+            assert_bit_equal(y, ref, f"stream_k={mode} {shape} asym={asym}")
