@@ -325,7 +325,7 @@ def run_qx_arm(args):
                 "d2h_bytes_per_step": 4 * n, "steps": e2e_steps},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": per_launch_gbs, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": per_launch_gbs / hbm_peak, "traffic": None,
+                     "frac": per_launch_gbs / hbm_peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
                      "peak_source": f"{peak_kind} HBM copy bandwidth",
                      "frac_of_nominal_8TBs": per_launch_gbs / 8000.0,
                      "note": "achieved = algorithmic bytes / whole step time (one kernel per "
@@ -373,6 +373,11 @@ def _time_calls(torch, fn, iters, warm=3):
     torch.cuda.synchronize()
     return a.elapsed_time(b) / (3 * iters) * 1e-3
 
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_tc_kernel launch on the headline
+# workload, from the ncu capture summarised in profiles/gemv_tc_q4_0_cfg1.md (algorithmic
+# bytes: 33 103 872)
+NCU_DRAM_BYTES_PER_LAUNCH = 33157632
 
 EXTRA_CASES = ("cfg2_w8a8_gemm", "cfg0_q8_0_gemv", "cfg3_q8_0_batched", "cfg4_q4_0_prefill")
 
