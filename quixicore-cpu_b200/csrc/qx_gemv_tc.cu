@@ -47,8 +47,6 @@ namespace {
 
 using namespace sm100;
 
-constexpr int kEpilogueWarps = 8;   // two sets of four (one warp per TMEM lane quarter)
-constexpr int kFirstUnpackWarp = 2 + kEpilogueWarps;
 constexpr int kSmemLimit = 227 * 1024;
 
 // weight slots (at most 8) that fit beside `work_slots` work slots
@@ -90,11 +88,14 @@ struct TcGeom {
   static constexpr int kXRingBytes = kFused ? kQuantWarps * kXRingSlots * MP * kSlabK * 4 : 0;
   static constexpr int kBudget = kSmemLimit - 1024 - 2048 - (kFused ? 8 * kConstBytes : 0) -
                                  kXRingBytes;  // slack, barriers, constants, activation ring
-  // three work slots unless that costs more than one weight slot
-  static constexpr int kWorkSlots = weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, 3) + 1 >=
-                                            weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, 2)
-                                        ? 3
-                                        : 2;
+  // the in-kernel quantizer has one work slot per quantizer warp; otherwise three work slots
+  // unless that costs more than one weight slot
+  static constexpr int kWorkSlots =
+      kFused ? kQuantWarps
+             : (weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, 3) + 1 >=
+                        weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, 2)
+                    ? 3
+                    : 2);
   static constexpr int kSlots = weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, kWorkSlots);
   // One TMEM stage (the unit handed from the MMA issuer to an epilogue set) holds several
   // accumulators when they are narrow: up to 128 columns for small batches (a whole slab
@@ -108,11 +109,20 @@ struct TcGeom {
   // Each epilogue set has its own ring of accumulators, so every TMEM barrier is used by
   // one set only (a parity wait cannot tell apart phases two steps apart).
   static constexpr int kTPerSet = kTStages / 2;
+  // Epilogue: two sets (alternate K units) of four warps (one per TMEM lane quarter); q8_0
+  // batches of 16 double that, the two warps of a quarter taking half of the activation rows
+  // each (the epilogue's instruction count bounds big batches; at 32 rows the extra warps
+  // cost more registers than they bring).
+  static constexpr int kEpiSplit = (MP == 16 && !kQ4) ? 2 : 1;
+  static constexpr int kEpiWarps = 8 * kEpiSplit;
+  static constexpr int kRowsPerThread = MP / kEpiSplit;  // activation rows per epilogue thread
   static constexpr int kUnpackWarps = kQ4 ? 4 : 0;
-  static constexpr int kQuantWarp = 2 + kEpilogueWarps + kUnpackWarps;  // fused only
-  static constexpr int kThreads =
-      32 * (2 + kEpilogueWarps + kUnpackWarps + (kFused ? kQuantWarps : 0));
-  static constexpr int kLdCols = kTCols >= 64 ? 64 : 32;   // columns fetched per TMEM wait
+  static constexpr int kFirstUnpackWarp = 2 + kEpiWarps;
+  static constexpr int kQuantWarp = kFirstUnpackWarp + kUnpackWarps;  // fused only
+  static constexpr int kThreads = 32 * (2 + kEpiWarps + kUnpackWarps + (kFused ? kQuantWarps : 0));
+  static constexpr int kColsPerWarp = kTCols / kEpiSplit;  // a warp's share of a stage
+  static constexpr int kLdCols = kColsPerWarp >= 64 ? 64 : 32;  // columns fetched per TMEM wait
+  static_assert(kEpiSplit == 1 || (kGroupsPerStage == 1 && kG == 1), "split stages hold one block");
   static constexpr bool kRollGroups = MP >= 8;
   static_assert(kSlots >= 2 && kTPerSet >= 1 && kN >= 32 && kN <= 256, "geometry");
   static_assert(!kFused || kWorkSlots == kQuantWarps, "one quantizer warp per work slot");
@@ -138,7 +148,7 @@ struct GemvTcParams {
 template <int FMT, int MP>
 struct __align__(8) GemvBarriers {
   uint64_t raw_full[TcGeom<FMT, MP>::kSlots];    // the slab's span landed in its weight slot
-  uint64_t done[TcGeom<FMT, MP>::kSlots];        // MMAs done + scales / constants consumed
+  uint64_t done[TcGeom<FMT, MP>::kSlots];        // the slab's epilogue is through (so are its MMAs)
   uint64_t x_full[TcGeom<FMT, MP>::kWorkSlots];  // activation image in the work slot
   uint64_t high_full[TcGeom<FMT, MP>::kWorkSlots];  // q4_0: high-nibble tile written
   uint64_t mma_done[TcGeom<FMT, MP>::kWorkSlots];   // the slab's MMAs have read the work slot
@@ -296,7 +306,8 @@ gemv_tc_kernel(const GemvTcParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < G::kSlots; ++s) {
       mbar_init(&bars->raw_full[s], 1);  // the producer's expect_tx arrival
-      mbar_init(&bars->done[s], 1 + 4);  // MMA commit + four epilogue warps
+      // one epilogue set: it has seen the slab's last accumulator, so the MMAs are done too
+      mbar_init(&bars->done[s], 4 * G::kEpiSplit);
       mbar_init(&bars->const_full[s], 1);
     }
     for (int s = 0; s < G::kWorkSlots; ++s) {
@@ -306,7 +317,7 @@ gemv_tc_kernel(const GemvTcParams p) {
     }
     for (int t = 0; t < G::kTStages; ++t) {
       mbar_init(&bars->tmem_full[t], 1);
-      mbar_init(&bars->tmem_empty[t], 4);
+      mbar_init(&bars->tmem_empty[t], 4 * G::kEpiSplit);
     }
     bars->abort_flag = 0;
     mbar_fence_init();
@@ -491,7 +502,6 @@ gemv_tc_kernel(const GemvTcParams p) {
         }
         if (!ok) break;
         tc_commit(&bars->mma_done[work.slot]);
-        tc_commit(&bars->done[raw.slot]);
         raw.advance(G::kSlots);
         work.advance(G::kWorkSlots);
         if (++slab == p.slabs) {
@@ -512,22 +522,24 @@ gemv_tc_kernel(const GemvTcParams p) {
         atomicCAS(p.error, 0, gave_up);
       }
     }
-  } else if (warp < 2 + kEpilogueWarps) {
+  } else if (warp < 2 + G::kEpiWarps) {
     // ------------------------------ epilogue ----------------------------------
     // Two sets of four warps; set e takes the K units with (unit & 1) == e, so while one
     // set waits on barriers, TMEM loads and conversions the other one issues.
-    const int eset = (warp - 2) >> 2;
+    const int eset = (warp - 2) / (4 * G::kEpiSplit);
+    const int split = ((warp - 2) >> 2) % G::kEpiSplit;  // which share of the activation rows
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are this warp's
+    constexpr int kMine = G::kRowsPerThread;
     const int row_in_tile = quarter * 32 + lane;
     const int epi_thread = threadIdx.x - 64;
-    float acc[MP];  // current unit
+    float acc[kMine];  // current unit, activation rows split * kMine ..
 #pragma unroll
-    for (int m = 0; m < MP; ++m) acc[m] = 0.0f;
+    for (int m = 0; m < kMine; ++m) acc[m] = 0.0f;
     int units_mine = 0;  // units of the current tile this thread has written
     // deferred completion check of the last counted share
     int pend_old = 0, pend_add = 0, pend_tile = 0;
     auto resolve_pending = [&]() {
-      if (pend_add > 0 && pend_old + pend_add == p.units_per_tile) {
+      if (pend_add > 0 && pend_old + pend_add == p.units_per_tile * G::kEpiSplit) {
         // this thread completed the row: add its unit sums in the fixed order
         const long long row = static_cast<long long>(pend_tile) * kTileRows + row_in_tile;
         const float* slots = p.partial +
@@ -600,14 +612,14 @@ gemv_tc_kernel(const GemvTcParams p) {
             }
           }
 #pragma unroll
-          for (int c0 = 0; c0 < G::kTCols; c0 += G::kLdCols) {
+          for (int c0 = 0; c0 < G::kColsPerWarp; c0 += G::kLdCols) {
             uint32_t v[G::kLdCols / 32][32];
-            const uint32_t taddr = tmem_base + ts * G::kTCols + c0 +
+            const uint32_t taddr = tmem_base + ts * G::kTCols + split * G::kColsPerWarp + c0 +
                                    (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
             for (int h = 0; h < G::kLdCols / 32; ++h) tmem_ld_32x32(taddr + 32 * h, v[h]);
             tmem_ld_wait();
-            if (c0 + G::kLdCols == G::kTCols) {  // all values in registers: hand the stage back
+            if (c0 + G::kLdCols == G::kColsPerWarp) {  // all values in registers: hand the stage back
               tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) mbar_arrive(&bars->tmem_empty[ts]);
@@ -615,10 +627,13 @@ gemv_tc_kernel(const GemvTcParams p) {
 #pragma unroll
             for (int q = 0; q < G::kLdCols / 4; ++q) {
               // columns 4*idx .. 4*idx+3: the four digit sums of (block class, activation row)
-              const int column = c0 + 4 * q;  // in the stage: accumulator, then (class, row)
+              // column in this warp's share of the stage: accumulator, then (class, row)
+              const int column = c0 + 4 * q;
               const int idx = (column % G::kN) / 4;
-              const int m = idx % MP;
-              const int j = (st * G::kGroupsPerStage + column / G::kN) * G::kG + idx / MP;
+              const int lm = G::kEpiSplit == 1 ? idx % MP : idx;  // row within this thread's share
+              const int m = split * kMine + lm;
+              const int j = (st * G::kGroupsPerStage + column / G::kN) * G::kG +
+                            (G::kEpiSplit == 1 ? idx / MP : 0);
               if (m < p.m) {
                 const int4 xc = xcs[j * MP + m];  // {scale, k_lo, k_hi, -}
                 const int s0 = static_cast<int>(v[(4 * q) >> 5][(4 * q) & 31]);
@@ -632,7 +647,7 @@ gemv_tc_kernel(const GemvTcParams p) {
                         ? *reinterpret_cast<const unsigned short*>(
                               raw_base + G::kScaleOffset + (row_in_tile * kSlabBlocks + j) * 2)
                         : static_cast<unsigned short>((scw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
-                acc[m] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[m]);
+                acc[lm] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[lm]);
               }
             }
           }
@@ -656,9 +671,10 @@ gemv_tc_kernel(const GemvTcParams p) {
                         (static_cast<long long>(tile) * p.units_per_tile + unit) * p.m * kTileRows +
                         row_in_tile;
 #pragma unroll
-          for (int m = 0; m < MP; ++m) {
-            if (m < p.m) part[m * kTileRows] = acc[m];
-            acc[m] = 0.0f;
+          for (int lm = 0; lm < kMine; ++lm) {
+            const int m = split * kMine + lm;
+            if (m < p.m) part[m * kTileRows] = acc[lm];
+            acc[lm] = 0.0f;
           }
           ++units_mine;
         }
@@ -702,12 +718,12 @@ gemv_tc_kernel(const GemvTcParams p) {
       *abort_flag = 1;
       atomicExch(p.error, 13);
     }
-  } else if (kQ4 && warp < kFirstUnpackWarp + G::kUnpackWarps) {
+  } else if (kQ4 && warp < G::kFirstUnpackWarp + G::kUnpackWarps) {
     // ------------------------------ q4_0 high nibbles -------------------------
     // The raw tile is [128 rows][8 blocks x 16 bytes] with swizzled chunks; the tile of the
     // masked bytes (16 * high nibble) has the same layout, so the extraction is position by
     // position. The four warps take a quarter of every slab each.
-    const int u = warp - kFirstUnpackWarp;
+    const int u = warp - G::kFirstUnpackWarp;
     bool ok = true;
     QX_PROF_DECL(w_raw);
     QX_PROF_DECL(w_slot);
