@@ -227,7 +227,27 @@ def run_qx_arm(args):
     y_full = torch.zeros(world * n, device="cuda")
     y_local = y_full[rank * n:(rank + 1) * n]
 
+    # Sharded runs: every rank streams its own shard and the output slices are exchanged. The
+    # exchange is fused into the GEMV (peer stores from its epilogue + a wait kernel); if the
+    # peer mapping cannot be set up, NCCL's all-gather takes its place.
+    gather, exchange = None, "none"
+    if world > 1:
+        try:
+            sharded = entry._load_file(entry.PKG_NAME + ".sharded", os.path.join(entry.PKG_DIR, "sharded.py"))
+            gather = sharded.PushAllGather(qx, n, 1)
+            exchange = "peer stores fused into the GEMV epilogue + wait kernel"
+        except Exception as exc:
+            print(f"bench: fused all-gather unavailable ({exc!r}); using NCCL", file=sys.stderr)
+            gather, exchange = None, "nccl all_gather_into_tensor"
+        flags = torch.tensor([1 if gather is not None else 0], device="cuda")
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)  # all ranks take the same path
+        if int(flags.item()) == 0:
+            gather, exchange = None, "nccl all_gather_into_tensor"
+
     def step(i):
+        if gather is not None:
+            gather.step(handles[i % copies], x_dev, 1)
+            return
         qx.check(handles[i % copies].qgemm_dev(x_dev, y_local, 1, n), "qx_qgemm_prepacked_dev")
         if world > 1:
             dist.all_gather_into_tensor(y_full, y_local)
@@ -245,11 +265,12 @@ def run_qx_arm(args):
 
     graph = None
     chunk = GRAPH_CHUNK - GRAPH_CHUNK % copies or copies
-    if world == 1 and args.steps >= chunk and not args.no_graph:
+    chunk -= chunk % 2  # fused all-gather: the result buffers alternate step by step
+    if (world == 1 or gather is not None) and args.steps >= chunk and chunk > 0 and not args.no_graph:
         # The steps are captured once and replayed, so the host's launch cost stays out of the
-        # timed region. Sharded runs launch step by step: a graph that also held the NCCL
-        # all-gathers did not make progress on two GPUs (both ranks stopped inside the first
-        # replay), so that combination is not used.
+        # timed region. Sharded runs that fall back to NCCL launch step by step: a graph that
+        # also held the NCCL all-gathers did not make progress on two GPUs (both ranks stopped
+        # inside the first replay), so that combination is not used.
         try:
             captured = torch.cuda.CUDAGraph()
             with torch.cuda.graph(captured):
@@ -316,7 +337,7 @@ def run_qx_arm(args):
         "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": WORKLOAD, "m": 1, "n": n, "k": k, "format": "q4_0",
-                   "sharding": f"rows x{world}" if world > 1 else "none",
+                   "sharding": f"rows x{world}" if world > 1 else "none", "exchange": exchange,
                    "l2_policy": f"rotates {copies} distinct weight copies "
                                 f"({copies * n * (k // 32) * 18 / 1e6:.0f} MB > L2 {info['l2_bytes'] / 1e6:.0f} MB)",
                    "cuda_graph": graph is not None, "variants": qx.variants()},

@@ -159,6 +159,51 @@ QX_API qx_status qx_qgemm_prepacked_bf16_dev(const qx_weights* weights, const ui
                                       float* y_dev, long long m, long long ldy,
                                       qx_workspace* workspace, void* stream);
 
+/* ---- row-sharded decode with the all-gather fused into the GEMV -------------------------
+ * One process per GPU; rank r keeps a contiguous row range of W (qx_weights_prepare with
+ * row_begin / row_count) and every rank ends up with the full output, the semantics of
+ * all_gather in kernels/collectives/collectives_ref.cpp:26-37. No counterpart in the
+ * reference's quantized-matmul API (its row partition is over threads of one process).
+ *
+ * Instead of a collective after the GEMV, the kernel's row finishers store each result
+ * into every rank's result buffer over NVLink (plain peer stores) and the last CTA sets a
+ * per-rank "slice complete" word on every rank; qx_allgather_wait_dev enqueues a small
+ * kernel that waits (bounded, 2 s) until all slices of the step have arrived. Steps
+ * alternate between two result buffers (a rank may be one step ahead of a peer), and the
+ * step number is kept in device memory, so both calls can be captured in a CUDA graph.
+ *
+ * Buffers that other ranks write must be peer-mappable: allocate them with qx_peer_alloc,
+ * pass the 64-byte handle to the other processes (any channel) and map it there with
+ * qx_peer_open. Result buffer layout: [2 parities][world][m][rows_per_rank] floats
+ * (uniform shards); control block: qx_push_control_bytes() bytes, zero-initialised by
+ * qx_peer_alloc. */
+typedef struct qx_push_plan {
+  int world;                 /* ranks, 2..8 */
+  int rank;                  /* this rank */
+  long long rows_per_rank;   /* rows of every shard (the handle's row count) */
+  float* results_local;      /* this rank's result buffer (device pointer) */
+  void* control_local;       /* this rank's control block */
+  float* results_peer[8];    /* results_peer[r]: rank r's result buffer mapped here (r != rank) */
+  void* control_peer[8];     /* control_peer[r]: rank r's control block mapped here (r != rank) */
+} qx_push_plan;
+
+QX_API size_t qx_push_control_bytes(void);
+QX_API qx_status qx_peer_alloc(size_t bytes, void** dev_ptr, unsigned char handle[64]);
+QX_API qx_status qx_peer_open(const unsigned char handle[64], void** dev_ptr);
+QX_API qx_status qx_peer_close(void* dev_ptr);
+QX_API qx_status qx_peer_free(void* dev_ptr);
+/* y = x . dequant(W_shard)^T for m <= 32 activation rows, written to this rank's slice of
+ * the step's result buffer on every rank. Only enqueues. */
+QX_API qx_status qx_qgemm_prepacked_push_dev(const qx_weights* weights, const float* x_dev,
+                                             long long m, const qx_push_plan* plan,
+                                             qx_workspace* workspace, void* stream);
+/* Enqueues the wait for all ranks' slices of the next step in order; *results_dev (host
+ * variable, optional) receives the device address of that step's [world][m][rows_per_rank]
+ * results in this rank's buffer. A wait that runs out sets the error word reported by the
+ * next host-pointer call (QX_STATUS_DEVICE_ERROR, role code 31). */
+QX_API qx_status qx_allgather_wait_dev(const qx_push_plan* plan, long long m, long long step,
+                                       const float** results_dev, void* stream);
+
 /* Decode GEMV (m = 1) that never allocates device memory. No counterpart in the
  * reference (its scratch is ordinary host memory).
  *

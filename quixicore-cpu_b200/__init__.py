@@ -43,6 +43,13 @@ class WeightsInfo(C.Structure):
                 ("preparation_ns", C.c_uint64), ("device", C.c_int), ("has_dense_bf16", C.c_int)]
 
 
+class PushPlan(C.Structure):
+    """qx_push_plan of include/qx_b200.h."""
+    _fields_ = [("world", C.c_int), ("rank", C.c_int), ("rows_per_rank", C.c_longlong),
+                ("results_local", C.c_void_p), ("control_local", C.c_void_p),
+                ("results_peer", C.c_void_p * 8), ("control_peer", C.c_void_p * 8)]
+
+
 class DeviceInfo(C.Structure):
     _fields_ = [("device", C.c_int), ("sm_major", C.c_int), ("sm_minor", C.c_int),
                 ("sm_count", C.c_int), ("max_smem_per_block", C.c_int), ("l2_bytes", C.c_int),
@@ -77,6 +84,12 @@ def _load():
         "qx_int8_gemm_dev": [_vp] * 8 + [_ll, _ll, _ll, _ll, C.c_int, C.c_int, _vp],
         "qx_qgemm_w8a32": [_vp] * 4 + [_ll, _ll, _ll],
         "qx_qgemm_w8a32_dev": [_vp] * 4 + [_ll, _ll, _ll, _ll, C.c_int, _vp, _vp],
+        "qx_peer_alloc": [_sz, C.POINTER(_vp), _vp],
+        "qx_peer_open": [_vp, C.POINTER(_vp)],
+        "qx_peer_close": [_vp],
+        "qx_peer_free": [_vp],
+        "qx_qgemm_prepacked_push_dev": [_vp, _vp, _ll, C.POINTER(PushPlan), _vp, _vp],
+        "qx_allgather_wait_dev": [C.POINTER(PushPlan), _ll, _ll, C.POINTER(_vp), _vp],
     }
     for name, argtypes in sig.items():
         fn = getattr(lib, name)
@@ -96,6 +109,7 @@ def _load():
     lib.qx_set_num_threads.restype = None
     lib.qx_num_threads.restype = C.c_int
     lib.qx_kernel_launch_count.restype = C.c_ulonglong
+    lib.qx_push_control_bytes.restype = _sz
     return lib
 
 
@@ -257,6 +271,36 @@ class PackedWeights:
         ldy = y.shape[-1] if ldy is None else ldy
         return lib.qx_qgemm_prepacked_bf16_dev(self.handle, _dev(x_bf16), _vp(y.data_ptr()), m,
                                                ldy, None, _stream())
+
+
+def peer_alloc(nbytes: int):
+    """(device pointer, 64-byte handle) of a zeroed buffer other processes can map."""
+    ptr, handle = _vp(), C.create_string_buffer(64)
+    check(lib.qx_peer_alloc(nbytes, C.byref(ptr), handle), "qx_peer_alloc")
+    return ptr.value, handle.raw
+
+
+def peer_open(handle: bytes) -> int:
+    ptr = _vp()
+    check(lib.qx_peer_open(C.create_string_buffer(handle, 64), C.byref(ptr)), "qx_peer_open")
+    return ptr.value
+
+
+def push_control_bytes() -> int:
+    return lib.qx_push_control_bytes()
+
+
+def qgemm_push_dev(weights: "PackedWeights", x, m: int, plan: PushPlan) -> int:
+    """Sharded GEMV whose results land in every rank's buffer (fused all-gather)."""
+    return lib.qx_qgemm_prepacked_push_dev(weights.handle, _dev(x), m, C.byref(plan), None, _stream())
+
+
+def allgather_wait_dev(plan: PushPlan, m: int, step: int) -> int:
+    """Enqueues the wait for step `step`; returns the device address of its results."""
+    out = _vp()
+    check(lib.qx_allgather_wait_dev(C.byref(plan), m, step, C.byref(out), _stream()),
+          "qx_allgather_wait_dev")
+    return out.value
 
 
 def int8_gemm_dev(w, x, ws, xs, y, m, n, k, row_sum=None, zp=None, acc=None, ldy=None,

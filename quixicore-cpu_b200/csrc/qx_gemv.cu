@@ -273,7 +273,11 @@ const char* gemv_variant_name() { return force_dp4a() ? "sm100a_dp4a" : "sm100a_
 // partial sums]; sizes depend only on (m, k, rows).
 qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev,
                            long long m, long long ldy, qx_workspace* ws,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, const GemvPush* push) {
+  if (push != nullptr && (m > kGemvMaxBatch || force_dp4a())) {
+    set_last_error_text("qgemm: pushing launches take at most 32 activation rows (tensor-core kernel)");
+    return QX_STATUS_INVALID_SHAPE;
+  }
   if (w->columns > (1LL << 24) || w->rows > (1LL << 31) - 256) {
     set_last_error_text("qgemm: shape beyond the GEMV kernels' 32-bit tile indices");
     return QX_STATUS_INVALID_SHAPE;
@@ -293,7 +297,7 @@ qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev
     }
     float* y = y_dev + m0 * ldy;
     if (!force_dp4a()) {
-      QX_TRY(launch_gemv_tc(w, x, ximg, y, mc, ldy, base, scratch, stream));
+      QX_TRY(launch_gemv_tc(w, x, ximg, y, mc, ldy, base, scratch, stream, push));
     } else {
       const dim3 grid(static_cast<unsigned>((w->rows + 7) / 8), static_cast<unsigned>(mc));
       const int mp = padded_batch(mc), nb = static_cast<int>(w->blocks_per_row);

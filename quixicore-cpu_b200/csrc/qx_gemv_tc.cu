@@ -48,6 +48,7 @@ namespace {
 using namespace sm100;
 
 constexpr int kSmemLimit = 227 * 1024;
+constexpr int kMaxPushPeers = 7;
 
 // weight slots (at most 8) that fit beside `work_slots` work slots
 constexpr int weight_slots_fit(int budget, int work_bytes, int weight_bytes, int work_slots) {
@@ -142,6 +143,19 @@ struct GemvTcParams {
   int x_vector;                  // x and ldx allow 16-byte loads
   int unit_slabs, units_per_tile;  // K split: units of unit_slabs slabs
   long long total_units;
+  // Row-sharded runs (one process per GPU): the finished outputs are also stored straight
+  // into the other ranks' result buffers over NVLink, and the last CTA of the launch tells
+  // every rank that this rank's slice is complete (an all-gather fused into the epilogue).
+  // Steps alternate between two result buffers; the step number lives in device memory
+  // (push_count), so the same launch can be replayed from a CUDA graph.
+  int peers;                        // other ranks (0: no push)
+  int* push_count;                  // local: pushes completed so far; this launch is step + 1
+  float* y_odd;                     // local result buffer of odd steps (y: even steps)
+  float* y_peer[kMaxPushPeers];     // the other ranks' even-step buffers, at this rank's slice
+  float* y_peer_odd[kMaxPushPeers];
+  int* peer_flag[kMaxPushPeers];    // on the other ranks: this rank's "slice complete" word
+  int* own_flag;                    // this rank's own word for its slice
+  int* launch_counter;              // local, zero between launches: CTAs that are done
   long long* debug;  // [ctas][32] counters, profiling builds only
 };
 
@@ -535,6 +549,8 @@ gemv_tc_kernel(const GemvTcParams p) {
     float acc[kMine];  // current unit, activation rows split * kMine ..
 #pragma unroll
     for (int m = 0; m < kMine; ++m) acc[m] = 0.0f;
+    // pushing launches alternate between two result buffers by the parity of their step
+    const bool push_odd = p.peers > 0 && ((__ldcg(p.push_count) + 1) & 1) != 0;
     int units_mine = 0;  // units of the current tile this thread has written
     // deferred completion check of the last counted share
     int pend_old = 0, pend_add = 0, pend_tile = 0;
@@ -561,7 +577,12 @@ gemv_tc_kernel(const GemvTcParams p) {
             if (u < p.units_per_tile) even += v[u];
             if (u + 1 < p.units_per_tile) odd += v[u + 1];
           }
-          if (row < p.rows) p.y[m * p.ldy + row] = even + odd;
+          if (row < p.rows) {
+            const float value = even + odd;
+            const long long at = m * p.ldy + row;
+            (push_odd ? p.y_odd : p.y)[at] = value;
+            for (int r = 0; r < p.peers; ++r) (push_odd ? p.y_peer_odd[r] : p.y_peer[r])[at] = value;
+          }
         }
         p.counters[static_cast<long long>(pend_tile) * kTileRows + row_in_tile] = 0;  // next launch
       }
@@ -895,11 +916,27 @@ gemv_tc_kernel(const GemvTcParams p) {
     }
   }
 
+  if (p.peers > 0) __threadfence_system();  // this thread's stores to the other ranks
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
+  }
+  if (p.peers > 0 && threadIdx.x == 0) {
+    // the CTA that finishes last publishes "this rank's slice is complete" on every rank
+    __threadfence();
+    const int finished = atomicAdd(p.launch_counter, 1);
+    if (finished == static_cast<int>(gridDim.x) - 1) {
+      *p.launch_counter = 0;  // next launch
+      const int step = *p.push_count + 1;
+      *p.push_count = step;
+      __threadfence_system();
+      for (int r = 0; r < p.peers; ++r) {
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flag[r]), "r"(step) : "memory");
+      }
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.own_flag), "r"(step) : "memory");
+    }
   }
   if (threadIdx.x == 0) QX_PROF_STAMP(15);
 }
@@ -1003,15 +1040,15 @@ bool gemv_tc_quantizes_in_kernel(int m) { return padded_batch(m) <= 2; }
 
 qx_status launch_gemv_tc(const qx_weights* w, const float* x, const uint8_t* ximg, float* y, int m,
                          long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const GemvPush* push) {
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
-  return launch_gemv_tc_at(w, x, ximg, y, m, ldy, ws_base, scratch, ctx->flag + 1, stream);
+  return launch_gemv_tc_at(w, x, ximg, y, m, ldy, ws_base, scratch, ctx->flag + 1, stream, push);
 }
 
 qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* ximg, float* y,
                             int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                            int* error_word, cudaStream_t stream) {
+                            int* error_word, cudaStream_t stream, const GemvPush* push) {
   GemvTcParams p{};
   p.panel = w->panel;
   p.ximg = ximg;
@@ -1031,6 +1068,22 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
   p.unit_slabs = scratch.unit_slabs;
   p.units_per_tile = scratch.units_per_tile;
   p.total_units = w->tiles * scratch.units_per_tile;
+  if (push != nullptr && push->peers > 0) {
+    if (push->peers > kMaxPushPeers) {
+      set_last_error_text("gemv: more than 7 peer ranks");
+      return QX_STATUS_INVALID_ARGUMENT;
+    }
+    p.peers = push->peers;
+    p.push_count = push->push_count;
+    p.y_odd = push->y_odd;
+    for (int r = 0; r < push->peers; ++r) {
+      p.y_peer[r] = push->y_peer[r];
+      p.y_peer_odd[r] = push->y_peer_odd[r];
+      p.peer_flag[r] = push->peer_flag[r];
+    }
+    p.own_flag = push->own_flag;
+    p.launch_counter = push->launch_counter;
+  }
   p.debug = gemv_profile_buffer();
   if (w->format == QX_FORMAT_Q8_0) {
     return launch_fmt<QX_FORMAT_Q8_0>(padded_batch(m), p, scratch.ctas, stream);

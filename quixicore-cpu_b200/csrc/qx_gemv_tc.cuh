@@ -22,6 +22,21 @@ struct GemvScratch {
 // between launches); the rest is laid out per call.
 qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScratch* out);
 
+// Row-sharded runs: where the kernel also stores its results on the other ranks
+// (peer-mapped device pointers, already offset to this rank's slice; two buffers that
+// alternate step by step) and the words it sets to the step number on every rank once the
+// whole slice is written. The step number is kept in device memory (push_count).
+struct GemvPush {
+  int peers = 0;
+  int* push_count = nullptr;      // device word: pushes completed so far
+  float* y_odd = nullptr;         // local buffer of odd steps (the y argument: even steps)
+  float* y_peer[7] = {};
+  float* y_peer_odd[7] = {};
+  int* peer_flag[7] = {};
+  int* own_flag = nullptr;
+  int* launch_counter = nullptr;  // device word, zero between launches
+};
+
 // Batches of one or two activation rows are quantized inside the GEMV kernel (it reads x);
 // larger ones need the slab images written by the quantizer kernel first (qx_gemv.cu).
 bool gemv_tc_quantizes_in_kernel(int m);
@@ -30,13 +45,13 @@ bool gemv_tc_quantizes_in_kernel(int m);
 // quantizes itself)
 qx_status launch_gemv_tc(const qx_weights* w, const float* x, const uint8_t* ximg, float* y, int m,
                          long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                         cudaStream_t stream);
+                         cudaStream_t stream, const GemvPush* push = nullptr);
 
 // Same, with the device word that receives a non-zero role code when a bounded wait gives
 // up passed in by the caller instead of taken from the per-device context.
 qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* ximg, float* y,
                             int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                            int* error_word, cudaStream_t stream);
+                            int* error_word, cudaStream_t stream, const GemvPush* push = nullptr);
 
 const char* gemv_variant_name();
 

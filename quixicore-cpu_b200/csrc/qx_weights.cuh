@@ -53,8 +53,10 @@ namespace qx {
 qx_status launch_relayout(const qx_weights* w, const uint8_t* src, cudaStream_t stream);
 
 // y[m][ldy] (+ row offset already applied by the caller) = x[m][k] . dequant(W)^T
+// `push` (qx_gemv_tc.cuh): also store the results on the other ranks (m <= 32 only).
+struct GemvPush;
 qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev,
                            long long m, long long ldy, qx_workspace* ws,
-                           cudaStream_t stream);
+                           cudaStream_t stream, const GemvPush* push = nullptr);
 
 }  // namespace qx
