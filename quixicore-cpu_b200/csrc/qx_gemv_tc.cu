@@ -549,14 +549,16 @@ gemv_tc_kernel(const GemvTcParams p) {
     float acc[kMine];  // current unit, activation rows split * kMine ..
 #pragma unroll
     for (int m = 0; m < kMine; ++m) acc[m] = 0.0f;
-    // pushing launches alternate between two result buffers by the parity of their step
-    const bool push_odd = p.peers > 0 && ((__ldcg(p.push_count) + 1) & 1) != 0;
     int units_mine = 0;  // units of the current tile this thread has written
     // deferred completion check of the last counted share
     int pend_old = 0, pend_add = 0, pend_tile = 0;
     auto resolve_pending = [&]() {
       if (pend_add > 0 && pend_old + pend_add == p.units_per_tile * G::kEpiSplit) {
         // this thread completed the row: add its unit sums in the fixed order
+        // (pushing launches alternate between two result buffers by the parity of their
+        // step; the counter is read here, after data has flowed through the pipeline, i.e.
+        // after the launch in front of this one has completed and advanced it)
+        const bool push_odd = p.peers > 0 && ((__ldcg(p.push_count) + 1) & 1) != 0;
         const long long row = static_cast<long long>(pend_tile) * kTileRows + row_in_tile;
         const float* slots = p.partial +
                              static_cast<long long>(pend_tile) * p.units_per_tile * p.m * kTileRows +
@@ -916,7 +918,6 @@ gemv_tc_kernel(const GemvTcParams p) {
     }
   }
 
-  if (p.peers > 0) __threadfence_system();  // this thread's stores to the other ranks
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {
@@ -924,7 +925,10 @@ gemv_tc_kernel(const GemvTcParams p) {
     tmem_dealloc(tmem_base, 512);
   }
   if (p.peers > 0 && threadIdx.x == 0) {
-    // the CTA that finishes last publishes "this rank's slice is complete" on every rank
+    // The CTA that finishes last publishes "this rank's slice is complete" on every rank.
+    // Ordering of the result stores before that word: the storing threads -> the barrier
+    // above -> this thread's fence and counter update (device scope) -> the last CTA's
+    // system-scope fence and release stores; the waiting rank acquires the word.
     __threadfence();
     const int finished = atomicAdd(p.launch_counter, 1);
     if (finished == static_cast<int>(gridDim.x) - 1) {

@@ -20,6 +20,11 @@ constexpr size_t kControlBytes = 256;
 // Lane r waits until rank r's slice of the next step has arrived (bounded), then lane 0
 // advances the local wait counter.
 __global__ void __launch_bounds__(32) allgather_wait_kernel(int* control, int world, int* error) {
+  // Launched programmatically: it may start while the GEMV in front of it still runs (it only
+  // polls), and the kernel behind it may start its own set-up at once; whatever that kernel
+  // reads of the gathered results it guards with griddepcontrol.wait, which returns when
+  // this kernel has finished.
+  asm volatile("griddepcontrol.launch_dependents;");
   const int lane = threadIdx.x;
   const int expected = control[kWaitCountWord] + 1;
   bool ok = true;
@@ -163,8 +168,17 @@ qx_status qx_allgather_wait_dev(const qx_push_plan* plan, long long m, long long
   if (m <= 0 || step <= 0) return QX_STATUS_INVALID_ARGUMENT;
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
-  allgather_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<int*>(plan->control_local), plan->world, ctx->flag + 1);
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(1);
+  config.blockDim = dim3(32);
+  config.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  QX_CUDA_TRY(cudaLaunchKernelEx(&config, allgather_wait_kernel, static_cast<int*>(plan->control_local),
+                                 plan->world, ctx->flag + 1));
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
   if (results_dev != nullptr) {
