@@ -239,7 +239,28 @@ def run_qx_arm(args):
         except Exception as exc:
             print(f"bench: fused all-gather unavailable ({exc!r}); using NCCL", file=sys.stderr)
             gather, exchange = None, "nccl all_gather_into_tensor"
-        flags = torch.tensor([1 if gather is not None else 0], device="cuda")
+        healthy = 1 if gather is not None else 0
+        if gather is not None:
+            # two trial steps: this rank's slice of the gathered result must equal its own GEMV
+            # bit for bit, and no kernel may have given up a wait (a tiny host-pointer call
+            # reports that)
+            try:
+                want = torch.zeros(n, device="cuda")
+                for trial in range(2):
+                    qx.check(handles[trial].qgemm_dev(x_dev, want, 1, n), "trial gemv")
+                    got_ptr = gather.step(handles[trial], x_dev, 1)
+                    torch.cuda.synchronize()
+                    got = _device_floats(torch, got_ptr + 4 * rank * n, n)
+                    if not torch.equal(got.view(torch.int32), want.view(torch.int32)):
+                        healthy = 0
+                tiny = wl.packed_blocks(fmt, 32, 32, c["d_lo"], c["d_hi"], seed=1)
+                status, _ = qx.qgemv(fmt, tiny, wl.activations_f32(1, 32)[0], 32, 32)
+                if status != qx.OK:
+                    healthy = 0
+            except Exception as exc:
+                print(f"bench: fused all-gather trial failed ({exc!r}); using NCCL", file=sys.stderr)
+                healthy = 0
+        flags = torch.tensor([healthy], device="cuda")
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)  # all ranks take the same path
         if int(flags.item()) == 0:
             gather, exchange = None, "nccl all_gather_into_tensor"
@@ -343,7 +364,10 @@ def run_qx_arm(args):
                    "cuda_graph": graph is not None, "variants": qx.variants()},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k,
-                "d2h_bytes_per_step": 4 * n, "steps": e2e_steps},
+                "d2h_bytes_per_step": 4 * n, "steps": e2e_steps,
+                "note": "host-pointer C entry point per step: x copied from pinned host memory, y "
+                        "written by the kernel into the caller's pinned host buffer, then one "
+                        "stream synchronisation"},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": {"bound": "hbm", "achieved": per_launch_gbs, "peak": hbm_peak, "unit": "GB/s",
                      "frac": per_launch_gbs / hbm_peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
@@ -372,6 +396,17 @@ def cpu_baseline(wl, c):
     return {"value": wl.algorithmic_bytes_qgemv(fmt, 1, n, k) / seconds / 1e9, "unit": "GB/s",
             "cores": threads, "kind": kind, "ms_per_call": seconds * 1e3,
             "sample": f"median of {calls} full-size qgemv calls ({n}x{k} q4_0)", "variants": variants}
+
+
+def _device_floats(torch, address: int, count: int):
+    """`count` floats at a raw device address, copied into a torch tensor."""
+    import ctypes
+    out = torch.empty(count, dtype=torch.float32, device="cuda")
+    cudart = ctypes.CDLL("libcudart.so.12")
+    cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+    if cudart.cudaMemcpy(out.data_ptr(), address, count * 4, 3) != 0:  # device to device
+        raise RuntimeError("cudaMemcpy failed")
+    return out
 
 
 def _time_calls(torch, fn, iters, warm=3):

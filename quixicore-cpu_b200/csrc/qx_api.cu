@@ -3,6 +3,7 @@
 // the operands through device memory on the library's own stream and wait for the
 // result, the `_dev` forms only enqueue.
 
+#include <chrono>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -45,19 +46,33 @@ qx_status d2h(void* dst, const void* src, size_t bytes, cudaStream_t s) {
   return QX_STATUS_OK;
 }
 
-// After a synchronise: a kernel whose bounded wait gave up leaves a code in flag[1].
-qx_status check_device_error(DeviceContext* ctx) {
-  int words[2] = {0, 0};
-  QX_CUDA_TRY(cudaMemcpy(words, ctx->flag, sizeof words, cudaMemcpyDeviceToHost));
-  if (words[1] != 0) {
-    (void)cudaMemset(ctx->flag, 0, 8);
+// Waits for the stream and reports a kernel whose bounded wait gave up (it leaves its role
+// code in the context's error word, host memory the kernels can address).
+qx_status sync_and_check(DeviceContext* ctx, cudaStream_t s) {
+  // Decode-sized calls finish within tens of microseconds: poll for a short while before
+  // falling back to the blocking wait (whose wake-up alone costs about that much).
+  const auto poll_until = std::chrono::steady_clock::now() + std::chrono::microseconds(150);
+  cudaError_t state = cudaStreamQuery(s);
+  while (state == cudaErrorNotReady && std::chrono::steady_clock::now() < poll_until) {
+    state = cudaStreamQuery(s);
+  }
+  if (state == cudaErrorNotReady) {
+    (void)cudaGetLastError();
+    state = cudaStreamSynchronize(s);
+  }
+  if (state != cudaSuccess) {
+    set_last_error("waiting for the stream", state);
+    return QX_STATUS_DEVICE_ERROR;
+  }
+  const int code = *static_cast<volatile int*>(ctx->error_host);
+  if (code != 0) {
+    *static_cast<volatile int*>(ctx->error_host) = 0;
     if (ctx->workspace.base != nullptr) {  // an aborted kernel may leave counters behind
       (void)cudaMemset(ctx->workspace.base, 0, kWorkspaceCounterBytes);
     }
     char text[96];
     std::snprintf(text, sizeof text,
-                  "a tensor-core kernel gave up a bounded wait (pipeline stalled, role code %d)",
-                  words[1]);
+                  "a tensor-core kernel gave up a bounded wait (pipeline stalled, role code %d)", code);
     set_last_error_text(text);
     return QX_STATUS_DEVICE_ERROR;
   }
@@ -179,12 +194,24 @@ qx_status qx_qgemm_prepacked(const qx_weights* weights, const float* x, float* y
   const size_t off_x = st.add(x_bytes), off_y = st.add(y_bytes);
   QX_TRY(ctx->ensure_staging(st.offset));
   QX_TRY(h2d(st.at(off_x), x, x_bytes, ctx->stream));
-  QX_TRY(launch_qgemm_f32(weights, reinterpret_cast<const float*>(st.at(off_x)),
-                          reinterpret_cast<float*>(st.at(off_y)), m, weights->rows,
-                          workspace != nullptr ? workspace : &ctx->workspace, ctx->stream));
-  QX_TRY(d2h(y, st.at(off_y), y_bytes, ctx->stream));
-  QX_CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-  return check_device_error(ctx);
+  // Results go straight to the caller's buffer when the GPU can address it (pinned or
+  // registered host memory): the kernel's row finishers write it over PCIe and the copy
+  // back is saved. Pageable memory takes the staged copy.
+  float* y_target = reinterpret_cast<float*>(st.at(off_y));
+  bool direct = false;
+  cudaPointerAttributes attributes{};
+  if (cudaPointerGetAttributes(&attributes, y) == cudaSuccess &&
+      attributes.type == cudaMemoryTypeHost && attributes.devicePointer != nullptr) {
+    y_target = static_cast<float*>(attributes.devicePointer);
+    direct = true;
+  } else {
+    (void)cudaGetLastError();  // unregistered host memory is not an error here
+  }
+  QX_TRY(launch_qgemm_f32(weights, reinterpret_cast<const float*>(st.at(off_x)), y_target, m,
+                          weights->rows, workspace != nullptr ? workspace : &ctx->workspace,
+                          ctx->stream));
+  if (!direct) QX_TRY(d2h(y, st.at(off_y), y_bytes, ctx->stream));
+  return sync_and_check(ctx, ctx->stream);
 }
 
 qx_status qx_qgemm_prepacked_dev(const qx_weights* weights, const float* x_dev, float* y_dev,
@@ -266,8 +293,7 @@ qx_status qx_int8_gemm(const int8_t* weights, const int8_t* x, const float* weig
   a.asymmetric = asymmetric != 0;
   QX_TRY(launch_int8_gemm(a, s));
   QX_TRY(d2h(y, st.at(off_y), y_bytes, s));
-  QX_CUDA_TRY(cudaStreamSynchronize(s));
-  return check_device_error(ctx);
+  return sync_and_check(ctx, s);
 }
 
 // kernels/quantization/qgemm_extended_ref.cpp:142-147
@@ -344,8 +370,7 @@ qx_status qx_qgemm_w8a32(const int8_t* weights, const float* weight_scale, const
                       reinterpret_cast<const float*>(st.at(off_x)),
                       reinterpret_cast<float*>(st.at(off_y)), m, n, k, n, &ctx->workspace, s));
   QX_TRY(d2h(y, st.at(off_y), y_bytes, s));
-  QX_CUDA_TRY(cudaStreamSynchronize(s));
-  return check_device_error(ctx);
+  return sync_and_check(ctx, s);
 }
 
 const char* qx_qgemm_w8a32_variant(void) { return "sm100a_fma"; }

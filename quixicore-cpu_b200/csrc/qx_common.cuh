@@ -69,7 +69,12 @@ struct DeviceContext {
   // staging buffers for host-pointer calls (grow-only)
   void* staging = nullptr;
   size_t staging_bytes = 0;
-  int* flag = nullptr;            // 4-byte device word for scale checks
+  int* flag = nullptr;            // device word for scale / finiteness checks
+  // Error word of the tensor-core kernels (a bounded wait that gave up leaves its role code
+  // there): pinned host memory the GPU can address, written only on that path, so the host
+  // reads it after a synchronisation without a copy.
+  int* error_host = nullptr;      // host address
+  int* error_dev = nullptr;       // device address of the same word
   qx_status ensure_staging(size_t bytes);
 };
 

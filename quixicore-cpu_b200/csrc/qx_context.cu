@@ -67,6 +67,9 @@ qx_status current_context(DeviceContext** out) {
     QX_CUDA_TRY(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking));
     QX_CUDA_TRY(cudaMalloc(&ctx->flag, 256));
     QX_CUDA_TRY(cudaMemset(ctx->flag, 0, 256));
+    QX_CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&ctx->error_host), 64, cudaHostAllocMapped));
+    ctx->error_host[0] = 0;
+    QX_CUDA_TRY(cudaHostGetDevicePointer(reinterpret_cast<void**>(&ctx->error_dev), ctx->error_host, 0));
     ctx->workspace.device = device;
     g_contexts[device] = std::move(ctx);
   }

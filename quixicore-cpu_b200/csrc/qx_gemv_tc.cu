@@ -414,7 +414,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       QX_PROF_STORE(0, w_empty);
       if (!ok) {
         *abort_flag = 1;
-        atomicCAS(p.error, 0, 11);
+        report_error(p.error, 11);
       }
     }
   } else if (warp == 1) {
@@ -533,7 +533,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       QX_PROF_STORE(17, w_high);
       if (!ok) {
         *abort_flag = 1;
-        atomicCAS(p.error, 0, gave_up);
+        report_error(p.error, gave_up);
       }
     }
   } else if (warp < 2 + G::kEpiWarps) {
@@ -739,7 +739,7 @@ gemv_tc_kernel(const GemvTcParams p) {
     }
     if (!ok) {
       *abort_flag = 1;
-      atomicExch(p.error, 13);
+      report_error(p.error, 13);
     }
   } else if (kQ4 && warp < G::kFirstUnpackWarp + G::kUnpackWarps) {
     // ------------------------------ q4_0 high nibbles -------------------------
@@ -786,7 +786,7 @@ gemv_tc_kernel(const GemvTcParams p) {
     }
     if (!ok) {
       *abort_flag = 1;
-      atomicCAS(p.error, 0, 14);
+      report_error(p.error, 14);
     }
   } else if (G::kFused && warp >= G::kQuantWarp) {
     // ------------------------------ activation quantizers ---------------------
@@ -914,7 +914,7 @@ gemv_tc_kernel(const GemvTcParams p) {
     }
     if (!ok) {
       *abort_flag = 1;
-      atomicCAS(p.error, 0, 18);
+      report_error(p.error, 18);
     }
   }
 
@@ -1047,7 +1047,7 @@ qx_status launch_gemv_tc(const qx_weights* w, const float* x, const uint8_t* xim
                          cudaStream_t stream, const GemvPush* push) {
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
-  return launch_gemv_tc_at(w, x, ximg, y, m, ldy, ws_base, scratch, ctx->flag + 1, stream, push);
+  return launch_gemv_tc_at(w, x, ximg, y, m, ldy, ws_base, scratch, ctx->error_dev, stream, push);
 }
 
 qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* ximg, float* y,

@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
       QX_PROF_STORE(1, QX_PROF_NOW() - t_start);
       if (!ok) {
         *abort_flag = 1;
-        atomicExch(p.error, 1);
+        report_error(p.error, 1);
       }
     }
   } else if (warp == 1) {
@@ -301,7 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
       QX_PROF_STORE(6, QX_PROF_NOW() - t_start);
       if (!ok) {
         *abort_flag = 1;
-        atomicExch(p.error, 2);
+        report_error(p.error, 2);
       }
     }
   } else {
@@ -464,7 +464,7 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
     }
     if (!ok) {
       *abort_flag = 1;
-      atomicExch(p.error, 3);
+      report_error(p.error, 3);
     }
   }
 
@@ -601,7 +601,7 @@ qx_status launch_int8_gemm_tc(const Int8GemmArgs& a, cudaStream_t stream) {
   p.o_tiles = static_cast<int>((a.n + na * kBM - 1) / (na * kBM));
   p.r_tiles = static_cast<int>(r_tiles);
   p.asymmetric = a.asymmetric ? 1 : 0;
-  p.error = ctx->flag + 1;
+  p.error = ctx->error_dev;
   p.debug = gemv_profile_buffer();
   const long long tiles = static_cast<long long>(p.o_tiles) * p.r_tiles;
   p.stream_k = stream_k ? 1 : 0;

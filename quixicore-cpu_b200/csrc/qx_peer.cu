@@ -41,7 +41,7 @@ __global__ void __launch_bounds__(32) allgather_wait_kernel(int* control, int wo
       __nanosleep(200);
     }
   }
-  if (!ok) atomicCAS(error, 0, 31);
+  if (!ok) sm100::report_error(error, 31);
   __syncwarp();
   if (lane == 0) control[kWaitCountWord] = expected;
 }
@@ -178,7 +178,7 @@ qx_status qx_allgather_wait_dev(const qx_push_plan* plan, long long m, long long
   config.attrs = &attribute;
   config.numAttrs = 1;
   QX_CUDA_TRY(cudaLaunchKernelEx(&config, allgather_wait_kernel, static_cast<int*>(plan->control_local),
-                                 plan->world, ctx->flag + 1));
+                                 plan->world, ctx->error_dev));
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
   if (results_dev != nullptr) {

@@ -190,7 +190,7 @@ q4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Q4GemmParams 
       }
       if (!ok) {
         *abort_flag = 1;
-        atomicCAS(p.error, 0, 21);
+        report_error(p.error, 21);
       }
     }
   } else if (warp == 1) {
@@ -241,7 +241,7 @@ q4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Q4GemmParams 
       }
       if (!ok) {
         *abort_flag = 1;
-        atomicCAS(p.error, 0, 22);
+        report_error(p.error, 22);
       }
     }
   } else if (warp < 2 + kEpiWarps) {
@@ -288,7 +288,7 @@ q4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Q4GemmParams 
     }
     if (!ok) {
       *abort_flag = 1;
-      atomicCAS(p.error, 0, 23);
+      report_error(p.error, 23);
     }
   } else {
     // ------------------------------ dequantisers ------------------------------
@@ -344,7 +344,7 @@ q4_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const Q4GemmParams 
     }
     if (!ok) {
       *abort_flag = 1;
-      atomicCAS(p.error, 0, 24);
+      report_error(p.error, 24);
     }
   }
 
@@ -432,7 +432,7 @@ qx_status launch_tc(const qx_weights* w, const uint16_t* x_bf16_dev, float* y_de
   p.bn = bn;
   p.o_tiles = static_cast<int>(w->tiles);
   p.r_tiles = static_cast<int>((m + bn - 1) / bn);
-  p.error = ctx->flag + 1;
+  p.error = ctx->error_dev;
   static bool attr_set = false;
   if (!attr_set) {
     QX_CUDA_TRY(cudaFuncSetAttribute(q4_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -80,6 +80,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   }
 }
 
+// Records why a kernel gives up (role / barrier code) in the caller's error word, which may
+// be host memory mapped into the device's address space: plain accesses only, first code
+// wins (approximately: concurrent reporters may overwrite each other, any of them will do).
+__device__ __forceinline__ void report_error(int* word, int code) {
+  volatile int* w = word;
+  if (*w == 0) *w = code;
+}
+
 // ---- TMA ---------------------------------------------------------------------------
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
