@@ -929,6 +929,9 @@ gemv_tc_kernel(const GemvTcParams p) {
     // Ordering of the result stores before that word: the storing threads -> the barrier
     // above -> this thread's fence and counter update (device scope) -> the last CTA's
     // system-scope fence and release stores; the waiting rank acquires the word.
+    // (Sending the finished slice from the last CTA as bulk copies instead of storing row by
+    // row from the finishers was measured slower: 21 against 18.5 us per step on two GPUs,
+    // 37 against 29 us on eight.)
     __threadfence();
     const int finished = atomicAdd(p.launch_counter, 1);
     if (finished == static_cast<int>(gridDim.x) - 1) {
