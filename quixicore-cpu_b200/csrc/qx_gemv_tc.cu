@@ -122,6 +122,8 @@ struct TcGeom {
   static constexpr int kQuantWarp = kFirstUnpackWarp + kUnpackWarps;  // fused only
   static constexpr int kThreads = 32 * (2 + kEpiWarps + kUnpackWarps + (kFused ? kQuantWarps : 0));
   static constexpr int kColsPerWarp = kTCols / kEpiSplit;  // a warp's share of a stage
+  // arrivals on a slot's `ready` barrier (0: the MMA issuer waits for the copies themselves)
+  static constexpr int kReadyCount = (kFused ? 1 : 0) + kUnpackWarps;
   static constexpr int kLdCols = kColsPerWarp >= 64 ? 64 : 32;  // columns fetched per TMEM wait
   static_assert(kEpiSplit == 1 || (kGroupsPerStage == 1 && kG == 1), "split stages hold one block");
   static constexpr bool kRollGroups = MP >= 8;
@@ -163,10 +165,11 @@ template <int FMT, int MP>
 struct __align__(8) GemvBarriers {
   uint64_t raw_full[TcGeom<FMT, MP>::kSlots];    // the slab's span landed in its weight slot
   uint64_t done[TcGeom<FMT, MP>::kSlots];        // the slab's epilogue is through (so are its MMAs)
-  uint64_t x_full[TcGeom<FMT, MP>::kWorkSlots];  // activation image in the work slot
-  uint64_t high_full[TcGeom<FMT, MP>::kWorkSlots];  // q4_0: high-nibble tile written
+  // everything the slab's MMAs read is in place: the span has landed (the warps below wait
+  // for that first) and the in-kernel quantizer warp / the four masking warps have written
+  // their parts. One barrier for the MMA issuer instead of one per producer.
+  uint64_t ready[TcGeom<FMT, MP>::kSlots];
   uint64_t mma_done[TcGeom<FMT, MP>::kWorkSlots];   // the slab's MMAs have read the work slot
-  uint64_t const_full[TcGeom<FMT, MP>::kSlots];     // block constants written (in-kernel quantizer)
   uint64_t tmem_full[TcGeom<FMT, MP>::kTStages];
   uint64_t tmem_empty[TcGeom<FMT, MP>::kTStages];
   uint32_t tmem_base;
@@ -322,11 +325,9 @@ gemv_tc_kernel(const GemvTcParams p) {
       mbar_init(&bars->raw_full[s], 1);  // the producer's expect_tx arrival
       // one epilogue set: it has seen the slab's last accumulator, so the MMAs are done too
       mbar_init(&bars->done[s], 4 * G::kEpiSplit);
-      mbar_init(&bars->const_full[s], 1);
+      mbar_init(&bars->ready[s], G::kReadyCount > 0 ? G::kReadyCount : 1);
     }
     for (int s = 0; s < G::kWorkSlots; ++s) {
-      mbar_init(&bars->x_full[s], 1);  // the slot's quantizer warp
-      mbar_init(&bars->high_full[s], kQ4 ? G::kUnpackWarps : 1);
       mbar_init(&bars->mma_done[s], 1);
     }
     for (int t = 0; t < G::kTStages; ++t) {
@@ -436,14 +437,10 @@ gemv_tc_kernel(const GemvTcParams p) {
       int slab_in_unit = slab - unit * p.unit_slabs;
       for (int i = 0; i < count && ok; ++i) {
         const uint32_t eset = static_cast<uint32_t>(unit & 1);
-        if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) {
+        if (!QX_PROF_WAIT(w_full, mbar_wait(G::kReadyCount > 0 ? &bars->ready[raw.slot]
+                                                                : &bars->raw_full[raw.slot],
+                                            raw.phase, abort_flag))) {
           ok = false;
-          break;
-        }
-        if (G::kFused &&
-            !QX_PROF_WAIT(w_x, mbar_wait(&bars->x_full[work.slot], work.phase, abort_flag))) {
-          ok = false;
-          gave_up = 15;
           break;
         }
         tc_fence_after_sync();
@@ -484,14 +481,6 @@ gemv_tc_kernel(const GemvTcParams p) {
             for (int t = 0; t < kSteps; ++t) {
               const uint64_t k = static_cast<uint64_t>(2 * (g * kSteps + t));
               mma_i8_ss(d_tmem, a_raw + k, b_low + k, idesc, t > 0 ? 1u : 0u);
-            }
-            if (g == 0) {
-              if (!QX_PROF_WAIT(w_high, mbar_wait(&bars->high_full[work.slot], work.phase, abort_flag))) {
-                ok = false;
-                gave_up = 17;
-                break;
-              }
-              tc_fence_after_sync();
             }
             const uint64_t a_high = make_sw128_kmajor_desc(sw);
             const uint64_t b_high = make_sw128_kmajor_desc(sb + G::kN * 128);
@@ -624,7 +613,7 @@ gemv_tc_kernel(const GemvTcParams p) {
             // (the in-kernel quantizer's work slot may already hold a later slab: its
             // constants have a barrier with the lifetime of the weight slot)
             if (!mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag) ||
-                (G::kFused && !mbar_wait(&bars->const_full[raw.slot], raw.phase, abort_flag))) {
+                (G::kFused && !mbar_wait(&bars->ready[raw.slot], raw.phase, abort_flag))) {
               ok = false;
               break;
             }
@@ -775,7 +764,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       }
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->high_full[work.slot]);
+      if (lane == 0) mbar_arrive(&bars->ready[raw.slot]);
       raw.advance(G::kSlots);
       work.advance(G::kWorkSlots);
     }
@@ -901,8 +890,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&bars->x_full[qw]);
-        mbar_arrive(&bars->const_full[raw.slot]);
+        mbar_arrive(&bars->ready[raw.slot]);
       }
       raw.advance_by(kW, G::kSlots);
       ++slot_uses;
