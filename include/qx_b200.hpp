@@ -1,0 +1,180 @@
+// C++ face of the qx_b200 C ABI with the names and calling conventions of the reference's
+// public API for this path (namespace quixicore_cpu): a translation unit written against
+//   include/quixicore_cpu/status.h, qgemv.h, qgemm.h, packed_weights.h, threading.h
+// of the reference compiles against this header instead and links libqx_b200.so.
+// Header-only; every function forwards to the C entry point named in its comment.
+// Differences from the reference, all additive: Status::kDeviceError (a CUDA failure or no
+// sm_100 device; last_error() has the text), and only QuantFormat::kQ8_0 / kQ4_0 are served
+// (every other format reports kUnsupportedFormat).
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <utility>
+
+#include "qx_b200.h"
+
+namespace quixicore_cpu {
+
+// include/quixicore_cpu/status.h:5-11 (values identical) + one additive value
+enum class Status : int {
+  kOk = 0,
+  kInvalidShape = 1,
+  kUnsupportedFormat = 2,
+  kInvalidArgument = 3,
+  kOutOfMemory = 4,
+  kDeviceError = 5,
+};
+
+// include/quixicore_cpu/qgemv.h:10-51: numeric values are part of the contract; the two
+// formats of this path
+enum class QuantFormat : int {
+  kQ8_0 = 0,
+  kQ4_0 = 1,
+};
+
+inline Status to_status(qx_status s) { return static_cast<Status>(static_cast<int>(s)); }
+inline const char* last_error() { return qx_last_error_string(); }
+
+// include/quixicore_cpu/qgemv.h:68-71 -> qx_qgemv_packed_size
+inline Status qgemv_packed_size(QuantFormat format, long long n, long long k, std::size_t* size) {
+  return to_status(qx_qgemv_packed_size(static_cast<int>(format), n, k, size));
+}
+// src/dispatch/qgemv.cpp:210-300 -> qx_qgemv_pack / qx_qgemv_unpack
+inline Status qgemv_pack(QuantFormat format, const float* weights, long long n, long long k,
+                         void* packed) {
+  return to_status(qx_qgemv_pack(static_cast<int>(format), weights, n, k, packed));
+}
+inline Status qgemv_unpack(QuantFormat format, const void* packed, long long n, long long k,
+                           float* weights) {
+  return to_status(qx_qgemv_unpack(static_cast<int>(format), packed, n, k, weights));
+}
+// include/quixicore_cpu/qgemv.h:108-109 -> qx_qgemv
+inline Status qgemv(QuantFormat format, const void* packed, const float* x, float* y, long long n,
+                    long long k) {
+  return to_status(qx_qgemv(static_cast<int>(format), packed, x, y, n, k));
+}
+// include/quixicore_cpu/qgemm.h:19-20 -> qx_qgemm
+inline Status qgemm(QuantFormat format, const void* packed_weights, const float* x, float* y,
+                    long long m, long long n, long long k) {
+  return to_status(qx_qgemm(static_cast<int>(format), packed_weights, x, y, m, n, k));
+}
+inline const char* qgemv_variant(QuantFormat format) {
+  return qx_qgemv_variant(static_cast<int>(format));
+}
+
+// include/quixicore_cpu/packed_weights.h:14-70: the panel layout argument of the reference
+// selects a CPU row tile; the device layout is fixed, so it is accepted and ignored.
+enum class CpuPanelLayout : int { kAuto = 0, kRowTile1 = 1, kRowTile4 = 4, kRowTile8 = 8, kRowTile16 = 16 };
+
+struct CpuPackedWeightsInfo {
+  QuantFormat format = QuantFormat::kQ8_0;
+  long long rows = 0, columns = 0, block_size = 0, blocks_per_row = 0;
+  std::size_t block_bytes = 0, contract_bytes = 0, prepared_bytes = 0;
+  double memory_amplification = 0.0;
+  std::uint64_t preparation_ns = 0;
+};
+
+using Workspace = qx_workspace;  // opaque; nullptr = the library's own
+
+// include/quixicore_cpu/packed_weights.h:72-97 (move-only owner of prepared weights) ->
+// qx_weights_prepare / qx_weights_get_info / qx_weights_destroy. The handle owns a device
+// copy; the caller may free the canonical bytes after prepare().
+class CpuPackedWeights {
+ public:
+  CpuPackedWeights() = default;
+  CpuPackedWeights(const CpuPackedWeights&) = delete;
+  CpuPackedWeights& operator=(const CpuPackedWeights&) = delete;
+  CpuPackedWeights(CpuPackedWeights&& other) noexcept : handle_(std::exchange(other.handle_, nullptr)) {}
+  CpuPackedWeights& operator=(CpuPackedWeights&& other) noexcept {
+    if (this != &other) {
+      reset();
+      handle_ = std::exchange(other.handle_, nullptr);
+    }
+    return *this;
+  }
+  ~CpuPackedWeights() { reset(); }
+
+  Status prepare(QuantFormat format, const void* packed, long long rows, long long columns,
+                 CpuPanelLayout /*layout*/ = CpuPanelLayout::kAuto) {
+    return prepare_rows(format, packed, rows, columns, 0, rows);
+  }
+  // additive: keep only rows [row_begin, row_begin + row_count) on this GPU (row sharding)
+  Status prepare_rows(QuantFormat format, const void* packed, long long rows, long long columns,
+                      long long row_begin, long long row_count) {
+    qx_weights* fresh = nullptr;
+    const Status status = to_status(qx_weights_prepare(static_cast<int>(format), packed, rows, columns,
+                                                       row_begin, row_count, &fresh));
+    if (status == Status::kOk) {  // like the reference: a failed prepare leaves *this untouched
+      reset();
+      handle_ = fresh;
+    }
+    return status;
+  }
+  bool ready() const noexcept { return handle_ != nullptr; }
+  void reset() noexcept {
+    qx_weights_destroy(handle_);
+    handle_ = nullptr;
+  }
+  CpuPackedWeightsInfo info() const {
+    CpuPackedWeightsInfo out;
+    qx_weights_info raw{};
+    if (handle_ != nullptr && qx_weights_get_info(handle_, &raw) == QX_STATUS_OK) {
+      out.format = static_cast<QuantFormat>(raw.format);
+      out.rows = raw.rows;
+      out.columns = raw.columns;
+      out.block_size = raw.block_size;
+      out.blocks_per_row = raw.blocks_per_row;
+      out.block_bytes = raw.block_bytes;
+      out.contract_bytes = raw.contract_bytes;
+      out.prepared_bytes = raw.prepared_bytes;
+      out.memory_amplification = raw.memory_amplification;
+      out.preparation_ns = raw.preparation_ns;
+    }
+    return out;
+  }
+  const qx_weights* handle() const noexcept { return handle_; }
+
+ private:
+  qx_weights* handle_ = nullptr;
+};
+
+// include/quixicore_cpu/qgemm.h:26-27 -> qx_qgemm_prepacked
+inline Status qgemm_prepacked(const CpuPackedWeights& weights, const float* x, float* y, long long m,
+                              Workspace* workspace = nullptr) {
+  return to_status(qx_qgemm_prepacked(weights.handle(), x, y, m, workspace));
+}
+
+// include/quixicore_cpu/qgemm.h:235-257 -> qx_int8_gemm / qx_qgemm_w8a8[_azp] / qx_qgemm_w8a32
+inline Status int8_gemm(const std::int8_t* weights, const std::int8_t* x, const float* weight_scale,
+                        const float* activation_scale, const std::int32_t* weight_row_sum,
+                        const int* activation_zero_point, float* y, long long m, long long n,
+                        long long k, bool asymmetric = false) {
+  return to_status(qx_int8_gemm(weights, x, weight_scale, activation_scale, weight_row_sum,
+                                activation_zero_point, y, m, n, k, asymmetric ? 1 : 0));
+}
+inline Status qgemm_w8a8(const std::int8_t* weights, const std::int8_t* x, const float* weight_scale,
+                         const float* activation_scale, float* y, long long m, long long n,
+                         long long k) {
+  return to_status(qx_qgemm_w8a8(weights, x, weight_scale, activation_scale, y, m, n, k));
+}
+inline Status qgemm_w8a8_azp(const std::int8_t* weights, const std::int8_t* x, const float* weight_scale,
+                             const float* activation_scale, const std::int32_t* weight_row_sum,
+                             const int* activation_zero_point, float* y, long long m, long long n,
+                             long long k) {
+  return to_status(qx_qgemm_w8a8_azp(weights, x, weight_scale, activation_scale, weight_row_sum,
+                                     activation_zero_point, y, m, n, k));
+}
+inline Status qgemm_w8a32(const std::int8_t* weights, const float* weight_scale, const float* x,
+                          float* y, long long m, long long n, long long k) {
+  return to_status(qx_qgemm_w8a32(weights, weight_scale, x, y, m, n, k));
+}
+inline const char* int8_gemm_variant() { return qx_int8_gemm_variant(); }
+inline const char* qgemm_w8a32_variant() { return qx_qgemm_w8a32_variant(); }
+
+// include/quixicore_cpu/threading.h: kept for source compatibility (the GPU path has no
+// thread pool; the value is stored and returned)
+inline void set_num_threads(int n) { qx_set_num_threads(n); }
+inline int num_threads() { return qx_num_threads(); }
+
+}  // namespace quixicore_cpu

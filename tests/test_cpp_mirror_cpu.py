@@ -1,0 +1,66 @@
+"""The C++ face of the C ABI (include/qx_b200.hpp, namespace quixicore_cpu) compiles as plain
+C++17, links against the library and reproduces the reference's host-side contract without
+a GPU: packed sizes (tests/correctness/test_qgemv.cpp:116-122) and the validation order of
+qgemv / qgemm / int8_gemm (format -> shape -> pointers; test_qgemv.cpp:106-107,
+src/dispatch/int8_gemm.cpp:72-85), all of which return before any device is touched."""
+
+import os
+import subprocess
+import sys
+import textwrap
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "quixicore-cpu_b200")
+
+PROGRAM = textwrap.dedent(r"""
+    #include <cstdio>
+    #include <cstdlib>
+    #include "qx_b200.hpp"
+    using namespace quixicore_cpu;
+    #define CHECK(cond) do { if (!(cond)) { std::printf("FAILED: %s (line %d)\n", #cond, __LINE__); return 1; } } while (0)
+    int main() {
+      std::size_t size = 0;
+      CHECK(qgemv_packed_size(QuantFormat::kQ8_0, 1, 32, &size) == Status::kOk && size == 34);
+      CHECK(qgemv_packed_size(QuantFormat::kQ4_0, 1, 32, &size) == Status::kOk && size == 18);
+      CHECK(qgemv_packed_size(QuantFormat::kQ8_0, 4096, 4096, &size) == Status::kOk && size == 17825792u);
+      CHECK(qgemv_packed_size(QuantFormat::kQ8_0, 3, 33, &size) == Status::kInvalidShape);
+      CHECK(qgemv_packed_size(static_cast<QuantFormat>(7), 1, 32, &size) == Status::kUnsupportedFormat);
+      float x[32] = {0}, y[1] = {0};
+      unsigned char packed[34] = {0};
+      // a null pointer together with a bad shape reports the shape
+      CHECK(qgemv(QuantFormat::kQ8_0, nullptr, x, y, 1, 31) == Status::kInvalidShape);
+      CHECK(qgemv(QuantFormat::kQ8_0, nullptr, x, y, 1, 32) == Status::kInvalidArgument);
+      CHECK(qgemv(QuantFormat::kQ8_0, packed, x, nullptr, 1, 32) == Status::kInvalidArgument);
+      CHECK(qgemv(static_cast<QuantFormat>(9), packed, x, y, 1, 32) == Status::kUnsupportedFormat);
+      CHECK(qgemm(QuantFormat::kQ4_0, packed, x, y, 0, 1, 32) == Status::kInvalidShape);
+      CHECK(int8_gemm(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, y, 0, 1, 4) == Status::kInvalidShape);
+      CHECK(int8_gemm(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, y, 1, 1, 4) == Status::kInvalidArgument);
+      CHECK(qgemm_w8a32(nullptr, nullptr, x, y, 1, 1, 0) == Status::kInvalidShape);
+      CpuPackedWeights weights;
+      CHECK(!weights.ready());
+      CHECK(weights.prepare(QuantFormat::kQ8_0, nullptr, 1, 32) == Status::kInvalidArgument);
+      CHECK(weights.prepare(QuantFormat::kQ8_0, packed, 1, 31) == Status::kInvalidShape);
+      CHECK(qgemm_prepacked(weights, x, y, 1) == Status::kInvalidArgument);  // not ready
+      CpuPackedWeights moved = std::move(weights);
+      CHECK(!moved.ready() && moved.info().rows == 0);
+      set_num_threads(4);
+      CHECK(num_threads() == 4);
+      CHECK(qgemv_variant(QuantFormat::kQ8_0) != nullptr && int8_gemm_variant() != nullptr);
+      std::printf("cpp mirror ok\n");
+      return 0;
+    }
+""")
+
+
+def test_cpp_mirror_compiles_links_and_validates(tmp_path):
+    source = tmp_path / "mirror.cpp"
+    source.write_text(PROGRAM)
+    exe = tmp_path / "mirror"
+    build = subprocess.run(
+        ["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-I", os.path.join(ROOT, "include"),
+         str(source), "-o", str(exe), "-L", PKG, "-lqx_b200", f"-Wl,-rpath,{PKG}"],
+        capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=60)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert "cpp mirror ok" in run.stdout
