@@ -433,7 +433,7 @@ def _time_calls(torch, fn, iters, warm=3):
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_tc_kernel launch on the headline
 # workload, from the ncu capture summarised in profiles/gemv_tc_q4_0_cfg1.md (algorithmic
 # bytes: 33 103 872)
-NCU_DRAM_BYTES_PER_LAUNCH = 33157632
+NCU_DRAM_BYTES_PER_LAUNCH = 33167104
 
 EXTRA_CASES = ("cfg2_w8a8_gemm", "cfg0_q8_0_gemv", "cfg3_q8_0_batched", "cfg4_q4_0_prefill")
 
