@@ -14,7 +14,12 @@
  *     kernel on the library's own stream and copy the result back before returning
  *     (drop-in semantics of the reference: synchronous, caller owns every buffer);
  *   - entry points ending in `_dev` take DEVICE pointers and a `cudaStream_t` passed as
- *     `void*`; they enqueue work and return without synchronising.
+ *     `void*`; they enqueue work and return without waiting for it. One exception: a call
+ *     whose scratch does not fit the workspace it was given (or the library's default one)
+ *     grows that workspace first, which synchronises the device, frees and allocates. To
+ *     keep `_dev` calls purely asynchronous (and legal inside stream capture), create the
+ *     workspace up front with qx_workspace_create(reserve_bytes) large enough for the
+ *     biggest call, or run each shape once before capturing.
  *
  * There is no CPU fallback: without a usable sm_100 device every compute entry point
  * returns QX_STATUS_DEVICE_ERROR.
@@ -67,9 +72,22 @@ typedef struct qx_device_info {
   int visible_devices;      /* CUDA devices visible to this process */
   int peer_access_mask;     /* bit i set: this device can map device i's memory */
   char name[64];
+  /* NVLink discovery (read-only driver queries per visible peer) */
+  int nvlink_peer_mask;     /* bit i set: peer i is reached over NVLink / NVSwitch (the pair
+                               supports native atomics over the link; PCIe paths do not) */
+  int nvlink_peers;         /* number of bits set in nvlink_peer_mask */
+  int nvlink_uniform;       /* 1: every NVLink peer has the best performance rank, i.e. a
+                               switched fabric with the same bandwidth to every peer */
+  signed char peer_performance_rank[16]; /* driver's link ranking of peer i (0 = best), -1: none */
 } qx_device_info;
 QX_API qx_status qx_device_query(qx_device_info* info);
 QX_API const char* qx_last_error_string(void);
+/* Reports and clears the current device's pipeline error word: QX_STATUS_DEVICE_ERROR (and
+ * a message naming the role code) if a kernel enqueued through a `_dev` entry point gave up
+ * one of its bounded waits since the last report, else QX_STATUS_OK. It does not wait for
+ * the GPU: synchronise the stream first. The host-pointer entry points make the same check
+ * before they return. No counterpart in the reference (its kernels cannot stall). */
+QX_API qx_status qx_check_device_errors(void);
 
 /* ---- sizes, authoring ---------------------------------------------------------- */
 
@@ -114,6 +132,8 @@ typedef struct qx_weights_info {
   uint64_t preparation_ns;
   int device;
   int has_dense_bf16;         /* 1 after the first prefill GEMM built its fp16 tile cache */
+  long long row_tile;         /* rows per panel tile on the device (128) */
+  size_t panel_bytes;         /* bytes of the device panel (padded tiles included) */
 } qx_weights_info;
 
 /* CpuPackedWeights::prepare(format, contract_packed, rows, columns, layout),
@@ -130,6 +150,10 @@ QX_API qx_status qx_weights_prepare_dev(int format, const void* contract_packed_
                                  long long row_count, void* stream, qx_weights** out);
 /* CpuPackedWeights::info(), packed_weights.h:88 */
 QX_API qx_status qx_weights_get_info(const qx_weights* weights, qx_weights_info* info);
+/* CpuPackedWeights::panel_data(), packed_weights.h:90: the re-laid-out panel. Here a DEVICE
+ * pointer ([tile][K-slab] spans, see qx_weights_info.row_tile / panel_bytes); NULL for a
+ * NULL handle. */
+QX_API const void* qx_weights_panel_dev(const qx_weights* weights);
 /* CpuPackedWeights::reset() / destructor, packed_weights.h:75,86 */
 QX_API void qx_weights_destroy(qx_weights* weights);
 
@@ -199,8 +223,9 @@ QX_API qx_status qx_qgemm_prepacked_push_dev(const qx_weights* weights, const fl
                                              qx_workspace* workspace, void* stream);
 /* Enqueues the wait for all ranks' slices of the next step in order; *results_dev (host
  * variable, optional) receives the device address of that step's [world][m][rows_per_rank]
- * results in this rank's buffer. A wait that runs out sets the error word reported by the
- * next host-pointer call (QX_STATUS_DEVICE_ERROR, role code 31). */
+ * results in this rank's buffer. A wait that runs out (2 s; QX_B200_WAIT_LIMIT_MS in the
+ * environment overrides it) sets the error word reported by qx_check_device_errors() or the
+ * next host-pointer call (QX_STATUS_DEVICE_ERROR, role code 31); the kernel then returns. */
 QX_API qx_status qx_allgather_wait_dev(const qx_push_plan* plan, long long m, long long step,
                                        const float** results_dev, void* stream);
 
@@ -226,7 +251,11 @@ QX_API qx_status qx_allgather_wait_dev(const qx_push_plan* plan, long long m, lo
  *  - all calls on a GPU share the array and it keeps the previous call's contents; each
  *    call clears the counters it needs on `stream` first. Calls that could overlap on the
  *    GPU (different streams, no ordering) race on it: keep them on one stream or order
- *    them with events.
+ *    them with events;
+ *  - a stalled pipeline is reported like everywhere else: the kernel leaves its role code in
+ *    the device's error word (host memory mapped when the weights were prepared, so nothing
+ *    is allocated here) and qx_check_device_errors() or the next host-pointer call on the
+ *    device returns QX_STATUS_DEVICE_ERROR.
  * Results are bit-identical to qx_qgemm_prepacked_dev with m = 1. */
 QX_API qx_status qx_qgemv_prepacked_noalloc_dev(const qx_weights* weights, const float* x_dev,
                                                 float* y_dev, void* stream);

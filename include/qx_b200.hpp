@@ -63,14 +63,31 @@ inline const char* qgemv_variant(QuantFormat format) {
   return qx_qgemv_variant(static_cast<int>(format));
 }
 
-// include/quixicore_cpu/packed_weights.h:14-70: the panel layout argument of the reference
-// selects a CPU row tile; the device layout is fixed, so it is accepted and ignored.
-enum class CpuPanelLayout : int { kAuto = 0, kRowTile1 = 1, kRowTile4 = 4, kRowTile8 = 8, kRowTile16 = 16 };
+// include/quixicore_cpu/packed_weights.h:14-20, same enumerators and values. The argument
+// selects a CPU row tile in the reference; the device panel has one layout (tiles of 128
+// rows), so every value is accepted and info().layout reports kAuto.
+enum class CpuPanelLayout {
+  kAuto,
+  kPortableRows1,
+  kNeonRows4,
+  kAvx2Rows8,
+  kAvx512Rows16,
+};
 
+// include/quixicore_cpu/packed_weights.h:36-67: the fields that have a meaning for q8_0 /
+// q4_0 weights on the device, under the reference's names.
 struct CpuPackedWeightsInfo {
   QuantFormat format = QuantFormat::kQ8_0;
-  long long rows = 0, columns = 0, block_size = 0, blocks_per_row = 0;
-  std::size_t block_bytes = 0, contract_bytes = 0, prepared_bytes = 0;
+  CpuPanelLayout layout = CpuPanelLayout::kAuto;
+  long long rows = 0;
+  long long columns = 0;
+  long long row_tile = 0;      // 128 on the device
+  long long block_size = 0;
+  long long blocks_per_row = 0;
+  std::size_t block_bytes = 0;
+  std::size_t contract_bytes = 0;
+  std::size_t panel_bytes = 0;
+  std::size_t prepared_bytes = 0;
   double memory_amplification = 0.0;
   std::uint64_t preparation_ns = 0;
 };
@@ -130,9 +147,16 @@ class CpuPackedWeights {
       out.prepared_bytes = raw.prepared_bytes;
       out.memory_amplification = raw.memory_amplification;
       out.preparation_ns = raw.preparation_ns;
+      out.row_tile = raw.row_tile;
+      out.panel_bytes = raw.panel_bytes;
     }
     return out;
   }
+  // packed_weights.h:89-90. The canonical bytes are not kept once the device panel is built
+  // (the caller still owns its copy), so contract_data() is null; panel_data() is the
+  // DEVICE address of the panel.
+  const void* contract_data() const noexcept { return nullptr; }
+  const void* panel_data() const noexcept { return qx_weights_panel_dev(handle_); }
   const qx_weights* handle() const noexcept { return handle_; }
 
  private:

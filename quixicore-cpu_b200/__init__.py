@@ -40,7 +40,8 @@ class WeightsInfo(C.Structure):
     _fields_ = [("format", C.c_int), ("rows", _ll), ("columns", _ll), ("block_size", _ll),
                 ("blocks_per_row", _ll), ("block_bytes", _sz), ("contract_bytes", _sz),
                 ("prepared_bytes", _sz), ("memory_amplification", C.c_double),
-                ("preparation_ns", C.c_uint64), ("device", C.c_int), ("has_dense_bf16", C.c_int)]
+                ("preparation_ns", C.c_uint64), ("device", C.c_int), ("has_dense_bf16", C.c_int),
+                ("row_tile", _ll), ("panel_bytes", _sz)]
 
 
 class PushPlan(C.Structure):
@@ -54,7 +55,8 @@ class DeviceInfo(C.Structure):
     _fields_ = [("device", C.c_int), ("sm_major", C.c_int), ("sm_minor", C.c_int),
                 ("sm_count", C.c_int), ("max_smem_per_block", C.c_int), ("l2_bytes", C.c_int),
                 ("hbm_bytes", _sz), ("visible_devices", C.c_int), ("peer_access_mask", C.c_int),
-                ("name", C.c_char * 64)]
+                ("name", C.c_char * 64), ("nvlink_peer_mask", C.c_int), ("nvlink_peers", C.c_int),
+                ("nvlink_uniform", C.c_int), ("peer_performance_rank", C.c_byte * 16)]
 
 
 def _load():
@@ -65,6 +67,7 @@ def _load():
     lib = C.CDLL(LIB_PATH)
     sig = {
         "qx_device_query": [C.POINTER(DeviceInfo)],
+        "qx_check_device_errors": [],
         "qx_qgemv_packed_size": [C.c_int, _ll, _ll, C.POINTER(_sz)],
         "qx_qgemv_pack": [C.c_int, _vp, _ll, _ll, _vp],
         "qx_qgemv_unpack": [C.c_int, _vp, _ll, _ll, _vp],
@@ -153,6 +156,7 @@ def device_info() -> dict:
     check(lib.qx_device_query(C.byref(info)), "qx_device_query")
     out = {name: getattr(info, name) for name, _ in DeviceInfo._fields_}
     out["name"] = info.name.decode()
+    out["peer_performance_rank"] = list(info.peer_performance_rank)
     return out
 
 

@@ -46,6 +46,8 @@ qx_status d2h(void* dst, const void* src, size_t bytes, cudaStream_t s) {
   return QX_STATUS_OK;
 }
 
+qx_status take_device_error(DeviceContext* ctx);
+
 // Waits for the stream and reports a kernel whose bounded wait gave up (it leaves its role
 // code in the context's error word, host memory the kernels can address).
 qx_status sync_and_check(DeviceContext* ctx, cudaStream_t s) {
@@ -64,19 +66,23 @@ qx_status sync_and_check(DeviceContext* ctx, cudaStream_t s) {
     set_last_error("waiting for the stream", state);
     return QX_STATUS_DEVICE_ERROR;
   }
+  return take_device_error(ctx);
+}
+
+// Reads and clears the error word of `ctx`; an aborted kernel may leave arrival counters
+// behind, so the default workspace's counter area is cleared with it.
+qx_status take_device_error(DeviceContext* ctx) {
   const int code = *static_cast<volatile int*>(ctx->error_host);
-  if (code != 0) {
-    *static_cast<volatile int*>(ctx->error_host) = 0;
-    if (ctx->workspace.base != nullptr) {  // an aborted kernel may leave counters behind
-      (void)cudaMemset(ctx->workspace.base, 0, kWorkspaceCounterBytes);
-    }
-    char text[96];
-    std::snprintf(text, sizeof text,
-                  "a tensor-core kernel gave up a bounded wait (pipeline stalled, role code %d)", code);
-    set_last_error_text(text);
-    return QX_STATUS_DEVICE_ERROR;
+  if (code == 0) return QX_STATUS_OK;
+  *static_cast<volatile int*>(ctx->error_host) = 0;
+  if (ctx->workspace.base != nullptr) {
+    (void)cudaMemset(ctx->workspace.base, 0, kWorkspaceCounterBytes);
   }
-  return QX_STATUS_OK;
+  char text[96];
+  std::snprintf(text, sizeof text,
+                "a kernel gave up a bounded wait (pipeline stalled, role code %d)", code);
+  set_last_error_text(text);
+  return QX_STATUS_DEVICE_ERROR;
 }
 
 bool all_finite_host(const float* v, long long count) {
@@ -172,6 +178,13 @@ qx_status qx_qgemv(int format, const void* packed, const float* x, float* y, lon
   if (packed_bytes(format, n, k, &bytes) != QX_STATUS_OK) return QX_STATUS_INVALID_SHAPE;
   if (packed == nullptr || x == nullptr || y == nullptr) return QX_STATUS_INVALID_ARGUMENT;
   return qx_qgemm(format, packed, x, y, 1, n, k);
+}
+
+qx_status qx_check_device_errors(void) {
+  int device = -1;
+  QX_CUDA_TRY(cudaGetDevice(&device));
+  DeviceContext* ctx = existing_context(device);
+  return ctx == nullptr ? QX_STATUS_OK : take_device_error(ctx);
 }
 
 const char* qx_qgemv_variant(int format) {

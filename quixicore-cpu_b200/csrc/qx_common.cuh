@@ -91,4 +91,28 @@ qx_status packed_bytes(int format, long long n, long long k, size_t* size);
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute of a kernel: every
+// device of the process that launches it needs its own opt-in. One instance of this guard
+// per kernel (a function-local static at the launch site) remembers which devices have it.
+struct SmemOptIn {
+  std::mutex mutex;
+  bool done[64] = {};
+  template <class Kernel>
+  qx_status ensure(Kernel kernel, size_t bytes) {
+    int device = -1;
+    QX_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= 64) return QX_STATUS_DEVICE_ERROR;
+    std::lock_guard<std::mutex> lock(mutex);
+    if (!done[device]) {
+      QX_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(bytes)));
+      done[device] = true;
+    }
+    return QX_STATUS_OK;
+  }
+};
+
+// Context of `device` if one exists already; never creates (and so never allocates).
+DeviceContext* existing_context(int device);
+
 }  // namespace qx

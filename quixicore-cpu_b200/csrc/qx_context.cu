@@ -77,6 +77,12 @@ qx_status current_context(DeviceContext** out) {
   return QX_STATUS_OK;
 }
 
+DeviceContext* existing_context(int device) {
+  if (device < 0 || device >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  return g_contexts[device].get();
+}
+
 bool valid_product3(long long a, long long b, long long c) {
   const long long dims[3] = {a, b, c};
   long long product = 1;
@@ -188,6 +194,35 @@ qx_status qx_device_query(qx_device_info* info) {
     int can = peer == device ? 1 : 0;
     if (peer != device) (void)cudaDeviceCanAccessPeer(&can, device, peer);
     if (can) info->peer_access_mask |= 1 << peer;
+    if (peer == device || !can || peer >= 16) continue;
+    // Link class of the pair as the driver reports it (read-only queries): native atomics
+    // over the link exist on NVLink / NVSwitch paths and not across PCIe; the performance
+    // rank orders a device's peers by link quality (0 = best).
+    int atomics = 0, rank = -1;
+    if (cudaDeviceGetP2PAttribute(&atomics, cudaDevP2PAttrNativeAtomicSupported, device, peer) != cudaSuccess) {
+      (void)cudaGetLastError();
+      atomics = 0;
+    }
+    if (cudaDeviceGetP2PAttribute(&rank, cudaDevP2PAttrPerformanceRank, device, peer) != cudaSuccess) {
+      (void)cudaGetLastError();
+      rank = -1;
+    }
+    if (atomics) info->nvlink_peer_mask |= 1 << peer;
+    info->peer_performance_rank[peer] = static_cast<signed char>(rank);
+  }
+  for (int peer = 0; peer < 16; ++peer) {
+    if (!(info->peer_access_mask & (1 << peer)) || peer == device) info->peer_performance_rank[peer] = -1;
+  }
+  {
+    int bits = 0;
+    for (int peer = 0; peer < 31; ++peer) bits += (info->nvlink_peer_mask >> peer) & 1;
+    info->nvlink_peers = bits;
+    // every NVLink peer at the same (best) rank: a switched fabric, uniform bandwidth to all
+    int uniform = bits > 0 ? 1 : 0;
+    for (int peer = 0; peer < 16; ++peer) {
+      if ((info->nvlink_peer_mask & (1 << peer)) && info->peer_performance_rank[peer] != 0) uniform = 0;
+    }
+    info->nvlink_uniform = uniform;
   }
   std::strncpy(info->name, prop.name, sizeof(info->name) - 1);
   return QX_STATUS_OK;

@@ -76,6 +76,11 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
                                                          long long total_threads) {
   // let the GEMV kernel behind this one start its set-up and weight pipeline right away
   asm volatile("griddepcontrol.launch_dependents;");
+  // This kernel is launched programmatically, so it may start while the kernel in front of
+  // it still runs. That kernel may be the producer of x (the previous layer's GEMV, the
+  // wait kernel of a sharded step) and may still read the images (the previous GEMV):
+  // nothing is read or written before it has finished.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const long long t = blockIdx.x * 256LL + threadIdx.x;
   if (t >= total_threads) return;
   const int ncols = digit_columns(FMT, mp);
@@ -115,9 +120,6 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
       }
       out = make_uint4(word[0], word[1], word[2], word[3]);
     }
-    // The images may still be read by the GEMV launched before this kernel (both are
-    // launched programmatically, so this kernel can start early): wait for it to finish.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     *reinterpret_cast<uint4*>(ximg + slab * image_bytes + ximage_chunk_offset(ncols, which, n, cc)) =
         out;
   } else {
@@ -142,7 +144,6 @@ __global__ void __launch_bounds__(256) quantize_x_kernel(const float* __restrict
       }
       if (FMT == QX_FORMAT_Q4_0) c.scale *= 0.0625f;  // the digit sums carry a factor 16
     }
-    asm volatile("griddepcontrol.wait;" ::: "memory");
     *reinterpret_cast<XConst*>(ximg + slab * image_bytes + ximage_const_offset(ncols, mp, j, row)) = c;
   }
 }
@@ -326,7 +327,7 @@ qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev
 // in a latency-critical thread where the implicit device synchronisation of cudaMalloc /
 // cudaFree is not acceptable. The regular entry points grow a workspace on demand and so
 // may allocate; this one never does. Its scratch memory (activation slab images, per-unit
-// partial sums, per-row counters and the pipeline error word) lives in the array below,
+// partial sums and per-row counters) lives in the array below,
 // which every GPU that loads the library holds from module load until the process exits.
 // ------------------------------------------------------------------------------------
 namespace qx {
@@ -390,21 +391,28 @@ extern "C" qx_status qx_qgemv_prepacked_noalloc_dev(const qx_weights* weights, c
   if (weights->columns > (1LL << 24)) return QX_STATUS_INVALID_SHAPE;
   GemvScratch scratch;
   QX_TRY(gemv_scratch_layout(weights, 1, dev->sm_count, &scratch));
-  const size_t error_offset = align_up(scratch.total_bytes, 256);
-  if (error_offset + 256 > kNoAllocScratchBytes) {
+  if (align_up(scratch.total_bytes, 256) > kNoAllocScratchBytes) {
     set_last_error_text(
         "qgemv (no-alloc): this weight matrix needs more scratch than the 6 MiB static array "
         "(limit is about rows * min(16, columns/256) * 4 B <= 5 MiB; use qx_qgemm_prepacked_dev)");
     return QX_STATUS_INVALID_SHAPE;
   }
+  // A bounded wait that gives up inside the kernel reports through the same word as every
+  // other entry point: the device's context was created when the weights were prepared, so
+  // looking it up allocates nothing. qx_check_device_errors() or the next host-pointer call
+  // on this device returns QX_STATUS_DEVICE_ERROR with the role code.
+  DeviceContext* ctx = existing_context(device);
+  if (ctx == nullptr) {
+    set_last_error_text("qgemv (no-alloc): no context on this device (prepare the weights here first)");
+    return QX_STATUS_DEVICE_ERROR;
+  }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint8_t* base = dev->scratch;
   // The array keeps whatever the previous call left. The kernel expects the row counters it
-  // uses and the error word to be zero; everything else is fully rewritten before it is read.
+  // uses to be zero; everything else is fully rewritten before it is read.
   QX_CUDA_TRY(cudaMemsetAsync(base, 0, static_cast<size_t>(weights->tiles) * kTileRows * sizeof(int), s));
-  QX_CUDA_TRY(cudaMemsetAsync(base + error_offset, 0, 256, s));
 
   uint8_t* ximg = base + scratch.ximg_offset;
   return launch_gemv_tc_at(weights, x_dev, ximg, y_dev, 1, weights->rows, base, scratch,
-                           reinterpret_cast<int*>(base + error_offset), s);
+                           ctx->error_dev, s);
 }

@@ -380,6 +380,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       // The weights do not depend on the kernel in front of this one: start the first
       // copies at once, and only then wait for the activation images.
       const int ahead = count < G::kSlots ? count : G::kSlots;
+      QX_PROF_STAMP(24);
       for (int i = 0; i < ahead; ++i) {
         mbar_arrive_expect_tx(&bars->raw_full[i], kTxBytes);
         bulk_copy_g2s(smem + i * G::kSlotBytes, wsrc, G::kWBytes, &bars->raw_full[i]);
@@ -413,6 +414,7 @@ gemv_tc_kernel(const GemvTcParams p) {
         freed.advance(G::kSlots);
       }
       QX_PROF_STORE(0, w_empty);
+      QX_PROF_STAMP(25);
       if (!ok) {
         *abort_flag = 1;
         report_error(p.error, 11);
@@ -516,6 +518,7 @@ gemv_tc_kernel(const GemvTcParams p) {
           ++unit;
         }
       }
+      QX_PROF_STAMP(26);
       QX_PROF_STORE(2, w_full);
       QX_PROF_STORE(3, w_tempty);
       QX_PROF_STORE(16, w_x);
@@ -583,6 +586,10 @@ gemv_tc_kernel(const GemvTcParams p) {
     uint32_t ring_pos = 0, tphase = 0;
     bool ok = true;
     QX_PROF_DECL(w_tfull);
+    QX_PROF_DECL(c_vis);
+    QX_PROF_DECL(c_ld);
+    QX_PROF_DECL(c_math);
+    QX_PROF_DECL(c_unit);
     const long long t_start = QX_PROF_NOW();
     int tile = static_cast<int>(s_begin / p.slabs);
     int slab = static_cast<int>(s_begin - static_cast<long long>(tile) * p.slabs);
@@ -607,6 +614,7 @@ gemv_tc_kernel(const GemvTcParams p) {
           }
           tc_fence_after_sync();
           if (i == 0 && st == 0 && epi_thread == 0) QX_PROF_STAMP(13);
+          QX_PROF_BEGIN();
           if (st == 0) {
             // these barriers completed before the MMAs ran; waiting on them here makes the
             // copied scales and the block constants visible to this thread
@@ -623,8 +631,10 @@ gemv_tc_kernel(const GemvTcParams p) {
               scw[0] = s4.x; scw[1] = s4.y; scw[2] = s4.z; scw[3] = s4.w;
             }
           }
+          QX_PROF_END(c_vis);
 #pragma unroll
           for (int c0 = 0; c0 < G::kColsPerWarp; c0 += G::kLdCols) {
+            const long long qx_tl_ = QX_PROF_NOW();
             uint32_t v[G::kLdCols / 32][32];
             const uint32_t taddr = tmem_base + ts * G::kTCols + split * G::kColsPerWarp + c0 +
                                    (static_cast<uint32_t>(quarter * 32) << 16);
@@ -636,6 +646,9 @@ gemv_tc_kernel(const GemvTcParams p) {
               __syncwarp();
               if (lane == 0) mbar_arrive(&bars->tmem_empty[ts]);
             }
+            const long long qx_tm_ = QX_PROF_NOW();
+            (void)qx_tl_;
+            QX_PROF_ADD(c_ld, qx_tm_ - qx_tl_);
 #pragma unroll
             for (int q = 0; q < G::kLdCols / 4; ++q) {
               // columns 4*idx .. 4*idx+3: the four digit sums of (block class, activation row)
@@ -662,6 +675,7 @@ gemv_tc_kernel(const GemvTcParams p) {
                 acc[lm] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[lm]);
               }
             }
+            QX_PROF_ADD(c_math, QX_PROF_NOW() - qx_tm_);
           }
           if (++ring_pos == G::kTPerSet) {
             ring_pos = 0;
@@ -676,6 +690,8 @@ gemv_tc_kernel(const GemvTcParams p) {
       work.advance(G::kWorkSlots);
 
       // ---- unit / tile boundaries ----
+      const long long qx_tu_ = QX_PROF_NOW();
+      (void)qx_tu_;
       const bool unit_end = slab_in_unit + 1 == p.unit_slabs || slab == p.slabs - 1;
       if (unit_end) {
         if (mine) {
@@ -709,6 +725,7 @@ gemv_tc_kernel(const GemvTcParams p) {
           units_mine = 0;
         }
       }
+      QX_PROF_ADD(c_unit, QX_PROF_NOW() - qx_tu_);
       // advance (tile, slab, unit) without divisions
       if (++slab == p.slabs) {
         slab = 0;
@@ -723,8 +740,13 @@ gemv_tc_kernel(const GemvTcParams p) {
     if (epi_thread == 0) QX_PROF_STAMP(14);
     resolve_pending();
     if (epi_thread == 0) {
+      QX_PROF_STAMP(27);
       QX_PROF_STORE(4, w_tfull);
       QX_PROF_STORE(6, QX_PROF_NOW() - t_start);
+      QX_PROF_STORE(1, c_vis);
+      QX_PROF_STORE(5, c_ld);
+      QX_PROF_STORE(7, c_math);
+      QX_PROF_STORE(8, c_unit);
     }
     if (!ok) {
       *abort_flag = 1;
@@ -746,6 +768,8 @@ gemv_tc_kernel(const GemvTcParams p) {
         ok = false;
         break;
       }
+      if (i == 0 && u == 0 && lane == 0) QX_PROF_STAMP(28);
+      if (i == count - 1 && u == 0 && lane == 0) QX_PROF_STAMP(29);
       if (i >= G::kWorkSlots) {  // the work slot's previous tile has been consumed
         if (!QX_PROF_WAIT(w_slot, mbar_wait(&bars->mma_done[work.slot], work.phase ^ 1u, abort_flag))) {
           ok = false;
@@ -948,13 +972,8 @@ template <int FMT, int MP>
 qx_status launch_one(const GemvTcParams& p, int grid, cudaStream_t stream) {
   constexpr size_t smem = gemv_smem_bytes<FMT, MP>();
   static_assert(smem <= kSmemLimit, "shared memory budget");
-  static bool attr_set = false;
-  if (!attr_set) {
-    QX_CUDA_TRY(cudaFuncSetAttribute(gemv_tc_kernel<FMT, MP>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(smem)));
-    attr_set = true;
-  }
+  static SmemOptIn opt_in;
+  QX_TRY(opt_in.ensure(gemv_tc_kernel<FMT, MP>, smem));
   // Programmatic dependent launch: this kernel may start while the kernel in front of it
   // (the activation quantizer, or whatever produces the activations) is still running.
   // Everything that does not depend on the activations (barrier set-up, TMEM allocation,
@@ -998,8 +1017,8 @@ long long* gemv_profile_buffer() {
 #ifdef QX_GEMV_PROFILE
   static long long* buffer = []() {
     long long* ptr = nullptr;
-    if (cudaMalloc(&ptr, 1024 * 32 * sizeof(long long)) != cudaSuccess) return static_cast<long long*>(nullptr);
-    (void)cudaMemset(ptr, 0, 1024 * 32 * sizeof(long long));
+    if (cudaMalloc(&ptr, 64 * 1024 * 32 * sizeof(long long)) != cudaSuccess) return static_cast<long long*>(nullptr);
+    (void)cudaMemset(ptr, 0, 64 * 1024 * 32 * sizeof(long long));
     return ptr;
   }();
   return buffer;
@@ -1080,6 +1099,12 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
     p.launch_counter = push->launch_counter;
   }
   p.debug = gemv_profile_buffer();
+#ifdef QX_GEMV_PROFILE
+  {
+    static int launch_seq = 0;
+    if (p.debug != nullptr) p.debug += static_cast<long long>(launch_seq++ % 64) * 1024 * 32;
+  }
+#endif
   if (w->format == QX_FORMAT_Q8_0) {
     return launch_fmt<QX_FORMAT_Q8_0>(padded_batch(m), p, scratch.ctas, stream);
   }
@@ -1093,13 +1118,13 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
 // host (32 values per CTA) and clears them.
 extern "C" QX_API int qx_debug_gemv_profile(long long* host_out, int ctas) {
   long long* buffer = qx::gemv_profile_buffer();
-  if (buffer == nullptr || ctas > 1024) return -1;
+  if (buffer == nullptr || ctas != 64 * 1024) return -1;
   if (cudaDeviceSynchronize() != cudaSuccess) return -2;
   if (cudaMemcpy(host_out, buffer, sizeof(long long) * 32 * ctas, cudaMemcpyDeviceToHost) !=
       cudaSuccess) {
     return -3;
   }
-  (void)cudaMemset(buffer, 0, 1024 * 32 * sizeof(long long));
+  (void)cudaMemset(buffer, 0, 64 * 1024 * 32 * sizeof(long long));
   return 0;
 }
 #endif

@@ -494,13 +494,8 @@ namespace {
 template <int NA>
 qx_status launch_tc_na(const CUtensorMap& map_w, const CUtensorMap& map_x, const TcParams& p,
                        int grid, cudaStream_t stream) {
-  static bool attr_set = false;
-  if (!attr_set) {
-    QX_CUDA_TRY(cudaFuncSetAttribute(int8_gemm_tc_kernel<NA>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(tc_smem_bytes(NA, 256))));
-    attr_set = true;
-  }
+  static SmemOptIn opt_in;
+  QX_TRY(opt_in.ensure(int8_gemm_tc_kernel<NA>, tc_smem_bytes(NA, 256)));
   int8_gemm_tc_kernel<NA><<<grid, kThreads, tc_smem_bytes(NA, p.bn), stream>>>(map_w, map_x, p);
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());

@@ -4,6 +4,9 @@
 // kernels/collectives/collectives_ref.cpp:26-37; the transport is plain peer stores from
 // the GEMV's row finishers (qx_gemv_tc.cu), no cluster multicast and no remote loads.
 
+#include <cstdlib>
+#include <cstring>
+
 #include "qx_gemv_tc.cuh"
 #include "qx_sm100.cuh"
 #include "qx_weights.cuh"
@@ -19,12 +22,18 @@ constexpr size_t kControlBytes = 256;
 
 // Lane r waits until rank r's slice of the next step has arrived (bounded), then lane 0
 // advances the local wait counter.
-__global__ void __launch_bounds__(32) allgather_wait_kernel(int* control, int world, int* error) {
+__global__ void __launch_bounds__(32) allgather_wait_kernel(int* control, int world, int* error,
+                                                            unsigned long long limit_ns) {
   // Launched programmatically: it may start while the GEMV in front of it still runs (it only
   // polls), and the kernel behind it may start its own set-up at once; whatever that kernel
   // reads of the gathered results it guards with griddepcontrol.wait, which returns when
   // this kernel has finished.
   asm volatile("griddepcontrol.launch_dependents;");
+  // The wait counter is advanced by the previous wait kernel of this chain, which may still
+  // be polling for a late peer when this one starts (the GEMV between the two triggers its
+  // dependents at its start): read it only after everything in front has finished. The GEMV
+  // in front sets this rank's own word at its very end, so this costs next to nothing.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int lane = threadIdx.x;
   const int expected = control[kWaitCountWord] + 1;
   bool ok = true;
@@ -34,16 +43,31 @@ __global__ void __launch_bounds__(32) allgather_wait_kernel(int* control, int wo
       int seen;
       asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(control + lane) : "memory");
       if (seen - expected >= 0) break;
-      if (sm100::global_timer_ns() - start > sm100::kWaitLimitNs) {
+      if (sm100::global_timer_ns() - start > limit_ns) {
         ok = false;
         break;
       }
-      __nanosleep(200);
+      // poll tightly while the slices are expected any moment, back off afterwards
+      if (sm100::global_timer_ns() - start > 20000ull) __nanosleep(200);
     }
   }
   if (!ok) sm100::report_error(error, 31);
   __syncwarp();
   if (lane == 0) control[kWaitCountWord] = expected;
+}
+
+// Time limit of the wait kernel: 2 s, or QX_B200_WAIT_LIMIT_MS milliseconds (1..10000) when
+// that is set in the environment (tests of the give-up path use a few milliseconds).
+unsigned long long wait_limit_ns() {
+  static const unsigned long long limit = []() -> unsigned long long {
+    const char* text = std::getenv("QX_B200_WAIT_LIMIT_MS");
+    if (text != nullptr) {
+      const long ms = std::strtol(text, nullptr, 10);
+      if (ms >= 1 && ms <= 10000) return static_cast<unsigned long long>(ms) * 1000000ull;
+    }
+    return sm100::kWaitLimitNs;
+  }();
+  return limit;
 }
 
 qx_status check_plan(const qx_push_plan* plan) {
@@ -178,7 +202,7 @@ qx_status qx_allgather_wait_dev(const qx_push_plan* plan, long long m, long long
   config.attrs = &attribute;
   config.numAttrs = 1;
   QX_CUDA_TRY(cudaLaunchKernelEx(&config, allgather_wait_kernel, static_cast<int*>(plan->control_local),
-                                 plan->world, ctx->error_dev));
+                                 plan->world, ctx->error_dev, wait_limit_ns()));
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
   if (results_dev != nullptr) {

@@ -433,12 +433,8 @@ qx_status launch_tc(const qx_weights* w, const uint16_t* x_bf16_dev, float* y_de
   p.o_tiles = static_cast<int>(w->tiles);
   p.r_tiles = static_cast<int>((m + bn - 1) / bn);
   p.error = ctx->error_dev;
-  static bool attr_set = false;
-  if (!attr_set) {
-    QX_CUDA_TRY(cudaFuncSetAttribute(q4_gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kQ4GemmSmem)));
-    attr_set = true;
-  }
+  static SmemOptIn opt_in;
+  QX_TRY(opt_in.ensure(q4_gemm_tc_kernel, kQ4GemmSmem));
   const long long tiles = static_cast<long long>(p.o_tiles) * p.r_tiles;
   const int grid = static_cast<int>(tiles < ctx->prop.multiProcessorCount
                                         ? tiles

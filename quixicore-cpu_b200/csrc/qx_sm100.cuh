@@ -18,7 +18,10 @@ constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 // Upper bound the hardware may keep a waiting thread suspended inside one try_wait (it
 // wakes at once when the barrier phase completes): waiting warps then take no issue
 // slots from the warps that have work.
-constexpr uint32_t kSuspendHintNs = 1000000u;
+#ifndef QX_SUSPEND_HINT_NS
+#define QX_SUSPEND_HINT_NS 1000000u
+#endif
+constexpr uint32_t kSuspendHintNs = QX_SUSPEND_HINT_NS;
 
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
@@ -57,6 +60,15 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
+#if QX_SUSPEND_HINT_NS == 0
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+#else
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
@@ -64,6 +76,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(done)
       : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
+#endif
   return done != 0;
 }
 // Bounded wait. Returns false when the limit ran out or *abort_flag became non-zero.
@@ -200,6 +213,7 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
 #define QX_PROF_NOW() clock64()
 #define QX_PROF_BEGIN() const long long qx_tb_ = clock64()
 #define QX_PROF_END(counter) counter += clock64() - qx_tb_
+#define QX_PROF_ADD(counter, value) counter += (value)
 #define QX_PROF_STAMP(slot) \
   if (p.debug != nullptr) p.debug[blockIdx.x * 32 + (slot)] = static_cast<long long>(sm100::global_timer_ns())
 #else
@@ -209,6 +223,7 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
 #define QX_PROF_NOW() 0
 #define QX_PROF_BEGIN()
 #define QX_PROF_END(counter)
+#define QX_PROF_ADD(counter, value)
 #define QX_PROF_STAMP(slot)
 #endif
 

@@ -197,8 +197,12 @@ qx_status qx_weights_get_info(const qx_weights* w, qx_weights_info* info) {
   info->preparation_ns = w->preparation_ns;
   info->device = w->device;
   info->has_dense_bf16 = w->dense_cache != nullptr ? 1 : 0;
+  info->row_tile = qx::kTileRows;
+  info->panel_bytes = w->panel_bytes();
   return QX_STATUS_OK;
 }
+
+const void* qx_weights_panel_dev(const qx_weights* w) { return w == nullptr ? nullptr : w->panel; }
 
 void qx_weights_destroy(qx_weights* w) {
   if (w == nullptr) return;

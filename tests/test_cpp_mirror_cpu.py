@@ -41,6 +41,18 @@ PROGRAM = textwrap.dedent(r"""
       CHECK(weights.prepare(QuantFormat::kQ8_0, nullptr, 1, 32) == Status::kInvalidArgument);
       CHECK(weights.prepare(QuantFormat::kQ8_0, packed, 1, 31) == Status::kInvalidShape);
       CHECK(qgemm_prepacked(weights, x, y, 1) == Status::kInvalidArgument);  // not ready
+      // the reference's layout enumerators (include/quixicore_cpu/packed_weights.h:14-20) and
+      // the info fields a caller may name
+      static_assert(static_cast<int>(CpuPanelLayout::kAuto) == 0 &&
+                    static_cast<int>(CpuPanelLayout::kPortableRows1) == 1 &&
+                    static_cast<int>(CpuPanelLayout::kNeonRows4) == 2 &&
+                    static_cast<int>(CpuPanelLayout::kAvx2Rows8) == 3 &&
+                    static_cast<int>(CpuPanelLayout::kAvx512Rows16) == 4, "layout values");
+      CHECK(weights.prepare(QuantFormat::kQ8_0, nullptr, 1, 32, CpuPanelLayout::kAvx512Rows16) ==
+            Status::kInvalidArgument);
+      const CpuPackedWeightsInfo blank = weights.info();
+      CHECK(blank.layout == CpuPanelLayout::kAuto && blank.row_tile == 0 && blank.panel_bytes == 0);
+      CHECK(weights.contract_data() == nullptr && weights.panel_data() == nullptr);
       CpuPackedWeights moved = std::move(weights);
       CHECK(!moved.ready() && moved.info().rows == 0);
       set_num_threads(4);
