@@ -78,6 +78,10 @@ struct TcGeom {
   // one entry per weight slot, because they are needed longer (until the epilogue has
   // read them) than the operands of the MMAs.
   static constexpr int kConstBytes = 128 * MP;
+  // ... a ring indexed by the CTA-local slab number, deep enough that the quantizer warps
+  // (at most kWorkSlots slabs ahead of the MMAs) never lap the epilogue (at most the
+  // accumulator ring behind the MMAs); checked below
+  static constexpr int kConstSlots = kFused ? (MP == 1 ? 32 : 16) : 0;
   // Images that come from the quantizer kernel travel with the weights (copied as far
   // ahead); images built in the kernel sit in the work slot.
   static constexpr int kSlotBytes = kWBytes + (kFused ? 0 : (kXBytes + 1023) / 1024 * 1024);
@@ -87,7 +91,7 @@ struct TcGeom {
   static constexpr int kQuantWarps = 3;  // == kWorkSlots when the kernel quantizes itself
   static constexpr int kXRingSlots = 4;  // per quantizer warp
   static constexpr int kXRingBytes = kFused ? kQuantWarps * kXRingSlots * MP * kSlabK * 4 : 0;
-  static constexpr int kBudget = kSmemLimit - 1024 - 2048 - (kFused ? 8 * kConstBytes : 0) -
+  static constexpr int kBudget = kSmemLimit - 1024 - 2048 - kConstSlots * kConstBytes -
                                  kXRingBytes;  // slack, barriers, constants, activation ring
   // the in-kernel quantizer has one work slot per quantizer warp; otherwise three work slots
   // unless that costs more than one weight slot
@@ -107,15 +111,24 @@ struct TcGeom {
   static constexpr int kStagesPerSlab = kGroups / kGroupsPerStage;
   static constexpr int kTCols = kN * kGroupsPerStage;  // TMEM columns per stage
   static constexpr int kTStages = 512 / kTCols > 16 ? 16 : 512 / kTCols;
+  // Epilogue sets take the K units in turn (unit mod kSets); which set sums a unit does not
+  // matter for the result (unit sums meet in scratch memory and are added in a fixed order).
+  // Decode batches are bound by the per-slab latency of an epilogue thread (barrier waits,
+  // TMEM load, a dependent chain per block), so a single activation row gets three sets; batches two (three
+  // would leave them too few registers per thread).
+#ifndef QX_GEMV_SETS1
+#define QX_GEMV_SETS1 3
+#endif
+  static constexpr int kSets = MP == 1 ? QX_GEMV_SETS1 : 2;
   // Each epilogue set has its own ring of accumulators, so every TMEM barrier is used by
   // one set only (a parity wait cannot tell apart phases two steps apart).
-  static constexpr int kTPerSet = kTStages / 2;
+  static constexpr int kTPerSet = kTStages / kSets;
   // Epilogue: two sets (alternate K units) of four warps (one per TMEM lane quarter); q8_0
   // batches of 16 double that, the two warps of a quarter taking half of the activation rows
   // each (the epilogue's instruction count bounds big batches; at 32 rows the extra warps
   // cost more registers than they bring).
   static constexpr int kEpiSplit = (MP == 16 && !kQ4) ? 2 : 1;
-  static constexpr int kEpiWarps = 8 * kEpiSplit;
+  static constexpr int kEpiWarps = 4 * kSets * kEpiSplit;
   static constexpr int kRowsPerThread = MP / kEpiSplit;  // activation rows per epilogue thread
   static constexpr int kUnpackWarps = kQ4 ? 4 : 0;
   static constexpr int kFirstUnpackWarp = 2 + kEpiWarps;
@@ -127,8 +140,13 @@ struct TcGeom {
   static constexpr int kLdCols = kColsPerWarp >= 64 ? 64 : 32;  // columns fetched per TMEM wait
   static_assert(kEpiSplit == 1 || (kGroupsPerStage == 1 && kG == 1), "split stages hold one block");
   static constexpr bool kRollGroups = MP >= 8;
-  static_assert(kSlots >= 2 && kTPerSet >= 1 && kN >= 32 && kN <= 256, "geometry");
+  static_assert(kSlots + kWorkSlots + kTStages + kConstSlots <= kThreads - 64, "one barrier group per thread");
+  static_assert(kSlots >= 2 && kTPerSet >= 1 && kTPerSet <= 15 && kN >= 32 && kN <= 256, "geometry");
+  static_assert(!kFused || kSlots > kWorkSlots, "a work slot's previous slab is newer than a weight slot's");
   static_assert(!kFused || kWorkSlots == kQuantWarps, "one quantizer warp per work slot");
+  // (depth only matters for speed: an entry is rewritten after the epilogue has released it)
+  static_assert(!kFused || kConstSlots >= kWorkSlots + kTStages / kStagesPerSlab + 4,
+                "constants ring deeper than quantizer lead + epilogue lag");
   static_assert(kScaleOffset + kSlabScaleBytes == kWBytes && kWBytes % 1024 == 0, "span");
 };
 
@@ -144,7 +162,8 @@ struct GemvTcParams {
   int m, slabs, tiles, nb;
   int x_vector;                  // x and ldx allow 16-byte loads
   int unit_slabs, units_per_tile;  // K split: units of unit_slabs slabs
-  long long total_units;
+  // unit ranges of the CTAs: CTA c takes units_per_cta units, the first units_rem CTAs one more
+  uint32_t units_per_cta, units_rem;
   // Row-sharded runs (one process per GPU): the finished outputs are also stored straight
   // into the other ranks' result buffers over NVLink, and the last CTA of the launch tells
   // every rank that this rank's slice is complete (an all-gather fused into the epilogue).
@@ -170,6 +189,10 @@ struct __align__(8) GemvBarriers {
   // their parts. One barrier for the MMA issuer instead of one per producer.
   uint64_t ready[TcGeom<FMT, MP>::kSlots];
   uint64_t mma_done[TcGeom<FMT, MP>::kWorkSlots];   // the slab's MMAs have read the work slot
+  // the block constants of CTA-local slab i are written (entry i mod kConstSlots)
+  uint64_t const_ready[TcGeom<FMT, MP>::kConstSlots > 0 ? TcGeom<FMT, MP>::kConstSlots : 1];
+  // ... and the epilogue set that used them is through with them
+  uint64_t const_free[TcGeom<FMT, MP>::kConstSlots > 0 ? TcGeom<FMT, MP>::kConstSlots : 1];
   uint64_t tmem_full[TcGeom<FMT, MP>::kTStages];
   uint64_t tmem_empty[TcGeom<FMT, MP>::kTStages];
   uint32_t tmem_base;
@@ -186,11 +209,6 @@ __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gsrc, 
 }
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-
-// start of CTA c's unit range
-__device__ __forceinline__ long long range_start(long long c, long long total, long long ctas) {
-  return c * total / ctas;
 }
 
 // Ring position i mod `slots` with the parity of i / slots.
@@ -310,7 +328,7 @@ gemv_tc_kernel(const GemvTcParams p) {
   uint8_t* work_ring = smem + G::kSlots * G::kSlotBytes;  // slot: [masked bytes (q4_0) | digits]
   // block constants of the slab in each weight slot (only when the kernel quantizes itself)
   uint8_t* const_ring = work_ring + G::kWorkSlots * G::kWorkBytes;
-  uint8_t* x_ring = const_ring + (G::kFused ? G::kSlots * G::kConstBytes : 0);
+  uint8_t* x_ring = const_ring + G::kConstSlots * G::kConstBytes;
   auto* bars = reinterpret_cast<GemvBarriers<FMT, MP>*>(x_ring + G::kXRingBytes);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -320,21 +338,62 @@ gemv_tc_kernel(const GemvTcParams p) {
   asm volatile("griddepcontrol.launch_dependents;");
   if (threadIdx.x == 0) QX_PROF_STAMP(10);
 
+  // This CTA's contiguous range of K units (32-bit arithmetic only: it sits in front of the
+  // first weight copy). Units tile every row tile's slabs contiguously, so the range is one
+  // contiguous range of global slabs (tile * slabs + slab).
+  const uint32_t cta = blockIdx.x;
+  const uint32_t u_begin = cta * p.units_per_cta + (cta < p.units_rem ? cta : p.units_rem);
+  const uint32_t u_end = u_begin + p.units_per_cta + (cta < p.units_rem ? 1u : 0u);
+  long long s_begin = 0, s_end = 0;
+  int tile0 = 0, slab0 = 0;  // row tile and K-slab (within the tile) of the range's first slab
+  if (u_end > u_begin) {
+    const uint32_t upt = static_cast<uint32_t>(p.units_per_tile);
+    const uint32_t tile_b = u_begin / upt, last = u_end - 1, tile_l = last / upt;
+    const int last_end = static_cast<int>(last - tile_l * upt + 1) * p.unit_slabs;
+    tile0 = static_cast<int>(tile_b);
+    slab0 = static_cast<int>(u_begin - tile_b * upt) * p.unit_slabs;
+    s_begin = static_cast<long long>(tile_b) * p.slabs + slab0;
+    s_end = static_cast<long long>(tile_l) * p.slabs + (last_end < p.slabs ? last_end : p.slabs);
+  }
+  const int count = static_cast<int>(s_end - s_begin);  // slabs of this CTA
+
+  // copy producer state (thread 0): next span to copy and the activation image that goes with it
+  constexpr uint32_t kTxBytes = G::kWBytes + (G::kFused ? 0 : G::kXBytes);
+  const uint8_t* wsrc = p.panel + s_begin * G::kWBytes;
+  const int ahead = count < G::kSlots ? count : G::kSlots;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < G::kSlots; ++s) {
-      mbar_init(&bars->raw_full[s], 1);  // the producer's expect_tx arrival
-      // one epilogue set: it has seen the slab's last accumulator, so the MMAs are done too
-      mbar_init(&bars->done[s], 4 * G::kEpiSplit);
-      mbar_init(&bars->ready[s], G::kReadyCount > 0 ? G::kReadyCount : 1);
-    }
-    for (int s = 0; s < G::kWorkSlots; ++s) {
-      mbar_init(&bars->mma_done[s], 1);
-    }
-    for (int t = 0; t < G::kTStages; ++t) {
-      mbar_init(&bars->tmem_full[t], 1);
-      mbar_init(&bars->tmem_empty[t], 4 * G::kEpiSplit);
-    }
+    // The weights depend on nothing in front of this kernel: the first copies leave before
+    // the rest of the CTA is set up (the other barriers, TMEM allocation, zero fill, the
+    // block-wide barrier). Initialising a barrier costs tens of cycles, so this thread does
+    // only the ones its copies complete on.
+    for (int s = 0; s < G::kSlots; ++s) mbar_init(&bars->raw_full[s], 1);  // expect_tx arrival
     bars->abort_flag = 0;
+    mbar_fence_init();
+    QX_PROF_STAMP(24);
+    for (int i = 0; i < ahead; ++i) {
+      mbar_arrive_expect_tx(&bars->raw_full[i], kTxBytes);
+      bulk_copy_g2s(smem + i * G::kSlotBytes, wsrc, G::kWBytes, &bars->raw_full[i]);
+      wsrc += G::kWBytes;
+    }
+  } else if (threadIdx.x >= 64) {
+    // every other barrier, one per thread
+    const int b = threadIdx.x - 64;
+    constexpr uint32_t kSetArrivals = 4 * G::kEpiSplit;  // the warps of one epilogue set
+    if (b < G::kSlots) {
+      // one epilogue set: it has seen the slab's last accumulator, so the MMAs are done too
+      mbar_init(&bars->done[b], kSetArrivals);
+      mbar_init(&bars->ready[b], G::kReadyCount > 0 ? G::kReadyCount : 1);
+    } else if (b < G::kSlots + G::kWorkSlots) {
+      mbar_init(&bars->mma_done[b - G::kSlots], 1);
+    } else if (b < G::kSlots + G::kWorkSlots + G::kTStages) {
+      const int t = b - G::kSlots - G::kWorkSlots;
+      mbar_init(&bars->tmem_full[t], 1);
+      mbar_init(&bars->tmem_empty[t], kSetArrivals);
+    } else if (b < G::kSlots + G::kWorkSlots + G::kTStages + G::kConstSlots) {
+      const int c = b - G::kSlots - G::kWorkSlots - G::kTStages;
+      mbar_init(&bars->const_ready[c], 1);
+      mbar_init(&bars->const_free[c], kSetArrivals);
+    }
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -355,38 +414,15 @@ gemv_tc_kernel(const GemvTcParams p) {
   const uint32_t tmem_base = bars->tmem_base;
   if (threadIdx.x == 0) QX_PROF_STAMP(11);
 
-  const long long u_begin = range_start(blockIdx.x, p.total_units, gridDim.x);
-  const long long u_end = range_start(blockIdx.x + 1LL, p.total_units, gridDim.x);
-  // units tile every row tile's slabs contiguously, so a CTA's units are one contiguous
-  // range of global slabs (tile * slabs + slab)
-  long long s_begin = 0, s_end = 0;
-  if (u_end > u_begin) {
-    const long long last = u_end - 1;
-    const int last_end = static_cast<int>(last % p.units_per_tile + 1) * p.unit_slabs;
-    s_begin = (u_begin / p.units_per_tile) * p.slabs + (u_begin % p.units_per_tile) * p.unit_slabs;
-    s_end = (last / p.units_per_tile) * p.slabs + (last_end < p.slabs ? last_end : p.slabs);
-  }
-  const int count = static_cast<int>(s_end - s_begin);  // slabs of this CTA
-
   if (warp == 0) {
     // ------------------------------ copy producer -----------------------------
     // Slab i uses weight slot i mod kSlots, free again when slab i - kSlots is done.
     if (lane == 0) {
       bool ok = true;
       QX_PROF_DECL(w_empty);
-      constexpr uint32_t kTxBytes = G::kWBytes + (G::kFused ? 0 : G::kXBytes);
-      const uint8_t* wsrc = p.panel + s_begin * G::kWBytes;
-      int xslab = static_cast<int>(s_begin % p.slabs);
-      // The weights do not depend on the kernel in front of this one: start the first
-      // copies at once, and only then wait for the activation images.
-      const int ahead = count < G::kSlots ? count : G::kSlots;
-      QX_PROF_STAMP(24);
-      for (int i = 0; i < ahead; ++i) {
-        mbar_arrive_expect_tx(&bars->raw_full[i], kTxBytes);
-        bulk_copy_g2s(smem + i * G::kSlotBytes, wsrc, G::kWBytes, &bars->raw_full[i]);
-        wsrc += G::kWBytes;
-      }
+      int xslab = slab0;
       if (!G::kFused) {
+        // the activation images are the output of the kernel in front of this one
         asm volatile("griddepcontrol.wait;" ::: "memory");
         QX_PROF_STAMP(12);
         for (int i = 0; i < ahead; ++i) {
@@ -427,21 +463,24 @@ gemv_tc_kernel(const GemvTcParams p) {
                              (static_cast<uint32_t>(G::kN >> 3) << 17) |
                              (static_cast<uint32_t>(kTileRows >> 4) << 24);
       RingPos raw, work;
-      uint32_t pos0 = 0, pos1 = 0, par0 = 0, par1 = 0;  // accumulator ring of each epilogue set
+      uint32_t ring_pos_all = 0, ring_par_all = 0;  // accumulator ring of each epilogue set: 4 bits each
       bool ok = true;
       int gave_up = 12;  // which wait ran out: 12 weights, 15 image, 16 accumulator, 17 high nibbles
       QX_PROF_DECL(w_full);
       QX_PROF_DECL(w_tempty);
       QX_PROF_DECL(w_x);
       QX_PROF_DECL(w_high);
-      int slab = static_cast<int>(s_begin % p.slabs);
+      int slab = slab0;
       int unit = slab / p.unit_slabs;
       int slab_in_unit = slab - unit * p.unit_slabs;
       for (int i = 0; i < count && ok; ++i) {
-        const uint32_t eset = static_cast<uint32_t>(unit & 1);
-        if (!QX_PROF_WAIT(w_full, mbar_wait(G::kReadyCount > 0 ? &bars->ready[raw.slot]
-                                                                : &bars->raw_full[raw.slot],
-                                            raw.phase, abort_flag))) {
+        const uint32_t eset = static_cast<uint32_t>(unit % G::kSets);
+        // `ready` covers the span only where the masking warps (which wait for it) arrive on
+        // it; the quantizer warps run ahead of the copies
+        if ((G::kUnpackWarps == 0 &&
+             !QX_PROF_WAIT(w_full, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) ||
+            (G::kReadyCount > 0 &&
+             !QX_PROF_WAIT(w_full, mbar_wait(&bars->ready[raw.slot], raw.phase, abort_flag)))) {
           ok = false;
           break;
         }
@@ -451,8 +490,8 @@ gemv_tc_kernel(const GemvTcParams p) {
         const uint32_t sb = G::kFused ? sw + G::kHBytes : sa + G::kWBytes;  // digit rows
 #pragma unroll
         for (int g = 0; g < G::kGroups; ++g) {
-          const uint32_t pos = eset != 0u ? pos1 : pos0;
-          const uint32_t par = eset != 0u ? par1 : par0;
+          const uint32_t pos = (ring_pos_all >> (4u * eset)) & 15u;
+          const uint32_t par = (ring_par_all >> (4u * eset)) & 1u;
           const uint32_t ts = eset * G::kTPerSet + pos;
           if (g % G::kGroupsPerStage == 0) {
             if (!QX_PROF_WAIT(w_tempty, mbar_wait(&bars->tmem_empty[ts], par ^ 1u, abort_flag))) {
@@ -496,13 +535,8 @@ gemv_tc_kernel(const GemvTcParams p) {
             tc_commit(&bars->tmem_full[ts]);
             const uint32_t next = pos + 1 == G::kTPerSet ? 0u : pos + 1;
             const uint32_t flip = pos + 1 == G::kTPerSet ? 1u : 0u;
-            if (eset != 0u) {
-              pos1 = next;
-              par1 ^= flip;
-            } else {
-              pos0 = next;
-              par0 ^= flip;
-            }
+            ring_pos_all = (ring_pos_all & ~(15u << (4u * eset))) | (next << (4u * eset));
+            ring_par_all ^= flip << (4u * eset);
           }
         }
         if (!ok) break;
@@ -530,8 +564,8 @@ gemv_tc_kernel(const GemvTcParams p) {
     }
   } else if (warp < 2 + G::kEpiWarps) {
     // ------------------------------ epilogue ----------------------------------
-    // Two sets of four warps; set e takes the K units with (unit & 1) == e, so while one
-    // set waits on barriers, TMEM loads and conversions the other one issues.
+    // kSets sets of four warps; set e takes the K units with unit mod kSets == e, so while one
+    // set waits on barriers, TMEM loads and conversions the others issue.
     const int eset = (warp - 2) / (4 * G::kEpiSplit);
     const int split = ((warp - 2) >> 2) % G::kEpiSplit;  // which share of the activation rows
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are this warp's
@@ -542,45 +576,71 @@ gemv_tc_kernel(const GemvTcParams p) {
 #pragma unroll
     for (int m = 0; m < kMine; ++m) acc[m] = 0.0f;
     int units_mine = 0;  // units of the current tile this thread has written
-    // deferred completion check of the last counted share
-    int pend_old = 0, pend_add = 0, pend_tile = 0;
-    auto resolve_pending = [&]() {
-      if (pend_add > 0 && pend_old + pend_add == p.units_per_tile * G::kEpiSplit) {
-        // this thread completed the row: add its unit sums in the fixed order
-        // (pushing launches alternate between two result buffers by the parity of their
-        // step; the counter is read here, after data has flowed through the pipeline, i.e.
-        // after the launch in front of this one has completed and advanced it)
-        const bool push_odd = p.peers > 0 && ((__ldcg(p.push_count) + 1) & 1) != 0;
-        const long long row = static_cast<long long>(pend_tile) * kTileRows + row_in_tile;
-        const float* slots = p.partial +
-                             static_cast<long long>(pend_tile) * p.units_per_tile * p.m * kTileRows +
-                             row_in_tile;
-        for (int m = 0; m < p.m; ++m) {
-          // units_per_tile <= 16: fetch all unit sums first (independent loads), then add
-          // the even and the odd ones in ascending order
-          float v[16];
+    // A share of a row = this thread's units of one tile. Counting a share in on the row's
+    // counter needs a fence (the unit sums must be visible before the count), and a fence
+    // waits for the thread's outstanding stores: right after the last unit sum was stored
+    // that is a microsecond, a slab later it is nearly free. So a finished share stays
+    // "open" until the end of this thread's next slab, is counted in there (the atomic's
+    // result is not looked at yet) and resolved another slab later -- only the last share of
+    // the CTA's range pays the full latency, after the loop.
+    int open_tile = 0, open_add = 0;              // written, not counted in
+    int cnt_tile = 0, cnt_add = 0, cnt_old = 0;   // counted in, result not looked at
+    // this thread completed the row's count in `tile`: add its unit sums in the fixed order
+    auto finish_row = [&](int done_tile) {
+      // (pushing launches alternate between two result buffers by the parity of their
+      // step; the counter is read here, after data has flowed through the pipeline, i.e.
+      // after the launch in front of this one has completed and advanced it)
+      const bool push_odd = p.peers > 0 && ((__ldcg(p.push_count) + 1) & 1) != 0;
+      const long long row = static_cast<long long>(done_tile) * kTileRows + row_in_tile;
+      const float* slots = p.partial +
+                           static_cast<long long>(done_tile) * p.units_per_tile * p.m * kTileRows +
+                           row_in_tile;
+      for (int m = 0; m < p.m; ++m) {
+        // units_per_tile <= 16: fetch all unit sums first (independent loads), then add
+        // the even and the odd ones in ascending order
+        float v[16];
 #pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            v[u] = u < p.units_per_tile
-                       ? __ldcg(slots + (static_cast<long long>(u) * p.m + m) * kTileRows)
-                       : 0.0f;
-          }
-          float even = 0.0f, odd = 0.0f;
-#pragma unroll
-          for (int u = 0; u < 16; u += 2) {
-            if (u < p.units_per_tile) even += v[u];
-            if (u + 1 < p.units_per_tile) odd += v[u + 1];
-          }
-          if (row < p.rows) {
-            const float value = even + odd;
-            const long long at = m * p.ldy + row;
-            (push_odd ? p.y_odd : p.y)[at] = value;
-            for (int r = 0; r < p.peers; ++r) (push_odd ? p.y_peer_odd[r] : p.y_peer[r])[at] = value;
-          }
+        for (int u = 0; u < 16; ++u) {
+          v[u] = u < p.units_per_tile
+                     ? __ldcg(slots + (static_cast<long long>(u) * p.m + m) * kTileRows)
+                     : 0.0f;
         }
-        p.counters[static_cast<long long>(pend_tile) * kTileRows + row_in_tile] = 0;  // next launch
+        float even = 0.0f, odd = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 16; u += 2) {
+          if (u < p.units_per_tile) even += v[u];
+          if (u + 1 < p.units_per_tile) odd += v[u + 1];
+        }
+        if (row < p.rows) {
+          const float value = even + odd;
+          const long long at = m * p.ldy + row;
+          (push_odd ? p.y_odd : p.y)[at] = value;
+          for (int r = 0; r < p.peers; ++r) (push_odd ? p.y_peer_odd[r] : p.y_peer[r])[at] = value;
+        }
       }
-      pend_add = 0;
+      p.counters[static_cast<long long>(done_tile) * kTileRows + row_in_tile] = 0;  // next launch
+    };
+    // Whoever completes a row's count adds its unit sums (acquire). Rows are independent,
+    // so no thread ever waits for another one.
+    auto resolve_counted = [&]() {
+      if (cnt_add > 0 && cnt_old + cnt_add == p.units_per_tile * G::kEpiSplit) {
+        asm volatile("fence.acq_rel.gpu;" ::: "memory");
+        finish_row(cnt_tile);
+      }
+      cnt_add = 0;
+    };
+    auto count_open = [&]() {
+      if (open_add == 0) return;
+      resolve_counted();
+      int* counter = p.counters + static_cast<long long>(open_tile) * kTileRows + row_in_tile;
+      asm volatile("fence.acq_rel.gpu;" ::: "memory");  // release: the share's unit sums
+      asm volatile("atom.add.relaxed.gpu.global.s32 %0, [%1], %2;"
+                   : "=r"(cnt_old)
+                   : "l"(counter), "r"(open_add)
+                   : "memory");
+      cnt_tile = open_tile;
+      cnt_add = open_add;
+      open_add = 0;
     };
     RingPos raw, work;
     uint32_t ring_pos = 0, tphase = 0;
@@ -591,16 +651,16 @@ gemv_tc_kernel(const GemvTcParams p) {
     QX_PROF_DECL(c_math);
     QX_PROF_DECL(c_unit);
     const long long t_start = QX_PROF_NOW();
-    int tile = static_cast<int>(s_begin / p.slabs);
-    int slab = static_cast<int>(s_begin - static_cast<long long>(tile) * p.slabs);
+    int tile = tile0;
+    int slab = slab0;
     int unit = slab / p.unit_slabs;
     int slab_in_unit = slab - unit * p.unit_slabs;
     for (int i = 0; i < count && ok; ++i) {
-      const bool mine = (unit & 1) == eset;
+      const bool mine = unit % G::kSets == eset;
       if (mine) {
         const uint8_t* raw_base = smem + raw.slot * G::kSlotBytes;
         const int4* xcs = reinterpret_cast<const int4*>(
-            G::kFused ? const_ring + raw.slot * G::kConstBytes
+            G::kFused ? const_ring + (i % (G::kConstSlots > 0 ? G::kConstSlots : 1)) * G::kConstBytes
                       : raw_base + G::kWBytes + G::kBBytes);
         uint32_t scw[4] = {0u, 0u, 0u, 0u};  // this row's eight fp16 block scales
         // (large batches keep the loop over accumulators rolled: unrolled, the loop body
@@ -617,11 +677,14 @@ gemv_tc_kernel(const GemvTcParams p) {
           QX_PROF_BEGIN();
           if (st == 0) {
             // these barriers completed before the MMAs ran; waiting on them here makes the
-            // copied scales and the block constants visible to this thread
-            // (the in-kernel quantizer's work slot may already hold a later slab: its
-            // constants have a barrier with the lifetime of the weight slot)
+            // copied scales and the block constants visible to this thread (the constants
+            // of the in-kernel quantizer have a ring and barriers of their own, indexed by
+            // the slab number: no other barrier of theirs is safe to wait on this late)
             if (!mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag) ||
-                (G::kFused && !mbar_wait(&bars->ready[raw.slot], raw.phase, abort_flag))) {
+                (G::kFused &&
+                 !mbar_wait(&bars->const_ready[i % (G::kConstSlots > 0 ? G::kConstSlots : 1)],
+                            static_cast<uint32_t>(i / (G::kConstSlots > 0 ? G::kConstSlots : 1)) & 1u,
+                            abort_flag))) {
               ok = false;
               break;
             }
@@ -665,8 +728,9 @@ gemv_tc_kernel(const GemvTcParams p) {
                 const int s1 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 1) & 31]);
                 const int s2 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 2) & 31]);
                 const int s3 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 3) & 31]);
-                const float sum = kQ4 ? block_sum(s0, s1, s2, s3, xc.y, xc.z)
-                                      : block_sum(s0, s1, s2);
+                const float sum =
+                    G::kFused ? (kQ4 ? block_sum_cvt(s0, s1, s2, s3, xc.y, xc.z) : block_sum_cvt(s0, s1, s2))
+                              : (kQ4 ? block_sum(s0, s1, s2, s3, xc.y, xc.z) : block_sum(s0, s1, s2));
                 const float d = half_bits_to_float(
                     G::kRollGroups
                         ? *reinterpret_cast<const unsigned short*>(
@@ -684,7 +748,11 @@ gemv_tc_kernel(const GemvTcParams p) {
         }
         if (!ok) break;
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->done[raw.slot]);  // scales / constants consumed
+        if (epi_thread == 0 && i / G::kSets < 10) QX_PROF_STAMP2(i / G::kSets);
+        if (lane == 0) {
+          mbar_arrive(&bars->done[raw.slot]);  // scales consumed
+          if (G::kFused) mbar_arrive(&bars->const_free[i % (G::kConstSlots > 0 ? G::kConstSlots : 1)]);
+        }
       }
       raw.advance(G::kSlots);
       work.advance(G::kWorkSlots);
@@ -695,6 +763,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       const bool unit_end = slab_in_unit + 1 == p.unit_slabs || slab == p.slabs - 1;
       if (unit_end) {
         if (mine) {
+          count_open();  // an older share: its unit sums were stored a slab or more ago
           float* part = p.partial +
                         (static_cast<long long>(tile) * p.units_per_tile + unit) * p.m * kTileRows +
                         row_in_tile;
@@ -708,19 +777,11 @@ gemv_tc_kernel(const GemvTcParams p) {
         }
         const bool share_end = slab == p.slabs - 1 || i == count - 1;
         if (share_end) {
-          // Count this thread's units of the row in on the row's counter (release: the unit
-          // sums above are published with it); whoever completes the count finishes the row
-          // (acquire). Rows are independent, so no thread ever waits for another one here,
-          // and the result of the atomic is only looked at one share later (or after the loop).
-          resolve_pending();
+          // this thread's units of the row are written: the share is counted in a slab later
           if (units_mine > 0) {
-            int* counter = p.counters + static_cast<long long>(tile) * kTileRows + row_in_tile;
-            asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;"
-                         : "=r"(pend_old)
-                         : "l"(counter), "r"(units_mine)
-                         : "memory");
-            pend_add = units_mine;
-            pend_tile = tile;
+            count_open();  // (only if this slab was not `mine`: at most one share stays open)
+            open_tile = tile;
+            open_add = units_mine;
           }
           units_mine = 0;
         }
@@ -738,7 +799,8 @@ gemv_tc_kernel(const GemvTcParams p) {
       }
     }
     if (epi_thread == 0) QX_PROF_STAMP(14);
-    resolve_pending();
+    count_open();
+    resolve_counted();
     if (epi_thread == 0) {
       QX_PROF_STAMP(27);
       QX_PROF_STORE(4, w_tfull);
@@ -813,7 +875,7 @@ gemv_tc_kernel(const GemvTcParams p) {
     const int qw = warp - G::kQuantWarp;
     bool ok = true;
     const int b = lane >> 2, q = lane & 3;
-    const int first_slab = static_cast<int>((s_begin + qw) % p.slabs);
+    const int first_slab = (slab0 + qw) % p.slabs;
     const int step = kW % p.slabs;  // slabs wrap around at the end of a row tile
     int copy_slab = first_slab, use_slab = first_slab;
     int copy_i = qw;  // CTA-local index of the next slab to copy
@@ -895,25 +957,30 @@ gemv_tc_kernel(const GemvTcParams p) {
       use_slab += step;
       if (use_slab >= p.slabs) use_slab -= p.slabs;
       use_entry = use_entry + 1 == G::kXRingSlots ? 0 : use_entry + 1;
-      // The MMAs of this work slot's previous slab have read its digits. The weights of slab
-      // i have landed in their slot, so the slab that used the slot (and its constants)
-      // before is done; the wait on mma_done made sure this is not an older phase.
+      // The MMAs of this work slot's previous slab have read its digits. Nothing here waits
+      // for the weights: the images are built up to kWorkSlots slabs ahead of the MMAs. That
+      // previous slab is i - kWorkSlots > i - kSlots, so the `ready` barrier of slab i's
+      // weight slot has long moved on to this slab's phase; the constants go to entry
+      // i mod kConstSlots once the epilogue has released its previous user.
       if ((slot_uses > 0 &&
            !QX_PROF_WAIT(w_free, mbar_wait(&bars->mma_done[qw], (slot_uses - 1u) & 1u, abort_flag))) ||
-          !QX_PROF_WAIT(w_free, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) {
+          (i >= G::kConstSlots &&
+           !mbar_wait(&bars->const_free[i % G::kConstSlots],
+                      (static_cast<uint32_t>(i / G::kConstSlots) - 1u) & 1u, abort_flag))) {
         ok = false;
         break;
       }
       {
         QX_PROF_BEGIN();
-        write_slab_image<FMT, MP>(digits,
-                                  reinterpret_cast<XConst*>(const_ring + raw.slot * G::kConstBytes),
-                                  digit_offset, cur_lo, cur_hi, cur_valid, lane);
+        write_slab_image<FMT, MP>(
+            digits, reinterpret_cast<XConst*>(const_ring + (i % G::kConstSlots) * G::kConstBytes),
+            digit_offset, cur_lo, cur_hi, cur_valid, lane);
         QX_PROF_END(c_image);
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
+        mbar_arrive(&bars->const_ready[i % G::kConstSlots]);
         mbar_arrive(&bars->ready[raw.slot]);
       }
       raw.advance_by(kW, G::kSlots);
@@ -964,7 +1031,7 @@ template <int FMT, int MP>
 constexpr size_t gemv_smem_bytes() {
   return 1024 + static_cast<size_t>(TcGeom<FMT, MP>::kSlots) * TcGeom<FMT, MP>::kSlotBytes +
          static_cast<size_t>(TcGeom<FMT, MP>::kWorkSlots) * TcGeom<FMT, MP>::kWorkBytes +
-         (TcGeom<FMT, MP>::kFused ? TcGeom<FMT, MP>::kSlots * TcGeom<FMT, MP>::kConstBytes : 0) +
+         TcGeom<FMT, MP>::kConstSlots * TcGeom<FMT, MP>::kConstBytes +
          TcGeom<FMT, MP>::kXRingBytes + sizeof(GemvBarriers<FMT, MP>) + 64;
 }
 
@@ -1014,7 +1081,7 @@ qx_status launch_fmt(int mp, const GemvTcParams& p, int grid, cudaStream_t strea
 
 // Device buffer the profiling build writes its cycle counters to (null otherwise).
 long long* gemv_profile_buffer() {
-#ifdef QX_GEMV_PROFILE
+#if defined(QX_GEMV_PROFILE) || defined(QX_GEMV_STAMPS)
   static long long* buffer = []() {
     long long* ptr = nullptr;
     if (cudaMalloc(&ptr, 64 * 1024 * 32 * sizeof(long long)) != cudaSuccess) return static_cast<long long*>(nullptr);
@@ -1081,7 +1148,9 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
   p.tiles = static_cast<int>(w->tiles);
   p.unit_slabs = scratch.unit_slabs;
   p.units_per_tile = scratch.units_per_tile;
-  p.total_units = w->tiles * scratch.units_per_tile;
+  const long long total_units = w->tiles * scratch.units_per_tile;  // < 2^23 (gemv_scratch_layout)
+  p.units_per_cta = static_cast<uint32_t>(total_units / scratch.ctas);
+  p.units_rem = static_cast<uint32_t>(total_units % scratch.ctas);
   if (push != nullptr && push->peers > 0) {
     if (push->peers > kMaxPushPeers) {
       set_last_error_text("gemv: more than 7 peer ranks");
@@ -1099,7 +1168,7 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
     p.launch_counter = push->launch_counter;
   }
   p.debug = gemv_profile_buffer();
-#ifdef QX_GEMV_PROFILE
+#if defined(QX_GEMV_PROFILE) || defined(QX_GEMV_STAMPS)
   {
     static int launch_seq = 0;
     if (p.debug != nullptr) p.debug += static_cast<long long>(launch_seq++ % 64) * 1024 * 32;
@@ -1113,7 +1182,7 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
 
 }  // namespace qx
 
-#ifdef QX_GEMV_PROFILE
+#if defined(QX_GEMV_PROFILE) || defined(QX_GEMV_STAMPS)
 // Profiling builds only: copies the per-CTA cycle counters of the last launches to the
 // host (32 values per CTA) and clears them.
 extern "C" QX_API int qx_debug_gemv_profile(long long* host_out, int ctas) {

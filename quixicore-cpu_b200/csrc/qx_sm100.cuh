@@ -15,14 +15,6 @@ namespace sm100 {
 // A wait gives up after this much wall time on the GPU's nanosecond timer (a poll of a
 // barrier that is not ready may itself sleep for a while, so counting polls is no bound).
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
-// Upper bound the hardware may keep a waiting thread suspended inside one try_wait (it
-// wakes at once when the barrier phase completes): waiting warps then take no issue
-// slots from the warps that have work.
-#ifndef QX_SUSPEND_HINT_NS
-#define QX_SUSPEND_HINT_NS 1000000u
-#endif
-constexpr uint32_t kSuspendHintNs = QX_SUSPEND_HINT_NS;
-
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -58,9 +50,11 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                "r"(bytes)
                : "memory");
 }
+// One poll of the barrier: the hardware may hold the thread for a short, system-chosen time
+// and wakes it at once when the phase completes. (An explicit, long suspend-time hint was
+// measured 2-3 % slower on the decode GEMV and no faster anywhere.)
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t done;
-#if QX_SUSPEND_HINT_NS == 0
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
@@ -68,15 +62,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "=r"(done)
       : "r"(smem_u32(bar)), "r"(parity)
       : "memory");
-#else
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(kSuspendHintNs)
-      : "memory");
-#endif
   return done != 0;
 }
 // Bounded wait. Returns false when the limit ran out or *abort_flag became non-zero.
@@ -216,6 +201,19 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
 #define QX_PROF_ADD(counter, value) counter += (value)
 #define QX_PROF_STAMP(slot) \
   if (p.debug != nullptr) p.debug[blockIdx.x * 32 + (slot)] = static_cast<long long>(sm100::global_timer_ns())
+#define QX_PROF_STAMP2(slot)
+#elif defined(QX_GEMV_STAMPS)
+// time stamps only (no wait accounting: that perturbs the pipeline)
+#define QX_PROF_DECL(name)
+#define QX_PROF_WAIT(counter, expr) (expr)
+#define QX_PROF_STORE(slot, value)
+#define QX_PROF_NOW() 0
+#define QX_PROF_BEGIN()
+#define QX_PROF_END(counter)
+#define QX_PROF_ADD(counter, value)
+#define QX_PROF_STAMP(slot) \
+  if (p.debug != nullptr) p.debug[blockIdx.x * 32 + (slot)] = static_cast<long long>(sm100::global_timer_ns())
+#define QX_PROF_STAMP2(slot) QX_PROF_STAMP(slot)
 #else
 #define QX_PROF_DECL(name)
 #define QX_PROF_WAIT(counter, expr) (expr)
@@ -225,6 +223,7 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
 #define QX_PROF_END(counter)
 #define QX_PROF_ADD(counter, value)
 #define QX_PROF_STAMP(slot)
+#define QX_PROF_STAMP2(slot)
 #endif
 
 // Device buffer [1024 CTAs][32] the profiling build writes its counters to (null otherwise).
