@@ -2,24 +2,30 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl qx|reference]
 
-Headline workload (N = 1): the 4-bit block GEMV at FFN-up shape -- M=1, K=4096 f32
+One GPU (the headline): the 4-bit block GEMV at FFN-up shape -- M=1, K=4096 f32
 activations ~N(0,1), N=14336 x K=4096 q4_0 weights (33 MB) -- measured as achieved HBM
-GB/s: algorithmic bytes (packed weights + activations read + outputs written) / time.
-A step is one GEMV call. The weights fit in L2, so the timed loop rotates over several
-distinct weight copies whose total size exceeds L2 (stated in `config`). With N > 1 every
-rank holds one such shard of an (N*14336) x 4096 matrix (weak scaling), computes its
-output slice and all ranks exchange slices (all-gather), as the sharded configurations of
-this path do.
+GB/s: algorithmic bytes (packed weights + activations read + outputs written) / time. A
+step is one GEMV call. The weights fit in L2, so the timed loop rotates over several
+distinct weight copies whose total size exceeds L2 (stated in `config`).
+
+N > 1 GPUs (one process per GPU): the batched q8_0 decode GEMV at the large FFN shape --
+N=28672 x K=8192 (240 MB) -- under STRONG scaling: the weight rows are split N ways, every
+rank streams its shard and all ranks end up with the full output. A step is one sharded
+GEMV including the exchange of the output slices (fused into the kernel: peer stores over
+NVLink + a wait kernel). `value` is the M=1 case; the M sweep, the kernel without the
+exchange, an NCCL all-gather leg and the one-GPU time of the whole matrix are in `extra`.
 
 Prints ONE JSON line (rank 0). `value` is timed with inputs resident in HBM, `e2e` through
-the host-pointer C entry point with pinned host buffers (host<->device copies inside the
-timed region), `cpu_baseline` is the reference's CPU path on this host's cores on a
-bounded sample, `roofline` relates the step to the measured HBM copy bandwidth.
+host buffers (host<->device copies inside the timed region), `cpu_baseline` is the
+reference's CPU path on this host's cores on a bounded sample, `roofline` relates the step
+to the measured HBM copy bandwidth. Whatever --steps is, the timed region lasts at least
+50 ms: the block of K steps is repeated (`config.timed_repeats`) and averaged.
 """
 
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -34,8 +40,11 @@ sys.path.insert(0, ROOT)
 import __graft_entry__ as entry  # noqa: E402
 
 METRIC = "decode GEMV achieved HBM GB/s"
-WORKLOAD = "cfg1_q4_0_gemv"
+WORKLOAD_1GPU = "cfg1_q4_0_gemv"
+WORKLOAD_SHARDED = "cfg3_q8_0_batched"
 GRAPH_CHUNK = 100
+MIN_TIMED_MS = 50.0
+FORMAT_NAMES = {0: "q8_0", 1: "q4_0"}
 
 
 def load_workloads():
@@ -115,10 +124,41 @@ class ClockSampler(threading.Thread):
 # CPU arm: the reference's own implementation on the host cores
 # ---------------------------------------------------------------------------------------
 
-def cpu_engine():
-    """(kind, call, threads): the built reference library when present, else the oracle port."""
+def host_cpu():
+    """(model string, logical CPUs, physical cores) of this host."""
+    model, cores = "unknown", set()
+    try:
+        physical = core = None
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                key, _, value = line.partition(":")
+                key, value = key.strip(), value.strip()
+                if key == "model name" and model == "unknown":
+                    model = value
+                elif key == "physical id":
+                    physical = value
+                elif key == "core id":
+                    core = value
+                elif not key and physical is not None and core is not None:
+                    cores.add((physical, core))
+                    physical = core = None
+        if physical is not None and core is not None:
+            cores.add((physical, core))
+    except OSError:
+        pass
+    logical = os.cpu_count() or 1
+    try:
+        logical = min(logical, len(os.sched_getaffinity(0)))
+    except (AttributeError, OSError):
+        pass
+    physical_cores = len(cores) if cores else max(1, logical // 2)
+    return model, logical, max(1, min(physical_cores, logical))
+
+
+def cpu_engine(threads: int):
+    """(kind, engine, threads, variants): the built reference library when present, else the
+    oracle port (single-threaded)."""
     oracle_mod = entry.load_oracle()
-    threads = os.cpu_count() or 1
     if oracle_mod.Reference.available():
         ref = oracle_mod.Reference()
         ref.set_num_threads(threads)
@@ -126,19 +166,43 @@ def cpu_engine():
     return "port", oracle_mod.Oracle(), 1, {}
 
 
-def time_cpu_gemv(engine_kind, engine, fmt, packed, x, n, k, budget_s, max_calls):
-    """Median seconds per call of the CPU GEMV over rows [0, n); at least 3 calls."""
-    def call():
-        if engine_kind == "reference":
-            return engine.qgemv(fmt, packed, x, n, k)
-        return engine.qgemv(fmt, packed, x, n, k, 0)
-    call()
-    times, start = [], time.perf_counter()
-    while len(times) < max_calls and (len(times) < 3 or time.perf_counter() - start < budget_s):
-        t0 = time.perf_counter()
+def cpu_gemv_call(kind, engine, fmt, packed, x, rows, k):
+    if kind == "reference":
+        return lambda: engine.qgemv(fmt, packed, x, rows, k)
+    return lambda: engine.qgemv(fmt, packed, x, rows, k, 0)
+
+
+def cpu_time_stats(call, budget_s: float = 6.0):
+    """Timing discipline of the reference's own bench harness
+    (benchmarks/harness/timing.cpp:19-83): warm-up of at least 3 calls AND 50 ms, then up to
+    20 samples of batched calls, each sample at least 2 ms; median / p20 / p80 / CV of the
+    per-call time. `budget_s` bounds the sampling (fewer samples for slow calls, at least 3)."""
+    t0 = time.perf_counter()
+    warm = 0
+    while warm < 3 or time.perf_counter() - t0 < 0.05:
         call()
-        times.append(time.perf_counter() - t0)
-    return statistics.median(times), len(times)
+        warm += 1
+    per_call = (time.perf_counter() - t0) / warm
+    batch = max(1, min(4096, int(np.ceil(0.002 / max(per_call, 1e-9)))))
+    samples = int(max(3, min(20, budget_s / max(per_call * batch, 1e-9))))
+    times = []
+    for _ in range(samples):
+        s0 = time.perf_counter()
+        for _ in range(batch):
+            call()
+        times.append((time.perf_counter() - s0) / batch)
+    times.sort()
+    median = statistics.median(times)
+    pick = lambda q: times[min(len(times) - 1, int(q * len(times)))]  # noqa: E731
+    cv = statistics.pstdev(times) / statistics.fmean(times) if len(times) > 1 else 0.0
+    return {"median_s": median, "p20_s": pick(0.2), "p80_s": pick(0.8), "cv": cv,
+            "samples": len(times), "calls_per_sample": batch, "warmup_calls": warm}
+
+
+def reference_workload(wl, gpus: int):
+    name = WORKLOAD_1GPU if gpus <= 1 else WORKLOAD_SHARDED
+    c = wl.CONFIGS[name]
+    return name, c["fmt"], c["n"], c["k"], c
 
 
 def run_reference_arm(args):
@@ -146,69 +210,205 @@ def run_reference_arm(args):
     if rank != 0:
         return
     wl = load_workloads()
-    c = wl.CONFIGS[WORKLOAD]
-    fmt, n, k = c["fmt"], c["n"], c["k"]
+    name, fmt, n, k, c = reference_workload(wl, args.gpus)
     packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0)
     x = wl.activations_f32(1, k, seed=0)[0].copy()
-    kind, engine, threads, variants = cpu_engine()
+    model, logical, physical = host_cpu()
+    kind, engine, threads, variants = cpu_engine(physical)
 
-    def call(rows):
-        if kind == "reference":
-            engine.qgemv(fmt, packed, x, rows, k)
-        else:
-            engine.qgemv(fmt, packed, x, rows, k, 0)
     # bound the run to about two minutes: shrink the per-step row sample if needed
-    call(n)
+    full = cpu_gemv_call(kind, engine, fmt, packed, x, n, k)
     t0 = time.perf_counter()
-    for _ in range(3):
-        call(n)
-    per_call = (time.perf_counter() - t0) / 3
+    warm = 0
+    while warm < 3 or time.perf_counter() - t0 < 0.05:  # the pool's threads spin up here
+        full()
+        warm += 1
+    per_call = (time.perf_counter() - t0) / warm
     rows = n
     total_steps = args.steps + args.warmup
     if per_call * total_steps > 120.0:
         rows = int(max(32 * threads, min(n, n * 120.0 / (per_call * total_steps))))
         rows -= rows % 32
         rows = max(rows, 32)
+    call = cpu_gemv_call(kind, engine, fmt, packed, x, rows, k)
     for _ in range(args.warmup):
-        call(rows)
+        call()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        call(rows)
+        call()
     elapsed = time.perf_counter() - t0
     step_bytes = wl.algorithmic_bytes_qgemv(fmt, 1, rows, k)
     value = step_bytes * args.steps / elapsed / 1e9
+    stats = cpu_time_stats(call, budget_s=4.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic",
-        "config": {"workload": WORKLOAD, "m": 1, "n": n, "k": k, "format": "q4_0",
+        "higher_is_better": True, "scaling": "weak" if args.gpus <= 1 else "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "m": 1, "n": n, "k": k, "format": FORMAT_NAMES[fmt],
                    "rows_per_step": rows, "variants": variants},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": kind,
-                         "sample": f"{args.steps} calls of the reference qgemv over {rows} of {n} rows"},
+                         "cpu_model": model, "logical_cpus": logical, "physical_cores": physical,
+                         "sample": f"{args.steps} calls of the reference qgemv over {rows} of {n} rows "
+                                   f"after {warm}+{args.warmup} warm-up calls (>= 50 ms)",
+                         "harness_stats": {
+                             "median_gbs": step_bytes / stats["median_s"] / 1e9,
+                             "p20_ms": stats["p20_s"] * 1e3, "median_ms": stats["median_s"] * 1e3,
+                             "p80_ms": stats["p80_s"] * 1e3, "cv": stats["cv"],
+                             "samples": stats["samples"], "calls_per_sample": stats["calls_per_sample"]}},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
 
 
+def cpu_baseline(wl, c):
+    """The reference's CPU GEMV on the headline workload: T = physical cores and T = 1."""
+    fmt, n, k = c["fmt"], c["n"], c["k"]
+    packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0)
+    x = wl.activations_f32(1, k, seed=0)[0].copy()
+    model, logical, physical = host_cpu()
+    step_bytes = wl.algorithmic_bytes_qgemv(fmt, 1, n, k)
+    kind, engine, threads, variants = cpu_engine(physical)
+    many = cpu_time_stats(cpu_gemv_call(kind, engine, fmt, packed, x, n, k), budget_s=8.0)
+    out = {"value": step_bytes / many["median_s"] / 1e9, "unit": "GB/s", "cores": threads,
+           "kind": kind, "cpu_model": model, "logical_cpus": logical, "physical_cores": physical,
+           "ms_per_call": many["median_s"] * 1e3, "p20_ms": many["p20_s"] * 1e3,
+           "p80_ms": many["p80_s"] * 1e3, "cv": many["cv"],
+           "sample": f"median of {many['samples']} samples x {many['calls_per_sample']} full-size qgemv "
+                     f"calls ({n}x{k} {FORMAT_NAMES[fmt]}) after {many['warmup_calls']} warm-up calls (>= 50 ms)",
+           "variants": variants}
+    if kind == "reference":
+        engine.set_num_threads(1)
+        one = cpu_time_stats(cpu_gemv_call(kind, engine, fmt, packed, x, n, k), budget_s=4.0)
+        out["single_thread"] = {"value": step_bytes / one["median_s"] / 1e9, "unit": "GB/s",
+                                "ms_per_call": one["median_s"] * 1e3, "cv": one["cv"],
+                                "samples": one["samples"]}
+        engine.set_num_threads(threads)
+    return out
+
+
 # ---------------------------------------------------------------------------------------
-# GPU arm
+# GPU arm, shared helpers
 # ---------------------------------------------------------------------------------------
 
-def run_qx_arm(args):
+_cudart = None
+
+
+def cudart():
+    global _cudart
+    if _cudart is None:
+        _cudart = ctypes.CDLL("libcudart.so.12")
+        _cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
+        _cudart.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                                            ctypes.c_int, ctypes.c_void_p]
+    return _cudart
+
+
+def _device_floats(torch, address: int, count: int):
+    """`count` floats at a raw device address, copied into a torch tensor."""
+    out = torch.empty(count, dtype=torch.float32, device="cuda")
+    if cudart().cudaMemcpy(out.data_ptr(), address, count * 4, 3) != 0:  # device to device
+        raise RuntimeError("cudaMemcpy failed")
+    return out
+
+
+class TimedBlock:
+    """K steps as CUDA graphs (a chunk replayed q times plus a remainder graph), so that the
+    host's launch cost stays out of the timed region; falls back to plain launches when
+    capture is refused."""
+
+    def __init__(self, torch, step, steps: int, period: int, allow_graph: bool = True):
+        self.torch, self.step, self.steps = torch, step, steps
+        chunk = min(steps, GRAPH_CHUNK)
+        if chunk >= period:
+            chunk -= chunk % period
+        self.chunk = max(1, chunk)
+        self.reps, self.rem = divmod(steps, self.chunk)
+        self.graph_chunk = self.graph_rem = None
+        # two plain steps first: a call shape that is new to the library's default workspace
+        # grows it (an allocation), which must not happen inside a capture. (Two, because the
+        # fused all-gather alternates between two result buffers step by step and every
+        # block of steps here is kept even.)
+        for i in range(2):
+            step(i)
+        torch.cuda.synchronize()
+        if allow_graph:
+            try:
+                self.graph_chunk = self._capture(0, self.chunk)
+                if self.rem:
+                    self.graph_rem = self._capture(self.reps * self.chunk, self.rem)
+            except Exception as exc:  # fall back to plain launches
+                print(f"bench: graph capture failed ({exc!r}); timing plain launches", file=sys.stderr)
+                self.graph_chunk = self.graph_rem = None
+                torch.cuda.synchronize()
+
+    def _capture(self, first: int, count: int):
+        graph = self.torch.cuda.CUDAGraph()
+        with self.torch.cuda.graph(graph):
+            for i in range(first, first + count):
+                self.step(i)
+        graph.replay()
+        self.torch.cuda.synchronize()
+        return graph
+
+    @property
+    def graphed(self):
+        return self.graph_chunk is not None
+
+    def run(self):
+        if self.graph_chunk is not None:
+            for _ in range(self.reps):
+                self.graph_chunk.replay()
+            if self.graph_rem is not None:
+                self.graph_rem.replay()
+        else:
+            for i in range(self.steps):
+                self.step(i)
+
+
+def time_block(torch, dist, block: TimedBlock, world: int):
+    """(ms per step, repeats): the block of K steps repeated until the region lasts at least
+    MIN_TIMED_MS, between barriers and synchronisations, CUDA events, max over ranks."""
+    def region(repeats):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(repeats):
+            block.run()
+        stop.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        ms = start.elapsed_time(stop)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+    probe = region(1)
+    repeats = max(1, int(np.ceil(1.1 * MIN_TIMED_MS / max(probe, 1e-6))))
+    if world > 1:  # every rank must run the same number of repeats
+        t = torch.tensor([repeats], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        repeats = int(t.item())
+    total = region(repeats)
+    return total / (repeats * block.steps), repeats, total
+
+
+# ---------------------------------------------------------------------------------------
+# GPU arm, one GPU: the headline
+# ---------------------------------------------------------------------------------------
+
+def run_single(args):
     import torch
-    import torch.distributed as dist
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     qx = entry.load_package()
     wl = load_workloads()
-    c = wl.CONFIGS[WORKLOAD]
+    c = wl.CONFIGS[WORKLOAD_1GPU]
     fmt, n, k = c["fmt"], c["n"], c["k"]
     step_bytes = wl.algorithmic_bytes_qgemv(fmt, 1, n, k)
     hbm_peak, bf16_peak, peak_kind = measured_peaks()
@@ -218,61 +418,201 @@ def run_qx_arm(args):
     copies = max(2, -(-2 * info["l2_bytes"] // (n * (k // 32) * 18)))
     handles = []
     for i in range(copies):
-        packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=rank * 1000 + i)
+        packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=i)
         h = qx.PackedWeights()
         qx.check(h.prepare(fmt, packed, n, k), "qx_weights_prepare")
         handles.append(h)
     x_host = wl.activations_f32(1, k, seed=0)
     x_dev = torch.from_numpy(x_host).cuda()
-    y_full = torch.zeros(world * n, device="cuda")
-    y_local = y_full[rank * n:(rank + 1) * n]
-
-    # Sharded runs: every rank streams its own shard and the output slices are exchanged. The
-    # exchange is fused into the GEMV (peer stores from its epilogue + a wait kernel); if the
-    # peer mapping cannot be set up, NCCL's all-gather takes its place.
-    gather, exchange = None, "none"
-    if world > 1:
-        try:
-            sharded = entry._load_file(entry.PKG_NAME + ".sharded", os.path.join(entry.PKG_DIR, "sharded.py"))
-            gather = sharded.PushAllGather(qx, n, 1)
-            exchange = "peer stores fused into the GEMV epilogue + wait kernel"
-        except Exception as exc:
-            print(f"bench: fused all-gather unavailable ({exc!r}); using NCCL", file=sys.stderr)
-            gather, exchange = None, "nccl all_gather_into_tensor"
-        healthy = 1 if gather is not None else 0
-        if gather is not None:
-            # two trial steps: this rank's slice of the gathered result must equal its own GEMV
-            # bit for bit, and no kernel may have given up a wait (a tiny host-pointer call
-            # reports that)
-            try:
-                want = torch.zeros(n, device="cuda")
-                for trial in range(2):
-                    qx.check(handles[trial].qgemm_dev(x_dev, want, 1, n), "trial gemv")
-                    got_ptr = gather.step(handles[trial], x_dev, 1)
-                    torch.cuda.synchronize()
-                    got = _device_floats(torch, got_ptr + 4 * rank * n, n)
-                    if not torch.equal(got.view(torch.int32), want.view(torch.int32)):
-                        healthy = 0
-                tiny = wl.packed_blocks(fmt, 32, 32, c["d_lo"], c["d_hi"], seed=1)
-                status, _ = qx.qgemv(fmt, tiny, wl.activations_f32(1, 32)[0], 32, 32)
-                if status != qx.OK:
-                    healthy = 0
-            except Exception as exc:
-                print(f"bench: fused all-gather trial failed ({exc!r}); using NCCL", file=sys.stderr)
-                healthy = 0
-        flags = torch.tensor([healthy], device="cuda")
-        dist.all_reduce(flags, op=dist.ReduceOp.MIN)  # all ranks take the same path
-        if int(flags.item()) == 0:
-            gather, exchange = None, "nccl all_gather_into_tensor"
+    y_dev = torch.zeros(n, device="cuda")
 
     def step(i):
-        if gather is not None:
-            gather.step(handles[i % copies], x_dev, 1)
-            return
-        qx.check(handles[i % copies].qgemm_dev(x_dev, y_local, 1, n), "qx_qgemm_prepacked_dev")
-        if world > 1:
-            dist.all_gather_into_tensor(y_full, y_local)
+        qx.check(handles[i % copies].qgemm_dev(x_dev, y_dev, 1, n), "qx_qgemm_prepacked_dev")
 
+    launches0 = qx.launch_count()
+    step(0)
+    launches_per_step = qx.launch_count() - launches0
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    block = TimedBlock(torch, step, args.steps, copies, allow_graph=not args.no_graph)
+    ms_per_step, repeats, total_ms = time_block(torch, None, block, 1)
+    clocks = sampler.stop()
+    value = step_bytes / (ms_per_step * 1e-3) / 1e9
+
+    # One launch that cannot overlap its neighbours (what a caller sees when other kernels
+    # sit between GEMVs): an unrelated 64 MB fill runs between consecutive GEMVs in a graph;
+    # the time of the same graph without the GEMVs is subtracted.
+    filler = torch.empty(16 << 20, dtype=torch.float32, device="cuda")
+    pairs = 2 * copies
+    t_pairs = _time_calls(torch, lambda i: (filler.fill_(1.0), step(i)), pairs)
+    t_fill = _time_calls(torch, lambda i: filler.fill_(1.0), pairs)
+    isolated_us = (t_pairs - t_fill) * 1e6
+    del filler
+
+    # end to end through the host-pointer entry point: pinned x in, pinned y out, every step
+    x_pin = torch.from_numpy(x_host).pin_memory()
+    y_pin = torch.zeros(n).pin_memory()
+    e2e_steps = max(10, min(args.steps, 2000))
+    for i in range(3):
+        qx.check(handles[i % copies].qgemm_prepacked_ptr(x_pin.data_ptr(), y_pin.data_ptr(), 1), "e2e")
+    t0 = time.perf_counter()
+    for i in range(e2e_steps):
+        qx.check(handles[i % copies].qgemm_prepacked_ptr(x_pin.data_ptr(), y_pin.data_ptr(), 1), "e2e")
+    e2e_s = time.perf_counter() - t0
+    e2e_value = step_bytes * e2e_steps / e2e_s / 1e9
+
+    line = {
+        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD_1GPU, "m": 1, "n": n, "k": k, "format": FORMAT_NAMES[fmt],
+                   "sharding": "none", "exchange": "none",
+                   "l2_policy": f"rotates {copies} distinct weight copies "
+                                f"({copies * n * (k // 32) * 18 / 1e6:.0f} MB > L2 {info['l2_bytes'] / 1e6:.0f} MB)",
+                   "cuda_graph": block.graphed, "timed_repeats": repeats,
+                   "timed_region_ms": total_ms, "variants": qx.variants()},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k,
+                "d2h_bytes_per_step": 4 * n, "steps": e2e_steps,
+                "note": "qx_qgemm_prepacked per step on a handle prepared once (the counterpart of "
+                        "CpuPackedWeights): x copied from pinned host memory, y written by the "
+                        "kernel into the caller's pinned host buffer, then one stream "
+                        "synchronisation. The literal qgemv(packed_host, ...) entry re-uploads the "
+                        "33 MB of weights per call and is not what this number measures"},
+        "gpu_launches": launches_per_step * args.steps * repeats,
+        "roofline": {"bound": "hbm", "achieved": value, "peak": hbm_peak, "unit": "GB/s",
+                     "frac": value / hbm_peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch "
+                                       "from an ncu capture of this workload, not measured by this run",
+                     "peak_source": f"{peak_kind} HBM copy bandwidth",
+                     "frac_of_nominal_8TBs": value / 8000.0,
+                     "isolated_launch_us": isolated_us,
+                     "isolated_frac": step_bytes / (isolated_us * 1e-6) / 1e9 / hbm_peak,
+                     "note": "achieved = algorithmic bytes / step time over back-to-back, "
+                             "graph-replayed steps (launch gaps included); isolated_launch_us = one "
+                             "launch between synchronisations"},
+    }
+    if not args.no_extra:
+        line["cpu_baseline"] = cpu_baseline(wl, c)
+        try:
+            line["extra"] = extra_measurements(qx, wl, torch, hbm_peak, bf16_peak)
+        except Exception as exc:  # the headline line must still be printed
+            line["extra"] = {"error": repr(exc)}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------
+# GPU arm, N > 1: the sharded decode configuration under strong scaling
+# ---------------------------------------------------------------------------------------
+
+def run_sharded(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ["RANK"])
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    qx = entry.load_package()
+    wl = load_workloads()
+    sharded = entry._load_file(entry.PKG_NAME + ".sharded", os.path.join(entry.PKG_DIR, "sharded.py"))
+    c = wl.CONFIGS[WORKLOAD_SHARDED]
+    fmt, n, k = c["fmt"], c["n"], c["k"]
+    sweep = tuple(c["m_sweep"])
+    hbm_peak, _, peak_kind = measured_peaks()
+    info = qx.device_info()
+    begin, rows = sharded.shard_rows(n, world, rank)
+    if rows * world != n:
+        raise SystemExit(f"bench: {n} rows do not split evenly over {world} ranks")
+    block_bytes = 34 if fmt == 0 else 18
+    shard_bytes = rows * (k // 32) * block_bytes
+
+    # The whole matrix (seed 0) on every rank: the unsharded GEMV is the reference of the
+    # self-check and the one-GPU time of the strong-scaling figure. Copy 0 of the shard is
+    # this rank's row range of it; further copies (other seeds) only keep the timed loop out
+    # of L2.
+    packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0)
+    full = qx.PackedWeights()
+    qx.check(full.prepare(fmt, packed, n, k), "prepare full")
+    copies = max(2, -(-2 * info["l2_bytes"] // shard_bytes))
+    handles = []
+    for i in range(copies):
+        h = qx.PackedWeights()
+        if i == 0:
+            qx.check(h.prepare(fmt, packed, n, k, begin, rows), "prepare shard")
+        else:
+            other = wl.packed_blocks(fmt, rows, k, c["d_lo"], c["d_hi"], seed=1000 * rank + i)
+            qx.check(h.prepare(fmt, other, rows, k), "prepare shard copy")
+        handles.append(h)
+    del packed
+    xs = {m: torch.from_numpy(wl.activations_f32(m, k, seed=m)).cuda() for m in sweep}
+
+    # the exchange fused into the GEMV; NCCL only if the peer mapping cannot be set up
+    gathers, exchange = {}, "peer stores fused into the GEMV epilogue + wait kernel"
+    healthy = 1
+    try:
+        for m in sweep:
+            gathers[m] = sharded.PushAllGather(qx, rows, m)
+    except Exception as exc:
+        print(f"bench: fused all-gather unavailable ({exc!r}); using NCCL", file=sys.stderr)
+        healthy = 0
+    flags = torch.tensor([healthy], device="cuda")
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    fused = int(flags.item()) == 1
+    if not fused:
+        gathers, exchange = {}, "nccl all_gather_into_tensor"
+
+    def gathered_matches(m, steps_to_check):
+        """Runs `steps_to_check` steps on the true shard and compares every rank's slice of the
+        gathered result with the unsharded GEMV, bit for bit."""
+        want = torch.zeros((m, n), device="cuda")
+        qx.check(full.qgemm_dev(xs[m], want, m, n), "unsharded gemv")
+        torch.cuda.synchronize()
+        ok = True
+        for _ in range(steps_to_check):
+            ptr = gathers[m].step(handles[0], xs[m], m)
+            torch.cuda.synchronize()
+            got = _device_floats(torch, ptr, world * m * rows).view(world, m, rows)
+            for r in range(world):
+                ok = ok and torch.equal(got[r].view(torch.int32),
+                                        want[:, r * rows:(r + 1) * rows].contiguous().view(torch.int32))
+        return ok
+
+    selfcheck = {"ok": None}
+    if fused:
+        checks = {}
+        try:
+            for m in (1, sweep[-1]):
+                checks[f"m{m}_both_parities_all_slices_bit_equal"] = gathered_matches(m, 2)
+            checks["no_wait_gave_up"] = qx.lib.qx_check_device_errors() == qx.OK
+        except Exception as exc:
+            print(f"bench: self-check raised {exc!r}", file=sys.stderr)
+            checks["exception"] = False
+        selfcheck = dict(checks)
+        mine = torch.tensor([1 if all(checks.values()) else 0], device="cuda")
+        dist.all_reduce(mine, op=dist.ReduceOp.MIN)
+        selfcheck["ok"] = bool(int(mine.item()))
+        selfcheck["ranks"] = world
+
+    y_full = torch.zeros((1, n), device="cuda")
+    y_local = torch.zeros((1, rows), device="cuda")
+
+    def step_m(m):
+        if fused:
+            return lambda i: gathers[m].step(handles[i % copies], xs[m], m)
+
+        def nccl_step(i):
+            qx.check(handles[i % copies].qgemm_dev(xs[1], y_local, 1, rows), "gemv")
+            dist.all_gather_into_tensor(y_full.view(-1), y_local.view(-1))
+        return nccl_step
+
+    step = step_m(1)
     launches0 = qx.launch_count()
     step(0)
     launches_per_step = qx.launch_count() - launches0
@@ -283,130 +623,118 @@ def run_qx_arm(args):
     for i in range(args.warmup):
         step(i)
     torch.cuda.synchronize()
-
-    graph = None
-    chunk = GRAPH_CHUNK - GRAPH_CHUNK % copies or copies
-    chunk -= chunk % 2  # fused all-gather: the result buffers alternate step by step
-    if (world == 1 or gather is not None) and args.steps >= chunk and chunk > 0 and not args.no_graph:
-        # The steps are captured once and replayed, so the host's launch cost stays out of the
-        # timed region. Sharded runs that fall back to NCCL launch step by step: a graph that
-        # also held the NCCL all-gathers did not make progress on two GPUs (both ranks stopped
-        # inside the first replay), so that combination is not used.
-        try:
-            captured = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(captured):
-                for i in range(chunk):
-                    step(i)
-            captured.replay()
-            torch.cuda.synchronize()
-            graph = captured
-        except Exception as exc:  # fall back to plain launches
-            print(f"bench: graph capture failed ({exc!r}); timing plain launches", file=sys.stderr)
-            graph = None
-            torch.cuda.synchronize()
-
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    done = 0
-    if graph is not None:
-        while done + chunk <= args.steps:
-            graph.replay()
-            done += chunk
-    for i in range(done, args.steps):
-        step(i)
-    stop.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    elapsed_ms = start.elapsed_time(stop)
+    period = copies if copies % 2 == 0 else 2 * copies  # result buffers alternate step by step
+    block = TimedBlock(torch, step, args.steps + (args.steps % 2 if fused else 0), period,
+                       allow_graph=fused and not args.no_graph)
+    ms_per_step, repeats, total_ms = time_block(torch, dist, block, world)
     clocks = sampler.stop()
-    if world > 1:
-        t = torch.tensor([elapsed_ms], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(t.item())
-    value = step_bytes * world * args.steps / (elapsed_ms * 1e-3) / 1e9
+    full_bytes = wl.algorithmic_bytes_qgemv(fmt, 1, n, k)
+    value = full_bytes / (ms_per_step * 1e-3) / 1e9
 
-    # end to end through the host-pointer entry point: pinned x in, pinned y out, every step
-    x_pin = torch.from_numpy(x_host).pin_memory()
+    # ---- explanatory figures -------------------------------------------------------------
+    def per_step_us(fn, count, use_graph=True):
+        blk = TimedBlock(torch, fn, count, period, allow_graph=use_graph and not args.no_graph)
+        ms, _, _ = time_block(torch, dist, blk, world)
+        return ms * 1e3
+
+    extra = {}
+    try:
+        y_shard = {m: torch.zeros((m, rows), device="cuda") for m in sweep}
+        y_whole = {m: torch.zeros((m, n), device="cuda") for m in sweep}
+        sweep_out = {}
+        for m in sweep:
+            count = 2 * period
+            local_us = per_step_us(lambda i, m=m: qx.check(
+                handles[i % copies].qgemm_dev(xs[m], y_shard[m], m, rows), "gemv"), count)
+            one_gpu_us = per_step_us(lambda i, m=m: qx.check(
+                full.qgemm_dev(xs[m], y_whole[m], m, n), "gemv"), 4)
+            entry_m = {"one_gpu_whole_matrix_us": one_gpu_us, "shard_kernel_only_us": local_us,
+                       "efficiency_kernel_only": one_gpu_us / (world * local_us)}
+            if fused:
+                step_us = ms_per_step * 1e3 if m == 1 else per_step_us(step_m(m), count)
+                entry_m.update({"sharded_step_us": step_us,
+                                "efficiency_with_exchange": one_gpu_us / (world * step_us),
+                                "aggregate_gbs": wl.algorithmic_bytes_qgemv(fmt, m, n, k) / step_us / 1e3})
+            sweep_out[f"m{m}"] = entry_m
+        extra["strong_scaling"] = {"definition": "t(1 GPU, whole matrix) / (N * t(N))", "m_sweep": sweep_out}
+        # the stated comparison: NCCL all-gather of the output slices after the shard's GEMV
+        def nccl_leg(i):
+            qx.check(handles[i % copies].qgemm_dev(xs[1], y_local, 1, rows), "gemv")
+            dist.all_gather_into_tensor(y_full.view(-1), y_local.view(-1))
+        for i in range(5):
+            nccl_leg(i)
+        extra["nccl_all_gather_leg"] = {"m": 1, "step_us": per_step_us(nccl_leg, 2 * period, use_graph=False),
+                                        "launch": "eager (not captured in a graph)"}
+    except Exception as exc:
+        extra["error"] = repr(exc)
+
+    # ---- end to end: host x in, gathered y out, every step ----------------------------------
+    x_pin = torch.from_numpy(wl.activations_f32(1, k, seed=1)).pin_memory()
     y_pin = torch.zeros(n).pin_memory()
-    e2e_steps = max(10, min(args.steps, 2000))
-    for i in range(3):
-        qx.check(handles[i % copies].qgemm_prepacked_ptr(x_pin.data_ptr(), y_pin.data_ptr(), 1), "e2e")
-    if world > 1:
-        dist.barrier()
+    x_stage = torch.zeros((1, k), device="cuda")
+    stream = torch.cuda.current_stream()
+
+    def e2e_step(i):
+        x_stage.copy_(x_pin, non_blocking=True)
+        if fused:
+            ptr = gathers[1].step(handles[i % copies], x_stage, 1)
+            cudart().cudaMemcpyAsync(y_pin.data_ptr(), ptr, 4 * n, 2, stream.cuda_stream)
+        else:
+            qx.check(handles[i % copies].qgemm_dev(x_stage, y_local, 1, rows), "gemv")
+            dist.all_gather_into_tensor(y_full.view(-1), y_local.view(-1))
+            y_pin.copy_(y_full.view(-1), non_blocking=True)
+        stream.synchronize()
+
+    e2e_steps = max(10, min(args.steps, 1000))
+    e2e_steps += e2e_steps % 2
+    for i in range(4):
+        e2e_step(i)
+    dist.barrier()
     t0 = time.perf_counter()
     for i in range(e2e_steps):
-        qx.check(handles[i % copies].qgemm_prepacked_ptr(x_pin.data_ptr(), y_pin.data_ptr(), 1), "e2e")
+        e2e_step(i)
     e2e_s = time.perf_counter() - t0
-    if world > 1:
-        t = torch.tensor([e2e_s], device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
-    e2e_value = step_bytes * world * e2e_steps / e2e_s / 1e9
+    t = torch.tensor([e2e_s], device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = full_bytes * e2e_steps / float(t.item()) / 1e9
 
-    if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+    if fused:  # once more after all the timed loops: the gathered result is still right
+        after = gathered_matches(1, 2) and qx.lib.qx_check_device_errors() == qx.OK
+        mine = torch.tensor([1 if after else 0], device="cuda")
+        dist.all_reduce(mine, op=dist.ReduceOp.MIN)
+        selfcheck["after_timed_loops_ok"] = bool(int(mine.item()))
+        selfcheck["ok"] = bool(selfcheck["ok"] and selfcheck["after_timed_loops_ok"])
 
-    per_launch_gbs = step_bytes * args.steps / (elapsed_ms * 1e-3) / 1e9  # this rank's GPU
-    line = {
-        "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "m": 1, "n": n, "k": k, "format": "q4_0",
-                   "sharding": f"rows x{world}" if world > 1 else "none", "exchange": exchange,
-                   "l2_policy": f"rotates {copies} distinct weight copies "
-                                f"({copies * n * (k // 32) * 18 / 1e6:.0f} MB > L2 {info['l2_bytes'] / 1e6:.0f} MB)",
-                   "cuda_graph": graph is not None, "variants": qx.variants()},
-        "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k,
-                "d2h_bytes_per_step": 4 * n, "steps": e2e_steps,
-                "note": "host-pointer C entry point per step: x copied from pinned host memory, y "
-                        "written by the kernel into the caller's pinned host buffer, then one "
-                        "stream synchronisation"},
-        "gpu_launches": launches_per_step * args.steps,
-        "roofline": {"bound": "hbm", "achieved": per_launch_gbs, "peak": hbm_peak, "unit": "GB/s",
-                     "frac": per_launch_gbs / hbm_peak, "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
-                     "peak_source": f"{peak_kind} HBM copy bandwidth",
-                     "frac_of_nominal_8TBs": per_launch_gbs / 8000.0,
-                     "note": "achieved = algorithmic bytes / whole step time (one kernel per "
-                             "step; launch gaps included)"},
-    }
-    if world == 1 and not args.no_extra:
-        line["cpu_baseline"] = cpu_baseline(wl, c)
-        try:
-            line["extra"] = extra_measurements(qx, wl, torch, hbm_peak, bf16_peak)
-        except Exception as exc:  # the headline line must still be printed
-            line["extra"] = {"error": repr(exc)}
-    print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
-
-
-def cpu_baseline(wl, c):
-    fmt, n, k = c["fmt"], c["n"], c["k"]
-    packed = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0)
-    x = wl.activations_f32(1, k, seed=0)[0].copy()
-    kind, engine, threads, variants = cpu_engine()
-    seconds, calls = time_cpu_gemv(kind, engine, fmt, packed, x, n, k, budget_s=10.0, max_calls=4000)
-    return {"value": wl.algorithmic_bytes_qgemv(fmt, 1, n, k) / seconds / 1e9, "unit": "GB/s",
-            "cores": threads, "kind": kind, "ms_per_call": seconds * 1e3,
-            "sample": f"median of {calls} full-size qgemv calls ({n}x{k} q4_0)", "variants": variants}
-
-
-def _device_floats(torch, address: int, count: int):
-    """`count` floats at a raw device address, copied into a torch tensor."""
-    import ctypes
-    out = torch.empty(count, dtype=torch.float32, device="cuda")
-    cudart = ctypes.CDLL("libcudart.so.12")
-    cudart.cudaMemcpy.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_int]
-    if cudart.cudaMemcpy(out.data_ptr(), address, count * 4, 3) != 0:  # device to device
-        raise RuntimeError("cudaMemcpy failed")
-    return out
+    if rank == 0:
+        per_gpu = value / world
+        line = {
+            "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": WORKLOAD_SHARDED, "m": 1, "n": n, "k": k,
+                       "format": FORMAT_NAMES[fmt], "sharding": f"rows /{world} ({rows} per rank)",
+                       "exchange": exchange,
+                       "l2_policy": f"rotates {copies} distinct shard copies "
+                                    f"({copies * shard_bytes / 1e6:.0f} MB > L2 {info['l2_bytes'] / 1e6:.0f} MB)",
+                       "cuda_graph": block.graphed, "timed_repeats": repeats,
+                       "timed_region_ms": total_ms, "variants": qx.variants()},
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": 4 * k,
+                    "d2h_bytes_per_step": 4 * n, "steps": e2e_steps,
+                    "note": "per step on every rank: x from pinned host memory to the GPU, the "
+                            "sharded GEMV with the exchange, the gathered 28672 results back to "
+                            "pinned host memory, one stream synchronisation (max over ranks)"},
+            "gpu_launches": launches_per_step * block.steps * repeats,
+            "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": per_gpu / hbm_peak, "traffic": None,
+                         "peak_source": f"{peak_kind} HBM copy bandwidth",
+                         "note": "per GPU: (algorithmic bytes of the whole matrix / N) / step time, "
+                                 "exchange included"},
+            "selfcheck": selfcheck,
+            "extra": extra,
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
 
 
 def _time_calls(torch, fn, iters, warm=3):
@@ -431,11 +759,11 @@ def _time_calls(torch, fn, iters, warm=3):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one gemv_tc_kernel launch on the headline
-# workload, from the ncu capture summarised in profiles/gemv_tc_q4_0_cfg1.md (algorithmic
-# bytes: 33 103 872)
+# workload from an ncu capture (algorithmic bytes: 33 103 872)
 NCU_DRAM_BYTES_PER_LAUNCH = 33167104
 
-EXTRA_CASES = ("cfg2_w8a8_gemm", "cfg0_q8_0_gemv", "cfg3_q8_0_batched", "cfg4_q4_0_prefill")
+EXTRA_CASES = ("cfg2_w8a8_gemm", "cfg0_q8_0_gemv", "cfg3_q8_0_batched", "cfg4_q4_0_prefill",
+               "w8a32_gemm")
 
 
 def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak, only=None):
@@ -450,6 +778,8 @@ def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak, only=None):
         out.update(_extra_cfg3(qx, wl, torch, hbm_peak))
     if only in (None, "cfg4_q4_0_prefill"):
         out.update(_extra_cfg4(qx, wl, torch, bf16_peak))
+    if only in (None, "w8a32_gemm"):
+        out.update(_extra_w8a32(qx, wl, torch, hbm_peak))
     return out
 
 
@@ -466,6 +796,8 @@ def _extra_cfg2(qx, wl, torch):
         qx.int8_gemm_dev(w_copies[i % 3], xd, wsd, xsd, y, m, n, k), "int8"), 30)
     out["cfg2_w8a8_gemm"] = {"tops": 2.0 * m * n * k / sec / 1e12, "us": sec * 1e6,
                              "frac_of_nominal_4500_tops": 2.0 * m * n * k / sec / 4.5e15,
+                             "peak_note": "4500 TOPS is the nominal dense int8 figure; no measured "
+                                          "int8 peak exists for this pool",
                              "variant": qx.variants()["int8_gemm"]}
     return out
 
@@ -532,6 +864,26 @@ def _extra_cfg4(qx, wl, torch, bf16_peak):
     return out
 
 
+def _extra_w8a32(qx, wl, torch, hbm_peak):
+    """Weight-only int8 GEMM at the reference bench's own shapes
+    (benchmarks/cases/colibri_ops.cpp:466-478). Algorithmic bytes: W (int8) + scales + X + Y."""
+    out = {}
+    for m, n, k in ((4, 1024, 1408), (16, 4096, 4096)):
+        rng = np.random.default_rng(m)
+        copies = 8 if n * k < (1 << 24) else 10
+        ws = [torch.from_numpy(rng.integers(-127, 128, (n, k), dtype=np.int8)).cuda() for _ in range(copies)]
+        scale = torch.from_numpy(rng.uniform(0.001, 0.01, n).astype(np.float32)).cuda()
+        xd = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).cuda()
+        yd = torch.zeros((m, n), device="cuda")
+        sec = _time_calls(torch, lambda i: qx.check(
+            qx.qgemm_w8a32_dev(ws[i % copies], scale, xd, yd, m, n, k), "w8a32"), 4 * copies)
+        nbytes = n * k + 4 * n + 4 * m * k + 4 * m * n
+        out[f"m{m}_n{n}_k{k}"] = {"us": sec * 1e6, "gbs": nbytes / sec / 1e9,
+                                  "frac_of_measured_hbm": nbytes / sec / 1e9 / hbm_peak,
+                                  "weights_in_l2": bool(n * k * copies < 120e6)}
+    return {"w8a32_gemm": out}
+
+
 def main():
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -554,8 +906,10 @@ def main():
         hbm_peak, bf16_peak, _ = measured_peaks()
         print(json.dumps(extra_measurements(entry.load_package(), load_workloads(), torch, hbm_peak,
                                             bf16_peak, only=args.extra_only)), flush=True)
+    elif int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        run_sharded(args)
     else:
-        run_qx_arm(args)
+        run_single(args)
 
 
 if __name__ == "__main__":

@@ -27,8 +27,16 @@ _ll = C.c_longlong
 _vp = C.c_void_p
 
 
-def build(reference_root: str = "/root/reference") -> None:
+def reference_root() -> str:
+    """Where the reference project's sources are looked for: $QX_REFERENCE_ROOT, else a
+    checkout named `reference` beside this repository."""
+    return os.environ.get("QX_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def build(reference_root: str | None = None) -> None:
     """Compile the C restatement, and the reference library when its sources exist."""
+    reference_root = reference_root or globals()["reference_root"]()
     subprocess.check_call(["make", "-s", "-C", HERE, "oracle"])
     if os.path.isdir(reference_root):
         subprocess.check_call(

@@ -109,25 +109,113 @@ __global__ void __launch_bounds__(256) check_finite_kernel(const float* __restri
   if (__syncthreads_or(bad) && threadIdx.x == 0) atomicOr(flag, 1);
 }
 
-// W8A32, CUDA-core version: one warp per output channel, f32 FMA over k, fixed butterfly.
-__global__ void __launch_bounds__(256) w8a32_simple_kernel(const int8_t* __restrict__ w,
+// ------------------------------------------------------------------------------------
+// W8A32: Y[r,o] = (sum_k X[r,k] * float(W[o,k])) * scale[o], f32 throughout
+// (kernels/quantization/w8a32_gemm_ref.cpp:7-24, w8a32_gemm_avx512.cpp:9-35).
+//
+// A weight-streaming kernel: the int8 weights are read ONCE for up to MT activation rows
+// (the reference re-reads a weight row per activation row), 16 bytes per lane and step, and
+// converted to f32 without the conversion unit (byte ^ 0x80 placed into the mantissa of
+// 2^23, minus 2^23 + 128: exact). A warp owns C output channels; a CTA (8 warps) stages the
+// activations of the current K-chunk (512 columns x MT rows) in shared memory, so one
+// 16-byte shared load feeds 4 * C multiply-adds. Per lane the products accumulate in k
+// order, the 32 lane sums are added by a fixed butterfly: deterministic, and independent of
+// the launch shape. Bound by HBM (the weight bytes) for a handful of rows, by the f32 FMA
+// rate from about 8 rows up (MT * 2 flops per weight byte).
+// ------------------------------------------------------------------------------------
+constexpr int kW8KChunk = 512;  // activation columns staged per step = 32 lanes x 16
+
+__device__ __forceinline__ void int8x4_to_float(uint32_t word, float (&out)[4]) {
+  const uint32_t biased = word ^ 0x80808080u;  // b + 128 in every byte
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[i] = __uint_as_float(__byte_perm(biased, 0x4B000000u, 0x7650 + i)) - 8388736.0f;
+  }
+}
+
+template <int MT, int C>
+__global__ void __launch_bounds__(256) w8a32_stream_kernel(const int8_t* __restrict__ w,
                                                            const float* __restrict__ ws,
                                                            const float* __restrict__ x,
-                                                           float* __restrict__ y, long long m,
+                                                           float* __restrict__ y, int m,
                                                            long long n, long long k,
-                                                           long long ldy) {
-  const int lane = threadIdx.x & 31;
-  const long long o = blockIdx.x * 8LL + (threadIdx.x >> 5);
-  if (o >= n) return;
-  const int8_t* wr = w + o * k;
-  const float scale = ws[o];
-  for (long long r = 0; r < m; ++r) {
-    const float* xr = x + r * k;
-    float sum = 0.0f;
-    for (long long i = lane; i < k; i += 32) sum = fmaf(xr[i], static_cast<float>(wr[i]), sum);
+                                                           long long ldy, int w_vector) {
+  __shared__ __align__(16) float xs[MT][kW8KChunk];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long o0 = (blockIdx.x * 8LL + warp) * C;
+  float acc[C][MT];
 #pragma unroll
-    for (int h = 16; h >= 1; h >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, h);
-    if (lane == 0) y[r * ldy + o] = __fmul_rn(sum, scale);
+  for (int c = 0; c < C; ++c) {
+#pragma unroll
+    for (int r = 0; r < MT; ++r) acc[c][r] = 0.0f;
+  }
+  for (long long k0 = 0; k0 < k; k0 += kW8KChunk) {
+    // this lane's 16 weight bytes of every channel: requested first, so that their latency
+    // runs under the staging of the activations
+    const long long kl = k0 + lane * 16;
+    uint32_t words[C][4];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+      const long long o = o0 + c;
+      words[c][0] = words[c][1] = words[c][2] = words[c][3] = 0u;
+      if (o < n && kl < k) {
+        const int8_t* src = w + o * k + kl;
+        if (w_vector != 0 && kl + 16 <= k) {
+          const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+          words[c][0] = v.x; words[c][1] = v.y; words[c][2] = v.z; words[c][3] = v.w;
+        } else {
+          for (int i = 0; i < 16 && kl + i < k; ++i) {
+            words[c][i >> 2] |= static_cast<uint32_t>(static_cast<uint8_t>(src[i])) << (8 * (i & 3));
+          }
+        }
+      }
+    }
+    __syncthreads();  // the previous chunk has been consumed
+    // column kk = 16 * lane + 4 * q + i of the chunk goes to position 128 * q + 4 * lane + i:
+    // the 32 lanes of a warp then read consecutive 16-byte pieces (no bank conflicts)
+    for (int i = threadIdx.x; i < MT * kW8KChunk; i += 256) {
+      const int r = i / kW8KChunk, kk = i % kW8KChunk;
+      const int at = ((kk >> 2) & 3) * 128 + (kk >> 4) * 4 + (kk & 3);
+      xs[r][at] = (r < m && k0 + kk < k) ? x[static_cast<long long>(r) * k + k0 + kk] : 0.0f;
+    }
+    __syncthreads();
+    float wf[C][16];
+#pragma unroll
+    for (int c = 0; c < C; ++c) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float f[4];
+        int8x4_to_float(words[c][q], f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) wf[c][4 * q + i] = f[i];
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float4 xv = *reinterpret_cast<const float4*>(&xs[r][q * 128 + lane * 4]);
+#pragma unroll
+        for (int c = 0; c < C; ++c) {
+          acc[c][r] = fmaf(xv.x, wf[c][4 * q], acc[c][r]);
+          acc[c][r] = fmaf(xv.y, wf[c][4 * q + 1], acc[c][r]);
+          acc[c][r] = fmaf(xv.z, wf[c][4 * q + 2], acc[c][r]);
+          acc[c][r] = fmaf(xv.w, wf[c][4 * q + 3], acc[c][r]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < C; ++c) {
+    const long long o = o0 + c;
+    const float scale = o < n ? ws[o] : 0.0f;
+#pragma unroll
+    for (int r = 0; r < MT; ++r) {
+      float sum = acc[c][r];
+#pragma unroll
+      for (int h = 16; h >= 1; h >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, h);
+      if (lane == 0 && o < n && r < m) y[r * ldy + o] = __fmul_rn(sum, scale);
+    }
   }
 }
 
@@ -157,10 +245,28 @@ qx_status launch_check_finite(const float* v, long long count, int* flag, cudaSt
 qx_status launch_w8a32(const int8_t* w, const float* ws, const float* x, float* y,
                        long long m, long long n, long long k, long long ldy,
                        qx_workspace* /*workspace*/, cudaStream_t stream) {
-  const unsigned grid = static_cast<unsigned>((n + 7) / 8);
-  w8a32_simple_kernel<<<grid, 256, 0, stream>>>(w, ws, x, y, m, n, k, ldy);
-  count_launch();
-  QX_CUDA_TRY(cudaGetLastError());
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  // 16-byte weight loads need 16-byte aligned rows
+  const int w_vector = (reinterpret_cast<uintptr_t>(w) % 16 == 0 && k % 16 == 0) ? 1 : 0;
+  // four channels per warp (each staged activation feeds four multiply-adds) when that still
+  // gives at least half of the SMs a CTA, else one
+  const bool wide = (n + 31) / 32 >= ctx->prop.multiProcessorCount / 2;
+  for (long long r0 = 0; r0 < m; r0 += 16) {
+    const int mc = static_cast<int>(m - r0 < 16 ? m - r0 : 16);
+    const float* xr = x + r0 * k;
+    float* yr = y + r0 * ldy;
+    const unsigned grid = static_cast<unsigned>(wide ? (n + 31) / 32 : (n + 7) / 8);
+    if (mc <= 4) {
+      if (wide) w8a32_stream_kernel<4, 4><<<grid, 256, 0, stream>>>(w, ws, xr, yr, mc, n, k, ldy, w_vector);
+      else w8a32_stream_kernel<4, 1><<<grid, 256, 0, stream>>>(w, ws, xr, yr, mc, n, k, ldy, w_vector);
+    } else {
+      if (wide) w8a32_stream_kernel<16, 4><<<grid, 256, 0, stream>>>(w, ws, xr, yr, mc, n, k, ldy, w_vector);
+      else w8a32_stream_kernel<16, 1><<<grid, 256, 0, stream>>>(w, ws, xr, yr, mc, n, k, ldy, w_vector);
+    }
+    count_launch();
+    QX_CUDA_TRY(cudaGetLastError());
+  }
   return QX_STATUS_OK;
 }
 

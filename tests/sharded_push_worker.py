@@ -67,6 +67,40 @@ def main() -> int:
             got = device_to_host(ptrs[s], n)
             assert np.array_equal(got.view(np.uint32), want[s].cpu().numpy().view(np.uint32)), \
                 f"rank {rank} fmt {fmt} graph step {s}"
+        # Many steps with nothing between them but the stream order, a different activation
+        # vector per step, and one rank held back on the host now and then: every step's
+        # full gathered result (all ranks' slices) is copied aside on the stream and compared
+        # afterwards. A wait that returned early, or a rank overwriting a buffer a peer
+        # still reads, shows up as a stale or mixed slice.
+        import time
+        for m in (1, 4):
+            steps = 24
+            gather_m = gather if m == 1 else sharded.PushAllGather(qx, rows, m)
+            xs_m = [torch.from_numpy(wl.activations_f32(m, k, seed=100 + s)).cuda() for s in range(steps)]
+            wants = []
+            for x in xs_m:
+                y = torch.zeros((m, n), device="cuda")
+                qx.check(full.qgemm_dev(x, y, m, n), "full gemm")
+                wants.append(y)
+            history = torch.zeros((steps, world, m, rows), device="cuda")
+            cudart = ctypes.CDLL("libcudart.so.12")
+            cudart.cudaMemcpyAsync.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                                               ctypes.c_int, ctypes.c_void_p]
+            torch.cuda.synchronize()
+            dist.barrier()
+            stream = torch.cuda.current_stream().cuda_stream
+            for s in range(steps):
+                if s % 5 == rank % 5 and s > 0:
+                    time.sleep(0.002)  # this rank falls behind on the host
+                ptr = gather_m.step(shard, xs_m[s], m)
+                assert cudart.cudaMemcpyAsync(history[s].data_ptr(), ptr, world * m * rows * 4, 3, stream) == 0
+            torch.cuda.synchronize()
+            for s in range(steps):
+                for r in range(world):
+                    want_slice = wants[s][:, r * rows:(r + 1) * rows].contiguous()
+                    assert torch.equal(history[s, r].view(torch.int32), want_slice.view(torch.int32)), \
+                        f"rank {rank} fmt {fmt} m {m}: unsynchronised step {s}, slice of rank {r} differs"
+            dist.barrier()
         status, _ = qx.qgemv(fmt, packed[: 32 * (k // 32) * (18 if fmt == 1 else 34)],
                              wl.activations_f32(1, k)[0], 32, k)  # host call: reports device errors
         assert status == qx.OK, qx.last_error()

@@ -77,3 +77,29 @@ def test_prefill_full_shape_subset(qx, orc, wl):
     sub = packed.reshape(n, -1)[rows].reshape(-1)
     _, ref = orc.qgemm(Q4_0, sub, wl.bf16_bits_to_f32(xb), m, len(rows), k)
     _check(got[:, rows], ref)
+
+
+def test_prefill_full_config(qx, orc, wl):
+    """The prefill configuration at its full shape (28672 x 8192 q4_0 weights, 2048 bf16
+    tokens): 64 seeded output channels x all 2048 tokens against the reference's f32 path on
+    the same inputs (every channel is an independent GEMV), at the stated 1e-2 bound."""
+    import torch
+    c = wl.CONFIGS["cfg4_q4_0_prefill"]
+    n, k, m = c["n"], c["k"], c["m"]
+    packed = wl.packed_blocks(Q4_0, n, k, c["d_lo"], c["d_hi"], seed=0)
+    xb = wl.to_bf16_bits(wl.activations_f32(m, k, seed=4))
+    weights = qx.PackedWeights()
+    assert weights.prepare(Q4_0, packed, n, k) == qx.OK, qx.last_error()
+    y = torch.full((m, n), -7.0, device="cuda")
+    x_dev = torch.from_numpy(xb.view(np.int16)).cuda()
+    assert weights.qgemm_bf16_dev(x_dev, y, m) == qx.OK, qx.last_error()
+    torch.cuda.synchronize()
+    rows = np.sort(np.random.default_rng(4).choice(n, 64, replace=False))
+    # first and last channel tile, and the tile boundaries in between, are always included
+    rows[:4] = (0, 127, 128, n - 1)
+    rows = np.unique(rows)
+    got = y[:, torch.from_numpy(rows).cuda()].cpu().numpy()
+    sub = packed.reshape(n, -1)[rows].reshape(-1).copy()
+    _, ref = orc.qgemm(Q4_0, sub, wl.bf16_bits_to_f32(xb), m, len(rows), k)
+    _check(got, ref)
+    assert qx.lib.qx_check_device_errors() == qx.OK, qx.last_error()
