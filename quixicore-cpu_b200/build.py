@@ -17,7 +17,7 @@ NVCC_FLAGS = [
     "-Xcompiler", "-fPIC,-fvisibility=hidden", "--expt-relaxed-constexpr",
     "-I", os.path.join(ROOT, "include"), "-I", CSRC,
 ]
-# developer switch: QX_B200_DEFINES="-DQX_GEMV_PROFILE" adds per-role wait accounting
+# developer switch: extra -D defines for experiments
 NVCC_FLAGS += os.environ.get("QX_B200_DEFINES", "").split()
 
 

@@ -82,6 +82,7 @@ struct TcGeom {
   // (at most kWorkSlots slabs ahead of the MMAs) never lap the epilogue (at most the
   // accumulator ring behind the MMAs); checked below
   static constexpr int kConstSlots = kFused ? (MP == 1 ? 32 : 16) : 0;
+  static constexpr int kConstRing = kConstSlots > 0 ? kConstSlots : 1;  // divisor (never 0)
   // Images that come from the quantizer kernel travel with the weights (copied as far
   // ahead); images built in the kernel sit in the work slot.
   static constexpr int kSlotBytes = kWBytes + (kFused ? 0 : (kXBytes + 1023) / 1024 * 1024);
@@ -116,10 +117,7 @@ struct TcGeom {
   // Decode batches are bound by the per-slab latency of an epilogue thread (barrier waits,
   // TMEM load, a dependent chain per block), so a single activation row gets three sets; batches two (three
   // would leave them too few registers per thread).
-#ifndef QX_GEMV_SETS1
-#define QX_GEMV_SETS1 3
-#endif
-  static constexpr int kSets = MP == 1 ? QX_GEMV_SETS1 : 2;
+  static constexpr int kSets = MP == 1 ? 3 : 2;
   // Each epilogue set has its own ring of accumulators, so every TMEM barrier is used by
   // one set only (a parity wait cannot tell apart phases two steps apart).
   static constexpr int kTPerSet = kTStages / kSets;
@@ -177,7 +175,6 @@ struct GemvTcParams {
   int* peer_flag[kMaxPushPeers];    // on the other ranks: this rank's "slice complete" word
   int* own_flag;                    // this rank's own word for its slice
   int* launch_counter;              // local, zero between launches: CTAs that are done
-  long long* debug;  // [ctas][32] counters, profiling builds only
 };
 
 template <int FMT, int MP>
@@ -336,7 +333,6 @@ gemv_tc_kernel(const GemvTcParams p) {
   // kernels queued behind this one may be scheduled as soon as SMs free up; whatever they
   // touch of this kernel's data they guard with their own griddepcontrol.wait
   asm volatile("griddepcontrol.launch_dependents;");
-  if (threadIdx.x == 0) QX_PROF_STAMP(10);
 
   // This CTA's contiguous range of K units (32-bit arithmetic only: it sits in front of the
   // first weight copy). Units tile every row tile's slabs contiguously, so the range is one
@@ -369,7 +365,6 @@ gemv_tc_kernel(const GemvTcParams p) {
     for (int s = 0; s < G::kSlots; ++s) mbar_init(&bars->raw_full[s], 1);  // expect_tx arrival
     bars->abort_flag = 0;
     mbar_fence_init();
-    QX_PROF_STAMP(24);
     for (int i = 0; i < ahead; ++i) {
       mbar_arrive_expect_tx(&bars->raw_full[i], kTxBytes);
       bulk_copy_g2s(smem + i * G::kSlotBytes, wsrc, G::kWBytes, &bars->raw_full[i]);
@@ -412,19 +407,16 @@ gemv_tc_kernel(const GemvTcParams p) {
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = bars->tmem_base;
-  if (threadIdx.x == 0) QX_PROF_STAMP(11);
 
   if (warp == 0) {
     // ------------------------------ copy producer -----------------------------
     // Slab i uses weight slot i mod kSlots, free again when slab i - kSlots is done.
     if (lane == 0) {
       bool ok = true;
-      QX_PROF_DECL(w_empty);
       int xslab = slab0;
       if (!G::kFused) {
         // the activation images are the output of the kernel in front of this one
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        QX_PROF_STAMP(12);
         for (int i = 0; i < ahead; ++i) {
           bulk_copy_g2s(smem + i * G::kSlotBytes + G::kWBytes,
                         p.ximg + static_cast<long long>(xslab) * G::kXBytes, G::kXBytes,
@@ -434,7 +426,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       }
       RingPos freed;  // slab i - kSlots
       for (int i = G::kSlots; i < count; ++i) {
-        if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag))) {
+        if (!mbar_wait(&bars->done[freed.slot], freed.phase, abort_flag)) {
           ok = false;
           break;
         }
@@ -449,8 +441,6 @@ gemv_tc_kernel(const GemvTcParams p) {
         }
         freed.advance(G::kSlots);
       }
-      QX_PROF_STORE(0, w_empty);
-      QX_PROF_STAMP(25);
       if (!ok) {
         *abort_flag = 1;
         report_error(p.error, 11);
@@ -466,10 +456,6 @@ gemv_tc_kernel(const GemvTcParams p) {
       uint32_t ring_pos_all = 0, ring_par_all = 0;  // accumulator ring of each epilogue set: 4 bits each
       bool ok = true;
       int gave_up = 12;  // which wait ran out: 12 weights, 15 image, 16 accumulator, 17 high nibbles
-      QX_PROF_DECL(w_full);
-      QX_PROF_DECL(w_tempty);
-      QX_PROF_DECL(w_x);
-      QX_PROF_DECL(w_high);
       int slab = slab0;
       int unit = slab / p.unit_slabs;
       int slab_in_unit = slab - unit * p.unit_slabs;
@@ -478,9 +464,9 @@ gemv_tc_kernel(const GemvTcParams p) {
         // `ready` covers the span only where the masking warps (which wait for it) arrive on
         // it; the quantizer warps run ahead of the copies
         if ((G::kUnpackWarps == 0 &&
-             !QX_PROF_WAIT(w_full, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) ||
+             !mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag)) ||
             (G::kReadyCount > 0 &&
-             !QX_PROF_WAIT(w_full, mbar_wait(&bars->ready[raw.slot], raw.phase, abort_flag)))) {
+             !mbar_wait(&bars->ready[raw.slot], raw.phase, abort_flag))) {
           ok = false;
           break;
         }
@@ -494,7 +480,7 @@ gemv_tc_kernel(const GemvTcParams p) {
           const uint32_t par = (ring_par_all >> (4u * eset)) & 1u;
           const uint32_t ts = eset * G::kTPerSet + pos;
           if (g % G::kGroupsPerStage == 0) {
-            if (!QX_PROF_WAIT(w_tempty, mbar_wait(&bars->tmem_empty[ts], par ^ 1u, abort_flag))) {
+            if (!mbar_wait(&bars->tmem_empty[ts], par ^ 1u, abort_flag)) {
               ok = false;
               gave_up = 16;
               break;
@@ -552,11 +538,6 @@ gemv_tc_kernel(const GemvTcParams p) {
           ++unit;
         }
       }
-      QX_PROF_STAMP(26);
-      QX_PROF_STORE(2, w_full);
-      QX_PROF_STORE(3, w_tempty);
-      QX_PROF_STORE(16, w_x);
-      QX_PROF_STORE(17, w_high);
       if (!ok) {
         *abort_flag = 1;
         report_error(p.error, gave_up);
@@ -571,7 +552,6 @@ gemv_tc_kernel(const GemvTcParams p) {
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are this warp's
     constexpr int kMine = G::kRowsPerThread;
     const int row_in_tile = quarter * 32 + lane;
-    const int epi_thread = threadIdx.x - 64;
     float acc[kMine];  // current unit, activation rows split * kMine ..
 #pragma unroll
     for (int m = 0; m < kMine; ++m) acc[m] = 0.0f;
@@ -645,12 +625,6 @@ gemv_tc_kernel(const GemvTcParams p) {
     RingPos raw, work;
     uint32_t ring_pos = 0, tphase = 0;
     bool ok = true;
-    QX_PROF_DECL(w_tfull);
-    QX_PROF_DECL(c_vis);
-    QX_PROF_DECL(c_ld);
-    QX_PROF_DECL(c_math);
-    QX_PROF_DECL(c_unit);
-    const long long t_start = QX_PROF_NOW();
     int tile = tile0;
     int slab = slab0;
     int unit = slab / p.unit_slabs;
@@ -660,7 +634,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       if (mine) {
         const uint8_t* raw_base = smem + raw.slot * G::kSlotBytes;
         const int4* xcs = reinterpret_cast<const int4*>(
-            G::kFused ? const_ring + (i % (G::kConstSlots > 0 ? G::kConstSlots : 1)) * G::kConstBytes
+            G::kFused ? const_ring + (i % G::kConstRing) * G::kConstBytes
                       : raw_base + G::kWBytes + G::kBBytes);
         uint32_t scw[4] = {0u, 0u, 0u, 0u};  // this row's eight fp16 block scales
         // (large batches keep the loop over accumulators rolled: unrolled, the loop body
@@ -668,13 +642,11 @@ gemv_tc_kernel(const GemvTcParams p) {
 #pragma unroll(G::kRollGroups ? 1 : G::kStagesPerSlab)
         for (int st = 0; st < G::kStagesPerSlab; ++st) {
           const uint32_t ts = eset * G::kTPerSet + ring_pos;
-          if (!QX_PROF_WAIT(w_tfull, mbar_wait(&bars->tmem_full[ts], tphase, abort_flag))) {
+          if (!mbar_wait(&bars->tmem_full[ts], tphase, abort_flag)) {
             ok = false;
             break;
           }
           tc_fence_after_sync();
-          if (i == 0 && st == 0 && epi_thread == 0) QX_PROF_STAMP(13);
-          QX_PROF_BEGIN();
           if (st == 0) {
             // these barriers completed before the MMAs ran; waiting on them here makes the
             // copied scales and the block constants visible to this thread (the constants
@@ -682,8 +654,8 @@ gemv_tc_kernel(const GemvTcParams p) {
             // the slab number: no other barrier of theirs is safe to wait on this late)
             if (!mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag) ||
                 (G::kFused &&
-                 !mbar_wait(&bars->const_ready[i % (G::kConstSlots > 0 ? G::kConstSlots : 1)],
-                            static_cast<uint32_t>(i / (G::kConstSlots > 0 ? G::kConstSlots : 1)) & 1u,
+                 !mbar_wait(&bars->const_ready[i % G::kConstRing],
+                            static_cast<uint32_t>(i / G::kConstRing) & 1u,
                             abort_flag))) {
               ok = false;
               break;
@@ -694,10 +666,8 @@ gemv_tc_kernel(const GemvTcParams p) {
               scw[0] = s4.x; scw[1] = s4.y; scw[2] = s4.z; scw[3] = s4.w;
             }
           }
-          QX_PROF_END(c_vis);
 #pragma unroll
           for (int c0 = 0; c0 < G::kColsPerWarp; c0 += G::kLdCols) {
-            const long long qx_tl_ = QX_PROF_NOW();
             uint32_t v[G::kLdCols / 32][32];
             const uint32_t taddr = tmem_base + ts * G::kTCols + split * G::kColsPerWarp + c0 +
                                    (static_cast<uint32_t>(quarter * 32) << 16);
@@ -709,9 +679,6 @@ gemv_tc_kernel(const GemvTcParams p) {
               __syncwarp();
               if (lane == 0) mbar_arrive(&bars->tmem_empty[ts]);
             }
-            const long long qx_tm_ = QX_PROF_NOW();
-            (void)qx_tl_;
-            QX_PROF_ADD(c_ld, qx_tm_ - qx_tl_);
 #pragma unroll
             for (int q = 0; q < G::kLdCols / 4; ++q) {
               // columns 4*idx .. 4*idx+3: the four digit sums of (block class, activation row)
@@ -739,7 +706,6 @@ gemv_tc_kernel(const GemvTcParams p) {
                 acc[lm] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[lm]);
               }
             }
-            QX_PROF_ADD(c_math, QX_PROF_NOW() - qx_tm_);
           }
           if (++ring_pos == G::kTPerSet) {
             ring_pos = 0;
@@ -748,18 +714,15 @@ gemv_tc_kernel(const GemvTcParams p) {
         }
         if (!ok) break;
         __syncwarp();
-        if (epi_thread == 0 && i / G::kSets < 10) QX_PROF_STAMP2(i / G::kSets);
         if (lane == 0) {
           mbar_arrive(&bars->done[raw.slot]);  // scales consumed
-          if (G::kFused) mbar_arrive(&bars->const_free[i % (G::kConstSlots > 0 ? G::kConstSlots : 1)]);
+          if (G::kFused) mbar_arrive(&bars->const_free[i % G::kConstRing]);
         }
       }
       raw.advance(G::kSlots);
       work.advance(G::kWorkSlots);
 
       // ---- unit / tile boundaries ----
-      const long long qx_tu_ = QX_PROF_NOW();
-      (void)qx_tu_;
       const bool unit_end = slab_in_unit + 1 == p.unit_slabs || slab == p.slabs - 1;
       if (unit_end) {
         if (mine) {
@@ -786,7 +749,6 @@ gemv_tc_kernel(const GemvTcParams p) {
           units_mine = 0;
         }
       }
-      QX_PROF_ADD(c_unit, QX_PROF_NOW() - qx_tu_);
       // advance (tile, slab, unit) without divisions
       if (++slab == p.slabs) {
         slab = 0;
@@ -798,18 +760,8 @@ gemv_tc_kernel(const GemvTcParams p) {
         ++unit;
       }
     }
-    if (epi_thread == 0) QX_PROF_STAMP(14);
     count_open();
     resolve_counted();
-    if (epi_thread == 0) {
-      QX_PROF_STAMP(27);
-      QX_PROF_STORE(4, w_tfull);
-      QX_PROF_STORE(6, QX_PROF_NOW() - t_start);
-      QX_PROF_STORE(1, c_vis);
-      QX_PROF_STORE(5, c_ld);
-      QX_PROF_STORE(7, c_math);
-      QX_PROF_STORE(8, c_unit);
-    }
     if (!ok) {
       *abort_flag = 1;
       report_error(p.error, 13);
@@ -821,19 +773,14 @@ gemv_tc_kernel(const GemvTcParams p) {
     // position. The four warps take a quarter of every slab each.
     const int u = warp - G::kFirstUnpackWarp;
     bool ok = true;
-    QX_PROF_DECL(w_raw);
-    QX_PROF_DECL(w_slot);
-    const long long t_u0 = QX_PROF_NOW();
     RingPos raw, work;
     for (int i = 0; i < count; ++i) {
-      if (!QX_PROF_WAIT(w_raw, mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag))) {
+      if (!mbar_wait(&bars->raw_full[raw.slot], raw.phase, abort_flag)) {
         ok = false;
         break;
       }
-      if (i == 0 && u == 0 && lane == 0) QX_PROF_STAMP(28);
-      if (i == count - 1 && u == 0 && lane == 0) QX_PROF_STAMP(29);
       if (i >= G::kWorkSlots) {  // the work slot's previous tile has been consumed
-        if (!QX_PROF_WAIT(w_slot, mbar_wait(&bars->mma_done[work.slot], work.phase ^ 1u, abort_flag))) {
+        if (!mbar_wait(&bars->mma_done[work.slot], work.phase ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
@@ -853,11 +800,6 @@ gemv_tc_kernel(const GemvTcParams p) {
       if (lane == 0) mbar_arrive(&bars->ready[raw.slot]);
       raw.advance(G::kSlots);
       work.advance(G::kWorkSlots);
-    }
-    if (lane == 0 && u == 0) {
-      QX_PROF_STORE(9, w_raw);
-      QX_PROF_STORE(20, w_slot);
-      QX_PROF_STORE(21, QX_PROF_NOW() - t_u0);
     }
     if (!ok) {
       *abort_flag = 1;
@@ -934,10 +876,6 @@ gemv_tc_kernel(const GemvTcParams p) {
     uint8_t* digits = work_ring + qw * G::kWorkBytes + G::kHBytes;
     // the activations may be the output of the kernel in front of this one
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (lane == 0 && qw == 0) QX_PROF_STAMP(12);
-    QX_PROF_DECL(w_free);
-    QX_PROF_DECL(c_image);
-    const long long t_q0 = QX_PROF_NOW();
     for (int k = 0; k < kAhead; ++k) copy_ahead();
     for (int i = qw; i < count; i += kW) {
       copy_ahead();
@@ -963,33 +901,26 @@ gemv_tc_kernel(const GemvTcParams p) {
       // weight slot has long moved on to this slab's phase; the constants go to entry
       // i mod kConstSlots once the epilogue has released its previous user.
       if ((slot_uses > 0 &&
-           !QX_PROF_WAIT(w_free, mbar_wait(&bars->mma_done[qw], (slot_uses - 1u) & 1u, abort_flag))) ||
-          (i >= G::kConstSlots &&
-           !mbar_wait(&bars->const_free[i % G::kConstSlots],
-                      (static_cast<uint32_t>(i / G::kConstSlots) - 1u) & 1u, abort_flag))) {
+           !mbar_wait(&bars->mma_done[qw], (slot_uses - 1u) & 1u, abort_flag)) ||
+          (i >= G::kConstRing &&
+           !mbar_wait(&bars->const_free[i % G::kConstRing],
+                      (static_cast<uint32_t>(i / G::kConstRing) - 1u) & 1u, abort_flag))) {
         ok = false;
         break;
       }
       {
-        QX_PROF_BEGIN();
         write_slab_image<FMT, MP>(
-            digits, reinterpret_cast<XConst*>(const_ring + (i % G::kConstSlots) * G::kConstBytes),
+            digits, reinterpret_cast<XConst*>(const_ring + (i % G::kConstRing) * G::kConstBytes),
             digit_offset, cur_lo, cur_hi, cur_valid, lane);
-        QX_PROF_END(c_image);
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(&bars->const_ready[i % G::kConstSlots]);
+        mbar_arrive(&bars->const_ready[i % G::kConstRing]);
         mbar_arrive(&bars->ready[raw.slot]);
       }
       raw.advance_by(kW, G::kSlots);
       ++slot_uses;
-    }
-    if (lane == 0 && qw == 0) {
-      QX_PROF_STORE(18, w_free);
-      QX_PROF_STORE(19, QX_PROF_NOW() - t_q0);
-      QX_PROF_STORE(22, c_image);
     }
     if (!ok) {
       *abort_flag = 1;
@@ -1024,7 +955,6 @@ gemv_tc_kernel(const GemvTcParams p) {
       asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.own_flag), "r"(step) : "memory");
     }
   }
-  if (threadIdx.x == 0) QX_PROF_STAMP(15);
 }
 
 template <int FMT, int MP>
@@ -1078,21 +1008,6 @@ qx_status launch_fmt(int mp, const GemvTcParams& p, int grid, cudaStream_t strea
 }
 
 }  // namespace
-
-// Device buffer the profiling build writes its cycle counters to (null otherwise).
-long long* gemv_profile_buffer() {
-#if defined(QX_GEMV_PROFILE) || defined(QX_GEMV_STAMPS)
-  static long long* buffer = []() {
-    long long* ptr = nullptr;
-    if (cudaMalloc(&ptr, 64 * 1024 * 32 * sizeof(long long)) != cudaSuccess) return static_cast<long long*>(nullptr);
-    (void)cudaMemset(ptr, 0, 64 * 1024 * 32 * sizeof(long long));
-    return ptr;
-  }();
-  return buffer;
-#else
-  return nullptr;
-#endif
-}
 
 // K split: units of U slabs with at most 16 units per row; a function of K alone.
 static int unit_slabs_for(long long slabs) { return static_cast<int>((slabs + 15) / 16); }
@@ -1167,13 +1082,6 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
     p.own_flag = push->own_flag;
     p.launch_counter = push->launch_counter;
   }
-  p.debug = gemv_profile_buffer();
-#if defined(QX_GEMV_PROFILE) || defined(QX_GEMV_STAMPS)
-  {
-    static int launch_seq = 0;
-    if (p.debug != nullptr) p.debug += static_cast<long long>(launch_seq++ % 64) * 1024 * 32;
-  }
-#endif
   if (w->format == QX_FORMAT_Q8_0) {
     return launch_fmt<QX_FORMAT_Q8_0>(padded_batch(m), p, scratch.ctas, stream);
   }
@@ -1181,19 +1089,3 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
 }
 
 }  // namespace qx
-
-#if defined(QX_GEMV_PROFILE) || defined(QX_GEMV_STAMPS)
-// Profiling builds only: copies the per-CTA cycle counters of the last launches to the
-// host (32 values per CTA) and clears them.
-extern "C" QX_API int qx_debug_gemv_profile(long long* host_out, int ctas) {
-  long long* buffer = qx::gemv_profile_buffer();
-  if (buffer == nullptr || ctas != 64 * 1024) return -1;
-  if (cudaDeviceSynchronize() != cudaSuccess) return -2;
-  if (cudaMemcpy(host_out, buffer, sizeof(long long) * 32 * ctas, cudaMemcpyDeviceToHost) !=
-      cudaSuccess) {
-    return -3;
-  }
-  (void)cudaMemset(buffer, 0, 64 * 1024 * 32 * sizeof(long long));
-  return 0;
-}
-#endif

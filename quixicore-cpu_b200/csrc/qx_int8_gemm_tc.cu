@@ -104,7 +104,6 @@ struct TcParams {
   int32_t* partial;    // [cta][2][bn][128] partial accumulators of split tiles (stream-K)
   int* tile_counters;  // [tiles], zero between launches (stream-K)
   int* error;    // device word, set non-zero when a bounded wait gave up
-  long long* debug;  // profiling builds only
 };
 
 // One contiguous piece of work: K-slabs [ks0, ks1) of a tile.
@@ -215,8 +214,6 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
     if (elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      QX_PROF_DECL(w_empty);
-      const long long t_start = QX_PROF_NOW();
       WorkIter work(p);
       Segment seg;
       while (ok && work.next(&seg)) {
@@ -224,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
         const int o0 = (tile / p.r_tiles) * (NA * kBM);
         const int r0 = (tile % p.r_tiles) * p.bn;
         for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
-          if (!QX_PROF_WAIT(w_empty, mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag))) {
+          if (!mbar_wait(&bars->empty[stage], phase ^ 1u, abort_flag)) {
             ok = false;
             break;
           }
@@ -238,8 +235,6 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
           }
         }
       }
-      QX_PROF_STORE(0, w_empty);
-      QX_PROF_STORE(1, QX_PROF_NOW() - t_start);
       if (!ok) {
         *abort_flag = 1;
         report_error(p.error, 1);
@@ -250,20 +245,17 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
     if (elect_one()) {
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      QX_PROF_DECL(w_full);
-      QX_PROF_DECL(w_tempty);
-      const long long t_start = QX_PROF_NOW();
       WorkIter work(p);
       Segment seg;
       while (ok && work.next(&seg)) {
-        if (!QX_PROF_WAIT(w_tempty, mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, abort_flag))) {
+        if (!mbar_wait(&bars->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
           ok = false;
           break;
         }
         tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * (NA * 256u);
         for (int ks = seg.ks0; ks < seg.ks1; ++ks) {
-          if (!QX_PROF_WAIT(w_full, mbar_wait(&bars->full[stage], phase, abort_flag))) {
+          if (!mbar_wait(&bars->full[stage], phase, abort_flag)) {
             ok = false;
             break;
           }
@@ -296,9 +288,6 @@ __global__ void __launch_bounds__(kThreads, 1) int8_gemm_tc_kernel(
           acc_phase ^= 1u;
         }
       }
-      QX_PROF_STORE(2, w_full);
-      QX_PROF_STORE(3, w_tempty);
-      QX_PROF_STORE(6, QX_PROF_NOW() - t_start);
       if (!ok) {
         *abort_flag = 1;
         report_error(p.error, 2);
@@ -597,7 +586,6 @@ qx_status launch_int8_gemm_tc(const Int8GemmArgs& a, cudaStream_t stream) {
   p.r_tiles = static_cast<int>(r_tiles);
   p.asymmetric = a.asymmetric ? 1 : 0;
   p.error = ctx->error_dev;
-  p.debug = gemv_profile_buffer();
   const long long tiles = static_cast<long long>(p.o_tiles) * p.r_tiles;
   p.stream_k = stream_k ? 1 : 0;
   if (stream_k) {

@@ -182,53 +182,6 @@ __device__ __forceinline__ uint64_t make_sw128_kmajor_desc(uint32_t smem_addr) {
 
 }  // namespace sm100
 
-// Optional per-role wait accounting (build with -DQX_GEMV_PROFILE): cycles spent in each
-// kind of barrier wait, written per CTA to the kernel parameter `debug`. Compiled out otherwise.
-#ifdef QX_GEMV_PROFILE
-#define QX_PROF_DECL(name) long long name = 0
-#define QX_PROF_WAIT(counter, expr)            \
-  [&]() {                                      \
-    const long long qx_t0_ = clock64();        \
-    const bool qx_ok_ = (expr);                \
-    counter += clock64() - qx_t0_;             \
-    return qx_ok_;                             \
-  }()
-#define QX_PROF_STORE(slot, value) \
-  if (p.debug != nullptr) p.debug[blockIdx.x * 32 + (slot)] = (value)
-#define QX_PROF_NOW() clock64()
-#define QX_PROF_BEGIN() const long long qx_tb_ = clock64()
-#define QX_PROF_END(counter) counter += clock64() - qx_tb_
-#define QX_PROF_ADD(counter, value) counter += (value)
-#define QX_PROF_STAMP(slot) \
-  if (p.debug != nullptr) p.debug[blockIdx.x * 32 + (slot)] = static_cast<long long>(sm100::global_timer_ns())
-#define QX_PROF_STAMP2(slot)
-#elif defined(QX_GEMV_STAMPS)
-// time stamps only (no wait accounting: that perturbs the pipeline)
-#define QX_PROF_DECL(name)
-#define QX_PROF_WAIT(counter, expr) (expr)
-#define QX_PROF_STORE(slot, value)
-#define QX_PROF_NOW() 0
-#define QX_PROF_BEGIN()
-#define QX_PROF_END(counter)
-#define QX_PROF_ADD(counter, value)
-#define QX_PROF_STAMP(slot) \
-  if (p.debug != nullptr) p.debug[blockIdx.x * 32 + (slot)] = static_cast<long long>(sm100::global_timer_ns())
-#define QX_PROF_STAMP2(slot) QX_PROF_STAMP(slot)
-#else
-#define QX_PROF_DECL(name)
-#define QX_PROF_WAIT(counter, expr) (expr)
-#define QX_PROF_STORE(slot, value)
-#define QX_PROF_NOW() 0
-#define QX_PROF_BEGIN()
-#define QX_PROF_END(counter)
-#define QX_PROF_ADD(counter, value)
-#define QX_PROF_STAMP(slot)
-#define QX_PROF_STAMP2(slot)
-#endif
-
-// Device buffer [1024 CTAs][32] the profiling build writes its counters to (null otherwise).
-long long* gemv_profile_buffer();
-
 // Host side: cuTensorMapEncodeTiled through the runtime's driver entry point lookup (the
 // library does not link libcuda). Encodes a row-major 2D tensor [rows][row_bytes /
 // elem_bytes] with the given box and the 128-byte swizzle.
