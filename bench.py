@@ -457,8 +457,8 @@ def run_single(args):
     # end to end through the host-pointer entry point: pinned x in, pinned y out, every step
     x_pin = torch.from_numpy(x_host).pin_memory()
     y_pin = torch.zeros(n).pin_memory()
-    e2e_steps = max(10, min(args.steps, 2000))
-    for i in range(3):
+    e2e_steps = max(300, min(args.steps, 2000))
+    for i in range(10):
         qx.check(handles[i % copies].qgemm_prepacked_ptr(x_pin.data_ptr(), y_pin.data_ptr(), 1), "e2e")
     t0 = time.perf_counter()
     for i in range(e2e_steps):
@@ -685,9 +685,9 @@ def run_sharded(args):
             y_pin.copy_(y_full.view(-1), non_blocking=True)
         stream.synchronize()
 
-    e2e_steps = max(10, min(args.steps, 1000))
+    e2e_steps = max(300, min(args.steps, 1000))
     e2e_steps += e2e_steps % 2
-    for i in range(4):
+    for i in range(10):
         e2e_step(i)
     dist.barrier()
     t0 = time.perf_counter()

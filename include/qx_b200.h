@@ -190,42 +190,49 @@ QX_API qx_status qx_qgemm_prepacked_bf16_dev(const qx_weights* weights, const ui
  * reference's quantized-matmul API (its row partition is over threads of one process).
  *
  * Instead of a collective after the GEMV, the kernel's row finishers store each result
- * into every rank's result buffer over NVLink (plain peer stores) and the last CTA sets a
- * per-rank "slice complete" word on every rank; qx_allgather_wait_dev enqueues a small
- * kernel that waits (bounded, 2 s) until all slices of the step have arrived. Steps
- * alternate between two result buffers (a rank may be one step ahead of a peer), and the
- * step number is kept in device memory, so both calls can be captured in a CUDA graph.
+ * into every other rank's INBOX over NVLink as one 8-byte cell {value, valid tag} (plain
+ * peer stores; data and tag travel together, so there are no flags and no fences), and
+ * qx_allgather_wait_dev enqueues the receiving kernel: it takes every cell as soon as its
+ * tag is set, writes the value into this rank's plain result buffer and clears the cell.
+ * It polls while this rank's own GEMV is still running and is through a moment after the
+ * last slice has arrived; every wait is bounded (2 s). Steps alternate between two halves
+ * of the buffers by the parity of `step`, so a rank may be one step ahead of a peer; `step`
+ * counts from 1 and must advance by one per push / wait pair on every rank. Nothing about
+ * a step lives in device memory, so both calls can be captured in a CUDA graph (a captured
+ * sequence that is replayed must hold an even number of steps).
  *
- * Buffers that other ranks write must be peer-mappable: allocate them with qx_peer_alloc,
- * pass the 64-byte handle to the other processes (any channel) and map it there with
- * qx_peer_open. Result buffer layout: [2 parities][world][m][rows_per_rank] floats
- * (uniform shards); control block: qx_push_control_bytes() bytes, zero-initialised by
- * qx_peer_alloc. */
+ * The inbox must be peer-mappable: allocate it with qx_peer_alloc
+ * (qx_push_inbox_bytes(world, m, rows) bytes, zero-initialised), pass the 64-byte handle to
+ * the other processes (any channel) and map it there with qx_peer_open. Layouts:
+ * results [2 parities][world][m][rows_per_rank] floats (ordinary device memory),
+ * inbox   [2 parities][world][m][rows_per_rank] 8-byte cells. */
 typedef struct qx_push_plan {
   int world;                 /* ranks, 2..8 */
   int rank;                  /* this rank */
   long long rows_per_rank;   /* rows of every shard (the handle's row count) */
   float* results_local;      /* this rank's result buffer (device pointer) */
-  void* control_local;       /* this rank's control block */
-  float* results_peer[8];    /* results_peer[r]: rank r's result buffer mapped here (r != rank) */
-  void* control_peer[8];     /* control_peer[r]: rank r's control block mapped here (r != rank) */
+  void* inbox_local;         /* this rank's inbox (device pointer) */
+  void* inbox_peer[8];       /* inbox_peer[r]: rank r's inbox mapped here (r != rank) */
 } qx_push_plan;
 
-QX_API size_t qx_push_control_bytes(void);
+QX_API size_t qx_push_inbox_bytes(int world, long long m, long long rows_per_rank);
 QX_API qx_status qx_peer_alloc(size_t bytes, void** dev_ptr, unsigned char handle[64]);
 QX_API qx_status qx_peer_open(const unsigned char handle[64], void** dev_ptr);
 QX_API qx_status qx_peer_close(void* dev_ptr);
 QX_API qx_status qx_peer_free(void* dev_ptr);
 /* y = x . dequant(W_shard)^T for m <= 32 activation rows, written to this rank's slice of
- * the step's result buffer on every rank. Only enqueues. */
+ * the step's result buffer and to every other rank's inbox. Only enqueues. */
 QX_API qx_status qx_qgemm_prepacked_push_dev(const qx_weights* weights, const float* x_dev,
                                              long long m, const qx_push_plan* plan,
-                                             qx_workspace* workspace, void* stream);
-/* Enqueues the wait for all ranks' slices of the next step in order; *results_dev (host
+                                             long long step, qx_workspace* workspace,
+                                             void* stream);
+/* Enqueues the receive of all other ranks' slices of step `step`; *results_dev (host
  * variable, optional) receives the device address of that step's [world][m][rows_per_rank]
- * results in this rank's buffer. A wait that runs out (2 s; QX_B200_WAIT_LIMIT_MS in the
- * environment overrides it) sets the error word reported by qx_check_device_errors() or the
- * next host-pointer call (QX_STATUS_DEVICE_ERROR, role code 31); the kernel then returns. */
+ * results in this rank's buffer, complete once this kernel has completed. A cell that does
+ * not arrive in time (2 s; QX_B200_WAIT_LIMIT_MS in the environment overrides it) sets the
+ * error word reported by qx_check_device_errors() or the next host-pointer call
+ * (QX_STATUS_DEVICE_ERROR, role code 31); the kernel then returns. After such an error the
+ * inbox may hold cells of the abandoned step: clear it before the plan is used again. */
 QX_API qx_status qx_allgather_wait_dev(const qx_push_plan* plan, long long m, long long step,
                                        const float** results_dev, void* stream);
 

@@ -47,8 +47,8 @@ class WeightsInfo(C.Structure):
 class PushPlan(C.Structure):
     """qx_push_plan of include/qx_b200.h."""
     _fields_ = [("world", C.c_int), ("rank", C.c_int), ("rows_per_rank", C.c_longlong),
-                ("results_local", C.c_void_p), ("control_local", C.c_void_p),
-                ("results_peer", C.c_void_p * 8), ("control_peer", C.c_void_p * 8)]
+                ("results_local", C.c_void_p), ("inbox_local", C.c_void_p),
+                ("inbox_peer", C.c_void_p * 8)]
 
 
 class DeviceInfo(C.Structure):
@@ -91,7 +91,7 @@ def _load():
         "qx_peer_open": [_vp, C.POINTER(_vp)],
         "qx_peer_close": [_vp],
         "qx_peer_free": [_vp],
-        "qx_qgemm_prepacked_push_dev": [_vp, _vp, _ll, C.POINTER(PushPlan), _vp, _vp],
+        "qx_qgemm_prepacked_push_dev": [_vp, _vp, _ll, C.POINTER(PushPlan), _ll, _vp, _vp],
         "qx_allgather_wait_dev": [C.POINTER(PushPlan), _ll, _ll, C.POINTER(_vp), _vp],
     }
     for name, argtypes in sig.items():
@@ -112,7 +112,8 @@ def _load():
     lib.qx_set_num_threads.restype = None
     lib.qx_num_threads.restype = C.c_int
     lib.qx_kernel_launch_count.restype = C.c_ulonglong
-    lib.qx_push_control_bytes.restype = _sz
+    lib.qx_push_inbox_bytes.argtypes = [C.c_int, _ll, _ll]
+    lib.qx_push_inbox_bytes.restype = _sz
     return lib
 
 
@@ -290,13 +291,14 @@ def peer_open(handle: bytes) -> int:
     return ptr.value
 
 
-def push_control_bytes() -> int:
-    return lib.qx_push_control_bytes()
+def push_inbox_bytes(world: int, m: int, rows_per_rank: int) -> int:
+    return lib.qx_push_inbox_bytes(world, m, rows_per_rank)
 
 
-def qgemm_push_dev(weights: "PackedWeights", x, m: int, plan: PushPlan) -> int:
+def qgemm_push_dev(weights: "PackedWeights", x, m: int, plan: PushPlan, step: int) -> int:
     """Sharded GEMV whose results land in every rank's buffer (fused all-gather)."""
-    return lib.qx_qgemm_prepacked_push_dev(weights.handle, _dev(x), m, C.byref(plan), None, _stream())
+    return lib.qx_qgemm_prepacked_push_dev(weights.handle, _dev(x), m, C.byref(plan), step, None,
+                                           _stream())
 
 
 def allgather_wait_dev(plan: PushPlan, m: int, step: int) -> int:

@@ -162,19 +162,11 @@ struct GemvTcParams {
   int unit_slabs, units_per_tile;  // K split: units of unit_slabs slabs
   // unit ranges of the CTAs: CTA c takes units_per_cta units, the first units_rem CTAs one more
   uint32_t units_per_cta, units_rem;
-  // Row-sharded runs (one process per GPU): the finished outputs are also stored straight
-  // into the other ranks' result buffers over NVLink, and the last CTA of the launch tells
-  // every rank that this rank's slice is complete (an all-gather fused into the epilogue).
-  // Steps alternate between two result buffers; the step number lives in device memory
-  // (push_count), so the same launch can be replayed from a CUDA graph.
-  int peers;                        // other ranks (0: no push)
-  int* push_count;                  // local: pushes completed so far; this launch is step + 1
-  float* y_odd;                     // local result buffer of odd steps (y: even steps)
-  float* y_peer[kMaxPushPeers];     // the other ranks' even-step buffers, at this rank's slice
-  float* y_peer_odd[kMaxPushPeers];
-  int* peer_flag[kMaxPushPeers];    // on the other ranks: this rank's "slice complete" word
-  int* own_flag;                    // this rank's own word for its slice
-  int* launch_counter;              // local, zero between launches: CTAs that are done
+  // Row-sharded runs (one process per GPU): every finished output is also stored into the
+  // other ranks' inboxes over NVLink as an 8-byte {value, valid} cell (an all-gather fused
+  // into the epilogue; the receiving side is allgather_unpack_kernel in qx_peer.cu).
+  int peers;                          // other ranks (0: no push)
+  PushCell* push_cells[kMaxPushPeers];  // the other ranks' inboxes, at this rank's slice
 };
 
 template <int FMT, int MP>
@@ -567,10 +559,6 @@ gemv_tc_kernel(const GemvTcParams p) {
     int cnt_tile = 0, cnt_add = 0, cnt_old = 0;   // counted in, result not looked at
     // this thread completed the row's count in `tile`: add its unit sums in the fixed order
     auto finish_row = [&](int done_tile) {
-      // (pushing launches alternate between two result buffers by the parity of their
-      // step; the counter is read here, after data has flowed through the pipeline, i.e.
-      // after the launch in front of this one has completed and advanced it)
-      const bool push_odd = p.peers > 0 && ((__ldcg(p.push_count) + 1) & 1) != 0;
       const long long row = static_cast<long long>(done_tile) * kTileRows + row_in_tile;
       const float* slots = p.partial +
                            static_cast<long long>(done_tile) * p.units_per_tile * p.m * kTileRows +
@@ -594,8 +582,13 @@ gemv_tc_kernel(const GemvTcParams p) {
         if (row < p.rows) {
           const float value = even + odd;
           const long long at = m * p.ldy + row;
-          (push_odd ? p.y_odd : p.y)[at] = value;
-          for (int r = 0; r < p.peers; ++r) (push_odd ? p.y_peer_odd[r] : p.y_peer[r])[at] = value;
+          p.y[at] = value;
+          for (int r = 0; r < p.peers; ++r) {
+            // value and tag in ONE 8-byte store: whoever sees the tag sees the value
+            asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p.push_cells[r] + at),
+                         "r"(__float_as_uint(value)), "r"(kPushValid)
+                         : "memory");
+          }
         }
       }
       p.counters[static_cast<long long>(done_tile) * kTileRows + row_in_tile] = 0;  // next launch
@@ -934,27 +927,6 @@ gemv_tc_kernel(const GemvTcParams p) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, 512);
   }
-  if (p.peers > 0 && threadIdx.x == 0) {
-    // The CTA that finishes last publishes "this rank's slice is complete" on every rank.
-    // Ordering of the result stores before that word: the storing threads -> the barrier
-    // above -> this thread's fence and counter update (device scope) -> the last CTA's
-    // system-scope fence and release stores; the waiting rank acquires the word.
-    // (Sending the finished slice from the last CTA as bulk copies instead of storing row by
-    // row from the finishers was measured slower: 21 against 18.5 us per step on two GPUs,
-    // 37 against 29 us on eight.)
-    __threadfence();
-    const int finished = atomicAdd(p.launch_counter, 1);
-    if (finished == static_cast<int>(gridDim.x) - 1) {
-      *p.launch_counter = 0;  // next launch
-      const int step = *p.push_count + 1;
-      *p.push_count = step;
-      __threadfence_system();
-      for (int r = 0; r < p.peers; ++r) {
-        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.peer_flag[r]), "r"(step) : "memory");
-      }
-      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p.own_flag), "r"(step) : "memory");
-    }
-  }
 }
 
 template <int FMT, int MP>
@@ -1072,15 +1044,7 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
       return QX_STATUS_INVALID_ARGUMENT;
     }
     p.peers = push->peers;
-    p.push_count = push->push_count;
-    p.y_odd = push->y_odd;
-    for (int r = 0; r < push->peers; ++r) {
-      p.y_peer[r] = push->y_peer[r];
-      p.y_peer_odd[r] = push->y_peer_odd[r];
-      p.peer_flag[r] = push->peer_flag[r];
-    }
-    p.own_flag = push->own_flag;
-    p.launch_counter = push->launch_counter;
+    for (int r = 0; r < push->peers; ++r) p.push_cells[r] = push->cells[r];
   }
   if (w->format == QX_FORMAT_Q8_0) {
     return launch_fmt<QX_FORMAT_Q8_0>(padded_batch(m), p, scratch.ctas, stream);

@@ -22,19 +22,19 @@ struct GemvScratch {
 // between launches); the rest is laid out per call.
 qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScratch* out);
 
-// Row-sharded runs: where the kernel also stores its results on the other ranks
-// (peer-mapped device pointers, already offset to this rank's slice; two buffers that
-// alternate step by step) and the words it sets to the step number on every rank once the
-// whole slice is written. The step number is kept in device memory (push_count).
+// Row-sharded runs: where the kernel also delivers its results to the other ranks. Every
+// finished output is stored as one 8-byte cell {value bits, valid tag} into each peer's
+// inbox (peer-mapped device pointers, already offset to this rank's slice of the step's
+// parity buffer). Data and tag travel in one store, so the receiver needs no flag and the
+// sender no fence: a cell whose tag is set holds its value.
+struct PushCell {
+  uint32_t value_bits;
+  uint32_t tag;  // kPushValid once written; the receiver clears it when it takes the value
+};
+constexpr uint32_t kPushValid = 1u;
 struct GemvPush {
   int peers = 0;
-  int* push_count = nullptr;      // device word: pushes completed so far
-  float* y_odd = nullptr;         // local buffer of odd steps (the y argument: even steps)
-  float* y_peer[7] = {};
-  float* y_peer_odd[7] = {};
-  int* peer_flag[7] = {};
-  int* own_flag = nullptr;
-  int* launch_counter = nullptr;  // device word, zero between launches
+  PushCell* cells[7] = {};
 };
 
 // Batches of one or two activation rows are quantized inside the GEMV kernel (it reads x);

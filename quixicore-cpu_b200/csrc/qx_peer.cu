@@ -1,8 +1,8 @@
 // Row-sharded decode across the GPUs of one node with the all-gather fused into the GEMV:
 // peer-mappable buffers (CUDA IPC, one process per GPU), the pushing GEMV entry point and
-// the kernel that waits for all ranks' slices. Semantics of all_gather in
-// kernels/collectives/collectives_ref.cpp:26-37; the transport is plain peer stores from
-// the GEMV's row finishers (qx_gemv_tc.cu), no cluster multicast and no remote loads.
+// the kernel that receives the other ranks' slices. Semantics of all_gather in
+// kernels/collectives/collectives_ref.cpp:26-37; the transport is plain 8-byte peer stores
+// from the GEMV's row finishers (qx_gemv_tc.cu), no cluster multicast and no remote loads.
 
 #include <cstdlib>
 #include <cstring>
@@ -14,50 +14,61 @@
 namespace qx {
 namespace {
 
-// control block of a rank: [0..7] slice-complete words (one per rank, written by that
-// rank), [16] pushes completed here, [17] waits completed here, [18] CTAs done in the
-// current launch
-constexpr int kFlagWords = 8, kPushCountWord = 16, kWaitCountWord = 17, kLaunchCounterWord = 18;
-constexpr size_t kControlBytes = 256;
-
-// Lane r waits until rank r's slice of the next step has arrived (bounded), then lane 0
-// advances the local wait counter.
-__global__ void __launch_bounds__(32) allgather_wait_kernel(int* control, int world, int* error,
-                                                            unsigned long long limit_ns) {
-  // Launched programmatically: it may start while the GEMV in front of it still runs (it only
-  // polls), and the kernel behind it may start its own set-up at once; whatever that kernel
-  // reads of the gathered results it guards with griddepcontrol.wait, which returns when
-  // this kernel has finished.
+// Receiving side of the fused all-gather. The inbox of a rank holds, per step parity, one
+// 8-byte cell per (sending rank, activation row, weight row): {value bits, valid tag}. The
+// senders (the GEMV kernels of the other ranks) store value and tag together; this kernel
+// takes every cell of the other ranks' slices as soon as its tag is set, writes the value
+// into the plain result buffer and clears the cell for the step after next. No flags, no
+// fences, no step counter in device memory: the tag travels with the data.
+//
+// It is launched programmatically, so it polls while this rank's own GEMV still runs (its
+// blocks fit beside the GEMV's on the SMs) and is through a moment after the last slice
+// has arrived. Before it exits, every thread waits for the kernels in front of it: when
+// this kernel has completed, this rank's own slice (written by its GEMV) is complete too,
+// which is what the kernel behind it relies on when it reads the gathered results.
+//
+// Why a cell is never overwritten before it is taken: a rank pushes step s + 2 into the
+// parity buffer of step s only after its own receive of step s + 1 has completed; that
+// needed the receiver's push of step s + 1, which the receiver enqueues behind its receive
+// of step s. Every wait is bounded: a cell that does not arrive within the limit makes the
+// thread record role code 31 and stop polling.
+__global__ void __launch_bounds__(256) allgather_unpack_kernel(PushCell* inbox, float* results,
+                                                               long long slice, int world, int rank,
+                                                               int* error,
+                                                               unsigned long long limit_ns) {
   asm volatile("griddepcontrol.launch_dependents;");
-  // The wait counter is advanced by the previous wait kernel of this chain, which may still
-  // be polling for a late peer when this one starts (the GEMV between the two triggers its
-  // dependents at its start): read it only after everything in front has finished. The GEMV
-  // in front sets this rank's own word at its very end, so this costs next to nothing.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  const int lane = threadIdx.x;
-  const int expected = control[kWaitCountWord] + 1;
+  const long long total = static_cast<long long>(world) * slice;
+  const unsigned long long start = sm100::global_timer_ns();
   bool ok = true;
-  if (lane < world) {
-    const unsigned long long start = sm100::global_timer_ns();
-    for (;;) {
-      int seen;
-      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(control + lane) : "memory");
-      if (seen - expected >= 0) break;
-      if (sm100::global_timer_ns() - start > limit_ns) {
-        ok = false;
-        break;
+  for (long long i = blockIdx.x * 256LL + threadIdx.x; i < total && ok; i += gridDim.x * 256LL) {
+    if (i / slice == rank) continue;  // this rank's own slice comes straight from its GEMV
+    uint32_t bits = 0, tag = 0;
+    for (uint32_t spin = 0;; ++spin) {
+      asm volatile("ld.relaxed.sys.global.v2.b32 {%0, %1}, [%2];"
+                   : "=r"(bits), "=r"(tag)
+                   : "l"(inbox + i)
+                   : "memory");
+      if (tag == kPushValid) break;
+      if ((spin & 15u) == 15u) {
+        const unsigned long long waited = sm100::global_timer_ns() - start;
+        if (waited > limit_ns) {
+          ok = false;
+          break;
+        }
+        // poll tightly while the slices are expected any moment, back off afterwards
+        if (waited > 20000ull) __nanosleep(200);
       }
-      // poll tightly while the slices are expected any moment, back off afterwards
-      if (sm100::global_timer_ns() - start > 20000ull) __nanosleep(200);
     }
+    if (!ok) break;
+    results[i] = __uint_as_float(bits);
+    asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %1};" ::"l"(inbox + i), "r"(0u) : "memory");
   }
   if (!ok) sm100::report_error(error, 31);
-  __syncwarp();
-  if (lane == 0) control[kWaitCountWord] = expected;
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 
-// Time limit of the wait kernel: 2 s, or QX_B200_WAIT_LIMIT_MS milliseconds (1..10000) when
-// that is set in the environment (tests of the give-up path use a few milliseconds).
+// Time limit of the receive kernel: 2 s, or QX_B200_WAIT_LIMIT_MS milliseconds (1..10000)
+// when that is set in the environment (tests of the give-up path use a few milliseconds).
 unsigned long long wait_limit_ns() {
   static const unsigned long long limit = []() -> unsigned long long {
     const char* text = std::getenv("QX_B200_WAIT_LIMIT_MS");
@@ -73,13 +84,8 @@ unsigned long long wait_limit_ns() {
 qx_status check_plan(const qx_push_plan* plan) {
   if (plan == nullptr || plan->world < 2 || plan->world > 8 || plan->rank < 0 ||
       plan->rank >= plan->world || plan->rows_per_rank <= 0 || plan->results_local == nullptr ||
-      plan->control_local == nullptr) {
+      plan->inbox_local == nullptr) {
     return QX_STATUS_INVALID_ARGUMENT;
-  }
-  for (int r = 0; r < plan->world; ++r) {
-    if (r != plan->rank && (plan->results_peer[r] == nullptr || plan->control_peer[r] == nullptr)) {
-      return QX_STATUS_INVALID_ARGUMENT;
-    }
   }
   return QX_STATUS_OK;
 }
@@ -89,7 +95,11 @@ qx_status check_plan(const qx_push_plan* plan) {
 
 extern "C" {
 
-size_t qx_push_control_bytes(void) { return qx::kControlBytes; }
+size_t qx_push_inbox_bytes(int world, long long m, long long rows_per_rank) {
+  if (world < 1 || m < 1 || rows_per_rank < 1) return 0;
+  return 2 * static_cast<size_t>(world) * static_cast<size_t>(m) * static_cast<size_t>(rows_per_rank) *
+         sizeof(qx::PushCell);
+}
 
 qx_status qx_peer_alloc(size_t bytes, void** dev_ptr, unsigned char handle[64]) {
   using namespace qx;
@@ -153,32 +163,27 @@ qx_status qx_peer_free(void* dev_ptr) {
 }
 
 qx_status qx_qgemm_prepacked_push_dev(const qx_weights* weights, const float* x_dev, long long m,
-                                      const qx_push_plan* plan, qx_workspace* workspace,
-                                      void* stream) {
+                                      const qx_push_plan* plan, long long step,
+                                      qx_workspace* workspace, void* stream) {
   using namespace qx;
   if (weights == nullptr || x_dev == nullptr) return QX_STATUS_INVALID_ARGUMENT;
   QX_TRY(check_plan(plan));
+  for (int r = 0; r < plan->world; ++r) {
+    if (r != plan->rank && plan->inbox_peer[r] == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  }
+  if (step <= 0) return QX_STATUS_INVALID_ARGUMENT;
   if (m <= 0 || m > kGemvMaxBatch || weights->rows != plan->rows_per_rank) return QX_STATUS_INVALID_SHAPE;
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
-  // result buffer: [parity][world][m][rows_per_rank]; this rank writes slice `rank`
+  // result buffer and inboxes: [parity][world][m][rows_per_rank]; this rank writes slice `rank`
   const long long slice = m * plan->rows_per_rank;
-  const long long parity_stride = static_cast<long long>(plan->world) * slice;
-  const long long offset = static_cast<long long>(plan->rank) * slice;
+  const long long offset = (step & 1) * plan->world * slice + static_cast<long long>(plan->rank) * slice;
   GemvPush push;
   push.peers = plan->world - 1;
-  int* control = static_cast<int*>(plan->control_local);
-  push.push_count = control + kPushCountWord;
-  push.launch_counter = control + kLaunchCounterWord;
-  push.own_flag = control + plan->rank;
-  push.y_odd = plan->results_local + parity_stride + offset;
   int slot = 0;
   for (int r = 0; r < plan->world; ++r) {
     if (r == plan->rank) continue;
-    push.y_peer[slot] = plan->results_peer[r] + offset;
-    push.y_peer_odd[slot] = plan->results_peer[r] + parity_stride + offset;
-    push.peer_flag[slot] = static_cast<int*>(plan->control_peer[r]) + plan->rank;
-    ++slot;
+    push.cells[slot++] = static_cast<PushCell*>(plan->inbox_peer[r]) + offset;
   }
   return launch_qgemm_f32(weights, x_dev, plan->results_local + offset, m, plan->rows_per_rank,
                           workspace != nullptr ? workspace : &ctx->workspace,
@@ -189,26 +194,30 @@ qx_status qx_allgather_wait_dev(const qx_push_plan* plan, long long m, long long
                                 const float** results_dev, void* stream) {
   using namespace qx;
   QX_TRY(check_plan(plan));
-  if (m <= 0 || step <= 0) return QX_STATUS_INVALID_ARGUMENT;
+  if (m <= 0 || m > kGemvMaxBatch || step <= 0) return QX_STATUS_INVALID_ARGUMENT;
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
+  const long long slice = m * plan->rows_per_rank;
+  const long long parity_offset = (step & 1) * plan->world * slice;
+  const long long cells = static_cast<long long>(plan->world - 1) * slice;
+  long long blocks = (cells + 1023) / 1024;  // about four cells per thread
+  blocks = blocks < 1 ? 1 : (blocks > 64 ? 64 : blocks);
   cudaLaunchConfig_t config{};
-  config.gridDim = dim3(1);
-  config.blockDim = dim3(32);
+  config.gridDim = dim3(static_cast<unsigned>(blocks));
+  config.blockDim = dim3(256);
   config.stream = static_cast<cudaStream_t>(stream);
   cudaLaunchAttribute attribute{};
   attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attribute.val.programmaticStreamSerializationAllowed = 1;
   config.attrs = &attribute;
   config.numAttrs = 1;
-  QX_CUDA_TRY(cudaLaunchKernelEx(&config, allgather_wait_kernel, static_cast<int*>(plan->control_local),
-                                 plan->world, ctx->error_dev, wait_limit_ns()));
+  QX_CUDA_TRY(cudaLaunchKernelEx(&config, allgather_unpack_kernel,
+                                 static_cast<PushCell*>(plan->inbox_local) + parity_offset,
+                                 plan->results_local + parity_offset, slice, plan->world, plan->rank,
+                                 ctx->error_dev, wait_limit_ns()));
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
-  if (results_dev != nullptr) {
-    const long long parity_stride = static_cast<long long>(plan->world) * m * plan->rows_per_rank;
-    *results_dev = plan->results_local + (step & 1) * parity_stride;
-  }
+  if (results_dev != nullptr) *results_dev = plan->results_local + parity_offset;
   return QX_STATUS_OK;
 }
 

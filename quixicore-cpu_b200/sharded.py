@@ -82,10 +82,11 @@ class PushAllGather:
     """Row-sharded decode with the all-gather fused into the GEMV kernel (peer stores over
     NVLink instead of a collective call): one instance per rank, built collectively.
 
-    Each rank allocates a peer-mappable result buffer [2][world][max_m][rows] and a control
-    block through the C library, the 64-byte handles travel through the process group
-    (all_gather_object), and every rank maps the others'. step() enqueues the GEMV and the
-    wait for all slices and returns the device address of the step's [world][m][rows] results.
+    Each rank allocates a result buffer [2][world][m][rows] and a peer-mappable inbox of the
+    same shape (8-byte cells) through the C library, the 64-byte inbox handles travel through
+    the process group (all_gather_object), and every rank maps the others'. step() enqueues
+    the GEMV and the receive of all other slices and returns the device address of the
+    step's [world][m][rows] results.
     """
 
     def __init__(self, qx, rows_per_rank: int, max_m: int = 1,
@@ -95,24 +96,24 @@ class PushAllGather:
         self.rank = dist.get_rank(group)
         self.rows, self.max_m = rows_per_rank, max_m
         result_bytes = 2 * self.world * max_m * rows_per_rank * 4
-        self.results, results_handle = qx.peer_alloc(result_bytes)
-        self.control, control_handle = qx.peer_alloc(qx.push_control_bytes())
+        self.results, _ = qx.peer_alloc(result_bytes)
+        self.inbox, inbox_handle = qx.peer_alloc(qx.push_inbox_bytes(self.world, max_m, rows_per_rank))
         handles = [None] * self.world
-        dist.all_gather_object(handles, (results_handle, control_handle), group=group)
+        dist.all_gather_object(handles, inbox_handle, group=group)
         plan = qx.PushPlan()
         plan.world, plan.rank, plan.rows_per_rank = self.world, self.rank, rows_per_rank
-        plan.results_local, plan.control_local = self.results, self.control
-        for r, (rh, ch) in enumerate(handles):
+        plan.results_local, plan.inbox_local = self.results, self.inbox
+        for r, handle in enumerate(handles):
             if r != self.rank:
-                plan.results_peer[r] = qx.peer_open(rh)
-                plan.control_peer[r] = qx.peer_open(ch)
+                plan.inbox_peer[r] = qx.peer_open(handle)
         self.plan = plan
         self.steps = 0
-        dist.barrier(group=group)  # every rank has mapped every buffer before anyone pushes
+        dist.barrier(group=group)  # every rank has mapped every inbox before anyone pushes
 
     def step(self, weights, x, m: int = 1) -> int:
         if m != self.max_m:
-            raise ValueError("the result buffer is laid out for max_m rows per step")
-        self.qx.check(self.qx.qgemm_push_dev(weights, x, m, self.plan), "qx_qgemm_prepacked_push_dev")
+            raise ValueError("the buffers are laid out for max_m rows per step")
         self.steps += 1
+        self.qx.check(self.qx.qgemm_push_dev(weights, x, m, self.plan, self.steps),
+                      "qx_qgemm_prepacked_push_dev")
         return self.qx.allgather_wait_dev(self.plan, m, self.steps)

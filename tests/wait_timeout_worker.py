@@ -2,7 +2,7 @@
 the safe form: the kernel returns by itself) and checks how the host learns of it.
 
 A two-rank push plan is built on ONE GPU whose "peer" buffers are local allocations, and
-the wait for the next step's slices is enqueued although no GEMV ever pushed one. With
+the receive of a step's slices is enqueued although no GEMV ever pushed one. With
 QX_B200_WAIT_LIMIT_MS=5 in the environment the wait kernel gives up after 5 ms, leaves role
 code 31 in the device's error word and returns; nothing faults, traps or hangs."""
 
@@ -40,9 +40,8 @@ def main() -> int:
     plan = qx.PushPlan()
     plan.world, plan.rank, plan.rows_per_rank = 2, 0, rows
     plan.results_local, _ = qx.peer_alloc(2 * 2 * rows * 4)
-    plan.control_local, _ = qx.peer_alloc(qx.push_control_bytes())
-    plan.results_peer[1], _ = qx.peer_alloc(2 * 2 * rows * 4)   # stand-ins for rank 1's buffers
-    plan.control_peer[1], _ = qx.peer_alloc(qx.push_control_bytes())
+    plan.inbox_local, _ = qx.peer_alloc(qx.push_inbox_bytes(2, 1, rows))
+    plan.inbox_peer[1], _ = qx.peer_alloc(qx.push_inbox_bytes(2, 1, rows))  # stand-in for rank 1's inbox
 
     for round_ in range(2):
         t0 = torch.cuda.Event(enable_timing=True)
