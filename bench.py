@@ -763,7 +763,7 @@ def _time_calls(torch, fn, iters, warm=3):
 NCU_DRAM_BYTES_PER_LAUNCH = 33167104
 
 EXTRA_CASES = ("cfg2_w8a8_gemm", "cfg0_q8_0_gemv", "cfg3_q8_0_batched", "cfg4_q4_0_prefill",
-               "w8a32_gemm")
+               "w8a32_gemm", "fused_decode", "lowbit_w4a8")
 
 
 def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak, only=None):
@@ -780,6 +780,10 @@ def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak, only=None):
         out.update(_extra_cfg4(qx, wl, torch, bf16_peak))
     if only in (None, "w8a32_gemm"):
         out.update(_extra_w8a32(qx, wl, torch, hbm_peak))
+    if only in (None, "fused_decode"):
+        out.update(_extra_fused(qx, wl, torch, hbm_peak))
+    if only in (None, "lowbit_w4a8"):
+        out.update(_extra_lowbit(qx, wl, torch, hbm_peak))
     return out
 
 
@@ -882,6 +886,73 @@ def _extra_w8a32(qx, wl, torch, hbm_peak):
                                   "frac_of_measured_hbm": nbytes / sec / 1e9 / hbm_peak,
                                   "weights_in_l2": bool(n * k * copies < 120e6)}
     return {"w8a32_gemm": out}
+
+
+def _extra_fused(qx, wl, torch, hbm_peak):
+    """The fused decode projections at the headline shape: up + gate (2 x 14336 x 4096 q4_0,
+    66 MB) in ONE launch, with and without the activation, and the activation-quantising
+    GEMV (qgemv_w8a8) on the headline matrix. Weight copies rotate (> L2)."""
+    c = wl.CONFIGS["cfg1_q4_0_gemv"]
+    fmt, n, k = c["fmt"], c["n"], c["k"]
+    copies = 5
+    fused, single = [], []
+    for i in range(copies):
+        parts = [wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=10 * i + s) for s in (1, 2)]
+        h = qx.PackedWeights()
+        qx.check(h.prepare_fused(fmt, parts, [n, n], k), "prepare_fused")
+        fused.append(h)
+    for i in range(9):
+        h = qx.PackedWeights()
+        qx.check(h.prepare(fmt, wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=100 + i), n, k), "prep")
+        single.append(h)
+    xd = torch.from_numpy(wl.activations_f32(1, k)).cuda()
+    up, gate = torch.zeros((1, n), device="cuda"), torch.zeros((1, n), device="cuda")
+    out, scratch = torch.zeros(n, device="cuda"), torch.zeros(2 * n, device="cuda")
+    yd = torch.zeros(n, device="cuda")
+    nbytes = 2 * n * (k // 32) * 18 + 4 * k + 8 * n
+    sec = _time_calls(torch, lambda i: qx.check(fused[i % copies].qgemm_fused_dev(xd, [up, gate], 1), "fused"), 40)
+    sec_act = _time_calls(torch, lambda i: qx.check(
+        fused[i % copies].up_gate_activation_dev(xd[0], out, scratch, True), "act"), 40)
+    sec_w8a8 = _time_calls(torch, lambda i: qx.check(single[i % 9].qgemv_w8a8_dev(xd[0], yd), "w8a8"), 90)
+    one = wl.algorithmic_bytes_qgemv(fmt, 1, n, k)
+    result = {"fused_decode": {
+        "up_gate_q4_0_14336x4096": {"us": sec * 1e6, "gbs": nbytes / sec / 1e9,
+                                    "frac_of_measured_hbm": nbytes / sec / 1e9 / hbm_peak,
+                                    "launches": 1, "bytes": nbytes},
+        "up_gate_activation_q4_0_14336x4096": {"us": sec_act * 1e6, "gbs": nbytes / sec_act / 1e9,
+                                               "frac_of_measured_hbm": nbytes / sec_act / 1e9 / hbm_peak,
+                                               "launches": 2},
+        "qgemv_w8a8_q4_0_14336x4096": {"us": sec_w8a8 * 1e6, "gbs": one / sec_w8a8 / 1e9,
+                                       "frac_of_measured_hbm": one / sec_w8a8 / 1e9 / hbm_peak}}}
+    for h in fused + single:
+        h.reset()
+    return result
+
+
+def _extra_lowbit(qx, wl, torch, hbm_peak):
+    """W4A8 over compact int4 rows (lowbit_gemm_w8a8) at decode batches; algorithmic bytes:
+    packed weights + scales + activations + outputs."""
+    import ctypes as C
+    out = {}
+    for m, n, k in ((1, 4096, 4096), (4, 14336, 4096), (16, 4096, 4096)):
+        rng = np.random.default_rng(m + n)
+        copies = max(2, int(280e6 // (n * k // 2)))
+        ws = [torch.from_numpy(rng.integers(0, 256, n * k // 2, dtype=np.uint8)).cuda() for _ in range(copies)]
+        scale = torch.from_numpy(rng.uniform(0.001, 0.01, n).astype(np.float32)).cuda()
+        xd = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).cuda()
+        yd = torch.zeros((m, n), device="cuda")
+        scratch = torch.zeros(qx.lib.qx_lowbit_w8a8_scratch_bytes(m, k), dtype=torch.uint8, device="cuda")
+        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+        def call(i):
+            qx.check(qx.lib.qx_lowbit_gemm_w8a8_dev(C.c_void_p(ws[i % copies].data_ptr()), C.c_void_p(scale.data_ptr()),
+                                                    C.c_void_p(xd.data_ptr()), C.c_void_p(yd.data_ptr()),
+                                                    C.c_void_p(scratch.data_ptr()), m, n, k, stream), "w4a8")
+        sec = _time_calls(torch, call, 4 * copies)
+        nbytes = n * k // 2 + 4 * n + 4 * m * k + 4 * m * n
+        out[f"m{m}_n{n}_k{k}"] = {"us": sec * 1e6, "gbs": nbytes / sec / 1e9,
+                                  "frac_of_measured_hbm": nbytes / sec / 1e9 / hbm_peak, "launches": 2}
+    return {"lowbit_w4a8": out}
 
 
 def main():

@@ -109,6 +109,34 @@ QX_API qx_status qx_qgemv(int format, const void* packed, const float* x, float*
 /* qgemm, include/quixicore_cpu/qgemm.h:19-20 (kernels/quantization/qgemm_ref.cpp:141-164) */
 QX_API qx_status qx_qgemm(int format, const void* packed_weights, const float* x, float* y,
                    long long m, long long n, long long k);
+/* ---- qgemv_w8a8: the activation-quantising GEMV, include/quixicore_cpu/qgemv_w8a8.h:17-29
+ * (src/dispatch/qgemv_w8a8.cpp:109-153; kernels/quantization/qgemv_w8a8_ref.cpp:18-41,
+ * 120-177). The activations are quantised per 32-element block to int8 (scale amax / 127,
+ * codes nearbyint(x / scale) clamped to +-127), the block dots are exact integers and each is
+ * scaled by d_block * scale_block in f32. Non-finite activations: QX_STATUS_INVALID_ARGUMENT
+ * (host-pointer form; the device form propagates NaN). */
+QX_API qx_status qx_qgemv_w8a8(int format, const void* packed_weights, const float* x, float* y,
+                        long long n, long long k);
+QX_API qx_status qx_qgemv_w8a8_packed_size(int format, long long n, long long k, long long* bytes);
+QX_API qx_status qx_qgemv_w8a8_pack(int format, const float* weights, long long n, long long k,
+                             void* packed);
+QX_API const char* qx_qgemv_w8a8_variant(int format);
+
+/* ---- fused decode projections, include/quixicore_cpu/qgemv.h:143-154
+ * (kernels/quantization/qgemv_fused_ref.cpp:195-340): several weight matrices over the same
+ * activation vector. Here they are ONE launch over a fused handle (the matrices laid out back
+ * to back on the device), which is what makes a decode layer's small GEMVs worth their fixed
+ * launch cost. HOST pointers; `gelu_tanh` non-zero selects tanh-GELU, zero SiLU. */
+QX_API qx_status qx_qgemv_up_gate(int format, const void* packed_up, const void* packed_gate,
+                           const float* x, float* up, float* gate, long long n, long long k);
+QX_API qx_status qx_qgemv_up_gate_activation(int format, const void* packed_up,
+                                      const void* packed_gate, const float* x, float* out,
+                                      long long n, long long k, int gelu_tanh);
+QX_API qx_status qx_qgemv_qkv(int format, const void* packed_q, const void* packed_k,
+                       const void* packed_v, const float* x, float* q, float* k_out,
+                       float* v_out, long long query_dim, long long kv_dim,
+                       long long input_dim);
+
 /* qgemv_variant, include/quixicore_cpu/qgemv.h (src/dispatch/qgemv.cpp:392-405): name of
  * the kernel family that serves the format, "unsupported" otherwise. */
 QX_API const char* qx_qgemv_variant(int format);
@@ -144,6 +172,13 @@ typedef struct qx_weights_info {
 QX_API qx_status qx_weights_prepare(int format, const void* contract_packed, long long rows,
                              long long columns, long long row_begin, long long row_count,
                              qx_weights** out);
+/* Several matrices with the same column count in one handle (up + gate, q + k + v), each a
+ * HOST pointer to canonical bytes of rows[i] x columns; count <= 4. One GEMV launch streams
+ * all of them (qx_qgemm_fused_dev). Additive: the reference fuses per call instead
+ * (kernels/quantization/qgemv_fused_ref.cpp:195-340). */
+QX_API qx_status qx_weights_prepare_fused(int format, const void* const* contract_packed,
+                                   const long long* rows, int count, long long columns,
+                                   qx_weights** out);
 /* Same, from canonical bytes already resident on the device (no host copy). */
 QX_API qx_status qx_weights_prepare_dev(int format, const void* contract_packed_dev,
                                  long long rows, long long columns, long long row_begin,
@@ -176,6 +211,19 @@ QX_API qx_status qx_qgemm_prepacked(const qx_weights* weights, const float* x, f
 QX_API qx_status qx_qgemm_prepacked_dev(const qx_weights* weights, const float* x_dev,
                                  float* y_dev, long long m, long long ldy,
                                  qx_workspace* workspace, void* stream);
+/* All matrices of a fused handle against the same activations: y_dev[i] (device pointers,
+ * one per matrix, dense [m][rows_i]) = x . dequant(W_i)^T, m <= 32, one launch. */
+QX_API qx_status qx_qgemm_fused_dev(const qx_weights* weights, const float* x_dev,
+                             float* const* y_dev, long long m, qx_workspace* workspace,
+                             void* stream);
+/* qgemv_up_gate_activation on a fused {up, gate} handle: out_dev[n] = act(gate) * up;
+ * scratch_dev holds 2 n floats (the two projections). */
+QX_API qx_status qx_qgemv_up_gate_activation_dev(const qx_weights* up_gate, const float* x_dev,
+                                          float* out_dev, float* scratch_dev, int gelu_tanh,
+                                          qx_workspace* workspace, void* stream);
+/* qgemv_w8a8 on a prepared handle, device pointers (m = 1). */
+QX_API qx_status qx_qgemv_w8a8_prepacked_dev(const qx_weights* weights, const float* x_dev,
+                                      float* y_dev, qx_workspace* workspace, void* stream);
 /* qgemm_prepacked_storage with bf16 input, include/quixicore_cpu/qgemm.h:32-34 restricted
  * to FloatStorageType::kBF16 input and f32 output: the M >= 64 prefill GEMM. x_bf16_dev
  * [m, columns] bf16 bits, device pointers. */
@@ -312,6 +360,55 @@ QX_API qx_status qx_qgemm_w8a32_dev(const int8_t* weights_dev, const float* weig
                              const float* x_dev, float* y_dev, long long m, long long n,
                              long long k, long long ldy, int check_scales,
                              qx_workspace* workspace, void* stream);
+
+/* ---- compact 4-bit rows (LowBitFormat) and the int8 activation quantiser -----------------
+ * quixicore_cpu::LowBitFormat, include/quixicore_cpu/lowbit.h:15-20: rows of ADJACENT 4-bit
+ * codes (element 2i in the low nibble, value = nibble - 8) with separate f32 scales, one per
+ * row (kInt4Row) or per group of group_size inputs (kInt4Group). The 2- and 3-bit formats of
+ * the enum are sized correctly by qx_lowbit_packed_size but not served by the kernels
+ * (QX_STATUS_UNSUPPORTED_FORMAT). */
+enum { QX_LOWBIT_INT2_ROW = 0, QX_LOWBIT_INT3_GROUP64 = 1, QX_LOWBIT_INT4_ROW = 2, QX_LOWBIT_INT4_GROUP = 3 };
+/* lowbit_packed_size, include/quixicore_cpu/lowbit.h:24-26 */
+QX_API qx_status qx_lowbit_packed_size(int format, long long rows, long long dim,
+                                long long group_size, size_t* weight_bytes,
+                                size_t* scale_count);
+/* lowbit_pack / lowbit_unpack, include/quixicore_cpu/lowbit.h:28-33. HOST pointers. */
+QX_API qx_status qx_lowbit_pack(int format, const float* weights, uint8_t* packed, float* scales,
+                         long long rows, long long dim, long long group_size);
+QX_API qx_status qx_lowbit_unpack(int format, const uint8_t* packed, const float* scales,
+                           float* weights, long long rows, long long dim, long long group_size);
+/* lowbit_gemm, include/quixicore_cpu/lowbit.h:36-39: Y[m,n] = X[m,k] . dequant(W[n,k])^T in
+ * f32. HOST pointers; the _dev form takes device pointers and a stream. */
+QX_API qx_status qx_lowbit_gemm(int format, const uint8_t* packed_weights, const float* weight_scales,
+                         const float* x, float* y, long long m, long long n, long long k,
+                         long long group_size);
+QX_API qx_status qx_lowbit_gemm_dev(int format, const uint8_t* packed_dev,
+                             const float* weight_scales_dev, const float* x_dev, float* y_dev,
+                             long long m, long long n, long long k, long long group_size,
+                             void* stream);
+QX_API const char* qx_lowbit_gemm_variant(int format);
+/* lowbit_gemm_w8a8, include/quixicore_cpu/lowbit.h:44-47 (src/dispatch/lowbit_w8a8.cpp:68-101):
+ * W4A8 for kInt4Row. Every activation row is quantised to int8 (quantize_int8 with one group
+ * per row), the dot is an exact integer, Y = float(dot) * weight_scale[o] * activation_scale[r]
+ * -- bit-identical to the reference. HOST pointers; the _dev form takes device pointers plus
+ * qx_lowbit_w8a8_scratch_bytes(m, k) bytes of device scratch (it allocates nothing). */
+QX_API qx_status qx_lowbit_gemm_w8a8(const uint8_t* packed_weights, const float* weight_scales,
+                              const float* x, float* y, long long m, long long n, long long k);
+QX_API size_t qx_lowbit_w8a8_scratch_bytes(long long m, long long k);
+QX_API qx_status qx_lowbit_gemm_w8a8_dev(const uint8_t* packed_dev, const float* weight_scales_dev,
+                                  const float* x_dev, float* y_dev, void* scratch_dev,
+                                  long long m, long long n, long long k, void* stream);
+QX_API const char* qx_lowbit_gemm_w8a8_variant(void);
+/* quantize_int8, include/quixicore_cpu/quantization.h (kernels/quantization/
+ * quantization_ref.cpp:143-168): per (row, group) scale = amax / 127, codes =
+ * clamp(nearbyint(x / scale), -127, 127); group_size 0 = one group per row. Bit-identical to
+ * the reference. HOST pointers; the _dev form takes device pointers (code_sums_dev optional:
+ * the sum of every group's codes). */
+QX_API qx_status qx_quantize_int8(const float* x, int8_t* codes, float* scales, long long rows,
+                           long long dim, long long group_size);
+QX_API qx_status qx_quantize_int8_dev(const float* x_dev, int8_t* codes_dev, float* scales_dev,
+                               int* code_sums_dev, long long rows, long long dim,
+                               long long group_size, void* stream);
 
 /* ---- threading: set_num_threads / num_threads, include/quixicore_cpu/threading.h:11-12.
  * The fork-join pool is replaced by CUDA streams; these are kept so callers link. The

@@ -196,6 +196,81 @@ inline Status qgemm_w8a32(const std::int8_t* weights, const float* weight_scale,
 inline const char* int8_gemm_variant() { return qx_int8_gemm_variant(); }
 inline const char* qgemm_w8a32_variant() { return qx_qgemm_w8a32_variant(); }
 
+// include/quixicore_cpu/qgemv_w8a8.h:17-29 -> qx_qgemv_w8a8*
+inline Status qgemv_w8a8(QuantFormat format, const void* packed_weights, const float* x, float* y,
+                         long long n, long long k) {
+  return to_status(qx_qgemv_w8a8(static_cast<int>(format), packed_weights, x, y, n, k));
+}
+inline Status qgemv_w8a8_packed_size(QuantFormat format, long long n, long long k, long long* bytes) {
+  return to_status(qx_qgemv_w8a8_packed_size(static_cast<int>(format), n, k, bytes));
+}
+inline Status qgemv_w8a8_pack(QuantFormat format, const float* weights, long long n, long long k,
+                              void* packed) {
+  return to_status(qx_qgemv_w8a8_pack(static_cast<int>(format), weights, n, k, packed));
+}
+inline const char* qgemv_w8a8_variant(QuantFormat format) {
+  return qx_qgemv_w8a8_variant(static_cast<int>(format));
+}
+
+// include/quixicore_cpu/qgemv.h:143-154 -> qx_qgemv_up_gate[_activation] / qx_qgemv_qkv
+inline Status qgemv_up_gate(QuantFormat format, const void* packed_up, const void* packed_gate,
+                            const float* x, float* up, float* gate, long long n, long long k) {
+  return to_status(qx_qgemv_up_gate(static_cast<int>(format), packed_up, packed_gate, x, up, gate, n, k));
+}
+inline Status qgemv_up_gate_activation(QuantFormat format, const void* packed_up,
+                                       const void* packed_gate, const float* x, float* out,
+                                       long long n, long long k, bool gelu_tanh = true) {
+  return to_status(qx_qgemv_up_gate_activation(static_cast<int>(format), packed_up, packed_gate, x, out,
+                                               n, k, gelu_tanh ? 1 : 0));
+}
+inline Status qgemv_qkv(QuantFormat format, const void* packed_q, const void* packed_k,
+                        const void* packed_v, const float* x, float* q, float* k_out, float* v_out,
+                        long long query_dim, long long kv_dim, long long input_dim) {
+  return to_status(qx_qgemv_qkv(static_cast<int>(format), packed_q, packed_k, packed_v, x, q, k_out,
+                                v_out, query_dim, kv_dim, input_dim));
+}
+
+// include/quixicore_cpu/lowbit.h:15-47 (values identical) -> qx_lowbit_*
+enum class LowBitFormat {
+  kInt2Row,
+  kInt3Group64,
+  kInt4Row,
+  kInt4Group,
+};
+inline Status lowbit_packed_size(LowBitFormat format, long long rows, long long dim,
+                                 long long group_size, std::size_t* weight_bytes,
+                                 std::size_t* scale_count) {
+  return to_status(qx_lowbit_packed_size(static_cast<int>(format), rows, dim, group_size, weight_bytes,
+                                         scale_count));
+}
+inline Status lowbit_pack(LowBitFormat format, const float* weights, std::uint8_t* packed,
+                          float* scales, long long rows, long long dim, long long group_size = 0) {
+  return to_status(qx_lowbit_pack(static_cast<int>(format), weights, packed, scales, rows, dim, group_size));
+}
+inline Status lowbit_unpack(LowBitFormat format, const std::uint8_t* packed, const float* scales,
+                            float* weights, long long rows, long long dim, long long group_size = 0) {
+  return to_status(qx_lowbit_unpack(static_cast<int>(format), packed, scales, weights, rows, dim, group_size));
+}
+inline Status lowbit_gemm(LowBitFormat format, const std::uint8_t* packed_weights,
+                          const float* weight_scales, const float* x, float* y, long long m,
+                          long long n, long long k, long long group_size = 0) {
+  return to_status(qx_lowbit_gemm(static_cast<int>(format), packed_weights, weight_scales, x, y, m, n, k,
+                                  group_size));
+}
+inline Status lowbit_gemm_w8a8(const std::uint8_t* packed_weights, const float* weight_scales,
+                               const float* x, float* y, long long m, long long n, long long k) {
+  return to_status(qx_lowbit_gemm_w8a8(packed_weights, weight_scales, x, y, m, n, k));
+}
+inline const char* lowbit_gemm_w8a8_variant() { return qx_lowbit_gemm_w8a8_variant(); }
+inline const char* lowbit_gemm_variant(LowBitFormat format) {
+  return qx_lowbit_gemm_variant(static_cast<int>(format));
+}
+// include/quixicore_cpu/quantization.h:42-43 -> qx_quantize_int8
+inline Status quantize_int8(const float* x, std::int8_t* codes, float* scales, long long rows,
+                            long long dim, long long group_size) {
+  return to_status(qx_quantize_int8(x, codes, scales, rows, dim, group_size));
+}
+
 // include/quixicore_cpu/threading.h: kept for source compatibility (the GPU path has no
 // thread pool; the value is stored and returned)
 inline void set_num_threads(int n) { qx_set_num_threads(n); }

@@ -83,6 +83,15 @@ class Oracle:
         L.qxo_panel_bytes.restype = _ll
         L.qxo_panel_bytes.argtypes = [C.c_int, _ll, _ll, _ll]
         L.qxo_build_panel.argtypes = [C.c_int, _vp, _ll, _ll, _ll, _vp]
+        L.qxo_qgemv_w8a8.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll, _vp, _vp]
+        L.qxo_gate_activation.argtypes = [_vp, _vp, _vp, _ll, C.c_int]
+        L.qxo_gate_activation.restype = None
+        L.qxo_quantize_int8.argtypes = [_vp, _vp, _vp, _ll, _ll, _ll]
+        L.qxo_lowbit_pack.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll]
+        L.qxo_lowbit_unpack.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll]
+        L.qxo_lowbit_gemm.argtypes = [C.c_int, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll]
+        L.qxo_lowbit_gemm_f64.argtypes = [C.c_int, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll]
+        L.qxo_lowbit_gemm_w8a8.argtypes = [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _vp, _vp]
 
     # scalar conversions
     def fp16_to_fp32(self, h):
@@ -147,6 +156,58 @@ class Oracle:
         self.lib.qxo_qgemm_w8a32_f64(_ptr(w), _ptr(ws), _ptr(x), _ptr(y), m, n, k)
         return y
 
+    # ---- callers either side of the GEMV
+    def qgemv_w8a8(self, fmt, packed, x, n, k):
+        y = np.zeros(n, np.float32)
+        codes, scales = np.zeros(max(k, 1), np.int8), np.zeros(max(k // 32, 1), np.float32)
+        status = self.lib.qxo_qgemv_w8a8(fmt, _ptr(packed), _ptr(x), _ptr(y), n, k, _ptr(codes),
+                                         _ptr(scales))
+        return status, y
+
+    def gate_activation(self, up, gate, gelu_tanh=True):
+        out = np.zeros_like(up)
+        self.lib.qxo_gate_activation(_ptr(up), _ptr(gate), _ptr(out), up.size, 1 if gelu_tanh else 0)
+        return out
+
+    def quantize_int8(self, x, rows, dim, group_size=0):
+        groups = dim // (group_size or dim)
+        codes, scales = np.zeros((rows, dim), np.int8), np.zeros((rows, groups), np.float32)
+        status = self.lib.qxo_quantize_int8(_ptr(x), _ptr(codes), _ptr(scales), rows, dim, group_size)
+        return status, codes, scales
+
+    def lowbit_pack(self, fmt, weights, rows, dim, group_size=0):
+        groups = 1 if fmt == 2 else -(-dim // group_size)
+        packed = np.zeros(rows * ((dim + 1) // 2), np.uint8)
+        scales = np.zeros((rows, groups), np.float32)
+        status = self.lib.qxo_lowbit_pack(fmt, _ptr(weights), _ptr(packed), _ptr(scales), rows, dim,
+                                          group_size)
+        return status, packed, scales
+
+    def lowbit_unpack(self, fmt, packed, scales, rows, dim, group_size=0):
+        out = np.zeros((rows, dim), np.float32)
+        status = self.lib.qxo_lowbit_unpack(fmt, _ptr(packed), _ptr(scales), _ptr(out), rows, dim,
+                                            group_size)
+        return status, out
+
+    def lowbit_gemm(self, fmt, packed, scales, x, m, n, k, group_size=0):
+        y = np.zeros((m, n), np.float32)
+        status = self.lib.qxo_lowbit_gemm(fmt, _ptr(packed), _ptr(scales), _ptr(x), _ptr(y), m, n, k,
+                                          group_size)
+        return status, y
+
+    def lowbit_gemm_f64(self, fmt, packed, scales, x, m, n, k, group_size=0):
+        y = np.zeros((m, n), np.float64)
+        status = self.lib.qxo_lowbit_gemm_f64(fmt, _ptr(packed), _ptr(scales), _ptr(x), _ptr(y), m, n,
+                                              k, group_size)
+        return status, y
+
+    def lowbit_gemm_w8a8(self, packed, scales, x, m, n, k):
+        y = np.zeros((m, n), np.float32)
+        codes, act = np.zeros(m * k, np.int8), np.zeros(m, np.float32)
+        status = self.lib.qxo_lowbit_gemm_w8a8(_ptr(packed), _ptr(scales), _ptr(x), _ptr(y), m, n, k,
+                                               _ptr(codes), _ptr(act))
+        return status, y
+
     def build_panel(self, fmt, packed, rows, cols, tile):
         size = self.lib.qxo_panel_bytes(fmt, rows, cols, tile)
         panel = np.full(max(size, 1), 0xAB, np.uint8)
@@ -193,6 +254,84 @@ class Reference:
         L.qxref_float_to_bf16.argtypes = [C.c_float]
         L.qxref_bf16_to_float.restype = C.c_float
         L.qxref_bf16_to_float.argtypes = [C.c_uint16]
+        # a library built before these entry points were added lacks them: rebuild it
+        if hasattr(L, "qxref_qgemv_w8a8"):
+            L.qxref_qgemv_w8a8.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll]
+            L.qxref_qgemv_w8a8_variant.restype = C.c_char_p
+            L.qxref_qgemv_w8a8_variant.argtypes = [C.c_int]
+            L.qxref_qgemv_up_gate.argtypes = [C.c_int, _vp, _vp, _vp, _vp, _vp, _ll, _ll]
+            L.qxref_qgemv_up_gate_activation.argtypes = [C.c_int, _vp, _vp, _vp, _vp, _ll, _ll, C.c_int]
+            L.qxref_qgemv_qkv.argtypes = [C.c_int] + [_vp] * 7 + [_ll, _ll, _ll]
+            L.qxref_quantize_int8.argtypes = [_vp, _vp, _vp, _ll, _ll, _ll]
+            L.qxref_lowbit_packed_size.argtypes = [C.c_int, _ll, _ll, _ll, C.POINTER(C.c_size_t),
+                                                   C.POINTER(C.c_size_t)]
+            L.qxref_lowbit_pack.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll]
+            L.qxref_lowbit_unpack.argtypes = [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll]
+            L.qxref_lowbit_gemm.argtypes = [C.c_int, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll]
+            L.qxref_lowbit_gemm_w8a8.argtypes = [_vp, _vp, _vp, _vp, _ll, _ll, _ll]
+            L.qxref_lowbit_gemm_w8a8_variant.restype = C.c_char_p
+            L.qxref_lowbit_gemm_variant.restype = C.c_char_p
+            L.qxref_lowbit_gemm_variant.argtypes = [C.c_int]
+
+    # ---- callers either side of the GEMV
+    def qgemv_w8a8(self, fmt, packed, x, n, k):
+        y = np.zeros(n, np.float32)
+        return self.lib.qxref_qgemv_w8a8(fmt, _ptr(packed), _ptr(x), _ptr(y), n, k), y
+
+    def up_gate(self, fmt, up_w, gate_w, x, n, k):
+        up, gate = np.zeros(n, np.float32), np.zeros(n, np.float32)
+        status = self.lib.qxref_qgemv_up_gate(fmt, _ptr(up_w), _ptr(gate_w), _ptr(x), _ptr(up),
+                                              _ptr(gate), n, k)
+        return status, up, gate
+
+    def up_gate_activation(self, fmt, up_w, gate_w, x, n, k, gelu_tanh=True):
+        out = np.zeros(n, np.float32)
+        status = self.lib.qxref_qgemv_up_gate_activation(fmt, _ptr(up_w), _ptr(gate_w), _ptr(x),
+                                                         _ptr(out), n, k, 1 if gelu_tanh else 0)
+        return status, out
+
+    def qkv(self, fmt, wq, wk, wv, x, query_dim, kv_dim, input_dim):
+        q, k_out, v_out = (np.zeros(query_dim, np.float32), np.zeros(kv_dim, np.float32),
+                           np.zeros(kv_dim, np.float32))
+        status = self.lib.qxref_qgemv_qkv(fmt, _ptr(wq), _ptr(wk), _ptr(wv), _ptr(x), _ptr(q),
+                                          _ptr(k_out), _ptr(v_out), query_dim, kv_dim, input_dim)
+        return status, q, k_out, v_out
+
+    def quantize_int8(self, x, rows, dim, group_size=0):
+        groups = dim // (group_size or dim)
+        codes, scales = np.zeros((rows, dim), np.int8), np.zeros((rows, groups), np.float32)
+        status = self.lib.qxref_quantize_int8(_ptr(x), _ptr(codes), _ptr(scales), rows, dim, group_size)
+        return status, codes, scales
+
+    def lowbit_packed_size(self, fmt, rows, dim, group_size=0):
+        wb, sc = C.c_size_t(0), C.c_size_t(0)
+        status = self.lib.qxref_lowbit_packed_size(fmt, rows, dim, group_size, C.byref(wb), C.byref(sc))
+        return status, wb.value, sc.value
+
+    def lowbit_pack(self, fmt, weights, rows, dim, group_size=0):
+        groups = 1 if fmt == 2 else -(-dim // group_size)
+        packed = np.zeros(rows * ((dim + 1) // 2), np.uint8)
+        scales = np.zeros((rows, groups), np.float32)
+        status = self.lib.qxref_lowbit_pack(fmt, _ptr(weights), _ptr(packed), _ptr(scales), rows, dim,
+                                            group_size)
+        return status, packed, scales
+
+    def lowbit_unpack(self, fmt, packed, scales, rows, dim, group_size=0):
+        out = np.zeros((rows, dim), np.float32)
+        status = self.lib.qxref_lowbit_unpack(fmt, _ptr(packed), _ptr(scales), _ptr(out), rows, dim,
+                                              group_size)
+        return status, out
+
+    def lowbit_gemm(self, fmt, packed, scales, x, m, n, k, group_size=0):
+        y = np.zeros((m, n), np.float32)
+        status = self.lib.qxref_lowbit_gemm(fmt, _ptr(packed), _ptr(scales), _ptr(x), _ptr(y), m, n, k,
+                                            group_size)
+        return status, y
+
+    def lowbit_gemm_w8a8(self, packed, scales, x, m, n, k):
+        y = np.zeros((m, n), np.float32)
+        status = self.lib.qxref_lowbit_gemm_w8a8(_ptr(packed), _ptr(scales), _ptr(x), _ptr(y), m, n, k)
+        return status, y
 
     def set_num_threads(self, n):
         self.lib.qxref_set_num_threads(int(n))

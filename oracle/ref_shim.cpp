@@ -134,3 +134,87 @@ uint16_t qxref_float_to_bf16(float value) { return qc::float_to_bf16(value); }
 float qxref_bf16_to_float(uint16_t bits) { return qc::bf16_to_float(bits); }
 
 }  // extern "C"
+
+// ---- the callers either side of the GEMV: activation-quantising GEMV, fused decode
+// projections, compact int4 rows, int8 activation quantiser -----------------------------
+#include "quixicore_cpu/lowbit.h"
+#include "quixicore_cpu/qgemv_w8a8.h"
+#include "quixicore_cpu/quantization.h"
+
+extern "C" {
+
+int qxref_qgemv_w8a8(int format, const void* packed, const float* x, float* y,
+                     long long n, long long k) {
+  return static_cast<int>(qc::qgemv_w8a8(static_cast<qc::QuantFormat>(format),
+                                         packed, x, y, n, k));
+}
+const char* qxref_qgemv_w8a8_variant(int format) {
+  return qc::qgemv_w8a8_variant(static_cast<qc::QuantFormat>(format));
+}
+int qxref_qgemv_up_gate(int format, const void* up_w, const void* gate_w,
+                        const float* x, float* up, float* gate, long long n,
+                        long long k) {
+  return static_cast<int>(qc::qgemv_up_gate(static_cast<qc::QuantFormat>(format),
+                                            up_w, gate_w, x, up, gate, n, k));
+}
+int qxref_qgemv_up_gate_activation(int format, const void* up_w,
+                                   const void* gate_w, const float* x,
+                                   float* out, long long n, long long k,
+                                   int gelu_tanh) {
+  return static_cast<int>(qc::qgemv_up_gate_activation(
+      static_cast<qc::QuantFormat>(format), up_w, gate_w, x, out, n, k,
+      gelu_tanh != 0));
+}
+int qxref_qgemv_qkv(int format, const void* wq, const void* wk, const void* wv,
+                    const float* x, float* q, float* k_out, float* v_out,
+                    long long query_dim, long long kv_dim, long long input_dim) {
+  return static_cast<int>(qc::qgemv_qkv(static_cast<qc::QuantFormat>(format), wq,
+                                        wk, wv, x, q, k_out, v_out, query_dim,
+                                        kv_dim, input_dim));
+}
+int qxref_quantize_int8(const float* x, int8_t* codes, float* scales,
+                        long long rows, long long dim, long long group_size) {
+  return static_cast<int>(
+      qc::quantize_int8(x, codes, scales, rows, dim, group_size));
+}
+int qxref_lowbit_packed_size(int format, long long rows, long long dim,
+                             long long group_size, size_t* weight_bytes,
+                             size_t* scale_count) {
+  return static_cast<int>(qc::lowbit_packed_size(
+      static_cast<qc::LowBitFormat>(format), rows, dim, group_size,
+      weight_bytes, scale_count));
+}
+int qxref_lowbit_pack(int format, const float* weights, uint8_t* packed,
+                      float* scales, long long rows, long long dim,
+                      long long group_size) {
+  return static_cast<int>(qc::lowbit_pack(static_cast<qc::LowBitFormat>(format),
+                                          weights, packed, scales, rows, dim,
+                                          group_size));
+}
+int qxref_lowbit_unpack(int format, const uint8_t* packed, const float* scales,
+                        float* weights, long long rows, long long dim,
+                        long long group_size) {
+  return static_cast<int>(qc::lowbit_unpack(
+      static_cast<qc::LowBitFormat>(format), packed, scales, weights, rows, dim,
+      group_size));
+}
+int qxref_lowbit_gemm(int format, const uint8_t* packed, const float* scales,
+                      const float* x, float* y, long long m, long long n,
+                      long long k, long long group_size) {
+  return static_cast<int>(qc::lowbit_gemm(static_cast<qc::LowBitFormat>(format),
+                                          packed, scales, x, y, m, n, k,
+                                          group_size));
+}
+int qxref_lowbit_gemm_w8a8(const uint8_t* packed, const float* scales,
+                           const float* x, float* y, long long m, long long n,
+                           long long k) {
+  return static_cast<int>(qc::lowbit_gemm_w8a8(packed, scales, x, y, m, n, k));
+}
+const char* qxref_lowbit_gemm_w8a8_variant() {
+  return qc::lowbit_gemm_w8a8_variant();
+}
+const char* qxref_lowbit_gemm_variant(int format) {
+  return qc::lowbit_gemm_variant(static_cast<qc::LowBitFormat>(format));
+}
+
+}  // extern "C"

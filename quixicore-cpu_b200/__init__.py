@@ -87,6 +87,25 @@ def _load():
         "qx_int8_gemm_dev": [_vp] * 8 + [_ll, _ll, _ll, _ll, C.c_int, C.c_int, _vp],
         "qx_qgemm_w8a32": [_vp] * 4 + [_ll, _ll, _ll],
         "qx_qgemm_w8a32_dev": [_vp] * 4 + [_ll, _ll, _ll, _ll, C.c_int, _vp, _vp],
+        "qx_qgemv_w8a8": [C.c_int, _vp, _vp, _vp, _ll, _ll],
+        "qx_qgemv_w8a8_packed_size": [C.c_int, _ll, _ll, C.POINTER(_ll)],
+        "qx_qgemv_w8a8_pack": [C.c_int, _vp, _ll, _ll, _vp],
+        "qx_qgemv_w8a8_prepacked_dev": [_vp, _vp, _vp, _vp, _vp],
+        "qx_qgemv_up_gate": [C.c_int, _vp, _vp, _vp, _vp, _vp, _ll, _ll],
+        "qx_qgemv_up_gate_activation": [C.c_int, _vp, _vp, _vp, _vp, _ll, _ll, C.c_int],
+        "qx_qgemv_qkv": [C.c_int] + [_vp] * 7 + [_ll, _ll, _ll],
+        "qx_weights_prepare_fused": [C.c_int, C.POINTER(_vp), C.POINTER(_ll), C.c_int, _ll, C.POINTER(_vp)],
+        "qx_qgemm_fused_dev": [_vp, _vp, C.POINTER(_vp), _ll, _vp, _vp],
+        "qx_qgemv_up_gate_activation_dev": [_vp, _vp, _vp, _vp, C.c_int, _vp, _vp],
+        "qx_lowbit_packed_size": [C.c_int, _ll, _ll, _ll, C.POINTER(_sz), C.POINTER(_sz)],
+        "qx_lowbit_pack": [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll],
+        "qx_lowbit_unpack": [C.c_int, _vp, _vp, _vp, _ll, _ll, _ll],
+        "qx_lowbit_gemm": [C.c_int, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll],
+        "qx_lowbit_gemm_dev": [C.c_int, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll, _vp],
+        "qx_lowbit_gemm_w8a8": [_vp, _vp, _vp, _vp, _ll, _ll, _ll],
+        "qx_lowbit_gemm_w8a8_dev": [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _vp],
+        "qx_quantize_int8": [_vp, _vp, _vp, _ll, _ll, _ll],
+        "qx_quantize_int8_dev": [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _vp],
         "qx_peer_alloc": [_sz, C.POINTER(_vp), _vp],
         "qx_peer_open": [_vp, C.POINTER(_vp)],
         "qx_peer_close": [_vp],
@@ -99,9 +118,14 @@ def _load():
         fn.argtypes = argtypes
         fn.restype = C.c_int
     for name in ("qx_last_error_string", "qx_qgemv_variant", "qx_int8_gemm_variant",
-                 "qx_qgemm_w8a32_variant"):
+                 "qx_qgemm_w8a32_variant", "qx_qgemv_w8a8_variant", "qx_lowbit_gemm_variant",
+                 "qx_lowbit_gemm_w8a8_variant"):
         getattr(lib, name).restype = C.c_char_p
     lib.qx_qgemv_variant.argtypes = [C.c_int]
+    lib.qx_qgemv_w8a8_variant.argtypes = [C.c_int]
+    lib.qx_lowbit_gemm_variant.argtypes = [C.c_int]
+    lib.qx_lowbit_w8a8_scratch_bytes.argtypes = [_ll, _ll]
+    lib.qx_lowbit_w8a8_scratch_bytes.restype = _sz
     lib.qx_weights_destroy.argtypes = [_vp]
     lib.qx_weights_destroy.restype = None
     lib.qx_workspace_destroy.argtypes = [_vp]
@@ -206,6 +230,71 @@ def qgemm_w8a32(w, ws, x, m, n, k):
     return lib.qx_qgemm_w8a32(_np(w), _np(ws), _np(x), _np(y), m, n, k), y
 
 
+# ---- callers either side of the GEMV (host buffers) ----
+
+def qgemv_w8a8(fmt, packed, x, n, k):
+    y = np.zeros(n, np.float32)
+    return lib.qx_qgemv_w8a8(fmt, _np(packed), _np(x), _np(y), n, k), y
+
+
+def qgemv_up_gate(fmt, packed_up, packed_gate, x, n, k):
+    up, gate = np.zeros(n, np.float32), np.zeros(n, np.float32)
+    status = lib.qx_qgemv_up_gate(fmt, _np(packed_up), _np(packed_gate), _np(x), _np(up), _np(gate), n, k)
+    return status, up, gate
+
+
+def qgemv_up_gate_activation(fmt, packed_up, packed_gate, x, n, k, gelu_tanh=True):
+    out = np.zeros(n, np.float32)
+    status = lib.qx_qgemv_up_gate_activation(fmt, _np(packed_up), _np(packed_gate), _np(x), _np(out),
+                                             n, k, 1 if gelu_tanh else 0)
+    return status, out
+
+
+def qgemv_qkv(fmt, wq, wk, wv, x, query_dim, kv_dim, input_dim):
+    q, k_out, v_out = (np.zeros(query_dim, np.float32), np.zeros(kv_dim, np.float32),
+                       np.zeros(kv_dim, np.float32))
+    status = lib.qx_qgemv_qkv(fmt, _np(wq), _np(wk), _np(wv), _np(x), _np(q), _np(k_out), _np(v_out),
+                              query_dim, kv_dim, input_dim)
+    return status, q, k_out, v_out
+
+
+LOWBIT_INT2_ROW, LOWBIT_INT3_GROUP64, LOWBIT_INT4_ROW, LOWBIT_INT4_GROUP = range(4)
+
+
+def lowbit_packed_size(fmt, rows, dim, group_size=0):
+    wb, sc = _sz(0), _sz(0)
+    status = lib.qx_lowbit_packed_size(fmt, rows, dim, group_size, C.byref(wb), C.byref(sc))
+    return status, wb.value, sc.value
+
+
+def lowbit_pack(fmt, weights, rows, dim, group_size=0):
+    status, wb, sc = lowbit_packed_size(fmt, rows, dim, group_size)
+    packed, scales = np.zeros(max(wb, 1), np.uint8), np.zeros(max(sc, 1), np.float32)
+    return lib.qx_lowbit_pack(fmt, _np(weights), _np(packed), _np(scales), rows, dim, group_size), \
+        packed[:wb], scales[:sc].reshape(rows, -1) if status == OK else scales
+
+
+def lowbit_unpack(fmt, packed, scales, rows, dim, group_size=0):
+    out = np.zeros((rows, dim), np.float32)
+    return lib.qx_lowbit_unpack(fmt, _np(packed), _np(scales), _np(out), rows, dim, group_size), out
+
+
+def lowbit_gemm(fmt, packed, scales, x, m, n, k, group_size=0):
+    y = np.zeros((m, n), np.float32)
+    return lib.qx_lowbit_gemm(fmt, _np(packed), _np(scales), _np(x), _np(y), m, n, k, group_size), y
+
+
+def lowbit_gemm_w8a8(packed, scales, x, m, n, k):
+    y = np.zeros((m, n), np.float32)
+    return lib.qx_lowbit_gemm_w8a8(_np(packed), _np(scales), _np(x), _np(y), m, n, k), y
+
+
+def quantize_int8(x, rows, dim, group_size=0):
+    groups = dim // (group_size or dim) if dim > 0 and (group_size or dim) > 0 else 1
+    codes, scales = np.zeros((rows, dim), np.int8), np.zeros((rows, max(groups, 1)), np.float32)
+    return lib.qx_quantize_int8(_np(x), _np(codes), _np(scales), rows, dim, group_size), codes, scales
+
+
 def variants() -> dict:
     return {
         "qgemv_q8_0": lib.qx_qgemv_variant(Q8_0).decode(),
@@ -266,6 +355,27 @@ class PackedWeights:
         ldy = y.shape[-1] if ldy is None else ldy
         return lib.qx_qgemm_prepacked_dev(self.handle, _dev(x), _vp(y.data_ptr()), m, ldy, None,
                                           _stream())
+
+    def prepare_fused(self, fmt, parts, rows, columns) -> int:
+        """Several matrices with the same column count in one handle (numpy host bytes)."""
+        self.reset()
+        pointers = (_vp * len(parts))(*[p.ctypes.data for p in parts])
+        counts = (_ll * len(parts))(*rows)
+        self._fused_keepalive = parts
+        return lib.qx_weights_prepare_fused(fmt, pointers, counts, len(parts), columns,
+                                            C.byref(self.handle))
+
+    def qgemm_fused_dev(self, x, outputs, m) -> int:
+        pointers = (_vp * len(outputs))(*[o.data_ptr() for o in outputs])
+        return lib.qx_qgemm_fused_dev(self.handle, _dev(x), pointers, m, None, _stream())
+
+    def up_gate_activation_dev(self, x, out, scratch, gelu_tanh=True) -> int:
+        return lib.qx_qgemv_up_gate_activation_dev(self.handle, _dev(x), _vp(out.data_ptr()),
+                                                   _vp(scratch.data_ptr()), 1 if gelu_tanh else 0,
+                                                   None, _stream())
+
+    def qgemv_w8a8_dev(self, x, y) -> int:
+        return lib.qx_qgemv_w8a8_prepacked_dev(self.handle, _dev(x), _vp(y.data_ptr()), None, _stream())
 
     def qgemv_noalloc_dev(self, x, y) -> int:
         """Decode GEMV through the entry point that never allocates device memory."""

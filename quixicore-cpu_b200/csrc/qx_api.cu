@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <limits>
 
 #include "qx_gemv_tc.cuh"
 #include "qx_int8_gemm.cuh"
@@ -17,6 +18,8 @@ qx_status launch_pack(int format, const float* w_dev, long long total_blocks, vo
                       int* bad_dev, cudaStream_t stream);
 qx_status launch_unpack(int format, const void* packed_dev, long long total_blocks, float* w_dev,
                         cudaStream_t stream);
+qx_status launch_gate_activation(const float* up, const float* gate, float* out, long long n,
+                                 bool gelu_tanh, cudaStream_t stream);
 qx_status launch_q4_gemm_bf16(const qx_weights* w, const uint16_t* x_bf16_dev, float* y_dev,
                               long long m, long long ldy, qx_workspace* ws, cudaStream_t stream);
 
@@ -185,6 +188,208 @@ qx_status qx_check_device_errors(void) {
   QX_CUDA_TRY(cudaGetDevice(&device));
   DeviceContext* ctx = existing_context(device);
   return ctx == nullptr ? QX_STATUS_OK : take_device_error(ctx);
+}
+
+// ---- qgemv_w8a8: block-quantised int8 activations (include/quixicore_cpu/qgemv_w8a8.h) ----
+
+// src/dispatch/qgemv_w8a8.cpp:109-125
+qx_status qx_qgemv_w8a8_packed_size(int format, long long n, long long k, long long* bytes) {
+  size_t packed = 0;
+  QX_TRY(qx_qgemv_packed_size(format, n, k, &packed));
+  if (bytes == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  if (packed > static_cast<size_t>(std::numeric_limits<long long>::max())) return QX_STATUS_INVALID_SHAPE;
+  *bytes = static_cast<long long>(packed);
+  return QX_STATUS_OK;
+}
+
+// src/dispatch/qgemv_w8a8.cpp:127-130
+qx_status qx_qgemv_w8a8_pack(int format, const float* weights, long long n, long long k,
+                             void* packed) {
+  return qx_qgemv_pack(format, weights, n, k, packed);
+}
+
+const char* qx_qgemv_w8a8_variant(int format) {
+  if (format == QX_FORMAT_Q8_0 || format == QX_FORMAT_Q4_0) return "sm100a_tcgen05_i8_blocks";
+  return "unsupported";
+}
+
+qx_status qx_qgemv_w8a8_prepacked_dev(const qx_weights* weights, const float* x_dev, float* y_dev,
+                                      qx_workspace* workspace, void* stream) {
+  if (weights == nullptr || x_dev == nullptr || y_dev == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  if (weights->segments != 1) return QX_STATUS_INVALID_ARGUMENT;
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  GemvOptions options;
+  options.int8_activations = true;
+  return launch_qgemm_f32(weights, x_dev, y_dev, 1, weights->rows,
+                          workspace != nullptr ? workspace : &ctx->workspace,
+                          static_cast<cudaStream_t>(stream), nullptr, &options);
+}
+
+// src/dispatch/qgemv_w8a8.cpp:131-153: format/shape -> null pointers -> finite activations
+qx_status qx_qgemv_w8a8(int format, const void* packed_weights, const float* x, float* y,
+                        long long n, long long k) {
+  QX_TRY(validate_nk(format, n, k));
+  size_t bytes = 0;
+  QX_TRY(packed_bytes(format, n, k, &bytes));
+  if (packed_weights == nullptr || x == nullptr || y == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  if (!all_finite_host(x, k)) return QX_STATUS_INVALID_ARGUMENT;
+  qx_weights* w = nullptr;
+  QX_TRY(qx_weights_prepare(format, packed_weights, n, k, 0, n, &w));
+  DeviceContext* ctx = nullptr;
+  qx_status status = current_context(&ctx);
+  if (status == QX_STATUS_OK) {
+    std::lock_guard<std::mutex> lock(ctx->mutex);
+    Staging st{ctx};
+    const size_t off_x = st.add(k * sizeof(float)), off_y = st.add(n * sizeof(float));
+    status = ctx->ensure_staging(st.offset);
+    if (status == QX_STATUS_OK) status = h2d(st.at(off_x), x, k * sizeof(float), ctx->stream);
+    if (status == QX_STATUS_OK) {
+      status = qx_qgemv_w8a8_prepacked_dev(w, reinterpret_cast<const float*>(st.at(off_x)),
+                                           reinterpret_cast<float*>(st.at(off_y)), nullptr, ctx->stream);
+    }
+    if (status == QX_STATUS_OK) status = d2h(y, st.at(off_y), n * sizeof(float), ctx->stream);
+    if (status == QX_STATUS_OK) status = sync_and_check(ctx, ctx->stream);
+  }
+  qx_weights_destroy(w);
+  return status;
+}
+
+// ---- fused decode projections (include/quixicore_cpu/qgemv.h:143-154) ----------------------
+
+qx_status qx_qgemm_fused_dev(const qx_weights* weights, const float* x_dev, float* const* y_dev,
+                             long long m, qx_workspace* workspace, void* stream) {
+  if (weights == nullptr || x_dev == nullptr || y_dev == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  if (m <= 0 || m > kGemvMaxBatch) return QX_STATUS_INVALID_SHAPE;
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  GemvOptions options;
+  for (int s = 0; s < weights->segments; ++s) {
+    if (y_dev[s] == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+    options.segment_y[s] = y_dev[s];
+  }
+  return launch_qgemm_f32(weights, x_dev, y_dev[0], m, weights->seg_rows[0],
+                          workspace != nullptr ? workspace : &ctx->workspace,
+                          static_cast<cudaStream_t>(stream), nullptr, &options);
+}
+
+qx_status qx_qgemv_up_gate_activation_dev(const qx_weights* up_gate, const float* x_dev,
+                                          float* out_dev, float* scratch_dev, int gelu_tanh,
+                                          qx_workspace* workspace, void* stream) {
+  if (up_gate == nullptr || x_dev == nullptr || out_dev == nullptr || scratch_dev == nullptr) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  if (up_gate->segments != 2 || up_gate->seg_rows[0] != up_gate->seg_rows[1]) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  const long long n = up_gate->seg_rows[0];
+  float* outputs[2] = {scratch_dev, scratch_dev + n};
+  QX_TRY(qx_qgemm_fused_dev(up_gate, x_dev, outputs, 1, workspace, stream));
+  return launch_gate_activation(outputs[0], outputs[1], out_dev, n, gelu_tanh != 0,
+                                static_cast<cudaStream_t>(stream));
+}
+
+namespace {
+// Shared host-pointer driver of the fused entry points: one fused handle from the parts,
+// x in, one GEMV launch, (optional activation), the outputs back.
+qx_status fused_host(int format, const void* const* parts, const long long* rows, int count,
+                     long long k, const float* x, float* const* outputs, float* activation_out,
+                     bool gelu_tanh) {
+  qx_weights* w = nullptr;
+  QX_TRY(qx_weights_prepare_fused(format, parts, rows, count, k, &w));
+  DeviceContext* ctx = nullptr;
+  qx_status status = current_context(&ctx);
+  if (status == QX_STATUS_OK) {
+    std::lock_guard<std::mutex> lock(ctx->mutex);
+    Staging st{ctx};
+    const size_t off_x = st.add(k * sizeof(float));
+    size_t off_y[qx_weights::kMaxSegments] = {};
+    for (int s = 0; s < count; ++s) off_y[s] = st.add(rows[s] * sizeof(float));
+    const size_t off_out = st.add(rows[0] * sizeof(float));
+    status = ctx->ensure_staging(st.offset);
+    if (status == QX_STATUS_OK) status = h2d(st.at(off_x), x, k * sizeof(float), ctx->stream);
+    float* y_dev[qx_weights::kMaxSegments] = {};
+    for (int s = 0; s < count; ++s) y_dev[s] = reinterpret_cast<float*>(st.at(off_y[s]));
+    if (status == QX_STATUS_OK) {
+      status = qx_qgemm_fused_dev(w, reinterpret_cast<const float*>(st.at(off_x)), y_dev, 1, nullptr,
+                                  ctx->stream);
+    }
+    if (status == QX_STATUS_OK && activation_out != nullptr) {
+      status = launch_gate_activation(y_dev[0], y_dev[1], reinterpret_cast<float*>(st.at(off_out)),
+                                      rows[0], gelu_tanh, ctx->stream);
+      if (status == QX_STATUS_OK) {
+        status = d2h(activation_out, st.at(off_out), rows[0] * sizeof(float), ctx->stream);
+      }
+    } else if (status == QX_STATUS_OK) {
+      for (int s = 0; s < count && status == QX_STATUS_OK; ++s) {
+        status = d2h(outputs[s], y_dev[s], rows[s] * sizeof(float), ctx->stream);
+      }
+    }
+    if (status == QX_STATUS_OK) status = sync_and_check(ctx, ctx->stream);
+  }
+  qx_weights_destroy(w);
+  return status;
+}
+
+// kernels/quantization/qgemv_fused_ref.cpp:170-182, 206-209: a format this path does not
+// serve is kUnsupportedFormat, a shape that does not fit the format kInvalidShape
+qx_status fused_layout_status(int format, long long n, long long k) {
+  size_t block_bytes = 0;
+  if (!format_info(format, &block_bytes)) return QX_STATUS_UNSUPPORTED_FORMAT;
+  size_t bytes = 0;
+  if (validate_nk(format, n, k) != QX_STATUS_OK || packed_bytes(format, n, k, &bytes) != QX_STATUS_OK) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  return QX_STATUS_OK;
+}
+}  // namespace
+
+// kernels/quantization/qgemv_fused_ref.cpp:195-237
+qx_status qx_qgemv_up_gate(int format, const void* packed_up, const void* packed_gate,
+                           const float* x, float* up, float* gate, long long n, long long k) {
+  if (!valid_product2(n, k)) return QX_STATUS_INVALID_SHAPE;
+  if (packed_up == nullptr || packed_gate == nullptr || x == nullptr || up == nullptr ||
+      gate == nullptr) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  QX_TRY(fused_layout_status(format, n, k));
+  const void* parts[2] = {packed_up, packed_gate};
+  const long long rows[2] = {n, n};
+  float* outputs[2] = {up, gate};
+  return fused_host(format, parts, rows, 2, k, x, outputs, nullptr, false);
+}
+
+// kernels/quantization/qgemv_fused_ref.cpp:239-286
+qx_status qx_qgemv_up_gate_activation(int format, const void* packed_up, const void* packed_gate,
+                                      const float* x, float* out, long long n, long long k,
+                                      int gelu_tanh) {
+  if (!valid_product2(n, k)) return QX_STATUS_INVALID_SHAPE;
+  if (packed_up == nullptr || packed_gate == nullptr || x == nullptr || out == nullptr) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  QX_TRY(fused_layout_status(format, n, k));
+  const void* parts[2] = {packed_up, packed_gate};
+  const long long rows[2] = {n, n};
+  float* outputs[2] = {nullptr, nullptr};
+  return fused_host(format, parts, rows, 2, k, x, outputs, out, gelu_tanh != 0);
+}
+
+// kernels/quantization/qgemv_fused_ref.cpp:288-340
+qx_status qx_qgemv_qkv(int format, const void* packed_q, const void* packed_k, const void* packed_v,
+                       const float* x, float* q, float* k_out, float* v_out, long long query_dim,
+                       long long kv_dim, long long input_dim) {
+  if (!valid_product3(query_dim, kv_dim, input_dim)) return QX_STATUS_INVALID_SHAPE;
+  if (kv_dim > (std::numeric_limits<long long>::max() - query_dim) / 2) return QX_STATUS_INVALID_SHAPE;
+  if (packed_q == nullptr || packed_k == nullptr || packed_v == nullptr || x == nullptr ||
+      q == nullptr || k_out == nullptr || v_out == nullptr) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  QX_TRY(fused_layout_status(format, query_dim, input_dim));
+  if (fused_layout_status(format, kv_dim, input_dim) != QX_STATUS_OK) return QX_STATUS_INVALID_SHAPE;
+  const void* parts[3] = {packed_q, packed_k, packed_v};
+  const long long rows[3] = {query_dim, kv_dim, kv_dim};
+  float* outputs[3] = {q, k_out, v_out};
+  return fused_host(format, parts, rows, 3, input_dim, x, outputs, nullptr, false);
 }
 
 const char* qx_qgemv_variant(int format) {

@@ -227,6 +227,27 @@ __global__ void __launch_bounds__(256) gemv_dp4a_kernel(
   if (lane == 0) y[m * ldy + row] = acc;
 }
 
+// out[i] = activate(gate[i]) * up[i], the formulas of
+// kernels/quantization/qgemv_fused_ref.cpp:184-192 (tanh-GELU or SiLU) in f32.
+__global__ void __launch_bounds__(256) gate_activation_kernel(const float* __restrict__ up,
+                                                              const float* __restrict__ gate,
+                                                              float* __restrict__ out, long long n,
+                                                              int gelu_tanh) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // up / gate come from the GEMV in front
+  const long long i = blockIdx.x * 256LL + threadIdx.x;
+  if (i >= n) return;
+  const float g = gate[i];
+  float a;
+  if (gelu_tanh != 0) {
+    const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    a = 0.5f * g * (1.0f + tanhf(inner));
+  } else {
+    a = g / (1.0f + expf(-g));
+  }
+  out[i] = a * up[i];
+}
+
 bool force_dp4a() {
   static const bool forced = []() {
     const char* v = std::getenv("QX_B200_GEMV_VARIANT");
@@ -268,13 +289,35 @@ qx_status launch_quantizer(const qx_weights* w, const float* x_dev, uint8_t* xim
 
 }  // namespace
 
+qx_status launch_gate_activation(const float* up, const float* gate, float* out, long long n,
+                                 bool gelu_tanh, cudaStream_t stream) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(static_cast<unsigned>((n + 255) / 256));
+  config.blockDim = dim3(256);
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  QX_CUDA_TRY(cudaLaunchKernelEx(&config, gate_activation_kernel, up, gate, out, n, gelu_tanh ? 1 : 0));
+  count_launch();
+  return QX_STATUS_OK;
+}
+
 const char* gemv_variant_name() { return force_dp4a() ? "sm100a_dp4a" : "sm100a_tcgen05_digits"; }
 
 // Workspace layout of one GEMV call: [row counters | activation slab images | per-unit
 // partial sums]; sizes depend only on (m, k, rows).
 qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev,
                            long long m, long long ldy, qx_workspace* ws,
-                           cudaStream_t stream, const GemvPush* push) {
+                           cudaStream_t stream, const GemvPush* push, const GemvOptions* options) {
+  if ((w->segments > 1 || (options != nullptr && options->int8_activations)) &&
+      (force_dp4a() || m > kGemvMaxBatch)) {
+    set_last_error_text("qgemm: fused handles and int8 activations take at most 32 activation rows "
+                        "(tensor-core kernel)");
+    return QX_STATUS_INVALID_SHAPE;
+  }
   if (push != nullptr && (m > kGemvMaxBatch || force_dp4a())) {
     set_last_error_text("qgemm: pushing launches take at most 32 activation rows (tensor-core kernel)");
     return QX_STATUS_INVALID_SHAPE;
@@ -298,7 +341,7 @@ qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev
     }
     float* y = y_dev + m0 * ldy;
     if (!force_dp4a()) {
-      QX_TRY(launch_gemv_tc(w, x, ximg, y, mc, ldy, base, scratch, stream, push));
+      QX_TRY(launch_gemv_tc(w, x, ximg, y, mc, ldy, base, scratch, stream, push, options));
     } else {
       const dim3 grid(static_cast<unsigned>((w->rows + 7) / 8), static_cast<unsigned>(mc));
       const int mp = padded_batch(mc), nb = static_cast<int>(w->blocks_per_row);

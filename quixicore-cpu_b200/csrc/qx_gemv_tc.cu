@@ -165,6 +165,14 @@ struct GemvTcParams {
   // Row-sharded runs (one process per GPU): every finished output is also stored into the
   // other ranks' inboxes over NVLink as an 8-byte {value, valid} cell (an all-gather fused
   // into the epilogue; the receiving side is allgather_unpack_kernel in qx_peer.cu).
+  // Fused handles (several matrices back to back): segment s starts at tile
+  // seg_tile_begin[s], has seg_rows[s] rows and writes dense [m][seg_rows[s]] outputs at
+  // seg_y[s]. One segment for ordinary handles: {0, rows, y with row stride ldy}.
+  int segments;
+  int seg_tile_begin[qx_weights::kMaxSegments];
+  long long seg_rows[qx_weights::kMaxSegments];
+  float* seg_y[qx_weights::kMaxSegments];
+  int int8_activations;               // in-kernel quantizer: the rule of qgemv_w8a8
   int peers;                          // other ranks (0: no push)
   PushCell* push_cells[kMaxPushPeers];  // the other ranks' inboxes, at this rank's slice
 };
@@ -245,7 +253,7 @@ template <int FMT, int MP>
 __device__ __forceinline__ void write_slab_image(uint8_t* digits, XConst* consts,
                                                  const int (&digit_offset)[MP][4],
                                                  const float4 (&lo)[MP], const float4 (&hi)[MP],
-                                                 bool block_valid, int lane) {
+                                                 bool block_valid, int lane, bool int8_activations) {
   using G = TcGeom<FMT, MP>;
   const int b = lane >> 2, q = lane & 3;
 #pragma unroll
@@ -260,9 +268,16 @@ __device__ __forceinline__ void write_slab_image(uint8_t* digits, XConst* consts
     const uint32_t eb_raw = amax_bits >> 23;
     const bool finite = eb_raw != 255u;
     const uint32_t eb = max(eb_raw, 30u);                       // envelope 2^(eb-126) > amax
-    const float scale_up = finite ? __uint_as_float((275u - eb) << 23) : 0.0f;  // 2^(22 - e)
+    float scale_up = finite ? __uint_as_float((275u - eb) << 23) : 0.0f;  // 2^(22 - e)
     // 2^(e - 22); q4_0: 2^(e - 26), its digit sums carry a factor 16
     float scale = __uint_as_float((eb - (FMT == QX_FORMAT_Q4_0 ? 25u : 21u)) << 23);
+    if (int8_activations) {
+      // qgemv_w8a8 (kernels/quantization/qgemv_w8a8_ref.cpp:18-41): scale = amax / 127,
+      // codes nearbyint(x * (1 / scale)) clamped to +-127, both divisions IEEE
+      const float block_scale = __fdiv_rn(__uint_as_float(amax_bits), 127.0f);
+      scale_up = (finite && block_scale != 0.0f) ? __fdiv_rn(1.0f, block_scale) : 0.0f;
+      scale = FMT == QX_FORMAT_Q4_0 ? block_scale * 0.0625f : block_scale;
+    }
     if (!finite) scale = __uint_as_float(0x7FC00000u);  // NaN/inf in -> NaN out
     if (!block_valid) scale = 0.0f;
     int t_lo[4], t_hi[4];
@@ -271,6 +286,10 @@ __device__ __forceinline__ void write_slab_image(uint8_t* digits, XConst* consts
       // |t| <= 2^22 (a non-finite block has scale_up = 0; 0 * inf = NaN converts to 0)
       t_lo[i] = __float2int_rn(v[i] * scale_up);
       t_hi[i] = __float2int_rn(v[4 + i] * scale_up);
+      if (int8_activations) {
+        t_lo[i] = max(-127, min(127, t_lo[i]));
+        t_hi[i] = max(-127, min(127, t_hi[i]));
+      }
     }
     uint32_t w_lo[4], w_hi[4];
     if (FMT == QX_FORMAT_Q8_0) {
@@ -559,7 +578,16 @@ gemv_tc_kernel(const GemvTcParams p) {
     int cnt_tile = 0, cnt_add = 0, cnt_old = 0;   // counted in, result not looked at
     // this thread completed the row's count in `tile`: add its unit sums in the fixed order
     auto finish_row = [&](int done_tile) {
-      const long long row = static_cast<long long>(done_tile) * kTileRows + row_in_tile;
+      int seg = 0;
+#pragma unroll
+      for (int q = 1; q < qx_weights::kMaxSegments; ++q) {
+        if (q < p.segments && done_tile >= p.seg_tile_begin[q]) seg = q;
+      }
+      const long long row =
+          static_cast<long long>(done_tile - p.seg_tile_begin[seg]) * kTileRows + row_in_tile;
+      const long long seg_rows = p.seg_rows[seg];
+      const long long ldy = p.segments > 1 ? seg_rows : p.ldy;
+      float* y_out = p.seg_y[seg];
       const float* slots = p.partial +
                            static_cast<long long>(done_tile) * p.units_per_tile * p.m * kTileRows +
                            row_in_tile;
@@ -579,10 +607,10 @@ gemv_tc_kernel(const GemvTcParams p) {
           if (u < p.units_per_tile) even += v[u];
           if (u + 1 < p.units_per_tile) odd += v[u + 1];
         }
-        if (row < p.rows) {
+        if (row < seg_rows) {
           const float value = even + odd;
-          const long long at = m * p.ldy + row;
-          p.y[at] = value;
+          const long long at = m * ldy + row;
+          y_out[at] = value;
           for (int r = 0; r < p.peers; ++r) {
             // value and tag in ONE 8-byte store: whoever sees the tag sees the value
             asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p.push_cells[r] + at),
@@ -904,7 +932,7 @@ gemv_tc_kernel(const GemvTcParams p) {
       {
         write_slab_image<FMT, MP>(
             digits, reinterpret_cast<XConst*>(const_ring + (i % G::kConstRing) * G::kConstBytes),
-            digit_offset, cur_lo, cur_hi, cur_valid, lane);
+            digit_offset, cur_lo, cur_hi, cur_valid, lane, p.int8_activations != 0);
       }
       fence_proxy_async_smem();
       __syncwarp();
@@ -1008,16 +1036,41 @@ bool gemv_tc_quantizes_in_kernel(int m) { return padded_batch(m) <= 2; }
 
 qx_status launch_gemv_tc(const qx_weights* w, const float* x, const uint8_t* ximg, float* y, int m,
                          long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                         cudaStream_t stream, const GemvPush* push) {
+                         cudaStream_t stream, const GemvPush* push, const GemvOptions* options) {
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
-  return launch_gemv_tc_at(w, x, ximg, y, m, ldy, ws_base, scratch, ctx->error_dev, stream, push);
+  return launch_gemv_tc_at(w, x, ximg, y, m, ldy, ws_base, scratch, ctx->error_dev, stream, push,
+                           options);
 }
 
 qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* ximg, float* y,
                             int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                            int* error_word, cudaStream_t stream, const GemvPush* push) {
+                            int* error_word, cudaStream_t stream, const GemvPush* push,
+                            const GemvOptions* options) {
   GemvTcParams p{};
+  p.segments = w->segments;
+  for (int s = 0; s < qx_weights::kMaxSegments; ++s) {
+    p.seg_tile_begin[s] = static_cast<int>(w->seg_tile_begin[s]);
+    p.seg_rows[s] = w->seg_rows[s];
+    p.seg_y[s] = (options != nullptr && options->segment_y[s] != nullptr) ? options->segment_y[s] : y;
+  }
+  if (w->segments > 1) {
+    for (int s = 0; s < w->segments; ++s) {
+      if (options == nullptr || options->segment_y[s] == nullptr) {
+        set_last_error_text("gemv: a fused handle needs one output pointer per segment");
+        return QX_STATUS_INVALID_ARGUMENT;
+      }
+    }
+    if (push != nullptr) {
+      set_last_error_text("gemv: fused handles cannot push to other ranks");
+      return QX_STATUS_INVALID_ARGUMENT;
+    }
+  }
+  p.int8_activations = (options != nullptr && options->int8_activations) ? 1 : 0;
+  if (p.int8_activations != 0 && m != 1) {
+    set_last_error_text("gemv: the int8 activation rule serves one activation row");
+    return QX_STATUS_INVALID_SHAPE;
+  }
   p.panel = w->panel;
   p.ximg = ximg;
   p.x = x;

@@ -45,13 +45,15 @@ bool gemv_tc_quantizes_in_kernel(int m);
 // quantizes itself)
 qx_status launch_gemv_tc(const qx_weights* w, const float* x, const uint8_t* ximg, float* y, int m,
                          long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                         cudaStream_t stream, const GemvPush* push = nullptr);
+                         cudaStream_t stream, const GemvPush* push = nullptr,
+                         const GemvOptions* options = nullptr);
 
 // Same, with the device word that receives a non-zero role code when a bounded wait gives
 // up passed in by the caller instead of taken from the per-device context.
 qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* ximg, float* y,
                             int m, long long ldy, uint8_t* ws_base, const GemvScratch& scratch,
-                            int* error_word, cudaStream_t stream, const GemvPush* push = nullptr);
+                            int* error_word, cudaStream_t stream, const GemvPush* push = nullptr,
+                            const GemvOptions* options = nullptr);
 
 const char* gemv_variant_name();
 

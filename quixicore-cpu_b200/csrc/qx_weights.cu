@@ -51,15 +51,22 @@ __global__ void __launch_bounds__(256) relayout_kernel(const unsigned short* __r
 }  // namespace
 
 qx_status launch_relayout(const qx_weights* w, const uint8_t* src, cudaStream_t stream) {
-  const long long total = w->tiles * w->slabs * kTileRows * kSlabBlocks;
+  return launch_relayout_segment(w, src, w->rows, 0, stream);
+}
+
+qx_status launch_relayout_segment(const qx_weights* w, const uint8_t* src, long long rows,
+                                  long long tile_begin, cudaStream_t stream) {
+  const long long tiles = (rows + kTileRows - 1) / kTileRows;
+  const long long total = tiles * w->slabs * kTileRows * kSlabBlocks;
   const unsigned grid = static_cast<unsigned>((total + 255) / 256);
   const auto* in = reinterpret_cast<const unsigned short*>(src);
+  uint8_t* panel = w->panel + static_cast<size_t>(tile_begin) * w->slabs * w->slab_bytes();
   if (w->format == QX_FORMAT_Q8_0) {
     relayout_kernel<QX_FORMAT_Q8_0><<<grid, 256, 0, stream>>>(
-        in, w->rows, w->blocks_per_row, w->slabs, total, w->panel);
+        in, rows, w->blocks_per_row, w->slabs, total, panel);
   } else {
     relayout_kernel<QX_FORMAT_Q4_0><<<grid, 256, 0, stream>>>(
-        in, w->rows, w->blocks_per_row, w->slabs, total, w->panel);
+        in, rows, w->blocks_per_row, w->slabs, total, panel);
   }
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
@@ -105,6 +112,7 @@ qx_status prepare_common(int format, const void* contract, bool contract_on_devi
   w->contract_bytes = shard_bytes;
   w->tiles = (row_count + kTileRows - 1) / kTileRows;
   w->slabs = (nb + kSlabBlocks - 1) / kSlabBlocks;
+  w->seg_rows[0] = row_count;
   const size_t panel_bytes = w->panel_bytes();
 
   auto fail = [&](qx_status status) {
@@ -171,6 +179,84 @@ qx_status qx_weights_prepare(int format, const void* contract_packed, long long 
   std::lock_guard<std::mutex> lock(ctx->mutex);
   return qx::prepare_common(format, contract_packed, false, rows, columns, row_begin, row_count,
                             ctx->stream, true, out);
+}
+
+qx_status qx_weights_prepare_fused(int format, const void* const* contract_packed,
+                                   const long long* rows, int count, long long columns,
+                                   qx_weights** out) {
+  using namespace qx;
+  const auto t0 = std::chrono::steady_clock::now();
+  if (out == nullptr || contract_packed == nullptr || rows == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  *out = nullptr;
+  if (count < 1 || count > qx_weights::kMaxSegments) return QX_STATUS_INVALID_ARGUMENT;
+  size_t block_bytes = 0;
+  if (!format_info(format, &block_bytes)) return QX_STATUS_UNSUPPORTED_FORMAT;
+  long long total_rows = 0;
+  for (int s = 0; s < count; ++s) {
+    if (contract_packed[s] == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+    QX_TRY(validate_nk(format, rows[s], columns));
+    size_t bytes = 0;
+    QX_TRY(packed_bytes(format, rows[s], columns, &bytes));
+    total_rows += rows[s];
+  }
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  const long long nb = columns / kBlockK;
+  auto* w = new (std::nothrow) qx_weights();
+  if (w == nullptr) return QX_STATUS_OUT_OF_MEMORY;
+  w->format = format;
+  w->device = ctx->device;
+  w->rows_total = total_rows;
+  w->rows = total_rows;
+  w->columns = columns;
+  w->blocks_per_row = nb;
+  w->block_bytes = block_bytes;
+  w->slabs = (nb + kSlabBlocks - 1) / kSlabBlocks;
+  w->segments = count;
+  size_t largest = 0;
+  for (int s = 0; s < count; ++s) {
+    w->seg_tile_begin[s] = w->tiles;
+    w->seg_rows[s] = rows[s];
+    w->tiles += (rows[s] + kTileRows - 1) / kTileRows;
+    const size_t bytes = static_cast<size_t>(rows[s]) * nb * block_bytes;
+    w->contract_bytes += bytes;
+    largest = bytes > largest ? bytes : largest;
+  }
+  const size_t panel_bytes = w->panel_bytes();
+  void* temp = nullptr;
+  auto fail = [&](const char* what, cudaError_t err) {
+    set_last_error(what, err);
+    if (temp != nullptr) (void)cudaFree(temp);
+    qx_weights_destroy(w);
+    return err == cudaErrorMemoryAllocation ? QX_STATUS_OUT_OF_MEMORY : QX_STATUS_DEVICE_ERROR;
+  };
+  cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&w->panel), align_up(panel_bytes, 256));
+  if (err != cudaSuccess) return fail("cudaMalloc(prepared planes)", err);
+  w->prepared_bytes = panel_bytes;
+  err = cudaMalloc(&temp, align_up(largest, 256));
+  if (err != cudaSuccess) return fail("cudaMalloc(canonical staging)", err);
+  for (int s = 0; s < count; ++s) {
+    const size_t bytes = static_cast<size_t>(rows[s]) * nb * block_bytes;
+    err = cudaMemcpyAsync(temp, contract_packed[s], bytes, cudaMemcpyHostToDevice, ctx->stream);
+    if (err != cudaSuccess) return fail("cudaMemcpyAsync(canonical bytes)", err);
+    const qx_status status = launch_relayout_segment(w, static_cast<const uint8_t*>(temp), rows[s],
+                                                     w->seg_tile_begin[s], ctx->stream);
+    if (status != QX_STATUS_OK) {
+      (void)cudaFree(temp);
+      qx_weights_destroy(w);
+      return status;
+    }
+    // the staging buffer is reused by the next segment
+    err = cudaStreamSynchronize(ctx->stream);
+    if (err != cudaSuccess) return fail("cudaStreamSynchronize(prepare)", err);
+  }
+  (void)cudaFree(temp);
+  w->preparation_ns = static_cast<uint64_t>(
+      std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now() - t0)
+          .count());
+  *out = w;
+  return QX_STATUS_OK;
 }
 
 qx_status qx_weights_prepare_dev(int format, const void* contract_packed_dev, long long rows,

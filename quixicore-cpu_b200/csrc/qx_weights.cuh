@@ -35,6 +35,14 @@ struct qx_weights {
   size_t prepared_bytes = 0;
   uint64_t preparation_ns = 0;
   uint8_t* panel = nullptr;  // device: [tile][slab]{codes, scales}
+  // A handle may hold several matrices with the same column count back to back ("fused"
+  // projections: up + gate, q + k + v), each starting on a tile boundary, so that one GEMV
+  // launch streams all of them. segment s covers tiles [seg_tile_begin[s], ...) and has
+  // seg_rows[s] rows; `rows` is their sum. Ordinary handles have one segment.
+  static constexpr int kMaxSegments = 4;
+  int segments = 1;
+  long long seg_tile_begin[kMaxSegments] = {0, 0, 0, 0};
+  long long seg_rows[kMaxSegments] = {0, 0, 0, 0};
   // Lazily built by the prefill GEMM (see qx_q4_gemm.cu); not part of prepared_bytes
   // until built.
   void* dense_cache = nullptr;
@@ -50,13 +58,28 @@ namespace qx {
 
 // Re-layout canonical blocks [rows][nb][block_bytes] -> panels. `src` points at the first
 // kept row's first block (device memory, 2-byte aligned).
+// Same for one segment of a fused handle: `rows` rows into the tiles from `tile_begin` on.
 qx_status launch_relayout(const qx_weights* w, const uint8_t* src, cudaStream_t stream);
+qx_status launch_relayout_segment(const qx_weights* w, const uint8_t* src, long long rows,
+                                  long long tile_begin, cudaStream_t stream);
 
 // y[m][ldy] (+ row offset already applied by the caller) = x[m][k] . dequant(W)^T
 // `push` (qx_gemv_tc.cuh): also store the results on the other ranks (m <= 32 only).
 struct GemvPush;
+// Extras of a GEMV launch: where a fused handle's segments write their outputs (dense
+// [m][seg_rows[s]] each; null: the y argument, one segment) and how the in-kernel quantizer
+// treats the activations.
+struct GemvOptions {
+  float* segment_y[qx_weights::kMaxSegments] = {nullptr, nullptr, nullptr, nullptr};
+  // false: 23-bit fixed point under a power-of-two block envelope (the f32 path).
+  // true: the activation quantisation of qgemv_w8a8 (per 32-block scale amax / 127, codes
+  // nearbyint(x / scale) clamped to +-127; kernels/quantization/qgemv_w8a8_ref.cpp:18-41);
+  // single activation row only.
+  bool int8_activations = false;
+};
 qx_status launch_qgemm_f32(const qx_weights* w, const float* x_dev, float* y_dev,
                            long long m, long long ldy, qx_workspace* ws,
-                           cudaStream_t stream, const GemvPush* push = nullptr);
+                           cudaStream_t stream, const GemvPush* push = nullptr,
+                           const GemvOptions* options = nullptr);
 
 }  // namespace qx

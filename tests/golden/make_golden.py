@@ -165,6 +165,53 @@ def generate(out_path: str) -> None:
         out[f"prepacked_{name}_70x6x96_y"] = y
         ref.prepacked_destroy(handle)
 
+    # ---- callers either side of the GEMV ------------------------------------------------
+    # qgemv_w8a8 (block-quantised int8 activations) and the fused decode projections
+    for fmt, name, lo, hi in ((Q8_0, "q8", 0.001, 0.02), (Q4_0, "q4", 0.002, 0.04)):
+        n, k = 40, 1024
+        packed = wl.packed_blocks(fmt, n, k, lo, hi, seed=31)
+        gate_w = wl.packed_blocks(fmt, n, k, lo, hi, seed=32)
+        x = wl.activations_f32(1, k, seed=31)[0].copy()
+        out[f"w8a8_{name}_variant"] = np.array(ref.lib.qxref_qgemv_w8a8_variant(fmt).decode())
+        _, y = ref.qgemv_w8a8(fmt, packed, x, n, k)
+        out[f"w8a8_{name}_{n}x{k}_y"] = y
+        _, up, gate = ref.up_gate(fmt, packed, gate_w, x, n, k)
+        out[f"upgate_{name}_{n}x{k}_up"], out[f"upgate_{name}_{n}x{k}_gate"] = up, gate
+        for gelu in (1, 0):
+            _, act = ref.up_gate_activation(fmt, packed, gate_w, x, n, k, bool(gelu))
+            out[f"upgate_{name}_{n}x{k}_act{gelu}"] = act
+        kv = 24
+        wk_ = wl.packed_blocks(fmt, kv, k, lo, hi, seed=33)
+        wv_ = wl.packed_blocks(fmt, kv, k, lo, hi, seed=34)
+        _, q, k_out, v_out = ref.qkv(fmt, packed, wk_, wv_, x, n, kv, k)
+        out[f"qkv_{name}_q"], out[f"qkv_{name}_k"], out[f"qkv_{name}_v"] = q, k_out, v_out
+
+    # quantize_int8 (kernels/quantization/quantization_ref.cpp:143-168)
+    xq = wl.activations_f32(5, 192, seed=41)
+    xq[1] = 0.0
+    xq[2, 7] = 1e-30
+    for group in (0, 32, 64):
+        _, codes, scales = ref.quantize_int8(xq, 5, 192, group)
+        out[f"quant_int8_g{group}_codes"], out[f"quant_int8_g{group}_scales"] = codes, scales
+
+    # compact int4 rows: authoring, f32 GEMM, W4A8 (tests/correctness/test_lowbit_w8a8.cpp)
+    out["lowbit_variant"] = np.array(ref.lib.qxref_lowbit_gemm_variant(2).decode())
+    out["lowbit_w8a8_variant"] = np.array(ref.lib.qxref_lowbit_gemm_w8a8_variant().decode())
+    for fmt, group, n, k, m in ((2, 0, 19, 200, 3), (3, 64, 17, 256, 2), (2, 0, 9, 33, 4)):
+        rng = np.random.Generator(np.random.Philox(key=[fmt * 100 + k, 7]))
+        w = (rng.integers(-1000, 1001, (n, k)).astype(np.float32) / np.float32(1000.0)) * np.float32(0.2)
+        x = rng.integers(-2000, 2001, (m, k)).astype(np.float32) / np.float32(500.0)
+        _, packed, scales = ref.lowbit_pack(fmt, w, n, k, group)
+        tag = f"lowbit_f{fmt}_{m}x{n}x{k}"
+        out[tag + "_packed"], out[tag + "_scales"] = packed, scales
+        _, dq = ref.lowbit_unpack(fmt, packed, scales, n, k, group)
+        out[tag + "_unpacked_sha"] = np.array(sha(dq))
+        _, y = ref.lowbit_gemm(fmt, packed, scales, x, m, n, k, group)
+        out[tag + "_y"] = y
+        if fmt == 2:
+            _, y8 = ref.lowbit_gemm_w8a8(packed, scales.reshape(-1), x, m, n, k)
+            out[tag + "_y_w8a8"] = y8
+
     np.savez_compressed(out_path, **out)
     print("wrote", out_path, {k: str(v) for k, v in variants.items()})
 
@@ -178,7 +225,7 @@ if __name__ == "__main__":
         env = dict(os.environ)
         subprocess.check_call([sys.executable, __file__, "--child",
                                os.path.join(HERE, "golden_default.npz")], env=env)
-        for name in ("QGEMV", "GGUF_GEMV", "INT8_GEMM", "W8A32"):
+        for name in ("QGEMV", "GGUF_GEMV", "INT8_GEMM", "W8A32", "QGEMV_W8A8", "LOWBIT_W8A8"):
             env[f"QUIXICORE_CPU_{name}_VARIANT"] = "ref"
         subprocess.check_call([sys.executable, __file__, "--child",
                                os.path.join(HERE, "golden_forced_ref.npz")], env=env)

@@ -59,6 +59,63 @@ def test_int8_and_w8a32_validation_order(qx):
     assert qx.qgemm_w8a32(w, ws_bad, xf, 1, 2, 4)[0] == qx.INVALID_ARGUMENT
 
 
+def test_w8a8_fused_and_lowbit_validation_order(qx):
+    """Checks the reference makes before it touches any data, in its order
+    (src/dispatch/qgemv_w8a8.cpp:131-146; kernels/quantization/qgemv_fused_ref.cpp:195-210,
+    288-300; kernels/quantization/lowbit_ref.cpp:203-222, 258-272, 366-380;
+    src/dispatch/lowbit_w8a8.cpp:68-80; quantization_ref.cpp:143-147)."""
+    x = np.zeros(64, np.float32)
+    y = np.zeros(4, np.float32)
+    packed = np.zeros(4 * 2 * 34, np.uint8)
+    P = lambda a: a.ctypes.data  # noqa: E731
+    assert qx.lib.qx_qgemv_w8a8(qx.Q8_0, None, None, None, 4, 33) == qx.INVALID_SHAPE
+    assert qx.lib.qx_qgemv_w8a8(11, P(packed), P(x), P(y), 4, 64) == qx.UNSUPPORTED_FORMAT
+    assert qx.lib.qx_qgemv_w8a8(qx.Q8_0, P(packed), None, P(y), 4, 64) == qx.INVALID_ARGUMENT
+    bad = x.copy()
+    bad[3] = np.inf
+    assert qx.lib.qx_qgemv_w8a8(qx.Q8_0, P(packed), P(bad), P(y), 4, 64) == qx.INVALID_ARGUMENT
+    size = C.c_longlong(0)
+    assert qx.lib.qx_qgemv_w8a8_packed_size(qx.Q4_0, 4, 64, C.byref(size)) == qx.OK and size.value == 4 * 2 * 18
+    assert qx.lib.qx_qgemv_w8a8_packed_size(qx.Q4_0, 4, 64, None) == qx.INVALID_ARGUMENT
+    assert qx.lib.qx_qgemv_w8a8_variant(3).decode() == "unsupported"
+    # fused projections: shape, then pointers, then format / layout
+    assert qx.lib.qx_qgemv_up_gate(qx.Q8_0, None, None, None, None, None, 0, 64) == qx.INVALID_SHAPE
+    assert qx.lib.qx_qgemv_up_gate(qx.Q8_0, P(packed), None, P(x), P(y), P(y), 4, 64) == qx.INVALID_ARGUMENT
+    assert qx.lib.qx_qgemv_up_gate(9, P(packed), P(packed), P(x), P(y), P(y), 4, 64) == qx.UNSUPPORTED_FORMAT
+    assert qx.lib.qx_qgemv_up_gate(qx.Q8_0, P(packed), P(packed), P(x), P(y), P(y), 4, 65) == qx.INVALID_SHAPE
+    assert qx.lib.qx_qgemv_up_gate_activation(qx.Q8_0, P(packed), P(packed), P(x), None, 4, 64, 1) == qx.INVALID_ARGUMENT
+    assert qx.lib.qx_qgemv_qkv(qx.Q8_0, None, None, None, None, None, None, None, 4, 0, 64) == qx.INVALID_SHAPE
+    assert qx.lib.qx_qgemv_qkv(qx.Q8_0, P(packed), P(packed), None, P(x), P(y), P(y), P(y), 4, 4, 64) == qx.INVALID_ARGUMENT
+    # compact int4 rows
+    assert qx.lowbit_packed_size(qx.LOWBIT_INT4_ROW, 3, 33) == (qx.OK, 3 * 17, 3)
+    assert qx.lowbit_packed_size(qx.LOWBIT_INT4_GROUP, 3, 130, 64) == (qx.OK, 3 * 65, 9)
+    assert qx.lowbit_packed_size(qx.LOWBIT_INT2_ROW, 2, 9) == (qx.OK, 2 * 3, 2)
+    assert qx.lowbit_packed_size(qx.LOWBIT_INT3_GROUP64, 2, 65) == (qx.OK, 2 * 48, 4)
+    assert qx.lowbit_packed_size(qx.LOWBIT_INT4_GROUP, 3, 130, 0)[0] == qx.INVALID_SHAPE
+    assert qx.lowbit_packed_size(7, 3, 130, 0)[0] == qx.INVALID_SHAPE
+    assert qx.lib.qx_lowbit_packed_size(qx.LOWBIT_INT4_ROW, 3, 33, 0, None, None) == qx.INVALID_ARGUMENT
+    w4 = np.zeros(3 * 17, np.uint8)
+    s4 = np.ones(3, np.float32)
+    xf = np.zeros((2, 33), np.float32)
+    yf = np.zeros((2, 3), np.float32)
+    assert qx.lib.qx_lowbit_gemm(qx.LOWBIT_INT4_ROW, P(w4), P(s4), P(xf), P(yf), 2, 0, 33, 0) == qx.INVALID_SHAPE
+    assert qx.lib.qx_lowbit_gemm(qx.LOWBIT_INT4_ROW, None, P(s4), P(xf), P(yf), 2, 3, 33, 0) == qx.INVALID_ARGUMENT
+    s_bad = s4.copy()
+    s_bad[1] = np.nan
+    assert qx.lib.qx_lowbit_gemm(qx.LOWBIT_INT4_ROW, P(w4), P(s_bad), P(xf), P(yf), 2, 3, 33, 0) == qx.INVALID_ARGUMENT
+    assert qx.lib.qx_lowbit_gemm(qx.LOWBIT_INT4_ROW, P(w4), P(s4), None, P(yf), 2, 3, 33, 0) == qx.INVALID_ARGUMENT
+    assert qx.lib.qx_lowbit_gemm_w8a8(P(w4), P(s4), P(xf), P(yf), 2, 3, 0) == qx.INVALID_SHAPE
+    assert qx.lib.qx_lowbit_gemm_w8a8(None, P(s4), P(xf), P(yf), 2, 3, 33) == qx.INVALID_ARGUMENT
+    x_bad = xf.copy()
+    x_bad[1, 2] = np.nan
+    assert qx.lib.qx_lowbit_gemm_w8a8(P(w4), P(s4), P(x_bad), P(yf), 2, 3, 33) == qx.INVALID_ARGUMENT
+    codes = np.zeros((2, 33), np.int8)
+    sc = np.zeros(2, np.float32)
+    assert qx.lib.qx_quantize_int8(P(xf), P(codes), P(sc), 2, 33, 16) == qx.INVALID_SHAPE
+    assert qx.lib.qx_quantize_int8(None, P(codes), P(sc), 2, 33, 0) == qx.INVALID_ARGUMENT
+    assert qx.lib.qx_quantize_int8(P(x_bad), P(codes), P(sc), 2, 33, 0) == qx.INVALID_ARGUMENT
+
+
 def test_variant_names_and_threads(qx):
     v = qx.variants()
     assert v["qgemv_q8_0"].startswith("sm100a") and v["qgemv_q4_0"].startswith("sm100a")

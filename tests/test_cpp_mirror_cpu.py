@@ -53,6 +53,19 @@ PROGRAM = textwrap.dedent(r"""
       const CpuPackedWeightsInfo blank = weights.info();
       CHECK(blank.layout == CpuPanelLayout::kAuto && blank.row_tile == 0 && blank.panel_bytes == 0);
       CHECK(weights.contract_data() == nullptr && weights.panel_data() == nullptr);
+      // callers either side of the GEMV: same names, same checks before any data is touched
+      CHECK(qgemv_w8a8(QuantFormat::kQ8_0, nullptr, x, y, 1, 31) == Status::kInvalidShape);
+      CHECK(qgemv_w8a8(QuantFormat::kQ8_0, nullptr, x, y, 1, 32) == Status::kInvalidArgument);
+      CHECK(qgemv_up_gate(QuantFormat::kQ4_0, packed, packed, x, nullptr, y, 1, 32) == Status::kInvalidArgument);
+      CHECK(qgemv_up_gate_activation(QuantFormat::kQ4_0, packed, packed, x, y, 0, 32) == Status::kInvalidShape);
+      CHECK(qgemv_qkv(QuantFormat::kQ8_0, packed, packed, packed, x, y, y, y, 1, 1, 33) == Status::kInvalidShape);
+      std::size_t wb = 0, sc = 0;
+      CHECK(lowbit_packed_size(LowBitFormat::kInt4Row, 3, 33, 0, &wb, &sc) == Status::kOk && wb == 51 && sc == 3);
+      CHECK(static_cast<int>(LowBitFormat::kInt4Group) == 3);
+      std::int8_t codes[32];
+      float scale[1];
+      CHECK(quantize_int8(nullptr, codes, scale, 1, 32, 0) == Status::kInvalidArgument);
+      CHECK(lowbit_gemm_w8a8(nullptr, scale, x, y, 1, 1, 32) == Status::kInvalidArgument);
       CpuPackedWeights moved = std::move(weights);
       CHECK(!moved.ready() && moved.info().rows == 0);
       set_num_threads(4);

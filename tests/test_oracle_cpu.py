@@ -180,3 +180,115 @@ def test_oracle_matches_live_reference(orc, ref, wl):
     _, y_ref = ref.qgemm_w8a8(w, x, ws, xs, 7, 33, 4096)
     _, y, _ = orc.int8_gemm(w, x, ws, xs, 7, 33, 4096)
     assert_bit_equal(y, y_ref, "live w8a8")
+
+
+# ---- callers either side of the GEMV: activation-quantising GEMV, fused decode projections,
+# ---- int8 activation quantiser, compact int4 rows ----------------------------------------
+
+def _fused_inputs(wl, fmt, lo, hi):
+    n, k, kv = 40, 1024, 24
+    up_w = wl.packed_blocks(fmt, n, k, lo, hi, seed=31)
+    gate_w = wl.packed_blocks(fmt, n, k, lo, hi, seed=32)
+    wk = wl.packed_blocks(fmt, kv, k, lo, hi, seed=33)
+    wv = wl.packed_blocks(fmt, kv, k, lo, hi, seed=34)
+    x = wl.activations_f32(1, k, seed=31)[0].copy()
+    return n, k, kv, up_w, gate_w, wk, wv, x
+
+
+@pytest.mark.parametrize("fmt,name,lo,hi", [(Q8_0, "q8", 0.001, 0.02), (Q4_0, "q4", 0.002, 0.04)])
+def test_w8a8_and_fused_projections_golden(orc, wl, golden, fmt, name, lo, hi):
+    """The portable kernels of the reference (forced-ref fixtures) bit for bit; the runtime
+    dispatched ones (default fixtures) within the f32 tolerance where their summation order
+    differs."""
+    n, k, kv, up_w, gate_w, wk, wv, x = _fused_inputs(wl, fmt, lo, hi)
+    g_ref, g_def = golden["forced_ref"], golden["default"]
+    status, y = orc.qgemv_w8a8(fmt, up_w, x, n, k)
+    assert status == 0
+    assert_bit_equal(y, g_ref[f"w8a8_{name}_{n}x{k}_y"], "qgemv_w8a8 vs reference (ref variant)")
+    assert np.allclose(y, g_def[f"w8a8_{name}_{n}x{k}_y"], rtol=1e-5, atol=1e-4)
+    _, up = orc.qgemv(fmt, up_w, x, n, k, 0)
+    _, gate = orc.qgemv(fmt, gate_w, x, n, k, 0)
+    for g in (g_ref, g_def):  # the fused entry points have one (portable) kernel on x86
+        assert_bit_equal(up, g[f"upgate_{name}_{n}x{k}_up"], "up")
+        assert_bit_equal(gate, g[f"upgate_{name}_{n}x{k}_gate"], "gate")
+        for gelu in (1, 0):
+            assert_bit_equal(orc.gate_activation(up, gate, bool(gelu)),
+                             g[f"upgate_{name}_{n}x{k}_act{gelu}"], f"activation gelu={gelu}")
+        assert_bit_equal(orc.qgemv(fmt, wk, x, kv, k, 0)[1], g[f"qkv_{name}_k"], "qkv k")
+        assert_bit_equal(orc.qgemv(fmt, wv, x, kv, k, 0)[1], g[f"qkv_{name}_v"], "qkv v")
+        assert_bit_equal(up, g[f"qkv_{name}_q"], "qkv q")
+    # non-finite activations are rejected (src/dispatch/qgemv_w8a8.cpp:141-145)
+    bad = x.copy()
+    bad[5] = np.inf
+    assert orc.qgemv_w8a8(fmt, up_w, bad, n, k)[0] == 3
+
+
+def test_quantize_int8_golden(orc, wl, golden):
+    x = wl.activations_f32(5, 192, seed=41)
+    x[1] = 0.0
+    x[2, 7] = 1e-30
+    for name in ("default", "forced_ref"):
+        for group in (0, 32, 64):
+            status, codes, scales = orc.quantize_int8(x, 5, 192, group)
+            assert status == 0
+            assert np.array_equal(codes, golden[name][f"quant_int8_g{group}_codes"])
+            assert_bit_equal(scales, golden[name][f"quant_int8_g{group}_scales"], "scales")
+    assert orc.quantize_int8(x, 5, 192, 50)[0] == 1       # group does not divide dim
+    bad = x.copy()
+    bad[0, 0] = np.nan
+    assert orc.quantize_int8(bad, 5, 192, 0)[0] == 3
+
+
+def _lowbit_case(fmt, n, k, m):
+    rng = np.random.Generator(np.random.Philox(key=[fmt * 100 + k, 7]))
+    w = (rng.integers(-1000, 1001, (n, k)).astype(np.float32) / np.float32(1000.0)) * np.float32(0.2)
+    x = rng.integers(-2000, 2001, (m, k)).astype(np.float32) / np.float32(500.0)
+    return w, x
+
+
+@pytest.mark.parametrize("fmt,group,n,k,m", [(2, 0, 19, 200, 3), (3, 64, 17, 256, 2), (2, 0, 9, 33, 4)])
+def test_lowbit_int4_golden(orc, golden, fmt, group, n, k, m):
+    import hashlib
+    w, x = _lowbit_case(fmt, n, k, m)
+    tag = f"lowbit_f{fmt}_{m}x{n}x{k}"
+    for name in ("default", "forced_ref"):
+        g = golden[name]
+        status, packed, scales = orc.lowbit_pack(fmt, w, n, k, group)
+        assert status == 0
+        assert np.array_equal(packed, g[tag + "_packed"])
+        assert_bit_equal(scales, g[tag + "_scales"], "scales")
+        _, dq = orc.lowbit_unpack(fmt, packed, scales, n, k, group)
+        assert hashlib.sha256(np.ascontiguousarray(dq).tobytes()).hexdigest() == str(g[tag + "_unpacked_sha"])
+        _, y = orc.lowbit_gemm(fmt, packed, scales, x, m, n, k, group)
+        # the f32 GEMM runs an AVX-512 variant on the generating host (another summation
+        # order): tolerance; the W4A8 route is exact integers and two multiplies: bits
+        assert np.allclose(y, g[tag + "_y"], rtol=1e-5, atol=1e-4), str(g["lowbit_variant"])
+        if fmt == 2:
+            _, y8 = orc.lowbit_gemm_w8a8(packed, scales.reshape(-1), x, m, n, k)
+            assert_bit_equal(y8, g[tag + "_y_w8a8"], "lowbit_gemm_w8a8")
+
+
+def test_new_entry_points_against_live_reference(orc, ref, wl):
+    if not hasattr(ref.lib, "qxref_qgemv_w8a8"):
+        pytest.skip("reference library built before these entry points were added")
+    for fmt, lo, hi in ((Q8_0, 0.001, 0.02), (Q4_0, 0.002, 0.04)):
+        n, k = 130, 2048
+        w = wl.packed_blocks(fmt, n, k, lo, hi, seed=51)
+        x = wl.activations_f32(1, k, seed=52)[0].copy()
+        a, b = orc.qgemv_w8a8(fmt, w, x, n, k)[1], ref.qgemv_w8a8(fmt, w, x, n, k)[1]
+        assert np.allclose(a, b, rtol=1e-5, atol=1e-4)
+    x = wl.activations_f32(7, 4096, seed=53)
+    for group in (0, 128):
+        _, c1, s1 = orc.quantize_int8(x, 7, 4096, group)
+        _, c2, s2 = ref.quantize_int8(x, 7, 4096, group)
+        assert np.array_equal(c1, c2)
+        assert_bit_equal(s1, s2, "quantize_int8 scales")
+    w, xx = _lowbit_case(2, 65, 1408, 4)
+    _, packed, scales = orc.lowbit_pack(2, w, 65, 1408, 0)
+    _, p2, s2 = ref.lowbit_pack(2, w, 65, 1408, 0)
+    assert np.array_equal(packed, p2)
+    assert_bit_equal(scales, s2, "lowbit scales")
+    assert_bit_equal(orc.lowbit_gemm_w8a8(packed, scales.reshape(-1), xx, 4, 65, 1408)[1],
+                     ref.lowbit_gemm_w8a8(packed, scales.reshape(-1), xx, 4, 65, 1408)[1], "W4A8")
+    assert np.allclose(orc.lowbit_gemm(2, packed, scales, xx, 4, 65, 1408)[1],
+                       ref.lowbit_gemm(2, packed, scales, xx, 4, 65, 1408)[1], rtol=1e-5, atol=1e-4)
