@@ -942,9 +942,9 @@ def _extra_lowbit(qx, wl, torch, hbm_peak):
         xd = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).cuda()
         yd = torch.zeros((m, n), device="cuda")
         scratch = torch.zeros(qx.lib.qx_lowbit_w8a8_scratch_bytes(m, k), dtype=torch.uint8, device="cuda")
-        stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
         def call(i):
+            stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)  # the capturing stream
             qx.check(qx.lib.qx_lowbit_gemm_w8a8_dev(C.c_void_p(ws[i % copies].data_ptr()), C.c_void_p(scale.data_ptr()),
                                                     C.c_void_p(xd.data_ptr()), C.c_void_p(yd.data_ptr()),
                                                     C.c_void_p(scratch.data_ptr()), m, n, k, stream), "w4a8")
