@@ -103,10 +103,10 @@ struct TcGeom {
                     ? 3
                     : 2);
   static constexpr int kSlots = weight_slots_fit(kBudget, kWorkBytes, kSlotBytes, kWorkSlots);
-  // One TMEM stage (the unit handed from the MMA issuer to an epilogue set) holds several
-  // accumulators when they are narrow: up to 128 columns for small batches (a whole slab
-  // per hand-over), 64 for larger ones (more stages in flight matter more there).
-  static constexpr int kStageTarget = MP <= 8 ? 128 : 64;
+  // One TMEM stage (the unit handed from the MMA issuer to the epilogue) holds several
+  // accumulators when they are narrow: up to 128 columns (a whole slab per hand-over for
+  // decode batches).
+  static constexpr int kStageTarget = 128;
   static constexpr int kGroupsPerStage =
       kN >= kStageTarget ? 1 : (kStageTarget / kN < kGroups ? kStageTarget / kN : kGroups);
   static constexpr int kStagesPerSlab = kGroups / kGroupsPerStage;
@@ -115,17 +115,18 @@ struct TcGeom {
   // Epilogue sets take the K units in turn (unit mod kSets); which set sums a unit does not
   // matter for the result (unit sums meet in scratch memory and are added in a fixed order).
   // Decode batches are bound by the per-slab latency of an epilogue thread (barrier waits,
-  // TMEM load, a dependent chain per block), so a single activation row gets three sets; batches two (three
-  // would leave them too few registers per thread).
-  static constexpr int kSets = MP == 1 ? 3 : 2;
+  // TMEM load, a dependent chain per block), so a single activation row gets three sets,
+  // two to four rows two. From eight rows on the epilogue is bound by its work per item and
+  // by how far the MMAs can run ahead in TMEM (a slab then fills half of it or more): ONE
+  // set whose warps all work on the same stage, each on a share of the activation rows.
+  static constexpr int kSets = MP == 1 ? 3 : (MP >= 8 ? 1 : 2);
   // Each epilogue set has its own ring of accumulators, so every TMEM barrier is used by
   // one set only (a parity wait cannot tell apart phases two steps apart).
   static constexpr int kTPerSet = kTStages / kSets;
-  // Epilogue: two sets (alternate K units) of four warps (one per TMEM lane quarter); q8_0
-  // batches of 16 double that, the two warps of a quarter taking half of the activation rows
-  // each (the epilogue's instruction count bounds big batches; at 32 rows the extra warps
-  // cost more registers than they bring).
-  static constexpr int kEpiSplit = (MP == 16 && !kQ4) ? 2 : 1;
+  // Epilogue: per set four warps (one per TMEM lane quarter) times kEpiSplit: from eight
+  // activation rows on, the kEpiSplit warps of a lane quarter take four (at 32 rows: eight)
+  // activation rows each, so a thread handles 32 (64) items per slab instead of 64 - 256.
+  static constexpr int kEpiSplit = MP >= 16 ? 4 : (MP == 8 ? 2 : 1);
   static constexpr int kEpiWarps = 4 * kSets * kEpiSplit;
   static constexpr int kRowsPerThread = MP / kEpiSplit;  // activation rows per epilogue thread
   static constexpr int kUnpackWarps = kQ4 ? 4 : 0;
@@ -136,8 +137,9 @@ struct TcGeom {
   // arrivals on a slot's `ready` barrier (0: the MMA issuer waits for the copies themselves)
   static constexpr int kReadyCount = (kFused ? 1 : 0) + kUnpackWarps;
   static constexpr int kLdCols = kColsPerWarp >= 64 ? 64 : 32;  // columns fetched per TMEM wait
-  static_assert(kEpiSplit == 1 || (kGroupsPerStage == 1 && kG == 1), "split stages hold one block");
-  static constexpr bool kRollGroups = MP >= 8;
+  static constexpr int kShareCols = 4 * kRowsPerThread;  // columns of (one block, a warp's rows)
+  static_assert(kEpiSplit == 1 || kShareCols == 16 || kShareCols == 32, "TMEM load widths");
+  static constexpr bool kRollGroups = MP >= 8 && kEpiSplit == 1;
   static_assert(kSlots + kWorkSlots + kTStages + kConstSlots <= kThreads - 64, "one barrier group per thread");
   static_assert(kSlots >= 2 && kTPerSet >= 1 && kTPerSet <= 15 && kN >= 32 && kN <= 256, "geometry");
   static_assert(!kFused || kSlots > kWorkSlots, "a work slot's previous slab is newer than a weight slot's");
@@ -687,6 +689,43 @@ gemv_tc_kernel(const GemvTcParams p) {
               scw[0] = s4.x; scw[1] = s4.y; scw[2] = s4.z; scw[3] = s4.w;
             }
           }
+          if constexpr (G::kEpiSplit > 1) {
+            // Row-split stages: this warp's share of every block of the stage (accumulator
+            // b / kG, block class b % kG, activation rows split * kMine ..) is fetched at
+            // once, the stage handed back, then the items are combined.
+            constexpr int kShares = G::kGroupsPerStage * G::kG;
+            uint32_t v[kShares][G::kShareCols];
+#pragma unroll
+            for (int b = 0; b < kShares; ++b) {
+              const uint32_t taddr = tmem_base + ts * G::kTCols + (b / G::kG) * G::kN +
+                                     (b % G::kG) * (4 * MP) + split * G::kShareCols +
+                                     (static_cast<uint32_t>(quarter * 32) << 16);
+              tmem_ld_cols(taddr, v[b]);
+            }
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->tmem_empty[ts]);
+#pragma unroll
+            for (int b = 0; b < kShares; ++b) {
+              const int j = (st * G::kGroupsPerStage + b / G::kG) * G::kG + b % G::kG;
+              const float d = half_bits_to_float(
+                  static_cast<unsigned short>((scw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
+#pragma unroll
+              for (int lm = 0; lm < kMine; ++lm) {
+                const int m = split * kMine + lm;
+                if (m < p.m) {
+                  const int4 xc = xcs[j * MP + m];  // {scale, k_lo, k_hi, -}
+                  const int s0 = static_cast<int>(v[b][4 * lm]);
+                  const int s1 = static_cast<int>(v[b][4 * lm + 1]);
+                  const int s2 = static_cast<int>(v[b][4 * lm + 2]);
+                  const int s3 = static_cast<int>(v[b][4 * lm + 3]);
+                  const float sum = kQ4 ? block_sum(s0, s1, s2, s3, xc.y, xc.z) : block_sum(s0, s1, s2);
+                  acc[lm] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[lm]);
+                }
+              }
+            }
+          } else {
 #pragma unroll
           for (int c0 = 0; c0 < G::kColsPerWarp; c0 += G::kLdCols) {
             uint32_t v[G::kLdCols / 32][32];
@@ -727,6 +766,7 @@ gemv_tc_kernel(const GemvTcParams p) {
                 acc[lm] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[lm]);
               }
             }
+          }
           }
           if (++ring_pos == G::kTPerSet) {
             ring_pos = 0;
