@@ -151,6 +151,32 @@ __device__ __forceinline__ float block_sum_cvt(int s0, int s1, int s2, int s3, i
   return fmaf(hi, 65536.0f, lo);
 }
 
+// The tensor-core kernel and the single-row decode kernel accumulate the two parts of a
+// block separately: with ds = d_b * scale_b (one rounded product),
+//   L += lo * ds,   H += hi * ds        (one chain each per block parity, ascending blocks)
+// and a K unit's sum is (65536 * H_even + L_even) + (65536 * H_odd + L_odd). lo and hi are
+// the values of block_sum above: lo = RN(256*s1 + s0 - k_lo), hi = 256*s3 + s2 - k_hi
+// (exact), for q8_0 lo = RN(256*s1 + s0), hi = s2. Both conversions give the same bits.
+struct BlockParts {
+  float lo, hi;
+};
+__device__ __forceinline__ BlockParts block_parts(int s0, int s1, int s2) {
+  return {fmaf(small_int_to_float(s1), 256.0f, small_int_to_float(s0)), small_int_to_float(s2)};
+}
+__device__ __forceinline__ BlockParts block_parts(int s0, int s1, int s2, int s3, int k_lo, int k_hi) {
+  return {fmaf(small_int_to_float(s1), 256.0f, small_int_to_float(s0 - k_lo)),
+          fmaf(small_int_to_float(s3), 256.0f, small_int_to_float(s2 - k_hi))};
+}
+__device__ __forceinline__ BlockParts block_parts_cvt(int s0, int s1, int s2) {
+  return {__int2float_rn(s0 + (s1 << 8)), small_int_to_float(s2)};
+}
+__device__ __forceinline__ BlockParts block_parts_cvt(int s0, int s1, int s2, int s3, int k_lo, int k_hi) {
+  return {__int2float_rn(s0 - k_lo + (s1 << 8)), __int2float_rn(s2 - k_hi + (s3 << 8))};
+}
+__device__ __forceinline__ float unit_sum(float l_even, float h_even, float l_odd, float h_odd) {
+  return __fadd_rn(fmaf(h_even, 65536.0f, l_even), fmaf(h_odd, 65536.0f, l_odd));
+}
+
 // q4_0 block constants from sum = sum_j t_j (|sum| <= 2^27): 128 * sum split at bit 16
 // without leaving 32 bits.
 __host__ __device__ inline void q4_offset_constants(int sum, int* k_lo, int* k_hi) {

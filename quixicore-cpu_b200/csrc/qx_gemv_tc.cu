@@ -565,9 +565,13 @@ gemv_tc_kernel(const GemvTcParams p) {
     const int quarter = warp & 3;  // TMEM lanes 32*quarter .. +31 are this warp's
     constexpr int kMine = G::kRowsPerThread;
     const int row_in_tile = quarter * 32 + lane;
-    float acc[kMine];  // current unit, activation rows split * kMine ..
+    // Current unit, activation rows split * kMine ..: four chains per row (qx_gemv.cuh:
+    // low and high part of the blocks, even and odd blocks, ascending block order each) that
+    // meet at the end of the unit. The single-row decode kernel (qx_gemv_decode.cu) sums in
+    // exactly this order, so a row of a batch and the same row alone give the same bits.
+    float acc[4][kMine];  // [2 * block parity + part]
 #pragma unroll
-    for (int m = 0; m < kMine; ++m) acc[m] = 0.0f;
+    for (int m = 0; m < kMine; ++m) acc[0][m] = acc[1][m] = acc[2][m] = acc[3][m] = 0.0f;
     int units_mine = 0;  // units of the current tile this thread has written
     // A share of a row = this thread's units of one tile. Counting a share in on the row's
     // counter needs a fence (the unit sums must be visible before the count), and a fence
@@ -720,8 +724,11 @@ gemv_tc_kernel(const GemvTcParams p) {
                   const int s1 = static_cast<int>(v[b][4 * lm + 1]);
                   const int s2 = static_cast<int>(v[b][4 * lm + 2]);
                   const int s3 = static_cast<int>(v[b][4 * lm + 3]);
-                  const float sum = kQ4 ? block_sum(s0, s1, s2, s3, xc.y, xc.z) : block_sum(s0, s1, s2);
-                  acc[lm] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[lm]);
+                  const BlockParts parts =
+                      kQ4 ? block_parts(s0, s1, s2, s3, xc.y, xc.z) : block_parts(s0, s1, s2);
+                  const float term_scale = __fmul_rn(d, __int_as_float(xc.x));
+                  acc[2 * (j & 1)][lm] = fmaf(parts.lo, term_scale, acc[2 * (j & 1)][lm]);
+                  acc[2 * (j & 1) + 1][lm] = fmaf(parts.hi, term_scale, acc[2 * (j & 1) + 1][lm]);
                 }
               }
             }
@@ -755,15 +762,22 @@ gemv_tc_kernel(const GemvTcParams p) {
                 const int s1 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 1) & 31]);
                 const int s2 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 2) & 31]);
                 const int s3 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 3) & 31]);
-                const float sum =
-                    G::kFused ? (kQ4 ? block_sum_cvt(s0, s1, s2, s3, xc.y, xc.z) : block_sum_cvt(s0, s1, s2))
-                              : (kQ4 ? block_sum(s0, s1, s2, s3, xc.y, xc.z) : block_sum(s0, s1, s2));
+                const BlockParts parts =
+                    G::kFused ? (kQ4 ? block_parts_cvt(s0, s1, s2, s3, xc.y, xc.z) : block_parts_cvt(s0, s1, s2))
+                              : (kQ4 ? block_parts(s0, s1, s2, s3, xc.y, xc.z) : block_parts(s0, s1, s2));
                 const float d = half_bits_to_float(
                     G::kRollGroups
                         ? *reinterpret_cast<const unsigned short*>(
                               raw_base + G::kScaleOffset + (row_in_tile * kSlabBlocks + j) * 2)
                         : static_cast<unsigned short>((scw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
-                acc[lm] = fmaf(sum, __fmul_rn(d, __int_as_float(xc.x)), acc[lm]);
+                const float term_scale = __fmul_rn(d, __int_as_float(xc.x));
+                if (j & 1) {
+                  acc[2][lm] = fmaf(parts.lo, term_scale, acc[2][lm]);
+                  acc[3][lm] = fmaf(parts.hi, term_scale, acc[3][lm]);
+                } else {
+                  acc[0][lm] = fmaf(parts.lo, term_scale, acc[0][lm]);
+                  acc[1][lm] = fmaf(parts.hi, term_scale, acc[1][lm]);
+                }
               }
             }
           }
@@ -794,8 +808,8 @@ gemv_tc_kernel(const GemvTcParams p) {
 #pragma unroll
           for (int lm = 0; lm < kMine; ++lm) {
             const int m = split * kMine + lm;
-            if (m < p.m) part[m * kTileRows] = acc[lm];
-            acc[lm] = 0.0f;
+            if (m < p.m) part[m * kTileRows] = unit_sum(acc[0][lm], acc[1][lm], acc[2][lm], acc[3][lm]);
+            acc[0][lm] = acc[1][lm] = acc[2][lm] = acc[3][lm] = 0.0f;
           }
           ++units_mine;
         }
@@ -1079,6 +1093,27 @@ qx_status launch_gemv_tc(const qx_weights* w, const float* x, const uint8_t* xim
                          cudaStream_t stream, const GemvPush* push, const GemvOptions* options) {
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
+  if (w->segments > 1) {
+    for (int s = 0; s < w->segments; ++s) {
+      if (options == nullptr || options->segment_y[s] == nullptr) {
+        set_last_error_text("gemv: a fused handle needs one output pointer per segment");
+        return QX_STATUS_INVALID_ARGUMENT;
+      }
+    }
+    if (push != nullptr) {
+      set_last_error_text("gemv: fused handles cannot push to other ranks");
+      return QX_STATUS_INVALID_ARGUMENT;
+    }
+  }
+  if (push != nullptr && push->peers > kMaxPushPeers) {
+    set_last_error_text("gemv: more than 7 peer ranks");
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  // a single activation row goes to the streaming decode kernel (same bits, see there)
+  if (gemv_decode_enabled() && gemv_decode_serves(w, m, scratch, ctx->prop.multiProcessorCount)) {
+    return launch_gemv_decode(w, x, y, scratch, ctx->prop.multiProcessorCount, ctx->error_dev,
+                              stream, push, options);
+  }
   return launch_gemv_tc_at(w, x, ximg, y, m, ldy, ws_base, scratch, ctx->error_dev, stream, push,
                            options);
 }

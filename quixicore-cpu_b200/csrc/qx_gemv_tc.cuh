@@ -55,6 +55,18 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
                             int* error_word, cudaStream_t stream, const GemvPush* push = nullptr,
                             const GemvOptions* options = nullptr);
 
+// ---- single-row decode kernel (qx_gemv_decode.cu) ----------------------------------------
+// Whether launch_gemv_tc hands single-row launches to it (on unless the environment says
+// QX_B200_DECODE_KERNEL=0), and whether it serves this handle: one activation row and a K
+// that splits into at most eight CTAs of at most eight slabs per row tile.
+bool gemv_decode_enabled();
+bool gemv_decode_serves(const qx_weights* w, int m, const GemvScratch& scratch, int sm_count);
+// Same results, bit for bit, as launch_gemv_tc_at with m = 1; needs no scratch memory.
+qx_status launch_gemv_decode(const qx_weights* w, const float* x, float* y,
+                             const GemvScratch& scratch, int sm_count, int* error_word,
+                             cudaStream_t stream, const GemvPush* push = nullptr,
+                             const GemvOptions* options = nullptr);
+
 const char* gemv_variant_name();
 
 }  // namespace qx
