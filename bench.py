@@ -758,9 +758,10 @@ def _time_calls(torch, fn, iters, warm=3):
     return a.elapsed_time(b) / (3 * iters) * 1e-3
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_tc_kernel launch on the headline
-# workload from an ncu capture (algorithmic bytes: 33 103 872)
-NCU_DRAM_BYTES_PER_LAUNCH = 33167104
+# dram__bytes_read.sum + dram__bytes_write.sum of one gemv_decode_kernel launch on the
+# headline workload from an ncu capture (algorithmic bytes: 33 103 872; the 57 KB of outputs
+# had not left L2 when the capture ended)
+NCU_DRAM_BYTES_PER_LAUNCH = 33078528
 
 EXTRA_CASES = ("cfg2_w8a8_gemm", "cfg0_q8_0_gemv", "cfg3_q8_0_batched", "cfg4_q4_0_prefill",
                "w8a32_gemm", "fused_decode", "lowbit_w4a8")

@@ -305,7 +305,12 @@ qx_status launch_gate_activation(const float* up, const float* gate, float* out,
   return QX_STATUS_OK;
 }
 
-const char* gemv_variant_name() { return force_dp4a() ? "sm100a_dp4a" : "sm100a_tcgen05_digits"; }
+// digits: activations as base-256 digits, exact int8 sums; tcgen05: the persistent tensor-core
+// kernel; mma: the streaming single-row kernel with warp-level MMAs (small matrices)
+const char* gemv_variant_name() {
+  if (force_dp4a()) return "sm100a_dp4a";
+  return gemv_decode_enabled() ? "sm100a_digits_tcgen05+mma" : "sm100a_digits_tcgen05";
+}
 
 // Workspace layout of one GEMV call: [row counters | activation slab images | per-unit
 // partial sums]; sizes depend only on (m, k, rows).

@@ -57,6 +57,7 @@ using namespace sm100;
 
 constexpr int kDecodeWarps = kTileRows / 16;
 constexpr int kDecodeThreads = 32 * kDecodeWarps;
+constexpr int kDecodeStages = 2;         // ring depth (spans of one slab)
 constexpr int kMaxCtaSlabs = 8;          // slabs of K per CTA (their digits stay in shared memory)
 constexpr int kMaxUnits = 16;            // units per row (gemv_scratch_layout)
 constexpr int kFragBytes = 4 * 32 * 16;  // per slab: [block pair][lane]{first b0, b1, second b0, b1}
@@ -71,8 +72,6 @@ struct DecodeParams {
   int slabs, nb, x_vector;
   int unit_slabs, units_per_tile;
   int ksplit;         // CTAs per row tile = cluster size
-  int units_per_cta;
-  int stages;         // ring depth
   int cta_slabs;      // most slabs any CTA handles (sizes the digit area)
   int segments;
   int seg_tile_begin[qx_weights::kMaxSegments];
@@ -81,6 +80,7 @@ struct DecodeParams {
   int int8_activations;
   int peers;
   PushCell* push_cells[kMaxPushPeers];
+  unsigned prefetch_stride;  // 0: a CTA calls only its own slabs into L2
 };
 
 struct __align__(8) DecodeBarriers {
@@ -117,6 +117,11 @@ __device__ __forceinline__ void cluster_store(uint32_t remote, float v) {
   asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
 }
 // shared-memory loads by 32-bit address (the lanes' addresses are built with XORs on it)
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   uint2 v;
   asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
@@ -254,17 +259,20 @@ __device__ __forceinline__ void write_slab_fragments(uint8_t* frags, LaneConst* 
   }
 }
 
-template <int FMT>
+// CS: slabs per CTA when every CTA of the launch has the same number (the loops over slabs
+// then unroll and the ring positions are constants), 0: read from the parameters.
+template <int FMT, int CS>
 __global__ void __launch_bounds__(kDecodeThreads, FMT == QX_FORMAT_Q4_0 ? 4 : 2)
 gemv_decode_kernel(const DecodeParams p) {
   constexpr bool kQ4 = FMT == QX_FORMAT_Q4_0;
   constexpr int kSpan = slab_span_bytes(FMT);
   constexpr int kScaleOffset = slab_code_bytes(FMT);
   constexpr int kCodeSets = kQ4 ? 1 : 2;  // q8_0: the two halves of a block are separate bytes
+  constexpr int kStages = kDecodeStages;
   static_assert(kSpan % 2048 == 0, "the lanes' XOR addressing needs stages on 2 KiB boundaries");
   // [ring: stages x span][fragments: cta_slabs x 2 KiB][constants][unit sums][barriers]
   extern __shared__ __align__(1024) uint8_t smem[];
-  uint8_t* frags = smem + p.stages * kSpan;
+  uint8_t* frags = smem + kStages * kSpan;
   LaneConst* consts = reinterpret_cast<LaneConst*>(frags + p.cta_slabs * kFragBytes);
   float* sums = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(consts) +
                                          p.cta_slabs * kLaneConstBytes);
@@ -280,22 +288,23 @@ gemv_decode_kernel(const DecodeParams p) {
 
   const int tile = static_cast<int>(blockIdx.x) / p.ksplit;
   const int part = static_cast<int>(blockIdx.x) - tile * p.ksplit;  // == cluster rank
-  const int unit_begin = part * p.units_per_cta;
-  const int unit_end = min(unit_begin + p.units_per_cta, p.units_per_tile);
+  // the tile's units in `ksplit` nearly equal consecutive shares
+  const int unit_begin = part * p.units_per_tile / p.ksplit;
+  const int unit_end = (part + 1) * p.units_per_tile / p.ksplit;
   const int slab_begin = unit_begin * p.unit_slabs;
   const int slab_end = min(unit_end * p.unit_slabs, p.slabs);
-  const int count = max(slab_end - slab_begin, 0);
+  const int count = CS > 0 ? CS : max(slab_end - slab_begin, 0);
   const uint8_t* wsrc = p.panel + (static_cast<long long>(tile) * p.slabs + slab_begin) * kSpan;
 
   if (threadIdx.x == 0) {
     // the weights depend on nothing in front of this kernel: the first copies leave at once
-    for (int s = 0; s < p.stages; ++s) {
+    for (int s = 0; s < kStages; ++s) {
       mbar_init(&bars->full[s], 1);
       bars->released[s] = 0;
     }
     bars->abort_flag = 0;
     mbar_fence_init();
-    const int ahead = min(count, p.stages);
+    const int ahead = min(count, kStages);
     for (int i = 0; i < ahead; ++i) {
       mbar_arrive_expect_tx(&bars->full[i], kSpan);
       bulk_copy_g2s(ring + i * kSpan, wsrc + static_cast<long long>(i) * kSpan, kSpan, &bars->full[i]);
@@ -303,6 +312,22 @@ gemv_decode_kernel(const DecodeParams p) {
     // ... and the CTA's other slabs are called into L2, so that they are near when the
     // stages come free
     for (int i = ahead; i < count; ++i) prefetch_l2(wsrc + static_cast<long long>(i) * kSpan, kSpan);
+    // Only about `prefetch_stride` CTAs of a launch find room on the SMs while the launch
+    // in front of it is still computing; the others start when that one leaves and would
+    // all ask HBM for their first slabs at once, with every SM waiting. So each CTA also
+    // calls into L2 what the CTAs `prefetch_stride`, 2 * `prefetch_stride`, ... further on
+    // will copy: the early CTAs between them fetch the whole matrix while the launch in
+    // front computes (a line that is in L2 already costs nothing).
+    if (p.prefetch_stride > 0) {
+      for (unsigned other = blockIdx.x + p.prefetch_stride; other < gridDim.x; other += p.prefetch_stride) {
+        const int o_tile = static_cast<int>(other) / p.ksplit;
+        const int o_part = static_cast<int>(other) - o_tile * p.ksplit;
+        const int o_begin = (o_part * p.units_per_tile / p.ksplit) * p.unit_slabs;
+        const int o_end = min(((o_part + 1) * p.units_per_tile / p.ksplit) * p.unit_slabs, p.slabs);
+        const uint8_t* src = p.panel + (static_cast<long long>(o_tile) * p.slabs + o_begin) * kSpan;
+        for (int i = 0; i < o_end - o_begin; ++i) prefetch_l2(src + static_cast<long long>(i) * kSpan, kSpan);
+      }
+    }
   }
   {
     // the quantizer writes only the non-zero positions of the fragment area
@@ -326,17 +351,18 @@ gemv_decode_kernel(const DecodeParams p) {
       kQ4 ? r0 * 128 + ((g >> 1) << 5) + ((hi ^ (g & 1)) << 4) + (t & 1) * 8
           : r0 * 128 + ((g >> 2) << 6) + (((2 * hi) ^ (g & 3)) << 4) + (t & 1) * 8;
   const uint32_t scale_base = kScaleOffset + (r0 * kSlabBlocks + hi) * 2;  // blocks 2 * pr + hi
-  uint32_t stage = 0, phase = 0;
-  int use = 0;  // how often the ring has wrapped
-  uint2 code[4][kCodeSets][2];  // [pair][MMA][row]: this lane's code bytes of the current slab
+  // [pair][MMA][K half]{row r0, row r0 + 8}: this lane's code bytes of the current slab
+  uint2 code[4][kCodeSets][2];
   uint32_t scale_bits[4];  // fp16 scales of this lane's block of each pair: row r0 | row r0 + 8
   bool ok = true;
-  // Takes slab i out of its stage into registers (the weights depend on nothing in front of
-  // this kernel) and frees the stage: the last warp through sends off the copy of the slab
-  // that uses the stage next (the count runs over all uses of a stage: nothing is reset).
+  // Takes slab i (stage i % 2, its use number i / 2) out of the ring into registers -- the
+  // weights depend on nothing in front of this kernel -- and frees the stage: the last warp
+  // through sends off the copy of the slab that uses the stage next (the count runs over
+  // all uses of a stage: nothing is reset).
   auto take_slab = [&](int i) -> bool {
+    const uint32_t stage = static_cast<uint32_t>(i) & 1u, use = static_cast<uint32_t>(i) >> 1;
     // (the outcome is made uniform: the lanes of a warp run MMAs and shuffles together)
-    if (!__all_sync(0xffffffffu, mbar_wait(&bars->full[stage], phase, abort_flag))) return false;
+    if (!__all_sync(0xffffffffu, mbar_wait(&bars->full[stage], use & 1u, abort_flag))) return false;
     const uint32_t base = ring + stage * kSpan;
 #pragma unroll
     for (int pr = 0; pr < 4; ++pr) {
@@ -345,8 +371,9 @@ gemv_decode_kernel(const DecodeParams p) {
         const uint32_t at = kQ4 ? base + (code_base ^ (pr << 5))
                                 : base + (pr >> 1) * (kTileRows * 128) +
                                       (code_base ^ (half << 4) ^ ((pr & 1) << 6));
-        code[pr][half][0] = lds64(at);
-        code[pr][half][1] = lds64(at + 8 * 128);
+        // four 32-bit loads, in the order the MMA wants its A registers (row g | row g + 8)
+        code[pr][half][0] = make_uint2(lds32(at), lds32(at + 8 * 128));
+        code[pr][half][1] = make_uint2(lds32(at + 4), lds32(at + 8 * 128 + 4));
       }
       scale_bits[pr] = static_cast<uint32_t>(lds16(base + scale_base + pr * 4)) |
                        (static_cast<uint32_t>(lds16(base + scale_base + pr * 4 + 8 * kSlabBlocks * 2)) << 16);
@@ -354,16 +381,11 @@ gemv_decode_kernel(const DecodeParams p) {
     __syncwarp();
     if (lane == 0) {
       const int before = atomicAdd(&bars->released[stage], 1);
-      if (before == kDecodeWarps * (use + 1) - 1 && i + p.stages < count) {
+      if (before == static_cast<int>(kDecodeWarps * (use + 1) - 1) && i + kStages < count) {
         mbar_arrive_expect_tx(&bars->full[stage], kSpan);
-        bulk_copy_g2s(base, wsrc + static_cast<long long>(i + p.stages) * kSpan, kSpan,
+        bulk_copy_g2s(base, wsrc + static_cast<long long>(i + kStages) * kSpan, kSpan,
                       &bars->full[stage]);
       }
-    }
-    if (++stage == static_cast<uint32_t>(p.stages)) {
-      stage = 0;
-      phase ^= 1u;
-      ++use;
     }
     return true;
   };
@@ -397,27 +419,28 @@ gemv_decode_kernel(const DecodeParams p) {
   // This lane's chain for its two rows: blocks of parity t / 2, low (t even) or high part.
   float acc0 = 0.0f, acc1 = 0.0f;
   int unit = unit_begin, slab_in_unit = 0;
-  for (int i = 0; i < count && ok; ++i) {
+#pragma unroll
+  for (int i = 0; i < (CS > 0 ? CS : count); ++i) {
+    if (!ok) break;
 #pragma unroll
     for (int pr = 0; pr < 4; ++pr) {
       const uint4 b = lds128(frag_at + pr * 512);
       const uint2 lc = lds64(const_at + pr * 32);  // {scale, -k of this lane's part}
       const int nk = static_cast<int>(lc.y);
       int c[4];
-      const uint2 u0 = code[pr][0][0], u1 = code[pr][0][1];
+      const uint2 lo = code[pr][0][0], up = code[pr][0][1];  // K slots 4t.. | 16 + 4t.., two rows each
       if (kQ4) {
-        // -k rides in as the accumulator input of the sums this lane combines first
-        mma_m16n8k32<true>(c, u0.x, u1.x, u0.y, u1.y, b.x, b.y, nk, 0, nk, 0);
-        mma_m16n8k32<true>(c, u0.x & 0xF0F0F0F0u, u1.x & 0xF0F0F0F0u, u0.y & 0xF0F0F0F0u,
-                           u1.y & 0xF0F0F0F0u, b.z, b.w, c[0], c[1], c[2], c[3]);
+        mma_m16n8k32<true>(c, lo.x, lo.y, up.x, up.y, b.x, b.y, 0, 0, 0, 0);
+        mma_m16n8k32<true>(c, lo.x & 0xF0F0F0F0u, lo.y & 0xF0F0F0F0u, up.x & 0xF0F0F0F0u,
+                           up.y & 0xF0F0F0F0u, b.z, b.w, c[0], c[1], c[2], c[3]);
       } else {
-        const uint2 v0 = code[pr][kCodeSets - 1][0], v1 = code[pr][kCodeSets - 1][1];
-        mma_m16n8k32<false>(c, u0.x, u1.x, u0.y, u1.y, b.x, b.y, 0, 0, 0, 0);
-        mma_m16n8k32<false>(c, v0.x, v1.x, v0.y, v1.y, b.z, b.w, c[0], c[1], c[2], c[3]);
+        const uint2 lo2 = code[pr][kCodeSets - 1][0], up2 = code[pr][kCodeSets - 1][1];
+        mma_m16n8k32<false>(c, lo.x, lo.y, up.x, up.y, b.x, b.y, 0, 0, 0, 0);
+        mma_m16n8k32<false>(c, lo2.x, lo2.y, up2.x, up2.y, b.z, b.w, c[0], c[1], c[2], c[3]);
       }
       // this lane's part of its block (low: s0 - k_lo + 256 s1; high: s2 - k_hi + 256 s3)
-      const float f0 = __int2float_rn(c[0] + (c[1] << 8));
-      const float f1 = __int2float_rn(c[2] + (c[3] << 8));
+      const float f0 = __int2float_rn(c[0] + nk + (c[1] << 8));
+      const float f1 = __int2float_rn(c[2] + nk + (c[3] << 8));
       const float scale = __uint_as_float(lc.x);
       const __half2 d = *reinterpret_cast<const __half2*>(&scale_bits[pr]);  // exact conversions
       acc0 = fmaf(f0, __fmul_rn(__low2float(d), scale), acc0);
@@ -479,13 +502,14 @@ gemv_decode_kernel(const DecodeParams p) {
 }
 
 struct DecodePlan {
-  int ksplit, units_per_cta, cta_slabs, stages;
+  int ksplit, cta_slabs;
+  long long free_slots;  // CTAs that fit on the device beside one launch
   size_t smem;
 };
 
 template <int FMT>
-constexpr size_t decode_smem_bytes(int stages, int cta_slabs) {
-  return static_cast<size_t>(stages) * slab_span_bytes(FMT) +
+constexpr size_t decode_smem_bytes(int cta_slabs) {
+  return static_cast<size_t>(kDecodeStages) * slab_span_bytes(FMT) +
          static_cast<size_t>(cta_slabs) * (kFragBytes + kLaneConstBytes) +
          kMaxUnits * kTileRows * sizeof(float) + sizeof(DecodeBarriers) + 64;
 }
@@ -505,26 +529,24 @@ bool plan_decode(const qx_weights* w, const GemvScratch& scratch, int sm_count, 
     const int upc = (units + ks - 1) / ks;
     const int cta_slabs = upc * unit_slabs;
     if (cta_slabs > kMaxCtaSlabs) continue;
-    const int stages = cta_slabs < 2 ? cta_slabs : 2;
-    const size_t smem = decode_smem_bytes<FMT>(stages, cta_slabs);
+    const size_t smem = decode_smem_bytes<FMT>(cta_slabs);
     int per_sm = static_cast<int>(kSmemPerSm / (smem + 1024));
     if (per_sm > kCtasByRegisters) per_sm = kCtasByRegisters;
     if (w->tiles * ks > static_cast<long long>(per_sm) * sm_count) continue;
     plan->ksplit = ks;
-    plan->units_per_cta = upc;
     plan->cta_slabs = cta_slabs;
-    plan->stages = stages;
     plan->smem = smem;
+    plan->free_slots = static_cast<long long>(per_sm) * sm_count - w->tiles * ks;
     found = true;
   }
   return found;
 }
 
-template <int FMT>
-qx_status launch_decode_fmt(const DecodeParams& p, const DecodePlan& plan, long long tiles,
+template <int FMT, int CS>
+qx_status launch_decode_one(const DecodeParams& p, const DecodePlan& plan, long long tiles,
                             cudaStream_t stream) {
   static SmemOptIn opt_in;
-  QX_TRY(opt_in.ensure(gemv_decode_kernel<FMT>, decode_smem_bytes<FMT>(2, kMaxCtaSlabs)));
+  QX_TRY(opt_in.ensure(gemv_decode_kernel<FMT, CS>, decode_smem_bytes<FMT>(kMaxCtaSlabs)));
   cudaLaunchConfig_t config{};
   config.gridDim = dim3(static_cast<unsigned>(tiles * plan.ksplit));
   config.blockDim = dim3(kDecodeThreads);
@@ -541,10 +563,20 @@ qx_status launch_decode_fmt(const DecodeParams& p, const DecodePlan& plan, long 
   attributes[1].val.clusterDim.z = 1;
   config.attrs = attributes;
   config.numAttrs = 2;
-  QX_CUDA_TRY(cudaLaunchKernelEx(&config, gemv_decode_kernel<FMT>, p));
+  QX_CUDA_TRY(cudaLaunchKernelEx(&config, gemv_decode_kernel<FMT, CS>, p));
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
   return QX_STATUS_OK;
+}
+
+template <int FMT>
+qx_status launch_decode_fmt(const DecodeParams& p, const DecodePlan& plan, long long tiles,
+                            cudaStream_t stream) {
+  // every CTA has plan.cta_slabs slabs when K divides evenly
+  const bool even = static_cast<long long>(plan.ksplit) * plan.cta_slabs == p.slabs;
+  if (even && plan.cta_slabs == 2) return launch_decode_one<FMT, 2>(p, plan, tiles, stream);
+  if (even && plan.cta_slabs == 4) return launch_decode_one<FMT, 4>(p, plan, tiles, stream);
+  return launch_decode_one<FMT, 0>(p, plan, tiles, stream);
 }
 
 }  // namespace
@@ -592,9 +624,8 @@ qx_status launch_gemv_decode(const qx_weights* w, const float* x, float* y,
   p.unit_slabs = scratch.unit_slabs;
   p.units_per_tile = scratch.units_per_tile;
   p.ksplit = plan.ksplit;
-  p.units_per_cta = plan.units_per_cta;
-  p.stages = plan.stages;
   p.cta_slabs = plan.cta_slabs;
+  p.prefetch_stride = plan.free_slots > 0 ? static_cast<unsigned>(plan.free_slots) : 0u;
   if (push != nullptr && push->peers > 0) {
     p.peers = push->peers;
     for (int r = 0; r < push->peers; ++r) p.push_cells[r] = push->cells[r];

@@ -29,9 +29,11 @@
 //
 // Work split and summation order. K is cut into units of `unit_slabs` slabs, a function of
 // K alone. A row's result is defined as (sum of its even units) + (sum of its odd units),
-// each in ascending order, every unit accumulated block by block from zero -- so it does
-// not depend on the number of rows, on how rows are sharded over GPUs, on the batch size
-// or on the SM count. The (row tile, unit) sequence is cut into equal contiguous ranges,
+// each in ascending order; a unit's sum comes from four chains over its blocks in ascending
+// order -- the low and the high part of the even blocks and of the odd blocks, qx_gemv.cuh
+// -- so it does not depend on the number of rows, on how rows are sharded over GPUs, on the
+// batch size, on the SM count or on which of the two GEMV kernels ran (a single activation
+// row on a small matrix goes to qx_gemv_decode.cu). The (row tile, unit) sequence is cut into equal contiguous ranges,
 // one per persistent CTA, so every SM streams the same number of bytes. Unit sums go to
 // scratch memory; each thread counts the units it wrote in on a per-row counter and the
 // thread that completes the count adds them in the fixed order: no thread waits for
