@@ -259,7 +259,7 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def cpu_baseline(wl, c):
@@ -316,10 +316,17 @@ def _device_floats(torch, address: int, count: int):
 class TimedBlock:
     """K steps as CUDA graphs (a chunk replayed q times plus a remainder graph), so that the
     host's launch cost stays out of the timed region; falls back to plain launches when
-    capture is refused."""
+    capture is refused. A K below GRAPH_CHUNK is captured `group` blocks to a graph (a graph
+    of a decode loop holds hundreds of kernels; a kernel at the head of a graph cannot
+    overlap with the one in front of it), and run() then runs that many blocks."""
 
     def __init__(self, torch, step, steps: int, period: int, allow_graph: bool = True):
-        self.torch, self.step, self.steps = torch, step, steps
+        self.torch, self.step, self.block_steps = torch, step, steps
+        self.group = max(1, GRAPH_CHUNK // steps) if allow_graph else 1
+        if self.group > 1 and (self.group * steps) % 2:
+            self.group += 1   # keep every run an even number of steps
+        steps = steps * self.group
+        self.steps = steps    # steps per run()
         chunk = min(steps, GRAPH_CHUNK)
         if chunk >= period:
             chunk -= chunk % period
@@ -342,6 +349,7 @@ class TimedBlock:
                 print(f"bench: graph capture failed ({exc!r}); timing plain launches", file=sys.stderr)
                 self.graph_chunk = self.graph_rem = None
                 torch.cuda.synchronize()
+        self.blocks_per_run = self.group
 
     def _capture(self, first: int, count: int):
         graph = self.torch.cuda.CUDAGraph()
@@ -368,8 +376,9 @@ class TimedBlock:
 
 
 def time_block(torch, dist, block: TimedBlock, world: int):
-    """(ms per step, repeats): the block of K steps repeated until the region lasts at least
-    MIN_TIMED_MS, between barriers and synchronisations, CUDA events, max over ranks."""
+    """(ms per step, blocks of K steps timed, ms): the block of K steps repeated until the
+    region lasts at least MIN_TIMED_MS, between barriers and synchronisations, CUDA events,
+    max over ranks."""
     def region(repeats):
         if world > 1:
             dist.barrier()
@@ -395,7 +404,7 @@ def time_block(torch, dist, block: TimedBlock, world: int):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         repeats = int(t.item())
     total = region(repeats)
-    return total / (repeats * block.steps), repeats, total
+    return total / (repeats * block.steps), repeats * block.blocks_per_run, total
 
 
 # ---------------------------------------------------------------------------------------
@@ -503,7 +512,7 @@ def run_single(args):
             line["extra"] = extra_measurements(qx, wl, torch, hbm_peak, bf16_peak)
         except Exception as exc:  # the headline line must still be printed
             line["extra"] = {"error": repr(exc)}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ---------------------------------------------------------------------------------------
@@ -724,7 +733,7 @@ def run_sharded(args):
                     "note": "per step on every rank: x from pinned host memory to the GPU, the "
                             "sharded GEMV with the exchange, the gathered 28672 results back to "
                             "pinned host memory, one stream synchronisation (max over ranks)"},
-            "gpu_launches": launches_per_step * block.steps * repeats,
+            "gpu_launches": launches_per_step * block.block_steps * repeats,
             "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": hbm_peak, "unit": "GB/s",
                          "frac": per_gpu / hbm_peak, "traffic": None,
                          "peak_source": f"{peak_kind} HBM copy bandwidth",
@@ -733,7 +742,7 @@ def run_sharded(args):
             "selfcheck": selfcheck,
             "extra": extra,
         }
-        print(json.dumps(line), flush=True)
+        emit(line)
     dist.destroy_process_group()
 
 
@@ -956,7 +965,26 @@ def _extra_lowbit(qx, wl, torch, hbm_peak):
     return {"lowbit_w4a8": out}
 
 
+_RESULT_FD = None
+
+
+def emit(line: dict):
+    """The one JSON line of the run, on the process's original standard output."""
+    text = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(text.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text)
+
+
 def main():
+    # Libraries loaded below (NCCL among them) write banners to standard output: everything
+    # except the result line goes to standard error.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20000)
@@ -976,8 +1004,8 @@ def main():
         import torch
         torch.cuda.set_device(0)
         hbm_peak, bf16_peak, _ = measured_peaks()
-        print(json.dumps(extra_measurements(entry.load_package(), load_workloads(), torch, hbm_peak,
-                                            bf16_peak, only=args.extra_only)), flush=True)
+        emit(extra_measurements(entry.load_package(), load_workloads(), torch, hbm_peak, bf16_peak,
+                                only=args.extra_only))
     elif int(os.environ.get("WORLD_SIZE", "1")) > 1:
         run_sharded(args)
     else:

@@ -60,7 +60,12 @@ constexpr int kDecodeThreads = 32 * kDecodeWarps;
 constexpr int kDecodeStages = 2;         // ring depth (spans of one slab)
 constexpr int kMaxCtaSlabs = 8;          // slabs of K per CTA (their digits stay in shared memory)
 constexpr int kMaxUnits = 16;            // units per row (gemv_scratch_layout)
-constexpr int kFragBytes = 4 * 32 * 16;  // per slab: [block pair][lane]{first b0, b1, second b0, b1}
+// B-operand fragments of a slab: per block pair 16 entries {first b0, b1, second b0, b1} for
+// the lanes whose fragment is not zero by construction (column block == K-slot block), then
+// zero entries for all other lanes: two of them (entries 16 and 20), so that the zero entry
+// a quarter warp reads lies in the other half of the banks than its four real entries
+constexpr int kFragPairBytes = 21 * 16;
+constexpr int kFragBytes = 4 * kFragPairBytes;
 constexpr int kLaneConstBytes = 4 * 4 * 8;  // per slab: [block pair][lane % 4]{scale, -k}
 constexpr int kMaxPushPeers = 7;
 constexpr int kSmemPerSm = 227 * 1024;
@@ -186,8 +191,8 @@ struct __align__(8) LaneConst {
 // (b = lane / 4, q = lane % 4) handles elements 4q..4q+3 (`lo`) and 16+4q..16+4q+3 (`hi`) of
 // block b -- the same values, rounded the same way, as the quantizer of the tensor-core
 // kernel. In the MMA pair of block pair b / 2 these are the K slots of lane t' =
-// 2 * (b % 2) + q / 2, register q % 2, and digit d is column g' = 4 * (b % 2) + d; every
-// other entry of the fragment area stays zero. The constants go where the consuming lanes
+// 2 * (b % 2) + q / 2, register q % 2, and digit d is column g' = 4 * (b % 2) + d; all
+// other lanes' fragments are zero. The constants go where the consuming lanes
 // look for them: entry [b / 2][2 * (b % 2) + part].
 template <int FMT>
 __device__ __forceinline__ void write_slab_fragments(uint8_t* frags, LaneConst* consts, float4 lo,
@@ -242,14 +247,17 @@ __device__ __forceinline__ void write_slab_fragments(uint8_t* frags, LaneConst* 
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
   }
   const int cb = b & 1;
-  const int t_dst = 2 * cb + (q >> 1), reg = q & 1;
-  uint32_t* entry = reinterpret_cast<uint32_t*>(frags) + (b >> 1) * (32 * 4);
+  const int reg = q & 1;
+  // entry of lane (g' = 4 * cb + d, t' = 2 * cb + q / 2): ((cb * 4 + d) * 2 + q / 2)
+  uint32_t* pair = reinterpret_cast<uint32_t*>(frags + (b >> 1) * kFragPairBytes);
 #pragma unroll
-  for (int d = 0; d < (FMT == QX_FORMAT_Q8_0 ? 3 : 4); ++d) {
-    const int lane_dst = 4 * (4 * cb + d) + t_dst;
-    entry[lane_dst * 4 + reg] = w_lo[d];
-    entry[lane_dst * 4 + 2 + reg] = w_hi[d];
+  for (int d = 0; d < 4; ++d) {  // (q8_0: the fourth digit is zero)
+    uint32_t* entry = pair + ((cb * 4 + d) * 2 + (q >> 1)) * 4;
+    entry[reg] = w_lo[d];
+    entry[2 + reg] = w_hi[d];
   }
+  // the pair's two zero entries: one word each from the eight lanes of the pair
+  pair[(cb == 0 ? 16 : 20) * 4 + q] = 0u;
   if (q == 0) {
     int k_lo = 0, k_hi = 0;
     if (FMT == QX_FORMAT_Q4_0) q4_offset_constants(sum, &k_lo, &k_hi);
@@ -270,7 +278,7 @@ gemv_decode_kernel(const DecodeParams p) {
   constexpr int kCodeSets = kQ4 ? 1 : 2;  // q8_0: the two halves of a block are separate bytes
   constexpr int kStages = kDecodeStages;
   static_assert(kSpan % 2048 == 0, "the lanes' XOR addressing needs stages on 2 KiB boundaries");
-  // [ring: stages x span][fragments: cta_slabs x 2 KiB][constants][unit sums][barriers]
+  // [ring: stages x span][fragments: cta_slabs x kFragBytes][constants][unit sums][barriers]
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* frags = smem + kStages * kSpan;
   LaneConst* consts = reinterpret_cast<LaneConst*>(frags + p.cta_slabs * kFragBytes);
@@ -327,13 +335,6 @@ gemv_decode_kernel(const DecodeParams p) {
         const uint8_t* src = p.panel + (static_cast<long long>(o_tile) * p.slabs + o_begin) * kSpan;
         for (int i = 0; i < o_end - o_begin; ++i) prefetch_l2(src + static_cast<long long>(i) * kSpan, kSpan);
       }
-    }
-  }
-  {
-    // the quantizer writes only the non-zero positions of the fragment area
-    uint4* area = reinterpret_cast<uint4*>(frags);
-    for (int i = threadIdx.x; i < p.cta_slabs * (kFragBytes / 16); i += kDecodeThreads) {
-      area[i] = make_uint4(0u, 0u, 0u, 0u);
     }
   }
   __syncthreads();
@@ -414,7 +415,10 @@ gemv_decode_kernel(const DecodeParams p) {
   __syncthreads();
 
   const uint32_t leader_sums = cluster_map(smem_u32(sums), 0);
-  uint32_t frag_at = smem_u32(frags) + lane * 16;
+  // (lanes whose fragment is zero by construction read the pair's zero entry)
+  // (real entries of quarter warp q = lane / 8: 4 * q .. 4 * q + 3)
+  uint32_t frag_at = smem_u32(frags) +
+                     ((g >> 2) == hi ? ((hi * 4 + (g & 3)) * 2 + (t & 1)) : ((lane >> 3) & 1 ? 16 : 20)) * 16;
   uint32_t const_at = smem_u32(consts) + t * 8;
   // This lane's chain for its two rows: blocks of parity t / 2, low (t even) or high part.
   float acc0 = 0.0f, acc1 = 0.0f;
@@ -424,7 +428,7 @@ gemv_decode_kernel(const DecodeParams p) {
     if (!ok) break;
 #pragma unroll
     for (int pr = 0; pr < 4; ++pr) {
-      const uint4 b = lds128(frag_at + pr * 512);
+      const uint4 b = lds128(frag_at + pr * kFragPairBytes);
       const uint2 lc = lds64(const_at + pr * 32);  // {scale, -k of this lane's part}
       const int nk = static_cast<int>(lc.y);
       int c[4];
@@ -576,6 +580,7 @@ qx_status launch_decode_fmt(const DecodeParams& p, const DecodePlan& plan, long 
   const bool even = static_cast<long long>(plan.ksplit) * plan.cta_slabs == p.slabs;
   if (even && plan.cta_slabs == 2) return launch_decode_one<FMT, 2>(p, plan, tiles, stream);
   if (even && plan.cta_slabs == 4) return launch_decode_one<FMT, 4>(p, plan, tiles, stream);
+  if (even && plan.cta_slabs == 8) return launch_decode_one<FMT, 8>(p, plan, tiles, stream);
   return launch_decode_one<FMT, 0>(p, plan, tiles, stream);
 }
 
