@@ -534,7 +534,7 @@ def run_sharded(args):
     c = wl.CONFIGS[WORKLOAD_SHARDED]
     fmt, n, k = c["fmt"], c["n"], c["k"]
     sweep = tuple(c["m_sweep"])
-    hbm_peak, _, peak_kind = measured_peaks()
+    hbm_peak, bf16_peak, peak_kind = measured_peaks()
     info = qx.device_info()
     begin, rows = sharded.shard_rows(n, world, rank)
     if rows * world != n:
@@ -676,6 +676,10 @@ def run_sharded(args):
                                         "launch": "eager (not captured in a graph)"}
     except Exception as exc:
         extra["error"] = repr(exc)
+    try:
+        extra["sharded_prefill_cfg4"] = _sharded_prefill(qx, wl, torch, dist, world, rank, bf16_peak)
+    except Exception as exc:
+        extra["sharded_prefill_cfg4"] = {"error": repr(exc)}
 
     # ---- end to end: host x in, gathered y out, every step ----------------------------------
     x_pin = torch.from_numpy(wl.activations_f32(1, k, seed=1)).pin_memory()
@@ -744,6 +748,53 @@ def run_sharded(args):
         }
         emit(line)
     dist.destroy_process_group()
+
+
+def _sharded_prefill(qx, wl, torch, dist, world, rank, bf16_peak):
+    """cfg4 (4-bit prefill GEMM, bf16 activations) with the weight rows sharded over the ranks:
+    M cut into chunks of 256 tokens, the NCCL all-gather of a chunk on a second stream under
+    the GEMM of the next (ShardedPrefill). Eager launches, CUDA events around 3 calls, max over
+    ranks. The f32 output is 235 MB, so the exchange moves (N-1)/N of that into every GPU."""
+    sharded = entry._load_file(entry.PKG_NAME + ".sharded", os.path.join(entry.PKG_DIR, "sharded.py"))
+    c = wl.CONFIGS["cfg4_q4_0_prefill"]
+    fmt, m, n, k = c["fmt"], c["m"], c["n"], c["k"]
+    begin, rows = sharded.shard_rows(n, world, rank)
+    blocks = wl.packed_blocks(fmt, n, k, c["d_lo"], c["d_hi"], seed=0)
+    shard = qx.PackedWeights()
+    qx.check(shard.prepare(fmt, blocks, n, k, begin, rows), "prepare shard")
+    del blocks
+    xb = torch.from_numpy(wl.to_bf16_bits(wl.activations_f32(m, k, seed=0)).view(np.int16)).cuda()
+
+    def compute(x_chunk, out):
+        qx.check(shard.qgemm_bf16_dev(x_chunk, out, x_chunk.shape[0]), "sharded prefill GEMM")
+
+    layer = sharded.ShardedPrefill(n, k, compute, chunk_rows=256, device="cuda")
+    local = torch.empty((m, rows), device="cuda")
+
+    def timed(fn, calls=3):
+        fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(calls):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / calls], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_exchange = timed(lambda: layer.forward(xb))
+    ms_kernel = timed(lambda: compute(xb, local))
+    flops = wl.flops_gemm(m, n, k) if hasattr(wl, "flops_gemm") else 2.0 * m * n * k
+    shard.reset()
+    return {"m": m, "n": n, "k": k, "rows_per_rank": rows, "chunk_rows": 256,
+            "ms_with_exchange": ms_exchange, "ms_shard_gemm_only": ms_kernel,
+            "aggregate_tflops": flops / (ms_exchange * 1e-3) / 1e12,
+            "frac_of_measured_bf16_per_gpu": flops / world / (ms_exchange * 1e-3) / 1e12 / bf16_peak,
+            "exchange": "NCCL all_gather_into_tensor per chunk on a second stream",
+            "output_layout": "[chunk][rank][256 tokens][rows_per_rank] f32"}
 
 
 def _time_calls(torch, fn, iters, warm=3):

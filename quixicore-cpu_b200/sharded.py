@@ -117,3 +117,65 @@ class PushAllGather:
         self.qx.check(self.qx.qgemm_push_dev(weights, x, m, self.plan, self.steps),
                       "qx_qgemm_prepacked_push_dev")
         return self.qx.allgather_wait_dev(self.plan, m, self.steps)
+
+
+class ShardedPrefill:
+    """Y[m, n] = X[m, k] . dequant(W)^T for prefill batches with W's rows sharded over the
+    process group (uniform shards), the exchange overlapped with the compute.
+
+    The activation rows are cut into chunks of `chunk_rows`. For chunk c the injected
+    compute(x_chunk [mc, k], out [mc, rows_local]) fills this rank's slice (on GPUs
+    ``PackedWeights.qgemm_bf16_dev``, the tensor-core GEMM); as soon as it is enqueued, the
+    all-gather of that chunk runs on a second stream while the GEMM of chunk c + 1 runs on
+    the first. The gathered result keeps the layout the exchange produces,
+    ``[chunk][rank][row in chunk][row of the rank's shard]`` -- no pass over the output to
+    re-order it; ``assemble`` copies it into a dense [m, n] matrix where a caller wants one.
+    """
+
+    def __init__(self, n: int, k: int, compute: Callable[[torch.Tensor, torch.Tensor], None],
+                 chunk_rows: int = 256, group: Optional[dist.ProcessGroup] = None,
+                 device: str = "cpu"):
+        self.n, self.k, self.chunk = n, k, chunk_rows
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.begin, self.rows = shard_rows(n, self.world, self.rank)
+        if any(shard_rows(n, self.world, r)[1] != self.rows for r in range(self.world)):
+            raise ValueError("ShardedPrefill needs shards of equal size")
+        self.compute = compute
+        self.device = device
+        self.side = torch.cuda.Stream() if str(device).startswith("cuda") else None
+        self.local = self.gathered = None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        m = x.shape[0]
+        if m % self.chunk:
+            raise ValueError("the batch must be a multiple of the chunk size")
+        chunks = m // self.chunk
+        if self.gathered is None or self.gathered.shape[0] != chunks:
+            self.local = torch.empty((chunks, self.chunk, self.rows), dtype=torch.float32,
+                                     device=self.device)
+            self.gathered = torch.empty((chunks, self.world, self.chunk, self.rows),
+                                        dtype=torch.float32, device=self.device)
+        for c in range(chunks):
+            self.compute(x[c * self.chunk:(c + 1) * self.chunk], self.local[c])
+            if self.world == 1:
+                self.gathered[c, 0].copy_(self.local[c])
+            elif self.side is None:
+                dist.all_gather_into_tensor(self.gathered[c].view(-1), self.local[c].view(-1),
+                                            group=self.group)
+            else:
+                done = torch.cuda.Event()
+                done.record()
+                self.side.wait_event(done)
+                with torch.cuda.stream(self.side):
+                    dist.all_gather_into_tensor(self.gathered[c].view(-1), self.local[c].view(-1),
+                                                group=self.group)
+        if self.side is not None and self.world > 1:
+            torch.cuda.current_stream().wait_stream(self.side)
+        return self.gathered
+
+    def assemble(self, gathered: torch.Tensor) -> torch.Tensor:
+        """Dense [m, n] copy of a forward() result."""
+        chunks = gathered.shape[0]
+        return gathered.permute(0, 2, 1, 3).reshape(chunks * self.chunk, self.world * self.rows)

@@ -72,3 +72,42 @@ def test_two_rank_gather_matches_unsharded(tmp_path, case):
     for rank in range(2):
         got = np.load(os.path.join(str(tmp_path), f"y{rank}.npy"))
         assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"rank {rank}"
+
+
+def _prefill_worker(rank, world, port, n, k, m, chunk, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    sharded, wl, oracle = _load()
+    orc = oracle.Oracle()
+    packed = wl.packed_blocks(1, n, k, 0.002, 0.04, seed=19)
+    x = wl.activations_f32(m, k, seed=19)
+    begin, rows = sharded.shard_rows(n, world, rank)
+    shard = packed.reshape(n, -1)[begin:begin + rows].copy().reshape(-1)
+
+    def compute(xt, out):
+        _, y = orc.qgemm(1, shard, np.ascontiguousarray(xt.numpy()), xt.shape[0], rows, k)
+        out.copy_(torch.from_numpy(y))
+
+    layer = sharded.ShardedPrefill(n, k, compute, chunk_rows=chunk)
+    gathered = layer.forward(torch.from_numpy(x))
+    assert tuple(gathered.shape) == (m // chunk, world, chunk, rows)
+    np.save(os.path.join(out_dir, f"p{rank}.npy"), layer.assemble(gathered).numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_rank_chunked_prefill_matches_unsharded(tmp_path):
+    """The M-chunked exchange of the sharded prefill: layout [chunk][rank][row][shard row],
+    assembled result equal to the unsharded product on both ranks."""
+    n, k, m, chunk = 256, 128, 12, 4
+    port = 29500 + (os.getpid() + 777) % 2000
+    mp.spawn(_prefill_worker, args=(2, port, n, k, m, chunk, str(tmp_path)), nprocs=2, join=True)
+    sharded, wl, oracle = _load()
+    packed = wl.packed_blocks(1, n, k, 0.002, 0.04, seed=19)
+    x = wl.activations_f32(m, k, seed=19)
+    _, want = oracle.Oracle().qgemm(1, packed, x, m, n, k)
+    for rank in range(2):
+        got = np.load(os.path.join(str(tmp_path), f"p{rank}.npy"))
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), f"rank {rank}"
+    with pytest.raises(ValueError):
+        sharded.ShardedPrefill(n, k, lambda a, b: None, chunk_rows=5).forward(torch.zeros((12, k)))
