@@ -44,6 +44,34 @@ qx_status h2d(void* dst, const void* src, size_t bytes, cudaStream_t s) {
   QX_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, s));
   return QX_STATUS_OK;
 }
+// Small inputs in pinned (device-addressable) host memory are fetched by a kernel instead of
+// the copy engine: the kernel lets the compute kernel queued behind it start at once
+// (programmatic dependent launch), so that one's weight prefetch runs while the activations
+// cross PCIe; a copy-engine transfer in front of a kernel is a full dependency.
+__global__ void __launch_bounds__(256) stage_in_kernel(const uint4* __restrict__ src,
+                                                       uint4* __restrict__ dst, size_t n16) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i < n16) dst[i] = src[i];
+}
+qx_status stage_in(void* dst, const void* src, size_t bytes, cudaStream_t s) {
+  constexpr size_t kLimit = 256 * 1024;
+  if (bytes > 0 && bytes <= kLimit && bytes % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(src) % 16 == 0 && reinterpret_cast<uintptr_t>(dst) % 16 == 0) {
+    cudaPointerAttributes attributes{};
+    if (cudaPointerGetAttributes(&attributes, src) == cudaSuccess &&
+        attributes.type == cudaMemoryTypeHost && attributes.devicePointer != nullptr) {
+      const size_t n16 = bytes / 16;
+      stage_in_kernel<<<static_cast<unsigned>((n16 + 255) / 256), 256, 0, s>>>(
+          static_cast<const uint4*>(attributes.devicePointer), static_cast<uint4*>(dst), n16);
+      count_launch();
+      QX_CUDA_TRY(cudaGetLastError());
+      return QX_STATUS_OK;
+    }
+    (void)cudaGetLastError();  // unregistered host memory is not an error here
+  }
+  return h2d(dst, src, bytes, s);
+}
 qx_status d2h(void* dst, const void* src, size_t bytes, cudaStream_t s) {
   QX_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, s));
   return QX_STATUS_OK;
@@ -411,7 +439,7 @@ qx_status qx_qgemm_prepacked(const qx_weights* weights, const float* x, float* y
   const size_t y_bytes = static_cast<size_t>(m) * weights->rows * sizeof(float);
   const size_t off_x = st.add(x_bytes), off_y = st.add(y_bytes);
   QX_TRY(ctx->ensure_staging(st.offset));
-  QX_TRY(h2d(st.at(off_x), x, x_bytes, ctx->stream));
+  QX_TRY(stage_in(st.at(off_x), x, x_bytes, ctx->stream));
   // Results go straight to the caller's buffer when the GPU can address it (pinned or
   // registered host memory): the kernel's row finishers write it over PCIe and the copy
   // back is saved. Pageable memory takes the staged copy.

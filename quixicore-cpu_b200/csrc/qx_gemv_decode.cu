@@ -630,7 +630,10 @@ qx_status launch_gemv_decode(const qx_weights* w, const float* x, float* y,
   p.units_per_tile = scratch.units_per_tile;
   p.ksplit = plan.ksplit;
   p.cta_slabs = plan.cta_slabs;
-  p.prefetch_stride = plan.free_slots > 0 ? static_cast<unsigned>(plan.free_slots) : 0u;
+  // (not when a CTA would have to call for more than eight others: few free places)
+  p.prefetch_stride = plan.free_slots * 8 >= w->tiles * plan.ksplit
+                          ? static_cast<unsigned>(plan.free_slots)
+                          : 0u;
   if (push != nullptr && push->peers > 0) {
     p.peers = push->peers;
     for (int r = 0; r < push->peers; ++r) p.push_cells[r] = push->cells[r];
