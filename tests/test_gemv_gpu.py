@@ -89,6 +89,27 @@ def test_batched_rows_equal_single_gemv(qx, orc, wl, fmt):
     assert_close_f32_path(np.stack(singles[:4]), ref, "batched vs oracle")
 
 
+@pytest.mark.parametrize("fmt", [Q8_0, Q4_0])
+@pytest.mark.parametrize("n,k", [(300, 3200), (257, 11008), (128, 416), (640, 1408), (384, 16384)])
+def test_single_row_kernel_equals_batch_rows_on_ragged_shapes(qx, orc, wl, fmt, n, k):
+    """A single activation row runs on the streaming decode kernel, two rows on the
+    persistent tensor-core kernel: same bits, also where K does not fill its last slab, the
+    units do not divide evenly over a tile's CTAs (13 and 15 units) or the rows do not fill
+    the last tile; both within the bound of the reference's f32 path."""
+    packed = wl.packed_blocks(fmt, n, k, *DIST[fmt], seed=29)
+    weights = qx.PackedWeights()
+    assert weights.prepare(fmt, packed, n, k) == qx.OK
+    x = wl.activations_f32(2, k, seed=29)
+    status, pair = weights.qgemm_prepacked(x, 2)
+    assert status == qx.OK, qx.last_error()
+    for r in range(2):
+        status, single = weights.qgemm_prepacked(x[r:r + 1].copy(), 1)
+        assert status == qx.OK, qx.last_error()
+        assert_bit_equal(single[0], pair[r], f"fmt {fmt} {n}x{k} row {r}")
+    _, ref = orc.qgemm(fmt, packed, x, 2, n, k, q4_variant=0)
+    assert_close_f32_path(pair, ref, f"fmt {fmt} {n}x{k} vs oracle")
+
+
 def test_batched_decode_full_config(qx, orc, oracle_mod, wl):
     """The batched decode configuration at its full shape (28672 x 8192 q8_0, M in
     {1, 4, 8, 16, 32}). With 8192 terms per output the reference's own f32 rounding noise
