@@ -131,7 +131,9 @@ struct TcGeom {
   static constexpr int kEpiSplit = MP >= 16 ? 4 : (MP == 8 ? 2 : 1);
   static constexpr int kEpiWarps = 4 * kSets * kEpiSplit;
   static constexpr int kRowsPerThread = MP / kEpiSplit;  // activation rows per epilogue thread
-  static constexpr int kUnpackWarps = kQ4 ? 4 : 0;
+  // (two instead of four at 32 activation rows: the CTA then has 640 threads, which leaves
+  // the epilogue 96 registers instead of 80 and its digit sums and accumulators unspilled)
+  static constexpr int kUnpackWarps = kQ4 ? (MP >= 32 ? 2 : 4) : 0;
   static constexpr int kFirstUnpackWarp = 2 + kEpiWarps;
   static constexpr int kQuantWarp = kFirstUnpackWarp + kUnpackWarps;  // fused only
   static constexpr int kThreads = 32 * (2 + kEpiWarps + kUnpackWarps + (kFused ? kQuantWarps : 0));
@@ -700,20 +702,39 @@ gemv_tc_kernel(const GemvTcParams p) {
             // b / kG, block class b % kG, activation rows split * kMine ..) is fetched at
             // once, the stage handed back, then the items are combined.
             constexpr int kShares = G::kGroupsPerStage * G::kG;
-            uint32_t v[kShares][G::kShareCols];
-#pragma unroll
-            for (int b = 0; b < kShares; ++b) {
+            // With 32 activation rows the CTA has so many threads that 64 registers of digit
+            // sums would spill: the shares are then fetched and combined one after the other
+            // (the stage is handed back after the last fetch either way).
+            constexpr bool kSerial = MP >= 32 && kShares > 1;
+            constexpr int kHeld = kSerial ? 1 : kShares;
+            uint32_t v[kHeld][G::kShareCols];
+            auto fetch = [&](int b) {
               const uint32_t taddr = tmem_base + ts * G::kTCols + (b / G::kG) * G::kN +
                                      (b % G::kG) * (4 * MP) + split * G::kShareCols +
                                      (static_cast<uint32_t>(quarter * 32) << 16);
-              tmem_ld_cols(taddr, v[b]);
+              tmem_ld_cols(taddr, v[kSerial ? 0 : b]);
+            };
+            auto hand_back = [&]() {
+              tmem_ld_wait();
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&bars->tmem_empty[ts]);
+            };
+            if (!kSerial) {
+#pragma unroll
+              for (int b = 0; b < kShares; ++b) fetch(b);
+              hand_back();
             }
-            tmem_ld_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->tmem_empty[ts]);
 #pragma unroll
             for (int b = 0; b < kShares; ++b) {
+              if (kSerial) {
+                fetch(b);
+                if (b == kShares - 1) {
+                  hand_back();
+                } else {
+                  tmem_ld_wait();
+                }
+              }
               const int j = (st * G::kGroupsPerStage + b / G::kG) * G::kG + b % G::kG;
               const float d = half_bits_to_float(
                   static_cast<unsigned short>((scw[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
@@ -722,10 +743,11 @@ gemv_tc_kernel(const GemvTcParams p) {
                 const int m = split * kMine + lm;
                 if (m < p.m) {
                   const int4 xc = xcs[j * MP + m];  // {scale, k_lo, k_hi, -}
-                  const int s0 = static_cast<int>(v[b][4 * lm]);
-                  const int s1 = static_cast<int>(v[b][4 * lm + 1]);
-                  const int s2 = static_cast<int>(v[b][4 * lm + 2]);
-                  const int s3 = static_cast<int>(v[b][4 * lm + 3]);
+                  const uint32_t* sums = v[kSerial ? 0 : b];
+                  const int s0 = static_cast<int>(sums[4 * lm]);
+                  const int s1 = static_cast<int>(sums[4 * lm + 1]);
+                  const int s2 = static_cast<int>(sums[4 * lm + 2]);
+                  const int s3 = static_cast<int>(sums[4 * lm + 3]);
                   const BlockParts parts =
                       kQ4 ? block_parts(s0, s1, s2, s3, xc.y, xc.z) : block_parts(s0, s1, s2);
                   const float term_scale = __fmul_rn(d, __int_as_float(xc.x));
@@ -847,7 +869,7 @@ gemv_tc_kernel(const GemvTcParams p) {
     // ------------------------------ q4_0 high nibbles -------------------------
     // The raw tile is [128 rows][8 blocks x 16 bytes] with swizzled chunks; the tile of the
     // masked bytes (16 * high nibble) has the same layout, so the extraction is position by
-    // position. The four warps take a quarter of every slab each.
+    // position. The warps take an equal share of every slab each.
     const int u = warp - G::kFirstUnpackWarp;
     bool ok = true;
     RingPos raw, work;
@@ -862,15 +884,23 @@ gemv_tc_kernel(const GemvTcParams p) {
           break;
         }
       }
-      const uint4* packed = reinterpret_cast<const uint4*>(smem + raw.slot * G::kSlotBytes) + u * 256;
-      uint4* high = reinterpret_cast<uint4*>(work_ring + work.slot * G::kWorkBytes) + u * 256;
-      uint4 w[8];
+      // 1024 16-byte chunks per tile, an equal share per warp, eight chunks per lane at a time
+      constexpr int kChunksPerWarp = 1024 / (G::kUnpackWarps > 0 ? G::kUnpackWarps : 1);
+      const uint4* packed =
+          reinterpret_cast<const uint4*>(smem + raw.slot * G::kSlotBytes) + u * kChunksPerWarp;
+      uint4* high =
+          reinterpret_cast<uint4*>(work_ring + work.slot * G::kWorkBytes) + u * kChunksPerWarp;
 #pragma unroll
-      for (int h = 0; h < 8; ++h) w[h] = packed[h * 32 + lane];
+      for (int batch = 0; batch < kChunksPerWarp / 256; ++batch) {
+        uint4 w[8];
 #pragma unroll
-      for (int h = 0; h < 8; ++h) {
-        high[h * 32 + lane] = make_uint4(w[h].x & 0xF0F0F0F0u, w[h].y & 0xF0F0F0F0u,
-                                         w[h].z & 0xF0F0F0F0u, w[h].w & 0xF0F0F0F0u);
+        for (int h = 0; h < 8; ++h) w[h] = packed[batch * 256 + h * 32 + lane];
+#pragma unroll
+        for (int h = 0; h < 8; ++h) {
+          high[batch * 256 + h * 32 + lane] =
+              make_uint4(w[h].x & 0xF0F0F0F0u, w[h].y & 0xF0F0F0F0u, w[h].z & 0xF0F0F0F0u,
+                         w[h].w & 0xF0F0F0F0u);
+        }
       }
       fence_proxy_async_smem();
       __syncwarp();
