@@ -131,9 +131,10 @@ struct TcGeom {
   static constexpr int kEpiSplit = MP >= 16 ? 4 : (MP == 8 ? 2 : 1);
   static constexpr int kEpiWarps = 4 * kSets * kEpiSplit;
   static constexpr int kRowsPerThread = MP / kEpiSplit;  // activation rows per epilogue thread
-  // (two instead of four at 32 activation rows: the CTA then has 640 threads, which leaves
-  // the epilogue 96 registers instead of 80 and its digit sums and accumulators unspilled)
-  static constexpr int kUnpackWarps = kQ4 ? (MP >= 32 ? 2 : 4) : 0;
+  // (two instead of four from 16 activation rows on: the CTA then has 640 threads, which
+  // leaves the epilogue 96 registers instead of 80 and its digit sums and accumulators
+  // unspilled)
+  static constexpr int kUnpackWarps = kQ4 ? (MP >= 16 ? 2 : 4) : 0;
   static constexpr int kFirstUnpackWarp = 2 + kEpiWarps;
   static constexpr int kQuantWarp = kFirstUnpackWarp + kUnpackWarps;  // fused only
   static constexpr int kThreads = 32 * (2 + kEpiWarps + kUnpackWarps + (kFused ? kQuantWarps : 0));
