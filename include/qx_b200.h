@@ -238,10 +238,11 @@ QX_API qx_status qx_qgemm_prepacked_bf16_dev(const qx_weights* weights, const ui
  * reference's quantized-matmul API (its row partition is over threads of one process).
  *
  * Instead of a collective after the GEMV, the kernel's row finishers store each result
- * into every other rank's INBOX over NVLink as one 8-byte cell {value, valid tag} (plain
- * peer stores; data and tag travel together, so there are no flags and no fences), and
- * qx_allgather_wait_dev enqueues the receiving kernel: it takes every cell as soon as its
- * tag is set, writes the value into this rank's plain result buffer and clears the cell.
+ * into every other rank's INBOX over NVLink as one 8-byte cell {value, tag of the step}
+ * (plain peer stores; data and tag travel together, so there are no flags and no fences),
+ * and qx_allgather_wait_dev enqueues the receiving kernel: it takes every cell as soon as it
+ * carries the step's tag, writes the value into this rank's plain result buffer and clears
+ * the cell (kernels of several steps can be resident at once; each takes only its own).
  * It polls while this rank's own GEMV is still running and is through a moment after the
  * last slice has arrived; every wait is bounded (2 s). Steps alternate between two halves
  * of the buffers by the parity of `step`, so a rank may be one step ahead of a peer; `step`

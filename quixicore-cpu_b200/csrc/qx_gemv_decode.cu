@@ -84,6 +84,7 @@ struct DecodeParams {
   float* seg_y[qx_weights::kMaxSegments];
   int int8_activations;
   int peers;
+  uint32_t push_tag;
   PushCell* push_cells[kMaxPushPeers];
   unsigned prefetch_stride;  // 0: a CTA calls only its own slabs into L2
 };
@@ -498,7 +499,7 @@ gemv_decode_kernel(const DecodeParams p) {
       for (int r = 0; r < p.peers; ++r) {
         // value and tag in ONE 8-byte store: whoever sees the tag sees the value
         asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p.push_cells[r] + row),
-                     "r"(__float_as_uint(value)), "r"(kPushValid)
+                     "r"(__float_as_uint(value)), "r"(p.push_tag)
                      : "memory");
       }
     }
@@ -643,6 +644,7 @@ qx_status launch_gemv_decode(const qx_weights* w, const float* x, float* y,
                           : 0u;
   if (push != nullptr && push->peers > 0) {
     p.peers = push->peers;
+    p.push_tag = push->tag;
     for (int r = 0; r < push->peers; ++r) p.push_cells[r] = push->cells[r];
   }
   return q4 ? launch_decode_fmt<QX_FORMAT_Q4_0>(p, plan, w->tiles, stream)

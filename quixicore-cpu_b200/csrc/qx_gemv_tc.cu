@@ -181,6 +181,7 @@ struct GemvTcParams {
   float* seg_y[qx_weights::kMaxSegments];
   int int8_activations;               // in-kernel quantizer: the rule of qgemv_w8a8
   int peers;                          // other ranks (0: no push)
+  uint32_t push_tag;                  // tag of this step's cells
   PushCell* push_cells[kMaxPushPeers];  // the other ranks' inboxes, at this rank's slice
 };
 
@@ -625,7 +626,7 @@ gemv_tc_kernel(const GemvTcParams p) {
           for (int r = 0; r < p.peers; ++r) {
             // value and tag in ONE 8-byte store: whoever sees the tag sees the value
             asm volatile("st.relaxed.sys.global.v2.b32 [%0], {%1, %2};" ::"l"(p.push_cells[r] + at),
-                         "r"(__float_as_uint(value)), "r"(kPushValid)
+                         "r"(__float_as_uint(value)), "r"(p.push_tag)
                          : "memory");
           }
         }
@@ -1205,6 +1206,7 @@ qx_status launch_gemv_tc_at(const qx_weights* w, const float* x, const uint8_t* 
       return QX_STATUS_INVALID_ARGUMENT;
     }
     p.peers = push->peers;
+    p.push_tag = push->tag;
     for (int r = 0; r < push->peers; ++r) p.push_cells[r] = push->cells[r];
   }
   if (w->format == QX_FORMAT_Q8_0) {

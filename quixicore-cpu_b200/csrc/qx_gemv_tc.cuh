@@ -23,17 +23,24 @@ struct GemvScratch {
 qx_status gemv_scratch_layout(const qx_weights* w, int m, int sm_count, GemvScratch* out);
 
 // Row-sharded runs: where the kernel also delivers its results to the other ranks. Every
-// finished output is stored as one 8-byte cell {value bits, valid tag} into each peer's
-// inbox (peer-mapped device pointers, already offset to this rank's slice of the step's
-// parity buffer). Data and tag travel in one store, so the receiver needs no flag and the
-// sender no fence: a cell whose tag is set holds its value.
+// finished output is stored as one 8-byte cell {value bits, tag of the step} into each
+// peer's inbox (peer-mapped device pointers, already offset to this rank's slice of the
+// step's parity buffer). Data and tag travel in one store, so the receiver needs no flag and
+// the sender no fence: a cell that carries the step's tag holds the step's value.
 struct PushCell {
   uint32_t value_bits;
-  uint32_t tag;  // kPushValid once written; the receiver clears it when it takes the value
+  uint32_t tag;  // push_tag(step); the receiver of that step clears it when it takes the value
 };
-constexpr uint32_t kPushValid = 1u;
+// Never zero, and different for steps that can be in flight at the same time: with small
+// kernels and programmatic dependent launch the receive kernels of several steps can be
+// resident at once and poll the same cells (steps two apart share a parity buffer); each
+// takes only the cells of its own step.
+inline uint32_t push_tag(long long step) {
+  return static_cast<uint32_t>(static_cast<unsigned long long>(step) & 0x7FFFFFFFull) | 0x80000000u;
+}
 struct GemvPush {
   int peers = 0;
+  uint32_t tag = 0;
   PushCell* cells[7] = {};
 };
 

@@ -15,11 +15,11 @@ namespace qx {
 namespace {
 
 // Receiving side of the fused all-gather. The inbox of a rank holds, per step parity, one
-// 8-byte cell per (sending rank, activation row, weight row): {value bits, valid tag}. The
-// senders (the GEMV kernels of the other ranks) store value and tag together; this kernel
-// takes every cell of the other ranks' slices as soon as its tag is set, writes the value
-// into the plain result buffer and clears the cell for the step after next. No flags, no
-// fences, no step counter in device memory: the tag travels with the data.
+// 8-byte cell per (sending rank, activation row, weight row): {value bits, tag of the step}.
+// The senders (the GEMV kernels of the other ranks) store value and tag together; this
+// kernel takes every cell of the other ranks' slices as soon as it carries this step's tag,
+// writes the value into the plain result buffer and clears the cell. No flags, no fences,
+// no step counter in device memory: the tag travels with the data.
 //
 // It is launched programmatically, so it polls while this rank's own GEMV still runs (its
 // blocks fit beside the GEMV's on the SMs) and is through a moment after the last slice
@@ -27,14 +27,20 @@ namespace {
 // this kernel has completed, this rank's own slice (written by its GEMV) is complete too,
 // which is what the kernel behind it relies on when it reads the gathered results.
 //
-// Why a cell is never overwritten before it is taken: a rank pushes step s + 2 into the
-// parity buffer of step s only after its own receive of step s + 1 has completed; that
-// needed the receiver's push of step s + 1, which the receiver enqueues behind its receive
-// of step s. Every wait is bounded: a cell that does not arrive within the limit makes the
-// thread record role code 31 and stop polling.
+// Why the tag is the step and not a valid bit: the kernels of a step are small, and with
+// programmatic dependent launch the kernels of the following steps start as soon as there
+// is room -- the receive kernels of steps s and s + 2, which share a parity buffer, can be
+// resident at the same time. With a plain valid bit the later one took cells of the
+// earlier step (and the earlier one then waited for them until its limit). Why a cell is
+// never overwritten before it is taken: a rank pushes step s + 2 into the parity buffer of
+// step s only after its own receive of step s + 1 has completed; that needed the
+// receiver's push of step s + 1, which the receiver's GEMV only makes after its receive of
+// step s has completed (it waits for the kernel in front before it reads its activations).
+// Every wait is bounded: a cell that does not arrive within the limit makes the thread
+// record role code 31 and stop polling.
 __global__ void __launch_bounds__(256) allgather_unpack_kernel(PushCell* inbox, float* results,
                                                                long long slice, int world, int rank,
-                                                               int* error,
+                                                               uint32_t step_tag, int* error,
                                                                unsigned long long limit_ns) {
   asm volatile("griddepcontrol.launch_dependents;");
   const long long total = static_cast<long long>(world) * slice;
@@ -48,7 +54,7 @@ __global__ void __launch_bounds__(256) allgather_unpack_kernel(PushCell* inbox, 
                    : "=r"(bits), "=r"(tag)
                    : "l"(inbox + i)
                    : "memory");
-      if (tag == kPushValid) break;
+      if (tag == step_tag) break;  // (cells of other steps are not this kernel's to take)
       if ((spin & 15u) == 15u) {
         const unsigned long long waited = sm100::global_timer_ns() - start;
         if (waited > limit_ns) {
@@ -180,6 +186,7 @@ qx_status qx_qgemm_prepacked_push_dev(const qx_weights* weights, const float* x_
   const long long offset = (step & 1) * plan->world * slice + static_cast<long long>(plan->rank) * slice;
   GemvPush push;
   push.peers = plan->world - 1;
+  push.tag = push_tag(step);
   int slot = 0;
   for (int r = 0; r < plan->world; ++r) {
     if (r == plan->rank) continue;
@@ -214,7 +221,7 @@ qx_status qx_allgather_wait_dev(const qx_push_plan* plan, long long m, long long
   QX_CUDA_TRY(cudaLaunchKernelEx(&config, allgather_unpack_kernel,
                                  static_cast<PushCell*>(plan->inbox_local) + parity_offset,
                                  plan->results_local + parity_offset, slice, plan->world, plan->rank,
-                                 ctx->error_dev, wait_limit_ns()));
+                                 push_tag(step), ctx->error_dev, wait_limit_ns()));
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
   if (results_dev != nullptr) *results_dev = plan->results_local + parity_offset;

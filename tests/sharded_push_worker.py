@@ -101,6 +101,25 @@ def main() -> int:
                     assert torch.equal(history[s, r].view(torch.int32), want_slice.view(torch.int32)), \
                         f"rank {rank} fmt {fmt} m {m}: unsynchronised step {s}, slice of rank {r} differs"
             dist.barrier()
+        # A long captured chain with nothing but the two kernels of every step in it: with
+        # programmatic dependent launch the kernels of several steps are resident at once
+        # (small grids leave room), among them receive kernels of steps two apart, which
+        # poll the same cells. Each must take only the cells of its own step.
+        chain = torch.cuda.CUDAGraph()
+        chain_ptrs = []
+        with torch.cuda.graph(chain):
+            for s in range(200):
+                chain_ptrs.append(gather.step(shard, xs[s % 2], 1))
+        dist.barrier()
+        for _ in range(3):
+            chain.replay()
+        torch.cuda.synchronize()
+        for s in (198, 199):
+            got = device_to_host(chain_ptrs[s], n)
+            assert np.array_equal(got.view(np.uint32), want[s % 2].cpu().numpy().view(np.uint32)), \
+                f"rank {rank} fmt {fmt}: step {s} of the long chain"
+        assert qx.lib.qx_check_device_errors() == qx.OK, f"rank {rank}: {qx.last_error()}"
+        dist.barrier()
         status, _ = qx.qgemv(fmt, packed[: 32 * (k // 32) * (18 if fmt == 1 else 34)],
                              wl.activations_f32(1, k)[0], 32, k)  # host call: reports device errors
         assert status == qx.OK, qx.last_error()
