@@ -520,36 +520,47 @@ constexpr size_t decode_smem_bytes(int cta_slabs) {
 }
 
 // How a handle is cut into CTAs: `ksplit` CTAs (a cluster) per row tile, each with at most
-// kMaxCtaSlabs slabs of K. The kernel only pays off when a whole launch is resident at once
-// (then the next launch's CTAs move in as this launch's leave). Best is a split that gives
-// every SM at most one CTA and most SMs one: the SMs are evenly loaded and the next launch
-// fits beside this one completely (4096 x 4096 q8_0: 128 CTAs of four slabs, 5.4 us, against
-// 6.8 us for 256 CTAs of two). Otherwise the finest split that still fits at once (14336 x
-// 4096 q4_0: 448 CTAs of four slabs; 224 CTAs of eight load the SMs 2 : 1 and take 15 us).
+// kMaxCtaSlabs slabs of K; a whole launch has to be resident at once (the next launch's CTAs
+// then move in as this launch's leave). Among the splits that allow that, measured on
+// matrices of 17 - 66 MB:
+//  - at most four slabs per CTA first: the ring has two stages, every further slab is a
+//    refill at L2 latency in the CTA's critical path (3584 x 8192 q8_0: 6.8 us with four
+//    slabs per CTA, 10.0 us with eight); q8_0 with more than four is left to the persistent
+//    kernel, q4_0 (four CTAs per SM to hide the refills) still wins with eight;
+//  - then a split that leaves room for a whole second launch beside this one (4096 x 4096
+//    q8_0: 5.4 us with 128 CTAs of four slabs, 6.8 us with 256 of two, which fill the SMs);
+//  - then the finest one: more CTAs are more warps per SM (4096 x 4096 q4_0: 4.3 us with
+//    256 CTAs of two slabs, 7.5 us with 128 of four).
 // Larger matrices stay with the persistent tensor-core kernel.
 template <int FMT>
 bool plan_decode(const qx_weights* w, const GemvScratch& scratch, int sm_count, DecodePlan* plan) {
   const int units = scratch.units_per_tile, unit_slabs = scratch.unit_slabs;
   if (units > kMaxUnits) return false;
   constexpr int kCtasByRegisters = FMT == QX_FORMAT_Q4_0 ? 4 : 2;  // __launch_bounds__
-  bool found = false, one_per_sm = false;
+  bool found = false;
+  int best_deep = 0, best_single = 0;  // of the plan found so far: > 4 slabs, no room for a second launch
   for (int ks = 1; ks <= 8; ks *= 2) {
     if (ks > 1 && ks > units) break;
     const int upc = (units + ks - 1) / ks;
     const int cta_slabs = upc * unit_slabs;
     if (cta_slabs > kMaxCtaSlabs) continue;
+    const int deep = cta_slabs > 4 ? 1 : 0;
+    if (deep != 0 && FMT != QX_FORMAT_Q4_0) continue;
     const size_t smem = decode_smem_bytes<FMT>(cta_slabs);
     int per_sm = static_cast<int>(kSmemPerSm / (smem + 1024));
     if (per_sm > kCtasByRegisters) per_sm = kCtasByRegisters;
-    const long long grid = w->tiles * ks;
-    if (grid > static_cast<long long>(per_sm) * sm_count) continue;
-    if (one_per_sm && grid > sm_count) break;  // keep the one-CTA-per-SM split found before
+    const long long grid = w->tiles * ks, slots = static_cast<long long>(per_sm) * sm_count;
+    if (grid > slots) continue;
+    const int single = 2 * grid > slots ? 1 : 0;
+    // ks ascends, so among equals the later (finer) split wins
+    if (found && (deep > best_deep || (deep == best_deep && single > best_single))) continue;
     plan->ksplit = ks;
     plan->cta_slabs = cta_slabs;
     plan->smem = smem;
-    plan->free_slots = static_cast<long long>(per_sm) * sm_count - grid;
+    plan->free_slots = slots - grid;
     found = true;
-    one_per_sm = grid <= sm_count && 4 * grid >= 3LL * sm_count;
+    best_deep = deep;
+    best_single = single;
   }
   return found;
 }
