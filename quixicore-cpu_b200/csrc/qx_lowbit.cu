@@ -26,6 +26,23 @@ namespace {
 
 constexpr int kInt2Row = 0, kInt3Group64 = 1, kInt4Row = 2, kInt4Group = 3;
 
+// Launch with programmatic dependent launch allowed: the kernel may start while the kernel
+// in front of it on the stream still runs and waits for it itself (griddepcontrol.wait).
+template <class... Params, class... Args>
+cudaError_t launch_dependent(void (*kernel)(Params...), unsigned grid, unsigned block,
+                             cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(grid);
+  config.blockDim = dim3(block);
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 // ---- quantize_int8 ---------------------------------------------------------------------
 // One warp per (row, group). max() is exact in any order; the divisions are IEEE like the
 // reference's; nearbyint = round half to even.
@@ -60,6 +77,53 @@ __global__ void __launch_bounds__(256) quantize_int8_kernel(const float* __restr
   }
 }
 
+// Long groups (a whole activation row of a few thousand elements): one block per group, so
+// the row is read with 256 lanes instead of 32. Same values: max and the integer sum do not
+// depend on the order. It lets the kernel behind it (the W4A8 GEMM, which first fetches
+// weights) start at once and waits for the kernel in front itself.
+__global__ void __launch_bounds__(256) quantize_int8_block_kernel(const float* __restrict__ x,
+                                                                  int8_t* __restrict__ codes,
+                                                                  float* __restrict__ scales,
+                                                                  int* __restrict__ code_sums,
+                                                                  long long group_size) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  // x may be the output of the kernel in front, and the codes are read by the GEMM in front
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  __shared__ float warp_max[8];
+  __shared__ int warp_sum[8];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long g = blockIdx.x;
+  const float* in = x + g * group_size;
+  float maximum = 0.0f;
+  for (long long i = threadIdx.x; i < group_size; i += 256) maximum = fmaxf(maximum, fabsf(in[i]));
+#pragma unroll
+  for (int h = 16; h >= 1; h >>= 1) maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, h));
+  if (lane == 0) warp_max[warp] = maximum;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < 8; ++w) maximum = fmaxf(maximum, warp_max[w]);
+  const float scale = __fdiv_rn(maximum, 127.0f);
+  const float inverse = scale > 0.0f ? __fdiv_rn(1.0f, scale) : 0.0f;
+  int sum = 0;
+  for (long long i = threadIdx.x; i < group_size; i += 256) {
+    int q = __float2int_rn(__fmul_rn(in[i], inverse));
+    q = max(-127, min(127, q));
+    codes[g * group_size + i] = static_cast<int8_t>(q);
+    sum += q;
+  }
+#pragma unroll
+  for (int h = 16; h >= 1; h >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, h);
+  if (lane == 0) warp_sum[warp] = sum;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int total = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) total += warp_sum[w];
+    scales[g] = scale;
+    if (code_sums != nullptr) code_sums[g] = total;
+  }
+}
+
 // ---- W4A8 ------------------------------------------------------------------------------
 __device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {
   int d;
@@ -75,6 +139,7 @@ __global__ void __launch_bounds__(256) lowbit_w8a8_kernel(
     const int8_t* __restrict__ x, const float* __restrict__ activation_scales,
     const int* __restrict__ code_sums, float* __restrict__ y, int m, long long n, long long k,
     int vector_ok) {
+  asm volatile("griddepcontrol.launch_dependents;");
   const int lane = threadIdx.x & 31;
   const long long o = blockIdx.x * 8LL + (threadIdx.x >> 5);
   if (o >= n) return;
@@ -83,22 +148,14 @@ __global__ void __launch_bounds__(256) lowbit_w8a8_kernel(
   int acc[MT];
 #pragma unroll
   for (int r = 0; r < MT; ++r) acc[r] = 0;
-  for (long long k0 = lane * 32LL; k0 < k; k0 += 32 * 32) {
-    uint32_t w[4] = {0u, 0u, 0u, 0u};
-    if (vector_ok != 0 && k0 + 32 <= k) {
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(wr + (k0 >> 1)));
-      w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
-    } else {
-      for (int i = 0; i < 16 && (k0 >> 1) + i < row_bytes; ++i) {
-        w[i >> 2] |= static_cast<uint32_t>(wr[(k0 >> 1) + i]) << (8 * (i & 3));
-      }
-    }
+  // 32 weights of this lane (four words) against the activation codes k0 .. k0 + 31 of every row
+  auto consume = [&](const uint32_t (&w)[4], long long k0, bool whole) {
 #pragma unroll
     for (int r = 0; r < MT; ++r) {
       if (r < m) {
         const int8_t* xr = x + static_cast<long long>(r) * k + k0;
         uint32_t xw[8] = {0u, 0u, 0u, 0u, 0u, 0u, 0u, 0u};
-        if (vector_ok != 0 && k0 + 32 <= k) {
+        if (whole) {
           const uint4 a = __ldg(reinterpret_cast<const uint4*>(xr));
           const uint4 b = __ldg(reinterpret_cast<const uint4*>(xr) + 1);
           xw[0] = a.x; xw[1] = a.y; xw[2] = a.z; xw[3] = a.w;
@@ -118,6 +175,44 @@ __global__ void __launch_bounds__(256) lowbit_w8a8_kernel(
           acc[r] = dp4a_us(hi, odd, acc[r]);
         }
       }
+    }
+  };
+  if (vector_ok != 0 && (k & 1023) == 0) {
+    // whole strides of the warp: the weight loads of four strides leave before they are used,
+    // the first four before this kernel waits for the activation codes of the kernel in front
+    bool waited = false;
+    for (long long kb = lane * 32LL; kb < k; kb += 4 * 1024) {
+      uint4 v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (kb + i * 1024 < k) v[i] = __ldg(reinterpret_cast<const uint4*>(wr + ((kb + i * 1024) >> 1)));
+      }
+      if (!waited) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        waited = true;
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (kb + i * 1024 < k) {
+          const uint32_t w[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+          consume(w, kb + i * 1024, true);
+        }
+      }
+    }
+  } else {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (long long k0 = lane * 32LL; k0 < k; k0 += 32 * 32) {
+      uint32_t w[4] = {0u, 0u, 0u, 0u};
+      const bool whole = vector_ok != 0 && k0 + 32 <= k;
+      if (whole) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(wr + (k0 >> 1)));
+        w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w;
+      } else {
+        for (int i = 0; i < 16 && (k0 >> 1) + i < row_bytes; ++i) {
+          w[i >> 2] |= static_cast<uint32_t>(wr[(k0 >> 1) + i]) << (8 * (i & 3));
+        }
+      }
+      consume(w, k0, whole);
     }
   }
   // an odd k leaves the high nibble of the last byte unused: its activation code is zero
@@ -323,8 +418,13 @@ qx_status launch_quantize_int8(const float* x, int8_t* codes, float* scales, int
                                long long rows, long long dim, long long group_size,
                                cudaStream_t stream) {
   const long long groups_total = rows * (dim / group_size);
-  quantize_int8_kernel<<<static_cast<unsigned>((groups_total + 7) / 8), 256, 0, stream>>>(
-      x, codes, scales, code_sums, groups_total, group_size);
+  if (group_size >= 1024 && groups_total <= 65535) {
+    QX_CUDA_TRY(launch_dependent(quantize_int8_block_kernel, static_cast<unsigned>(groups_total), 256,
+                                 stream, x, codes, scales, code_sums, group_size));
+  } else {
+    quantize_int8_kernel<<<static_cast<unsigned>((groups_total + 7) / 8), 256, 0, stream>>>(
+        x, codes, scales, code_sums, groups_total, group_size);
+  }
   count_launch();
   QX_CUDA_TRY(cudaGetLastError());
   return QX_STATUS_OK;
@@ -354,13 +454,13 @@ qx_status launch_lowbit_w8a8(const uint8_t* packed, const float* weight_scales, 
   const unsigned grid = static_cast<unsigned>((n + 7) / 8);
   return for_row_chunks(m, [&](long long r0, int mc) {
     if (mc <= 2) {
-      lowbit_w8a8_kernel<2><<<grid, 256, 0, stream>>>(packed, weight_scales, codes + r0 * k,
-                                                      activation_scales + r0, code_sums + r0,
-                                                      y + r0 * n, mc, n, k, vector_ok);
+      (void)launch_dependent(lowbit_w8a8_kernel<2>, grid, 256, stream, packed, weight_scales,
+                             codes + r0 * k, activation_scales + r0, code_sums + r0, y + r0 * n, mc,
+                             n, k, vector_ok);
     } else {
-      lowbit_w8a8_kernel<8><<<grid, 256, 0, stream>>>(packed, weight_scales, codes + r0 * k,
-                                                      activation_scales + r0, code_sums + r0,
-                                                      y + r0 * n, mc, n, k, vector_ok);
+      (void)launch_dependent(lowbit_w8a8_kernel<8>, grid, 256, stream, packed, weight_scales,
+                             codes + r0 * k, activation_scales + r0, code_sums + r0, y + r0 * n, mc,
+                             n, k, vector_ok);
     }
   });
 }
