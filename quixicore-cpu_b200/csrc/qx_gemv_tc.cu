@@ -751,7 +751,7 @@ gemv_tc_kernel(const GemvTcParams p) {
                   const int s2 = static_cast<int>(sums[4 * lm + 2]);
                   const int s3 = static_cast<int>(sums[4 * lm + 3]);
                   const BlockParts parts =
-                      kQ4 ? block_parts(s0, s1, s2, s3, xc.y, xc.z) : block_parts(s0, s1, s2);
+                      kQ4 ? block_parts_cvt(s0, s1, s2, s3, xc.y, xc.z) : block_parts_cvt(s0, s1, s2);
                   const float term_scale = __fmul_rn(d, __int_as_float(xc.x));
                   acc[2 * (j & 1)][lm] = fmaf(parts.lo, term_scale, acc[2 * (j & 1)][lm]);
                   acc[2 * (j & 1) + 1][lm] = fmaf(parts.hi, term_scale, acc[2 * (j & 1) + 1][lm]);
@@ -790,7 +790,7 @@ gemv_tc_kernel(const GemvTcParams p) {
                 const int s3 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 3) & 31]);
                 const BlockParts parts =
                     G::kFused ? (kQ4 ? block_parts_cvt(s0, s1, s2, s3, xc.y, xc.z) : block_parts_cvt(s0, s1, s2))
-                              : (kQ4 ? block_parts(s0, s1, s2, s3, xc.y, xc.z) : block_parts(s0, s1, s2));
+                              : (kQ4 ? block_parts_cvt(s0, s1, s2, s3, xc.y, xc.z) : block_parts_cvt(s0, s1, s2));
                 const float d = half_bits_to_float(
                     G::kRollGroups
                         ? *reinterpret_cast<const unsigned short*>(
