@@ -169,7 +169,7 @@ __device__ __forceinline__ BlockParts block_parts(int s0, int s1, int s2, int s3
           fmaf(small_int_to_float(s3), 256.0f, small_int_to_float(s2 - k_hi))};
 }
 __device__ __forceinline__ BlockParts block_parts_cvt(int s0, int s1, int s2) {
-  return {__int2float_rn(s0 + (s1 << 8)), small_int_to_float(s2)};
+  return {__int2float_rn(s0 + (s1 << 8)), __int2float_rn(s2)};
 }
 __device__ __forceinline__ BlockParts block_parts_cvt(int s0, int s1, int s2, int s3, int k_lo, int k_hi) {
   return {__int2float_rn(s0 - k_lo + (s1 << 8)), __int2float_rn(s2 - k_hi + (s3 << 8))};
