@@ -743,7 +743,7 @@ gemv_tc_kernel(const GemvTcParams p) {
 #pragma unroll
               for (int lm = 0; lm < kMine; ++lm) {
                 const int m = split * kMine + lm;
-                if (m < p.m) {
+                {  // (rows past the batch have zero digits and a zero scale: no guard needed)
                   const int4 xc = xcs[j * MP + m];  // {scale, k_lo, k_hi, -}
                   const uint32_t* sums = v[kSerial ? 0 : b];
                   const int s0 = static_cast<int>(sums[4 * lm]);
@@ -782,7 +782,7 @@ gemv_tc_kernel(const GemvTcParams p) {
               const int m = split * kMine + lm;
               const int j = (st * G::kGroupsPerStage + column / G::kN) * G::kG +
                             (G::kEpiSplit == 1 ? idx / MP : 0);
-              if (m < p.m) {
+              {  // (rows past the batch have zero digits: their sums are zero, never stored)
                 const int4 xc = xcs[j * MP + m];  // {scale, k_lo, k_hi, -}
                 const int s0 = static_cast<int>(v[(4 * q) >> 5][(4 * q) & 31]);
                 const int s1 = static_cast<int>(v[(4 * q) >> 5][(4 * q + 1) & 31]);

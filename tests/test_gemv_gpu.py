@@ -80,7 +80,7 @@ def test_batched_rows_equal_single_gemv(qx, orc, wl, fmt):
     assert weights.prepare(fmt, packed, n, k) == qx.OK
     x = wl.activations_f32(32, k, seed=3)
     singles = [weights.qgemm_prepacked(x[r:r + 1].copy(), 1)[1][0] for r in range(32)]
-    for m in (1, 4, 8, 16, 32):
+    for m in (1, 2, 3, 4, 5, 8, 13, 16, 21, 32):  # (padded batches among them)
         status, y = weights.qgemm_prepacked(x[:m].copy(), m)
         assert status == qx.OK, qx.last_error()
         for r in range(m):
