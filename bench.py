@@ -824,7 +824,7 @@ def _time_calls(torch, fn, iters, warm=3):
 NCU_DRAM_BYTES_PER_LAUNCH = 33078528
 
 EXTRA_CASES = ("cfg2_w8a8_gemm", "cfg0_q8_0_gemv", "cfg3_q8_0_batched", "cfg4_q4_0_prefill",
-               "w8a32_gemm", "fused_decode", "lowbit_w4a8")
+               "w8a32_gemm", "fused_decode", "lowbit_w4a8", "canonical_projection")
 
 
 def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak, only=None):
@@ -845,6 +845,8 @@ def extra_measurements(qx, wl, torch, hbm_peak, bf16_peak, only=None):
         out.update(_extra_fused(qx, wl, torch, hbm_peak))
     if only in (None, "lowbit_w4a8"):
         out.update(_extra_lowbit(qx, wl, torch, hbm_peak))
+    if only in (None, "canonical_projection"):
+        out.update(_extra_canonical(qx, wl, torch, hbm_peak))
     return out
 
 
@@ -1014,6 +1016,41 @@ def _extra_lowbit(qx, wl, torch, hbm_peak):
         out[f"m{m}_n{n}_k{k}"] = {"us": sec * 1e6, "gbs": nbytes / sec / 1e9,
                                   "frac_of_measured_hbm": nbytes / sec / 1e9 / hbm_peak, "launches": 2}
     return {"lowbit_w4a8": out}
+
+
+def _extra_canonical(qx, wl, torch, hbm_peak):
+    """Canonical prepared projections (kInt8Symmetric with channel scales, kInt4Symmetric with
+    groups of 128) with bf16 activations and outputs, bias and SiLU, at decode batches.
+    Algorithmic bytes: codes + scales + X + bias + Y. Weight copies rotate (> L2)."""
+    out = {}
+    for layout, group, m, n, k in ((qx.INT8_SYMMETRIC, 0, 1, 4096, 4096), (qx.INT8_SYMMETRIC, 0, 1, 14336, 4096),
+                                   (qx.INT8_SYMMETRIC, 0, 8, 4096, 4096), (qx.INT4_SYMMETRIC, 128, 1, 14336, 4096),
+                                   (qx.INT4_SYMMETRIC, 128, 8, 4096, 4096)):
+        rng = np.random.default_rng(n + m)
+        code_bytes = n * k if layout == qx.INT8_SYMMETRIC else n * k // 2
+        groups = 1 if group == 0 else k // group
+        copies = max(3, int(300e6 // code_bytes))
+        handles = []
+        for _ in range(copies):
+            data = rng.integers(0, 256, code_bytes, dtype=np.uint8)
+            scales = rng.uniform(0.001, 0.01, n * groups).astype(np.float32)
+            h = qx.CanonicalWeights()
+            mode = qx.SCALE_CHANNEL if group == 0 else qx.SCALE_GROUP
+            qx.check(h.prepare(qx.canonical_view(layout, mode, n, k, group or k, data, scales)), "prepare")
+            handles.append(h)
+        xd = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).cuda().to(torch.bfloat16)
+        bias = torch.from_numpy(rng.standard_normal(n, dtype=np.float32)).cuda()
+        yd = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
+        sec = _time_calls(torch, lambda i: qx.check(
+            handles[i % copies].qgemm_storage_dev(xd, qx.BF16, yd, qx.BF16, m, bias=bias,
+                                                  activation=qx.ACT_SILU), "canonical"), 4 * copies)
+        nbytes = code_bytes + 4 * n * groups + 2 * m * k + 4 * n + 2 * m * n
+        name = ("int8" if layout == qx.INT8_SYMMETRIC else "int4g128") + f"_m{m}_n{n}_k{k}"
+        out[name] = {"us": sec * 1e6, "gbs": nbytes / sec / 1e9,
+                     "frac_of_measured_hbm": nbytes / sec / 1e9 / hbm_peak, "launches": 1}
+        for h in handles:
+            h.reset()
+    return {"canonical_projection": out}
 
 
 _RESULT_FD = None

@@ -411,6 +411,103 @@ QX_API qx_status qx_quantize_int8_dev(const float* x_dev, int8_t* codes_dev, flo
                                int* code_sums_dev, long long rows, long long dim,
                                long long group_size, void* stream);
 
+/* ---- canonical prepared projections (CanonicalQuantTensor -> prepared weights) ------------
+ * The reference prepares a CanonicalQuantTensor (include/quixicore_cpu/quant_import.h:24-36)
+ * with CpuPackedWeights::prepare(tensor) (src/memory/packed_weights.cpp:280-398) and runs
+ * typed projections on it (include/quixicore_cpu/qgemm.h:29-42). This library serves the two
+ * symmetric integer layouts of that contract:
+ *   kInt8Symmetric  one signed byte per element, rows of `columns` bytes;
+ *   kInt4Symmetric  two elements per byte, the lower K index in the low nibble, a nibble
+ *                   n >= 8 meaning n - 16 (kernels/quantization/qgemm_canonical.cpp:81-84,
+ *                   160-163);
+ * with f32 scales per row / output channel or per (row, group of group_size columns)
+ * (scale_index, qgemm_canonical.cpp:86-115). Enum values are the reference's
+ * (include/quixicore_cpu/quant_contract.h:12-38); every other layout is reported as
+ * QX_STATUS_UNSUPPORTED_FORMAT. */
+enum { QX_CANONICAL_INT4_SYMMETRIC = 0, QX_CANONICAL_INT8_SYMMETRIC = 2 };
+enum { QX_SCALE_NONE = 0, QX_SCALE_TENSOR = 1, QX_SCALE_ROW = 2, QX_SCALE_CHANNEL = 3, QX_SCALE_GROUP = 4 };
+/* FloatStorageType, include/quixicore_cpu/float_storage.h:18 */
+enum { QX_STORAGE_F32 = 0, QX_STORAGE_F16 = 1, QX_STORAGE_BF16 = 2 };
+/* LinearActivation, include/quixicore_cpu/ops.h:56 */
+enum { QX_ACTIVATION_NONE = 0, QX_ACTIVATION_GELU_ERF = 1, QX_ACTIVATION_GELU_TANH = 2,
+       QX_ACTIVATION_SILU = 3, QX_ACTIVATION_RELU2 = 4 };
+
+/* The fields of CanonicalQuantTensor this path reads, as a view over caller-owned HOST
+ * arrays: metadata.layout / scale_mode / logical_rows / logical_columns / group_size,
+ * data, scales. */
+typedef struct qx_canonical_tensor {
+  int layout;             /* QX_CANONICAL_* */
+  int scale_mode;         /* QX_SCALE_ROW, QX_SCALE_CHANNEL or QX_SCALE_GROUP */
+  long long rows;         /* output channels N */
+  long long columns;      /* input features K */
+  long long group_size;   /* columns per scale for QX_SCALE_GROUP; 0 or `columns` otherwise */
+  const uint8_t* data;    /* canonical bytes: rows * columns (int8) or rows * columns / 2 */
+  size_t data_bytes;
+  const float* scales;    /* rows (row / channel) or rows * (columns / group_size) */
+  size_t scale_count;
+} qx_canonical_tensor;
+
+typedef struct qx_canonical_weights qx_canonical_weights;
+
+/* CpuPackedWeights::prepare(const CanonicalQuantTensor&), include/quixicore_cpu/
+ * packed_weights.h (src/memory/packed_weights.cpp:280-398), with the checks of
+ * validate_canonical_quant_tensor (kernels/quantization/quant_import_ref.cpp:401-476) for
+ * these layouts. Uploads codes and scales once; the handle owns its device memory. */
+QX_API qx_status qx_canonical_prepare(const qx_canonical_tensor* tensor,
+                                      qx_canonical_weights** out);
+QX_API void qx_canonical_destroy(qx_canonical_weights* weights);
+
+/* qgemm_prepacked_storage, include/quixicore_cpu/qgemm.h:32-34: Y[m,rows] =
+ * X[m,columns] . dequantize(W)^T with x and y stored as f32, f16 or bf16 (converted at the
+ * kernel boundary, f32 arithmetic in between). x_count / y_count are the element counts of
+ * FloatStorageInput / FloatStorageOutput and must equal m * columns / m * rows. HOST
+ * pointers. Results agree with the reference within the tolerance of its own test
+ * (|a - e| <= 4e-5 * (1 + |e|), tests/correctness/test_quant_projection_matrix.cpp:54-57):
+ * the reference's summation order differs between its ISA variants, so there is no single
+ * bit pattern to match. */
+QX_API qx_status qx_qgemm_prepacked_storage(const qx_canonical_weights* weights, const void* x,
+                                            int x_type, long long x_count, void* y, int y_type,
+                                            long long y_count, long long m);
+/* qgemm_prepacked_epilogue_storage, include/quixicore_cpu/qgemm.h:37-42: the same with an
+ * output-channel bias (may be NULL) added and the activation applied before the store
+ * (store_projection_output, qgemm_canonical.cpp:2570-2581). */
+QX_API qx_status qx_qgemm_prepacked_epilogue_storage(const qx_canonical_weights* weights,
+                                                     const void* x, int x_type, long long x_count,
+                                                     const float* bias, void* y, int y_type,
+                                                     long long y_count, long long m,
+                                                     int activation);
+/* DEVICE pointers and a stream; allocates nothing and does not synchronise. */
+QX_API qx_status qx_qgemm_prepacked_epilogue_storage_dev(const qx_canonical_weights* weights,
+                                                         const void* x_dev, int x_type,
+                                                         const float* bias_dev, void* y_dev,
+                                                         int y_type, long long m, int activation,
+                                                         void* stream);
+QX_API const char* qx_canonical_gemm_variant(void);
+
+/* import_smoothquant_w8a8, include/quixicore_cpu/quant_import.h:117-133
+ * (kernels/quantization/quant_import_ref.cpp:1051-1116): signed int8 weights [rows,columns]
+ * with one f32 scale per output channel become a kInt8Symmetric tensor with channel scales
+ * and group_size = columns; the per-row sums of the codes (the correction term of the
+ * asymmetric W8A8 route) are copied when supplied and computed otherwise. Host-side format
+ * conversion, no device work: *tensor becomes a view of the source arrays and
+ * row_sums_out[rows] is filled. */
+typedef struct qx_smoothquant_source {
+  const int8_t* weights;
+  size_t weight_count;
+  const float* weight_scales;
+  size_t weight_scale_count;
+  const float* activation_scales;
+  size_t activation_scale_count;
+  const int* activation_zero_points;
+  size_t activation_zero_point_count;
+  const int32_t* row_sums;
+  size_t row_sum_count;
+  long long rows;
+  long long columns;
+} qx_smoothquant_source;
+QX_API qx_status qx_import_smoothquant_w8a8(const qx_smoothquant_source* source,
+                                            qx_canonical_tensor* tensor, int32_t* row_sums_out);
+
 /* ---- threading: set_num_threads / num_threads, include/quixicore_cpu/threading.h:11-12.
  * The fork-join pool is replaced by CUDA streams; these are kept so callers link. The
  * value is stored and returned, results never depend on it. */

@@ -54,6 +54,20 @@ def packed_size(fmt: int, n: int, k: int) -> int:
     return n * (k // 32) * BLOCK_BYTES[fmt]
 
 
+# storage element types of FloatStorageType (f16 / bf16 travel as their 16-bit patterns)
+STORAGE_DTYPES = {0: np.float32, 1: np.uint16, 2: np.uint16}
+
+
+class CanonicalTensor:
+    """The fields of a CanonicalQuantTensor the projections read."""
+
+    def __init__(self, layout, scale_mode, rows, columns, group_size, data, scales):
+        self.layout, self.scale_mode = layout, scale_mode
+        self.rows, self.columns, self.group_size = rows, columns, group_size
+        self.data = np.ascontiguousarray(data, np.uint8).reshape(-1)
+        self.scales = np.ascontiguousarray(scales, np.float32).reshape(-1)
+
+
 class Oracle:
     """Plain-C restatement (qx_oracle.c)."""
 
@@ -92,6 +106,14 @@ class Oracle:
         L.qxo_lowbit_gemm.argtypes = [C.c_int, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll]
         L.qxo_lowbit_gemm_f64.argtypes = [C.c_int, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _ll]
         L.qxo_lowbit_gemm_w8a8.argtypes = [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _vp, _vp]
+        L.qxo_quantize_canonical.argtypes = [C.c_int, _vp, _ll, _ll, _ll, _vp, _vp,
+                                             C.POINTER(C.c_int), C.POINTER(_ll)]
+        L.qxo_canonical_gemm.argtypes = [C.c_int, C.c_int, _ll, _ll, _ll, _vp, C.c_size_t, _vp,
+                                         C.c_size_t, _vp, C.c_int, _ll, _vp, _vp, C.c_int, _ll,
+                                         _ll, C.c_int]
+        L.qxo_canonical_gemm_f64.argtypes = [C.c_int, _ll, _ll, _ll, _vp, _vp, _vp, C.c_int, _vp, _ll]
+        L.qxo_import_smoothquant_row_sums.argtypes = [_vp, C.c_size_t, _vp, C.c_size_t, _vp,
+                                                      C.c_size_t, _vp, C.c_size_t, _ll, _ll, _vp]
 
     # scalar conversions
     def fp16_to_fp32(self, h):
@@ -215,6 +237,44 @@ class Oracle:
         return status, panel[:max(size, 0)]
 
 
+    # ---- canonical prepared projections (kInt8Symmetric = 2, kInt4Symmetric = 0)
+    def quantize_canonical(self, layout, values, rows, columns, group_size=0):
+        """-> status, CanonicalTensor"""
+        data = np.zeros(rows * columns // (1 if layout == 2 else 2), np.uint8)
+        groups = columns // (group_size or columns)
+        scales = np.zeros(rows * groups, np.float32)
+        mode, stored = C.c_int(0), _ll(0)
+        status = self.lib.qxo_quantize_canonical(layout, _ptr(values), rows, columns, group_size,
+                                                 _ptr(data), _ptr(scales), C.byref(mode),
+                                                 C.byref(stored))
+        return status, CanonicalTensor(layout, mode.value, rows, columns, stored.value, data, scales)
+
+    def canonical_gemm(self, t, x, x_type, m, bias=None, y_type=0, activation=0,
+                       x_count=None, y_count=None):
+        y = np.zeros(max(m, 1) * t.rows, STORAGE_DTYPES.get(y_type, np.float32))
+        status = self.lib.qxo_canonical_gemm(
+            t.layout, t.scale_mode, t.rows, t.columns, t.group_size, _ptr(t.data), t.data.size,
+            _ptr(t.scales), t.scales.size, _ptr(x), x_type,
+            m * t.columns if x_count is None else x_count, _ptr(bias), _ptr(y), y_type,
+            m * t.rows if y_count is None else y_count, m, activation)
+        return status, y.reshape(max(m, 1), t.rows)
+
+    def canonical_gemm_f64(self, t, x, x_type, m):
+        y = np.zeros((m, t.rows), np.float64)
+        self.lib.qxo_canonical_gemm_f64(t.layout, t.rows, t.columns, t.scales.size // t.rows,
+                                        _ptr(t.data), _ptr(t.scales), _ptr(x), x_type, _ptr(y), m)
+        return y
+
+    def import_smoothquant_row_sums(self, weights, weight_scales, activation_scales, rows, columns,
+                                    row_sums=None):
+        out = np.zeros(rows, np.int32)
+        status = self.lib.qxo_import_smoothquant_row_sums(
+            _ptr(weights), weights.size, _ptr(weight_scales), weight_scales.size,
+            _ptr(activation_scales), activation_scales.size, _ptr(row_sums),
+            0 if row_sums is None else row_sums.size, rows, columns, _ptr(out))
+        return status, out
+
+
 class Reference:
     """The unmodified reference library behind oracle/ref_shim.cpp."""
 
@@ -232,6 +292,19 @@ class Reference:
         L.qxref_int8_gemm.argtypes = [_vp] * 7 + [_ll, _ll, _ll, C.c_int]
         L.qxref_qgemm_w8a8.argtypes = [_vp] * 5 + [_ll, _ll, _ll]
         L.qxref_qgemm_w8a32.argtypes = [_vp] * 4 + [_ll, _ll, _ll]
+        L.qxref_quantize_canonical.argtypes = [C.c_int, _vp, _ll, _ll, _ll, _vp, C.c_size_t, _vp,
+                                               C.c_size_t, C.POINTER(C.c_size_t),
+                                               C.POINTER(C.c_size_t), C.POINTER(C.c_int),
+                                               C.POINTER(_ll)]
+        L.qxref_canonical_validate.argtypes = [C.c_int, C.c_int, _ll, _ll, _ll, _vp, C.c_size_t,
+                                               _vp, C.c_size_t]
+        L.qxref_canonical_gemm.argtypes = [C.c_int, C.c_int, _ll, _ll, _ll, _vp, C.c_size_t, _vp,
+                                           C.c_size_t, _vp, C.c_int, _ll, _vp, _vp, C.c_int, _ll,
+                                           _ll, C.c_int]
+        L.qxref_import_smoothquant.argtypes = [_vp, C.c_size_t, _vp, C.c_size_t, _vp, C.c_size_t,
+                                               _vp, C.c_size_t, _vp, C.c_size_t, _ll, _ll, _vp, _vp,
+                                               _vp, C.POINTER(C.c_int), C.POINTER(C.c_int),
+                                               C.POINTER(_ll)]
         L.qxref_packed_create.argtypes = [C.c_int, _vp, _ll, _ll, C.c_int, C.POINTER(_vp)]
         L.qxref_packed_destroy.argtypes = [_vp]
         L.qxref_packed_destroy.restype = None
@@ -332,6 +405,48 @@ class Reference:
         y = np.zeros((m, n), np.float32)
         status = self.lib.qxref_lowbit_gemm_w8a8(_ptr(packed), _ptr(scales), _ptr(x), _ptr(y), m, n, k)
         return status, y
+
+    # ---- canonical prepared projections
+    def quantize_canonical(self, layout, values, rows, columns, group_size=0):
+        data = np.zeros(rows * columns, np.uint8)
+        scales = np.zeros(rows * columns, np.float32)
+        nb, ns, mode, stored = C.c_size_t(0), C.c_size_t(0), C.c_int(0), _ll(0)
+        status = self.lib.qxref_quantize_canonical(
+            layout, _ptr(values), rows, columns, group_size, _ptr(data), data.size, _ptr(scales),
+            scales.size, C.byref(nb), C.byref(ns), C.byref(mode), C.byref(stored))
+        return status, CanonicalTensor(layout, mode.value, rows, columns, stored.value,
+                                       data[:nb.value].copy(), scales[:ns.value].copy())
+
+    def canonical_validate(self, t, data_bytes=None, scale_count=None):
+        return self.lib.qxref_canonical_validate(
+            t.layout, t.scale_mode, t.rows, t.columns, t.group_size, _ptr(t.data),
+            t.data.size if data_bytes is None else data_bytes, _ptr(t.scales),
+            t.scales.size if scale_count is None else scale_count)
+
+    def canonical_gemm(self, t, x, x_type, m, bias=None, y_type=0, activation=0,
+                       x_count=None, y_count=None):
+        y = np.zeros(max(m, 1) * t.rows, STORAGE_DTYPES.get(y_type, np.float32))
+        status = self.lib.qxref_canonical_gemm(
+            t.layout, t.scale_mode, t.rows, t.columns, t.group_size, _ptr(t.data), t.data.size,
+            _ptr(t.scales), t.scales.size, _ptr(x), x_type,
+            m * t.columns if x_count is None else x_count, _ptr(bias), _ptr(y), y_type,
+            m * t.rows if y_count is None else y_count, m, activation)
+        return status, y.reshape(max(m, 1), t.rows)
+
+    def import_smoothquant(self, weights, weight_scales, activation_scales, rows, columns,
+                           zero_points=None, row_sums=None):
+        data = np.zeros(rows * columns, np.uint8)
+        scales = np.zeros(rows, np.float32)
+        sums = np.zeros(rows, np.int32)
+        layout, mode, group = C.c_int(-1), C.c_int(-1), _ll(-1)
+        status = self.lib.qxref_import_smoothquant(
+            _ptr(weights), weights.size, _ptr(weight_scales), weight_scales.size,
+            _ptr(activation_scales), activation_scales.size, _ptr(zero_points),
+            0 if zero_points is None else zero_points.size, _ptr(row_sums),
+            0 if row_sums is None else row_sums.size, rows, columns, _ptr(data), _ptr(scales),
+            _ptr(sums), C.byref(layout), C.byref(mode), C.byref(group))
+        return status, CanonicalTensor(layout.value, mode.value, rows, columns, group.value, data,
+                                       scales), sums
 
     def set_num_threads(self, n):
         self.lib.qxref_set_num_threads(int(n))

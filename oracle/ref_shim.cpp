@@ -218,3 +218,124 @@ const char* qxref_lowbit_gemm_variant(int format) {
 }
 
 }  // extern "C"
+
+// ---- canonical prepared projections: CanonicalQuantTensor -> CpuPackedWeights::prepare ->
+// qgemm_prepacked_epilogue_storage, the canonical quantiser and the SmoothQuant importer ---
+#include <algorithm>
+#include <vector>
+
+#include "quixicore_cpu/ops.h"
+#include "quixicore_cpu/quant_import.h"
+
+extern "C" {
+
+// quantize_canonical for a layout with f32 scales (int8 / int4 symmetric): writes the
+// canonical bytes, the scale table and the metadata the projection needs.
+int qxref_quantize_canonical(int layout, const float* values, long long rows,
+                             long long columns, long long group_size,
+                             uint8_t* data, size_t data_capacity, float* scales,
+                             size_t scale_capacity, size_t* data_bytes,
+                             size_t* scale_count, int* scale_mode,
+                             long long* stored_group_size) {
+  qc::CanonicalQuantTensor tensor;
+  const qc::Status status = qc::quantize_canonical(
+      {values, qc::FloatStorageType::kF32, rows * columns}, rows, columns,
+      static_cast<qc::CanonicalQuantLayout>(layout), group_size, &tensor);
+  if (status != qc::Status::kOk) return static_cast<int>(status);
+  if (tensor.data.size() > data_capacity || tensor.scales.size() > scale_capacity) {
+    return static_cast<int>(qc::Status::kInvalidShape);
+  }
+  std::copy(tensor.data.begin(), tensor.data.end(), data);
+  std::copy(tensor.scales.begin(), tensor.scales.end(), scales);
+  *data_bytes = tensor.data.size();
+  *scale_count = tensor.scales.size();
+  *scale_mode = static_cast<int>(tensor.metadata.scale_mode);
+  *stored_group_size = tensor.metadata.group_size;
+  return 0;
+}
+
+static qc::Status make_tensor(int layout, int scale_mode, long long rows,
+                              long long columns, long long group_size,
+                              const uint8_t* data, size_t data_bytes,
+                              const float* scales, size_t scale_count,
+                              qc::CanonicalQuantTensor* tensor) {
+  tensor->metadata.layout = static_cast<qc::CanonicalQuantLayout>(layout);
+  tensor->metadata.logical_rows = rows;
+  tensor->metadata.logical_columns = columns;
+  tensor->metadata.group_size = group_size;
+  tensor->metadata.scale_mode = static_cast<qc::QuantScaleMode>(scale_mode);
+  tensor->metadata.scale_encoding = qc::QuantScaleEncoding::kFP32;
+  tensor->metadata.scale_count = scale_count;
+  tensor->data.assign(data, data + data_bytes);
+  tensor->scales.assign(scales, scales + scale_count);
+  return qc::validate_canonical_quant_tensor(*tensor);
+}
+
+// validate_canonical_quant_tensor on a tensor assembled from plain arrays
+int qxref_canonical_validate(int layout, int scale_mode, long long rows,
+                             long long columns, long long group_size,
+                             const uint8_t* data, size_t data_bytes,
+                             const float* scales, size_t scale_count) {
+  qc::CanonicalQuantTensor tensor;
+  return static_cast<int>(make_tensor(layout, scale_mode, rows, columns, group_size,
+                                      data, data_bytes, scales, scale_count, &tensor));
+}
+
+// CpuPackedWeights::prepare(tensor) + qgemm_prepacked_epilogue_storage
+int qxref_canonical_gemm(int layout, int scale_mode, long long rows,
+                         long long columns, long long group_size,
+                         const uint8_t* data, size_t data_bytes,
+                         const float* scales, size_t scale_count, const void* x,
+                         int x_type, long long x_count, const float* bias, void* y,
+                         int y_type, long long y_count, long long m,
+                         int activation) {
+  qc::CanonicalQuantTensor tensor;
+  qc::Status status = make_tensor(layout, scale_mode, rows, columns, group_size, data,
+                                  data_bytes, scales, scale_count, &tensor);
+  if (status != qc::Status::kOk) return static_cast<int>(status);
+  qc::CpuPackedWeights prepared;
+  status = prepared.prepare(tensor);
+  if (status != qc::Status::kOk) return static_cast<int>(status);
+  return static_cast<int>(qc::qgemm_prepacked_epilogue_storage(
+      prepared, {x, static_cast<qc::FloatStorageType>(x_type), x_count}, bias,
+      {y, static_cast<qc::FloatStorageType>(y_type), y_count}, m,
+      static_cast<qc::LinearActivation>(activation)));
+}
+
+// import_smoothquant_w8a8: returns the tensor's fields through plain arrays
+int qxref_import_smoothquant(const int8_t* weights, size_t weight_count,
+                             const float* weight_scales, size_t weight_scale_count,
+                             const float* activation_scales,
+                             size_t activation_scale_count,
+                             const int* activation_zero_points,
+                             size_t activation_zero_point_count,
+                             const int32_t* row_sums, size_t row_sum_count,
+                             long long rows, long long columns, uint8_t* data_out,
+                             float* scales_out, int32_t* row_sums_out, int* layout,
+                             int* scale_mode, long long* group_size) {
+  qc::SmoothQuantW8A8Source source;
+  source.weights = weights;
+  source.weight_count = weight_count;
+  source.weight_scales = weight_scales;
+  source.weight_scale_count = weight_scale_count;
+  source.activation_scales = activation_scales;
+  source.activation_scale_count = activation_scale_count;
+  source.activation_zero_points = activation_zero_points;
+  source.activation_zero_point_count = activation_zero_point_count;
+  source.row_sums = row_sums;
+  source.row_sum_count = row_sum_count;
+  source.rows = rows;
+  source.columns = columns;
+  qc::CanonicalQuantTensor tensor;
+  const qc::Status status = qc::import_smoothquant_w8a8(source, &tensor);
+  if (status != qc::Status::kOk) return static_cast<int>(status);
+  std::copy(tensor.data.begin(), tensor.data.end(), data_out);
+  std::copy(tensor.scales.begin(), tensor.scales.end(), scales_out);
+  std::copy(tensor.row_sums.begin(), tensor.row_sums.end(), row_sums_out);
+  *layout = static_cast<int>(tensor.metadata.layout);
+  *scale_mode = static_cast<int>(tensor.metadata.scale_mode);
+  *group_size = tensor.metadata.group_size;
+  return 0;
+}
+
+}  // extern "C"

@@ -51,6 +51,22 @@ class PushPlan(C.Structure):
                 ("inbox_peer", C.c_void_p * 8)]
 
 
+class CanonicalTensorView(C.Structure):
+    """qx_canonical_tensor of include/qx_b200.h."""
+    _fields_ = [("layout", C.c_int), ("scale_mode", C.c_int), ("rows", _ll), ("columns", _ll),
+                ("group_size", _ll), ("data", _vp), ("data_bytes", _sz), ("scales", _vp),
+                ("scale_count", _sz)]
+
+
+class SmoothQuantSource(C.Structure):
+    """qx_smoothquant_source of include/qx_b200.h."""
+    _fields_ = [("weights", _vp), ("weight_count", _sz), ("weight_scales", _vp),
+                ("weight_scale_count", _sz), ("activation_scales", _vp),
+                ("activation_scale_count", _sz), ("activation_zero_points", _vp),
+                ("activation_zero_point_count", _sz), ("row_sums", _vp), ("row_sum_count", _sz),
+                ("rows", _ll), ("columns", _ll)]
+
+
 class DeviceInfo(C.Structure):
     _fields_ = [("device", C.c_int), ("sm_major", C.c_int), ("sm_minor", C.c_int),
                 ("sm_count", C.c_int), ("max_smem_per_block", C.c_int), ("l2_bytes", C.c_int),
@@ -106,6 +122,14 @@ def _load():
         "qx_lowbit_gemm_w8a8_dev": [_vp, _vp, _vp, _vp, _vp, _ll, _ll, _ll, _vp],
         "qx_quantize_int8": [_vp, _vp, _vp, _ll, _ll, _ll],
         "qx_quantize_int8_dev": [_vp, _vp, _vp, _vp, _ll, _ll, _ll, _vp],
+        "qx_canonical_prepare": [C.POINTER(CanonicalTensorView), C.POINTER(_vp)],
+        "qx_qgemm_prepacked_storage": [_vp, _vp, C.c_int, _ll, _vp, C.c_int, _ll, _ll],
+        "qx_qgemm_prepacked_epilogue_storage": [_vp, _vp, C.c_int, _ll, _vp, _vp, C.c_int, _ll,
+                                                _ll, C.c_int],
+        "qx_qgemm_prepacked_epilogue_storage_dev": [_vp, _vp, C.c_int, _vp, _vp, C.c_int, _ll,
+                                                    C.c_int, _vp],
+        "qx_import_smoothquant_w8a8": [C.POINTER(SmoothQuantSource),
+                                       C.POINTER(CanonicalTensorView), _vp],
         "qx_peer_alloc": [_sz, C.POINTER(_vp), _vp],
         "qx_peer_open": [_vp, C.POINTER(_vp)],
         "qx_peer_close": [_vp],
@@ -119,7 +143,7 @@ def _load():
         fn.restype = C.c_int
     for name in ("qx_last_error_string", "qx_qgemv_variant", "qx_int8_gemm_variant",
                  "qx_qgemm_w8a32_variant", "qx_qgemv_w8a8_variant", "qx_lowbit_gemm_variant",
-                 "qx_lowbit_gemm_w8a8_variant"):
+                 "qx_lowbit_gemm_w8a8_variant", "qx_canonical_gemm_variant"):
         getattr(lib, name).restype = C.c_char_p
     lib.qx_qgemv_variant.argtypes = [C.c_int]
     lib.qx_qgemv_w8a8_variant.argtypes = [C.c_int]
@@ -128,6 +152,8 @@ def _load():
     lib.qx_lowbit_w8a8_scratch_bytes.restype = _sz
     lib.qx_weights_destroy.argtypes = [_vp]
     lib.qx_weights_destroy.restype = None
+    lib.qx_canonical_destroy.argtypes = [_vp]
+    lib.qx_canonical_destroy.restype = None
     lib.qx_workspace_destroy.argtypes = [_vp]
     lib.qx_workspace_destroy.restype = None
     lib.qx_workspace_capacity.argtypes = [_vp]
@@ -386,6 +412,87 @@ class PackedWeights:
         ldy = y.shape[-1] if ldy is None else ldy
         return lib.qx_qgemm_prepacked_bf16_dev(self.handle, _dev(x_bf16), _vp(y.data_ptr()), m,
                                                ldy, None, _stream())
+
+
+# ---- canonical prepared projections (CanonicalQuantTensor -> prepare -> typed projection) ----
+INT4_SYMMETRIC, INT8_SYMMETRIC = 0, 2
+SCALE_ROW, SCALE_CHANNEL, SCALE_GROUP = 2, 3, 4
+F32, F16, BF16 = 0, 1, 2
+STORAGE_DTYPES = {F32: np.float32, F16: np.uint16, BF16: np.uint16}
+ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, ACT_RELU2 = range(5)
+
+
+def canonical_view(layout, scale_mode, rows, columns, group_size, data, scales,
+                   data_bytes=None, scale_count=None) -> CanonicalTensorView:
+    """A qx_canonical_tensor over numpy arrays (the arrays must outlive the view)."""
+    return CanonicalTensorView(layout, scale_mode, rows, columns, group_size, _np(data),
+                               (0 if data is None else data.size) if data_bytes is None else data_bytes,
+                               _np(scales),
+                               (0 if scales is None else scales.size) if scale_count is None else scale_count)
+
+
+class CanonicalWeights:
+    """Device-resident prepared canonical tensor (CpuPackedWeights::prepare(tensor))."""
+
+    def __init__(self):
+        self.handle = _vp()
+        self.rows = self.columns = 0
+
+    def prepare(self, view: CanonicalTensorView) -> int:
+        self.reset()
+        status = lib.qx_canonical_prepare(C.byref(view), C.byref(self.handle))
+        if status == OK:
+            self.rows, self.columns = view.rows, view.columns
+        return status
+
+    def ready(self) -> bool:
+        return bool(self.handle)
+
+    def reset(self) -> None:
+        if self.handle:
+            lib.qx_canonical_destroy(self.handle)
+        self.handle = _vp()
+
+    def __del__(self):
+        try:
+            self.reset()
+        except Exception:
+            pass
+
+    def qgemm_storage(self, x, x_type, m, y_type=F32, bias=None, activation=None,
+                      x_count=None, y_count=None):
+        """qgemm_prepacked_storage (activation None) / qgemm_prepacked_epilogue_storage."""
+        y = np.zeros(max(m, 1) * max(self.rows, 1), STORAGE_DTYPES.get(y_type, np.float32))
+        x_count = m * self.columns if x_count is None else x_count
+        y_count = m * self.rows if y_count is None else y_count
+        if activation is None and bias is None:
+            status = lib.qx_qgemm_prepacked_storage(self.handle, _np(x), x_type, x_count, _np(y),
+                                                    y_type, y_count, m)
+        else:
+            status = lib.qx_qgemm_prepacked_epilogue_storage(
+                self.handle, _np(x), x_type, x_count, _np(bias), _np(y), y_type, y_count, m,
+                ACT_NONE if activation is None else activation)
+        return status, y.reshape(max(m, 1), max(self.rows, 1))
+
+    def qgemm_storage_dev(self, x, x_type, y, y_type, m, bias=None, activation=ACT_NONE) -> int:
+        return lib.qx_qgemm_prepacked_epilogue_storage_dev(
+            self.handle, _vp(x.data_ptr()), x_type, _dev(bias), _vp(y.data_ptr()), y_type, m,
+            activation, _stream())
+
+
+def import_smoothquant_w8a8(weights, weight_scales, activation_scales, rows, columns,
+                            zero_points=None, row_sums=None):
+    """-> (status, qx_canonical_tensor view of the source arrays, row sums)."""
+    source = SmoothQuantSource(
+        _np(weights), 0 if weights is None else weights.size, _np(weight_scales),
+        0 if weight_scales is None else weight_scales.size, _np(activation_scales),
+        0 if activation_scales is None else activation_scales.size, _np(zero_points),
+        0 if zero_points is None else zero_points.size, _np(row_sums),
+        0 if row_sums is None else row_sums.size, rows, columns)
+    view = CanonicalTensorView()
+    sums = np.zeros(max(rows, 1), np.int32)
+    status = lib.qx_import_smoothquant_w8a8(C.byref(source), C.byref(view), _np(sums))
+    return status, view, sums[:max(rows, 0)]
 
 
 def peer_alloc(nbytes: int):

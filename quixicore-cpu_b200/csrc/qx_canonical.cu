@@ -1,0 +1,753 @@
+// Canonical prepared projections for the symmetric integer layouts (kInt8Symmetric,
+// kInt4Symmetric) with typed input / output, bias and activation epilogue, and the
+// SmoothQuant importer that produces such a tensor.
+//
+// Replaces, for these two layouts,
+//   CpuPackedWeights::prepare(const CanonicalQuantTensor&)   src/memory/packed_weights.cpp:280-398
+//   qgemm_prepacked_storage / qgemm_prepacked_epilogue_storage
+//                                   kernels/quantization/qgemm_canonical.cpp:4460-4648
+//   canonical_storage_panels (the portable schedule)         qgemm_canonical.cpp:2745-2863
+//   store_projection_output / projection_activation          qgemm_canonical.cpp:361-379, 2570-2581
+//   import_smoothquant_w8a8          kernels/quantization/quant_import_ref.cpp:1051-1116
+//
+// Arithmetic. The reference decodes a weight to f32 as scale * float(code) (one rounding,
+// decode_prepared_chunk, qgemm_canonical.cpp:150-176) and multiplies it into one of four f32
+// accumulators chosen by (column & 3); its AVX2 / NEON schedules order the same terms
+// differently again, so its own test compares against a tolerance (4e-5 * (1 + |expected|))
+// and so do this path's tests. Here every lane of a warp sums code * x over the 16 columns
+// it loaded (f32 multiply-adds on exactly converted codes), multiplies that partial sum by
+// the scale of its group once (when a scale group boundary falls inside the 16 columns every
+// weight is scaled on its own, as in the reference), and the 32 lane sums meet in a
+// butterfly. Inputs stored as f16 / bf16 are widened exactly, the output is rounded once at
+// the store. A token's result does not depend on the batch it is computed in.
+//
+// HBM layout. Codes stay in the canonical row-major byte order (a row of K int8 codes or
+// K/2 nibble pairs is already what a warp wants to stream with 16-byte loads), followed by
+// the f32 scale table [rows][groups]. Nothing is re-tiled, so prepared bytes = canonical
+// bytes.
+//
+// Kernel. CUDA cores, bound by HBM for a few tokens and by the FMA pipe for many (a
+// tensor-core schedule for long prefills is not built for this path). A CTA of WARPS warps
+// owns WARPS * ROWS output channels and TM tokens; K advances in chunks of 32 lanes x 16
+// columns. The codes, scales and activations of chunk c + 1 are loaded into registers
+// (16-byte / 8-byte vector loads) while the multiply-adds of chunk c run; the activations
+// are converted to f32 once and published to the CTA through one of two shared-memory
+// buffers (one barrier per chunk), laid out so that a lane's float4 reads are conflict free.
+// The tile shape is chosen per launch so that the CTAs fill the SMs evenly.
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <cmath>
+#include <mutex>
+#include <new>
+
+#include "qx_common.cuh"
+
+struct qx_canonical_weights {
+  int layout = 0;
+  int scale_mode = 0;
+  int device = -1;
+  long long rows = 0;
+  long long columns = 0;
+  long long group_size = 0;     // columns per scale (== columns for row / channel scales)
+  long long groups_per_row = 1;
+  size_t data_bytes = 0;
+  size_t scale_count = 0;
+  uint8_t* data = nullptr;      // device: canonical codes
+  float* scales = nullptr;      // device: [rows][groups_per_row]
+};
+
+namespace qx {
+namespace {
+
+struct CanonicalParams {
+  const uint8_t* data;
+  const float* scales;
+  const void* x;
+  const float* bias;
+  void* y;
+  long long rows, columns, group_size, groups_per_row, m;
+  int x_type, y_type, activation;
+  int vector_rows;   // 1: every row of codes starts on a 16-byte (int8) / 8-byte (int4) boundary
+  int vector_x;      // 1: every activation row starts on a boundary of four elements
+};
+
+__device__ __forceinline__ float load_storage(const void* base, int type, long long index) {
+  if (type == QX_STORAGE_F32) return static_cast<const float*>(base)[index];
+  const uint16_t bits = static_cast<const uint16_t*>(base)[index];
+  if (type == QX_STORAGE_F16) return __half2float(__ushort_as_half(bits));
+  return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+}
+
+// float_to_bf16 of the reference (kernels/utils/float_storage_ref.cpp:184-193): round to
+// nearest even on the bit pattern; a NaN keeps its upper payload with the quiet bit set.
+__device__ __forceinline__ uint16_t to_bf16_bits(float value) {
+  const uint32_t bits = __float_as_uint(value);
+  if ((bits & 0x7f800000u) == 0x7f800000u && (bits & 0x007fffffu) != 0) {
+    return static_cast<uint16_t>((bits >> 16) | 0x0040u);
+  }
+  return static_cast<uint16_t>((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
+}
+
+__device__ __forceinline__ void store_storage(void* base, int type, long long index, float value) {
+  if (type == QX_STORAGE_F32) {
+    static_cast<float*>(base)[index] = value;
+  } else if (type == QX_STORAGE_F16) {
+    static_cast<uint16_t*>(base)[index] = __half_as_ushort(__float2half_rn(value));
+  } else {
+    static_cast<uint16_t*>(base)[index] = to_bf16_bits(value);
+  }
+}
+
+// projection_activation, qgemm_canonical.cpp:361-379
+__device__ __forceinline__ float apply_activation(float v, int activation) {
+  switch (activation) {
+    case QX_ACTIVATION_GELU_ERF:
+      return 0.5f * v * (1.0f + erff(v * 0.7071067811865475f));
+    case QX_ACTIVATION_GELU_TANH:
+      return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    case QX_ACTIVATION_SILU:
+      return v / (1.0f + expf(-v));
+    case QX_ACTIVATION_RELU2:
+      return v > 0.0f ? v * v : 0.0f;
+    default:
+      return v;
+  }
+}
+
+// A lane owns 16 consecutive columns per K chunk (one 16-byte load of int8 codes, one 8-byte
+// load of int4 codes); a chunk is 32 lanes x 16 = 512 columns, i.e. 128 float4 units of
+// activations per token.
+constexpr int kElems = 16;
+constexpr int kChunk = 32 * kElems;
+constexpr int kUnits = kChunk / 4;
+
+struct LaneCodes {
+  uint32_t w[4];  // int8: four words of four codes; int4: w[0], w[1] hold eight nibbles each
+};
+
+// The four codes of float4 group j (columns 4j .. 4j+3 of the lane's span) as floats, without
+// the integer-to-float unit: a code is moved into the mantissa of 2^23 and the offset is
+// subtracted, which is exact. int8: byte ^ 0x80 = code + 128; int4: nibble ^ 8 = code + 8
+// (n >= 8 means n - 16), the lower column in the low nibble.
+template <int LAYOUT>
+__device__ __forceinline__ void decode4(const LaneCodes& codes, int j, float (&f)[4]) {
+  if (LAYOUT == QX_CANONICAL_INT8_SYMMETRIC) {
+    const uint32_t word = codes.w[j] ^ 0x80808080u;
+    f[0] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7440)) - 8388736.0f;
+    f[1] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7441)) - 8388736.0f;
+    f[2] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7442)) - 8388736.0f;
+    f[3] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7443)) - 8388736.0f;
+  } else {
+    const uint32_t word = codes.w[j >> 1] ^ 0x88888888u;
+    const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;
+    if ((j & 1) == 0) {
+      f[0] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7440)) - 8388616.0f;
+      f[1] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7440)) - 8388616.0f;
+      f[2] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7441)) - 8388616.0f;
+      f[3] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7441)) - 8388616.0f;
+    } else {
+      f[0] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7442)) - 8388616.0f;
+      f[1] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7442)) - 8388616.0f;
+      f[2] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7443)) - 8388616.0f;
+      f[3] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7443)) - 8388616.0f;
+    }
+  }
+}
+
+// Codes of columns k_lane .. k_lane + 15 of one row; `src` points at the row's byte for
+// column k_lane. Columns at or past `columns` stay zero.
+template <int LAYOUT>
+__device__ __forceinline__ LaneCodes load_codes(const uint8_t* src, bool vector, int k_lane,
+                                                int columns) {
+  LaneCodes out = {{0u, 0u, 0u, 0u}};
+  if (vector && k_lane + kElems <= columns) {
+    if (LAYOUT == QX_CANONICAL_INT8_SYMMETRIC) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(src));
+      out.w[0] = v.x; out.w[1] = v.y; out.w[2] = v.z; out.w[3] = v.w;
+    } else {
+      const uint2 v = __ldg(reinterpret_cast<const uint2*>(src));
+      out.w[0] = v.x; out.w[1] = v.y;
+    }
+    return out;
+  }
+  // ragged tail or rows that do not start on a vector boundary: byte by byte
+  const int left = columns - k_lane;
+  const int span = left < kElems ? left : kElems;
+  const int bytes = LAYOUT == QX_CANONICAL_INT8_SYMMETRIC ? span : (span + 1) / 2;
+  uint32_t w0 = 0u, w1 = 0u, w2 = 0u, w3 = 0u;
+  for (int b = 0; b < bytes; ++b) {
+    const uint32_t v = static_cast<uint32_t>(src[b]) << (8 * (b & 3));
+    if (b < 4) w0 |= v; else if (b < 8) w1 |= v; else if (b < 12) w2 |= v; else w3 |= v;
+  }
+  out.w[0] = w0; out.w[1] = w1; out.w[2] = w2; out.w[3] = w3;
+  return out;  // a zero code decodes to zero in both layouts
+}
+
+// Four activations starting at element `index` (column k of a token's row), widened to f32.
+__device__ __forceinline__ float4 load_x4(const CanonicalParams& p, long long index, int k,
+                                          int columns) {
+  if (p.vector_x && k + 4 <= columns) {
+    if (p.x_type == QX_STORAGE_F32) return __ldg(reinterpret_cast<const float4*>(p.x) + (index >> 2));
+    const uint2 raw = __ldg(reinterpret_cast<const uint2*>(p.x) + (index >> 2));
+    if (p.x_type == QX_STORAGE_F16) {
+      const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+      const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+      return make_float4(lo.x, lo.y, hi.x, hi.y);
+    }
+    return make_float4(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u),
+                       __uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+  }
+  float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    if (k + c < columns) v[c] = load_storage(p.x, p.x_type, index + c);
+  }
+  return make_float4(v[0], v[1], v[2], v[3]);
+}
+
+template <int LAYOUT, int TM, int ROWS, int WARPS>
+__global__ void __launch_bounds__(32 * WARPS) canonical_gemm_kernel(const CanonicalParams p) {
+  constexpr bool kInt8 = LAYOUT == QX_CANONICAL_INT8_SYMMETRIC;
+  constexpr int kThreadsHere = 32 * WARPS;
+  constexpr int kUnitsPerThread = (TM * kUnits + kThreadsHere - 1) / kThreadsHere;
+  // two buffers of the chunk's activations: float4 unit (token, group g of lane `owner`) sits
+  // at [token][g * 32 + owner], so that the 32 lanes read 32 consecutive float4
+  __shared__ float4 xs[2][TM][kUnits];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int columns = static_cast<int>(p.columns);
+  const long long row0 = (static_cast<long long>(blockIdx.x) * WARPS + warp) * ROWS;
+  const long long token0 = static_cast<long long>(blockIdx.y) * TM;
+  const int tokens = static_cast<int>(p.m - token0 < TM ? p.m - token0 : TM);
+  // one scale per lane span when a span never straddles a scale group
+  const int group_size = static_cast<int>(p.group_size);
+  const bool uniform_scale = group_size % kElems == 0;
+  const int chunks = (columns + kChunk - 1) / kChunk;
+
+  // per row: where this lane's codes of chunk 0 start, and the row of the scale table
+  const uint8_t* code_ptr[ROWS];
+  const float* scale_row[ROWS];
+  bool row_ok[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const long long row = row0 + r;
+    row_ok[r] = row < p.rows;
+    const long long safe = row_ok[r] ? row : 0;
+    code_ptr[r] = p.data + safe * (kInt8 ? p.columns : p.columns / 2) + lane * (kInt8 ? kElems : kElems / 2);
+    scale_row[r] = p.scales + safe * p.groups_per_row;
+  }
+  // per staged unit of this thread: element index of chunk 0 and the shared-memory slot
+  long long x_index[kUnitsPerThread];
+  int x_column[kUnitsPerThread];  // column of chunk 0, or a column past the end when unused
+  int x_slot[kUnitsPerThread];
+#pragma unroll
+  for (int i = 0; i < kUnitsPerThread; ++i) {
+    const int u = threadIdx.x + i * kThreadsHere;
+    const int token = u / kUnits, q = u % kUnits;
+    const bool used = u < TM * kUnits && token < tokens;
+    x_column[i] = used ? 4 * q : 0x40000000;
+    x_index[i] = (token0 + (used ? token : 0)) * p.columns + 4 * q;
+    x_slot[i] = u < TM * kUnits ? token * kUnits + (q & 3) * 32 + (q >> 2) : -1;
+  }
+
+  float acc[ROWS][TM];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+    for (int t = 0; t < TM; ++t) acc[r][t] = 0.0f;
+  }
+
+  LaneCodes codes[ROWS];
+  float scale[ROWS];
+  float4 xr[kUnitsPerThread];
+  auto fetch = [&](int chunk, LaneCodes (&into)[ROWS], float (&scales)[ROWS]) {
+    const int k0 = chunk * kChunk;
+    const int k_lane = k0 + lane * kElems;
+    const int group = uniform_scale ? k_lane / group_size : 0;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      if (row_ok[r] && k_lane < columns) {
+        into[r] = load_codes<LAYOUT>(code_ptr[r] + (kInt8 ? k0 : k0 / 2), p.vector_rows != 0,
+                                     k_lane, columns);
+        scales[r] = uniform_scale ? __ldg(scale_row[r] + group) : 0.0f;
+      } else {
+        into[r] = LaneCodes{{0u, 0u, 0u, 0u}};
+        scales[r] = 0.0f;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kUnitsPerThread; ++i) {
+      xr[i] = x_column[i] + k0 < columns
+                  ? load_x4(p, x_index[i] + k0, x_column[i] + k0, columns)
+                  : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    }
+  };
+  fetch(0, codes, scale);
+
+  for (int chunk = 0; chunk < chunks; ++chunk) {
+    float4* buf = &xs[chunk & 1][0][0];
+#pragma unroll
+    for (int i = 0; i < kUnitsPerThread; ++i) {
+      if (x_slot[i] >= 0) buf[x_slot[i]] = xr[i];
+    }
+    // One barrier per chunk: a warp that writes buffer (chunk + 1) & 1 next has passed this
+    // barrier, so every warp has finished the math of chunk - 1, the last reader of that buffer.
+    __syncthreads();
+    LaneCodes next_codes[ROWS];
+    float next_scale[ROWS];
+    if (chunk + 1 < chunks) fetch(chunk + 1, next_codes, next_scale);  // in flight under the math
+    if (uniform_scale) {
+      // sum of the lane's 16 columns on raw codes, scaled once: scale * sum(code * x)
+      float part[ROWS][TM];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+        for (int t = 0; t < TM; ++t) part[r][t] = 0.0f;
+      }
+#pragma unroll
+      for (int j = 0; j < kElems / 4; ++j) {
+        float4 xv[TM];
+#pragma unroll
+        for (int t = 0; t < TM; ++t) xv[t] = buf[t * kUnits + j * 32 + lane];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          float f[4];
+          decode4<LAYOUT>(codes[r], j, f);
+#pragma unroll
+          for (int t = 0; t < TM; ++t) {
+            part[r][t] = fmaf(f[0], xv[t].x, part[r][t]);
+            part[r][t] = fmaf(f[1], xv[t].y, part[r][t]);
+            part[r][t] = fmaf(f[2], xv[t].z, part[r][t]);
+            part[r][t] = fmaf(f[3], xv[t].w, part[r][t]);
+          }
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+        for (int t = 0; t < TM; ++t) acc[r][t] = fmaf(scale[r], part[r][t], acc[r][t]);
+      }
+    } else {
+      // a scale group boundary inside the span: every weight is scaled on its own, as the
+      // reference decodes it (scale * float(code), qgemm_canonical.cpp:150-176)
+      const int k_lane = chunk * kChunk + lane * kElems;
+#pragma unroll
+      for (int j = 0; j < kElems / 4; ++j) {
+        float4 xv[TM];
+#pragma unroll
+        for (int t = 0; t < TM; ++t) xv[t] = buf[t * kUnits + j * 32 + lane];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          float f[4];
+          decode4<LAYOUT>(codes[r], j, f);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const int k = k_lane + 4 * j + c;
+            const float s = (row_ok[r] && k < columns) ? scale_row[r][k / group_size] : 0.0f;
+            f[c] = __fmul_rn(s, f[c]);
+          }
+#pragma unroll
+          for (int t = 0; t < TM; ++t) {
+            acc[r][t] = fmaf(f[0], xv[t].x, acc[r][t]);
+            acc[r][t] = fmaf(f[1], xv[t].y, acc[r][t]);
+            acc[r][t] = fmaf(f[2], xv[t].z, acc[r][t]);
+            acc[r][t] = fmaf(f[3], xv[t].w, acc[r][t]);
+          }
+        }
+      }
+    }
+    if (chunk + 1 < chunks) {
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        codes[r] = next_codes[r];
+        scale[r] = next_scale[r];
+      }
+    }
+  }
+
+  // ---- the 32 partial sums of an output meet in a butterfly; lane (r * TM + t) % 32 stores it
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+    for (int t = 0; t < TM; ++t) {
+      float v = acc[r][t];
+#pragma unroll
+      for (int h = 16; h >= 1; h >>= 1) v += __shfl_xor_sync(0xffffffffu, v, h);
+      const long long row = row0 + r;
+      if (lane == ((r * TM + t) & 31) && row_ok[r] && t < tokens) {
+        if (p.bias != nullptr) v += p.bias[row];
+        v = apply_activation(v, p.activation);
+        store_storage(p.y, p.y_type, (token0 + t) * p.rows + row, v);
+      }
+    }
+  }
+}
+
+template <int LAYOUT, int TM, int ROWS, int WARPS>
+qx_status launch_one(const CanonicalParams& p, cudaStream_t stream) {
+  const long long gx = (p.rows + WARPS * ROWS - 1) / (WARPS * ROWS);
+  const long long gy = (p.m + TM - 1) / TM;
+  if (gx > 0x7fffffffLL || gy > 65535) {
+    set_last_error_text("canonical projection: shape too large for one launch");
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  canonical_gemm_kernel<LAYOUT, TM, ROWS, WARPS>
+      <<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(gy)), 32 * WARPS, 0, stream>>>(p);
+  count_launch();
+  QX_CUDA_TRY(cudaGetLastError());
+  return QX_STATUS_OK;
+}
+
+// Tile shapes, largest first: rows per warp x warps per CTA. The first whose CTAs fill the
+// SMs evenly (at least 90 % of the slots of its last round busy) wins, else the most even:
+// 14336 rows on 148 SMs leave a quarter of the machine idle with 64-row CTAs and 7 % with
+// 8-row CTAs. Eight-token tiles keep two rows per warp (register budget).
+struct TileShape {
+  int rows, warps;
+};
+inline int pick_shape(const TileShape* shapes, int count, long long rows, long long token_tiles,
+                      int sm_count) {
+  int best = 0;
+  double best_fill = -1.0;
+  for (int i = 0; i < count; ++i) {
+    const long long per_cta = static_cast<long long>(shapes[i].rows) * shapes[i].warps;
+    const long long ctas = (rows + per_cta - 1) / per_cta * token_tiles;
+    const long long rounds = (ctas + sm_count - 1) / sm_count;
+    const double fill = static_cast<double>(ctas) / static_cast<double>(rounds * sm_count);
+    if (fill >= 0.9) return i;
+    if (fill > best_fill) {
+      best_fill = fill;
+      best = i;
+    }
+  }
+  return best;
+}
+
+template <int LAYOUT, int TM>
+qx_status launch_tokens(const CanonicalParams& p, int sm_count, cudaStream_t stream) {
+  const long long token_tiles = (p.m + TM - 1) / TM;
+  if constexpr (TM == 1) {
+    constexpr TileShape kShapes[4] = {{8, 8}, {4, 8}, {4, 4}, {2, 4}};
+    switch (pick_shape(kShapes, 4, p.rows, token_tiles, sm_count)) {
+      case 0: return launch_one<LAYOUT, TM, 8, 8>(p, stream);
+      case 1: return launch_one<LAYOUT, TM, 4, 8>(p, stream);
+      case 2: return launch_one<LAYOUT, TM, 4, 4>(p, stream);
+      default: return launch_one<LAYOUT, TM, 2, 4>(p, stream);
+    }
+  } else if constexpr (TM == 4) {
+    constexpr TileShape kShapes[3] = {{4, 8}, {4, 4}, {2, 4}};
+    switch (pick_shape(kShapes, 3, p.rows, token_tiles, sm_count)) {
+      case 0: return launch_one<LAYOUT, TM, 4, 8>(p, stream);
+      case 1: return launch_one<LAYOUT, TM, 4, 4>(p, stream);
+      default: return launch_one<LAYOUT, TM, 2, 4>(p, stream);
+    }
+  } else {
+    constexpr TileShape kShapes[2] = {{2, 8}, {2, 4}};
+    switch (pick_shape(kShapes, 2, p.rows, token_tiles, sm_count)) {
+      case 0: return launch_one<LAYOUT, TM, 2, 8>(p, stream);
+      default: return launch_one<LAYOUT, TM, 2, 4>(p, stream);
+    }
+  }
+}
+
+template <int LAYOUT>
+qx_status launch_layout(const CanonicalParams& p, int sm_count, cudaStream_t stream) {
+  if (p.m == 1) return launch_tokens<LAYOUT, 1>(p, sm_count, stream);
+  if (p.m <= 4) return launch_tokens<LAYOUT, 4>(p, sm_count, stream);
+  return launch_tokens<LAYOUT, 8>(p, sm_count, stream);
+}
+
+bool known_storage(int type) {
+  return type == QX_STORAGE_F32 || type == QX_STORAGE_F16 || type == QX_STORAGE_BF16;
+}
+size_t storage_bytes(int type) { return type == QX_STORAGE_F32 ? 4 : 2; }
+bool known_activation(int activation) {
+  return activation >= QX_ACTIVATION_NONE && activation <= QX_ACTIVATION_RELU2;
+}
+
+qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_type,
+                           const float* bias, void* y, int y_type, long long m, int activation,
+                           cudaStream_t stream) {
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  if (ctx->device != w->device) {
+    set_last_error_text("canonical projection: weights were prepared on another device");
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  if (w->columns > (1LL << 30)) {
+    set_last_error_text("canonical projection: more than 2^30 columns");
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  CanonicalParams p{};
+  p.data = w->data;
+  p.scales = w->scales;
+  p.x = x;
+  p.bias = bias;
+  p.y = y;
+  p.rows = w->rows;
+  p.columns = w->columns;
+  p.group_size = w->group_size;
+  p.groups_per_row = w->groups_per_row;
+  p.m = m;
+  p.x_type = x_type;
+  p.y_type = y_type;
+  p.activation = activation;
+  const bool int8 = w->layout == QX_CANONICAL_INT8_SYMMETRIC;
+  const long long row_bytes = int8 ? w->columns : w->columns / 2;
+  const int code_vector = int8 ? 16 : 8;
+  p.vector_rows = (row_bytes % code_vector == 0 &&
+                   reinterpret_cast<uintptr_t>(w->data) % code_vector == 0) ? 1 : 0;
+  const int x_vector = x_type == QX_STORAGE_F32 ? 16 : 8;
+  p.vector_x = (w->columns % 4 == 0 && reinterpret_cast<uintptr_t>(x) % x_vector == 0) ? 1 : 0;
+  const int sm_count = ctx->prop.multiProcessorCount;
+  return w->layout == QX_CANONICAL_INT8_SYMMETRIC
+             ? launch_layout<QX_CANONICAL_INT8_SYMMETRIC>(p, sm_count, stream)
+             : launch_layout<QX_CANONICAL_INT4_SYMMETRIC>(p, sm_count, stream);
+}
+
+bool finite_nonnegative(const float* v, size_t count) {
+  for (size_t i = 0; i < count; ++i) {
+    if (!std::isfinite(v[i]) || v[i] < 0.0f) return false;
+  }
+  return true;
+}
+bool finite_all(const float* v, size_t count) {
+  for (size_t i = 0; i < count; ++i) {
+    if (!std::isfinite(v[i])) return false;
+  }
+  return true;
+}
+
+// Shape checks shared by prepare and the entry points.
+qx_status validate_tensor(const qx_canonical_tensor* t, long long* groups_per_row,
+                          long long* group_size) {
+  if (t->layout != QX_CANONICAL_INT8_SYMMETRIC && t->layout != QX_CANONICAL_INT4_SYMMETRIC) {
+    return QX_STATUS_UNSUPPORTED_FORMAT;
+  }
+  if (!valid_product2(t->rows, t->columns)) return QX_STATUS_INVALID_SHAPE;
+  if (t->group_size < 0 || (t->group_size > 0 && t->columns % t->group_size != 0)) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  // validate_quant_metadata counts the scales its mode implies first
+  // (src/memory/quant_contract.cpp:176-208) ...
+  const size_t rows = static_cast<size_t>(t->rows), columns = static_cast<size_t>(t->columns);
+  size_t expected_scales = 0;
+  long long groups = 1, size = t->columns;
+  switch (t->scale_mode) {
+    case QX_SCALE_NONE: break;
+    case QX_SCALE_TENSOR: expected_scales = 1; break;
+    case QX_SCALE_ROW:
+    case QX_SCALE_CHANNEL: expected_scales = rows; break;
+    case QX_SCALE_GROUP:
+      if (t->group_size <= 0) return QX_STATUS_INVALID_SHAPE;
+      groups = t->columns / t->group_size;
+      size = t->group_size;
+      expected_scales = rows * static_cast<size_t>(groups);
+      break;
+    case 5:  // kBlock
+      if (t->scale_count == 0) return QX_STATUS_INVALID_SHAPE;
+      expected_scales = t->scale_count;
+      break;
+    case 6:  // kMicroscaleK32
+    case 8:  // kTurboQuantK32
+      expected_scales = rows * (columns / 32);
+      break;
+    case 7:  // kNVFP4K16
+      expected_scales = rows * (columns / 16);
+      break;
+    default: return QX_STATUS_INVALID_ARGUMENT;
+  }
+  if (t->scale_count != expected_scales) return QX_STATUS_INVALID_SHAPE;
+  // ... then validate_canonical_quant_tensor accepts row, channel and group scales for the
+  // integer layouts (kernels/quantization/quant_import_ref.cpp:406-421)
+  if (t->scale_mode != QX_SCALE_ROW && t->scale_mode != QX_SCALE_CHANNEL &&
+      t->scale_mode != QX_SCALE_GROUP) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  size_t expected = rows * columns;
+  if (t->layout == QX_CANONICAL_INT4_SYMMETRIC) {
+    if ((t->columns & 1) != 0) return QX_STATUS_INVALID_SHAPE;
+    expected /= 2;
+  }
+  if (t->data_bytes != expected) return QX_STATUS_INVALID_SHAPE;
+  if (t->data == nullptr || t->scales == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  if (!finite_nonnegative(t->scales, t->scale_count)) return QX_STATUS_INVALID_SHAPE;
+  *groups_per_row = groups;
+  *group_size = size;
+  return QX_STATUS_OK;
+}
+
+}  // namespace
+}  // namespace qx
+
+using namespace qx;
+
+extern "C" {
+
+qx_status qx_canonical_prepare(const qx_canonical_tensor* tensor, qx_canonical_weights** out) {
+  if (tensor == nullptr || out == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  *out = nullptr;
+  long long groups = 1, size = 0;
+  QX_TRY(validate_tensor(tensor, &groups, &size));
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  qx_canonical_weights* w = new (std::nothrow) qx_canonical_weights();
+  if (w == nullptr) return QX_STATUS_OUT_OF_MEMORY;
+  w->layout = tensor->layout;
+  w->scale_mode = tensor->scale_mode;
+  w->device = ctx->device;
+  w->rows = tensor->rows;
+  w->columns = tensor->columns;
+  w->group_size = size;
+  w->groups_per_row = groups;
+  w->data_bytes = tensor->data_bytes;
+  w->scale_count = tensor->scale_count;
+  // one allocation: codes, then the scale table on a 256-byte boundary
+  const size_t scale_offset = align_up(tensor->data_bytes, 256);
+  void* block = nullptr;
+  cudaError_t err = cudaMalloc(&block, scale_offset + tensor->scale_count * sizeof(float));
+  if (err != cudaSuccess) {
+    set_last_error("cudaMalloc(canonical weights)", err);
+    delete w;
+    return err == cudaErrorMemoryAllocation ? QX_STATUS_OUT_OF_MEMORY : QX_STATUS_DEVICE_ERROR;
+  }
+  w->data = static_cast<uint8_t*>(block);
+  w->scales = reinterpret_cast<float*>(w->data + scale_offset);
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  err = cudaMemcpyAsync(w->data, tensor->data, tensor->data_bytes, cudaMemcpyHostToDevice,
+                        ctx->stream);
+  if (err == cudaSuccess) {
+    err = cudaMemcpyAsync(w->scales, tensor->scales, tensor->scale_count * sizeof(float),
+                          cudaMemcpyHostToDevice, ctx->stream);
+  }
+  if (err == cudaSuccess) err = cudaStreamSynchronize(ctx->stream);
+  if (err != cudaSuccess) {
+    set_last_error("upload of canonical weights", err);
+    (void)cudaFree(block);
+    delete w;
+    return QX_STATUS_DEVICE_ERROR;
+  }
+  *out = w;
+  return QX_STATUS_OK;
+}
+
+void qx_canonical_destroy(qx_canonical_weights* weights) {
+  if (weights == nullptr) return;
+  if (weights->data != nullptr) (void)cudaFree(weights->data);
+  delete weights;
+}
+
+qx_status qx_qgemm_prepacked_epilogue_storage_dev(const qx_canonical_weights* weights,
+                                                  const void* x_dev, int x_type,
+                                                  const float* bias_dev, void* y_dev, int y_type,
+                                                  long long m, int activation, void* stream) {
+  if (!known_activation(activation)) return QX_STATUS_INVALID_ARGUMENT;
+  if (weights == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  if (!valid_product2(m, weights->columns) || !valid_product2(m, weights->rows)) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  if (!known_storage(x_type) || !known_storage(y_type)) return QX_STATUS_UNSUPPORTED_FORMAT;
+  if (x_dev == nullptr || y_dev == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  return launch_canonical(weights, x_dev, x_type, bias_dev, y_dev, y_type, m, activation,
+                          static_cast<cudaStream_t>(stream));
+}
+
+qx_status qx_qgemm_prepacked_epilogue_storage(const qx_canonical_weights* weights, const void* x,
+                                              int x_type, long long x_count, const float* bias,
+                                              void* y, int y_type, long long y_count, long long m,
+                                              int activation) {
+  // validation order of qgemm_prepacked_storage_impl, qgemm_canonical.cpp:4460-4481
+  if (!known_activation(activation)) return QX_STATUS_INVALID_ARGUMENT;
+  if (weights == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  if (!valid_product2(m, weights->columns) || !valid_product2(m, weights->rows) ||
+      x_count != m * weights->columns || y_count != m * weights->rows) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  if (!known_storage(x_type) || !known_storage(y_type)) return QX_STATUS_UNSUPPORTED_FORMAT;
+  if (x == nullptr || y == nullptr) return QX_STATUS_INVALID_ARGUMENT;
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  std::lock_guard<std::mutex> lock(ctx->mutex);
+  const size_t x_bytes = static_cast<size_t>(x_count) * storage_bytes(x_type);
+  const size_t y_bytes = static_cast<size_t>(y_count) * storage_bytes(y_type);
+  const size_t bias_bytes = bias != nullptr ? static_cast<size_t>(weights->rows) * 4 : 0;
+  const size_t off_x = 0, off_bias = align_up(x_bytes, 256);
+  const size_t off_y = off_bias + align_up(bias_bytes == 0 ? 1 : bias_bytes, 256);
+  QX_TRY(ctx->ensure_staging(off_y + align_up(y_bytes, 256)));
+  uint8_t* stage = static_cast<uint8_t*>(ctx->staging);
+  cudaStream_t s = ctx->stream;
+  QX_CUDA_TRY(cudaMemcpyAsync(stage + off_x, x, x_bytes, cudaMemcpyHostToDevice, s));
+  if (bias != nullptr) {
+    QX_CUDA_TRY(cudaMemcpyAsync(stage + off_bias, bias, bias_bytes, cudaMemcpyHostToDevice, s));
+  }
+  QX_TRY(launch_canonical(weights, stage + off_x, x_type,
+                          bias != nullptr ? reinterpret_cast<const float*>(stage + off_bias)
+                                          : nullptr,
+                          stage + off_y, y_type, m, activation, s));
+  QX_CUDA_TRY(cudaMemcpyAsync(y, stage + off_y, y_bytes, cudaMemcpyDeviceToHost, s));
+  QX_CUDA_TRY(cudaStreamSynchronize(s));
+  return QX_STATUS_OK;
+}
+
+qx_status qx_qgemm_prepacked_storage(const qx_canonical_weights* weights, const void* x,
+                                     int x_type, long long x_count, void* y, int y_type,
+                                     long long y_count, long long m) {
+  return qx_qgemm_prepacked_epilogue_storage(weights, x, x_type, x_count, nullptr, y, y_type,
+                                             y_count, m, QX_ACTIVATION_NONE);
+}
+
+const char* qx_canonical_gemm_variant(void) { return "sm100a_stream_fma_typed"; }
+
+qx_status qx_import_smoothquant_w8a8(const qx_smoothquant_source* source,
+                                     qx_canonical_tensor* tensor, int32_t* row_sums_out) {
+  // check order of import_smoothquant_w8a8, quant_import_ref.cpp:1053-1074
+  if (source == nullptr || tensor == nullptr || row_sums_out == nullptr ||
+      source->weights == nullptr || source->weight_scales == nullptr ||
+      source->activation_scales == nullptr || !valid_product2(source->rows, source->columns)) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  const size_t elements =
+      static_cast<size_t>(source->rows) * static_cast<size_t>(source->columns);
+  if (source->weight_count != elements ||
+      source->weight_scale_count != static_cast<size_t>(source->rows) ||
+      source->activation_scale_count == 0 ||
+      (source->activation_zero_point_count != 0 &&
+       (source->activation_zero_points == nullptr ||
+        source->activation_zero_point_count != source->activation_scale_count)) ||
+      (source->row_sum_count != 0 &&
+       (source->row_sums == nullptr ||
+        source->row_sum_count != static_cast<size_t>(source->rows))) ||
+      !finite_all(source->weight_scales, source->weight_scale_count) ||
+      !finite_all(source->activation_scales, source->activation_scale_count)) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  // validate_canonical_quant_tensor rejects a negative scale (quant_import_ref.cpp:470-476)
+  if (!finite_nonnegative(source->weight_scales, source->weight_scale_count)) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  for (long long row = 0; row < source->rows; ++row) {
+    if (source->row_sum_count != 0) {
+      row_sums_out[row] = source->row_sums[row];
+    } else {
+      int32_t sum = 0;
+      const int8_t* codes = source->weights + row * source->columns;
+      for (long long column = 0; column < source->columns; ++column) sum += codes[column];
+      row_sums_out[row] = sum;
+    }
+  }
+  tensor->layout = QX_CANONICAL_INT8_SYMMETRIC;
+  tensor->scale_mode = QX_SCALE_CHANNEL;
+  tensor->rows = source->rows;
+  tensor->columns = source->columns;
+  tensor->group_size = source->columns;
+  tensor->data = reinterpret_cast<const uint8_t*>(source->weights);
+  tensor->data_bytes = elements;
+  tensor->scales = source->weight_scales;
+  tensor->scale_count = source->weight_scale_count;
+  return QX_STATUS_OK;
+}
+
+}  // extern "C"
