@@ -476,7 +476,10 @@ QX_API qx_status qx_qgemm_prepacked_epilogue_storage(const qx_canonical_weights*
                                                      const float* bias, void* y, int y_type,
                                                      long long y_count, long long m,
                                                      int activation);
-/* DEVICE pointers and a stream; allocates nothing and does not synchronise. */
+/* DEVICE pointers and a stream. Enqueues two kernels (the digits of the activations, then the
+ * projection) and returns without waiting; the digit images (1792 bytes per token and 512
+ * columns) live in the library's default workspace, which grows -- and then synchronises the
+ * device -- the first time a larger call arrives. */
 QX_API qx_status qx_qgemm_prepacked_epilogue_storage_dev(const qx_canonical_weights* weights,
                                                          const void* x_dev, int x_type,
                                                          const float* bias_dev, void* y_dev,

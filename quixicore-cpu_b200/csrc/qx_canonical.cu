@@ -14,35 +14,38 @@
 // decode_prepared_chunk, qgemm_canonical.cpp:150-176) and multiplies it into one of four f32
 // accumulators chosen by (column & 3); its AVX2 / NEON schedules order the same terms
 // differently again, so its own test compares against a tolerance (4e-5 * (1 + |expected|))
-// and so do this path's tests. Here every lane of a warp sums code * x over the 16 columns
-// it loaded (f32 multiply-adds on exactly converted codes), multiplies that partial sum by
-// the scale of its group once (when a scale group boundary falls inside the 16 columns every
-// weight is scaled on its own, as in the reference), and the 32 lane sums meet in a
-// butterfly. Inputs stored as f16 / bf16 are widened exactly, the output is rounded once at
-// the store. A token's result does not depend on the batch it is computed in.
+// and so do this path's tests. Two paths here, both summing a lane's 16 columns first, scaling
+// that partial sum by the weight scale once, and joining the 32 lane sums in a butterfly:
+//   digits  (scale groups that are multiples of 16 columns, or one scale per row): the
+//           activations of a span become exact 8-bit digits under a power-of-two envelope and
+//           the sums are integer dot products; see "digit kernels" below;
+//   floats  (a scale group boundary inside 16 columns): f32 multiply-adds on exactly
+//           converted codes, every weight scaled on its own as in the reference.
+// Inputs stored as f16 / bf16 are widened exactly, the output is rounded once at the store.
+// A token's result does not depend on the batch it is computed in.
 //
 // HBM layout. Codes stay in the canonical row-major byte order (a row of K int8 codes or
 // K/2 nibble pairs is already what a warp wants to stream with 16-byte loads), followed by
 // the f32 scale table [rows][groups]. Nothing is re-tiled, so prepared bytes = canonical
-// bytes.
+// bytes. The digit images of a call's activations (1792 bytes per token and 512 columns)
+// live in the device's default workspace.
 //
-// Kernel. CUDA cores, bound by HBM for a few tokens and by the FMA pipe for many (a
-// tensor-core schedule for long prefills is not built for this path). A CTA of WARPS warps
-// owns WARPS * ROWS output channels and TM tokens; K advances in chunks of 32 lanes x 16
-// columns. The codes, scales and activations of chunk c + 1 are loaded into registers
-// (16-byte / 8-byte vector loads) while the multiply-adds of chunk c run; the activations
-// are converted to f32 once and published to the CTA through one of two shared-memory
-// buffers (one barrier per chunk), laid out so that a lane's float4 reads are conflict free.
-// The tile shape is chosen per launch so that the CTAs fill the SMs evenly.
+// Kernels. CUDA cores; a tensor-core schedule for long prefills is not built for this path.
+// Measured on 14336 x 4096 int8 with one bf16 token: 18 us per call for both launches (the
+// digit kernel and the projection behind it), 3.2 TB/s of the weights' bytes, about half of
+// the measured copy bandwidth; the float path ran the same shape in 24 us at 10 instructions
+// per weight, bound by instruction issue.
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <mutex>
 #include <new>
 
 #include "qx_common.cuh"
+#include "qx_gemv.cuh"
 
 struct qx_canonical_weights {
   int layout = 0;
@@ -386,6 +389,340 @@ __global__ void __launch_bounds__(32 * WARPS) canonical_gemm_kernel(const Canoni
   }
 }
 
+// ---- digit kernels: the path of every tensor whose scale groups are multiples of 16 columns
+//
+// Activation digits. Per token and per span of 16 columns (one lane's columns of a chunk) the
+// activations are written as 23-bit signed fixed point under the span's power-of-two
+// envelope, x = e * t with |t| <= 2^22, and t is split into balanced base-256 digits
+// t = 65536 * p2 + 256 * p1 + p0, each a signed byte. A span's dot product with 16 integer
+// codes is then three exact integer dot products per four columns (dp4a), combined once per
+// span in f32 and multiplied by e and by the weight scale: about one instruction per weight
+// instead of the three or four of a float multiply-add on a decoded weight, which is what
+// lets a single token run at memory speed. The only rounding on the activation side is the
+// fixed-point step, at most 2^-23 of the span's envelope per element -- of the order of one
+// f32 rounding in the reference's own sum; the integer sums are exact.
+//
+// A small kernel in front writes the digits of all tokens once per call (a few KB per token,
+// read back by every warp through L1 / L2); the projection kernel is launched as its
+// programmatic dependent: it fetches its first codes while the digits are still being
+// written and waits for them itself.
+//
+// int4 without sign extension: a nibble n (meaning n - 16 when n >= 8) xor 8 is the unsigned
+// u = code + 8, so sum(code * t) = sum(u * t) - 8 * sum(t); sum(t) of the span is stored with
+// the digits. The even and odd nibbles of a word are two masked operands, and the digit
+// words of a span are stored in that order (even columns of a word, then odd).
+//
+// Digit image of one (token, chunk): three planes of 128 words (word = span * 4 + g), then
+// 32 envelopes, then 32 span sums.
+constexpr int kImageWords = 3 * 128 + 32 + 32;
+
+template <int LAYOUT>
+__global__ void __launch_bounds__(128) canonical_digits_prepass(const CanonicalParams p,
+                                                                uint32_t* __restrict__ image) {
+  // Let the projection kernel behind start (it fetches weights first), then wait for the
+  // work in front: the activations may be its output, and the projection of the previous
+  // call may still be reading the images this kernel overwrites.
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  constexpr bool kInt8 = LAYOUT == QX_CANONICAL_INT8_SYMMETRIC;
+  const int columns = static_cast<int>(p.columns);
+  const int chunks = (columns + kChunk - 1) / kChunk;
+  const int chunk = blockIdx.x % chunks;
+  const long long token = blockIdx.x / chunks;
+  const int word = threadIdx.x;  // span * 4 + g
+  const int span_k = chunk * kChunk + (word >> 2) * kElems;
+  const int g = word & 3;
+  float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+  if (span_k < columns) {
+    const long long base = token * p.columns;
+    if (kInt8) {
+      v = load_x4(p, base + span_k + 4 * g, span_k + 4 * g, columns);
+    } else {
+      // even (g & 1 == 0) or odd columns of the eight columns of code word g >> 1
+      const int k8 = span_k + 8 * (g >> 1);
+      const float4 a = load_x4(p, base + k8, k8, columns);
+      const float4 b = load_x4(p, base + k8 + 4, k8 + 4, columns);
+      v = (g & 1) ? make_float4(a.y, a.w, b.y, b.w) : make_float4(a.x, a.z, b.x, b.z);
+    }
+  }
+  // the span's largest magnitude: the four words of a span sit in four adjacent lanes
+  float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+  // fmaxf drops a NaN operand: the sum of magnitudes keeps it
+  if (!(fabsf(v.x) + fabsf(v.y) + fabsf(v.z) + fabsf(v.w) < __uint_as_float(0x7f800000u))) {
+    amax = __uint_as_float(0x7f800000u);
+  }
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  // envelope 2^E > amax; t = x * 2^22 / 2^E. Spans below 2^-103 count as zero; a NaN or
+  // infinity makes the envelope NaN, which reaches every output of the token.
+  int biased = static_cast<int>(__float_as_uint(amax) >> 23) + 1;  // exponent of 2^E
+  biased = biased < 24 ? 24 : biased;
+  const bool finite = biased < 256;
+  const float to_fixed = finite ? __uint_as_float(static_cast<uint32_t>(276 - biased) << 23) : 0.0f;
+  const float e = finite ? __uint_as_float(static_cast<uint32_t>(biased - 22) << 23)
+                         : __uint_as_float(0x7fc00000u);
+  const float xs[4] = {v.x, v.y, v.z, v.w};
+  uint32_t w0 = 0u, w1 = 0u, w2 = 0u;
+  int tsum = 0;
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int t = finite ? __float2int_rn(xs[c] * to_fixed) : 0;
+    const int p0 = ((t + 128) & 255) - 128;
+    const int t1 = (t - p0) >> 8;
+    const int p1 = ((t1 + 128) & 255) - 128;
+    const int p2 = (t1 - p1) >> 8;
+    w0 |= static_cast<uint32_t>(p0 & 255) << (8 * c);
+    w1 |= static_cast<uint32_t>(p1 & 255) << (8 * c);
+    w2 |= static_cast<uint32_t>(p2 & 255) << (8 * c);
+    tsum += t;
+  }
+  tsum += __shfl_xor_sync(0xffffffffu, tsum, 1);
+  tsum += __shfl_xor_sync(0xffffffffu, tsum, 2);
+  uint32_t* out = image + static_cast<long long>(blockIdx.x) * kImageWords;
+  out[word] = w0;
+  out[128 + word] = w1;
+  out[256 + word] = w2;
+  if (g == 0) {
+    out[384 + (word >> 2)] = __float_as_uint(e);
+    out[416 + (word >> 2)] = static_cast<uint32_t>(tsum);
+  }
+}
+
+// One (token, chunk) image as a lane uses it: its span's four digit words of every plane.
+struct SpanDigits {
+  uint4 d0, d1, d2;
+  float e;
+  int tsum;
+};
+__device__ __forceinline__ SpanDigits load_span(const uint32_t* image, int lane) {
+  SpanDigits s;
+  s.d0 = __ldg(reinterpret_cast<const uint4*>(image) + lane);
+  s.d1 = __ldg(reinterpret_cast<const uint4*>(image + 128) + lane);
+  s.d2 = __ldg(reinterpret_cast<const uint4*>(image + 256) + lane);
+  s.e = __uint_as_float(__ldg(image + 384 + lane));
+  s.tsum = static_cast<int>(__ldg(image + 416 + lane));
+  return s;
+}
+
+constexpr int kDigitWarps = 4;  // independent warps per CTA: no shared memory, no barrier
+constexpr int kStep = 1;       // chunks a lane requests at once (measured: 1 is as fast as 4)
+
+template <int LAYOUT, int TM, int ROWS>
+__global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
+    const CanonicalParams p, const uint32_t* __restrict__ image) {
+  constexpr bool kInt8 = LAYOUT == QX_CANONICAL_INT8_SYMMETRIC;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int columns = static_cast<int>(p.columns);
+  const long long row0 = (static_cast<long long>(blockIdx.x) * kDigitWarps + warp) * ROWS;
+  const long long token0 = static_cast<long long>(blockIdx.y) * TM;
+  const int tokens = static_cast<int>(p.m - token0 < TM ? p.m - token0 : TM);
+  const int group_size = static_cast<int>(p.group_size);
+  const int chunks = (columns + kChunk - 1) / kChunk;
+
+  const uint8_t* code_ptr[ROWS];
+  const float* scale_row[ROWS];
+  bool row_ok[ROWS];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+    const long long row = row0 + r;
+    row_ok[r] = row < p.rows;
+    const long long safe = row_ok[r] ? row : 0;
+    code_ptr[r] = p.data + safe * (kInt8 ? p.columns : p.columns / 2) + lane * (kInt8 ? kElems : kElems / 2);
+    scale_row[r] = p.scales + safe * p.groups_per_row;
+  }
+  // the images of this CTA's tokens: [token][chunk]
+  const uint32_t* token_image[TM];
+#pragma unroll
+  for (int t = 0; t < TM; ++t) {
+    token_image[t] = image + (token0 + (t < tokens ? t : 0)) * chunks * kImageWords;
+  }
+
+  // A step is kStep consecutive chunks: a lane requests its 16 bytes of each of them at once.
+  auto fetch_codes = [&](int step, LaneCodes (&into)[kStep][ROWS], float (&scales)[kStep][ROWS]) {
+#pragma unroll
+    for (int u = 0; u < kStep; ++u) {
+      const int k0 = (step * kStep + u) * kChunk;
+      const int k_lane = k0 + lane * kElems;
+      const int group = p.groups_per_row == 1 ? 0 : k_lane / group_size;
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        if (row_ok[r] && k_lane < columns) {
+          into[u][r] = load_codes<LAYOUT>(code_ptr[r] + (kInt8 ? k0 : k0 / 2), p.vector_rows != 0,
+                                          k_lane, columns);
+          scales[u][r] = __ldg(scale_row[r] + group);
+        } else {
+          into[u][r] = LaneCodes{{0u, 0u, 0u, 0u}};
+          scales[u][r] = 0.0f;
+        }
+      }
+    }
+  };
+
+  float acc[ROWS][TM];
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+    for (int t = 0; t < TM; ++t) acc[r][t] = 0.0f;
+  }
+  LaneCodes codes[kStep][ROWS];
+  float scale[kStep][ROWS];
+  fetch_codes(0, codes, scale);  // weights do not depend on the kernel in front
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  const int steps = (chunks + kStep - 1) / kStep;
+  for (int step = 0; step < steps; ++step) {
+    const bool more = step + 1 < steps;
+    LaneCodes next_codes[kStep][ROWS];
+    float next_scale[kStep][ROWS];
+    if (more) fetch_codes(step + 1, next_codes, next_scale);  // HBM loads in flight under the math
+#pragma unroll
+    for (int u = 0; u < kStep; ++u) {
+      const int chunk = step * kStep + u;
+      if (chunk < chunks) {
+        if (!kInt8) {
+          // split every code word into its even and odd nibbles
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) {
+            const uint32_t a = codes[u][r].w[0] ^ 0x88888888u, b = codes[u][r].w[1] ^ 0x88888888u;
+            codes[u][r].w[0] = a & 0x0F0F0F0Fu;
+            codes[u][r].w[1] = (a >> 4) & 0x0F0F0F0Fu;
+            codes[u][r].w[2] = b & 0x0F0F0F0Fu;
+            codes[u][r].w[3] = (b >> 4) & 0x0F0F0F0Fu;
+          }
+        }
+#pragma unroll
+        for (int t = 0; t < TM; ++t) {
+          const SpanDigits span = load_span(token_image[t] + chunk * kImageWords, lane);
+          const uint4 d0 = span.d0, d1 = span.d1, d2 = span.d2;
+          const float e = t < tokens ? span.e : 0.0f;
+          const int tsum8 = 8 * span.tsum;
+#pragma unroll
+          for (int r = 0; r < ROWS; ++r) {
+            const uint32_t* w = codes[u][r].w;
+            float sum;
+            if (kInt8) {
+              int s0 = dp4a_ss(w[0], d0.x, 0), s1 = dp4a_ss(w[0], d1.x, 0), s2 = dp4a_ss(w[0], d2.x, 0);
+              s0 = dp4a_ss(w[1], d0.y, s0); s1 = dp4a_ss(w[1], d1.y, s1); s2 = dp4a_ss(w[1], d2.y, s2);
+              s0 = dp4a_ss(w[2], d0.z, s0); s1 = dp4a_ss(w[2], d1.z, s1); s2 = dp4a_ss(w[2], d2.z, s2);
+              s0 = dp4a_ss(w[3], d0.w, s0); s1 = dp4a_ss(w[3], d1.w, s1); s2 = dp4a_ss(w[3], d2.w, s2);
+              sum = block_sum(s0, s1, s2);  // |s_d| <= 16 * 128 * 128 < 2^21
+            } else {
+              int s0 = dp4a_us(w[0], d0.x, 0), s1 = dp4a_us(w[0], d1.x, 0), s2 = dp4a_us(w[0], d2.x, 0);
+              s0 = dp4a_us(w[1], d0.y, s0); s1 = dp4a_us(w[1], d1.y, s1); s2 = dp4a_us(w[1], d2.y, s2);
+              s0 = dp4a_us(w[2], d0.z, s0); s1 = dp4a_us(w[2], d1.z, s1); s2 = dp4a_us(w[2], d2.z, s2);
+              s0 = dp4a_us(w[3], d0.w, s0); s1 = dp4a_us(w[3], d1.w, s1); s2 = dp4a_us(w[3], d2.w, s2);
+              // sum(u * t) - 8 * sum(t): |.| <= 16 * 15 * 2^22 < 2^30, exact in int32
+              sum = __int2float_rn((s2 << 16) + (s1 << 8) + s0 - tsum8);
+            }
+            acc[r][t] = fmaf(scale[u][r] * e, sum, acc[r][t]);
+          }
+        }
+      }
+    }
+    if (more) {
+#pragma unroll
+      for (int u = 0; u < kStep; ++u) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          codes[u][r] = next_codes[u][r];
+          scale[u][r] = next_scale[u][r];
+        }
+      }
+    }
+  }
+
+  // ---- the 32 span sums of an output meet in a butterfly; lane (r * TM + t) % 32 stores it
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+    for (int t = 0; t < TM; ++t) {
+      float v = acc[r][t];
+#pragma unroll
+      for (int h = 16; h >= 1; h >>= 1) v += __shfl_xor_sync(0xffffffffu, v, h);
+      const long long row = row0 + r;
+      if (lane == ((r * TM + t) & 31) && row_ok[r] && t < tokens) {
+        if (p.bias != nullptr) v += p.bias[row];
+        v = apply_activation(v, p.activation);
+        store_storage(p.y, p.y_type, (token0 + t) * p.rows + row, v);
+      }
+    }
+  }
+}
+
+// bytes of digit images of a call
+size_t digit_image_bytes(long long m, long long columns) {
+  const long long chunks = (columns + kChunk - 1) / kChunk;
+  return static_cast<size_t>(m) * static_cast<size_t>(chunks) * kImageWords * sizeof(uint32_t);
+}
+
+template <int LAYOUT, int TM, int ROWS>
+qx_status launch_digits_one(const CanonicalParams& p, const uint32_t* image, cudaStream_t stream) {
+  const long long gx = (p.rows + kDigitWarps * ROWS - 1) / (kDigitWarps * ROWS);
+  const long long gy = (p.m + TM - 1) / TM;
+  if (gx > 0x7fffffffLL || gy > 65535) {
+    set_last_error_text("canonical projection: shape too large for one launch");
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  // programmatic dependent of the digit kernel in front: waits for it itself
+  cudaLaunchConfig_t config{};
+  config.gridDim = dim3(static_cast<unsigned>(gx), static_cast<unsigned>(gy));
+  config.blockDim = dim3(32 * kDigitWarps);
+  config.stream = stream;
+  cudaLaunchAttribute attribute{};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  QX_CUDA_TRY(cudaLaunchKernelEx(&config, canonical_digits_kernel<LAYOUT, TM, ROWS>, p, image));
+  count_launch();
+  return QX_STATUS_OK;
+}
+
+template <int LAYOUT, int TM>
+qx_status launch_digits_tokens(const CanonicalParams& p, const uint32_t* image, int sm_count,
+                               cudaStream_t stream) {
+  const long long token_tiles = (p.m + TM - 1) / TM;
+  const long long wanted = 10LL * sm_count;
+  // measured on 14336 x 4096 and 4096 x 4096: two rows per warp for one or two tokens (the
+  // more warps the better: 18 us against 25 us with four rows), four for a tile of four tokens
+  int rows = (TM == 4 && (p.rows + 3) / 4 * token_tiles >= wanted) ? 4 : 2;
+  // developer switch: QX_B200_CANONICAL_ROWS=2|4
+  if (const char* forced = std::getenv("QX_B200_CANONICAL_ROWS")) {
+    const int asked = forced[0] - '0';
+    if (asked == 2 || asked == 4) rows = asked;
+  }
+  if (rows == 4) return launch_digits_one<LAYOUT, TM, 4>(p, image, stream);
+  return launch_digits_one<LAYOUT, TM, 2>(p, image, stream);
+}
+
+template <int LAYOUT>
+qx_status launch_digits(const CanonicalParams& p, uint32_t* image, int sm_count,
+                        cudaStream_t stream) {
+  const long long chunks = (p.columns + kChunk - 1) / kChunk;
+  const long long blocks = p.m * chunks;
+  if (blocks > 0x7fffffffLL) {
+    set_last_error_text("canonical projection: too many tokens for one launch");
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  {
+    cudaLaunchConfig_t config{};
+    config.gridDim = dim3(static_cast<unsigned>(blocks));
+    config.blockDim = dim3(128);
+    config.stream = stream;
+    cudaLaunchAttribute attribute{};
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    QX_CUDA_TRY(cudaLaunchKernelEx(&config, canonical_digits_prepass<LAYOUT>, p, image));
+    count_launch();
+  }
+  if (p.m == 1) return launch_digits_tokens<LAYOUT, 1>(p, image, sm_count, stream);
+  if (p.m == 2) return launch_digits_tokens<LAYOUT, 2>(p, image, sm_count, stream);
+  return launch_digits_tokens<LAYOUT, 4>(p, image, sm_count, stream);
+}
+
 template <int LAYOUT, int TM, int ROWS, int WARPS>
 qx_status launch_one(const CanonicalParams& p, cudaStream_t stream) {
   const long long gx = (p.rows + WARPS * ROWS - 1) / (WARPS * ROWS);
@@ -503,9 +840,18 @@ qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_t
   const int x_vector = x_type == QX_STORAGE_F32 ? 16 : 8;
   p.vector_x = (w->columns % 4 == 0 && reinterpret_cast<uintptr_t>(x) % x_vector == 0) ? 1 : 0;
   const int sm_count = ctx->prop.multiProcessorCount;
-  return w->layout == QX_CANONICAL_INT8_SYMMETRIC
-             ? launch_layout<QX_CANONICAL_INT8_SYMMETRIC>(p, sm_count, stream)
-             : launch_layout<QX_CANONICAL_INT4_SYMMETRIC>(p, sm_count, stream);
+  if (p.groups_per_row == 1 || p.group_size % kElems == 0) {
+    // digit path: the images of the activations live behind the counters of the workspace
+    const size_t image_bytes = digit_image_bytes(m, w->columns);
+    QX_TRY(ctx->workspace.reserve(kWorkspaceCounterBytes + image_bytes));
+    uint32_t* image = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ctx->workspace.base) +
+                                                  kWorkspaceCounterBytes);
+    return int8 ? launch_digits<QX_CANONICAL_INT8_SYMMETRIC>(p, image, sm_count, stream)
+                : launch_digits<QX_CANONICAL_INT4_SYMMETRIC>(p, image, sm_count, stream);
+  }
+  // a scale group boundary inside 16 columns: float multiply-adds on decoded weights
+  return int8 ? launch_layout<QX_CANONICAL_INT8_SYMMETRIC>(p, sm_count, stream)
+              : launch_layout<QX_CANONICAL_INT4_SYMMETRIC>(p, sm_count, stream);
 }
 
 bool finite_nonnegative(const float* v, size_t count) {

@@ -88,7 +88,9 @@ def test_golden_cases_of_the_reference(qx, orc, oracle_mod, canon):
             assert agrees(y, orc.canonical_gemm(t, x, storage, m)[1], exact), (name, storage, "oracle")
             if name.startswith("t_"):  # the reference test's own shapes: its literal rule
                 assert close(y, canon[f"{name}/y_x{storage}"]), (name, storage)
-        assert qx.launch_count() - before == 3
+        # digits of the activations + projection per call; one kernel when a scale group
+        # boundary falls inside 16 columns
+        assert qx.launch_count() - before == (6 if (group % 16 == 0 or mode != GROUP) else 3)
         x32 = np.ascontiguousarray(canon[name + "/x0"])
         bias = np.ascontiguousarray(canon[name + "/bias"])
         exact_sum = orc.canonical_gemm_f64(t, x32, F32, m) + bias.astype(np.float64)[None, :]
