@@ -31,8 +31,8 @@
 // live in the device's default workspace.
 //
 // Kernels. CUDA cores; a tensor-core schedule for long prefills is not built for this path.
-// Measured on 14336 x 4096 int8 with one bf16 token: 18 us per call for both launches (the
-// digit kernel and the projection behind it), 3.2 TB/s of the weights' bytes, about half of
+// Measured on 14336 x 4096 int8 with one bf16 token: 17 us per call for both launches (the
+// digit kernel and the projection behind it), 3.4 TB/s of the weights' bytes, about half of
 // the measured copy bandwidth; the float path ran the same shape in 24 us at 10 instructions
 // per weight, bound by instruction issue.
 
@@ -43,6 +43,7 @@
 #include <cstdlib>
 #include <mutex>
 #include <new>
+#include <type_traits>
 
 #include "qx_common.cuh"
 #include "qx_gemv.cuh"
@@ -504,6 +505,26 @@ __device__ __forceinline__ SpanDigits load_span(const uint32_t* image, int lane)
   return s;
 }
 
+// sum over the lane's 16 columns of code * t from the digit words; w: the span's four code
+// words (int8), or its even / odd nibble words after the xor with 8 (int4)
+template <int LAYOUT>
+__device__ __forceinline__ float span_dot(const uint32_t (&w)[4], const uint4& d0, const uint4& d1,
+                                          const uint4& d2, int tsum8) {
+  if (LAYOUT == QX_CANONICAL_INT8_SYMMETRIC) {
+    int s0 = dp4a_ss(w[0], d0.x, 0), s1 = dp4a_ss(w[0], d1.x, 0), s2 = dp4a_ss(w[0], d2.x, 0);
+    s0 = dp4a_ss(w[1], d0.y, s0); s1 = dp4a_ss(w[1], d1.y, s1); s2 = dp4a_ss(w[1], d2.y, s2);
+    s0 = dp4a_ss(w[2], d0.z, s0); s1 = dp4a_ss(w[2], d1.z, s1); s2 = dp4a_ss(w[2], d2.z, s2);
+    s0 = dp4a_ss(w[3], d0.w, s0); s1 = dp4a_ss(w[3], d1.w, s1); s2 = dp4a_ss(w[3], d2.w, s2);
+    return block_sum(s0, s1, s2);  // |s_d| <= 16 * 128 * 128 < 2^21
+  }
+  int s0 = dp4a_us(w[0], d0.x, 0), s1 = dp4a_us(w[0], d1.x, 0), s2 = dp4a_us(w[0], d2.x, 0);
+  s0 = dp4a_us(w[1], d0.y, s0); s1 = dp4a_us(w[1], d1.y, s1); s2 = dp4a_us(w[1], d2.y, s2);
+  s0 = dp4a_us(w[2], d0.z, s0); s1 = dp4a_us(w[2], d1.z, s1); s2 = dp4a_us(w[2], d2.z, s2);
+  s0 = dp4a_us(w[3], d0.w, s0); s1 = dp4a_us(w[3], d1.w, s1); s2 = dp4a_us(w[3], d2.w, s2);
+  // sum(u * t) - 8 * sum(t): |.| <= 16 * 15 * 2^22 < 2^30, exact in int32
+  return __int2float_rn((s2 << 16) + (s1 << 8) + s0 - tsum8);
+}
+
 constexpr int kDigitWarps = 4;  // independent warps per CTA: no shared memory, no barrier
 constexpr int kStep = 1;       // chunks a lane requests at once (measured: 1 is as fast as 4)
 
@@ -565,6 +586,64 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
 #pragma unroll
     for (int t = 0; t < TM; ++t) acc[r][t] = 0.0f;
   }
+  // Whole rows, whole chunks, vector loads: the common shape, without a predicate in the loop.
+  if (p.vector_rows != 0 && row0 + ROWS <= p.rows && columns % kChunk == 0) {
+    using Vec = typename std::conditional<kInt8, uint4, uint2>::type;
+    const Vec* vec_ptr[ROWS];
+    float row_scale[ROWS];
+    const bool single = p.groups_per_row == 1;
+    const int spans_per_group = single ? 1 : group_size / kElems;
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+      vec_ptr[r] = reinterpret_cast<const Vec*>(code_ptr[r]);
+      row_scale[r] = single ? __ldg(scale_row[r]) : 0.0f;
+    }
+    Vec current[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) current[r] = __ldg(vec_ptr[r]);  // independent of the kernel in front
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int chunk = 0; chunk < chunks; ++chunk) {
+      Vec next[ROWS];
+      if (chunk + 1 < chunks) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) next[r] = __ldg(vec_ptr[r] + (chunk + 1) * 32);
+      }
+      float s[ROWS];
+      if (single) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) s[r] = row_scale[r];
+      } else {
+        const int group = (chunk * 32 + lane) / spans_per_group;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) s[r] = __ldg(scale_row[r] + group);
+      }
+      uint32_t w[ROWS][4];
+#pragma unroll
+      for (int r = 0; r < ROWS; ++r) {
+        if constexpr (kInt8) {
+          w[r][0] = current[r].x; w[r][1] = current[r].y; w[r][2] = current[r].z; w[r][3] = current[r].w;
+        } else {
+          const uint32_t a = current[r].x ^ 0x88888888u, b = current[r].y ^ 0x88888888u;
+          w[r][0] = a & 0x0F0F0F0Fu; w[r][1] = (a >> 4) & 0x0F0F0F0Fu;
+          w[r][2] = b & 0x0F0F0F0Fu; w[r][3] = (b >> 4) & 0x0F0F0F0Fu;
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < TM; ++t) {
+        const SpanDigits span = load_span(token_image[t] + chunk * kImageWords, lane);
+        const float e = t < tokens ? span.e : 0.0f;
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+          acc[r][t] = fmaf(s[r] * e, span_dot<LAYOUT>(w[r], span.d0, span.d1, span.d2, 8 * span.tsum),
+                           acc[r][t]);
+        }
+      }
+      if (chunk + 1 < chunks) {
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) current[r] = next[r];
+      }
+    }
+  } else {
   LaneCodes codes[kStep][ROWS];
   float scale[kStep][ROWS];
   fetch_codes(0, codes, scale);  // weights do not depend on the kernel in front
@@ -599,22 +678,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
           const int tsum8 = 8 * span.tsum;
 #pragma unroll
           for (int r = 0; r < ROWS; ++r) {
-            const uint32_t* w = codes[u][r].w;
-            float sum;
-            if (kInt8) {
-              int s0 = dp4a_ss(w[0], d0.x, 0), s1 = dp4a_ss(w[0], d1.x, 0), s2 = dp4a_ss(w[0], d2.x, 0);
-              s0 = dp4a_ss(w[1], d0.y, s0); s1 = dp4a_ss(w[1], d1.y, s1); s2 = dp4a_ss(w[1], d2.y, s2);
-              s0 = dp4a_ss(w[2], d0.z, s0); s1 = dp4a_ss(w[2], d1.z, s1); s2 = dp4a_ss(w[2], d2.z, s2);
-              s0 = dp4a_ss(w[3], d0.w, s0); s1 = dp4a_ss(w[3], d1.w, s1); s2 = dp4a_ss(w[3], d2.w, s2);
-              sum = block_sum(s0, s1, s2);  // |s_d| <= 16 * 128 * 128 < 2^21
-            } else {
-              int s0 = dp4a_us(w[0], d0.x, 0), s1 = dp4a_us(w[0], d1.x, 0), s2 = dp4a_us(w[0], d2.x, 0);
-              s0 = dp4a_us(w[1], d0.y, s0); s1 = dp4a_us(w[1], d1.y, s1); s2 = dp4a_us(w[1], d2.y, s2);
-              s0 = dp4a_us(w[2], d0.z, s0); s1 = dp4a_us(w[2], d1.z, s1); s2 = dp4a_us(w[2], d2.z, s2);
-              s0 = dp4a_us(w[3], d0.w, s0); s1 = dp4a_us(w[3], d1.w, s1); s2 = dp4a_us(w[3], d2.w, s2);
-              // sum(u * t) - 8 * sum(t): |.| <= 16 * 15 * 2^22 < 2^30, exact in int32
-              sum = __int2float_rn((s2 << 16) + (s1 << 8) + s0 - tsum8);
-            }
+            const float sum = span_dot<LAYOUT>(codes[u][r].w, d0, d1, d2, tsum8);
             acc[r][t] = fmaf(scale[u][r] * e, sum, acc[r][t]);
           }
         }
@@ -631,6 +695,8 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
       }
     }
   }
+
+  }  // general path
 
   // ---- the 32 span sums of an output meet in a butterfly; lane (r * TM + t) % 32 stores it
 #pragma unroll
@@ -682,11 +748,11 @@ qx_status launch_digits_one(const CanonicalParams& p, const uint32_t* image, cud
 template <int LAYOUT, int TM>
 qx_status launch_digits_tokens(const CanonicalParams& p, const uint32_t* image, int sm_count,
                                cudaStream_t stream) {
-  const long long token_tiles = (p.m + TM - 1) / TM;
-  const long long wanted = 10LL * sm_count;
-  // measured on 14336 x 4096 and 4096 x 4096: two rows per warp for one or two tokens (the
-  // more warps the better: 18 us against 25 us with four rows), four for a tile of four tokens
-  int rows = (TM == 4 && (p.rows + 3) / 4 * token_tiles >= wanted) ? 4 : 2;
+  // Two rows per warp: measured on 14336 x 4096 and 4096 x 4096 with 1 and 8 tokens, the more
+  // warps the better (17.1 us against 18.5 us with four rows for one token, 20.6 against 21.9
+  // for eight).
+  (void)sm_count;
+  int rows = 2;
   // developer switch: QX_B200_CANONICAL_ROWS=2|4
   if (const char* forced = std::getenv("QX_B200_CANONICAL_ROWS")) {
     const int asked = forced[0] - '0';
