@@ -273,6 +273,92 @@ inline Status quantize_int8(const float* x, std::int8_t* codes, float* scales, l
 
 // include/quixicore_cpu/threading.h: kept for source compatibility (the GPU path has no
 // thread pool; the value is stored and returned)
+// ---- canonical prepared projections ---------------------------------------------------
+// include/quixicore_cpu/quant_contract.h:12-38, float_storage.h:18-30, ops.h:56 (values equal)
+enum class CanonicalQuantLayout : int { kInt4Symmetric = 0, kInt8Symmetric = 2 };
+enum class QuantScaleMode : int { kNone = 0, kTensor = 1, kRow = 2, kChannel = 3, kGroup = 4 };
+enum class FloatStorageType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
+enum class LinearActivation : int { kNone = 0, kGeluErf = 1, kGeluTanh = 2, kSilu = 3, kRelu2 = 4 };
+struct FloatStorageInput {
+  const void* data = nullptr;
+  FloatStorageType type = FloatStorageType::kF32;
+  long long count = 0;
+};
+struct FloatStorageOutput {
+  void* data = nullptr;
+  FloatStorageType type = FloatStorageType::kF32;
+  long long count = 0;
+};
+// The fields of quixicore_cpu::CanonicalQuantTensor (include/quixicore_cpu/quant_import.h:24-36)
+// this path reads, as a view over the caller's arrays.
+struct CanonicalQuantTensorView {
+  CanonicalQuantLayout layout = CanonicalQuantLayout::kInt8Symmetric;
+  QuantScaleMode scale_mode = QuantScaleMode::kRow;
+  long long logical_rows = 0, logical_columns = 0, group_size = 0;
+  const std::uint8_t* data = nullptr;
+  std::size_t data_bytes = 0;
+  const float* scales = nullptr;
+  std::size_t scale_count = 0;
+};
+// CpuPackedWeights::prepare(const CanonicalQuantTensor&) (packed_weights.h) -> qx_canonical_prepare
+class CanonicalPackedWeights {
+ public:
+  CanonicalPackedWeights() = default;
+  CanonicalPackedWeights(const CanonicalPackedWeights&) = delete;
+  CanonicalPackedWeights& operator=(const CanonicalPackedWeights&) = delete;
+  ~CanonicalPackedWeights() { reset(); }
+  Status prepare(const CanonicalQuantTensorView& t) {
+    const qx_canonical_tensor view{static_cast<int>(t.layout), static_cast<int>(t.scale_mode),
+                                   t.logical_rows, t.logical_columns, t.group_size, t.data,
+                                   t.data_bytes, t.scales, t.scale_count};
+    qx_canonical_weights* fresh = nullptr;
+    const Status status = to_status(qx_canonical_prepare(&view, &fresh));
+    if (status == Status::kOk) {
+      reset();
+      handle_ = fresh;
+    }
+    return status;
+  }
+  bool ready() const noexcept { return handle_ != nullptr; }
+  void reset() noexcept {
+    qx_canonical_destroy(handle_);
+    handle_ = nullptr;
+  }
+  const qx_canonical_weights* handle() const noexcept { return handle_; }
+
+ private:
+  qx_canonical_weights* handle_ = nullptr;
+};
+// include/quixicore_cpu/qgemm.h:32-42
+inline Status qgemm_prepacked_epilogue_storage(const CanonicalPackedWeights& weights, FloatStorageInput x,
+                                               const float* bias, FloatStorageOutput y, long long m,
+                                               LinearActivation activation, Workspace* = nullptr) {
+  return to_status(qx_qgemm_prepacked_epilogue_storage(weights.handle(), x.data, static_cast<int>(x.type),
+                                                       x.count, bias, y.data, static_cast<int>(y.type),
+                                                       y.count, m, static_cast<int>(activation)));
+}
+inline Status qgemm_prepacked_storage(const CanonicalPackedWeights& weights, FloatStorageInput x,
+                                      FloatStorageOutput y, long long m, Workspace* = nullptr) {
+  return to_status(qx_qgemm_prepacked_storage(weights.handle(), x.data, static_cast<int>(x.type), x.count,
+                                              y.data, static_cast<int>(y.type), y.count, m));
+}
+// include/quixicore_cpu/quant_import.h:117-133: the view aliases the source's arrays; the row
+// sums of the codes are written to row_sums[rows]
+using SmoothQuantW8A8Source = qx_smoothquant_source;
+inline Status import_smoothquant_w8a8(const SmoothQuantW8A8Source& source, CanonicalQuantTensorView* tensor,
+                                      std::int32_t* row_sums) {
+  if (tensor == nullptr) return Status::kInvalidArgument;
+  qx_canonical_tensor view{};
+  const Status status = to_status(qx_import_smoothquant_w8a8(&source, &view, row_sums));
+  if (status == Status::kOk) {
+    *tensor = CanonicalQuantTensorView{static_cast<CanonicalQuantLayout>(view.layout),
+                                       static_cast<QuantScaleMode>(view.scale_mode), view.rows,
+                                       view.columns, view.group_size, view.data, view.data_bytes,
+                                       view.scales, view.scale_count};
+  }
+  return status;
+}
+
 inline void set_num_threads(int n) { qx_set_num_threads(n); }
 inline int num_threads() { return qx_num_threads(); }
 

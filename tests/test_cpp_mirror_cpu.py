@@ -66,6 +66,40 @@ PROGRAM = textwrap.dedent(r"""
       float scale[1];
       CHECK(quantize_int8(nullptr, codes, scale, 1, 32, 0) == Status::kInvalidArgument);
       CHECK(lowbit_gemm_w8a8(nullptr, scale, x, y, 1, 1, 32) == Status::kInvalidArgument);
+      // canonical tensors: checks of validate_canonical_quant_tensor before any device work,
+      // and the SmoothQuant importer (host only)
+      std::uint8_t cdata[64] = {0};
+      float cscales[2] = {0.5f, 0.25f};
+      CanonicalQuantTensorView view{CanonicalQuantLayout::kInt8Symmetric, QuantScaleMode::kRow, 2, 32, 32,
+                                    cdata, 64, cscales, 2};
+      CanonicalPackedWeights canonical;
+      view.data_bytes = 63;
+      CHECK(canonical.prepare(view) == Status::kInvalidShape);
+      view.data_bytes = 64;
+      view.scale_mode = QuantScaleMode::kTensor;
+      CHECK(canonical.prepare(view) == Status::kInvalidShape);     // one scale expected
+      view.scale_count = 1;
+      CHECK(canonical.prepare(view) == Status::kInvalidArgument);  // mode not served by this layout
+      view.layout = static_cast<CanonicalQuantLayout>(5);
+      CHECK(canonical.prepare(view) == Status::kUnsupportedFormat);
+      CHECK(!canonical.ready());
+      CHECK(qgemm_prepacked_storage(canonical, {x, FloatStorageType::kF32, 32}, {y, FloatStorageType::kF32, 1}, 1) ==
+            Status::kInvalidArgument);
+      CHECK(qgemm_prepacked_epilogue_storage(canonical, {x, FloatStorageType::kBF16, 32}, nullptr,
+                                             {y, FloatStorageType::kF16, 1}, 1, static_cast<LinearActivation>(7)) ==
+            Status::kInvalidArgument);
+      const std::int8_t sq_weights[4] = {-127, -64, 0, 127};
+      const float sq_scale[1] = {0.25f}, sq_act[1] = {0.125f};
+      SmoothQuantW8A8Source sq{};
+      sq.weights = sq_weights; sq.weight_count = 4; sq.weight_scales = sq_scale; sq.weight_scale_count = 1;
+      sq.activation_scales = sq_act; sq.activation_scale_count = 1; sq.rows = 1; sq.columns = 4;
+      CanonicalQuantTensorView imported;
+      std::int32_t row_sum[1] = {0};
+      CHECK(import_smoothquant_w8a8(sq, &imported, row_sum) == Status::kOk);
+      CHECK(imported.layout == CanonicalQuantLayout::kInt8Symmetric && imported.scale_mode == QuantScaleMode::kChannel);
+      CHECK(imported.group_size == 4 && imported.data_bytes == 4 && row_sum[0] == -64);
+      sq.weight_count = 3;
+      CHECK(import_smoothquant_w8a8(sq, &imported, row_sum) == Status::kInvalidShape);
       CpuPackedWeights moved = std::move(weights);
       CHECK(!moved.ready() && moved.info().rows == 0);
       set_num_threads(4);
