@@ -415,16 +415,22 @@ QX_API qx_status qx_quantize_int8_dev(const float* x_dev, int8_t* codes_dev, flo
  * The reference prepares a CanonicalQuantTensor (include/quixicore_cpu/quant_import.h:24-36)
  * with CpuPackedWeights::prepare(tensor) (src/memory/packed_weights.cpp:280-398) and runs
  * typed projections on it (include/quixicore_cpu/qgemm.h:29-42). This library serves the two
- * symmetric integer layouts of that contract:
+ * integer layouts of that contract:
  *   kInt8Symmetric  one signed byte per element, rows of `columns` bytes;
  *   kInt4Symmetric  two elements per byte, the lower K index in the low nibble, a nibble
  *                   n >= 8 meaning n - 16 (kernels/quantization/qgemm_canonical.cpp:81-84,
  *                   160-163);
+ *   kUInt4Affine    the same nibbles read as 0..15 with an f32 zero point beside every scale:
+ *                   value = scale * (nibble - zero) (qgemm_canonical.cpp:164-167) -- the layout
+ *                   the AWQ and GPTQ importers produce;
  * with f32 scales per row / output channel or per (row, group of group_size columns)
- * (scale_index, qgemm_canonical.cpp:86-115). Enum values are the reference's
+ * (scale_index, qgemm_canonical.cpp:86-115). GPTQ act-order tensors carry two optional maps of
+ * `columns` ints: group_index (packed column -> scale group) and act_order (packed column ->
+ * column of the activations), both honoured as in canonical_storage_panels
+ * (qgemm_canonical.cpp:2823-2840). Enum values are the reference's
  * (include/quixicore_cpu/quant_contract.h:12-38); every other layout is reported as
  * QX_STATUS_UNSUPPORTED_FORMAT. */
-enum { QX_CANONICAL_INT4_SYMMETRIC = 0, QX_CANONICAL_INT8_SYMMETRIC = 2 };
+enum { QX_CANONICAL_INT4_SYMMETRIC = 0, QX_CANONICAL_UINT4_AFFINE = 1, QX_CANONICAL_INT8_SYMMETRIC = 2 };
 enum { QX_SCALE_NONE = 0, QX_SCALE_TENSOR = 1, QX_SCALE_ROW = 2, QX_SCALE_CHANNEL = 3, QX_SCALE_GROUP = 4 };
 /* FloatStorageType, include/quixicore_cpu/float_storage.h:18 */
 enum { QX_STORAGE_F32 = 0, QX_STORAGE_F16 = 1, QX_STORAGE_BF16 = 2 };
@@ -445,6 +451,12 @@ typedef struct qx_canonical_tensor {
   size_t data_bytes;
   const float* scales;    /* rows (row / channel) or rows * (columns / group_size) */
   size_t scale_count;
+  const float* zero_points;   /* kUInt4Affine: one per scale; NULL / 0 otherwise */
+  size_t zero_point_count;
+  const int* group_index;     /* optional, `columns` entries (4-bit layouts only) */
+  size_t group_index_count;
+  const int* act_order;       /* optional, a permutation of 0 .. columns-1 */
+  size_t act_order_count;
 } qx_canonical_tensor;
 
 typedef struct qx_canonical_weights qx_canonical_weights;
@@ -510,6 +522,51 @@ typedef struct qx_smoothquant_source {
 } qx_smoothquant_source;
 QX_API qx_status qx_import_smoothquant_w8a8(const qx_smoothquant_source* source,
                                             qx_canonical_tensor* tensor, int32_t* row_sums_out);
+
+/* import_awq_u4, include/quixicore_cpu/quant_import.h:56-69 (quant_import_ref.cpp:840-903):
+ * AWQ GEMM checkpoints -- qweight[K, N/8] words of eight 4-bit codes in the lane order
+ * {0,4,1,5,2,6,3,7}, qzeros[K/group, N/8], scales[K/group, N] -- become a kUInt4Affine tensor
+ * [N rows, K columns] with group scales and zero points. Host-side format conversion: the
+ * caller provides data_out[N*K/2], scales_out[N*K/group] and zero_points_out[N*K/group];
+ * *tensor becomes a view of them. */
+typedef struct qx_awq_u4_source {
+  const uint32_t* qweight;
+  size_t qweight_words;
+  const uint32_t* qzeros;
+  size_t qzero_words;
+  const float* scales;
+  size_t scale_count;
+  long long input_features;
+  long long output_features;
+  long long group_size;
+} qx_awq_u4_source;
+QX_API qx_status qx_import_awq_u4(const qx_awq_u4_source* source, qx_canonical_tensor* tensor,
+                                  uint8_t* data_out, float* scales_out, float* zero_points_out);
+
+/* import_gptq_u4, include/quixicore_cpu/quant_import.h:71-92 (quant_import_ref.cpp:905-999):
+ * qweight[K/8, N], qzeros[G, N/8], scales[G, N]; V1 checkpoints store zero - 1; `symmetric`
+ * folds the zero point into signed codes (kInt4Symmetric), otherwise kUInt4Affine; group_index
+ * and act_order are passed through (the tensor view points at the source's arrays).
+ * zero_points_out may be NULL for symmetric sources. */
+typedef struct qx_gptq_u4_source {
+  const uint32_t* qweight;
+  size_t qweight_words;
+  const uint32_t* qzeros;
+  size_t qzero_words;
+  const float* scales;
+  size_t scale_count;
+  const int* group_index;
+  size_t group_index_count;
+  const int* act_order;
+  size_t act_order_count;
+  long long input_features;
+  long long output_features;
+  long long group_size;
+  int symmetric;
+  int gptq_v2;
+} qx_gptq_u4_source;
+QX_API qx_status qx_import_gptq_u4(const qx_gptq_u4_source* source, qx_canonical_tensor* tensor,
+                                   uint8_t* data_out, float* scales_out, float* zero_points_out);
 
 /* ---- threading: set_num_threads / num_threads, include/quixicore_cpu/threading.h:11-12.
  * The fork-join pool is replaced by CUDA streams; these are kept so callers link. The

@@ -275,7 +275,7 @@ inline Status quantize_int8(const float* x, std::int8_t* codes, float* scales, l
 // thread pool; the value is stored and returned)
 // ---- canonical prepared projections ---------------------------------------------------
 // include/quixicore_cpu/quant_contract.h:12-38, float_storage.h:18-30, ops.h:56 (values equal)
-enum class CanonicalQuantLayout : int { kInt4Symmetric = 0, kInt8Symmetric = 2 };
+enum class CanonicalQuantLayout : int { kInt4Symmetric = 0, kUInt4Affine = 1, kInt8Symmetric = 2 };
 enum class QuantScaleMode : int { kNone = 0, kTensor = 1, kRow = 2, kChannel = 3, kGroup = 4 };
 enum class FloatStorageType : int { kF32 = 0, kF16 = 1, kBF16 = 2 };
 enum class LinearActivation : int { kNone = 0, kGeluErf = 1, kGeluTanh = 2, kSilu = 3, kRelu2 = 4 };
@@ -299,7 +299,38 @@ struct CanonicalQuantTensorView {
   std::size_t data_bytes = 0;
   const float* scales = nullptr;
   std::size_t scale_count = 0;
+  const float* zero_points = nullptr;   // kUInt4Affine
+  std::size_t zero_point_count = 0;
+  const int* group_index = nullptr;     // GPTQ: packed column -> scale group
+  std::size_t group_index_count = 0;
+  const int* act_order = nullptr;       // GPTQ: packed column -> activation column
+  std::size_t act_order_count = 0;
 };
+inline qx_canonical_tensor to_c(const CanonicalQuantTensorView& t) {
+  return qx_canonical_tensor{static_cast<int>(t.layout), static_cast<int>(t.scale_mode), t.logical_rows,
+                             t.logical_columns, t.group_size, t.data, t.data_bytes, t.scales,
+                             t.scale_count, t.zero_points, t.zero_point_count, t.group_index,
+                             t.group_index_count, t.act_order, t.act_order_count};
+}
+inline CanonicalQuantTensorView from_c(const qx_canonical_tensor& v) {
+  CanonicalQuantTensorView t;
+  t.layout = static_cast<CanonicalQuantLayout>(v.layout);
+  t.scale_mode = static_cast<QuantScaleMode>(v.scale_mode);
+  t.logical_rows = v.rows;
+  t.logical_columns = v.columns;
+  t.group_size = v.group_size;
+  t.data = v.data;
+  t.data_bytes = v.data_bytes;
+  t.scales = v.scales;
+  t.scale_count = v.scale_count;
+  t.zero_points = v.zero_points;
+  t.zero_point_count = v.zero_point_count;
+  t.group_index = v.group_index;
+  t.group_index_count = v.group_index_count;
+  t.act_order = v.act_order;
+  t.act_order_count = v.act_order_count;
+  return t;
+}
 // CpuPackedWeights::prepare(const CanonicalQuantTensor&) (packed_weights.h) -> qx_canonical_prepare
 class CanonicalPackedWeights {
  public:
@@ -308,9 +339,7 @@ class CanonicalPackedWeights {
   CanonicalPackedWeights& operator=(const CanonicalPackedWeights&) = delete;
   ~CanonicalPackedWeights() { reset(); }
   Status prepare(const CanonicalQuantTensorView& t) {
-    const qx_canonical_tensor view{static_cast<int>(t.layout), static_cast<int>(t.scale_mode),
-                                   t.logical_rows, t.logical_columns, t.group_size, t.data,
-                                   t.data_bytes, t.scales, t.scale_count};
+    const qx_canonical_tensor view = to_c(t);
     qx_canonical_weights* fresh = nullptr;
     const Status status = to_status(qx_canonical_prepare(&view, &fresh));
     if (status == Status::kOk) {
@@ -350,12 +379,27 @@ inline Status import_smoothquant_w8a8(const SmoothQuantW8A8Source& source, Canon
   if (tensor == nullptr) return Status::kInvalidArgument;
   qx_canonical_tensor view{};
   const Status status = to_status(qx_import_smoothquant_w8a8(&source, &view, row_sums));
-  if (status == Status::kOk) {
-    *tensor = CanonicalQuantTensorView{static_cast<CanonicalQuantLayout>(view.layout),
-                                       static_cast<QuantScaleMode>(view.scale_mode), view.rows,
-                                       view.columns, view.group_size, view.data, view.data_bytes,
-                                       view.scales, view.scale_count};
-  }
+  if (status == Status::kOk) *tensor = from_c(view);
+  return status;
+}
+// include/quixicore_cpu/quant_import.h:56-92: the caller provides the arrays the view points at
+// (data N*K/2 bytes, scales and zero points N*K/group floats)
+using AwqU4Source = qx_awq_u4_source;
+using GptqU4Source = qx_gptq_u4_source;
+inline Status import_awq_u4(const AwqU4Source& source, CanonicalQuantTensorView* tensor, std::uint8_t* data,
+                            float* scales, float* zero_points) {
+  if (tensor == nullptr) return Status::kInvalidArgument;
+  qx_canonical_tensor view{};
+  const Status status = to_status(qx_import_awq_u4(&source, &view, data, scales, zero_points));
+  if (status == Status::kOk) *tensor = from_c(view);
+  return status;
+}
+inline Status import_gptq_u4(const GptqU4Source& source, CanonicalQuantTensorView* tensor, std::uint8_t* data,
+                             float* scales, float* zero_points) {
+  if (tensor == nullptr) return Status::kInvalidArgument;
+  qx_canonical_tensor view{};
+  const Status status = to_status(qx_import_gptq_u4(&source, &view, data, scales, zero_points));
+  if (status == Status::kOk) *tensor = from_c(view);
   return status;
 }
 

@@ -61,11 +61,25 @@ STORAGE_DTYPES = {0: np.float32, 1: np.uint16, 2: np.uint16}
 class CanonicalTensor:
     """The fields of a CanonicalQuantTensor the projections read."""
 
-    def __init__(self, layout, scale_mode, rows, columns, group_size, data, scales):
+    def __init__(self, layout, scale_mode, rows, columns, group_size, data, scales, zeros=None,
+                 group_index=None, act_order=None):
         self.layout, self.scale_mode = layout, scale_mode
         self.rows, self.columns, self.group_size = rows, columns, group_size
         self.data = np.ascontiguousarray(data, np.uint8).reshape(-1)
         self.scales = np.ascontiguousarray(scales, np.float32).reshape(-1)
+        self.zeros = None if zeros is None else np.ascontiguousarray(zeros, np.float32).reshape(-1)
+        self.group_index = None if group_index is None else np.ascontiguousarray(group_index, np.int32)
+        self.act_order = None if act_order is None else np.ascontiguousarray(act_order, np.int32)
+
+    def extras(self):
+        """(zeros, count, group_index, count, act_order, count) as ctypes arguments"""
+        def pair(a):
+            return (_ptr(a), 0 if a is None else a.size)
+        return pair(self.zeros) + pair(self.group_index) + pair(self.act_order)
+
+    @property
+    def plain(self):
+        return self.zeros is None and self.group_index is None and self.act_order is None
 
 
 class Oracle:
@@ -111,6 +125,12 @@ class Oracle:
         L.qxo_canonical_gemm.argtypes = [C.c_int, C.c_int, _ll, _ll, _ll, _vp, C.c_size_t, _vp,
                                          C.c_size_t, _vp, C.c_int, _ll, _vp, _vp, C.c_int, _ll,
                                          _ll, C.c_int]
+        L.qxo_canonical_gemm_ex.argtypes = [C.c_int, C.c_int, _ll, _ll, _ll, _vp, C.c_size_t, _vp,
+                                            C.c_size_t, _vp, C.c_size_t, _vp, C.c_size_t, _vp,
+                                            C.c_size_t, _vp, C.c_int, _ll, _vp, _vp, C.c_int, _ll,
+                                            _ll, C.c_int]
+        L.qxo_canonical_gemm_ex_f64.argtypes = [C.c_int, _ll, _ll, _ll, _vp, _vp, _vp, _vp, _vp, _vp,
+                                                C.c_int, _vp, _ll]
         L.qxo_canonical_gemm_f64.argtypes = [C.c_int, _ll, _ll, _ll, _vp, _vp, _vp, C.c_int, _vp, _ll]
         L.qxo_import_smoothquant_row_sums.argtypes = [_vp, C.c_size_t, _vp, C.c_size_t, _vp,
                                                       C.c_size_t, _vp, C.c_size_t, _ll, _ll, _vp]
@@ -252,17 +272,26 @@ class Oracle:
     def canonical_gemm(self, t, x, x_type, m, bias=None, y_type=0, activation=0,
                        x_count=None, y_count=None):
         y = np.zeros(max(m, 1) * t.rows, STORAGE_DTYPES.get(y_type, np.float32))
-        status = self.lib.qxo_canonical_gemm(
-            t.layout, t.scale_mode, t.rows, t.columns, t.group_size, _ptr(t.data), t.data.size,
-            _ptr(t.scales), t.scales.size, _ptr(x), x_type,
-            m * t.columns if x_count is None else x_count, _ptr(bias), _ptr(y), y_type,
-            m * t.rows if y_count is None else y_count, m, activation)
+        x_count = m * t.columns if x_count is None else x_count
+        y_count = m * t.rows if y_count is None else y_count
+        if t.plain and t.layout != 1:
+            status = self.lib.qxo_canonical_gemm(
+                t.layout, t.scale_mode, t.rows, t.columns, t.group_size, _ptr(t.data), t.data.size,
+                _ptr(t.scales), t.scales.size, _ptr(x), x_type, x_count, _ptr(bias), _ptr(y),
+                y_type, y_count, m, activation)
+        else:
+            status = self.lib.qxo_canonical_gemm_ex(
+                t.layout, t.scale_mode, t.rows, t.columns, t.group_size, _ptr(t.data), t.data.size,
+                _ptr(t.scales), t.scales.size, *t.extras(), _ptr(x), x_type, x_count, _ptr(bias),
+                _ptr(y), y_type, y_count, m, activation)
         return status, y.reshape(max(m, 1), t.rows)
 
     def canonical_gemm_f64(self, t, x, x_type, m):
         y = np.zeros((m, t.rows), np.float64)
-        self.lib.qxo_canonical_gemm_f64(t.layout, t.rows, t.columns, t.scales.size // t.rows,
-                                        _ptr(t.data), _ptr(t.scales), _ptr(x), x_type, _ptr(y), m)
+        self.lib.qxo_canonical_gemm_ex_f64(t.layout, t.rows, t.columns, t.scales.size // t.rows,
+                                           _ptr(t.data), _ptr(t.scales), _ptr(t.zeros),
+                                           _ptr(t.group_index), _ptr(t.act_order), _ptr(x), x_type,
+                                           _ptr(y), m)
         return y
 
     def import_smoothquant_row_sums(self, weights, weight_scales, activation_scales, rows, columns,
@@ -301,6 +330,15 @@ class Reference:
         L.qxref_canonical_gemm.argtypes = [C.c_int, C.c_int, _ll, _ll, _ll, _vp, C.c_size_t, _vp,
                                            C.c_size_t, _vp, C.c_int, _ll, _vp, _vp, C.c_int, _ll,
                                            _ll, C.c_int]
+        L.qxref_canonical_gemm_ex.argtypes = [C.c_int, C.c_int, _ll, _ll, _ll, _vp, C.c_size_t, _vp,
+                                              C.c_size_t, _vp, C.c_size_t, _vp, C.c_size_t, _vp,
+                                              C.c_size_t, _vp, C.c_int, _ll, _vp, _vp, C.c_int, _ll,
+                                              _ll, C.c_int]
+        L.qxref_import_awq_u4.argtypes = [_vp, C.c_size_t, _vp, C.c_size_t, _vp, C.c_size_t, _ll, _ll,
+                                          _ll, _vp, _vp, _vp, _vp]
+        L.qxref_import_gptq_u4.argtypes = [_vp, C.c_size_t, _vp, C.c_size_t, _vp, C.c_size_t, _vp,
+                                           C.c_size_t, _vp, C.c_size_t, _ll, _ll, _ll, C.c_int,
+                                           C.c_int, _vp, _vp, _vp, _vp]
         L.qxref_import_smoothquant.argtypes = [_vp, C.c_size_t, _vp, C.c_size_t, _vp, C.c_size_t,
                                                _vp, C.c_size_t, _vp, C.c_size_t, _ll, _ll, _vp, _vp,
                                                _vp, C.POINTER(C.c_int), C.POINTER(C.c_int),
@@ -432,6 +470,46 @@ class Reference:
             m * t.columns if x_count is None else x_count, _ptr(bias), _ptr(y), y_type,
             m * t.rows if y_count is None else y_count, m, activation)
         return status, y.reshape(max(m, 1), t.rows)
+
+    def canonical_gemm_ex(self, t, x, x_type, m, bias=None, y_type=0, activation=0):
+        y = np.zeros(max(m, 1) * t.rows, STORAGE_DTYPES.get(y_type, np.float32))
+        status = self.lib.qxref_canonical_gemm_ex(
+            t.layout, t.scale_mode, t.rows, t.columns, t.group_size, _ptr(t.data), t.data.size,
+            _ptr(t.scales), t.scales.size, *t.extras(), _ptr(x), x_type, m * t.columns, _ptr(bias),
+            _ptr(y), y_type, m * t.rows, m, activation)
+        return status, y.reshape(max(m, 1), t.rows)
+
+    def _imported(self, status, n, k, group, data, scales, zeros, meta, group_index, act_order):
+        if status != 0:
+            return status, None
+        groups = k // group
+        zc = int(meta[3])
+        return status, CanonicalTensor(int(meta[0]), int(meta[1]), n, k, int(meta[2]), data[:n * k // 2],
+                                       scales[:n * groups], zeros[:zc] if zc else None,
+                                       group_index if meta[4] else None, act_order if meta[5] else None)
+
+    def import_awq_u4(self, qweight, qzeros, scales, k, n, group):
+        data = np.zeros(max(n * k // 2, 1), np.uint8)
+        out_scales = np.zeros(max(scales.size, 1), np.float32)
+        zeros = np.zeros(max(scales.size, 1), np.float32)
+        meta = np.zeros(6, np.int32)
+        status = self.lib.qxref_import_awq_u4(_ptr(qweight), qweight.size, _ptr(qzeros), qzeros.size,
+                                              _ptr(scales), scales.size, k, n, group, _ptr(data),
+                                              _ptr(out_scales), _ptr(zeros), _ptr(meta))
+        return self._imported(status, n, k, group, data, out_scales, zeros, meta, None, None)
+
+    def import_gptq_u4(self, qweight, qzeros, scales, k, n, group, symmetric=False, v2=False,
+                       group_index=None, act_order=None):
+        data = np.zeros(max(n * k // 2, 1), np.uint8)
+        out_scales = np.zeros(max(scales.size, 1), np.float32)
+        zeros = np.zeros(max(scales.size, 1), np.float32)
+        meta = np.zeros(6, np.int32)
+        status = self.lib.qxref_import_gptq_u4(
+            _ptr(qweight), qweight.size, _ptr(qzeros), qzeros.size, _ptr(scales), scales.size,
+            _ptr(group_index), 0 if group_index is None else group_index.size, _ptr(act_order),
+            0 if act_order is None else act_order.size, k, n, group, int(symmetric), int(v2),
+            _ptr(data), _ptr(out_scales), _ptr(zeros), _ptr(meta))
+        return self._imported(status, n, k, group, data, out_scales, zeros, meta, group_index, act_order)
 
     def import_smoothquant(self, weights, weight_scales, activation_scales, rows, columns,
                            zero_points=None, row_sums=None):

@@ -338,4 +338,116 @@ int qxref_import_smoothquant(const int8_t* weights, size_t weight_count,
   return 0;
 }
 
+
+// tensors with zero points and the GPTQ column maps
+static qc::Status make_tensor_ex(int layout, int scale_mode, long long rows, long long columns,
+                                 long long group_size, const uint8_t* data, size_t data_bytes,
+                                 const float* scales, size_t scale_count, const float* zeros,
+                                 size_t zero_count, const int* group_index, size_t group_index_count,
+                                 const int* act_order, size_t act_order_count,
+                                 qc::CanonicalQuantTensor* tensor) {
+  tensor->metadata.layout = static_cast<qc::CanonicalQuantLayout>(layout);
+  tensor->metadata.logical_rows = rows;
+  tensor->metadata.logical_columns = columns;
+  tensor->metadata.group_size = group_size;
+  tensor->metadata.scale_mode = static_cast<qc::QuantScaleMode>(scale_mode);
+  tensor->metadata.scale_encoding = qc::QuantScaleEncoding::kFP32;
+  tensor->metadata.scale_count = scale_count;
+  tensor->metadata.zero_point_mode =
+      zero_count != 0 ? qc::QuantZeroPointMode::kFractional : qc::QuantZeroPointMode::kNone;
+  tensor->metadata.zero_point_count = zero_count;
+  tensor->metadata.group_index_count = group_index_count;
+  tensor->metadata.act_order_count = act_order_count;
+  tensor->data.assign(data, data + data_bytes);
+  tensor->scales.assign(scales, scales + scale_count);
+  if (zero_count != 0) tensor->zero_points.assign(zeros, zeros + zero_count);
+  if (group_index_count != 0) tensor->group_index.assign(group_index, group_index + group_index_count);
+  if (act_order_count != 0) tensor->act_order.assign(act_order, act_order + act_order_count);
+  return qc::validate_canonical_quant_tensor(*tensor);
+}
+
+int qxref_canonical_gemm_ex(int layout, int scale_mode, long long rows, long long columns,
+                            long long group_size, const uint8_t* data, size_t data_bytes,
+                            const float* scales, size_t scale_count, const float* zeros,
+                            size_t zero_count, const int* group_index, size_t group_index_count,
+                            const int* act_order, size_t act_order_count, const void* x,
+                            int x_type, long long x_count, const float* bias, void* y,
+                            int y_type, long long y_count, long long m, int activation) {
+  qc::CanonicalQuantTensor tensor;
+  qc::Status status = make_tensor_ex(layout, scale_mode, rows, columns, group_size, data, data_bytes,
+                                     scales, scale_count, zeros, zero_count, group_index,
+                                     group_index_count, act_order, act_order_count, &tensor);
+  if (status != qc::Status::kOk) return static_cast<int>(status);
+  qc::CpuPackedWeights prepared;
+  status = prepared.prepare(tensor);
+  if (status != qc::Status::kOk) return static_cast<int>(status);
+  return static_cast<int>(qc::qgemm_prepacked_epilogue_storage(
+      prepared, {x, static_cast<qc::FloatStorageType>(x_type), x_count}, bias,
+      {y, static_cast<qc::FloatStorageType>(y_type), y_count}, m,
+      static_cast<qc::LinearActivation>(activation)));
+}
+
+static int export_tensor(const qc::CanonicalQuantTensor& tensor, uint8_t* data_out, float* scales_out,
+                         float* zeros_out, int* meta) {
+  std::copy(tensor.data.begin(), tensor.data.end(), data_out);
+  std::copy(tensor.scales.begin(), tensor.scales.end(), scales_out);
+  std::copy(tensor.zero_points.begin(), tensor.zero_points.end(), zeros_out);
+  meta[0] = static_cast<int>(tensor.metadata.layout);
+  meta[1] = static_cast<int>(tensor.metadata.scale_mode);
+  meta[2] = static_cast<int>(tensor.metadata.group_size);
+  meta[3] = static_cast<int>(tensor.zero_points.size());
+  meta[4] = static_cast<int>(tensor.group_index.size());
+  meta[5] = static_cast<int>(tensor.act_order.size());
+  return 0;
+}
+
+int qxref_import_awq_u4(const uint32_t* qweight, size_t qweight_words, const uint32_t* qzeros,
+                        size_t qzero_words, const float* scales, size_t scale_count,
+                        long long input_features, long long output_features, long long group_size,
+                        uint8_t* data_out, float* scales_out, float* zeros_out, int* meta) {
+  qc::AwqU4Source source;
+  source.qweight = qweight;
+  source.qweight_words = qweight_words;
+  source.qzeros = qzeros;
+  source.qzero_words = qzero_words;
+  source.scales = scales;
+  source.scale_count = scale_count;
+  source.input_features = input_features;
+  source.output_features = output_features;
+  source.group_size = group_size;
+  qc::CanonicalQuantTensor tensor;
+  const qc::Status status = qc::import_awq_u4(source, &tensor);
+  if (status != qc::Status::kOk) return static_cast<int>(status);
+  return export_tensor(tensor, data_out, scales_out, zeros_out, meta);
+}
+
+int qxref_import_gptq_u4(const uint32_t* qweight, size_t qweight_words, const uint32_t* qzeros,
+                         size_t qzero_words, const float* scales, size_t scale_count,
+                         const int* group_index, size_t group_index_count, const int* act_order,
+                         size_t act_order_count, long long input_features,
+                         long long output_features, long long group_size, int symmetric,
+                         int gptq_v2, uint8_t* data_out, float* scales_out, float* zeros_out,
+                         int* meta) {
+  qc::GptqU4Source source;
+  source.qweight = qweight;
+  source.qweight_words = qweight_words;
+  source.qzeros = qzeros;
+  source.qzero_words = qzero_words;
+  source.scales = scales;
+  source.scale_count = scale_count;
+  source.group_index = group_index;
+  source.group_index_count = group_index_count;
+  source.act_order = act_order;
+  source.act_order_count = act_order_count;
+  source.input_features = input_features;
+  source.output_features = output_features;
+  source.group_size = group_size;
+  source.symmetric = symmetric != 0;
+  source.gptq_v2 = gptq_v2 != 0;
+  qc::CanonicalQuantTensor tensor;
+  const qc::Status status = qc::import_gptq_u4(source, &tensor);
+  if (status != qc::Status::kOk) return static_cast<int>(status);
+  return export_tensor(tensor, data_out, scales_out, zeros_out, meta);
+}
+
 }  // extern "C"

@@ -55,7 +55,25 @@ class CanonicalTensorView(C.Structure):
     """qx_canonical_tensor of include/qx_b200.h."""
     _fields_ = [("layout", C.c_int), ("scale_mode", C.c_int), ("rows", _ll), ("columns", _ll),
                 ("group_size", _ll), ("data", _vp), ("data_bytes", _sz), ("scales", _vp),
-                ("scale_count", _sz)]
+                ("scale_count", _sz), ("zero_points", _vp), ("zero_point_count", _sz),
+                ("group_index", _vp), ("group_index_count", _sz), ("act_order", _vp),
+                ("act_order_count", _sz)]
+
+
+class AwqU4Source(C.Structure):
+    """qx_awq_u4_source of include/qx_b200.h."""
+    _fields_ = [("qweight", _vp), ("qweight_words", _sz), ("qzeros", _vp), ("qzero_words", _sz),
+                ("scales", _vp), ("scale_count", _sz), ("input_features", _ll),
+                ("output_features", _ll), ("group_size", _ll)]
+
+
+class GptqU4Source(C.Structure):
+    """qx_gptq_u4_source of include/qx_b200.h."""
+    _fields_ = [("qweight", _vp), ("qweight_words", _sz), ("qzeros", _vp), ("qzero_words", _sz),
+                ("scales", _vp), ("scale_count", _sz), ("group_index", _vp),
+                ("group_index_count", _sz), ("act_order", _vp), ("act_order_count", _sz),
+                ("input_features", _ll), ("output_features", _ll), ("group_size", _ll),
+                ("symmetric", C.c_int), ("gptq_v2", C.c_int)]
 
 
 class SmoothQuantSource(C.Structure):
@@ -130,6 +148,8 @@ def _load():
                                                     C.c_int, _vp],
         "qx_import_smoothquant_w8a8": [C.POINTER(SmoothQuantSource),
                                        C.POINTER(CanonicalTensorView), _vp],
+        "qx_import_awq_u4": [C.POINTER(AwqU4Source), C.POINTER(CanonicalTensorView), _vp, _vp, _vp],
+        "qx_import_gptq_u4": [C.POINTER(GptqU4Source), C.POINTER(CanonicalTensorView), _vp, _vp, _vp],
         "qx_peer_alloc": [_sz, C.POINTER(_vp), _vp],
         "qx_peer_open": [_vp, C.POINTER(_vp)],
         "qx_peer_close": [_vp],
@@ -415,7 +435,7 @@ class PackedWeights:
 
 
 # ---- canonical prepared projections (CanonicalQuantTensor -> prepare -> typed projection) ----
-INT4_SYMMETRIC, INT8_SYMMETRIC = 0, 2
+INT4_SYMMETRIC, UINT4_AFFINE, INT8_SYMMETRIC = 0, 1, 2
 SCALE_ROW, SCALE_CHANNEL, SCALE_GROUP = 2, 3, 4
 F32, F16, BF16 = 0, 1, 2
 STORAGE_DTYPES = {F32: np.float32, F16: np.uint16, BF16: np.uint16}
@@ -423,12 +443,16 @@ ACT_NONE, ACT_GELU_ERF, ACT_GELU_TANH, ACT_SILU, ACT_RELU2 = range(5)
 
 
 def canonical_view(layout, scale_mode, rows, columns, group_size, data, scales,
-                   data_bytes=None, scale_count=None) -> CanonicalTensorView:
+                   data_bytes=None, scale_count=None, zeros=None, group_index=None,
+                   act_order=None) -> CanonicalTensorView:
     """A qx_canonical_tensor over numpy arrays (the arrays must outlive the view)."""
+    def count(a):
+        return 0 if a is None else a.size
     return CanonicalTensorView(layout, scale_mode, rows, columns, group_size, _np(data),
-                               (0 if data is None else data.size) if data_bytes is None else data_bytes,
-                               _np(scales),
-                               (0 if scales is None else scales.size) if scale_count is None else scale_count)
+                               count(data) if data_bytes is None else data_bytes, _np(scales),
+                               count(scales) if scale_count is None else scale_count, _np(zeros),
+                               count(zeros), _np(group_index), count(group_index), _np(act_order),
+                               count(act_order))
 
 
 class CanonicalWeights:
@@ -493,6 +517,37 @@ def import_smoothquant_w8a8(weights, weight_scales, activation_scales, rows, col
     sums = np.zeros(max(rows, 1), np.int32)
     status = lib.qx_import_smoothquant_w8a8(C.byref(source), C.byref(view), _np(sums))
     return status, view, sums[:max(rows, 0)]
+
+
+def import_awq_u4(qweight, qzeros, scales, k, n, group):
+    """-> (status, view, (data, scales, zero points) arrays the view points at)."""
+    groups = max(k // group, 1) if group > 0 else 1
+    data = np.zeros(max(n * k // 2, 1), np.uint8)
+    out_scales = np.zeros(max(n * groups, 1), np.float32)
+    zeros = np.zeros(max(n * groups, 1), np.float32)
+    source = AwqU4Source(_np(qweight), 0 if qweight is None else qweight.size, _np(qzeros),
+                         0 if qzeros is None else qzeros.size, _np(scales),
+                         0 if scales is None else scales.size, k, n, group)
+    view = CanonicalTensorView()
+    status = lib.qx_import_awq_u4(C.byref(source), C.byref(view), _np(data), _np(out_scales), _np(zeros))
+    return status, view, (data, out_scales, zeros)
+
+
+def import_gptq_u4(qweight, qzeros, scales, k, n, group, symmetric=False, v2=False,
+                   group_index=None, act_order=None):
+    groups = max(k // group, 1) if group > 0 else 1
+    data = np.zeros(max(n * k // 2, 1), np.uint8)
+    out_scales = np.zeros(max(n * groups, 1), np.float32)
+    zeros = np.zeros(max(n * groups, 1), np.float32)
+    source = GptqU4Source(_np(qweight), 0 if qweight is None else qweight.size, _np(qzeros),
+                          0 if qzeros is None else qzeros.size, _np(scales),
+                          0 if scales is None else scales.size, _np(group_index),
+                          0 if group_index is None else group_index.size, _np(act_order),
+                          0 if act_order is None else act_order.size, k, n, group, int(symmetric),
+                          int(v2))
+    view = CanonicalTensorView()
+    status = lib.qx_import_gptq_u4(C.byref(source), C.byref(view), _np(data), _np(out_scales), _np(zeros))
+    return status, view, (data, out_scales, zeros)
 
 
 def peer_alloc(nbytes: int):

@@ -44,6 +44,7 @@
 #include <mutex>
 #include <new>
 #include <type_traits>
+#include <vector>
 
 #include "qx_common.cuh"
 #include "qx_gemv.cuh"
@@ -60,6 +61,9 @@ struct qx_canonical_weights {
   size_t scale_count = 0;
   uint8_t* data = nullptr;      // device: canonical codes
   float* scales = nullptr;      // device: [rows][groups_per_row]
+  float* zeros = nullptr;       // device: [rows][groups_per_row] (kUInt4Affine), else null
+  int* group_index = nullptr;   // device: [columns] packed column -> scale group, or null
+  int* act_order = nullptr;     // device: [columns] packed column -> activation column, or null
 };
 
 namespace qx {
@@ -68,6 +72,8 @@ namespace {
 struct CanonicalParams {
   const uint8_t* data;
   const float* scales;
+  const float* zeros;        // kUInt4Affine: zero point beside every scale
+  const int* group_index;    // optional: packed column -> scale group
   const void* x;
   const float* bias;
   void* y;
@@ -144,18 +150,21 @@ __device__ __forceinline__ void decode4(const LaneCodes& codes, int j, float (&f
     f[2] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7442)) - 8388736.0f;
     f[3] = __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7443)) - 8388736.0f;
   } else {
-    const uint32_t word = codes.w[j >> 1] ^ 0x88888888u;
+    // symmetric: nibble ^ 8 = code + 8; affine: the nibble itself, 0 .. 15
+    constexpr bool kSigned = LAYOUT == QX_CANONICAL_INT4_SYMMETRIC;
+    constexpr float kOffset = kSigned ? 8388616.0f : 8388608.0f;
+    const uint32_t word = kSigned ? codes.w[j >> 1] ^ 0x88888888u : codes.w[j >> 1];
     const uint32_t lo = word & 0x0F0F0F0Fu, hi = (word >> 4) & 0x0F0F0F0Fu;
     if ((j & 1) == 0) {
-      f[0] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7440)) - 8388616.0f;
-      f[1] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7440)) - 8388616.0f;
-      f[2] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7441)) - 8388616.0f;
-      f[3] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7441)) - 8388616.0f;
+      f[0] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7440)) - kOffset;
+      f[1] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7440)) - kOffset;
+      f[2] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7441)) - kOffset;
+      f[3] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7441)) - kOffset;
     } else {
-      f[0] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7442)) - 8388616.0f;
-      f[1] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7442)) - 8388616.0f;
-      f[2] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7443)) - 8388616.0f;
-      f[3] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7443)) - 8388616.0f;
+      f[0] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7442)) - kOffset;
+      f[1] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7442)) - kOffset;
+      f[2] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7443)) - kOffset;
+      f[3] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7443)) - kOffset;
     }
   }
 }
@@ -226,14 +235,13 @@ __global__ void __launch_bounds__(32 * WARPS) canonical_gemm_kernel(const Canoni
   const long long row0 = (static_cast<long long>(blockIdx.x) * WARPS + warp) * ROWS;
   const long long token0 = static_cast<long long>(blockIdx.y) * TM;
   const int tokens = static_cast<int>(p.m - token0 < TM ? p.m - token0 : TM);
-  // one scale per lane span when a span never straddles a scale group
   const int group_size = static_cast<int>(p.group_size);
-  const bool uniform_scale = group_size % kElems == 0;
   const int chunks = (columns + kChunk - 1) / kChunk;
 
   // per row: where this lane's codes of chunk 0 start, and the row of the scale table
   const uint8_t* code_ptr[ROWS];
   const float* scale_row[ROWS];
+  const float* zero_row[ROWS];
   bool row_ok[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
@@ -242,6 +250,7 @@ __global__ void __launch_bounds__(32 * WARPS) canonical_gemm_kernel(const Canoni
     const long long safe = row_ok[r] ? row : 0;
     code_ptr[r] = p.data + safe * (kInt8 ? p.columns : p.columns / 2) + lane * (kInt8 ? kElems : kElems / 2);
     scale_row[r] = p.scales + safe * p.groups_per_row;
+    zero_row[r] = LAYOUT == QX_CANONICAL_UINT4_AFFINE ? p.zeros + safe * p.groups_per_row : nullptr;
   }
   // per staged unit of this thread: element index of chunk 0 and the shared-memory slot
   long long x_index[kUnitsPerThread];
@@ -265,21 +274,17 @@ __global__ void __launch_bounds__(32 * WARPS) canonical_gemm_kernel(const Canoni
   }
 
   LaneCodes codes[ROWS];
-  float scale[ROWS];
   float4 xr[kUnitsPerThread];
-  auto fetch = [&](int chunk, LaneCodes (&into)[ROWS], float (&scales)[ROWS]) {
+  auto fetch = [&](int chunk, LaneCodes (&into)[ROWS]) {
     const int k0 = chunk * kChunk;
     const int k_lane = k0 + lane * kElems;
-    const int group = uniform_scale ? k_lane / group_size : 0;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       if (row_ok[r] && k_lane < columns) {
         into[r] = load_codes<LAYOUT>(code_ptr[r] + (kInt8 ? k0 : k0 / 2), p.vector_rows != 0,
                                      k_lane, columns);
-        scales[r] = uniform_scale ? __ldg(scale_row[r] + group) : 0.0f;
       } else {
         into[r] = LaneCodes{{0u, 0u, 0u, 0u}};
-        scales[r] = 0.0f;
       }
     }
 #pragma unroll
@@ -289,7 +294,7 @@ __global__ void __launch_bounds__(32 * WARPS) canonical_gemm_kernel(const Canoni
                   : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     }
   };
-  fetch(0, codes, scale);
+  fetch(0, codes);
 
   for (int chunk = 0; chunk < chunks; ++chunk) {
     float4* buf = &xs[chunk & 1][0][0];
@@ -301,42 +306,11 @@ __global__ void __launch_bounds__(32 * WARPS) canonical_gemm_kernel(const Canoni
     // barrier, so every warp has finished the math of chunk - 1, the last reader of that buffer.
     __syncthreads();
     LaneCodes next_codes[ROWS];
-    float next_scale[ROWS];
-    if (chunk + 1 < chunks) fetch(chunk + 1, next_codes, next_scale);  // in flight under the math
-    if (uniform_scale) {
-      // sum of the lane's 16 columns on raw codes, scaled once: scale * sum(code * x)
-      float part[ROWS][TM];
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-#pragma unroll
-        for (int t = 0; t < TM; ++t) part[r][t] = 0.0f;
-      }
-#pragma unroll
-      for (int j = 0; j < kElems / 4; ++j) {
-        float4 xv[TM];
-#pragma unroll
-        for (int t = 0; t < TM; ++t) xv[t] = buf[t * kUnits + j * 32 + lane];
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-          float f[4];
-          decode4<LAYOUT>(codes[r], j, f);
-#pragma unroll
-          for (int t = 0; t < TM; ++t) {
-            part[r][t] = fmaf(f[0], xv[t].x, part[r][t]);
-            part[r][t] = fmaf(f[1], xv[t].y, part[r][t]);
-            part[r][t] = fmaf(f[2], xv[t].z, part[r][t]);
-            part[r][t] = fmaf(f[3], xv[t].w, part[r][t]);
-          }
-        }
-      }
-#pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-#pragma unroll
-        for (int t = 0; t < TM; ++t) acc[r][t] = fmaf(scale[r], part[r][t], acc[r][t]);
-      }
-    } else {
-      // a scale group boundary inside the span: every weight is scaled on its own, as the
-      // reference decodes it (scale * float(code), qgemm_canonical.cpp:150-176)
+    if (chunk + 1 < chunks) fetch(chunk + 1, next_codes);  // in flight under the math
+    {
+      // every weight is decoded on its own, as the reference does it: scale * float(code), or
+      // scale * (float(nibble) - zero) for the affine layout (qgemm_canonical.cpp:150-176), the
+      // group of a column from group_index when the tensor has one (scale_index, :86-115)
       const int k_lane = chunk * kChunk + lane * kElems;
 #pragma unroll
       for (int j = 0; j < kElems / 4; ++j) {
@@ -350,8 +324,14 @@ __global__ void __launch_bounds__(32 * WARPS) canonical_gemm_kernel(const Canoni
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             const int k = k_lane + 4 * j + c;
-            const float s = (row_ok[r] && k < columns) ? scale_row[r][k / group_size] : 0.0f;
-            f[c] = __fmul_rn(s, f[c]);
+            float s = 0.0f, z = 0.0f;
+            if (row_ok[r] && k < columns) {
+              const int group = p.group_index != nullptr ? p.group_index[k]
+                                                         : (p.groups_per_row == 1 ? 0 : k / group_size);
+              s = scale_row[r][group];
+              if (LAYOUT == QX_CANONICAL_UINT4_AFFINE) z = zero_row[r][group];
+            }
+            f[c] = __fmul_rn(s, LAYOUT == QX_CANONICAL_UINT4_AFFINE ? __fsub_rn(f[c], z) : f[c]);
           }
 #pragma unroll
           for (int t = 0; t < TM; ++t) {
@@ -365,10 +345,7 @@ __global__ void __launch_bounds__(32 * WARPS) canonical_gemm_kernel(const Canoni
     }
     if (chunk + 1 < chunks) {
 #pragma unroll
-      for (int r = 0; r < ROWS; ++r) {
-        codes[r] = next_codes[r];
-        scale[r] = next_scale[r];
-      }
+      for (int r = 0; r < ROWS; ++r) codes[r] = next_codes[r];
     }
   }
 
@@ -509,7 +486,7 @@ __device__ __forceinline__ SpanDigits load_span(const uint32_t* image, int lane)
 // words (int8), or its even / odd nibble words after the xor with 8 (int4)
 template <int LAYOUT>
 __device__ __forceinline__ float span_dot(const uint32_t (&w)[4], const uint4& d0, const uint4& d1,
-                                          const uint4& d2, int tsum8) {
+                                          const uint4& d2, int tsum, float zero) {
   if (LAYOUT == QX_CANONICAL_INT8_SYMMETRIC) {
     int s0 = dp4a_ss(w[0], d0.x, 0), s1 = dp4a_ss(w[0], d1.x, 0), s2 = dp4a_ss(w[0], d2.x, 0);
     s0 = dp4a_ss(w[1], d0.y, s0); s1 = dp4a_ss(w[1], d1.y, s1); s2 = dp4a_ss(w[1], d2.y, s2);
@@ -521,8 +498,16 @@ __device__ __forceinline__ float span_dot(const uint32_t (&w)[4], const uint4& d
   s0 = dp4a_us(w[1], d0.y, s0); s1 = dp4a_us(w[1], d1.y, s1); s2 = dp4a_us(w[1], d2.y, s2);
   s0 = dp4a_us(w[2], d0.z, s0); s1 = dp4a_us(w[2], d1.z, s1); s2 = dp4a_us(w[2], d2.z, s2);
   s0 = dp4a_us(w[3], d0.w, s0); s1 = dp4a_us(w[3], d1.w, s1); s2 = dp4a_us(w[3], d2.w, s2);
-  // sum(u * t) - 8 * sum(t): |.| <= 16 * 15 * 2^22 < 2^30, exact in int32
-  return __int2float_rn((s2 << 16) + (s1 << 8) + s0 - tsum8);
+  // sum(u * t): |.| <= 16 * 15 * 2^22 < 2^30, exact in int32
+  const int ut = (s2 << 16) + (s1 << 8) + s0;
+  if (LAYOUT == QX_CANONICAL_INT4_SYMMETRIC) return __int2float_rn(ut - 8 * tsum);  // u = code + 8
+  // affine: sum((u - zero) * t) = sum(u * t) - zero * sum(t); exact in int32 for the usual
+  // integer zero points 0 .. 15 (|.| < 2^31), in f32 for a fractional one
+  const int whole = __float2int_rn(zero);
+  if (zero == static_cast<float>(whole) && whole >= 0 && whole <= 15) {
+    return __int2float_rn(ut - whole * tsum);
+  }
+  return fmaf(-zero, __int2float_rn(tsum), __int2float_rn(ut));
 }
 
 constexpr int kDigitWarps = 4;  // independent warps per CTA: no shared memory, no barrier
@@ -532,6 +517,8 @@ template <int LAYOUT, int TM, int ROWS>
 __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
     const CanonicalParams p, const uint32_t* __restrict__ image) {
   constexpr bool kInt8 = LAYOUT == QX_CANONICAL_INT8_SYMMETRIC;
+  constexpr bool kAffine = LAYOUT == QX_CANONICAL_UINT4_AFFINE;
+  constexpr uint32_t kNibbleXor = LAYOUT == QX_CANONICAL_INT4_SYMMETRIC ? 0x88888888u : 0u;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int columns = static_cast<int>(p.columns);
@@ -543,6 +530,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
 
   const uint8_t* code_ptr[ROWS];
   const float* scale_row[ROWS];
+  const float* zero_row[ROWS];
   bool row_ok[ROWS];
 #pragma unroll
   for (int r = 0; r < ROWS; ++r) {
@@ -551,6 +539,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
     const long long safe = row_ok[r] ? row : 0;
     code_ptr[r] = p.data + safe * (kInt8 ? p.columns : p.columns / 2) + lane * (kInt8 ? kElems : kElems / 2);
     scale_row[r] = p.scales + safe * p.groups_per_row;
+    zero_row[r] = kAffine ? p.zeros + safe * p.groups_per_row : nullptr;
   }
   // the images of this CTA's tokens: [token][chunk]
   const uint32_t* token_image[TM];
@@ -560,7 +549,8 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
   }
 
   // A step is kStep consecutive chunks: a lane requests its 16 bytes of each of them at once.
-  auto fetch_codes = [&](int step, LaneCodes (&into)[kStep][ROWS], float (&scales)[kStep][ROWS]) {
+  auto fetch_codes = [&](int step, LaneCodes (&into)[kStep][ROWS], float (&scales)[kStep][ROWS],
+                         float (&zeros)[kStep][ROWS]) {
 #pragma unroll
     for (int u = 0; u < kStep; ++u) {
       const int k0 = (step * kStep + u) * kChunk;
@@ -568,10 +558,12 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
       const int group = p.groups_per_row == 1 ? 0 : k_lane / group_size;
 #pragma unroll
       for (int r = 0; r < ROWS; ++r) {
+        zeros[u][r] = 0.0f;
         if (row_ok[r] && k_lane < columns) {
           into[u][r] = load_codes<LAYOUT>(code_ptr[r] + (kInt8 ? k0 : k0 / 2), p.vector_rows != 0,
                                           k_lane, columns);
           scales[u][r] = __ldg(scale_row[r] + group);
+          if (kAffine) zeros[u][r] = __ldg(zero_row[r] + group);
         } else {
           into[u][r] = LaneCodes{{0u, 0u, 0u, 0u}};
           scales[u][r] = 0.0f;
@@ -590,13 +582,14 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
   if (p.vector_rows != 0 && row0 + ROWS <= p.rows && columns % kChunk == 0) {
     using Vec = typename std::conditional<kInt8, uint4, uint2>::type;
     const Vec* vec_ptr[ROWS];
-    float row_scale[ROWS];
+    float row_scale[ROWS], row_zero[ROWS];
     const bool single = p.groups_per_row == 1;
     const int spans_per_group = single ? 1 : group_size / kElems;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
       vec_ptr[r] = reinterpret_cast<const Vec*>(code_ptr[r]);
       row_scale[r] = single ? __ldg(scale_row[r]) : 0.0f;
+      row_zero[r] = (single && kAffine) ? __ldg(zero_row[r]) : 0.0f;
     }
     Vec current[ROWS];
 #pragma unroll
@@ -608,14 +601,20 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) next[r] = __ldg(vec_ptr[r] + (chunk + 1) * 32);
       }
-      float s[ROWS];
+      float s[ROWS], z[ROWS];
       if (single) {
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) s[r] = row_scale[r];
+        for (int r = 0; r < ROWS; ++r) {
+          s[r] = row_scale[r];
+          z[r] = row_zero[r];
+        }
       } else {
         const int group = (chunk * 32 + lane) / spans_per_group;
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) s[r] = __ldg(scale_row[r] + group);
+        for (int r = 0; r < ROWS; ++r) {
+          s[r] = __ldg(scale_row[r] + group);
+          z[r] = kAffine ? __ldg(zero_row[r] + group) : 0.0f;
+        }
       }
       uint32_t w[ROWS][4];
 #pragma unroll
@@ -623,7 +622,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
         if constexpr (kInt8) {
           w[r][0] = current[r].x; w[r][1] = current[r].y; w[r][2] = current[r].z; w[r][3] = current[r].w;
         } else {
-          const uint32_t a = current[r].x ^ 0x88888888u, b = current[r].y ^ 0x88888888u;
+          const uint32_t a = current[r].x ^ kNibbleXor, b = current[r].y ^ kNibbleXor;
           w[r][0] = a & 0x0F0F0F0Fu; w[r][1] = (a >> 4) & 0x0F0F0F0Fu;
           w[r][2] = b & 0x0F0F0F0Fu; w[r][3] = (b >> 4) & 0x0F0F0F0Fu;
         }
@@ -634,7 +633,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
         const float e = t < tokens ? span.e : 0.0f;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-          acc[r][t] = fmaf(s[r] * e, span_dot<LAYOUT>(w[r], span.d0, span.d1, span.d2, 8 * span.tsum),
+          acc[r][t] = fmaf(s[r] * e, span_dot<LAYOUT>(w[r], span.d0, span.d1, span.d2, span.tsum, z[r]),
                            acc[r][t]);
         }
       }
@@ -645,16 +644,16 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
     }
   } else {
   LaneCodes codes[kStep][ROWS];
-  float scale[kStep][ROWS];
-  fetch_codes(0, codes, scale);  // weights do not depend on the kernel in front
+  float scale[kStep][ROWS], zero[kStep][ROWS];
+  fetch_codes(0, codes, scale, zero);  // weights do not depend on the kernel in front
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   const int steps = (chunks + kStep - 1) / kStep;
   for (int step = 0; step < steps; ++step) {
     const bool more = step + 1 < steps;
     LaneCodes next_codes[kStep][ROWS];
-    float next_scale[kStep][ROWS];
-    if (more) fetch_codes(step + 1, next_codes, next_scale);  // HBM loads in flight under the math
+    float next_scale[kStep][ROWS], next_zero[kStep][ROWS];
+    if (more) fetch_codes(step + 1, next_codes, next_scale, next_zero);  // HBM loads in flight under the math
 #pragma unroll
     for (int u = 0; u < kStep; ++u) {
       const int chunk = step * kStep + u;
@@ -663,7 +662,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
           // split every code word into its even and odd nibbles
 #pragma unroll
           for (int r = 0; r < ROWS; ++r) {
-            const uint32_t a = codes[u][r].w[0] ^ 0x88888888u, b = codes[u][r].w[1] ^ 0x88888888u;
+            const uint32_t a = codes[u][r].w[0] ^ kNibbleXor, b = codes[u][r].w[1] ^ kNibbleXor;
             codes[u][r].w[0] = a & 0x0F0F0F0Fu;
             codes[u][r].w[1] = (a >> 4) & 0x0F0F0F0Fu;
             codes[u][r].w[2] = b & 0x0F0F0F0Fu;
@@ -675,10 +674,9 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
           const SpanDigits span = load_span(token_image[t] + chunk * kImageWords, lane);
           const uint4 d0 = span.d0, d1 = span.d1, d2 = span.d2;
           const float e = t < tokens ? span.e : 0.0f;
-          const int tsum8 = 8 * span.tsum;
 #pragma unroll
           for (int r = 0; r < ROWS; ++r) {
-            const float sum = span_dot<LAYOUT>(codes[u][r].w, d0, d1, d2, tsum8);
+            const float sum = span_dot<LAYOUT>(codes[u][r].w, d0, d1, d2, span.tsum, zero[u][r]);
             acc[r][t] = fmaf(scale[u][r] * e, sum, acc[r][t]);
           }
         }
@@ -691,6 +689,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
         for (int r = 0; r < ROWS; ++r) {
           codes[u][r] = next_codes[u][r];
           scale[u][r] = next_scale[u][r];
+          zero[u][r] = next_zero[u][r];
         }
       }
     }
@@ -871,6 +870,28 @@ bool known_activation(int activation) {
   return activation >= QX_ACTIVATION_NONE && activation <= QX_ACTIVATION_RELU2;
 }
 
+// GPTQ act-order: packed column k of the weights multiplies activation column order[k]
+// (canonical_storage_panels, qgemm_canonical.cpp:2823-2840). The activations are gathered
+// once per call into packed order (f32), so that the kernels read them in order.
+__global__ void __launch_bounds__(256) gather_activations_kernel(const void* __restrict__ x,
+                                                                 int x_type,
+                                                                 const int* __restrict__ order,
+                                                                 float* __restrict__ out,
+                                                                 long long columns) {
+  const long long token = blockIdx.y;
+  for (long long k = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; k < columns;
+       k += 256LL * gridDim.x) {
+    out[token * columns + k] = load_storage(x, x_type, token * columns + order[k]);
+  }
+}
+
+template <int LAYOUT>
+qx_status launch_any(const CanonicalParams& p, bool digits, uint32_t* image, int sm_count,
+                     cudaStream_t stream) {
+  if (digits) return launch_digits<LAYOUT>(p, image, sm_count, stream);
+  return launch_layout<LAYOUT>(p, sm_count, stream);
+}
+
 qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_type,
                            const float* bias, void* y, int y_type, long long m, int activation,
                            cudaStream_t stream) {
@@ -880,13 +901,15 @@ qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_t
     set_last_error_text("canonical projection: weights were prepared on another device");
     return QX_STATUS_INVALID_ARGUMENT;
   }
-  if (w->columns > (1LL << 30)) {
-    set_last_error_text("canonical projection: more than 2^30 columns");
+  if (w->columns > (1LL << 30) || m > 65535) {
+    set_last_error_text("canonical projection: more than 2^30 columns or 65535 tokens");
     return QX_STATUS_INVALID_SHAPE;
   }
   CanonicalParams p{};
   p.data = w->data;
   p.scales = w->scales;
+  p.zeros = w->zeros;
+  p.group_index = w->group_index;
   p.x = x;
   p.bias = bias;
   p.y = y;
@@ -903,21 +926,41 @@ qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_t
   const int code_vector = int8 ? 16 : 8;
   p.vector_rows = (row_bytes % code_vector == 0 &&
                    reinterpret_cast<uintptr_t>(w->data) % code_vector == 0) ? 1 : 0;
-  const int x_vector = x_type == QX_STORAGE_F32 ? 16 : 8;
-  p.vector_x = (w->columns % 4 == 0 && reinterpret_cast<uintptr_t>(x) % x_vector == 0) ? 1 : 0;
-  const int sm_count = ctx->prop.multiProcessorCount;
-  if (p.groups_per_row == 1 || p.group_size % kElems == 0) {
-    // digit path: the images of the activations live behind the counters of the workspace
-    const size_t image_bytes = digit_image_bytes(m, w->columns);
-    QX_TRY(ctx->workspace.reserve(kWorkspaceCounterBytes + image_bytes));
-    uint32_t* image = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ctx->workspace.base) +
-                                                  kWorkspaceCounterBytes);
-    return int8 ? launch_digits<QX_CANONICAL_INT8_SYMMETRIC>(p, image, sm_count, stream)
-                : launch_digits<QX_CANONICAL_INT4_SYMMETRIC>(p, image, sm_count, stream);
+  // digit path: one scale (and zero point) per 16 columns, groups in column order; otherwise
+  // float multiply-adds on weights decoded one by one
+  const bool digits = w->group_index == nullptr &&
+                      (p.groups_per_row == 1 || p.group_size % kElems == 0);
+  // workspace behind its counters: [gathered activations (act-order)][digit images]
+  const size_t gather_bytes =
+      w->act_order != nullptr ? align_up(static_cast<size_t>(m) * w->columns * sizeof(float), 256) : 0;
+  const size_t image_bytes = digits ? digit_image_bytes(m, w->columns) : 0;
+  uint32_t* image = nullptr;
+  if (gather_bytes + image_bytes != 0) {
+    QX_TRY(ctx->workspace.reserve(kWorkspaceCounterBytes + gather_bytes + image_bytes));
+    uint8_t* scratch = static_cast<uint8_t*>(ctx->workspace.base) + kWorkspaceCounterBytes;
+    image = reinterpret_cast<uint32_t*>(scratch + gather_bytes);
+    if (w->act_order != nullptr) {
+      float* gathered = reinterpret_cast<float*>(scratch);
+      const unsigned gx = static_cast<unsigned>(w->columns + 255) / 256;
+      gather_activations_kernel<<<dim3(gx < 64 ? gx : 64, static_cast<unsigned>(m)), 256, 0, stream>>>(
+          x, x_type, w->act_order, gathered, w->columns);
+      count_launch();
+      QX_CUDA_TRY(cudaGetLastError());
+      p.x = gathered;
+      p.x_type = QX_STORAGE_F32;
+    }
   }
-  // a scale group boundary inside 16 columns: float multiply-adds on decoded weights
-  return int8 ? launch_layout<QX_CANONICAL_INT8_SYMMETRIC>(p, sm_count, stream)
-              : launch_layout<QX_CANONICAL_INT4_SYMMETRIC>(p, sm_count, stream);
+  const int x_vector = p.x_type == QX_STORAGE_F32 ? 16 : 8;
+  p.vector_x = (w->columns % 4 == 0 && reinterpret_cast<uintptr_t>(p.x) % x_vector == 0) ? 1 : 0;
+  const int sm_count = ctx->prop.multiProcessorCount;
+  switch (w->layout) {
+    case QX_CANONICAL_INT8_SYMMETRIC:
+      return launch_any<QX_CANONICAL_INT8_SYMMETRIC>(p, digits, image, sm_count, stream);
+    case QX_CANONICAL_INT4_SYMMETRIC:
+      return launch_any<QX_CANONICAL_INT4_SYMMETRIC>(p, digits, image, sm_count, stream);
+    default:
+      return launch_any<QX_CANONICAL_UINT4_AFFINE>(p, digits, image, sm_count, stream);
+  }
 }
 
 bool finite_nonnegative(const float* v, size_t count) {
@@ -936,12 +979,23 @@ bool finite_all(const float* v, size_t count) {
 // Shape checks shared by prepare and the entry points.
 qx_status validate_tensor(const qx_canonical_tensor* t, long long* groups_per_row,
                           long long* group_size) {
-  if (t->layout != QX_CANONICAL_INT8_SYMMETRIC && t->layout != QX_CANONICAL_INT4_SYMMETRIC) {
+  if (t->layout != QX_CANONICAL_INT8_SYMMETRIC && t->layout != QX_CANONICAL_INT4_SYMMETRIC &&
+      t->layout != QX_CANONICAL_UINT4_AFFINE) {
     return QX_STATUS_UNSUPPORTED_FORMAT;
   }
+  const bool four_bit = t->layout != QX_CANONICAL_INT8_SYMMETRIC;
   if (!valid_product2(t->rows, t->columns)) return QX_STATUS_INVALID_SHAPE;
   if (t->group_size < 0 || (t->group_size > 0 && t->columns % t->group_size != 0)) {
     return QX_STATUS_INVALID_SHAPE;
+  }
+  // the optional column maps (src/memory/quant_contract.cpp:120-137): full length, and only
+  // for the 4-bit layouts
+  if ((t->act_order_count != 0 && t->act_order_count != static_cast<size_t>(t->columns)) ||
+      (t->group_index_count != 0 && t->group_index_count != static_cast<size_t>(t->columns))) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  if ((t->group_index_count != 0 || t->act_order_count != 0) && !four_bit) {
+    return QX_STATUS_INVALID_ARGUMENT;
   }
   // validate_quant_metadata counts the scales its mode implies first
   // (src/memory/quant_contract.cpp:176-208) ...
@@ -973,6 +1027,10 @@ qx_status validate_tensor(const qx_canonical_tensor* t, long long* groups_per_ro
     default: return QX_STATUS_INVALID_ARGUMENT;
   }
   if (t->scale_count != expected_scales) return QX_STATUS_INVALID_SHAPE;
+  // one zero point per scale for the affine layout, none otherwise (quant_contract.cpp:213-218)
+  if (t->zero_point_count != (t->layout == QX_CANONICAL_UINT4_AFFINE ? expected_scales : 0)) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
   // ... then validate_canonical_quant_tensor accepts row, channel and group scales for the
   // integer layouts (kernels/quantization/quant_import_ref.cpp:406-421)
   if (t->scale_mode != QX_SCALE_ROW && t->scale_mode != QX_SCALE_CHANNEL &&
@@ -980,13 +1038,34 @@ qx_status validate_tensor(const qx_canonical_tensor* t, long long* groups_per_ro
     return QX_STATUS_INVALID_ARGUMENT;
   }
   size_t expected = rows * columns;
-  if (t->layout == QX_CANONICAL_INT4_SYMMETRIC) {
+  if (four_bit) {
     if ((t->columns & 1) != 0) return QX_STATUS_INVALID_SHAPE;
     expected /= 2;
   }
   if (t->data_bytes != expected) return QX_STATUS_INVALID_SHAPE;
-  if (t->data == nullptr || t->scales == nullptr) return QX_STATUS_INVALID_ARGUMENT;
-  if (!finite_nonnegative(t->scales, t->scale_count)) return QX_STATUS_INVALID_SHAPE;
+  if (t->data == nullptr || t->scales == nullptr ||
+      (t->zero_point_count != 0 && t->zero_points == nullptr) ||
+      (t->group_index_count != 0 && t->group_index == nullptr) ||
+      (t->act_order_count != 0 && t->act_order == nullptr)) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  if (!finite_nonnegative(t->scales, t->scale_count) ||
+      !finite_all(t->zero_points, t->zero_point_count)) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  // act_order is a permutation of the columns, group_index names existing groups
+  // (quant_import_ref.cpp:477-490)
+  if (t->act_order_count != 0) {
+    std::vector<uint8_t> seen(static_cast<size_t>(t->columns), 0);
+    for (size_t i = 0; i < t->act_order_count; ++i) {
+      const int v = t->act_order[i];
+      if (v < 0 || v >= t->columns || seen[static_cast<size_t>(v)] != 0) return QX_STATUS_INVALID_ARGUMENT;
+      seen[static_cast<size_t>(v)] = 1;
+    }
+  }
+  for (size_t i = 0; i < t->group_index_count; ++i) {
+    if (t->group_index[i] < 0 || t->group_index[i] >= groups) return QX_STATUS_INVALID_ARGUMENT;
+  }
   *groups_per_row = groups;
   *group_size = size;
   return QX_STATUS_OK;
@@ -1017,10 +1096,14 @@ qx_status qx_canonical_prepare(const qx_canonical_tensor* tensor, qx_canonical_w
   w->groups_per_row = groups;
   w->data_bytes = tensor->data_bytes;
   w->scale_count = tensor->scale_count;
-  // one allocation: codes, then the scale table on a 256-byte boundary
+  // one allocation: codes, then every table on a 256-byte boundary
   const size_t scale_offset = align_up(tensor->data_bytes, 256);
+  const size_t zero_offset = scale_offset + align_up(tensor->scale_count * sizeof(float), 256);
+  const size_t group_offset = zero_offset + align_up(tensor->zero_point_count * sizeof(float), 256);
+  const size_t order_offset = group_offset + align_up(tensor->group_index_count * sizeof(int), 256);
+  const size_t total = order_offset + align_up(tensor->act_order_count * sizeof(int), 256);
   void* block = nullptr;
-  cudaError_t err = cudaMalloc(&block, scale_offset + tensor->scale_count * sizeof(float));
+  cudaError_t err = cudaMalloc(&block, total);
   if (err != cudaSuccess) {
     set_last_error("cudaMalloc(canonical weights)", err);
     delete w;
@@ -1028,13 +1111,20 @@ qx_status qx_canonical_prepare(const qx_canonical_tensor* tensor, qx_canonical_w
   }
   w->data = static_cast<uint8_t*>(block);
   w->scales = reinterpret_cast<float*>(w->data + scale_offset);
+  if (tensor->zero_point_count != 0) w->zeros = reinterpret_cast<float*>(w->data + zero_offset);
+  if (tensor->group_index_count != 0) w->group_index = reinterpret_cast<int*>(w->data + group_offset);
+  if (tensor->act_order_count != 0) w->act_order = reinterpret_cast<int*>(w->data + order_offset);
   std::lock_guard<std::mutex> lock(ctx->mutex);
-  err = cudaMemcpyAsync(w->data, tensor->data, tensor->data_bytes, cudaMemcpyHostToDevice,
-                        ctx->stream);
-  if (err == cudaSuccess) {
-    err = cudaMemcpyAsync(w->scales, tensor->scales, tensor->scale_count * sizeof(float),
-                          cudaMemcpyHostToDevice, ctx->stream);
-  }
+  auto upload = [&](void* dst, const void* src, size_t bytes) {
+    if (err == cudaSuccess && bytes != 0) {
+      err = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream);
+    }
+  };
+  upload(w->data, tensor->data, tensor->data_bytes);
+  upload(w->scales, tensor->scales, tensor->scale_count * sizeof(float));
+  upload(w->zeros, tensor->zero_points, tensor->zero_point_count * sizeof(float));
+  upload(w->group_index, tensor->group_index, tensor->group_index_count * sizeof(int));
+  upload(w->act_order, tensor->act_order, tensor->act_order_count * sizeof(int));
   if (err == cudaSuccess) err = cudaStreamSynchronize(ctx->stream);
   if (err != cudaSuccess) {
     set_last_error("upload of canonical weights", err);
@@ -1159,7 +1249,149 @@ qx_status qx_import_smoothquant_w8a8(const qx_smoothquant_source* source,
   tensor->data_bytes = elements;
   tensor->scales = source->weight_scales;
   tensor->scale_count = source->weight_scale_count;
+  tensor->zero_points = nullptr;
+  tensor->zero_point_count = 0;
+  tensor->group_index = nullptr;
+  tensor->group_index_count = 0;
+  tensor->act_order = nullptr;
+  tensor->act_order_count = 0;
   return QX_STATUS_OK;
+}
+
+namespace {
+void put_nibble(uint8_t* bytes, size_t element, unsigned code) {
+  const int shift = static_cast<int>(4 * (element & 1));
+  bytes[element / 2] = static_cast<uint8_t>((bytes[element / 2] & ~(0x0fu << shift)) |
+                                            ((code & 0x0fu) << shift));
+}
+// the view a 4-bit importer returns over the caller's output arrays
+void fill_view(qx_canonical_tensor* t, int layout, long long n, long long k, long long group,
+               const uint8_t* data, const float* scales, const float* zeros, size_t groups) {
+  t->layout = layout;
+  t->scale_mode = QX_SCALE_GROUP;
+  t->rows = n;
+  t->columns = k;
+  t->group_size = group;
+  t->data = data;
+  t->data_bytes = static_cast<size_t>(n) * static_cast<size_t>(k) / 2;
+  t->scales = scales;
+  t->scale_count = static_cast<size_t>(n) * groups;
+  t->zero_points = zeros;
+  t->zero_point_count = zeros != nullptr ? static_cast<size_t>(n) * groups : 0;
+  t->group_index = nullptr;
+  t->group_index_count = 0;
+  t->act_order = nullptr;
+  t->act_order_count = 0;
+}
+}  // namespace
+
+qx_status qx_import_awq_u4(const qx_awq_u4_source* source, qx_canonical_tensor* tensor,
+                           uint8_t* data_out, float* scales_out, float* zero_points_out) {
+  // checks of import_awq_u4, quant_import_ref.cpp:842-860
+  if (source == nullptr || tensor == nullptr || data_out == nullptr || scales_out == nullptr ||
+      zero_points_out == nullptr || source->qweight == nullptr || source->qzeros == nullptr ||
+      source->scales == nullptr || source->input_features <= 0 || source->output_features <= 0 ||
+      source->group_size <= 0 || source->input_features % source->group_size != 0 ||
+      source->output_features % 8 != 0 || source->input_features % 2 != 0) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  const size_t k = static_cast<size_t>(source->input_features);
+  const size_t n = static_cast<size_t>(source->output_features);
+  const size_t groups = k / static_cast<size_t>(source->group_size);
+  if (source->qweight_words != k * (n / 8) || source->qzero_words != groups * (n / 8) ||
+      source->scale_count != groups * n || !finite_all(source->scales, source->scale_count)) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  // a negative scale fails validate_canonical_quant_tensor (quant_import_ref.cpp:470-476)
+  if (!finite_nonnegative(source->scales, source->scale_count)) return QX_STATUS_INVALID_SHAPE;
+  // AWQ packs output channel o of a word at nibble kAwqReverseOrder[o & 7] (:17, :869-880)
+  static const int kAwqReverseOrder[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+  for (size_t i = 0; i < n * k / 2; ++i) data_out[i] = 0;
+  for (size_t output = 0; output < n; ++output) {
+    const size_t word_column = output / 8;
+    const int lane = kAwqReverseOrder[output & 7];
+    for (size_t input = 0; input < k; ++input) {
+      const uint32_t word = source->qweight[input * (n / 8) + word_column];
+      put_nibble(data_out, output * k + input, (word >> (4 * lane)) & 0x0fu);
+    }
+    for (size_t group = 0; group < groups; ++group) {
+      const uint32_t word = source->qzeros[group * (n / 8) + word_column];
+      scales_out[output * groups + group] = source->scales[group * n + output];
+      zero_points_out[output * groups + group] = static_cast<float>((word >> (4 * lane)) & 0x0fu);
+    }
+  }
+  fill_view(tensor, QX_CANONICAL_UINT4_AFFINE, source->output_features, source->input_features,
+            source->group_size, data_out, scales_out, zero_points_out, groups);
+  return QX_STATUS_OK;
+}
+
+qx_status qx_import_gptq_u4(const qx_gptq_u4_source* source, qx_canonical_tensor* tensor,
+                            uint8_t* data_out, float* scales_out, float* zero_points_out) {
+  // checks of import_gptq_u4, quant_import_ref.cpp:907-930
+  if (source == nullptr || tensor == nullptr || data_out == nullptr || scales_out == nullptr ||
+      source->qweight == nullptr || source->qzeros == nullptr || source->scales == nullptr ||
+      source->input_features <= 0 || source->output_features <= 0 ||
+      source->input_features % 8 != 0 || source->output_features % 8 != 0 ||
+      source->group_size <= 0 || source->input_features % source->group_size != 0 ||
+      (source->symmetric == 0 && zero_points_out == nullptr)) {
+    return QX_STATUS_INVALID_ARGUMENT;
+  }
+  const size_t k = static_cast<size_t>(source->input_features);
+  const size_t n = static_cast<size_t>(source->output_features);
+  const size_t groups = k / static_cast<size_t>(source->group_size);
+  if (source->qweight_words != (k / 8) * n || source->qzero_words != groups * (n / 8) ||
+      source->scale_count != groups * n ||
+      (source->group_index_count != 0 &&
+       (source->group_index == nullptr || source->group_index_count != k)) ||
+      (source->act_order_count != 0 &&
+       (source->act_order == nullptr || source->act_order_count != k)) ||
+      !finite_all(source->scales, source->scale_count)) {
+    return QX_STATUS_INVALID_SHAPE;
+  }
+  const bool symmetric = source->symmetric != 0;
+  auto zero_of = [&](size_t group, size_t output) {
+    const uint32_t word = source->qzeros[group * (n / 8) + output / 8];
+    int zero = static_cast<int>((word >> (4 * (output & 7))) & 0x0fu);
+    if (source->gptq_v2 == 0) zero = (zero + 1) & 0x0f;  // V1 checkpoints store zero - 1
+    return zero;
+  };
+  for (size_t i = 0; i < n * k / 2; ++i) data_out[i] = 0;
+  for (size_t output = 0; output < n; ++output) {
+    for (size_t input = 0; input < k; ++input) {
+      const uint32_t word = source->qweight[(input / 8) * n + output];
+      const int raw = static_cast<int>((word >> (4 * (input & 7))) & 0x0fu);
+      int code = raw;
+      if (symmetric) {
+        // the zero point is folded into a signed code (:947-959)
+        const size_t zero_group = source->group_index_count == 0
+                                      ? input / static_cast<size_t>(source->group_size)
+                                      : static_cast<size_t>(source->group_index[input]);
+        if (zero_group >= groups) return QX_STATUS_INVALID_ARGUMENT;
+        int folded = raw - zero_of(zero_group, output);
+        folded = folded < -8 ? -8 : (folded > 7 ? 7 : folded);
+        code = folded & 0x0f;
+      }
+      put_nibble(data_out, output * k + input, static_cast<unsigned>(code));
+    }
+    for (size_t group = 0; group < groups; ++group) {
+      scales_out[output * groups + group] = source->scales[group * n + output];
+      if (!symmetric) zero_points_out[output * groups + group] = static_cast<float>(zero_of(group, output));
+    }
+  }
+  fill_view(tensor, symmetric ? QX_CANONICAL_INT4_SYMMETRIC : QX_CANONICAL_UINT4_AFFINE,
+            source->output_features, source->input_features, source->group_size, data_out,
+            scales_out, symmetric ? nullptr : zero_points_out, groups);
+  if (source->group_index_count != 0) {
+    tensor->group_index = source->group_index;
+    tensor->group_index_count = k;
+  }
+  if (source->act_order_count != 0) {
+    tensor->act_order = source->act_order;
+    tensor->act_order_count = k;
+  }
+  // what validate_canonical_quant_tensor then rejects (quant_import_ref.cpp:470-490)
+  long long groups_checked = 0, size_checked = 0;
+  return validate_tensor(tensor, &groups_checked, &size_checked);
 }
 
 }  // extern "C"

@@ -115,6 +115,77 @@ def main():
     out["smoothquant/imported_meta"] = np.array([t.layout, t.scale_mode, t.group_size], np.int64)
     out["smoothquant/imported_data"] = t.data
     out["smoothquant/imported_row_sums"] = sums
+    # ---- AWQ / GPTQ: the fragments of the reference's importer test and table
+    # (tests/correctness/test_quant_import.cpp:148-247, rows awq_u4 / gptq_u4 of the .tsv), and
+    # seeded checkpoints run through the reference's projection
+    for row_name in ("awq_u4", "gptq_u4"):
+        for r in rows:
+            if r[0] == row_name:
+                out[f"import_table/{r[0]}/{r[1]}/codes"] = np.frombuffer(bytes.fromhex(r[4]), np.uint8)
+    k = n = 8
+    frag = {}
+    frag["awq"] = ref.import_awq_u4(np.full(k, 0x76543210, np.uint32), np.array([0x33333333], np.uint32),
+                                    np.full(n, 0.25, np.float32), k, n, 8)
+    frag["gptq_v1"] = ref.import_gptq_u4(np.full(n, 0x76543210, np.uint32), np.array([0x22222222], np.uint32),
+                                         np.full(n, 0.5, np.float32), k, n, 8)
+    gi = np.array([1, 1, 1, 1, 0, 0, 0, 0], np.int32)
+    ao = np.array([4, 5, 6, 7, 0, 1, 2, 3], np.int32)
+    frag["gptq_v2_sym"] = ref.import_gptq_u4(
+        np.full(n, 0x76543210, np.uint32), np.array([0x88888888] * 2, np.uint32),
+        np.concatenate([np.full(n, 1.0, np.float32), np.full(n, 2.0, np.float32)]), k, n, 4,
+        symmetric=True, v2=True, group_index=gi, act_order=ao)
+    for name, (status, t) in frag.items():
+        assert status == 0, name
+        out[f"fragment/{name}/meta"] = np.array([t.layout, t.scale_mode, t.group_size], np.int64)
+        out[f"fragment/{name}/data"] = t.data
+        out[f"fragment/{name}/scales"] = t.scales
+        out[f"fragment/{name}/zeros"] = np.zeros(0, np.float32) if t.zeros is None else t.zeros
+
+    seeded = []
+    for kind, k, n, group, m, seed in (("awq", 256, 64, 64, 3, 1), ("gptq_v1", 512, 40, 128, 5, 2),
+                                      ("gptq_v2", 1024, 24, 32, 2, 3), ("gptq_sym_order", 128, 16, 32, 3, 4),
+                                      ("gptq_order", 256, 16, 64, 2, 5)):
+        rng = np.random.Generator(np.random.Philox(key=[seed, 777]))
+        groups = k // group
+        scales = rng.uniform(0.005, 0.05, groups * n).astype(np.float32)
+        qzeros = rng.integers(0, 2 ** 32, groups * (n // 8), dtype=np.uint64).astype(np.uint32)
+        name = f"checkpoint/{kind}_k{k}_n{n}_g{group}_m{m}"
+        if kind == "awq":
+            qweight = rng.integers(0, 2 ** 32, k * (n // 8), dtype=np.uint64).astype(np.uint32)
+            status, t = ref.import_awq_u4(qweight, qzeros, scales, k, n, group)
+            extra = {}
+        else:
+            qweight = rng.integers(0, 2 ** 32, (k // 8) * n, dtype=np.uint64).astype(np.uint32)
+            extra = {}
+            if "order" in kind:
+                # act-order checkpoint: a permutation of the columns; packed column i belongs to
+                # the group of the logical column it came from
+                order = rng.permutation(k).astype(np.int32)
+                extra = {"act_order": order, "group_index": (order // group).astype(np.int32)}
+            status, t = ref.import_gptq_u4(qweight, qzeros, scales, k, n, group,
+                                           symmetric="sym" in kind, v2=kind != "gptq_v1", **extra)
+        assert status == 0, (kind, status)
+        seeded.append(name)
+        out[name + "/qweight"], out[name + "/qzeros"], out[name + "/qscales"] = qweight, qzeros, scales
+        for key, value in extra.items():
+            out[f"{name}/{key}"] = value
+        out[name + "/meta"] = np.array([t.layout, t.scale_mode, n, k, t.group_size, m,
+                                        int("sym" in kind), int(kind != "gptq_v1")], np.int64)
+        out[name + "/data"], out[name + "/scales"] = t.data, t.scales
+        out[name + "/zeros"] = np.zeros(0, np.float32) if t.zeros is None else t.zeros
+        x = rng.standard_normal((m, k)).astype(np.float32)
+        bias = rng.standard_normal(n).astype(np.float32)
+        out[name + "/x0"], out[name + "/bias"] = x, bias
+        status, y = ref.canonical_gemm_ex(t, x, F32, m)
+        assert status == 0
+        out[name + "/y_x0"] = y
+        xb = encode(ref, x, BF16)
+        out[name + "/x2"] = xb
+        status, y = ref.canonical_gemm_ex(t, np.ascontiguousarray(xb), BF16, m, bias=bias, y_type=BF16,
+                                          activation=3)
+        assert status == 0
+        out[name + "/y_x2_silu_bf16"] = y
+    out["checkpoints"] = np.array(seeded)
     np.savez_compressed(os.path.join(HERE, "golden_canonical.npz"), **out)
     print("wrote golden_canonical.npz:", len(names), "cases")
 

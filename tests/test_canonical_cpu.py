@@ -218,3 +218,128 @@ def test_prepare_rejects_bad_tensors_without_a_device(qx):
     assert qx.lib.qx_qgemm_prepacked_storage(None, x.ctypes.data, F32, k, x.ctypes.data, F32, n, 1) == 3
     assert qx.lib.qx_qgemm_prepacked_epilogue_storage(None, x.ctypes.data, F32, k, None, x.ctypes.data,
                                                       F32, n, 1, 9) == 3
+
+
+# ---- AWQ / GPTQ importers and the affine layout -----------------------------------------------
+
+UINT4 = 1
+
+
+def _checkpoint(canon, name):
+    meta = [int(v) for v in canon[name + "/meta"]]
+    layout, mode, n, k, group, m, symmetric, v2 = meta
+    extra = {key: np.ascontiguousarray(canon[f"{name}/{key}"]) for key in ("group_index", "act_order")
+             if f"{name}/{key}" in canon}
+    return dict(layout=layout, mode=mode, n=n, k=k, group=group, m=m, symmetric=bool(symmetric),
+                v2=bool(v2), extra=extra, awq="/awq_" in name,
+                qweight=np.ascontiguousarray(canon[name + "/qweight"]),
+                qzeros=np.ascontiguousarray(canon[name + "/qzeros"]),
+                qscales=np.ascontiguousarray(canon[name + "/qscales"]))
+
+
+def _import(qx, c):
+    if c["awq"]:
+        return qx.import_awq_u4(c["qweight"], c["qzeros"], c["qscales"], c["k"], c["n"], c["group"])
+    return qx.import_gptq_u4(c["qweight"], c["qzeros"], c["qscales"], c["k"], c["n"], c["group"],
+                             symmetric=c["symmetric"], v2=c["v2"], **c["extra"])
+
+
+def test_awq_gptq_importers_match_reference_bits(qx, canon):
+    # the fragments of the reference's importer test, whose codes its golden table lists
+    k = n = 8
+    status, view, (data, scales, zeros) = qx.import_awq_u4(
+        np.full(k, 0x76543210, np.uint32), np.array([0x33333333], np.uint32),
+        np.full(n, 0.25, np.float32), k, n, 8)
+    assert status == 0 and (view.layout, view.scale_mode, view.group_size) == (UINT4, GROUP, 8)
+    assert np.array_equal(data, canon["import_table/awq_u4/group8_reverse_lane/codes"])
+    assert np.array_equal(data, canon["fragment/awq/data"])
+    assert np.array_equal(zeros, canon["fragment/awq/zeros"]) and np.all(zeros == 3.0)
+    assert np.array_equal(scales, canon["fragment/awq/scales"])
+    status, view, (data, scales, zeros) = qx.import_gptq_u4(
+        np.full(n, 0x76543210, np.uint32), np.array([0x22222222], np.uint32),
+        np.full(n, 0.5, np.float32), k, n, 8)
+    assert status == 0 and view.layout == UINT4
+    assert np.array_equal(data[:4], canon["import_table/gptq_u4/v1_asymmetric/codes"])
+    assert np.array_equal(data, canon["fragment/gptq_v1/data"]) and np.all(zeros == 3.0)
+    gi = np.array([1, 1, 1, 1, 0, 0, 0, 0], np.int32)
+    ao = np.array([4, 5, 6, 7, 0, 1, 2, 3], np.int32)
+    status, view, (data, scales, zeros) = qx.import_gptq_u4(
+        np.full(n, 0x76543210, np.uint32), np.array([0x88888888] * 2, np.uint32),
+        np.concatenate([np.full(n, 1.0, np.float32), np.full(n, 2.0, np.float32)]), k, n, 4,
+        symmetric=True, v2=True, group_index=gi, act_order=ao)
+    assert status == 0 and view.layout == INT4 and view.zero_point_count == 0
+    assert (view.group_index_count, view.act_order_count) == (8, 8)
+    assert np.array_equal(data, canon["fragment/gptq_v2_sym/data"])
+    assert np.array_equal(scales, canon["fragment/gptq_v2_sym/scales"])
+    # seeded checkpoints
+    for name in canon["checkpoints"]:
+        c = _checkpoint(canon, str(name))
+        status, view, (data, scales, zeros) = _import(qx, c)
+        assert status == 0, name
+        assert (view.layout, view.scale_mode, view.group_size) == (c["layout"], c["mode"], c["group"])
+        assert np.array_equal(data, canon[str(name) + "/data"]), name
+        assert np.array_equal(scales.view(np.uint32), canon[str(name) + "/scales"].view(np.uint32))
+        want_zeros = canon[str(name) + "/zeros"]
+        assert view.zero_point_count == want_zeros.size
+        if want_zeros.size:
+            assert np.array_equal(zeros, want_zeros)
+
+
+def test_awq_gptq_importer_checks(qx):
+    k, n, group = 16, 8, 8
+    qw = np.zeros(k * (n // 8), np.uint32)
+    qz = np.zeros((k // group) * (n // 8), np.uint32)
+    sc = np.ones((k // group) * n, np.float32)
+    assert qx.import_awq_u4(qw, qz, sc, k, n, group)[0] == 0
+    assert qx.import_awq_u4(None, qz, sc, k, n, group)[0] == 3
+    assert qx.import_awq_u4(qw, qz, sc, k, 12, group)[0] == 3          # N not a multiple of 8
+    assert qx.import_awq_u4(qw, qz, sc, k, n, 5)[0] == 3               # group does not divide K
+    assert qx.import_awq_u4(qw[:-1], qz, sc, k, n, group)[0] == 1
+    assert qx.import_awq_u4(qw, qz, sc[:-1], k, n, group)[0] == 1
+    bad = sc.copy()
+    bad[3] = np.nan
+    assert qx.import_awq_u4(qw, qz, bad, k, n, group)[0] == 1
+    gq = np.zeros((k // 8) * n, np.uint32)
+    assert qx.import_gptq_u4(gq, qz, sc, k, n, group)[0] == 0
+    assert qx.import_gptq_u4(gq, qz, sc, 12, n, 4)[0] == 3             # K not a multiple of 8
+    assert qx.import_gptq_u4(gq[:-1], qz, sc, k, n, group)[0] == 1
+    assert qx.import_gptq_u4(gq, qz, sc, k, n, group, group_index=np.zeros(3, np.int32))[0] == 1
+    assert qx.import_gptq_u4(gq, qz, sc, k, n, group, act_order=np.zeros(k, np.int32))[0] == 3  # not a permutation
+    assert qx.import_gptq_u4(gq, qz, sc, k, n, group, group_index=np.full(k, 9, np.int32))[0] == 3
+
+
+def test_importers_match_reference_library(qx, ref):
+    rng = np.random.default_rng(21)
+    k, n, group = 64, 16, 16
+    groups = k // group
+    sc = rng.uniform(0.01, 0.1, groups * n).astype(np.float32)
+    qz = rng.integers(0, 2 ** 32, groups * (n // 8), dtype=np.uint64).astype(np.uint32)
+    qw = rng.integers(0, 2 ** 32, k * (n // 8), dtype=np.uint64).astype(np.uint32)
+    s1, view, (data, scales, zeros) = qx.import_awq_u4(qw, qz, sc, k, n, group)
+    s2, t = ref.import_awq_u4(qw, qz, sc, k, n, group)
+    assert s1 == s2 == 0 and np.array_equal(data, t.data) and np.array_equal(zeros, t.zeros)
+    gq = rng.integers(0, 2 ** 32, (k // 8) * n, dtype=np.uint64).astype(np.uint32)
+    for symmetric in (False, True):
+        for v2 in (False, True):
+            s1, view, (data, scales, zeros) = qx.import_gptq_u4(gq, qz, sc, k, n, group, symmetric, v2)
+            s2, t = ref.import_gptq_u4(gq, qz, sc, k, n, group, symmetric, v2)
+            assert s1 == s2 == 0 and view.layout == t.layout
+            assert np.array_equal(data, t.data) and np.array_equal(scales, t.scales)
+            if not symmetric:
+                assert np.array_equal(zeros, t.zeros)
+
+
+def test_oracle_affine_and_act_order_within_reference_tolerance(orc, oracle_mod, canon):
+    for name in canon["checkpoints"]:
+        name = str(name)
+        c = _checkpoint(canon, name)
+        zeros = canon[name + "/zeros"]
+        t = oracle_mod.CanonicalTensor(c["layout"], c["mode"], c["n"], c["k"], c["group"],
+                                       canon[name + "/data"], canon[name + "/scales"],
+                                       zeros if zeros.size else None, c["extra"].get("group_index"),
+                                       c["extra"].get("act_order"))
+        x = np.ascontiguousarray(canon[name + "/x0"])
+        status, y = orc.canonical_gemm(t, x, F32, c["m"])
+        assert status == 0
+        exact = orc.canonical_gemm_f64(t, x, F32, c["m"])
+        assert close(y, exact) and close(canon[name + "/y_x0"], exact), name

@@ -208,3 +208,94 @@ def test_smoothquant_import_feeds_both_routes(qx, orc, oracle_mod):
     _, want, _ = orc.int8_gemm(codes.reshape(rows, cols), xq, ws, np.full(m, acts[0], np.float32),
                                m, rows, cols)
     assert np.array_equal(y8.view(np.uint32), np.asarray(want, np.float32).view(np.uint32))
+
+
+# ---- kUInt4Affine, AWQ / GPTQ checkpoints, act-order ------------------------------------------
+
+UINT4 = 1
+
+
+def test_awq_gptq_checkpoints_through_import_prepare_and_projection(qx, orc, oracle_mod, canon):
+    for name in canon["checkpoints"]:
+        name = str(name)
+        layout, mode, n, k, group, m, symmetric, v2 = (int(v) for v in canon[name + "/meta"])
+        extra = {key: np.ascontiguousarray(canon[f"{name}/{key}"]) for key in ("group_index", "act_order")
+                 if f"{name}/{key}" in canon}
+        qweight, qzeros, qscales = (np.ascontiguousarray(canon[f"{name}/{key}"])
+                                    for key in ("qweight", "qzeros", "qscales"))
+        if "/awq_" in name:
+            status, view, arrays = qx.import_awq_u4(qweight, qzeros, qscales, k, n, group)
+        else:
+            status, view, arrays = qx.import_gptq_u4(qweight, qzeros, qscales, k, n, group,
+                                                     symmetric=bool(symmetric), v2=bool(v2), **extra)
+        assert status == qx.OK, name
+        w = qx.CanonicalWeights()
+        assert w.prepare(view) == qx.OK, qx.last_error()
+        zeros = canon[name + "/zeros"]
+        t = oracle_mod.CanonicalTensor(layout, mode, n, k, group, canon[name + "/data"],
+                                       canon[name + "/scales"], zeros if zeros.size else None,
+                                       extra.get("group_index"), extra.get("act_order"))
+        x = np.ascontiguousarray(canon[name + "/x0"])
+        status, y = w.qgemm_storage(x, F32, m)
+        assert status == qx.OK, qx.last_error()
+        exact = orc.canonical_gemm_f64(t, x, F32, m)
+        assert close(y, exact), (name, "f64")
+        assert agrees(y, canon[name + "/y_x0"], exact), (name, "reference")
+        # bf16 in, bias + SiLU, bf16 out
+        xb = np.ascontiguousarray(canon[name + "/x2"])
+        bias = np.ascontiguousarray(canon[name + "/bias"])
+        status, yb = w.qgemm_storage(xb, BF16, m, y_type=BF16, bias=bias, activation=3)
+        assert status == qx.OK, qx.last_error()
+        exact_b = activation_f64(orc.canonical_gemm_f64(t, xb, BF16, m) + bias.astype(np.float64)[None, :], 3)
+        assert close(widen(yb, BF16), exact_b, OUT_TOLERANCE[BF16]), (name, "bf16 f64")
+        assert agrees(widen(yb, BF16), widen(canon[name + "/y_x2_silu_bf16"], BF16), exact_b,
+                      OUT_TOLERANCE[BF16]), (name, "bf16 reference")
+        w.reset()
+
+
+@pytest.mark.parametrize("case", [(4096, 4096, 128, 1), (14336, 4096, 128, 1), (1000, 1056, 32, 5),
+                                  (300, 2080, 16, 3), (64, 72, 8, 2), (96, 1024, 1024, 9)])
+def test_affine_seeded_shapes_against_float64(qx, orc, oracle_mod, case):
+    n, k, group, m = case
+    rng = np.random.Generator(np.random.Philox(key=[n + k, group * 10 + m]))
+    data = rng.integers(0, 256, n * k // 2, dtype=np.uint8)
+    groups = k // group
+    scales = rng.uniform(0.002, 0.03, n * groups).astype(np.float32)
+    zeros = rng.integers(0, 16, n * groups).astype(np.float32)
+    zeros[::7] += 0.5  # fractional zero points take the f32 branch
+    t = oracle_mod.CanonicalTensor(UINT4, GROUP, n, k, group, data, scales, zeros)
+    w = qx.CanonicalWeights()
+    assert w.prepare(qx.canonical_view(UINT4, GROUP, n, k, group, data, scales, zeros=zeros)) == qx.OK, \
+        qx.last_error()
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    status, y = w.qgemm_storage(x, F32, m)
+    assert status == qx.OK, qx.last_error()
+    exact = orc.canonical_gemm_f64(t, x, F32, m)
+    assert close(y, exact), case
+    if n * k * m <= 1 << 25:
+        seq = orc.canonical_gemm(t, x, F32, m)[1]
+        assert np.abs(y - exact).max() <= max(2 * np.abs(seq - exact).max(), 2e-6 * np.abs(exact).max())
+
+
+def test_affine_prepare_checks(qx):
+    n, k, group = 4, 32, 16
+    data, scales = np.zeros(n * k // 2, np.uint8), np.ones(n * 2, np.float32)
+    zeros = np.ones(n * 2, np.float32)
+    w = qx.CanonicalWeights()
+    assert w.prepare(qx.canonical_view(UINT4, GROUP, n, k, group, data, scales, zeros=zeros)) == 0
+    assert w.prepare(qx.canonical_view(UINT4, GROUP, n, k, group, data, scales)) == 1           # zero points missing
+    assert w.prepare(qx.canonical_view(INT4, GROUP, n, k, group, data, scales, zeros=zeros)) == 1  # none expected
+    order = np.arange(k, dtype=np.int32)
+    assert w.prepare(qx.canonical_view(UINT4, GROUP, n, k, group, data, scales, zeros=zeros,
+                                       act_order=order[:-1])) == 1
+    order[0] = 1
+    assert w.prepare(qx.canonical_view(UINT4, GROUP, n, k, group, data, scales, zeros=zeros,
+                                       act_order=order)) == 3
+    assert w.prepare(qx.canonical_view(UINT4, GROUP, n, k, group, data, scales, zeros=zeros,
+                                       group_index=np.full(k, 2, np.int32))) == 3
+    codes8 = np.zeros(n * k, np.uint8)
+    assert w.prepare(qx.canonical_view(INT8, ROW, n, k, k, codes8, scales[:n],
+                                       act_order=np.arange(k, dtype=np.int32))) == 3
+    bad = zeros.copy()
+    bad[1] = np.inf
+    assert w.prepare(qx.canonical_view(UINT4, GROUP, n, k, group, data, scales, zeros=bad)) == 1

@@ -70,8 +70,11 @@ PROGRAM = textwrap.dedent(r"""
       // and the SmoothQuant importer (host only)
       std::uint8_t cdata[64] = {0};
       float cscales[2] = {0.5f, 0.25f};
-      CanonicalQuantTensorView view{CanonicalQuantLayout::kInt8Symmetric, QuantScaleMode::kRow, 2, 32, 32,
-                                    cdata, 64, cscales, 2};
+      CanonicalQuantTensorView view;
+      view.layout = CanonicalQuantLayout::kInt8Symmetric;
+      view.scale_mode = QuantScaleMode::kRow;
+      view.logical_rows = 2; view.logical_columns = 32; view.group_size = 32;
+      view.data = cdata; view.data_bytes = 64; view.scales = cscales; view.scale_count = 2;
       CanonicalPackedWeights canonical;
       view.data_bytes = 63;
       CHECK(canonical.prepare(view) == Status::kInvalidShape);
@@ -100,6 +103,21 @@ PROGRAM = textwrap.dedent(r"""
       CHECK(imported.group_size == 4 && imported.data_bytes == 4 && row_sum[0] == -64);
       sq.weight_count = 3;
       CHECK(import_smoothquant_w8a8(sq, &imported, row_sum) == Status::kInvalidShape);
+      // the AWQ fragment of the reference's importer test (test_quant_import.cpp:148-185)
+      std::uint32_t awq_weight[8], awq_zero[1] = {0x33333333u};
+      float awq_scale[8], awq_out_scale[8], awq_out_zero[8];
+      for (int i = 0; i < 8; ++i) { awq_weight[i] = 0x76543210u; awq_scale[i] = 0.25f; }
+      std::uint8_t awq_data[32];
+      AwqU4Source awq{};
+      awq.qweight = awq_weight; awq.qweight_words = 8; awq.qzeros = awq_zero; awq.qzero_words = 1;
+      awq.scales = awq_scale; awq.scale_count = 8; awq.input_features = 8; awq.output_features = 8; awq.group_size = 8;
+      CHECK(import_awq_u4(awq, &imported, awq_data, awq_out_scale, awq_out_zero) == Status::kOk);
+      CHECK(imported.layout == CanonicalQuantLayout::kUInt4Affine && imported.zero_point_count == 8);
+      CHECK(awq_data[0] == 0x00 && awq_data[4] == 0x44 && awq_data[28] == 0x77 && awq_out_zero[5] == 3.0f);
+      awq.output_features = 12;
+      CHECK(import_awq_u4(awq, &imported, awq_data, awq_out_scale, awq_out_zero) == Status::kInvalidArgument);
+      GptqU4Source gptq{};
+      CHECK(import_gptq_u4(gptq, &imported, awq_data, awq_out_scale, awq_out_zero) == Status::kInvalidArgument);
       CpuPackedWeights moved = std::move(weights);
       CHECK(!moved.ready() && moved.info().rows == 0);
       set_num_threads(4);
