@@ -1019,13 +1019,14 @@ def _extra_lowbit(qx, wl, torch, hbm_peak):
 
 
 def _extra_canonical(qx, wl, torch, hbm_peak):
-    """Canonical prepared projections (kInt8Symmetric with channel scales, kInt4Symmetric with
-    groups of 128) with bf16 activations and outputs, bias and SiLU, at decode batches.
+    """Canonical prepared projections (kInt8Symmetric with channel scales, kInt4Symmetric and
+    kUInt4Affine with groups of 128) with bf16 activations and outputs, bias and SiLU, at decode
+    batches.
     Algorithmic bytes: codes + scales + X + bias + Y. Weight copies rotate (> L2)."""
     out = {}
     for layout, group, m, n, k in ((qx.INT8_SYMMETRIC, 0, 1, 4096, 4096), (qx.INT8_SYMMETRIC, 0, 1, 14336, 4096),
                                    (qx.INT8_SYMMETRIC, 0, 8, 4096, 4096), (qx.INT4_SYMMETRIC, 128, 1, 14336, 4096),
-                                   (qx.INT4_SYMMETRIC, 128, 8, 4096, 4096)):
+                                   (qx.INT4_SYMMETRIC, 128, 8, 4096, 4096), (qx.UINT4_AFFINE, 128, 1, 14336, 4096)):
         rng = np.random.default_rng(n + m)
         code_bytes = n * k if layout == qx.INT8_SYMMETRIC else n * k // 2
         groups = 1 if group == 0 else k // group
@@ -1034,9 +1035,12 @@ def _extra_canonical(qx, wl, torch, hbm_peak):
         for _ in range(copies):
             data = rng.integers(0, 256, code_bytes, dtype=np.uint8)
             scales = rng.uniform(0.001, 0.01, n * groups).astype(np.float32)
+            zeros = (rng.integers(0, 16, n * groups).astype(np.float32)
+                     if layout == qx.UINT4_AFFINE else None)
             h = qx.CanonicalWeights()
             mode = qx.SCALE_CHANNEL if group == 0 else qx.SCALE_GROUP
-            qx.check(h.prepare(qx.canonical_view(layout, mode, n, k, group or k, data, scales)), "prepare")
+            qx.check(h.prepare(qx.canonical_view(layout, mode, n, k, group or k, data, scales,
+                                                 zeros=zeros)), "prepare")
             handles.append(h)
         xd = torch.from_numpy(rng.standard_normal((m, k), dtype=np.float32)).cuda().to(torch.bfloat16)
         bias = torch.from_numpy(rng.standard_normal(n, dtype=np.float32)).cuda()
@@ -1044,8 +1048,10 @@ def _extra_canonical(qx, wl, torch, hbm_peak):
         sec = _time_calls(torch, lambda i: qx.check(
             handles[i % copies].qgemm_storage_dev(xd, qx.BF16, yd, qx.BF16, m, bias=bias,
                                                   activation=qx.ACT_SILU), "canonical"), 4 * copies)
-        nbytes = code_bytes + 4 * n * groups + 2 * m * k + 4 * n + 2 * m * n
-        name = ("int8" if layout == qx.INT8_SYMMETRIC else "int4g128") + f"_m{m}_n{n}_k{k}"
+        nbytes = (code_bytes + 4 * n * groups * (2 if layout == qx.UINT4_AFFINE else 1) + 2 * m * k +
+                  4 * n + 2 * m * n)
+        name = {qx.INT8_SYMMETRIC: "int8", qx.INT4_SYMMETRIC: "int4g128",
+                qx.UINT4_AFFINE: "uint4affine_g128"}[layout] + f"_m{m}_n{n}_k{k}"
         out[name] = {"us": sec * 1e6, "gbs": nbytes / sec / 1e9,
                      "frac_of_measured_hbm": nbytes / sec / 1e9 / hbm_peak,
                      "launches": 2}  # the digits of the activations, then the projection

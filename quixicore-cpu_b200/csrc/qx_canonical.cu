@@ -1,14 +1,16 @@
-// Canonical prepared projections for the symmetric integer layouts (kInt8Symmetric,
-// kInt4Symmetric) with typed input / output, bias and activation epilogue, and the
-// SmoothQuant importer that produces such a tensor.
+// Canonical prepared projections for the integer layouts kInt8Symmetric, kInt4Symmetric and
+// kUInt4Affine (zero points; GPTQ group index and act-order) with typed input / output, bias
+// and activation epilogue, and the SmoothQuant, AWQ and GPTQ importers that produce such
+// tensors.
 //
-// Replaces, for these two layouts,
+// Replaces, for these layouts,
 //   CpuPackedWeights::prepare(const CanonicalQuantTensor&)   src/memory/packed_weights.cpp:280-398
 //   qgemm_prepacked_storage / qgemm_prepacked_epilogue_storage
 //                                   kernels/quantization/qgemm_canonical.cpp:4460-4648
 //   canonical_storage_panels (the portable schedule)         qgemm_canonical.cpp:2745-2863
 //   store_projection_output / projection_activation          qgemm_canonical.cpp:361-379, 2570-2581
 //   import_smoothquant_w8a8          kernels/quantization/quant_import_ref.cpp:1051-1116
+//   import_awq_u4 / import_gptq_u4   kernels/quantization/quant_import_ref.cpp:840-999
 //
 // Arithmetic. The reference decodes a weight to f32 as scale * float(code) (one rounding,
 // decode_prepared_chunk, qgemm_canonical.cpp:150-176) and multiplies it into one of four f32
@@ -19,8 +21,10 @@
 //   digits  (scale groups that are multiples of 16 columns, or one scale per row): the
 //           activations of a span become exact 8-bit digits under a power-of-two envelope and
 //           the sums are integer dot products; see "digit kernels" below;
-//   floats  (a scale group boundary inside 16 columns): f32 multiply-adds on exactly
-//           converted codes, every weight scaled on its own as in the reference.
+//   floats  (a scale group boundary inside 16 columns, or a GPTQ group index): f32
+//           multiply-adds on exactly converted codes, every weight decoded on its own as in
+//           the reference (scale * code, or scale * (nibble - zero)).
+// With an act-order map the activations are first gathered into packed column order.
 // Inputs stored as f16 / bf16 are widened exactly, the output is rounded once at the store.
 // A token's result does not depend on the batch it is computed in.
 //
