@@ -68,6 +68,7 @@ struct qx_canonical_weights {
   float* zeros = nullptr;       // device: [rows][groups_per_row] (kUInt4Affine), else null
   int* group_index = nullptr;   // device: [columns] packed column -> scale group, or null
   int* act_order = nullptr;     // device: [columns] packed column -> activation column, or null
+  bool integral_zeros = false;  // every zero point is one of 0, 1, .. 15 (the usual case)
 };
 
 namespace qx {
@@ -78,6 +79,7 @@ struct CanonicalParams {
   const float* scales;
   const float* zeros;        // kUInt4Affine: zero point beside every scale
   const int* group_index;    // optional: packed column -> scale group
+  int integral_zeros;        // every zero point is one of 0 .. 15: exact integer arithmetic
   const void* x;
   const float* bias;
   void* y;
@@ -490,7 +492,7 @@ __device__ __forceinline__ SpanDigits load_span(const uint32_t* image, int lane)
 // words (int8), or its even / odd nibble words after the xor with 8 (int4)
 template <int LAYOUT>
 __device__ __forceinline__ float span_dot(const uint32_t (&w)[4], const uint4& d0, const uint4& d1,
-                                          const uint4& d2, int tsum, float zero) {
+                                          const uint4& d2, int tsum, float zero, bool integral_zero) {
   if (LAYOUT == QX_CANONICAL_INT8_SYMMETRIC) {
     int s0 = dp4a_ss(w[0], d0.x, 0), s1 = dp4a_ss(w[0], d1.x, 0), s2 = dp4a_ss(w[0], d2.x, 0);
     s0 = dp4a_ss(w[1], d0.y, s0); s1 = dp4a_ss(w[1], d1.y, s1); s2 = dp4a_ss(w[1], d2.y, s2);
@@ -505,12 +507,9 @@ __device__ __forceinline__ float span_dot(const uint32_t (&w)[4], const uint4& d
   // sum(u * t): |.| <= 16 * 15 * 2^22 < 2^30, exact in int32
   const int ut = (s2 << 16) + (s1 << 8) + s0;
   if (LAYOUT == QX_CANONICAL_INT4_SYMMETRIC) return __int2float_rn(ut - 8 * tsum);  // u = code + 8
-  // affine: sum((u - zero) * t) = sum(u * t) - zero * sum(t); exact in int32 for the usual
-  // integer zero points 0 .. 15 (|.| < 2^31), in f32 for a fractional one
-  const int whole = __float2int_rn(zero);
-  if (zero == static_cast<float>(whole) && whole >= 0 && whole <= 15) {
-    return __int2float_rn(ut - whole * tsum);
-  }
+  // affine: sum((u - zero) * t) = sum(u * t) - zero * sum(t); exact in int32 when the tensor's
+  // zero points are the usual integers 0 .. 15 (|.| < 2^31), in f32 otherwise
+  if (integral_zero) return __int2float_rn(ut - __float2int_rn(zero) * tsum);
   return fmaf(-zero, __int2float_rn(tsum), __int2float_rn(ut));
 }
 
@@ -523,6 +522,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
   constexpr bool kInt8 = LAYOUT == QX_CANONICAL_INT8_SYMMETRIC;
   constexpr bool kAffine = LAYOUT == QX_CANONICAL_UINT4_AFFINE;
   constexpr uint32_t kNibbleXor = LAYOUT == QX_CANONICAL_INT4_SYMMETRIC ? 0x88888888u : 0u;
+  const bool integral = p.integral_zeros != 0;
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int columns = static_cast<int>(p.columns);
@@ -637,7 +637,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
         const float e = t < tokens ? span.e : 0.0f;
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
-          acc[r][t] = fmaf(s[r] * e, span_dot<LAYOUT>(w[r], span.d0, span.d1, span.d2, span.tsum, z[r]),
+          acc[r][t] = fmaf(s[r] * e, span_dot<LAYOUT>(w[r], span.d0, span.d1, span.d2, span.tsum, z[r], integral),
                            acc[r][t]);
         }
       }
@@ -680,7 +680,7 @@ __global__ void __launch_bounds__(32 * kDigitWarps) canonical_digits_kernel(
           const float e = t < tokens ? span.e : 0.0f;
 #pragma unroll
           for (int r = 0; r < ROWS; ++r) {
-            const float sum = span_dot<LAYOUT>(codes[u][r].w, d0, d1, d2, span.tsum, zero[u][r]);
+            const float sum = span_dot<LAYOUT>(codes[u][r].w, d0, d1, d2, span.tsum, zero[u][r], integral);
             acc[r][t] = fmaf(scale[u][r] * e, sum, acc[r][t]);
           }
         }
@@ -914,6 +914,7 @@ qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_t
   p.scales = w->scales;
   p.zeros = w->zeros;
   p.group_index = w->group_index;
+  p.integral_zeros = w->integral_zeros ? 1 : 0;
   p.x = x;
   p.bias = bias;
   p.y = y;
@@ -1100,6 +1101,14 @@ qx_status qx_canonical_prepare(const qx_canonical_tensor* tensor, qx_canonical_w
   w->groups_per_row = groups;
   w->data_bytes = tensor->data_bytes;
   w->scale_count = tensor->scale_count;
+  w->integral_zeros = tensor->zero_point_count != 0;
+  for (size_t i = 0; i < tensor->zero_point_count; ++i) {
+    const float z = tensor->zero_points[i];
+    if (!(z >= 0.0f && z <= 15.0f && z == static_cast<float>(static_cast<int>(z)))) {
+      w->integral_zeros = false;
+      break;
+    }
+  }
   // one allocation: codes, then every table on a 256-byte boundary
   const size_t scale_offset = align_up(tensor->data_bytes, 256);
   const size_t zero_offset = scale_offset + align_up(tensor->scale_count * sizeof(float), 256);
