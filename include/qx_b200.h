@@ -489,14 +489,15 @@ QX_API qx_status qx_qgemm_prepacked_epilogue_storage(const qx_canonical_weights*
                                                      long long y_count, long long m,
                                                      int activation);
 /* DEVICE pointers and a stream. Enqueues two kernels (the digits of the activations, then the
- * projection) and returns without waiting; the digit images (1792 bytes per token and 512
- * columns) live in the library's default workspace, which grows -- and then synchronises the
- * device -- the first time a larger call arrives. */
+ * projection; one more when the tensor has an act-order map) and returns without waiting. The
+ * digit images (1792 bytes per token and 512 columns) live in `workspace` (NULL: the library's
+ * default one), which grows -- and then synchronises the device -- the first time a larger call
+ * arrives; calls that may run concurrently on different streams need workspaces of their own. */
 QX_API qx_status qx_qgemm_prepacked_epilogue_storage_dev(const qx_canonical_weights* weights,
                                                          const void* x_dev, int x_type,
                                                          const float* bias_dev, void* y_dev,
                                                          int y_type, long long m, int activation,
-                                                         void* stream);
+                                                         qx_workspace* workspace, void* stream);
 QX_API const char* qx_canonical_gemm_variant(void);
 
 /* import_smoothquant_w8a8, include/quixicore_cpu/quant_import.h:117-133

@@ -145,7 +145,7 @@ def _load():
         "qx_qgemm_prepacked_epilogue_storage": [_vp, _vp, C.c_int, _ll, _vp, _vp, C.c_int, _ll,
                                                 _ll, C.c_int],
         "qx_qgemm_prepacked_epilogue_storage_dev": [_vp, _vp, C.c_int, _vp, _vp, C.c_int, _ll,
-                                                    C.c_int, _vp],
+                                                    C.c_int, _vp, _vp],
         "qx_import_smoothquant_w8a8": [C.POINTER(SmoothQuantSource),
                                        C.POINTER(CanonicalTensorView), _vp],
         "qx_import_awq_u4": [C.POINTER(AwqU4Source), C.POINTER(CanonicalTensorView), _vp, _vp, _vp],
@@ -501,7 +501,7 @@ class CanonicalWeights:
     def qgemm_storage_dev(self, x, x_type, y, y_type, m, bias=None, activation=ACT_NONE) -> int:
         return lib.qx_qgemm_prepacked_epilogue_storage_dev(
             self.handle, _vp(x.data_ptr()), x_type, _dev(bias), _vp(y.data_ptr()), y_type, m,
-            activation, _stream())
+            activation, None, _stream())
 
 
 def import_smoothquant_w8a8(weights, weight_scales, activation_scales, rows, columns,

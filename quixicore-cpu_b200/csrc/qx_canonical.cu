@@ -898,9 +898,10 @@ qx_status launch_any(const CanonicalParams& p, bool digits, uint32_t* image, int
 
 qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_type,
                            const float* bias, void* y, int y_type, long long m, int activation,
-                           cudaStream_t stream) {
+                           qx_workspace* workspace, cudaStream_t stream) {
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
+  if (workspace == nullptr) workspace = &ctx->workspace;
   if (ctx->device != w->device) {
     set_last_error_text("canonical projection: weights were prepared on another device");
     return QX_STATUS_INVALID_ARGUMENT;
@@ -941,8 +942,8 @@ qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_t
   const size_t image_bytes = digits ? digit_image_bytes(m, w->columns) : 0;
   uint32_t* image = nullptr;
   if (gather_bytes + image_bytes != 0) {
-    QX_TRY(ctx->workspace.reserve(kWorkspaceCounterBytes + gather_bytes + image_bytes));
-    uint8_t* scratch = static_cast<uint8_t*>(ctx->workspace.base) + kWorkspaceCounterBytes;
+    QX_TRY(workspace->reserve(kWorkspaceCounterBytes + gather_bytes + image_bytes));
+    uint8_t* scratch = static_cast<uint8_t*>(workspace->base) + kWorkspaceCounterBytes;
     image = reinterpret_cast<uint32_t*>(scratch + gather_bytes);
     if (w->act_order != nullptr) {
       float* gathered = reinterpret_cast<float*>(scratch);
@@ -1158,7 +1159,8 @@ void qx_canonical_destroy(qx_canonical_weights* weights) {
 qx_status qx_qgemm_prepacked_epilogue_storage_dev(const qx_canonical_weights* weights,
                                                   const void* x_dev, int x_type,
                                                   const float* bias_dev, void* y_dev, int y_type,
-                                                  long long m, int activation, void* stream) {
+                                                  long long m, int activation,
+                                                  qx_workspace* workspace, void* stream) {
   if (!known_activation(activation)) return QX_STATUS_INVALID_ARGUMENT;
   if (weights == nullptr) return QX_STATUS_INVALID_ARGUMENT;
   if (!valid_product2(m, weights->columns) || !valid_product2(m, weights->rows)) {
@@ -1166,7 +1168,7 @@ qx_status qx_qgemm_prepacked_epilogue_storage_dev(const qx_canonical_weights* we
   }
   if (!known_storage(x_type) || !known_storage(y_type)) return QX_STATUS_UNSUPPORTED_FORMAT;
   if (x_dev == nullptr || y_dev == nullptr) return QX_STATUS_INVALID_ARGUMENT;
-  return launch_canonical(weights, x_dev, x_type, bias_dev, y_dev, y_type, m, activation,
+  return launch_canonical(weights, x_dev, x_type, bias_dev, y_dev, y_type, m, activation, workspace,
                           static_cast<cudaStream_t>(stream));
 }
 
@@ -1201,7 +1203,7 @@ qx_status qx_qgemm_prepacked_epilogue_storage(const qx_canonical_weights* weight
   QX_TRY(launch_canonical(weights, stage + off_x, x_type,
                           bias != nullptr ? reinterpret_cast<const float*>(stage + off_bias)
                                           : nullptr,
-                          stage + off_y, y_type, m, activation, s));
+                          stage + off_y, y_type, m, activation, nullptr, s));
   QX_CUDA_TRY(cudaMemcpyAsync(y, stage + off_y, y_bytes, cudaMemcpyDeviceToHost, s));
   QX_CUDA_TRY(cudaStreamSynchronize(s));
   return QX_STATUS_OK;
