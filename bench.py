@@ -1026,11 +1026,12 @@ def _extra_canonical(qx, wl, torch, hbm_peak):
     out = {}
     for layout, group, m, n, k in ((qx.INT8_SYMMETRIC, 0, 1, 4096, 4096), (qx.INT8_SYMMETRIC, 0, 1, 14336, 4096),
                                    (qx.INT8_SYMMETRIC, 0, 8, 4096, 4096), (qx.INT4_SYMMETRIC, 128, 1, 14336, 4096),
-                                   (qx.INT4_SYMMETRIC, 128, 8, 4096, 4096), (qx.UINT4_AFFINE, 128, 1, 14336, 4096)):
+                                   (qx.INT4_SYMMETRIC, 128, 8, 4096, 4096), (qx.UINT4_AFFINE, 128, 1, 14336, 4096),
+                                   (qx.INT8_SYMMETRIC, 0, 512, 14336, 4096)):
         rng = np.random.default_rng(n + m)
         code_bytes = n * k if layout == qx.INT8_SYMMETRIC else n * k // 2
         groups = 1 if group == 0 else k // group
-        copies = max(3, int(300e6 // code_bytes))
+        copies = max(3, int(300e6 // code_bytes)) if m < 32 else 2
         handles = []
         for _ in range(copies):
             data = rng.integers(0, 256, code_bytes, dtype=np.uint8)
@@ -1047,14 +1048,19 @@ def _extra_canonical(qx, wl, torch, hbm_peak):
         yd = torch.zeros((m, n), dtype=torch.bfloat16, device="cuda")
         sec = _time_calls(torch, lambda i: qx.check(
             handles[i % copies].qgemm_storage_dev(xd, qx.BF16, yd, qx.BF16, m, bias=bias,
-                                                  activation=qx.ACT_SILU), "canonical"), 4 * copies)
+                                                  activation=qx.ACT_SILU), "canonical"),
+            4 * copies if m < 32 else 4)
         nbytes = (code_bytes + 4 * n * groups * (2 if layout == qx.UINT4_AFFINE else 1) + 2 * m * k +
                   4 * n + 2 * m * n)
         name = {qx.INT8_SYMMETRIC: "int8", qx.INT4_SYMMETRIC: "int4g128",
                 qx.UINT4_AFFINE: "uint4affine_g128"}[layout] + f"_m{m}_n{n}_k{k}"
         out[name] = {"us": sec * 1e6, "gbs": nbytes / sec / 1e9,
                      "frac_of_measured_hbm": nbytes / sec / 1e9 / hbm_peak,
-                     "launches": 2}  # the digits of the activations, then the projection
+                     # the digits of the activations, then the projection; from 32 tokens on
+                     # row digits, the W8A8 tensor-core GEMM on the digit planes and the combine per 256 tokens
+                     "launches": 2 if m < 32 else 3 * ((m + 255) // 256)}
+        if m >= 32:
+            out[name]["tops"] = 2.0 * m * n * k / sec / 1e12
         for h in handles:
             h.reset()
     return {"canonical_projection": out}

@@ -489,9 +489,11 @@ QX_API qx_status qx_qgemm_prepacked_epilogue_storage(const qx_canonical_weights*
                                                      long long y_count, long long m,
                                                      int activation);
 /* DEVICE pointers and a stream. Enqueues two kernels (the digits of the activations, then the
- * projection; one more when the tensor has an act-order map) and returns without waiting. The
- * digit images (1792 bytes per token and 512 columns) live in `workspace` (NULL: the library's
- * default one), which grows -- and then synchronises the device -- the first time a larger call
+ * projection; one more when the tensor has an act-order map; three per 256 tokens on the
+ * tensor-core route that int8 tensors with one scale per row take from 32 tokens on) and
+ * returns without waiting. The digit images (1792 bytes per token and 512 columns; on the
+ * tensor-core route 4 * min(m, 256) * (columns + 4 * rows) bytes) live in `workspace` (NULL:
+ * the library's default one), which grows -- and then synchronises the device -- the first time a larger call
  * arrives; calls that may run concurrently on different streams need workspaces of their own. */
 QX_API qx_status qx_qgemm_prepacked_epilogue_storage_dev(const qx_canonical_weights* weights,
                                                          const void* x_dev, int x_type,

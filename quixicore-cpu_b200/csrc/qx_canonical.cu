@@ -25,8 +25,11 @@
 //           multiply-adds on exactly converted codes, every weight decoded on its own as in
 //           the reference (scale * code, or scale * (nibble - zero)).
 // With an act-order map the activations are first gathered into packed column order.
+//   tensor cores (int8 with one scale per row, 32 tokens or more): four digit planes under a
+//           per-token envelope through the W8A8 GEMM; see "long prefills" below.
 // Inputs stored as f16 / bf16 are widened exactly, the output is rounded once at the store.
-// A token's result does not depend on the batch it is computed in.
+// On the first two paths a token's result does not depend on the batch it is computed in; a
+// batch that crosses 32 tokens changes route and with it the rounding (same tolerance).
 //
 // HBM layout. Codes stay in the canonical row-major byte order (a row of K int8 codes or
 // K/2 nibble pairs is already what a warp wants to stream with 16-byte loads), followed by
@@ -34,7 +37,7 @@
 // bytes. The digit images of a call's activations (1792 bytes per token and 512 columns)
 // live in the device's default workspace.
 //
-// Kernels. CUDA cores; a tensor-core schedule for long prefills is not built for this path.
+// Kernels. CUDA cores for decode-sized batches, the tcgen05 W8A8 GEMM for int8 prefills.
 // Measured on 14336 x 4096 int8 with one bf16 token: 17 us per call for both launches (the
 // digit kernel and the projection behind it), 3.4 TB/s of the weights' bytes, about half of
 // the measured copy bandwidth; the float path ran the same shape in 24 us at 10 instructions
@@ -52,6 +55,7 @@
 
 #include "qx_common.cuh"
 #include "qx_gemv.cuh"
+#include "qx_int8_gemm.cuh"
 
 struct qx_canonical_weights {
   int layout = 0;
@@ -889,6 +893,150 @@ __global__ void __launch_bounds__(256) gather_activations_kernel(const void* __r
   }
 }
 
+// ---- long prefills of int8 tensors with one scale per row: the tensor cores --------------
+// From 32 tokens on, four digit planes of the activations become four int8 "token" rows each
+// and the W8A8 tensor-core GEMM (qx_int8_gemm_tc.cu) forms the exact integer sums
+//   A_d[t, o] = sum_k code[o, k] * p_d[t, k],      d = 0 .. 3,
+// over the whole row. The envelope is therefore one power of two per TOKEN, not per 16
+// columns, and the fixed point has 31 bits (x = e * t, |t| <= 2^30, t = sum_d 256^d p_d with
+// balanced signed bytes): with three planes the fixed-point step of a whole row's envelope
+// showed in outputs near zero at K = 4096 (errors of 1e-4 against a tolerance of 4e-5), with
+// four it is below the f32 roundings that follow. The GEMM's own epilogue scales float(A_d) by
+// the weight scale of the channel and by e * 256^d (two rounded multiplies), and a last kernel
+// adds the four planes, the bias, applies the activation and stores the output type.
+// |A_d| <= K * 128 * 128 fits int32 for K <= 131000 (the GEMM's own limit). Tokens whose
+// largest magnitude is below 2^-70 count as zero.
+constexpr long long kPrefillTokens = 32;
+constexpr long long kPrefillChunk = 256;  // tokens per GEMM launch: bounds the scratch
+constexpr int kPlanes = 4;
+
+__global__ void __launch_bounds__(256) canonical_row_digits_kernel(
+    const void* __restrict__ x, int x_type, long long columns, long long chunk_tokens,
+    int8_t* __restrict__ planes, float* __restrict__ plane_scale) {
+  __shared__ float warp_max[8];
+  const long long token = blockIdx.x;
+  const long long base = token * columns;
+  float amax = 0.0f;
+  bool finite = true;
+  for (long long k = threadIdx.x; k < columns; k += 256) {
+    const float v = fabsf(load_storage(x, x_type, base + k));
+    finite = finite && v < __uint_as_float(0x7f800000u);  // false for NaN and infinity
+    amax = fmaxf(amax, v);
+  }
+  if (!finite) amax = __uint_as_float(0x7f800000u);
+#pragma unroll
+  for (int h = 16; h >= 1; h >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, h));
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+#pragma unroll
+  for (int w = 0; w < 8; ++w) amax = fmaxf(amax, warp_max[w]);
+  int biased = static_cast<int>(__float_as_uint(amax) >> 23) + 1;  // exponent of 2^E > amax
+  biased = biased < 58 ? 58 : biased;                               // keeps e normal
+  const bool ok = biased < 256;
+  // t = x * 2^30 / 2^E: the factor's exponent 284 - biased is a normal float for 58 .. 255
+  const float to_fixed = ok ? __uint_as_float(static_cast<uint32_t>(284 - biased) << 23) : 0.0f;
+  const float e = ok ? __uint_as_float(static_cast<uint32_t>(biased - 30) << 23)
+                     : __uint_as_float(0x7fc00000u);
+  int8_t* out[kPlanes];
+#pragma unroll
+  for (int d = 0; d < kPlanes; ++d) out[d] = planes + (d * chunk_tokens + token) * columns;
+  for (long long k = threadIdx.x; k < columns; k += 256) {
+    int t = ok ? __float2int_rn(load_storage(x, x_type, base + k) * to_fixed) : 0;
+#pragma unroll
+    for (int d = 0; d < kPlanes - 1; ++d) {
+      const int digit = ((t + 128) & 255) - 128;
+      out[d][k] = static_cast<int8_t>(digit);
+      t = (t - digit) >> 8;
+    }
+    out[kPlanes - 1][k] = static_cast<int8_t>(t);
+  }
+  if (threadIdx.x == 0) {
+    float weight = e;
+#pragma unroll
+    for (int d = 0; d < kPlanes; ++d) {
+      plane_scale[d * chunk_tokens + token] = weight;
+      weight *= 256.0f;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) canonical_combine_kernel(
+    const float* __restrict__ partial, long long chunk_tokens, long long tokens, long long rows,
+    const float* __restrict__ bias, int activation, void* __restrict__ y, int y_type) {
+  const long long total = tokens * rows;
+  const long long plane = chunk_tokens * rows;
+  for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < total;
+       i += 256LL * gridDim.x) {
+    // largest plane first
+    float v = partial[(kPlanes - 1) * plane + i];
+#pragma unroll
+    for (int d = kPlanes - 2; d >= 0; --d) v += partial[d * plane + i];
+    if (bias != nullptr) v += bias[i % rows];
+    store_storage(y, y_type, i, apply_activation(v, activation));
+  }
+}
+
+size_t prefill_scratch_bytes(long long m, long long rows, long long columns) {
+  const long long chunk = m < kPrefillChunk ? m : kPrefillChunk;
+  return align_up(static_cast<size_t>(kPlanes * chunk * columns), 256) +
+         align_up(static_cast<size_t>(kPlanes * chunk) * sizeof(float), 256) +
+         static_cast<size_t>(kPlanes * chunk * rows) * sizeof(float);
+}
+
+qx_status launch_prefill_int8(const CanonicalParams& p, uint8_t* scratch, int sm_count,
+                              cudaStream_t stream) {
+  const long long chunk = p.m < kPrefillChunk ? p.m : kPrefillChunk;
+  int8_t* planes = reinterpret_cast<int8_t*>(scratch);
+  float* plane_scale = reinterpret_cast<float*>(scratch + align_up(static_cast<size_t>(kPlanes * chunk * p.columns), 256));
+  float* partial = plane_scale + align_up(static_cast<size_t>(kPlanes * chunk) * sizeof(float), 256) / sizeof(float);
+  const size_t x_bytes = p.x_type == QX_STORAGE_F32 ? 4 : 2, y_bytes = p.y_type == QX_STORAGE_F32 ? 4 : 2;
+  for (long long t0 = 0; t0 < p.m; t0 += chunk) {
+    const long long tokens = p.m - t0 < chunk ? p.m - t0 : chunk;
+    const uint8_t* x = static_cast<const uint8_t*>(p.x) + static_cast<size_t>(t0 * p.columns) * x_bytes;
+    canonical_row_digits_kernel<<<static_cast<unsigned>(tokens), 256, 0, stream>>>(
+        x, p.x_type, p.columns, chunk, planes, plane_scale);
+    count_launch();
+    QX_CUDA_TRY(cudaGetLastError());
+    if (tokens < chunk) {
+      // the planes of a short last chunk are not contiguous token rows: run them one by one
+      for (int d = 0; d < kPlanes; ++d) {
+        Int8GemmArgs a{};
+        a.w = reinterpret_cast<const int8_t*>(p.data);
+        a.x = planes + d * chunk * p.columns;
+        a.ws = p.scales;
+        a.as = plane_scale + d * chunk;
+        a.y = partial + d * chunk * p.rows;
+        a.m = tokens;
+        a.n = p.rows;
+        a.k = p.columns;
+        a.ldy = p.rows;
+        QX_TRY(launch_int8_gemm(a, stream));
+      }
+    } else {
+      Int8GemmArgs a{};
+      a.w = reinterpret_cast<const int8_t*>(p.data);
+      a.x = planes;
+      a.ws = p.scales;
+      a.as = plane_scale;
+      a.y = partial;
+      a.m = kPlanes * chunk;
+      a.n = p.rows;
+      a.k = p.columns;
+      a.ldy = p.rows;
+      QX_TRY(launch_int8_gemm(a, stream));
+    }
+    uint8_t* y = static_cast<uint8_t*>(p.y) + static_cast<size_t>(t0 * p.rows) * y_bytes;
+    const long long total = tokens * p.rows;
+    const long long blocks = (total + 255) / 256;
+    const long long cap = 8LL * sm_count;
+    canonical_combine_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, stream>>>(
+        partial, chunk, tokens, p.rows, p.bias, p.activation, y, p.y_type);
+    count_launch();
+    QX_CUDA_TRY(cudaGetLastError());
+  }
+  return QX_STATUS_OK;
+}
+
 template <int LAYOUT>
 qx_status launch_any(const CanonicalParams& p, bool digits, uint32_t* image, int sm_count,
                      cudaStream_t stream) {
@@ -939,12 +1087,18 @@ qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_t
   // workspace behind its counters: [gathered activations (act-order)][digit images]
   const size_t gather_bytes =
       w->act_order != nullptr ? align_up(static_cast<size_t>(m) * w->columns * sizeof(float), 256) : 0;
-  const size_t image_bytes = digits ? digit_image_bytes(m, w->columns) : 0;
+  // int8 with one scale per row, 32 tokens or more: the tensor-core route
+  const bool prefill = int8 && p.groups_per_row == 1 && m >= kPrefillTokens && w->columns <= 131000;
+  const size_t image_bytes = prefill ? prefill_scratch_bytes(m, w->rows, w->columns)
+                                     : (digits ? digit_image_bytes(m, w->columns) : 0);
   uint32_t* image = nullptr;
   if (gather_bytes + image_bytes != 0) {
     QX_TRY(workspace->reserve(kWorkspaceCounterBytes + gather_bytes + image_bytes));
     uint8_t* scratch = static_cast<uint8_t*>(workspace->base) + kWorkspaceCounterBytes;
     image = reinterpret_cast<uint32_t*>(scratch + gather_bytes);
+    if (prefill) {
+      return launch_prefill_int8(p, scratch + gather_bytes, ctx->prop.multiProcessorCount, stream);
+    }
     if (w->act_order != nullptr) {
       float* gathered = reinterpret_cast<float*>(scratch);
       const unsigned gx = static_cast<unsigned>(w->columns + 255) / 256;

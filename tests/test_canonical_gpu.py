@@ -90,7 +90,11 @@ def test_golden_cases_of_the_reference(qx, orc, oracle_mod, canon):
                 assert close(y, canon[f"{name}/y_x{storage}"]), (name, storage)
         # digits of the activations + projection per call; one kernel when a scale group
         # boundary falls inside 16 columns
-        assert qx.launch_count() - before == (6 if (group % 16 == 0 or mode != GROUP) else 3)
+        if layout == INT8 and mode != GROUP and m >= 32:
+            expected = 9  # tensor-core route: row digits, W8A8 GEMM on the digit planes, combine
+        else:
+            expected = 6 if (group % 16 == 0 or mode != GROUP) else 3
+        assert qx.launch_count() - before == expected
         x32 = np.ascontiguousarray(canon[name + "/x0"])
         bias = np.ascontiguousarray(canon[name + "/bias"])
         exact_sum = orc.canonical_gemm_f64(t, x32, F32, m) + bias.astype(np.float64)[None, :]
@@ -299,3 +303,37 @@ def test_affine_prepare_checks(qx):
     bad = zeros.copy()
     bad[1] = np.inf
     assert w.prepare(qx.canonical_view(UINT4, GROUP, n, k, group, data, scales, zeros=bad)) == 1
+
+
+@pytest.mark.parametrize("case", [(4096, 4096, 64), (1000, 1008, 300), (257, 272, 33), (14336, 4096, 512)])
+def test_int8_prefill_on_the_tensor_cores(qx, orc, oracle_mod, case):
+    # 32 tokens or more of an int8 tensor with one scale per row: digit planes under a per-token
+    # envelope through the W8A8 tensor-core GEMM (300 tokens = a full chunk of 256 and a short one)
+    n, k, m = case
+    rng = np.random.Generator(np.random.Philox(key=[n, k + m]))
+    status, t = orc.quantize_canonical(INT8, rng.standard_normal((n, k)).astype(np.float32), n, k, 0)
+    assert status == 0
+    w = prepared(qx, t.layout, CHANNEL, n, k, t.group_size, t.data, t.scales)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    x[1] *= 1e-6   # a quiet token next to loud ones: the envelope is per token
+    x[2, ::3] = 0.0
+    bias = rng.standard_normal(n).astype(np.float32)
+    before = qx.launch_count()
+    status, y = w.qgemm_storage(x, F32, m)
+    assert status == qx.OK, qx.last_error()
+    assert qx.launch_count() - before >= 3
+    # float64 on a sample of rows of the big case, on everything otherwise
+    rows = slice(None) if n * k * m <= 1 << 28 else slice(0, 8)
+    xs = np.ascontiguousarray(x[rows])
+    ms = xs.shape[0]
+    exact = orc.canonical_gemm_f64(t, xs, F32, ms)
+    assert close(y[rows], exact), case
+    # typed: bf16 in, bias + tanh-GELU, f16 out
+    import torch
+    xb = np.ascontiguousarray(torch.from_numpy(x).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16))
+    status, yt = w.qgemm_storage(xb, BF16, m, y_type=F16, bias=bias, activation=2)
+    assert status == qx.OK, qx.last_error()
+    exact_t = activation_f64(orc.canonical_gemm_f64(t, np.ascontiguousarray(xb[rows]), BF16, ms) +
+                             bias.astype(np.float64)[None, :], 2)
+    assert close(widen(yt, F16)[rows], exact_t, OUT_TOLERANCE[F16]), case
+    assert qx.lib.qx_check_device_errors() == qx.OK
