@@ -1056,9 +1056,9 @@ def _extra_canonical(qx, wl, torch, hbm_peak):
                 qx.UINT4_AFFINE: "uint4affine_g128"}[layout] + f"_m{m}_n{n}_k{k}"
         out[name] = {"us": sec * 1e6, "gbs": nbytes / sec / 1e9,
                      "frac_of_measured_hbm": nbytes / sec / 1e9 / hbm_peak,
-                     # the digits of the activations, then the projection; from 32 tokens on
+                     # the digits of the activations, then the projection; from five tokens on
                      # row digits, the W8A8 tensor-core GEMM on the digit planes and the combine per 256 tokens
-                     "launches": 2 if m < 32 else 3 * ((m + 255) // 256)}
+                     "launches": 2 if (m < 5 or layout != qx.INT8_SYMMETRIC) else 3 * ((m + 255) // 256)}
         if m >= 32:
             out[name]["tops"] = 2.0 * m * n * k / sec / 1e12
         for h in handles:

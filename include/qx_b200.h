@@ -490,7 +490,7 @@ QX_API qx_status qx_qgemm_prepacked_epilogue_storage(const qx_canonical_weights*
                                                      int activation);
 /* DEVICE pointers and a stream. Enqueues two kernels (the digits of the activations, then the
  * projection; one more when the tensor has an act-order map; three per 256 tokens on the
- * tensor-core route that int8 tensors with one scale per row take from 32 tokens on) and
+ * tensor-core route that int8 tensors with one scale per row take from five tokens on) and
  * returns without waiting. The digit images (1792 bytes per token and 512 columns; on the
  * tensor-core route 4 * min(m, 256) * (columns + 4 * rows) bytes) live in `workspace` (NULL:
  * the library's default one), which grows -- and then synchronises the device -- the first time a larger call

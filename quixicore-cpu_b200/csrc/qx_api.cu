@@ -619,7 +619,7 @@ qx_status qx_qgemm_w8a32(const int8_t* weights, const float* weight_scale, const
   return sync_and_check(ctx, s);
 }
 
-const char* qx_qgemm_w8a32_variant(void) { return "sm100a_stream_fma"; }
+const char* qx_qgemm_w8a32_variant(void) { return "sm100a_stream_fma+tcgen05_digit_planes"; }
 
 qx_status qx_qgemm_w8a32_dev(const int8_t* weights_dev, const float* weight_scale_dev,
                              const float* x_dev, float* y_dev, long long m, long long n,

@@ -25,11 +25,11 @@
 //           multiply-adds on exactly converted codes, every weight decoded on its own as in
 //           the reference (scale * code, or scale * (nibble - zero)).
 // With an act-order map the activations are first gathered into packed column order.
-//   tensor cores (int8 with one scale per row, 32 tokens or more): four digit planes under a
+//   tensor cores (int8 with one scale per row, five tokens or more): four digit planes under a
 //           per-token envelope through the W8A8 GEMM; see "long prefills" below.
 // Inputs stored as f16 / bf16 are widened exactly, the output is rounded once at the store.
 // On the first two paths a token's result does not depend on the batch it is computed in; a
-// batch that crosses 32 tokens changes route and with it the rounding (same tolerance).
+// batch that crosses five tokens changes route and with it the rounding (same tolerance).
 //
 // HBM layout. Codes stay in the canonical row-major byte order (a row of K int8 codes or
 // K/2 nibble pairs is already what a warp wants to stream with 16-byte loads), followed by
@@ -88,6 +88,7 @@ struct CanonicalParams {
   const float* bias;
   void* y;
   long long rows, columns, group_size, groups_per_row, m;
+  long long ldy;     // row stride of y in elements (the tensor-core route; rows elsewhere)
   int x_type, y_type, activation;
   int vector_rows;   // 1: every row of codes starts on a 16-byte (int8) / 8-byte (int4) boundary
   int vector_x;      // 1: every activation row starts on a boundary of four elements
@@ -893,8 +894,10 @@ __global__ void __launch_bounds__(256) gather_activations_kernel(const void* __r
   }
 }
 
-// ---- long prefills of int8 tensors with one scale per row: the tensor cores --------------
-// From 32 tokens on, four digit planes of the activations become four int8 "token" rows each
+// ---- five tokens or more of int8 tensors with one scale per row: the tensor cores ----------
+// (Measured on 14336 x 4096 / 4096 x 4096: 4 tokens 23.7 / 18.1 us here against 34.4 / 14.8 us
+// on the digit kernel, 8 tokens 21.7 / 16.3 against 56.5 / 19.5, 16 tokens 22.8 / 16.8 against
+// 102.8 / 33.9.) Four digit planes of the activations become four int8 "token" rows each
 // and the W8A8 tensor-core GEMM (qx_int8_gemm_tc.cu) forms the exact integer sums
 //   A_d[t, o] = sum_k code[o, k] * p_d[t, k],      d = 0 .. 3,
 // over the whole row. The envelope is therefore one power of two per TOKEN, not per 16
@@ -906,7 +909,7 @@ __global__ void __launch_bounds__(256) gather_activations_kernel(const void* __r
 // adds the four planes, the bias, applies the activation and stores the output type.
 // |A_d| <= K * 128 * 128 fits int32 for K <= 131000 (the GEMM's own limit). Tokens whose
 // largest magnitude is below 2^-70 count as zero.
-constexpr long long kPrefillTokens = 32;
+constexpr long long kPrefillTokens = 5;
 constexpr long long kPrefillChunk = 256;  // tokens per GEMM launch: bounds the scratch
 constexpr int kPlanes = 4;
 
@@ -962,7 +965,7 @@ __global__ void __launch_bounds__(256) canonical_row_digits_kernel(
 
 __global__ void __launch_bounds__(256) canonical_combine_kernel(
     const float* __restrict__ partial, long long chunk_tokens, long long tokens, long long rows,
-    const float* __restrict__ bias, int activation, void* __restrict__ y, int y_type) {
+    long long ldy, const float* __restrict__ bias, int activation, void* __restrict__ y, int y_type) {
   const long long total = tokens * rows;
   const long long plane = chunk_tokens * rows;
   for (long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x; i < total;
@@ -971,8 +974,9 @@ __global__ void __launch_bounds__(256) canonical_combine_kernel(
     float v = partial[(kPlanes - 1) * plane + i];
 #pragma unroll
     for (int d = kPlanes - 2; d >= 0; --d) v += partial[d * plane + i];
-    if (bias != nullptr) v += bias[i % rows];
-    store_storage(y, y_type, i, apply_activation(v, activation));
+    const long long token = i / rows, row = i - token * rows;
+    if (bias != nullptr) v += bias[row];
+    store_storage(y, y_type, token * ldy + row, apply_activation(v, activation));
   }
 }
 
@@ -1025,12 +1029,12 @@ qx_status launch_prefill_int8(const CanonicalParams& p, uint8_t* scratch, int sm
       a.ldy = p.rows;
       QX_TRY(launch_int8_gemm(a, stream));
     }
-    uint8_t* y = static_cast<uint8_t*>(p.y) + static_cast<size_t>(t0 * p.rows) * y_bytes;
+    uint8_t* y = static_cast<uint8_t*>(p.y) + static_cast<size_t>(t0 * p.ldy) * y_bytes;
     const long long total = tokens * p.rows;
     const long long blocks = (total + 255) / 256;
     const long long cap = 8LL * sm_count;
     canonical_combine_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, stream>>>(
-        partial, chunk, tokens, p.rows, p.bias, p.activation, y, p.y_type);
+        partial, chunk, tokens, p.rows, p.ldy, p.bias, p.activation, y, p.y_type);
     count_launch();
     QX_CUDA_TRY(cudaGetLastError());
   }
@@ -1068,6 +1072,7 @@ qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_t
   p.bias = bias;
   p.y = y;
   p.rows = w->rows;
+  p.ldy = w->rows;
   p.columns = w->columns;
   p.group_size = w->group_size;
   p.groups_per_row = w->groups_per_row;
@@ -1087,8 +1092,14 @@ qx_status launch_canonical(const qx_canonical_weights* w, const void* x, int x_t
   // workspace behind its counters: [gathered activations (act-order)][digit images]
   const size_t gather_bytes =
       w->act_order != nullptr ? align_up(static_cast<size_t>(m) * w->columns * sizeof(float), 256) : 0;
-  // int8 with one scale per row, 32 tokens or more: the tensor-core route
-  const bool prefill = int8 && p.groups_per_row == 1 && m >= kPrefillTokens && w->columns <= 131000;
+  // int8 with one scale per row, five tokens or more: the tensor-core route
+  long long prefill_from = kPrefillTokens;
+  // developer switch: QX_B200_CANONICAL_PREFILL_TOKENS=<n> moves the threshold
+  if (const char* forced = std::getenv("QX_B200_CANONICAL_PREFILL_TOKENS")) {
+    const long long asked = std::atoll(forced);
+    if (asked > 0) prefill_from = asked;
+  }
+  const bool prefill = int8 && p.groups_per_row == 1 && m >= prefill_from && w->columns <= 131000;
   const size_t image_bytes = prefill ? prefill_scratch_bytes(m, w->rows, w->columns)
                                      : (digits ? digit_image_bytes(m, w->columns) : 0);
   uint32_t* image = nullptr;
@@ -1232,6 +1243,35 @@ qx_status validate_tensor(const qx_canonical_tensor* t, long long* groups_per_ro
 }
 
 }  // namespace
+
+// qgemm_w8a32 (int8 weights, one f32 scale per row, f32 in and out) from five tokens on: the
+// same digit planes through the W8A8 tensor-core GEMM.
+bool w8a32_planes_serves(long long m, long long k) { return m >= kPrefillTokens && k <= 131000 && m <= 65535; }
+qx_status launch_w8a32_planes(const int8_t* w, const float* ws, const float* x, float* y,
+                              long long m, long long n, long long k, long long ldy,
+                              qx_workspace* workspace, cudaStream_t stream) {
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  if (workspace == nullptr) workspace = &ctx->workspace;
+  CanonicalParams p{};
+  p.data = reinterpret_cast<const uint8_t*>(w);
+  p.scales = ws;
+  p.x = x;
+  p.y = y;
+  p.rows = n;
+  p.ldy = ldy;
+  p.columns = k;
+  p.group_size = k;
+  p.groups_per_row = 1;
+  p.m = m;
+  p.x_type = QX_STORAGE_F32;
+  p.y_type = QX_STORAGE_F32;
+  p.activation = QX_ACTIVATION_NONE;
+  QX_TRY(workspace->reserve(kWorkspaceCounterBytes + prefill_scratch_bytes(m, n, k)));
+  return launch_prefill_int8(p, static_cast<uint8_t*>(workspace->base) + kWorkspaceCounterBytes,
+                             ctx->prop.multiProcessorCount, stream);
+}
+
 }  // namespace qx
 
 using namespace qx;

@@ -35,6 +35,14 @@ qx_status launch_w8a32(const int8_t* w, const float* ws, const float* x, float* 
                        long long m, long long n, long long k, long long ldy,
                        qx_workspace* workspace, cudaStream_t stream);
 
+// qgemm_w8a32 from five activation rows on: four exact 8-bit digit planes of the activations
+// (31-bit fixed point under one power-of-two envelope per row) through the W8A8 GEMM above,
+// combined in f32 (qx_canonical.cu).
+bool w8a32_planes_serves(long long m, long long k);
+qx_status launch_w8a32_planes(const int8_t* w, const float* ws, const float* x, float* y,
+                              long long m, long long n, long long k, long long ldy,
+                              qx_workspace* workspace, cudaStream_t stream);
+
 const char* int8_gemm_variant_name();
 
 }  // namespace qx

@@ -244,7 +244,10 @@ qx_status launch_check_finite(const float* v, long long count, int* flag, cudaSt
 
 qx_status launch_w8a32(const int8_t* w, const float* ws, const float* x, float* y,
                        long long m, long long n, long long k, long long ldy,
-                       qx_workspace* /*workspace*/, cudaStream_t stream) {
+                       qx_workspace* workspace, cudaStream_t stream) {
+  // five rows or more: the tensor cores (digit planes through the W8A8 GEMM); measured on
+  // 4096 x 4096 with 16 rows: 17 us against 37 us for the streaming kernel below
+  if (w8a32_planes_serves(m, k)) return launch_w8a32_planes(w, ws, x, y, m, n, k, ldy, workspace, stream);
   DeviceContext* ctx = nullptr;
   QX_TRY(current_context(&ctx));
   // 16-byte weight loads need 16-byte aligned rows
