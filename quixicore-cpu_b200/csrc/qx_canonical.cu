@@ -511,12 +511,19 @@ __device__ __forceinline__ float span_dot(const uint32_t (&w)[4], const uint4& d
   s0 = dp4a_us(w[3], d0.w, s0); s1 = dp4a_us(w[3], d1.w, s1); s2 = dp4a_us(w[3], d2.w, s2);
   // sum(u * t): |.| <= 16 * 15 * 2^22 < 2^30, exact in int32
   const int ut = (s2 << 16) + (s1 << 8) + s0;
-  if (LAYOUT == QX_CANONICAL_INT4_SYMMETRIC) return __int2float_rn(ut - 8 * tsum);  // u = code + 8
+  if (LAYOUT == QX_CANONICAL_INT4_SYMMETRIC || LAYOUT == 3 /* kLayoutInt4Offset8 */) {
+    return __int2float_rn(ut - 8 * tsum);  // u = code + 8
+  }
   // affine: sum((u - zero) * t) = sum(u * t) - zero * sum(t); exact in int32 when the tensor's
   // zero points are the usual integers 0 .. 15 (|.| < 2^31), in f32 otherwise
   if (integral_zero) return __int2float_rn(ut - __float2int_rn(zero) * tsum);
   return fmaf(-zero, __int2float_rn(tsum), __int2float_rn(ut));
 }
+
+// Internal fourth layout of the digit kernels: adjacent nibbles meaning nibble - 8 (the compact
+// int4 rows of lowbit_gemm, kernels/quantization/lowbit_ref.cpp:229-256): the symmetric path
+// without the xor.
+constexpr int kLayoutInt4Offset8 = 3;
 
 constexpr int kDigitWarps = 4;  // independent warps per CTA: no shared memory, no barrier
 constexpr int kStep = 1;       // chunks a lane requests at once (measured: 1 is as fast as 4)
@@ -1243,6 +1250,39 @@ qx_status validate_tensor(const qx_canonical_tensor* t, long long* groups_per_ro
 }
 
 }  // namespace
+
+// lowbit_gemm on compact int4 rows (value = nibble - 8, one f32 scale per row or per group of a
+// multiple of 16 columns, even column count): the digit kernels.
+bool int4_offset8_digits_serves(long long m, long long k, long long groups, long long group_size) {
+  return m <= 65535 && k % 2 == 0 && k <= (1LL << 30) &&
+         (groups == 1 || (group_size % kElems == 0 && k % group_size == 0));
+}
+qx_status launch_int4_offset8_digits(const uint8_t* packed, const float* scales, const float* x,
+                                     float* y, long long m, long long n, long long k,
+                                     long long groups, long long group_size, cudaStream_t stream) {
+  DeviceContext* ctx = nullptr;
+  QX_TRY(current_context(&ctx));
+  CanonicalParams p{};
+  p.data = packed;
+  p.scales = scales;
+  p.x = x;
+  p.y = y;
+  p.rows = n;
+  p.ldy = n;
+  p.columns = k;
+  p.group_size = groups == 1 ? k : group_size;
+  p.groups_per_row = groups;
+  p.m = m;
+  p.x_type = QX_STORAGE_F32;
+  p.y_type = QX_STORAGE_F32;
+  p.activation = QX_ACTIVATION_NONE;
+  p.vector_rows = ((k / 2) % 8 == 0 && reinterpret_cast<uintptr_t>(packed) % 8 == 0) ? 1 : 0;
+  p.vector_x = (k % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0) ? 1 : 0;
+  QX_TRY(ctx->workspace.reserve(kWorkspaceCounterBytes + digit_image_bytes(m, k)));
+  uint32_t* image = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(ctx->workspace.base) +
+                                                kWorkspaceCounterBytes);
+  return launch_digits<kLayoutInt4Offset8>(p, image, ctx->prop.multiProcessorCount, stream);
+}
 
 // qgemm_w8a32 (int8 weights, one f32 scale per row, f32 in and out) from five tokens on: the
 // same digit planes through the W8A8 tensor-core GEMM.

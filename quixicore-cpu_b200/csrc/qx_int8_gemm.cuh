@@ -43,6 +43,14 @@ qx_status launch_w8a32_planes(const int8_t* w, const float* ws, const float* x, 
                               long long m, long long n, long long k, long long ldy,
                               qx_workspace* workspace, cudaStream_t stream);
 
+// lowbit_gemm on compact int4 rows through the digit kernels of qx_canonical.cu (exact 8-bit
+// activation digits per 16 columns, dp4a): rows of an even number of columns with one scale
+// per row or per group of a multiple of 16 columns.
+bool int4_offset8_digits_serves(long long m, long long k, long long groups, long long group_size);
+qx_status launch_int4_offset8_digits(const uint8_t* packed, const float* scales, const float* x,
+                                     float* y, long long m, long long n, long long k,
+                                     long long groups, long long group_size, cudaStream_t stream);
+
 const char* int8_gemm_variant_name();
 
 }  // namespace qx

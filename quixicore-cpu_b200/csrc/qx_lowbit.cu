@@ -20,6 +20,7 @@
 #include <limits>
 
 #include "qx_common.cuh"
+#include "qx_int8_gemm.cuh"
 
 namespace qx {
 namespace {
@@ -468,6 +469,11 @@ qx_status launch_lowbit_w8a8(const uint8_t* packed, const float* weight_scales, 
 qx_status launch_lowbit_f32(const uint8_t* packed, const float* scales, const float* x, float* y,
                             long long m, long long n, long long k, long long groups,
                             long long group_size, cudaStream_t stream) {
+  // rows of an even number of columns with scale groups of a multiple of 16 columns: the digit
+  // kernels (exact 8-bit activation digits, dp4a); everything else: the float kernel below
+  if (int4_offset8_digits_serves(m, k, groups, group_size)) {
+    return launch_int4_offset8_digits(packed, scales, x, y, m, n, k, groups, group_size, stream);
+  }
   const int vector_ok = (reinterpret_cast<uintptr_t>(packed) % 16 == 0 && k % 32 == 0 &&
                          reinterpret_cast<uintptr_t>(x) % 16 == 0)
                             ? 1
@@ -604,7 +610,7 @@ qx_status qx_lowbit_gemm_w8a8(const uint8_t* packed_weights, const float* weight
 const char* qx_lowbit_gemm_w8a8_variant(void) { return "sm100a_dp4a_stream"; }
 
 const char* qx_lowbit_gemm_variant(int format) {
-  return int4_format(format) ? "sm100a_stream_fma" : "unsupported";
+  return int4_format(format) ? "sm100a_digits_dp4a+stream_fma" : "unsupported";
 }
 
 // lowbit_gemm (int4 row / group formats), DEVICE pointers.
