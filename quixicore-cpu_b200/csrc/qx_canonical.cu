@@ -819,56 +819,12 @@ qx_status launch_one(const CanonicalParams& p, cudaStream_t stream) {
   return QX_STATUS_OK;
 }
 
-// Tile shapes, largest first: rows per warp x warps per CTA. The first whose CTAs fill the
-// SMs evenly (at least 90 % of the slots of its last round busy) wins, else the most even:
-// 14336 rows on 148 SMs leave a quarter of the machine idle with 64-row CTAs and 7 % with
-// 8-row CTAs. Eight-token tiles keep two rows per warp (register budget).
-struct TileShape {
-  int rows, warps;
-};
-inline int pick_shape(const TileShape* shapes, int count, long long rows, long long token_tiles,
-                      int sm_count) {
-  int best = 0;
-  double best_fill = -1.0;
-  for (int i = 0; i < count; ++i) {
-    const long long per_cta = static_cast<long long>(shapes[i].rows) * shapes[i].warps;
-    const long long ctas = (rows + per_cta - 1) / per_cta * token_tiles;
-    const long long rounds = (ctas + sm_count - 1) / sm_count;
-    const double fill = static_cast<double>(ctas) / static_cast<double>(rounds * sm_count);
-    if (fill >= 0.9) return i;
-    if (fill > best_fill) {
-      best_fill = fill;
-      best = i;
-    }
-  }
-  return best;
-}
-
+// The float path is the rare one (a scale group boundary inside 16 columns, or a GPTQ group
+// index): one tile shape, two rows per warp and four warps per CTA, which measured best or
+// close to it on every shape tried when this kernel still served all tensors.
 template <int LAYOUT, int TM>
-qx_status launch_tokens(const CanonicalParams& p, int sm_count, cudaStream_t stream) {
-  const long long token_tiles = (p.m + TM - 1) / TM;
-  if constexpr (TM == 1) {
-    constexpr TileShape kShapes[4] = {{8, 8}, {4, 8}, {4, 4}, {2, 4}};
-    switch (pick_shape(kShapes, 4, p.rows, token_tiles, sm_count)) {
-      case 0: return launch_one<LAYOUT, TM, 8, 8>(p, stream);
-      case 1: return launch_one<LAYOUT, TM, 4, 8>(p, stream);
-      case 2: return launch_one<LAYOUT, TM, 4, 4>(p, stream);
-      default: return launch_one<LAYOUT, TM, 2, 4>(p, stream);
-    }
-  } else if constexpr (TM == 4) {
-    constexpr TileShape kShapes[3] = {{4, 8}, {4, 4}, {2, 4}};
-    switch (pick_shape(kShapes, 3, p.rows, token_tiles, sm_count)) {
-      case 0: return launch_one<LAYOUT, TM, 4, 8>(p, stream);
-      case 1: return launch_one<LAYOUT, TM, 4, 4>(p, stream);
-      default: return launch_one<LAYOUT, TM, 2, 4>(p, stream);
-    }
-  } else {
-    constexpr TileShape kShapes[2] = {{2, 8}, {2, 4}};
-    switch (pick_shape(kShapes, 2, p.rows, token_tiles, sm_count)) {
-      case 0: return launch_one<LAYOUT, TM, 2, 8>(p, stream);
-      default: return launch_one<LAYOUT, TM, 2, 4>(p, stream);
-    }
-  }
+qx_status launch_tokens(const CanonicalParams& p, int /*sm_count*/, cudaStream_t stream) {
+  return launch_one<LAYOUT, TM, 2, 4>(p, stream);
 }
 
 template <int LAYOUT>
