@@ -1,7 +1,9 @@
 """Generates golden_canonical.npz by RUNNING THE UNMODIFIED REFERENCE
 (oracle/_ref/libqx_ref.so): canonical kInt8Symmetric / kInt4Symmetric tensors made by the
 reference's quantize_canonical, and the outputs of its qgemm_prepacked_epilogue_storage for
-every storage type and activation.
+every storage type and activation; AWQ and GPTQ checkpoints (the fragments of the reference's
+importer test and seeded ones: V1, V2, symmetric, act-order) imported by the reference's
+import_awq_u4 / import_gptq_u4 and run through the same projection.
 
     python tests/golden/make_golden_canonical.py
 
