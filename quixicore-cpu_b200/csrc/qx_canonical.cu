@@ -906,7 +906,12 @@ __global__ void __launch_bounds__(256) canonical_row_digits_kernel(
   int8_t* out[kPlanes];
 #pragma unroll
   for (int d = 0; d < kPlanes; ++d) out[d] = planes + (d * chunk_tokens + token) * columns;
-  for (long long k = threadIdx.x; k < columns; k += 256) {
+  // a row's digits are written by gridDim.y CTAs, each its slice of the columns (every one of
+  // them has scanned the whole row for the envelope)
+  const long long slice = (columns + gridDim.y - 1) / gridDim.y;
+  const long long k_begin = blockIdx.y * slice;
+  const long long k_end = k_begin + slice < columns ? k_begin + slice : columns;
+  for (long long k = k_begin + threadIdx.x; k < k_end; k += 256) {
     int t = ok ? __float2int_rn(load_storage(x, x_type, base + k) * to_fixed) : 0;
 #pragma unroll
     for (int d = 0; d < kPlanes - 1; ++d) {
@@ -916,7 +921,7 @@ __global__ void __launch_bounds__(256) canonical_row_digits_kernel(
     }
     out[kPlanes - 1][k] = static_cast<int8_t>(t);
   }
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0 && blockIdx.y == 0) {
     float weight = e;
 #pragma unroll
     for (int d = 0; d < kPlanes; ++d) {
@@ -960,7 +965,11 @@ qx_status launch_prefill_int8(const CanonicalParams& p, uint8_t* scratch, int sm
   for (long long t0 = 0; t0 < p.m; t0 += chunk) {
     const long long tokens = p.m - t0 < chunk ? p.m - t0 : chunk;
     const uint8_t* x = static_cast<const uint8_t*>(p.x) + static_cast<size_t>(t0 * p.columns) * x_bytes;
-    canonical_row_digits_kernel<<<static_cast<unsigned>(tokens), 256, 0, stream>>>(
+    // few tokens: several CTAs per row, so that the kernel is not one serial loop per row
+    const long long wanted = (2LL * sm_count + tokens - 1) / tokens;
+    const long long most = (p.columns + 1023) / 1024;
+    const unsigned splits = static_cast<unsigned>(wanted < 1 ? 1 : (wanted > most ? most : (wanted > 16 ? 16 : wanted)));
+    canonical_row_digits_kernel<<<dim3(static_cast<unsigned>(tokens), splits), 256, 0, stream>>>(
         x, p.x_type, p.columns, chunk, planes, plane_scale);
     count_launch();
     QX_CUDA_TRY(cudaGetLastError());
